@@ -1,0 +1,156 @@
+/*
+ * libneura_cuda — C ABI of the B200 (sm_100a) quantized-linear path for Neura.
+ *
+ * The reference (formetaohy/Neura) has no FFI boundary of its own: its operator
+ * API for this path is `Graph::matmul` over a block-quantised parameter
+ * (crates/neura-graph/src/op.rs:17), executed by `Runtime::{open, load, write,
+ * run, read}` (crates/neura-runtime/src/runtime.rs:183,356,1020,833,1064) on a
+ * device heap that holds GGUF blocks verbatim (crates/neura-runtime/src/store.rs:77-157).
+ * Each entry point below names the reference item it stands in for; a thin Rust
+ * crate binds them one to one.
+ *
+ * Conventions
+ *  - every call returns int32_t: 0 = ok, negative = host-side refusal (the
+ *    sentence is in neura_cuda_last_error(), thread-local), positive = CUDA error code;
+ *  - pointers named *_dev are device pointers of the context's GPU, *_host are host pointers;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *  - a context is used by one host thread at a time and its calls share one
+ *    scratch area: work submitted through one context must be stream-ordered;
+ *  - the library never falls back to the CPU.
+ */
+#ifndef NEURA_CUDA_H
+#define NEURA_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element codes: discriminants of neura_abi::Element (crates/neura-abi/src/element.rs:3-17). */
+#define NC_ELEMENT_SINGLE 0u
+#define NC_ELEMENT_BFLOAT16 2u
+#define NC_ELEMENT_Q8_0 8u
+#define NC_ELEMENT_Q4K 9u
+
+/* How the blocks of a weight tensor are laid out in device memory. */
+#define NC_LAYOUT_GGUF 0u   /* verbatim GGUF: row after row, blocks in order (what store.rs:131-135 copies) */
+#define NC_LAYOUT_TILED 1u  /* neura_cuda_weight_seal output: same bytes, permuted per 16-row tile for the MMA kernels */
+
+/* Pointwise op codes of the fused epilogue: neura-pointwise declaration order
+ * (crates/neura-pointwise/src/op.rs:141-170). */
+#define NC_OP_ADD 0u
+#define NC_OP_MUL 1u
+#define NC_OP_SUB 2u
+#define NC_OP_DIV 3u
+#define NC_OP_MAXIMUM 4u
+#define NC_OP_MINIMUM 5u
+#define NC_OP_RELU 6u
+#define NC_OP_SQRT 7u
+#define NC_OP_RECIP 8u
+#define NC_OP_EXP 9u
+#define NC_OP_LOG 10u
+#define NC_OP_TANH 11u
+#define NC_OP_SIGMOID 12u
+#define NC_OP_NEG 13u
+#define NC_OP_ABS 14u
+#define NC_OP_IDENTITY 15u
+#define NC_OP_SIN 16u
+#define NC_OP_COS 17u
+#define NC_OP_POW 18u
+#define NC_OP_FLOOR 19u
+#define NC_OP_GELU 20u
+#define NC_OP_SILU 21u
+
+#define NC_MAX_STEPS 4u
+
+typedef struct nc_context nc_context;
+
+/* A weight matrix on the device: the subset of ValueRecord{base, element, dims, strides}
+ * (crates/neura-abi/src/record.rs:151-165) a linear layer needs.  `n` output
+ * features (GGUF ne[1]), `k` input features (GGUF ne[0], contiguous inside a row). */
+typedef struct nc_weight {
+    const void *data_dev;
+    uint32_t element; /* NC_ELEMENT_Q8_0 | NC_ELEMENT_Q4K */
+    uint32_t layout;  /* NC_LAYOUT_* */
+    uint32_t n;
+    uint32_t k;
+} nc_weight;
+
+/* One step of the fused epilogue: StepRecord{op, operand, swapped}
+ * (crates/neura-abi/src/record.rs:72-76), applied like `chained`
+ * (crates/neura-kernel/src/pointwise.rs:90-104).  The operand is read at the
+ * output coordinate through broadcast strides (in elements; 0 broadcasts). */
+typedef struct nc_step {
+    uint32_t op;
+    uint32_t swapped;         /* 1: the operand is the op's first argument */
+    const float *operand_dev; /* NULL for a unary op */
+    int64_t row_stride;
+    int64_t col_stride;
+} nc_step;
+
+/* Thread-local sentence for the last negative return (the reference panics with
+ * a sentence on host contract violations, e.g. store.rs:90-123). */
+const char *neura_cuda_last_error(void);
+
+/* Runtime::open (runtime.rs:183): binds the calling thread's work to one GPU and
+ * allocates the context's scratch (activation staging, split-tile partials). */
+int32_t neura_cuda_open(int32_t device, nc_context **out);
+int32_t neura_cuda_close(nc_context *ctx);
+
+/* Element::payload_bytes (element.rs:231-241); 0 for an element the path does not hold. */
+uint64_t neura_cuda_payload_bytes(uint32_t element, uint64_t elements);
+/* Bytes neura_cuda_weight_seal writes for an [n, k] matrix (rows padded to 16). */
+uint64_t neura_cuda_sealed_bytes(uint32_t element, uint32_t n, uint32_t k);
+
+/* Device memory and copies: GpuBuffer / Runtime::write / Runtime::read
+ * (crates/neura-gpu/src/buffer.rs:30-177, runtime.rs:1020,1064).  The copies are
+ * asynchronous on `stream`; neura_cuda_sync completes them (Run::complete, runtime.rs:123). */
+int32_t neura_cuda_alloc(nc_context *ctx, uint64_t bytes, void **out_dev);
+int32_t neura_cuda_free(nc_context *ctx, void *ptr_dev);
+int32_t neura_cuda_host_alloc(nc_context *ctx, uint64_t bytes, void **out_host); /* pinned */
+int32_t neura_cuda_host_free(nc_context *ctx, void *ptr_host);
+int32_t neura_cuda_write(nc_context *ctx, void *stream, void *dst_dev, const void *src_host, uint64_t bytes);
+int32_t neura_cuda_read(nc_context *ctx, void *stream, void *dst_host, const void *src_dev, uint64_t bytes);
+int32_t neura_cuda_sync(nc_context *ctx, void *stream);
+
+/* Grows the context's scratch ahead of time so that later linear calls of up to
+ * `rows` activation rows against matrices of up to [n, k] never allocate. */
+int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k);
+
+/* The load step after pour_one (store.rs:77-157): permutes a verbatim GGUF tensor
+ * into the tiled layout the MMA kernels stream.  Out of place; `dst_dev` holds
+ * neura_cuda_sealed_bytes().  Dequantised values are unchanged bit for bit. */
+int32_t neura_cuda_weight_seal(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k,
+                               const void *gguf_dev, void *dst_dev);
+
+/* unpack (crates/neura-precision/src/ggml.rs:22-38, q8_0_values :211-216,
+ * q4_k_values :336-350): out_dev[n*k] f32, bit-exact, for either layout. */
+int32_t neura_cuda_dequant(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev);
+
+/* pack (ggml.rs:8-20, q8_0 :201-209, affine_block :149-199) on the device, the
+ * counterpart of the reference's device packer (crates/neura-kernel/src/task/convert.rs:355-431):
+ * `elements` f32 (a multiple of the block) -> GGUF blocks, bit-exact with the host packer. */
+int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, const float *src_dev,
+                            uint64_t elements, void *dst_dev);
+
+/* run_matmul + chained (crates/neura-kernel/src/task/matmul.rs:376-517, pointwise.rs:90-104):
+ *   out[r*out_stride + c] = chain(sum_k W[c][k] * x[r*x_stride + k]),  r < rows, c < w->n
+ * f32 activations, f32 accumulation, f32 output (promote(Single, Q*) = Single, element.rs:306-323).
+ * Needs a NC_LAYOUT_TILED weight. */
+int32_t neura_cuda_linear(nc_context *ctx, void *stream, const nc_weight *w, const float *x_dev, uint32_t rows,
+                          uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
+                          uint32_t n_steps);
+
+/* The same product called the way Runtime::{write, run, read} are (runtime.rs:1020,833,1064):
+ * activations come from and results return to host memory; blocks until done. */
+int32_t neura_cuda_linear_host(nc_context *ctx, void *stream, const nc_weight *w, const float *x_host,
+                               uint32_t rows, float *out_host, const nc_step *chain, uint32_t n_steps);
+
+/* Kernel launches issued through this context since it was opened. */
+uint64_t neura_cuda_launches(const nc_context *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEURA_CUDA_H */

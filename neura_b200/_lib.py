@@ -1,0 +1,81 @@
+"""ctypes loader for libneura_cuda.so.  There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libneura_cuda.so")
+
+# every symbol include/neura_cuda.h declares
+SYMBOLS = [
+    "neura_cuda_last_error", "neura_cuda_open", "neura_cuda_close", "neura_cuda_payload_bytes",
+    "neura_cuda_sealed_bytes", "neura_cuda_alloc", "neura_cuda_free", "neura_cuda_host_alloc",
+    "neura_cuda_host_free", "neura_cuda_write", "neura_cuda_read", "neura_cuda_sync", "neura_cuda_reserve",
+    "neura_cuda_weight_seal", "neura_cuda_dequant", "neura_cuda_quantize", "neura_cuda_linear",
+    "neura_cuda_linear_host", "neura_cuda_launches",
+]
+
+
+class NcWeight(ctypes.Structure):
+    _fields_ = [
+        ("data_dev", ctypes.c_void_p),
+        ("element", ctypes.c_uint32),
+        ("layout", ctypes.c_uint32),
+        ("n", ctypes.c_uint32),
+        ("k", ctypes.c_uint32),
+    ]
+
+
+class NcStep(ctypes.Structure):
+    _fields_ = [
+        ("op", ctypes.c_uint32),
+        ("swapped", ctypes.c_uint32),
+        ("operand_dev", ctypes.c_void_p),
+        ("row_stride", ctypes.c_int64),
+        ("col_stride", ctypes.c_int64),
+    ]
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library (once) and declares the signatures of the C ABI."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m neura_b200.build` (nvcc, sm_100a); "
+            "this package has no other implementation of the path"
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    i32, u32, u64, p = ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
+    pp = ctypes.POINTER(ctypes.c_void_p)
+    sig = {
+        "neura_cuda_last_error": (ctypes.c_char_p, []),
+        "neura_cuda_open": (i32, [i32, pp]),
+        "neura_cuda_close": (i32, [p]),
+        "neura_cuda_payload_bytes": (u64, [u32, u64]),
+        "neura_cuda_sealed_bytes": (u64, [u32, u32, u32]),
+        "neura_cuda_alloc": (i32, [p, u64, pp]),
+        "neura_cuda_free": (i32, [p, p]),
+        "neura_cuda_host_alloc": (i32, [p, u64, pp]),
+        "neura_cuda_host_free": (i32, [p, p]),
+        "neura_cuda_write": (i32, [p, p, p, p, u64]),
+        "neura_cuda_read": (i32, [p, p, p, p, u64]),
+        "neura_cuda_sync": (i32, [p, p]),
+        "neura_cuda_reserve": (i32, [p, u32, u32, u32]),
+        "neura_cuda_weight_seal": (i32, [p, p, u32, u32, u32, p, p]),
+        "neura_cuda_dequant": (i32, [p, p, ctypes.POINTER(NcWeight), p]),
+        "neura_cuda_quantize": (i32, [p, p, u32, p, u64, p]),
+        "neura_cuda_linear": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, u64, p, u64, ctypes.POINTER(NcStep), u32]),
+        "neura_cuda_linear_host": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, p, ctypes.POINTER(NcStep), u32]),
+        "neura_cuda_launches": (u64, [p]),
+    }
+    for name in SYMBOLS:
+        fn = getattr(lib, name)  # raises AttributeError if the library does not export it
+        fn.restype, fn.argtypes = sig[name]
+    _lib = lib
+    return lib

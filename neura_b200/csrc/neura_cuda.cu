@@ -1,0 +1,419 @@
+// libneura_cuda: the extern "C" surface declared in include/neura_cuda.h.
+// Built for sm_100a only; there is no CPU path behind any entry point.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "common.cuh"
+#include "gemv_mma.cuh"
+#include "layout.cuh"
+#include "prep.cuh"
+#include "quantize.cuh"
+
+using namespace nc;
+
+namespace {
+
+thread_local std::string g_error;
+
+int32_t refuse(int32_t code, const char *fmt, ...) {
+    char text[512];
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(text, sizeof text, fmt, args);
+    va_end(args);
+    g_error = text;
+    return code;
+}
+
+int32_t cuda_refuse(cudaError_t e, const char *what) {
+    char text[512];
+    snprintf(text, sizeof text, "%s: %s", what, cudaGetErrorString(e));
+    g_error = text;
+    return (int32_t)e;
+}
+
+#define NC_CUDA(call)                                         \
+    do {                                                      \
+        cudaError_t e_ = (call);                              \
+        if (e_ != cudaSuccess) return cuda_refuse(e_, #call); \
+    } while (0)
+
+constexpr int32_t kBadArgument = -1;
+constexpr int32_t kBadState = -2;
+constexpr uint32_t kMaxRowsPerPass = 16;  // activation rows one GEMV launch carries
+
+struct Region {
+    void *ptr = nullptr;
+    uint64_t bytes = 0;
+};
+
+}  // namespace
+
+struct nc_context {
+    int device = 0;
+    int sms = 0;
+    Region dig, cs, partial, counters, stage_x, stage_out;
+    uint64_t launches = 0;
+};
+
+namespace {
+
+// Grows a scratch region (never shrinks).  Growing frees the old block, which
+// waits for the device: callers that cannot afford that call neura_cuda_reserve first.
+int32_t ensure(Region &region, uint64_t bytes, bool zero) {
+    if (region.bytes >= bytes) return 0;
+    if (region.ptr) NC_CUDA(cudaFree(region.ptr));
+    region.ptr = nullptr;
+    region.bytes = 0;
+    const uint64_t want = (bytes + 255) / 256 * 256;
+    NC_CUDA(cudaMalloc(&region.ptr, want));
+    if (zero) NC_CUDA(cudaMemset(region.ptr, 0, want));
+    region.bytes = want;
+    return 0;
+}
+
+uint32_t block_elements(uint32_t element) {
+    return element == NC_ELEMENT_Q8_0 ? kQ8Block : element == NC_ELEMENT_Q4K ? kSuperBlock : 0;
+}
+uint32_t block_bytes(uint32_t element) {
+    return element == NC_ELEMENT_Q8_0 ? kQ8Bytes : element == NC_ELEMENT_Q4K ? kQ4kBytes : 0;
+}
+
+struct GemvPlan {
+    uint32_t ntiles, upt, nwarps, q, r, maxp, blocks;
+};
+
+// The (q, r) split of gemv_mma.cuh for a grid that fills the GPU once.
+GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t k, int resident_blocks_per_sm) {
+    GemvPlan plan;
+    plan.ntiles = (n + kTileRows - 1) / kTileRows;
+    plan.upt = k / block_elements(element);
+    const uint64_t units = (uint64_t)plan.ntiles * plan.upt;
+    const uint64_t least = element == NC_ELEMENT_Q4K ? 2 : 8;  // units a warp should at least stream
+    uint64_t warps = (uint64_t)ctx->sms * resident_blocks_per_sm * 8;
+    if (warps > units / least) warps = units / least;
+    if (warps < 1) warps = 1;
+    plan.nwarps = (uint32_t)warps;
+    plan.q = (uint32_t)(units / warps);
+    plan.r = (uint32_t)(units % warps);
+    plan.maxp = (plan.upt + plan.q - 1) / plan.q + 1;
+    plan.blocks = (plan.nwarps + 7) / 8;
+    return plan;
+}
+
+template <int NT>
+int32_t launch_gemv(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
+    auto kernel = element == NC_ELEMENT_Q4K ? gemv_q4k_kernel<NT> : gemv_q8_0_kernel<NT>;
+    const size_t smem = 8 * 16 * (NT * 8 + 1) * sizeof(float);
+    int resident = 0;
+    NC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, 256, smem));
+    if (resident < 1) return refuse(kBadState, "the product kernel does not fit an SM");
+    if (resident > 4) resident = 4;
+    const GemvPlan plan = plan_gemv(ctx, element, n, k, resident);
+    const uint64_t cells = (uint64_t)p.rows * 16;
+    int32_t rc;
+    if ((rc = ensure(ctx->partial, (uint64_t)plan.ntiles * plan.maxp * cells * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx->counters, (uint64_t)plan.ntiles * sizeof(unsigned int), true))) return rc;
+    p.partial = (float *)ctx->partial.ptr;
+    p.counters = (unsigned int *)ctx->counters.ptr;
+    p.upt = plan.upt;
+    p.nwarps = plan.nwarps;
+    p.q = plan.q;
+    p.r = plan.r;
+    p.maxp = plan.maxp;
+    kernel<<<plan.blocks, 256, smem, stream>>>(p);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int32_t check_weight(const nc_weight *w) {
+    if (!w || !w->data_dev) return refuse(kBadArgument, "a product needs a weight on the device");
+    const uint32_t per = block_elements(w->element);
+    if (!per)
+        return refuse(kBadArgument, "element %u is not a block format this path multiplies (Q8_0 = 8, Q4K = 9)",
+                      w->element);
+    if (w->n == 0 || w->k == 0 || w->k % per)
+        return refuse(kBadArgument, "a [%u, %u] weight does not fill whole blocks of %u along its rows", w->n,
+                      w->k, per);
+    if ((uintptr_t)w->data_dev % 16)
+        return refuse(kBadArgument, "a weight starts on a 16-byte boundary");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *neura_cuda_last_error(void) { return g_error.c_str(); }
+
+int32_t neura_cuda_open(int32_t device, nc_context **out) {
+    if (!out) return refuse(kBadArgument, "open needs somewhere to put the context");
+    *out = nullptr;
+    int count = 0;
+    NC_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count)
+        return refuse(kBadArgument, "device %d is not one of the %d GPUs this process sees", device, count);
+    NC_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    NC_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return refuse(kBadState, "this library holds sm_100a code only and device %d is sm_%d%d", device, prop.major,
+                      prop.minor);
+    nc_context *ctx = new (std::nothrow) nc_context();
+    if (!ctx) return refuse(kBadState, "out of host memory");
+    ctx->device = device;
+    ctx->sms = prop.multiProcessorCount;
+    *out = ctx;
+    return 0;
+}
+
+int32_t neura_cuda_close(nc_context *ctx) {
+    if (!ctx) return 0;
+    cudaSetDevice(ctx->device);
+    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->partial, &ctx->counters, &ctx->stage_x, &ctx->stage_out})
+        if (region->ptr) cudaFree(region->ptr);
+    delete ctx;
+    return 0;
+}
+
+uint64_t neura_cuda_payload_bytes(uint32_t element, uint64_t elements) {
+    if (element == NC_ELEMENT_SINGLE) return elements * 4;
+    if (element == NC_ELEMENT_BFLOAT16) return elements * 2;
+    const uint32_t per = block_elements(element);
+    if (!per) return 0;
+    return (elements + per - 1) / per * block_bytes(element);
+}
+
+uint64_t neura_cuda_sealed_bytes(uint32_t element, uint32_t n, uint32_t k) {
+    const uint32_t per = block_elements(element);
+    if (!per || k % per) return 0;
+    const uint64_t padded = ((uint64_t)n + kTileRows - 1) / kTileRows * kTileRows;
+    return padded * (k / per) * block_bytes(element);
+}
+
+int32_t neura_cuda_alloc(nc_context *ctx, uint64_t bytes, void **out_dev) {
+    if (!ctx || !out_dev) return refuse(kBadArgument, "alloc needs a context and somewhere to put the pointer");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    NC_CUDA(cudaMalloc(out_dev, bytes ? bytes : 1));
+    return 0;
+}
+
+int32_t neura_cuda_free(nc_context *ctx, void *ptr_dev) {
+    if (!ctx) return refuse(kBadArgument, "free needs a context");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    NC_CUDA(cudaFree(ptr_dev));
+    return 0;
+}
+
+int32_t neura_cuda_host_alloc(nc_context *ctx, uint64_t bytes, void **out_host) {
+    if (!ctx || !out_host) return refuse(kBadArgument, "host_alloc needs a context and somewhere to put the pointer");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    NC_CUDA(cudaMallocHost(out_host, bytes ? bytes : 1));
+    return 0;
+}
+
+int32_t neura_cuda_host_free(nc_context *ctx, void *ptr_host) {
+    if (!ctx) return refuse(kBadArgument, "host_free needs a context");
+    NC_CUDA(cudaFreeHost(ptr_host));
+    return 0;
+}
+
+int32_t neura_cuda_write(nc_context *ctx, void *stream, void *dst_dev, const void *src_host, uint64_t bytes) {
+    if (!ctx || (bytes && (!dst_dev || !src_host))) return refuse(kBadArgument, "write needs both ends of the copy");
+    NC_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return 0;
+}
+
+int32_t neura_cuda_read(nc_context *ctx, void *stream, void *dst_host, const void *src_dev, uint64_t bytes) {
+    if (!ctx || (bytes && (!dst_host || !src_dev))) return refuse(kBadArgument, "read needs both ends of the copy");
+    NC_CUDA(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return 0;
+}
+
+int32_t neura_cuda_sync(nc_context *ctx, void *stream) {
+    if (!ctx) return refuse(kBadArgument, "sync needs a context");
+    NC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return 0;
+}
+
+int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k) {
+    if (!ctx || !rows || !n || !k) return refuse(kBadArgument, "reserve needs a context and a shape");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    const uint32_t pass = rows < kMaxRowsPerPass ? rows : kMaxRowsPerPass;
+    const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
+    int32_t rc;
+    if ((rc = ensure(ctx->dig, kpad * 3 * pass, false))) return rc;
+    if ((rc = ensure(ctx->cs, kpad / 32 * 3 * pass * sizeof(float), false))) return rc;
+    // partial sums: the widest split is one unit per warp and two warps per tile ... bounded by the
+    // plan for the narrowest block (32), computed with the resident grid of the largest kernel
+    const uint32_t ntiles = (n + kTileRows - 1) / kTileRows;
+    for (uint32_t element : {NC_ELEMENT_Q8_0, NC_ELEMENT_Q4K}) {
+        if (k % block_elements(element)) continue;
+        for (int resident = 1; resident <= 4; ++resident) {
+            const GemvPlan plan = plan_gemv(ctx, element, n, k, resident);
+            if ((rc = ensure(ctx->partial, (uint64_t)plan.ntiles * plan.maxp * pass * 16 * sizeof(float), false)))
+                return rc;
+        }
+    }
+    if ((rc = ensure(ctx->counters, (uint64_t)ntiles * sizeof(unsigned int), true))) return rc;
+    if ((rc = ensure(ctx->stage_x, (uint64_t)rows * k * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx->stage_out, (uint64_t)rows * n * sizeof(float), false))) return rc;
+    return 0;
+}
+
+int32_t neura_cuda_weight_seal(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k,
+                               const void *gguf_dev, void *dst_dev) {
+    if (!ctx || !gguf_dev || !dst_dev) return refuse(kBadArgument, "seal needs a context, a source and a destination");
+    const uint32_t per = block_elements(element);
+    if (!per || !n || !k || k % per)
+        return refuse(kBadArgument, "a [%u, %u] tensor of element %u is not whole blocks this path seals", n, k, element);
+    if ((uintptr_t)gguf_dev % (element == NC_ELEMENT_Q4K ? 8 : 2) || (uintptr_t)dst_dev % 16)
+        return refuse(kBadArgument, "seal reads an 8-byte aligned tensor and writes a 16-byte aligned one");
+    const uint64_t bytes = neura_cuda_sealed_bytes(element, n, k);
+    const uint64_t granules = element == NC_ELEMENT_Q4K ? bytes / 8 : bytes / 2;
+    const uint64_t want = (granules + 255) / 256;
+    const unsigned int blocks = (unsigned int)(want < (uint64_t)ctx->sms * 32 ? want : (uint64_t)ctx->sms * 32);
+    if (element == NC_ELEMENT_Q4K)
+        seal_q4k_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)gguf_dev, (uint8_t *)dst_dev, n,
+                                                                  k / per, granules);
+    else
+        seal_q8_0_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)gguf_dev, (uint8_t *)dst_dev, n,
+                                                                   k / per, granules);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int32_t neura_cuda_dequant(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev) {
+    if (!ctx || !out_dev) return refuse(kBadArgument, "dequant needs a context and a destination");
+    int32_t rc;
+    if ((rc = check_weight(w))) return rc;
+    if (w->layout != NC_LAYOUT_GGUF && w->layout != NC_LAYOUT_TILED)
+        return refuse(kBadArgument, "layout %u is neither the GGUF nor the tiled order", w->layout);
+    WeightView view{(const uint8_t *)w->data_dev, w->element, w->layout, w->n, w->k};
+    const uint64_t total = (uint64_t)w->n * w->k;
+    const uint64_t want = (total + 255) / 256;
+    const unsigned int blocks = (unsigned int)(want < (uint64_t)ctx->sms * 32 ? want : (uint64_t)ctx->sms * 32);
+    dequant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(view, out_dev);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, const float *src_dev,
+                            uint64_t elements, void *dst_dev) {
+    if (!ctx || !src_dev || !dst_dev) return refuse(kBadArgument, "quantize needs a context, a source and a destination");
+    const uint32_t per = block_elements(element);
+    if (!per || !elements || elements % per)
+        return refuse(kBadArgument, "%llu numbers do not fill whole blocks of element %u",
+                      (unsigned long long)elements, element);
+    if ((uintptr_t)dst_dev % 2 || (uintptr_t)src_dev % 4)
+        return refuse(kBadArgument, "quantize reads 4-byte aligned numbers and writes 2-byte aligned blocks");
+    const uint64_t blocks = elements / per;
+    const uint64_t want = (blocks + 7) / 8;
+    const unsigned int grid = (unsigned int)(want < (uint64_t)ctx->sms * 16 ? want : (uint64_t)ctx->sms * 16);
+    if (element == NC_ELEMENT_Q8_0)
+        quantize_q8_0_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(src_dev, (uint8_t *)dst_dev, blocks);
+    else
+        quantize_q4k_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(src_dev, (uint8_t *)dst_dev, blocks);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_dev, uint32_t rows,
+                          uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
+                          uint32_t n_steps) {
+    if (!ctx || !x_dev || !out_dev) return refuse(kBadArgument, "a product needs a context, activations and an output");
+    int32_t rc;
+    if ((rc = check_weight(w))) return rc;
+    if (w->layout != NC_LAYOUT_TILED)
+        return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order");
+    if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
+    if (x_stride < w->k || out_stride < w->n)
+        return refuse(kBadArgument, "rows of %u activations and %u outputs overlap at strides %llu and %llu", w->k, w->n,
+                      (unsigned long long)x_stride, (unsigned long long)out_stride);
+    if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
+        return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
+    if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const uint32_t granule = w->element == NC_ELEMENT_Q4K ? 256 : 32;
+    const uint64_t kpad = ((uint64_t)w->k + 255) / 256 * 256;
+
+    for (uint32_t first = 0; first < rows; first += kMaxRowsPerPass) {
+        const uint32_t pass = rows - first < kMaxRowsPerPass ? rows - first : kMaxRowsPerPass;
+        const uint32_t ncols = pass * 3;
+        if ((rc = ensure(ctx->dig, kpad * ncols, false))) return rc;
+        if ((rc = ensure(ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
+
+        PrepParams prep;
+        prep.x = x_dev + (uint64_t)first * x_stride;
+        prep.x_stride = x_stride;
+        prep.dig = (int8_t *)ctx->dig.ptr;
+        prep.cs = (float *)ctx->cs.ptr;
+        prep.rows = pass;
+        prep.k = w->k;
+        prep.ncols = ncols;
+        prep.granule = granule;
+        prep.vector = ((uintptr_t)prep.x % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
+        const uint64_t prep_warps = (uint64_t)pass * (kpad / 256);
+        prep_kernel<<<(unsigned int)((prep_warps + 3) / 4), 128, 0, stream>>>(prep);
+        ctx->launches++;
+        NC_CUDA(cudaGetLastError());
+
+        GemvParams p;
+        memset(&p, 0, sizeof p);
+        p.w = (const uint8_t *)w->data_dev;
+        p.dig = prep.dig;
+        p.cs = prep.cs;
+        p.out = out_dev + (uint64_t)first * out_stride;
+        p.out_stride = out_stride;
+        p.n = w->n;
+        p.rows = pass;
+        p.ncols = ncols;
+        p.chain.n = n_steps;
+        for (uint32_t s = 0; s < n_steps; ++s) {
+            p.chain.step[s] = chain[s];
+            if (chain[s].operand_dev)  // the operand is read at this pass's rows
+                p.chain.step[s].operand_dev = chain[s].operand_dev + (int64_t)first * chain[s].row_stride;
+        }
+        const int nt = (int)((ncols + 7) / 8);
+        switch (nt) {
+        case 1: rc = launch_gemv<1>(ctx, stream, w->element, p, w->n, w->k); break;
+        case 2: rc = launch_gemv<2>(ctx, stream, w->element, p, w->n, w->k); break;
+        case 3: rc = launch_gemv<3>(ctx, stream, w->element, p, w->n, w->k); break;
+        case 4: rc = launch_gemv<4>(ctx, stream, w->element, p, w->n, w->k); break;
+        case 5: rc = launch_gemv<5>(ctx, stream, w->element, p, w->n, w->k); break;
+        default: rc = launch_gemv<6>(ctx, stream, w->element, p, w->n, w->k); break;
+        }
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+int32_t neura_cuda_linear_host(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_host,
+                               uint32_t rows, float *out_host, const nc_step *chain, uint32_t n_steps) {
+    if (!ctx || !x_host || !out_host) return refuse(kBadArgument, "a product needs a context, activations and an output");
+    int32_t rc;
+    if ((rc = check_weight(w))) return rc;
+    if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const uint64_t x_bytes = (uint64_t)rows * w->k * sizeof(float), out_bytes = (uint64_t)rows * w->n * sizeof(float);
+    if ((rc = ensure(ctx->stage_x, x_bytes, false))) return rc;
+    if ((rc = ensure(ctx->stage_out, out_bytes, false))) return rc;
+    NC_CUDA(cudaMemcpyAsync(ctx->stage_x.ptr, x_host, x_bytes, cudaMemcpyHostToDevice, stream));
+    if ((rc = neura_cuda_linear(ctx, stream_, w, (const float *)ctx->stage_x.ptr, rows, w->k,
+                                (float *)ctx->stage_out.ptr, w->n, chain, n_steps)))
+        return rc;
+    NC_CUDA(cudaMemcpyAsync(out_host, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, stream));
+    NC_CUDA(cudaStreamSynchronize(stream));
+    return 0;
+}
+
+uint64_t neura_cuda_launches(const nc_context *ctx) { return ctx ? ctx->launches : 0; }
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+// Activation staging for the integer-MMA product.
+//
+// The decode product keeps f32 activations (the reference never quantises them,
+// crates/neura-kernel/src/dot.rs:583-619), but a scalar f32 FMA per weight cannot keep
+// up with HBM3e on B200 (about three issue slots per Q4_K weight at 6.5 TB/s).  So the
+// activations are rewritten once per call as block fixed point: inside each exponent
+// granule (256 elements for Q4_K, 32 for Q8_0) x = v * 2^-s with |v| < 2^22, and the
+// integer v is split into three balanced base-256 digits v = d0 + 256 d1 + 65536 d2,
+// each an int8.  Digit planes are columns of the s8 MMA operand; the integer dot
+// products are exact, so the result differs from a sequential f32 sum only by the
+// 2^-23 (relative to the granule's peak) rounding of v and by f32 accumulation order.
+//
+//   dig[kb][col][32]   int8, kb = 32-element block of K, col = 3*row + digit, natural element order
+//   cs[gi][col]        f32 2^-s * 256^digit, gi = exponent granule of K
+#pragma once
+#include "common.cuh"
+
+namespace nc {
+
+struct PrepParams {
+    const float *x;     // [rows][x_stride]
+    uint64_t x_stride;
+    int8_t *dig;
+    float *cs;
+    uint32_t rows, k, ncols;
+    uint32_t granule;   // 256 or 32
+    uint32_t vector;    // 1: rows start 16-byte aligned, so a lane may fetch float4
+};
+
+// One warp per (row, 256-element chunk): lane l owns elements [8l, 8l+8) of the chunk.
+__global__ void prep_kernel(const __grid_constant__ PrepParams p) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t chunks = (p.k + 255) / 256;
+    const uint64_t total = (uint64_t)p.rows * chunks;
+    const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    for (uint64_t w = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total; w += warps) {
+        const uint32_t row = (uint32_t)(w / chunks), chunk = (uint32_t)(w % chunks);
+        const uint32_t at = chunk * 256 + lane * 8;
+        const bool live = at < p.k;  // k is a multiple of 32, so a lane is live or dead as a whole
+        float v[8];
+        float peak = 0.0f;
+        bool odd = false;  // an inf or a nan among this lane's numbers
+        if (live) {
+            const float *from = p.x + (uint64_t)row * p.x_stride + at;
+            if (p.vector) {
+                const float4 a = *reinterpret_cast<const float4 *>(from);
+                const float4 b = *reinterpret_cast<const float4 *>(from + 4);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+                v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = from[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                peak = fmaxf(peak, fabsf(v[i]));
+                odd |= !(fabsf(v[i]) <= 3.0e38f);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        }
+        // granule peak: 4 lanes share a 32-block, the warp shares the 256-chunk
+        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 1));
+        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 2));
+        if (p.granule == 256) {
+            peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 4));
+            peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 8));
+            peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 16));
+        }
+        // peak < 2^e  ->  |x * 2^(22-e)| < 2^22
+        int s = 0;
+        float unscale = 1.0f;
+        const uint32_t vote = __ballot_sync(0xffffffffu, odd);
+        const bool finite = p.granule == 256 ? vote == 0u : ((vote >> (lane & ~3u)) & 0xfu) == 0u;
+        if (peak > 0.0f && finite) {
+            int e;
+            frexpf(peak, &e);
+            s = min(max(22 - e, -100), 120);
+            unscale = ldexpf(1.0f, -s);
+        }
+        if (!finite) unscale = __int_as_float(0x7fc00000);  // the product of this granule reads as nan
+        if (!live) continue;
+        const float up = ldexpf(1.0f, s);
+        uint32_t d[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            int q = finite ? __float2int_rn(v[i] * up) : 0;
+            const int d0 = (int)(int8_t)(q & 255);
+            q = (q - d0) >> 8;
+            const int d1 = (int)(int8_t)(q & 255);
+            const int d2 = (q - d1) >> 8;
+            d[0][i >> 2] |= (uint32_t)(d0 & 255) << (8 * (i & 3));
+            d[1][i >> 2] |= (uint32_t)(d1 & 255) << (8 * (i & 3));
+            d[2][i >> 2] |= (uint32_t)(d2 & 255) << (8 * (i & 3));
+        }
+        const uint32_t kb = chunk * 8 + (lane >> 2);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const uint32_t col = row * 3 + j;
+            *reinterpret_cast<uint2 *>(p.dig + ((uint64_t)kb * p.ncols + col) * 32 + (lane & 3) * 8) =
+                make_uint2(d[j][0], d[j][1]);
+        }
+        const bool writes = p.granule == 256 ? lane == 0 : (lane & 3) == 0;
+        if (writes) {
+            const uint32_t gi = p.granule == 256 ? chunk : kb;
+            float c = unscale;
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                p.cs[(uint64_t)gi * p.ncols + row * 3 + j] = c;
+                c *= 256.0f;
+            }
+        }
+    }
+}
+
+}  // namespace nc

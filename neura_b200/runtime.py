@@ -1,0 +1,261 @@
+"""Host-side mirror of the reference's runtime surface for the quantized-linear path.
+
+The reference drives this path through ``Runtime::{open, load, write, run, read}``
+(crates/neura-runtime/src/runtime.rs:183,356,1020,833,1064) with weights poured
+verbatim from a GGUF (crates/neura-runtime/src/store.rs:77-157) and products
+declared by ``Graph::matmul`` over ``decoder::matrix`` parameters
+(crates/neura-graph/src/op.rs:17, crates/neura-decoder/src/parameter.rs:5-41).
+This module keeps those names and argument meanings over the C ABI of
+``libneura_cuda``; host contract violations raise ``NeuraCudaError`` with the
+library's sentence where the reference panics with one.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Iterable, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import NcStep, NcWeight
+
+SINGLE, BFLOAT16, Q8_0, Q4K = 0, 2, 8, 9
+LAYOUT_GGUF, LAYOUT_TILED = 0, 1
+
+# neura-pointwise op codes (crates/neura-pointwise/src/op.rs:141-170)
+ADD, MUL, SUB, DIV, MAXIMUM, MINIMUM, RELU, SQRT, RECIP, EXP = range(10)
+LOG, TANH, SIGMOID, NEG, ABS, IDENTITY, SIN, COS, POW, FLOOR, GELU, SILU = range(10, 22)
+
+_BLOCK = {Q8_0: (32, 34), Q4K: (256, 144)}
+
+
+class NeuraCudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise NeuraCudaError(code, _lib.load().neura_cuda_last_error().decode("utf-8", "replace"))
+
+
+def payload_bytes(element: int, elements: int) -> int:
+    """Element::payload_bytes (crates/neura-abi/src/element.rs:231-241)."""
+    return int(_lib.load().neura_cuda_payload_bytes(element, elements))
+
+
+@dataclass
+class DeviceTensor:
+    """A run of f32 (or raw bytes) in device memory owned by a Runtime."""
+    ptr: int
+    nbytes: int
+    shape: tuple
+
+    @property
+    def rows(self) -> int:
+        return int(np.prod(self.shape[:-1])) if len(self.shape) > 1 else 1
+
+
+@dataclass
+class Weight:
+    """A sealed [n, k] block-quantised matrix: what ``decoder::matrix`` declares and ``load`` pours."""
+    ptr: int
+    element: int
+    layout: int
+    n: int
+    k: int
+    nbytes: int
+
+    def record(self) -> NcWeight:
+        return NcWeight(self.ptr, self.element, self.layout, self.n, self.k)
+
+
+@dataclass
+class Step:
+    """One epilogue step (StepRecord, crates/neura-abi/src/record.rs:72-76)."""
+    op: int
+    operand: Optional[DeviceTensor] = None
+    swapped: bool = False
+    row_stride: Optional[int] = None
+    col_stride: Optional[int] = None
+
+
+class Runtime:
+    """One GPU, one stream of work: the role of neura_runtime::Runtime for this path."""
+
+    def __init__(self, device: int = 0, stream: int = 0):
+        self._lib = _lib.load()
+        handle = ctypes.c_void_p()
+        _check(self._lib.neura_cuda_open(device, ctypes.byref(handle)))
+        self._ctx = handle
+        self.device = device
+        self.stream = ctypes.c_void_p(stream)
+        self._owned: list[int] = []
+
+    # -- lifetime ---------------------------------------------------------------
+    def close(self) -> None:
+        if self._ctx:
+            for ptr in self._owned:
+                self._lib.neura_cuda_free(self._ctx, ctypes.c_void_p(ptr))
+            self._owned.clear()
+            self._lib.neura_cuda_close(self._ctx)
+            self._ctx = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- memory -----------------------------------------------------------------
+    def alloc(self, nbytes: int) -> int:
+        out = ctypes.c_void_p()
+        _check(self._lib.neura_cuda_alloc(self._ctx, nbytes, ctypes.byref(out)))
+        self._owned.append(out.value)
+        return out.value
+
+    def free(self, ptr: int) -> None:
+        self._owned.remove(ptr)
+        _check(self._lib.neura_cuda_free(self._ctx, ctypes.c_void_p(ptr)))
+
+    def tensor(self, *shape: int) -> DeviceTensor:
+        nbytes = int(np.prod(shape)) * 4
+        return DeviceTensor(self.alloc(nbytes), nbytes, tuple(shape))
+
+    def write(self, tensor: DeviceTensor, values: np.ndarray) -> None:
+        """Runtime::write (runtime.rs:1020): host numbers into a device value."""
+        values = np.ascontiguousarray(values)
+        if values.nbytes != tensor.nbytes:
+            raise ValueError(f"writing {values.nbytes} bytes into a value of {tensor.nbytes}")
+        _check(self._lib.neura_cuda_write(self._ctx, self.stream, ctypes.c_void_p(tensor.ptr),
+                                          ctypes.c_void_p(values.ctypes.data), values.nbytes))
+        self.sync()  # `values` may be pageable and short-lived
+
+    def read(self, tensor: DeviceTensor, dtype=np.float32) -> np.ndarray:
+        """Runtime::read (runtime.rs:1064): blocking readback."""
+        out = np.empty(tensor.nbytes // np.dtype(dtype).itemsize, dtype=dtype)
+        _check(self._lib.neura_cuda_read(self._ctx, self.stream, ctypes.c_void_p(out.ctypes.data),
+                                         ctypes.c_void_p(tensor.ptr), tensor.nbytes))
+        self.sync()
+        return out.reshape(tensor.shape) if dtype == np.float32 else out
+
+    def sync(self) -> None:
+        _check(self._lib.neura_cuda_sync(self._ctx, self.stream))
+
+    def reserve(self, rows: int, n: int, k: int) -> None:
+        _check(self._lib.neura_cuda_reserve(self._ctx, rows, n, k))
+
+    @property
+    def launches(self) -> int:
+        return int(self._lib.neura_cuda_launches(self._ctx))
+
+    # -- weights ----------------------------------------------------------------
+    def upload(self, data: np.ndarray) -> DeviceTensor:
+        data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        t = DeviceTensor(self.alloc(max(16, data.nbytes)), data.nbytes, (data.nbytes,))
+        _check(self._lib.neura_cuda_write(self._ctx, self.stream, ctypes.c_void_p(t.ptr),
+                                          ctypes.c_void_p(data.ctypes.data), data.nbytes))
+        self.sync()
+        return t
+
+    def load(self, element: int, n: int, k: int, gguf_bytes: np.ndarray, seal: bool = True) -> Weight:
+        """Runtime::load for one tensor: pours the GGUF payload verbatim (store.rs:131-135)
+        and seals it into the tiled layout.  The GGUF shape contract is decoder::matrix's:
+        ne[0] = k (columns), ne[1] = n (rows) (crates/neura-decoder/src/parameter.rs:7-13)."""
+        if element not in _BLOCK:
+            raise NeuraCudaError(-1, f"element {element} is not a block format this path loads")
+        per, _ = _BLOCK[element]
+        if k % per:
+            raise NeuraCudaError(-1, f"rows of {k} numbers do not fill whole blocks of {per}")
+        need = payload_bytes(element, n * k)
+        data = np.ascontiguousarray(gguf_bytes).view(np.uint8).reshape(-1)
+        if data.size < need:
+            raise NeuraCudaError(-1, f"a [{n}, {k}] tensor packs {need} bytes and the source holds {data.size}")
+        raw = self.upload(data[:need])
+        if not seal:
+            return Weight(raw.ptr, element, LAYOUT_GGUF, n, k, need)
+        sealed = self.seal_device(element, n, k, raw.ptr)
+        self.sync()
+        self.free(raw.ptr)
+        return sealed
+
+    def seal_device(self, element: int, n: int, k: int, gguf_ptr: int) -> Weight:
+        nbytes = int(self._lib.neura_cuda_sealed_bytes(element, n, k))
+        dst = self.alloc(nbytes)
+        _check(self._lib.neura_cuda_weight_seal(self._ctx, self.stream, element, n, k,
+                                                ctypes.c_void_p(gguf_ptr), ctypes.c_void_p(dst)))
+        return Weight(dst, element, LAYOUT_TILED, n, k, nbytes)
+
+    def dequant(self, weight: Weight) -> np.ndarray:
+        """unpack (crates/neura-precision/src/lib.rs:25) run on the device: [n, k] f32."""
+        out = self.tensor(weight.n, weight.k)
+        rec = weight.record()
+        _check(self._lib.neura_cuda_dequant(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(out.ptr)))
+        values = self.read(out)
+        self.free(out.ptr)
+        return values
+
+    def quantize(self, element: int, values: np.ndarray) -> np.ndarray:
+        """pack (crates/neura-precision/src/lib.rs:5) run on the device: GGUF block bytes."""
+        values = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+        src = self.tensor(values.size)
+        self.write(src, values)
+        nbytes = payload_bytes(element, values.size)
+        dst = DeviceTensor(self.alloc(nbytes), nbytes, (nbytes,))
+        _check(self._lib.neura_cuda_quantize(self._ctx, self.stream, element, ctypes.c_void_p(src.ptr),
+                                             values.size, ctypes.c_void_p(dst.ptr)))
+        out = self.read(dst, dtype=np.uint8)
+        self.free(src.ptr)
+        self.free(dst.ptr)
+        return out
+
+    # -- the product ------------------------------------------------------------
+    @staticmethod
+    def _steps(chain: Optional[Sequence[Step]], n: int):
+        chain = list(chain or [])
+        arr = (NcStep * max(1, len(chain)))()
+        for i, step in enumerate(chain):
+            arr[i].op = step.op
+            arr[i].swapped = int(step.swapped)
+            if step.operand is None:
+                arr[i].operand_dev, arr[i].row_stride, arr[i].col_stride = None, 0, 0
+                continue
+            shape = step.operand.shape
+            rows = int(np.prod(shape[:-1])) if len(shape) > 1 else 1
+            cols = shape[-1]
+            if cols not in (1, n):
+                raise NeuraCudaError(-1, f"an operand of {cols} columns does not broadcast over {n}")
+            arr[i].operand_dev = step.operand.ptr
+            arr[i].row_stride = step.row_stride if step.row_stride is not None else (cols if rows > 1 else 0)
+            arr[i].col_stride = step.col_stride if step.col_stride is not None else (1 if cols > 1 else 0)
+        return arr, len(chain)
+
+    def linear(self, weight: Weight, x: DeviceTensor, out: DeviceTensor, chain: Optional[Sequence[Step]] = None,
+               rows: Optional[int] = None) -> None:
+        """graph.matmul(x, permute(W)) plus the fused chain, on device values (asynchronous)."""
+        rows = rows if rows is not None else x.rows
+        arr, count = self._steps(chain, weight.n)
+        rec = weight.record()
+        _check(self._lib.neura_cuda_linear(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(x.ptr), rows,
+                                           x.shape[-1], ctypes.c_void_p(out.ptr), out.shape[-1], arr, count))
+
+    def linear_host(self, weight: Weight, x: np.ndarray, chain: Optional[Sequence[Step]] = None,
+                    out: Optional[np.ndarray] = None) -> np.ndarray:
+        """write + run + read in one call: host activations in, host results out."""
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, weight.k)
+        if out is None:
+            out = np.empty((x.shape[0], weight.n), dtype=np.float32)
+        arr, count = self._steps(chain, weight.n)
+        rec = weight.record()
+        _check(self._lib.neura_cuda_linear_host(self._ctx, self.stream, ctypes.byref(rec),
+                                                ctypes.c_void_p(x.ctypes.data), x.shape[0],
+                                                ctypes.c_void_p(out.ctypes.data), arr, count))
+        return out

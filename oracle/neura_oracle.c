@@ -1,0 +1,519 @@
+/*
+ * CPU oracle for the quantized-linear path of Neura (test infrastructure only).
+ *
+ * This file is a plain-C restatement of the reference's host arithmetic for the
+ * path "GGUF block pack/unpack -> linear layer product -> fused pointwise
+ * epilogue".  It exists so that the CUDA library can be checked against it; no
+ * product code calls into it.  Every function cites the reference file it
+ * follows (paths are relative to the reference's repository root).
+ *
+ * Parity status: the block *layouts* are pinned (block byte counts from
+ * crates/neura-abi/tests/layout.rs:148-158, the Q4_K walk by three independent
+ * restatements inside the reference, and by the published GGML layout).  The
+ * *quantiser* (which nibble/int8 code a float becomes) is "parity unpinned":
+ * the reference holds no known-answer test for Q8_0 or Q4_K bytes and cannot be
+ * compiled here (no Rust toolchain), so the quantiser follows the reference's
+ * source by reading only.
+ *
+ * Build: see oracle/Makefile (gcc -O2 -ffp-contract=off: the reference's Rust
+ * never contracts a*b+c into an fma, so neither may this file).
+ */
+#include <math.h>
+#include <float.h>
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define NRO_SINGLE 0u
+#define NRO_Q8_0 8u /* crates/neura-abi/src/element.rs:3-17 (enum discriminants) */
+#define NRO_Q4K 9u
+
+#define QUANT_BLOCK 32      /* element.rs:35 */
+#define SUPER_BLOCK 256     /* element.rs:36 */
+#define SUPER_SUB_BLOCK 32  /* element.rs:37 */
+#define SUPER_SCALE_BYTES 12 /* element.rs:40 */
+#define Q8_0_BYTES 34       /* element.rs:155-158: 2 + 32 */
+#define Q4K_BYTES 144       /* element.rs:159-162: 4 + 12 + 128 */
+
+/* ------------------------------------------------------------------ */
+/* IEEE binary16 <-> binary32, round-to-nearest-even, subnormals kept. */
+/* The reference calls crate `half` 2.7.1 (Cargo.lock:98-99) at        */
+/* crates/neura-precision/src/ggml.rs:75,79,410; this restates the     */
+/* published IEEE 754 conversion that crate implements.                */
+/* ------------------------------------------------------------------ */
+static uint32_t f32_bits(float v) { uint32_t b; memcpy(&b, &v, 4); return b; }
+static float bits_f32(uint32_t b) { float v; memcpy(&v, &b, 4); return v; }
+
+uint16_t nro_f32_to_f16(float value) {
+    uint32_t x = f32_bits(value);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t mag = x & 0x7fffffffu;
+    if (mag >= 0x7f800000u) { /* inf / nan */
+        if (mag > 0x7f800000u) return (uint16_t)(sign | 0x7e00u | ((mag >> 13) & 0x3ffu));
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (mag >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u); /* rounds to inf: >= 65520 */
+    if (mag < 0x38800000u) { /* below 2^-14: subnormal half or zero */
+        if (mag < 0x33000000u) return (uint16_t)sign; /* < 2^-25 rounds to zero */
+        uint32_t exp = mag >> 23;
+        uint32_t man = (mag & 0x7fffffu) | 0x800000u;
+        uint32_t shift = 126u - exp; /* 14..24 */
+        uint32_t half = man >> shift;
+        uint32_t rest = man & ((1u << shift) - 1u);
+        uint32_t mid = 1u << (shift - 1u);
+        if (rest > mid || (rest == mid && (half & 1u))) half++;
+        return (uint16_t)(sign | half);
+    }
+    uint32_t half = ((mag >> 13) - (112u << 10));
+    uint32_t rest = mag & 0x1fffu;
+    if (rest > 0x1000u || (rest == 0x1000u && (half & 1u))) half++;
+    return (uint16_t)(sign | half);
+}
+
+float nro_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    if (exp == 0) {
+        if (man == 0) return bits_f32(sign);
+        float v = (float)man * (1.0f / 16777216.0f); /* man * 2^-24, exact */
+        return sign ? -v : v;
+    }
+    if (exp == 31) return bits_f32(sign | 0x7f800000u | (man << 13));
+    return bits_f32(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* crates/neura-precision/src/lib.rs:325-329 */
+uint16_t nro_bf16_rne(float value) {
+    uint32_t bits = f32_bits(value);
+    uint32_t rounded = bits + (0x7fffu + ((bits >> 16) & 1u));
+    return (uint16_t)(rounded >> 16);
+}
+
+float nro_bf16_to_f32(uint16_t h) { return bits_f32((uint32_t)h << 16); }
+
+/* ------------------------------------------------------------------ */
+/* PRNG: crates/neura-graph/src/init.rs:86-96                          */
+/* ------------------------------------------------------------------ */
+static float unit(uint32_t *entropy) {
+    *entropy ^= *entropy << 13;
+    *entropy ^= *entropy >> 17;
+    *entropy ^= *entropy << 5;
+    return (float)(*entropy >> 8) / (float)(1u << 24);
+}
+
+static float normal(uint32_t *entropy) {
+    float u = unit(entropy);
+    if (!(u > FLT_MIN)) u = FLT_MIN; /* f32::max(MIN_POSITIVE) */
+    float radius = sqrtf(-2.0f * logf(u));
+    return radius * cosf(6.28318530717958647692f * unit(entropy));
+}
+
+/* Init::Uniform{low,high}.samples (init.rs:63-70); the state is read and
+ * written back so that consecutive tensors can share one stream. */
+void nro_uniform(uint32_t *entropy, float low, float high, uint64_t count, float *out) {
+    for (uint64_t i = 0; i < count; ++i) out[i] = low + (high - low) * unit(entropy);
+}
+
+/* Init::Normal{mean,deviation}.samples (init.rs:71-79) */
+void nro_normal(uint32_t *entropy, float mean, float deviation, uint64_t count, float *out) {
+    for (uint64_t i = 0; i < count; ++i) out[i] = mean + deviation * normal(entropy);
+}
+
+/* ------------------------------------------------------------------ */
+/* Block geometry: crates/neura-abi/src/element.rs:145-178,231-268     */
+/* ------------------------------------------------------------------ */
+int nro_block(uint32_t element, uint32_t *elements, uint32_t *bytes) {
+    switch (element) {
+    case NRO_Q8_0: *elements = QUANT_BLOCK; *bytes = Q8_0_BYTES; return 0;
+    case NRO_Q4K: *elements = SUPER_BLOCK; *bytes = Q4K_BYTES; return 0;
+    default: return -1;
+    }
+}
+
+uint64_t nro_payload_bytes(uint32_t element, uint64_t elements) {
+    uint32_t per, bytes;
+    if (element == NRO_SINGLE) return elements * 4u;
+    if (nro_block(element, &per, &bytes)) return 0;
+    return (elements + per - 1) / per * bytes;
+}
+
+/* payload rounded up to whole 4-byte words, as pack() pads it (ggml.rs:17-18) */
+uint64_t nro_packed_bytes(uint32_t element, uint64_t elements) {
+    return (nro_payload_bytes(element, elements) + 3u) / 4u * 4u;
+}
+
+/* ------------------------------------------------------------------ */
+/* Host quantiser: crates/neura-precision/src/ggml.rs                  */
+/* ------------------------------------------------------------------ */
+static float least(float a, float b) { return a < b ? a : b; }       /* ggml.rs:90-92 */
+static float greatest(float a, float b) { return a > b ? a : b; }    /* ggml.rs:94-96 */
+static float clampf(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+static void put_half(uint8_t *field, int at, float value) { /* ggml.rs:78-80 */
+    uint16_t h = nro_f32_to_f16(value);
+    field[at] = (uint8_t)(h & 0xff);
+    field[at + 1] = (uint8_t)(h >> 8);
+}
+static float half_at(const uint8_t *field, int at) { /* ggml.rs:74-76 */
+    return nro_f16_to_f32((uint16_t)(field[at] | (field[at + 1] << 8)));
+}
+
+/* ggml.rs:201-209 (q8_0) with peak() from :98-108 */
+static void q8_0_encode(const float *values, uint8_t *out) {
+    float size = 0.0f;
+    for (int i = 0; i < QUANT_BLOCK; ++i)
+        if (size < fabsf(values[i])) size = fabsf(values[i]);
+    float quantum = size / 127.0f;
+    float inverse = quantum == 0.0f ? 0.0f : 1.0f / quantum;
+    put_half(out, 0, quantum);
+    for (int i = 0; i < QUANT_BLOCK; ++i) {
+        float code = clampf(roundf(values[i] * inverse), -127.0f, 127.0f);
+        out[2 + i] = (uint8_t)(int8_t)code;
+    }
+}
+
+/* ggml.rs:211-216 */
+static void q8_0_decode(const uint8_t *field, float *out) {
+    float quantum = half_at(field, 0);
+    for (int i = 0; i < QUANT_BLOCK; ++i) out[i] = (float)(int8_t)field[2 + i] * quantum;
+}
+
+/* ggml.rs:127-136 */
+static void scale_min_k4(const uint8_t *scales, int at, uint32_t *scale, uint32_t *min) {
+    if (at < 4) {
+        *scale = scales[at] & 63u;
+        *min = scales[at + 4] & 63u;
+    } else {
+        *scale = (uint32_t)(scales[at + 4] & 0x0f) | ((uint32_t)(scales[at - 4] >> 6) << 4);
+        *min = (uint32_t)(scales[at + 4] >> 4) | ((uint32_t)(scales[at] >> 6) << 4);
+    }
+}
+
+/* ggml.rs:138-147 */
+static void put_scale_min_k4(uint8_t *scales, int at, uint32_t scale, uint32_t min) {
+    if (at < 4) {
+        scales[at] = (uint8_t)scale;
+        scales[at + 4] = (uint8_t)min;
+    } else {
+        scales[at + 4] = (uint8_t)((scale & 0x0f) | ((min & 0x0f) << 4));
+        scales[at - 4] |= (uint8_t)((scale >> 4) << 6);
+        scales[at] |= (uint8_t)((min >> 4) << 6);
+    }
+}
+
+static float scale_of(float quantum, float low) { return quantum == 0.0f ? 0.0f : low / quantum; } /* :116-118 */
+
+static uint32_t quantized(float value, float quantum, float low, float high) { /* :120-125 */
+    if (quantum == 0.0f) return 0;
+    return (uint32_t)clampf(roundf(value / quantum), low, high);
+}
+
+/* ggml.rs:149-199 with steps = 15, sub = 32 (q4_k, :314-316) */
+static void q4_k_encode(const float *values, uint8_t *field) {
+    const int count = SUPER_BLOCK / SUPER_SUB_BLOCK;
+    float lows[8], quantums[8];
+    for (int at = 0; at < count; ++at) {
+        float low = 0.0f, high = 0.0f; /* span(): fold from (0, 0) */
+        for (int i = 0; i < SUPER_SUB_BLOCK; ++i) {
+            float v = values[at * SUPER_SUB_BLOCK + i];
+            low = least(low, v);
+            high = greatest(high, v);
+        }
+        lows[at] = least(0.0f, low);
+        quantums[at] = (high - lows[at]) / 15.0f;
+    }
+    float scale = 0.0f, min = 0.0f;
+    for (int at = 0; at < count; ++at) scale = greatest(scale, quantums[at]);
+    scale = scale / 63.0f;
+    for (int at = 0; at < count; ++at) min = greatest(min, -lows[at]);
+    min = min / 63.0f;
+    uint8_t codes[8], mins[8];
+    for (int at = 0; at < count; ++at) {
+        codes[at] = (uint8_t)clampf(roundf(scale_of(scale, quantums[at])), 0.0f, 63.0f);
+        mins[at] = (uint8_t)clampf(roundf(scale_of(min, -lows[at])), 0.0f, 63.0f);
+    }
+    uint8_t scales[SUPER_SCALE_BYTES];
+    memset(scales, 0, sizeof scales);
+    for (int at = 0; at < count; ++at) put_scale_min_k4(scales, at, codes[at], mins[at]);
+    memset(field, 0, Q4K_BYTES);
+    put_half(field, 0, scale);
+    put_half(field, 2, min);
+    memcpy(field + 4, scales, SUPER_SCALE_BYTES);
+    for (int at = 0; at < count; ++at) {
+        /* the codes are taken with the unrounded f32 scale and min, not the stored halves */
+        float quantum = scale * (float)codes[at];
+        float low = min * (float)mins[at];
+        for (int within = 0; within < SUPER_SUB_BLOCK; ++within) {
+            uint32_t code = quantized(values[at * SUPER_SUB_BLOCK + within] + low, quantum, 0.0f, 15.0f);
+            int group = at / 2;
+            int seat = at % 2;
+            field[16 + group * SUPER_SUB_BLOCK + within] |= (uint8_t)((code & 0x0f) << (seat ? 4 : 0));
+        }
+    }
+}
+
+/* ggml.rs:336-350 */
+static void q4_k_decode(const uint8_t *field, float *out) {
+    float scale = half_at(field, 0);
+    float min = half_at(field, 2);
+    int n = 0;
+    for (int group = 0; group < 4; ++group) {
+        for (int seat = 0; seat < 2; ++seat) {
+            uint32_t code, offset;
+            scale_min_k4(field + 4, group * 2 + seat, &code, &offset);
+            float quantum = scale * (float)code;
+            float low = min * (float)offset;
+            for (int within = 0; within < SUPER_SUB_BLOCK; ++within) {
+                uint8_t byte = field[16 + group * 32 + within];
+                uint32_t quant = seat ? (uint32_t)(byte >> 4) : (uint32_t)(byte & 0x0f);
+                out[n++] = quantum * (float)quant - low;
+            }
+        }
+    }
+}
+
+/* pack(): ggml.rs:8-20.  `out` must hold nro_packed_bytes(element, count). */
+int nro_pack(uint32_t element, const float *values, uint64_t count, uint8_t *out) {
+    uint32_t per, bytes;
+    if (nro_block(element, &per, &bytes)) return -1;
+    uint64_t blocks = (count + per - 1) / per;
+    for (uint64_t b = 0; b < blocks; ++b) {
+        float held[SUPER_BLOCK];
+        memset(held, 0, sizeof held);
+        uint64_t have = count - b * per < per ? count - b * per : per;
+        memcpy(held, values + b * per, have * sizeof(float));
+        if (element == NRO_Q8_0) q8_0_encode(held, out + b * bytes);
+        else q4_k_encode(held, out + b * bytes);
+    }
+    uint64_t end = blocks * bytes;
+    uint64_t padded = (end + 3u) / 4u * 4u;
+    for (uint64_t i = end; i < padded; ++i) out[i] = 0;
+    return 0;
+}
+
+/* unpack(): ggml.rs:22-38 */
+int nro_unpack(uint32_t element, uint64_t count, const uint8_t *bytes_in, float *out) {
+    uint32_t per, bytes;
+    if (nro_block(element, &per, &bytes)) return -1;
+    uint64_t blocks = (count + per - 1) / per;
+    for (uint64_t b = 0; b < blocks; ++b) {
+        float held[SUPER_BLOCK];
+        if (element == NRO_Q8_0) q8_0_decode(bytes_in + b * bytes, held);
+        else q4_k_decode(bytes_in + b * bytes, held);
+        uint64_t have = count - b * per < per ? count - b * per : per;
+        memcpy(out + b * per, held, have * sizeof(float));
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------ */
+/* Second restatement of the decoders, after the device code's scalar  */
+/* fetch: crates/neura-kernel/src/fetch.rs:183-267.  Used by the tests */
+/* to cross-pin the walk above (the reference states it three times).  */
+/* ------------------------------------------------------------------ */
+static uint32_t ggml_byte(const uint8_t *heap, uint64_t at) { return heap[at]; }
+
+static uint32_t ggml_k4_scale(const uint8_t *heap, uint64_t base, uint32_t at) { /* fetch.rs:209-218 */
+    int upper = at >= 4u;
+    uint32_t seat = upper ? at - 4u : 0u;
+    uint32_t low = upper ? (ggml_byte(heap, base + at + 4u) & 0xfu) : (ggml_byte(heap, base + at) & 63u);
+    return low | (upper ? ((ggml_byte(heap, base + seat) >> 6) << 4) : 0u);
+}
+
+static uint32_t ggml_k4_min(const uint8_t *heap, uint64_t base, uint32_t at) { /* fetch.rs:220-225 */
+    int upper = at >= 4u;
+    uint32_t packed = ggml_byte(heap, base + at + 4u);
+    uint32_t low = upper ? packed >> 4 : packed & 63u;
+    return low | (upper ? ((ggml_byte(heap, base + at) >> 6) << 4) : 0u);
+}
+
+float nro_fetch(uint32_t element, const uint8_t *heap, uint64_t at) {
+    if (element == NRO_Q8_0) { /* fetch.rs:236-240 */
+        uint64_t base = at / QUANT_BLOCK * Q8_0_BYTES;
+        uint32_t byte = ggml_byte(heap, base + 2u + at % QUANT_BLOCK);
+        float signed_code = (float)((int32_t)byte - (byte >= 128u ? 256 : 0));
+        return signed_code * half_at(heap + base, 0);
+    }
+    if (element == NRO_Q4K) { /* fetch.rs:256-267 */
+        uint64_t base = at / SUPER_BLOCK * Q4K_BYTES;
+        uint32_t within = (uint32_t)(at % SUPER_BLOCK);
+        uint32_t group = within / 64u;
+        uint32_t seat = (within % 64u) / SUPER_SUB_BLOCK;
+        uint32_t lane = within % SUPER_SUB_BLOCK;
+        uint32_t sub = group * 2u + seat;
+        uint32_t packed = ggml_byte(heap, base + 16u + group * 32u + lane);
+        uint32_t quant = seat == 1u ? packed >> 4 : packed & 0xfu;
+        float a = half_at(heap + base, 0) * (float)ggml_k4_scale(heap, base + 4u, sub);
+        float b = half_at(heap + base, 2) * (float)ggml_k4_min(heap, base + 4u, sub);
+        return a * (float)quant - b;
+    }
+    return NAN;
+}
+
+/* ------------------------------------------------------------------ */
+/* Pointwise epilogue: crates/neura-pointwise/src/op.rs:141-170 (op    */
+/* codes in declaration order) and neura-kernel/src/pointwise.rs:66-68 */
+/* ------------------------------------------------------------------ */
+enum {
+    OP_ADD = 0, OP_MUL, OP_SUB, OP_DIV, OP_MAXIMUM, OP_MINIMUM, OP_RELU, OP_SQRT, OP_RECIP, OP_EXP,
+    OP_LOG, OP_TANH, OP_SIGMOID, OP_NEG, OP_ABS, OP_IDENTITY, OP_SIN, OP_COS, OP_POW, OP_FLOOR,
+    OP_GELU, OP_SILU
+};
+
+static float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+float nro_op_apply(uint32_t op, float a, float b) {
+    switch (op) {
+    case OP_ADD: return a + b;
+    case OP_MUL: return a * b;
+    case OP_SUB: return a - b;
+    case OP_DIV: return a / b;
+    case OP_MAXIMUM: return a > b ? a : b;
+    case OP_MINIMUM: return a < b ? a : b;
+    case OP_RELU: return a > 0.0f ? a : 0.0f;
+    case OP_SQRT: return sqrtf(a);
+    case OP_RECIP: return 1.0f / a;
+    case OP_EXP: return expf(a);
+    case OP_LOG: return logf(a);
+    case OP_TANH: return tanhf(a);
+    case OP_SIGMOID: return sigmoidf(a);
+    case OP_NEG: return -a;
+    case OP_ABS: return fabsf(a);
+    case OP_IDENTITY: return a;
+    case OP_SIN: return sinf(a);
+    case OP_COS: return cosf(a);
+    case OP_POW: return powf(a, b);
+    case OP_FLOOR: return floorf(a);
+    case OP_GELU: {
+        float inner = 0.7978845608f * (a + 0.044715f * a * a * a);
+        return 0.5f * a * (1.0f + tanhf(inner));
+    }
+    case OP_SILU: return a * sigmoidf(a);
+    default: return NAN;
+    }
+}
+
+/* One step of `chained` (pointwise.rs:90-104): operand is fetched at the output
+ * coordinate through broadcast strides; `swapped` puts the operand first. */
+typedef struct {
+    uint32_t op;
+    uint32_t swapped;
+    const float *operand;   /* NULL: the step is unary (operand reads as 0) */
+    int64_t row_stride;     /* elements between output rows of the operand (0 = broadcast) */
+    int64_t col_stride;     /* elements between output columns of the operand (0 = broadcast) */
+} nro_step;
+
+static float chained(const nro_step *steps, uint32_t n_steps, uint64_t row, uint64_t col, float carried) {
+    float result = carried;
+    for (uint32_t s = 0; s < n_steps; ++s) {
+        float operand = steps[s].operand
+            ? steps[s].operand[(int64_t)row * steps[s].row_stride + (int64_t)col * steps[s].col_stride]
+            : 0.0f;
+        result = steps[s].swapped ? nro_op_apply(steps[s].op, operand, result)
+                                  : nro_op_apply(steps[s].op, result, operand);
+    }
+    return result;
+}
+
+/* ------------------------------------------------------------------ */
+/* The product itself.  The reference has no host matmul; its tests    */
+/* state the expected result as a sequential f32 loop over             */
+/* unpack(pack(w)) (crates/neura-runtime/tests/runtime.rs:72-83):      */
+/*   total += weight[column*depth + step] * inputs[row*depth + step]   */
+/* ------------------------------------------------------------------ */
+typedef struct {
+    uint32_t element;
+    const uint8_t *packed; /* N rows, each ceil(K/per) blocks, row-major, K contiguous */
+    const float *weight;   /* or: already unpacked f32 [N][K] (packed == NULL) */
+    const float *x;        /* [rows][x_stride] */
+    float *out;            /* [rows][out_stride] */
+    uint64_t rows, n, k, x_stride, out_stride;
+    const nro_step *steps;
+    uint32_t n_steps;
+    uint64_t c0, c1;       /* column range of this worker */
+    int round_bf16;        /* prefill variant: weights and activations rounded to bf16 first */
+} product_job;
+
+static void *product_worker(void *arg) {
+    product_job *job = (product_job *)arg;
+    uint32_t per = 1, bytes = 4;
+    if (job->packed) nro_block(job->element, &per, &bytes);
+    uint64_t row_bytes = (job->k + per - 1) / per * bytes;
+    float *held = (float *)malloc(((job->k + per - 1) / per * per) * sizeof(float));
+    for (uint64_t c = job->c0; c < job->c1; ++c) {
+        const float *w;
+        if (job->packed) {
+            nro_unpack(job->element, job->k, job->packed + c * row_bytes, held);
+            w = held;
+        } else {
+            w = job->weight + c * job->k;
+        }
+        if (job->round_bf16) {
+            if (w != held) memcpy(held, w, job->k * sizeof(float));
+            for (uint64_t s = 0; s < job->k; ++s) held[s] = nro_bf16_to_f32(nro_bf16_rne(held[s]));
+            w = held;
+        }
+        for (uint64_t r = 0; r < job->rows; ++r) {
+            const float *x = job->x + r * job->x_stride;
+            float total = 0.0f;
+            if (job->round_bf16) {
+                for (uint64_t s = 0; s < job->k; ++s) total += w[s] * nro_bf16_to_f32(nro_bf16_rne(x[s]));
+            } else {
+                for (uint64_t s = 0; s < job->k; ++s) total += w[s] * x[s];
+            }
+            job->out[r * job->out_stride + c] = chained(job->steps, job->n_steps, r, c, total);
+        }
+    }
+    free(held);
+    return NULL;
+}
+
+static int run_product(product_job base, int threads) {
+    if (threads < 1) threads = 1;
+    if ((uint64_t)threads > base.n) threads = (int)(base.n ? base.n : 1);
+    pthread_t *ids = (pthread_t *)malloc(sizeof(pthread_t) * threads);
+    product_job *jobs = (product_job *)malloc(sizeof(product_job) * threads);
+    for (int t = 0; t < threads; ++t) {
+        jobs[t] = base;
+        jobs[t].c0 = base.n * t / threads;
+        jobs[t].c1 = base.n * (t + 1) / threads;
+        if (threads == 1) product_worker(&jobs[t]);
+        else pthread_create(&ids[t], NULL, product_worker, &jobs[t]);
+    }
+    if (threads > 1)
+        for (int t = 0; t < threads; ++t) pthread_join(ids[t], NULL);
+    free(ids);
+    free(jobs);
+    return 0;
+}
+
+/* out[r][c] = chain(sum_k unpack(W)[c][k] * x[r][k]); rows of W are packed
+ * independently (each row is a whole number of blocks, as a GGUF stores it). */
+int nro_linear(uint32_t element, const uint8_t *packed, uint64_t n, uint64_t k, const float *x, uint64_t rows,
+               uint64_t x_stride, float *out, uint64_t out_stride, const nro_step *steps, uint32_t n_steps,
+               int threads) {
+    uint32_t per, bytes;
+    if (nro_block(element, &per, &bytes) || k % per) return -1;
+    product_job job = {element, packed, NULL, x, out, rows, n, k, x_stride, out_stride, steps, n_steps, 0, 0, 0};
+    return run_product(job, threads);
+}
+
+/* Prefill variant: dequantised weights and the activations are rounded to
+ * bf16 (RNE) before the f32 product, which is what the tensor-core path does. */
+int nro_linear_bf16(uint32_t element, const uint8_t *packed, uint64_t n, uint64_t k, const float *x,
+                    uint64_t rows, uint64_t x_stride, float *out, uint64_t out_stride, const nro_step *steps,
+                    uint32_t n_steps, int threads) {
+    uint32_t per, bytes;
+    if (nro_block(element, &per, &bytes) || k % per) return -1;
+    product_job job = {element, packed, NULL, x, out, rows, n, k, x_stride, out_stride, steps, n_steps, 0, 0, 1};
+    return run_product(job, threads);
+}
+
+/* The reference tests' loop on an already unpacked weight (runtime.rs:72-83). */
+int nro_matmul_f32(const float *weight, uint64_t n, uint64_t k, const float *x, uint64_t rows, float *out,
+                   int threads) {
+    product_job job = {NRO_SINGLE, NULL, weight, x, out, rows, n, k, k, n, NULL, 0, 0, 0, 0};
+    return run_product(job, threads);
+}

@@ -1,0 +1,29 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    import oracle as module
+
+    module.build()
+    return module
+
+
+@pytest.fixture(scope="session")
+def runtime():
+    import neura_b200
+
+    rt = neura_b200.Runtime(0)
+    yield rt
+    rt.close()

@@ -1,0 +1,164 @@
+"""CUDA path against the CPU oracle, through the C ABI (needs a B200)."""
+import numpy as np
+import pytest
+
+import neura_b200 as nb
+
+pytestmark = pytest.mark.gpu
+
+ELEMENTS = [nb.Q8_0, nb.Q4K]
+# the reference's own bar: |device - naive f32 loop| <= 1e-3 absolute on uniform(-1, 1) data
+# (crates/neura-runtime/tests/runtime.rs:85, tests/support/mod.rs:50-67)
+ABS_TOL = 1e-3
+# BASELINE north star: within 1e-3 relative
+REL_TOL = 1e-3
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def weights(oracle, element, n, k, seed=23, normal=False):
+    stream = oracle.Stream(seed)
+    w = stream.normal(n * k, 0.0, 0.02) if normal else stream.uniform(n * k)
+    return w.reshape(n, k), oracle.pack_rows(element, w.reshape(n, k))
+
+
+def assert_close(actual, expected, what=""):
+    err = np.abs(actual - expected)
+    scale = np.sqrt(np.mean(expected.astype(np.float64) ** 2)) + 1e-30
+    assert err.max() <= ABS_TOL * max(1.0, scale / 15.0) or err.max() <= REL_TOL * scale, (
+        f"{what}: max |diff| {err.max():.3e} at {np.unravel_index(err.argmax(), err.shape)}, rms of expected {scale:.3e}")
+
+
+@pytest.mark.parametrize("element", ELEMENTS)
+@pytest.mark.parametrize("n,k", [(16, 256), (40, 512), (1024, 2048), (33, 1280)])
+def test_dequant_is_bit_exact_in_both_layouts(runtime, oracle, element, n, k):
+    _, packed = weights(oracle, element, n, k)
+    expected = oracle.unpack(element, n * k, packed).reshape(n, k)
+    raw = runtime.load(element, n, k, packed, seal=False)
+    assert np.array_equal(bits(runtime.dequant(raw)), bits(expected))
+    sealed = runtime.load(element, n, k, packed)
+    assert sealed.layout == nb.LAYOUT_TILED
+    assert np.array_equal(bits(runtime.dequant(sealed)), bits(expected))
+
+
+@pytest.mark.parametrize("element", ELEMENTS)
+@pytest.mark.parametrize("normal", [False, True])
+def test_device_packer_matches_host_packer_bit_for_bit(runtime, oracle, element, normal):
+    # a_quantized_tensor_reads_back_the_blocks_a_device_packs (runtime.rs:717-736)
+    w, packed = weights(oracle, element, 64, 1024, seed=5, normal=normal)
+    got = runtime.quantize(element, w)
+    assert np.array_equal(got, packed[: got.size])
+
+
+@pytest.mark.parametrize("element", ELEMENTS)
+def test_device_packer_handles_zero_and_constant_blocks(runtime, oracle, element):
+    w = np.zeros((4, 512), dtype=np.float32)
+    w[1] = 0.75
+    w[2, ::3] = -1e-3
+    w[3] = np.linspace(-2, 5, 512, dtype=np.float32)
+    packed = oracle.pack_rows(element, w)
+    assert np.array_equal(runtime.quantize(element, w), packed)
+
+
+@pytest.mark.parametrize("element", ELEMENTS)
+@pytest.mark.parametrize("rows", [1, 2, 4])
+def test_a_narrow_product_walks_the_quantized_weight(runtime, oracle, element, rows):
+    # a_narrow_product_walks_the_quantized_weight_a_gguf_stores (runtime.rs:12-86)
+    depth, columns = 2048, 1024
+    _, packed = weights(oracle, element, columns, depth, seed=23)
+    x = oracle.random(rows * depth, 29).reshape(rows, depth)
+    expected = oracle.linear(element, packed, columns, depth, x, threads=8)
+    w = runtime.load(element, columns, depth, packed)
+    got = runtime.linear_host(w, x)
+    assert np.abs(got - expected).max() <= ABS_TOL
+
+
+@pytest.mark.parametrize("element", ELEMENTS)
+def test_a_wide_product_walks_the_quantized_weight(runtime, oracle, element):
+    # a_wide_product_walks_the_quantized_weight_a_gguf_stores (runtime.rs:88-144)
+    rows, depth, columns = 8, 512, 4096
+    _, packed = weights(oracle, element, columns, depth, seed=23)
+    x = oracle.random(rows * depth, 29).reshape(rows, depth)
+    expected = oracle.linear(element, packed, columns, depth, x, threads=8)
+    w = runtime.load(element, columns, depth, packed)
+    got = runtime.linear_host(w, x)
+    assert np.abs(got - expected).max() <= ABS_TOL
+
+
+@pytest.mark.parametrize("element,n,k", [
+    (nb.Q8_0, 4864, 896),    # config 1: Qwen2.5-0.5B up projection
+    (nb.Q8_0, 1, 32), (nb.Q8_0, 17, 96), (nb.Q8_0, 130, 4864),
+    (nb.Q4K, 1, 256), (nb.Q4K, 31, 768), (nb.Q4K, 1000, 3584), (nb.Q4K, 48, 27648),
+])
+@pytest.mark.parametrize("rows", [1, 3, 5, 16, 19])
+def test_products_over_ragged_shapes(runtime, oracle, element, n, k, rows):
+    _, packed = weights(oracle, element, n, k, seed=101, normal=True)
+    x = oracle.Stream(7).normal(rows * k).reshape(rows, k)
+    expected = oracle.linear(element, packed, n, k, x, threads=8)
+    w = runtime.load(element, n, k, packed)
+    got = runtime.linear_host(w, x)
+    assert_close(got, expected, f"element {element} [{n},{k}] rows {rows}")
+
+
+@pytest.mark.parametrize("element", ELEMENTS)
+def test_the_fused_chain_applies_its_steps_in_order(runtime, oracle, element):
+    n, k, rows = 96, 512, 3
+    _, packed = weights(oracle, element, n, k, seed=3, normal=True)
+    x = oracle.Stream(11).normal(rows * k).reshape(rows, k)
+    gate = oracle.Stream(13).normal(rows * n).reshape(rows, n)
+    bias = oracle.Stream(17).normal(n)
+    chain_o = [(oracle.ADD, bias), (oracle.SILU, None), (oracle.MUL, gate), (oracle.SUB, gate, True)]
+    expected = oracle.linear(element, packed, n, k, x, chain=chain_o)
+    w = runtime.load(element, n, k, packed)
+    xd, od = runtime.tensor(rows, k), runtime.tensor(rows, n)
+    gd, bd = runtime.tensor(rows, n), runtime.tensor(n)
+    runtime.write(xd, x); runtime.write(gd, gate); runtime.write(bd, bias)
+    chain = [nb.Step(nb.ADD, bd), nb.Step(nb.SILU), nb.Step(nb.MUL, gd), nb.Step(nb.SUB, gd, swapped=True)]
+    runtime.linear(w, xd, od, chain)
+    got = runtime.read(od)
+    assert_close(got, expected, "chain")
+
+
+def test_activations_far_from_one_keep_their_precision(runtime, oracle):
+    # block fixed point must follow the magnitude of each stretch of the activations
+    n, k = 64, 1024
+    _, packed = weights(oracle, nb.Q4K, n, k, seed=9, normal=True)
+    x = oracle.Stream(21).normal(k).reshape(1, k)
+    x[0, :256] *= 1e-6
+    x[0, 256:512] *= 1e4
+    x[0, 512:768] = 0.0
+    expected = oracle.linear(nb.Q4K, packed, n, k, x)
+    got = runtime.linear_host(runtime.load(nb.Q4K, n, k, packed), x)
+    assert_close(got, expected, "mixed magnitudes")
+    tiny = (x * 1e-30).astype(np.float32)
+    expected = oracle.linear(nb.Q4K, packed, n, k, tiny)
+    got = runtime.linear_host(runtime.load(nb.Q4K, n, k, packed), tiny)
+    assert np.abs(got - expected).max() <= 1e-3 * np.abs(expected).max()
+
+
+def test_the_library_refuses_what_the_reference_panics_on(runtime, oracle):
+    _, packed = weights(oracle, nb.Q4K, 16, 256)
+    with pytest.raises(nb.NeuraCudaError):
+        runtime.load(nb.Q4K, 16, 200, packed)           # rows that do not fill blocks
+    with pytest.raises(nb.NeuraCudaError):
+        runtime.load(nb.Q4K, 64, 256, packed)           # a source shorter than its shape (store.rs:90-123)
+    raw = runtime.load(nb.Q4K, 16, 256, packed, seal=False)
+    with pytest.raises(nb.NeuraCudaError):
+        runtime.linear_host(raw, np.zeros((1, 256), np.float32))  # the product wants a sealed weight
+
+
+def test_device_packer_keeps_the_sign_of_a_zero_extreme(runtime, oracle):
+    # least/greatest (ggml.rs:90-96) return their second argument on a tie, which decides
+    # whether an all-positive or all-zero block stores +0 or -0 in its fp16 fields
+    w = np.zeros((6, 256), dtype=np.float32)
+    w[1, 5] = -0.0
+    w[2] = np.abs(oracle.Stream(3).normal(256)) + 0.1
+    w[3] = -np.abs(oracle.Stream(4).normal(256)) - 0.1
+    w[4, 40:] = 1.0
+    w[4, 7] = -0.0
+    w[5, :200] = -1.0
+    w[5, 255] = -0.0
+    packed = oracle.pack_rows(nb.Q4K, w)
+    assert np.array_equal(runtime.quantize(nb.Q4K, w), packed)
