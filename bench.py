@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Decode throughput of the quantized-linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one decoded token's pass over every Q4_K projection of a Qwen2.5-32B-shaped
+decoder (64 layers of q/k/v, output, gate, up, down, then the head: 17.99 GB of GGUF
+blocks, far larger than L2, so every step streams them from HBM).  Prints ONE JSON line.
+With N > 1 (launched under torchrun) every rank runs the same model on its own GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s (Q4_K Qwen-shaped)"
+UNIT = "tok/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            data = json.load(fh)
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        self.file.flush()
+        self.file.seek(0)
+        sm, smax, reasons = [], [], set()
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                   parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = sorted(sm)[len(sm) // 4:]  # drop the idle samples before and after the region
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def workload_config(name: str):
+    from neura_b200 import qwen
+
+    if name == "qwen2.5-32b-q4_k":
+        return qwen.QWEN25_32B_Q4K
+    if name == "qwen2.5-0.5b-q8_0":
+        return qwen.QWEN25_05B_Q8
+    if name.startswith("qwen2.5-32b-q4_k-"):
+        return qwen.scaled(qwen.QWEN25_32B_Q4K, int(name.rsplit("-", 1)[1].rstrip("l")))
+    raise SystemExit(f"unknown workload {name}")
+
+
+def cpu_baseline(config, seconds: float = 12.0):
+    """The oracle's product (the reference tests' f32 loop over unpacked blocks) on the host
+    cores, on a bounded sample of the token: rows of the up projection of one layer."""
+    import numpy as np
+    import oracle
+
+    cores = os.cpu_count() or 1
+    k = config.hidden
+    n = min(config.feed_forward, 4096)
+    w = oracle.Stream(23).normal(n * k, 0.0, 0.02).reshape(n, k)
+    packed = oracle.pack_rows(config.element, w)
+    x = oracle.Stream(29).normal(k).reshape(1, k)
+    oracle.linear(config.element, packed, n, k, x, threads=cores)  # warm-up
+    runs, spent = 0, 0.0
+    while spent < seconds and runs < 64:
+        t0 = time.perf_counter()
+        oracle.linear(config.element, packed, n, k, x, threads=cores)
+        spent += time.perf_counter() - t0
+        runs += 1
+    per_weight = spent / runs / (n * k)
+    tok_s = 1.0 / (per_weight * config.weight_elements())
+    return {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{runs} runs of a [{n}x{k}] {('Q4_K' if config.element == 9 else 'Q8_0')} product at batch 1 "
+                      f"({spent:.1f} s), scaled by weights per token ({config.weight_elements()})"}
+
+
+def run_reference(args):
+    """The reference has no CPU (or CUDA) implementation of the product; its only executable
+    statement of it is the f32 loop of its tests, which the oracle restates.  This arm times
+    that on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    config = workload_config(args.workload)
+    import numpy as np  # noqa: F401
+    import oracle
+
+    cores = os.cpu_count() or 1
+    k, n = config.hidden, min(config.feed_forward, 2048)
+    w = oracle.Stream(23).normal(n * k, 0.0, 0.02).reshape(n, k)
+    packed = oracle.pack_rows(config.element, w)
+    x = oracle.Stream(29).normal(k).reshape(1, k)
+    for _ in range(max(1, args.warmup)):
+        oracle.linear(config.element, packed, n, k, x, threads=cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.linear(config.element, packed, n, k, x, threads=cores)
+    elapsed = time.perf_counter() - t0
+    scale = config.weight_elements() / (n * k)
+    ms_per_step = elapsed / args.steps * scale * 1e3
+    value = 1e3 / ms_per_step
+    sample = (f"each step = a [{n}x{k}] product at batch 1 on {cores} threads, scaled by weights per token "
+              f"(x{scale:.0f})")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": config.name, "batch": 1},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        dist = None
+        torch.cuda.set_device(local)
+
+    import neura_b200 as nb
+    from neura_b200 import qwen
+    from neura_b200.synthetic import synthetic_weights
+
+    config = workload_config(args.workload)
+    rows = args.batch
+    rt = nb.Runtime(local)
+    rt.use_stream(rt.new_stream())
+    tstream = torch.cuda.ExternalStream(rt.stream.value, device=torch.device("cuda", local))
+    weights = synthetic_weights(rt, config, seed=23 + rank)
+    stack = qwen.LinearStack(rt, config, weights, rows=rows)
+
+    # pinned host buffers of the end-to-end path: the token's input activations in, logits out
+    x_host = torch.randn(rows, config.hidden, generator=torch.Generator().manual_seed(29)).pin_memory()
+    top_host = torch.empty(rows, config.vocab, dtype=torch.float32).pin_memory()
+    h2d, d2h = x_host.numel() * 4, top_host.numel() * 4
+
+    def write_input():
+        rt._lib.neura_cuda_write(rt._ctx, rt.stream, stack.hidden.ptr, x_host.data_ptr(), h2d)
+
+    def read_output():
+        rt._lib.neura_cuda_read(rt._ctx, rt.stream, top_host.data_ptr(), stack.logits.ptr, d2h)
+
+    write_input()
+    stack.token()          # eager once: sizes every scratch region before recording
+    rt.sync()
+    program = stack.record()
+    launches0 = rt.launches
+
+    def barrier():
+        rt.sync()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput -------------------------------------------------
+    for _ in range(max(3, args.warmup)):
+        write_input()
+        rt.run(program)
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        time.sleep(0.15)
+        start.record(tstream)
+        for _ in range(args.steps):
+            rt.run(program)
+        stop.record(tstream)
+        barrier()
+        time.sleep(0.15)
+    ms = start.elapsed_time(stop)
+    launches = rt.launches - launches0 - max(3, args.warmup) * stack.launches_per_token()
+    clock_summary = clocks.summary()
+
+    # ---- end to end: host buffers in and out every step -------------------------------
+    barrier()
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = args.steps
+    t_start.record(tstream)
+    for _ in range(e2e_steps):
+        write_input()
+        rt.run(program)
+        read_output()
+        rt.sync()
+    t_stop.record(tstream)
+    barrier()
+    e2e_ms = t_start.elapsed_time(t_stop)
+
+    # ---- roofline of the dominant kernel (the Q4_K product), timed on its own ----------
+    peak, peak_kind = measured_peaks()
+    name, n, k = "ffn_up", config.feed_forward, config.hidden
+    rt.stage(stack.hidden, config.element)
+    reps = 4
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for layer in range(config.layers):
+        rt.linear_staged(weights[f"blk.{layer}.{name}.weight"], stack.held)
+    rt.sync()
+    r0.record(tstream)
+    for _ in range(reps):
+        for layer in range(config.layers):  # 64 different matrices: 5 GB between reuses, L2 holds none of it
+            rt.linear_staged(weights[f"blk.{layer}.{name}.weight"], stack.held)
+    r1.record(tstream)
+    rt.sync()
+    kernel_ms = r0.elapsed_time(r1) / (reps * config.layers)
+    algorithmic = nb.payload_bytes(config.element, n * k) + 4 * rows * k + 4 * rows * n
+    achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
+
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=torch.device("cuda", local))
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(times[0]), float(times[1])
+    if rank == 0:
+        tokens = rows * args.steps * world
+        line = {
+            "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": config.name, "batch": rows, "part": "projections and head of every layer "
+                       "(norms, RoPE and attention not yet in the step)", "parallelism": f"replicas x{world}",
+                       "l2": "inputs larger than L2 (17.99 GB of weights per step)",
+                       "weight_bytes_per_token": config.weight_bytes()},
+            "clocks": clock_summary,
+            "e2e": {"value": rows * e2e_steps * world / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": f"gemv_q4k_kernel<NT> on [{n}x{k}] at batch {rows}",
+                         "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
+                         "step_gbs": config.weight_bytes() / (ms / args.steps * 1e-3) / 1e9},
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(config)
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="qwen2.5-32b-q4_k")
+    parser.add_argument("--batch", type=int, default=1)
+    parser.add_argument("--no-cpu", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

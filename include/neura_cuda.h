@@ -142,12 +142,38 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream, const nc_weight *w, con
                           uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
                           uint32_t n_steps);
 
+/* The two halves of neura_cuda_linear, for callers that feed several weights with the
+ * same activations (q/k/v, gate/up: examples/qwen/attention.rs:106-125, mlp.rs:31-32).
+ * neura_cuda_stage rewrites up to 16 rows of f32 activations into the context's
+ * staging area in the form the MMA kernels read (three int8 digit planes per row, an
+ * exponent per block of the weight format `element`); neura_cuda_linear_staged runs
+ * the product of the staged rows with `w`.  The staging is overwritten by the next
+ * neura_cuda_stage or neura_cuda_linear on the context. */
+int32_t neura_cuda_stage(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                         uint32_t k, uint32_t element);
+int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev,
+                                 uint64_t out_stride, const nc_step *chain, uint32_t n_steps);
+
 /* The same product called the way Runtime::{write, run, read} are (runtime.rs:1020,833,1064):
  * activations come from and results return to host memory; blocks until done. */
 int32_t neura_cuda_linear_host(nc_context *ctx, void *stream, const nc_weight *w, const float *x_host,
                                uint32_t rows, float *out_host, const nc_step *chain, uint32_t n_steps);
 
-/* Kernel launches issued through this context since it was opened. */
+/* Runtime::compile / Runtime::run (runtime.rs:528,833): the calls issued on `stream`
+ * between capture_begin and capture_end are recorded into a program (a CUDA graph)
+ * instead of running; program_run replays them with one launch.  `stream` must not be
+ * the default stream.  Scratch cannot grow while recording: neura_cuda_reserve first. */
+typedef struct nc_program nc_program;
+int32_t neura_cuda_capture_begin(nc_context *ctx, void *stream);
+int32_t neura_cuda_capture_end(nc_context *ctx, void *stream, nc_program **out);
+int32_t neura_cuda_program_run(nc_context *ctx, void *stream, nc_program *program);
+int32_t neura_cuda_program_free(nc_context *ctx, nc_program *program);
+
+/* Streams for callers without a CUDA runtime of their own (Queue, crates/neura-gpu/src/context.rs:287). */
+int32_t neura_cuda_stream_create(nc_context *ctx, void **out_stream);
+int32_t neura_cuda_stream_destroy(nc_context *ctx, void *stream);
+
+/* Kernel launches issued through this context since it was opened (replays included). */
 uint64_t neura_cuda_launches(const nc_context *ctx);
 
 #ifdef __cplusplus

@@ -13,7 +13,9 @@ SYMBOLS = [
     "neura_cuda_sealed_bytes", "neura_cuda_alloc", "neura_cuda_free", "neura_cuda_host_alloc",
     "neura_cuda_host_free", "neura_cuda_write", "neura_cuda_read", "neura_cuda_sync", "neura_cuda_reserve",
     "neura_cuda_weight_seal", "neura_cuda_dequant", "neura_cuda_quantize", "neura_cuda_linear",
-    "neura_cuda_linear_host", "neura_cuda_launches",
+    "neura_cuda_linear_host", "neura_cuda_launches", "neura_cuda_stage", "neura_cuda_linear_staged",
+    "neura_cuda_capture_begin", "neura_cuda_capture_end", "neura_cuda_program_run", "neura_cuda_program_free",
+    "neura_cuda_stream_create", "neura_cuda_stream_destroy",
 ]
 
 
@@ -73,6 +75,14 @@ def load() -> ctypes.CDLL:
         "neura_cuda_linear": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, u64, p, u64, ctypes.POINTER(NcStep), u32]),
         "neura_cuda_linear_host": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, p, ctypes.POINTER(NcStep), u32]),
         "neura_cuda_launches": (u64, [p]),
+        "neura_cuda_stage": (i32, [p, p, p, u32, u64, u32, u32]),
+        "neura_cuda_linear_staged": (i32, [p, p, ctypes.POINTER(NcWeight), p, u64, ctypes.POINTER(NcStep), u32]),
+        "neura_cuda_capture_begin": (i32, [p, p]),
+        "neura_cuda_capture_end": (i32, [p, p, pp]),
+        "neura_cuda_program_run": (i32, [p, p, p]),
+        "neura_cuda_program_free": (i32, [p, p]),
+        "neura_cuda_stream_create": (i32, [p, pp]),
+        "neura_cuda_stream_destroy": (i32, [p, p]),
     }
     for name in SYMBOLS:
         fn = getattr(lib, name)  # raises AttributeError if the library does not export it

@@ -56,15 +56,26 @@ struct nc_context {
     int device = 0;
     int sms = 0;
     Region dig, cs, partial, counters, stage_x, stage_out;
+    uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
     uint64_t launches = 0;
+    bool capturing = false;
+    uint64_t capture_mark = 0;
+};
+
+struct nc_program {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches = 0;  // kernels one run replays
 };
 
 namespace {
 
 // Grows a scratch region (never shrinks).  Growing frees the old block, which
 // waits for the device: callers that cannot afford that call neura_cuda_reserve first.
-int32_t ensure(Region &region, uint64_t bytes, bool zero) {
+int32_t ensure(nc_context *ctx, Region &region, uint64_t bytes, bool zero) {
     if (region.bytes >= bytes) return 0;
+    if (ctx->capturing)
+        return refuse(kBadState, "a recorded program may not grow the scratch: call neura_cuda_reserve for its largest product first");
     if (region.ptr) NC_CUDA(cudaFree(region.ptr));
     region.ptr = nullptr;
     region.bytes = 0;
@@ -115,8 +126,8 @@ int32_t launch_gemv(nc_context *ctx, cudaStream_t stream, uint32_t element, Gemv
     const GemvPlan plan = plan_gemv(ctx, element, n, k, resident);
     const uint64_t cells = (uint64_t)p.rows * 16;
     int32_t rc;
-    if ((rc = ensure(ctx->partial, (uint64_t)plan.ntiles * plan.maxp * cells * sizeof(float), false))) return rc;
-    if ((rc = ensure(ctx->counters, (uint64_t)plan.ntiles * sizeof(unsigned int), true))) return rc;
+    if ((rc = ensure(ctx, ctx->partial, (uint64_t)plan.ntiles * plan.maxp * cells * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->counters, (uint64_t)plan.ntiles * sizeof(unsigned int), true))) return rc;
     p.partial = (float *)ctx->partial.ptr;
     p.counters = (unsigned int *)ctx->counters.ptr;
     p.upt = plan.upt;
@@ -246,8 +257,8 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     const uint32_t pass = rows < kMaxRowsPerPass ? rows : kMaxRowsPerPass;
     const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
     int32_t rc;
-    if ((rc = ensure(ctx->dig, kpad * 3 * pass, false))) return rc;
-    if ((rc = ensure(ctx->cs, kpad / 32 * 3 * pass * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->dig, kpad * 3 * pass, false))) return rc;
+    if ((rc = ensure(ctx, ctx->cs, kpad / 32 * 3 * pass * sizeof(float), false))) return rc;
     // partial sums: the widest split is one unit per warp and two warps per tile ... bounded by the
     // plan for the narrowest block (32), computed with the resident grid of the largest kernel
     const uint32_t ntiles = (n + kTileRows - 1) / kTileRows;
@@ -255,13 +266,13 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
         if (k % block_elements(element)) continue;
         for (int resident = 1; resident <= 4; ++resident) {
             const GemvPlan plan = plan_gemv(ctx, element, n, k, resident);
-            if ((rc = ensure(ctx->partial, (uint64_t)plan.ntiles * plan.maxp * pass * 16 * sizeof(float), false)))
+            if ((rc = ensure(ctx, ctx->partial, (uint64_t)plan.ntiles * plan.maxp * pass * 16 * sizeof(float), false)))
                 return rc;
         }
     }
-    if ((rc = ensure(ctx->counters, (uint64_t)ntiles * sizeof(unsigned int), true))) return rc;
-    if ((rc = ensure(ctx->stage_x, (uint64_t)rows * k * sizeof(float), false))) return rc;
-    if ((rc = ensure(ctx->stage_out, (uint64_t)rows * n * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->counters, (uint64_t)ntiles * sizeof(unsigned int), true))) return rc;
+    if ((rc = ensure(ctx, ctx->stage_x, (uint64_t)rows * k * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->stage_out, (uint64_t)rows * n * sizeof(float), false))) return rc;
     return 0;
 }
 
@@ -325,72 +336,102 @@ int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, con
     return 0;
 }
 
+int32_t neura_cuda_stage(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                         uint32_t k, uint32_t element) {
+    if (!ctx || !x_dev) return refuse(kBadArgument, "staging needs a context and activations");
+    const uint32_t per = block_elements(element);
+    if (!per || !k || k % per)
+        return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
+    if (rows == 0 || rows > kMaxRowsPerPass)
+        return refuse(kBadArgument, "one staging holds 1 to %u rows, not %u", kMaxRowsPerPass, rows);
+    if (x_stride < k) return refuse(kBadArgument, "rows of %u activations overlap at stride %llu", k, (unsigned long long)x_stride);
+    if ((uintptr_t)x_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
+    const uint32_t ncols = rows * 3;
+    int32_t rc;
+    if ((rc = ensure(ctx, ctx->dig, kpad * ncols, false))) return rc;
+    if ((rc = ensure(ctx, ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
+    PrepParams prep;
+    prep.x = x_dev;
+    prep.x_stride = x_stride;
+    prep.dig = (int8_t *)ctx->dig.ptr;
+    prep.cs = (float *)ctx->cs.ptr;
+    prep.rows = rows;
+    prep.k = k;
+    prep.ncols = ncols;
+    prep.granule = element == NC_ELEMENT_Q4K ? 256 : 32;
+    prep.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
+    const uint64_t prep_warps = (uint64_t)rows * (kpad / 256);
+    prep_kernel<<<(unsigned int)((prep_warps + 3) / 4), 128, 0, (cudaStream_t)stream_>>>(prep);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+    ctx->staged_rows = rows;
+    ctx->staged_k = k;
+    ctx->staged_granule = prep.granule;
+    return 0;
+}
+
+int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight *w, float *out_dev,
+                                 uint64_t out_stride, const nc_step *chain, uint32_t n_steps) {
+    if (!ctx || !out_dev) return refuse(kBadArgument, "a product needs a context and an output");
+    int32_t rc;
+    if ((rc = check_weight(w))) return rc;
+    if (w->layout != NC_LAYOUT_TILED)
+        return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order");
+    const uint32_t granule = w->element == NC_ELEMENT_Q4K ? 256 : 32;
+    if (!ctx->staged_rows || ctx->staged_k != w->k || ctx->staged_granule != granule)
+        return refuse(kBadArgument, "the staged activations (%u rows of %u for blocks of %u) do not fit a [%u, %u] weight of element %u",
+                      ctx->staged_rows, ctx->staged_k, ctx->staged_granule, w->n, w->k, w->element);
+    if (out_stride < w->n)
+        return refuse(kBadArgument, "rows of %u outputs overlap at stride %llu", w->n, (unsigned long long)out_stride);
+    if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
+        return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
+    if ((uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    GemvParams p;
+    memset(&p, 0, sizeof p);
+    p.w = (const uint8_t *)w->data_dev;
+    p.dig = (const int8_t *)ctx->dig.ptr;
+    p.cs = (const float *)ctx->cs.ptr;
+    p.out = out_dev;
+    p.out_stride = out_stride;
+    p.n = w->n;
+    p.rows = ctx->staged_rows;
+    p.ncols = ctx->staged_rows * 3;
+    p.chain.n = n_steps;
+    for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
+    cudaStream_t stream = (cudaStream_t)stream_;
+    switch ((p.ncols + 7) / 8) {
+    case 1: return launch_gemv<1>(ctx, stream, w->element, p, w->n, w->k);
+    case 2: return launch_gemv<2>(ctx, stream, w->element, p, w->n, w->k);
+    case 3: return launch_gemv<3>(ctx, stream, w->element, p, w->n, w->k);
+    case 4: return launch_gemv<4>(ctx, stream, w->element, p, w->n, w->k);
+    case 5: return launch_gemv<5>(ctx, stream, w->element, p, w->n, w->k);
+    default: return launch_gemv<6>(ctx, stream, w->element, p, w->n, w->k);
+    }
+}
+
 int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_dev, uint32_t rows,
                           uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
                           uint32_t n_steps) {
     if (!ctx || !x_dev || !out_dev) return refuse(kBadArgument, "a product needs a context, activations and an output");
     int32_t rc;
     if ((rc = check_weight(w))) return rc;
-    if (w->layout != NC_LAYOUT_TILED)
-        return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order");
     if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
-    if (x_stride < w->k || out_stride < w->n)
-        return refuse(kBadArgument, "rows of %u activations and %u outputs overlap at strides %llu and %llu", w->k, w->n,
-                      (unsigned long long)x_stride, (unsigned long long)out_stride);
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
-    if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
-    cudaStream_t stream = (cudaStream_t)stream_;
-    const uint32_t granule = w->element == NC_ELEMENT_Q4K ? 256 : 32;
-    const uint64_t kpad = ((uint64_t)w->k + 255) / 256 * 256;
-
     for (uint32_t first = 0; first < rows; first += kMaxRowsPerPass) {
         const uint32_t pass = rows - first < kMaxRowsPerPass ? rows - first : kMaxRowsPerPass;
-        const uint32_t ncols = pass * 3;
-        if ((rc = ensure(ctx->dig, kpad * ncols, false))) return rc;
-        if ((rc = ensure(ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
-
-        PrepParams prep;
-        prep.x = x_dev + (uint64_t)first * x_stride;
-        prep.x_stride = x_stride;
-        prep.dig = (int8_t *)ctx->dig.ptr;
-        prep.cs = (float *)ctx->cs.ptr;
-        prep.rows = pass;
-        prep.k = w->k;
-        prep.ncols = ncols;
-        prep.granule = granule;
-        prep.vector = ((uintptr_t)prep.x % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
-        const uint64_t prep_warps = (uint64_t)pass * (kpad / 256);
-        prep_kernel<<<(unsigned int)((prep_warps + 3) / 4), 128, 0, stream>>>(prep);
-        ctx->launches++;
-        NC_CUDA(cudaGetLastError());
-
-        GemvParams p;
-        memset(&p, 0, sizeof p);
-        p.w = (const uint8_t *)w->data_dev;
-        p.dig = prep.dig;
-        p.cs = prep.cs;
-        p.out = out_dev + (uint64_t)first * out_stride;
-        p.out_stride = out_stride;
-        p.n = w->n;
-        p.rows = pass;
-        p.ncols = ncols;
-        p.chain.n = n_steps;
+        if ((rc = neura_cuda_stage(ctx, stream_, x_dev + (uint64_t)first * x_stride, pass, x_stride, w->k, w->element)))
+            return rc;
+        nc_step steps[NC_MAX_STEPS];
         for (uint32_t s = 0; s < n_steps; ++s) {
-            p.chain.step[s] = chain[s];
+            steps[s] = chain[s];
             if (chain[s].operand_dev)  // the operand is read at this pass's rows
-                p.chain.step[s].operand_dev = chain[s].operand_dev + (int64_t)first * chain[s].row_stride;
+                steps[s].operand_dev = chain[s].operand_dev + (int64_t)first * chain[s].row_stride;
         }
-        const int nt = (int)((ncols + 7) / 8);
-        switch (nt) {
-        case 1: rc = launch_gemv<1>(ctx, stream, w->element, p, w->n, w->k); break;
-        case 2: rc = launch_gemv<2>(ctx, stream, w->element, p, w->n, w->k); break;
-        case 3: rc = launch_gemv<3>(ctx, stream, w->element, p, w->n, w->k); break;
-        case 4: rc = launch_gemv<4>(ctx, stream, w->element, p, w->n, w->k); break;
-        case 5: rc = launch_gemv<5>(ctx, stream, w->element, p, w->n, w->k); break;
-        default: rc = launch_gemv<6>(ctx, stream, w->element, p, w->n, w->k); break;
-        }
-        if (rc) return rc;
+        if ((rc = neura_cuda_linear_staged(ctx, stream_, w, out_dev + (uint64_t)first * out_stride, out_stride, steps,
+                                           n_steps)))
+            return rc;
     }
     return 0;
 }
@@ -403,8 +444,8 @@ int32_t neura_cuda_linear_host(nc_context *ctx, void *stream_, const nc_weight *
     if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
     cudaStream_t stream = (cudaStream_t)stream_;
     const uint64_t x_bytes = (uint64_t)rows * w->k * sizeof(float), out_bytes = (uint64_t)rows * w->n * sizeof(float);
-    if ((rc = ensure(ctx->stage_x, x_bytes, false))) return rc;
-    if ((rc = ensure(ctx->stage_out, out_bytes, false))) return rc;
+    if ((rc = ensure(ctx, ctx->stage_x, x_bytes, false))) return rc;
+    if ((rc = ensure(ctx, ctx->stage_out, out_bytes, false))) return rc;
     NC_CUDA(cudaMemcpyAsync(ctx->stage_x.ptr, x_host, x_bytes, cudaMemcpyHostToDevice, stream));
     if ((rc = neura_cuda_linear(ctx, stream_, w, (const float *)ctx->stage_x.ptr, rows, w->k,
                                 (float *)ctx->stage_out.ptr, w->n, chain, n_steps)))
@@ -415,5 +456,67 @@ int32_t neura_cuda_linear_host(nc_context *ctx, void *stream_, const nc_weight *
 }
 
 uint64_t neura_cuda_launches(const nc_context *ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t neura_cuda_capture_begin(nc_context *ctx, void *stream) {
+    if (!ctx) return refuse(kBadArgument, "capture needs a context");
+    if (ctx->capturing) return refuse(kBadState, "this context is already recording a program");
+    if (!stream) return refuse(kBadArgument, "a program is recorded on a stream of its own, not the default stream");
+    NC_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    ctx->capture_mark = ctx->launches;
+    return 0;
+}
+
+int32_t neura_cuda_capture_end(nc_context *ctx, void *stream, nc_program **out) {
+    if (!ctx || !out) return refuse(kBadArgument, "capture needs a context and somewhere to put the program");
+    if (!ctx->capturing) return refuse(kBadState, "no program is being recorded");
+    ctx->capturing = false;
+    cudaGraph_t graph = nullptr;
+    NC_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &graph));
+    nc_program *program = new (std::nothrow) nc_program();
+    if (!program) return refuse(kBadState, "out of host memory");
+    program->graph = graph;
+    program->launches = ctx->launches - ctx->capture_mark;
+    ctx->launches = ctx->capture_mark;  // recording launched nothing
+    cudaError_t e = cudaGraphInstantiate(&program->exec, graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        delete program;
+        return cuda_refuse(e, "cudaGraphInstantiate");
+    }
+    *out = program;
+    return 0;
+}
+
+int32_t neura_cuda_program_run(nc_context *ctx, void *stream, nc_program *program) {
+    if (!ctx || !program || !program->exec) return refuse(kBadArgument, "run needs a context and a recorded program");
+    NC_CUDA(cudaGraphLaunch(program->exec, (cudaStream_t)stream));
+    ctx->launches += program->launches;
+    return 0;
+}
+
+int32_t neura_cuda_stream_create(nc_context *ctx, void **out_stream) {
+    if (!ctx || !out_stream) return refuse(kBadArgument, "stream_create needs a context and somewhere to put the stream");
+    cudaStream_t stream;
+    NC_CUDA(cudaSetDevice(ctx->device));
+    NC_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    *out_stream = (void *)stream;
+    return 0;
+}
+
+int32_t neura_cuda_stream_destroy(nc_context *ctx, void *stream) {
+    if (!ctx) return refuse(kBadArgument, "stream_destroy needs a context");
+    if (stream) NC_CUDA(cudaStreamDestroy((cudaStream_t)stream));
+    return 0;
+}
+
+int32_t neura_cuda_program_free(nc_context *ctx, nc_program *program) {
+    (void)ctx;
+    if (!program) return 0;
+    if (program->exec) cudaGraphExecDestroy(program->exec);
+    if (program->graph) cudaGraphDestroy(program->graph);
+    delete program;
+    return 0;
+}
 
 }  // extern "C"

@@ -1,0 +1,127 @@
+"""Qwen2.5-shaped decoders over the quantized-linear path.
+
+The wiring follows the reference's example model (examples/qwen/mlp.rs:29-36,
+attention.rs:98-153, model.rs:77-103): every projection is
+``graph.matmul(x, permute(W))`` over a ``decoder::matrix`` parameter, the MLP is
+``down(silu(gate(x)) * up(x))`` and residual adds ride the products as fused
+chain steps.  The shapes are the Qwen2.5 ones the benchmark configurations name
+(no delta-net layers, no attention gate).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+from .runtime import ADD, MUL, SILU, Q4K, Q8_0, DeviceTensor, Runtime, Step, Weight, payload_bytes
+
+
+@dataclass(frozen=True)
+class Config:
+    name: str
+    layers: int
+    hidden: int
+    heads: int
+    key_heads: int
+    head_width: int
+    feed_forward: int
+    vocab: int
+    element: int
+    floor: float = 1e-6          # RMSNorm epsilon
+    rope_base: float = 1e6
+    tied_head: bool = False      # logits against the token embedding (examples/qwen/model.rs:83)
+
+    @property
+    def query_width(self) -> int:
+        return self.heads * self.head_width
+
+    @property
+    def key_width(self) -> int:
+        return self.key_heads * self.head_width
+
+    def linears(self) -> List[tuple]:
+        """(name, n, k) of the projections of one layer, in call order."""
+        return [
+            ("attn_q", self.query_width, self.hidden),
+            ("attn_k", self.key_width, self.hidden),
+            ("attn_v", self.key_width, self.hidden),
+            ("attn_output", self.hidden, self.query_width),
+            ("ffn_gate", self.feed_forward, self.hidden),
+            ("ffn_up", self.feed_forward, self.hidden),
+            ("ffn_down", self.hidden, self.feed_forward),
+        ]
+
+    def weight_elements(self) -> int:
+        per_layer = sum(n * k for _, n, k in self.linears())
+        return self.layers * per_layer + self.vocab * self.hidden
+
+    def weight_bytes(self) -> int:
+        """GGUF payload bytes one decoded token streams (projections and the head)."""
+        return payload_bytes(self.element, self.weight_elements())
+
+
+QWEN25_05B_Q8 = Config("qwen2.5-0.5b-q8_0", 24, 896, 14, 2, 64, 4864, 151936, Q8_0, tied_head=True)
+QWEN25_7B_MLP_Q4K = Config("qwen2.5-7b-q4_k", 28, 3584, 28, 4, 128, 18944, 152064, Q4K)
+QWEN25_32B_Q4K = Config("qwen2.5-32b-q4_k", 64, 5120, 40, 8, 128, 27648, 152064, Q4K)
+
+PRESETS: Dict[str, Config] = {c.name: c for c in (QWEN25_05B_Q8, QWEN25_7B_MLP_Q4K, QWEN25_32B_Q4K)}
+
+
+def scaled(config: Config, layers: int, vocab: Optional[int] = None) -> Config:
+    """The same layer shapes with fewer layers (and a smaller vocabulary) for tests."""
+    return Config(f"{config.name}-{layers}l", layers, config.hidden, config.heads, config.key_heads,
+                  config.head_width, config.feed_forward, vocab or config.vocab, config.element, config.floor,
+                  config.rope_base, config.tied_head)
+
+
+class LinearStack:
+    """The projections of a decoder, called in order on one token's activations.
+
+    This is the part of a decode step the quantized-linear path owns: per layer
+    q/k/v (one staging of the normed hidden state), the output projection with
+    the residual add fused, gate and up (one staging; ``silu(gate) * up`` fused
+    into the up product) and down with its residual add, then the head.  What
+    sits between them in a full model (norms, RoPE, attention) is not part of it.
+    """
+
+    def __init__(self, rt: Runtime, config: Config, weights: Dict[str, Weight], rows: int = 1):
+        self.rt, self.config, self.weights, self.rows = rt, config, weights, rows
+        c = config
+        self.hidden = rt.tensor(rows, c.hidden)
+        self.qkv = rt.tensor(rows, c.query_width + 2 * c.key_width)
+        self.attended = rt.tensor(rows, c.query_width)
+        self.gate = rt.tensor(rows, c.feed_forward)
+        self.held = rt.tensor(rows, c.feed_forward)
+        self.logits = rt.tensor(rows, c.vocab)
+        widest_n = max(c.vocab, c.feed_forward)
+        rt.reserve(rows, widest_n, max(c.hidden, c.feed_forward, c.query_width))
+        self.program: Optional[int] = None
+
+    def layer(self, index: int) -> None:
+        rt, c, w = self.rt, self.config, self.weights
+        at = lambda name: w[f"blk.{index}.{name}.weight"]  # noqa: E731
+        rt.stage(self.hidden, c.element)
+        rt.linear_staged(at("attn_qkv"), self.qkv)
+        # stands where attention would: the query third of qkv feeds the output projection
+        rt.stage(self.qkv, c.element, k=c.query_width)
+        rt.linear_staged(at("attn_output"), self.hidden, [Step(ADD, self.hidden)])
+        rt.stage(self.hidden, c.element)
+        rt.linear_staged(at("ffn_gate"), self.gate, [Step(SILU)])
+        rt.linear_staged(at("ffn_up"), self.held, [Step(MUL, self.gate)])
+        rt.stage(self.held, c.element)
+        rt.linear_staged(at("ffn_down"), self.hidden, [Step(ADD, self.hidden)])
+
+    def token(self) -> None:
+        for index in range(self.config.layers):
+            self.layer(index)
+        self.rt.stage(self.hidden, self.config.element)
+        self.rt.linear_staged(self.weights["output.weight"], self.logits)
+
+    def record(self) -> int:
+        """Runtime::compile: one token's launches as a replayable program."""
+        self.rt.capture_begin()
+        self.token()
+        self.program = self.rt.capture_end()
+        return self.program
+
+    def launches_per_token(self) -> int:
+        return self.config.layers * 9 + 2

@@ -187,12 +187,23 @@ class Runtime:
         self.free(raw.ptr)
         return sealed
 
-    def seal_device(self, element: int, n: int, k: int, gguf_ptr: int) -> Weight:
-        nbytes = int(self._lib.neura_cuda_sealed_bytes(element, n, k))
-        dst = self.alloc(nbytes)
+    def sealed_bytes(self, element: int, n: int, k: int) -> int:
+        return int(self._lib.neura_cuda_sealed_bytes(element, n, k))
+
+    def seal_device(self, element: int, n: int, k: int, gguf_ptr: int, dst: Optional[int] = None) -> Weight:
+        """Seals a GGUF tensor already on the device; into ``dst`` if given (a caller that lays
+        several tensors of the same ``k`` end to end, each a multiple of 16 rows, gets one
+        weight of their rows stacked, e.g. q, k and v)."""
+        nbytes = self.sealed_bytes(element, n, k)
+        if dst is None:
+            dst = self.alloc(nbytes)
         _check(self._lib.neura_cuda_weight_seal(self._ctx, self.stream, element, n, k,
                                                 ctypes.c_void_p(gguf_ptr), ctypes.c_void_p(dst)))
         return Weight(dst, element, LAYOUT_TILED, n, k, nbytes)
+
+    def quantize_device(self, element: int, src_ptr: int, elements: int, dst_ptr: int) -> None:
+        _check(self._lib.neura_cuda_quantize(self._ctx, self.stream, element, ctypes.c_void_p(src_ptr), elements,
+                                             ctypes.c_void_p(dst_ptr)))
 
     def dequant(self, weight: Weight) -> np.ndarray:
         """unpack (crates/neura-precision/src/lib.rs:25) run on the device: [n, k] f32."""
@@ -246,6 +257,46 @@ class Runtime:
         rec = weight.record()
         _check(self._lib.neura_cuda_linear(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(x.ptr), rows,
                                            x.shape[-1], ctypes.c_void_p(out.ptr), out.shape[-1], arr, count))
+
+    def stage(self, x: DeviceTensor, element: int, rows: Optional[int] = None, k: Optional[int] = None) -> None:
+        """First half of ``linear``: rewrites up to 16 activation rows for the MMA kernels."""
+        rows = rows if rows is not None else x.rows
+        k = k if k is not None else x.shape[-1]
+        _check(self._lib.neura_cuda_stage(self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1], k, element))
+
+    def linear_staged(self, weight: Weight, out: DeviceTensor, chain: Optional[Sequence[Step]] = None,
+                      out_ptr: Optional[int] = None, out_stride: Optional[int] = None) -> None:
+        """Second half of ``linear``: the staged rows times ``weight``."""
+        arr, count = self._steps(chain, weight.n)
+        rec = weight.record()
+        _check(self._lib.neura_cuda_linear_staged(
+            self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(out_ptr if out_ptr is not None else out.ptr),
+            out_stride if out_stride is not None else out.shape[-1], arr, count))
+
+    # -- recorded programs --------------------------------------------------------
+    def new_stream(self) -> int:
+        out = ctypes.c_void_p()
+        _check(self._lib.neura_cuda_stream_create(self._ctx, ctypes.byref(out)))
+        return out.value
+
+    def use_stream(self, stream: int) -> None:
+        self.stream = ctypes.c_void_p(stream)
+
+    def capture_begin(self) -> None:
+        """Runtime::compile (runtime.rs:528): start recording the calls that follow."""
+        _check(self._lib.neura_cuda_capture_begin(self._ctx, self.stream))
+
+    def capture_end(self) -> int:
+        out = ctypes.c_void_p()
+        _check(self._lib.neura_cuda_capture_end(self._ctx, self.stream, ctypes.byref(out)))
+        return out.value
+
+    def run(self, program: int) -> None:
+        """Runtime::run (runtime.rs:833): replay a recorded program (asynchronous)."""
+        _check(self._lib.neura_cuda_program_run(self._ctx, self.stream, ctypes.c_void_p(program)))
+
+    def program_free(self, program: int) -> None:
+        _check(self._lib.neura_cuda_program_free(self._ctx, ctypes.c_void_p(program)))
 
     def linear_host(self, weight: Weight, x: np.ndarray, chain: Optional[Sequence[Step]] = None,
                     out: Optional[np.ndarray] = None) -> np.ndarray:

@@ -1,0 +1,62 @@
+"""Synthetic decoder weights made on the GPU: N(0, 0.02) numbers (torch's generator, used
+only as a source of random f32), quantised by the library's device packer and sealed.
+The benchmark uses this in place of a GGUF file; the tests use the oracle's packer."""
+from __future__ import annotations
+
+from typing import Dict
+
+from .qwen import Config
+from .runtime import Runtime, Weight, payload_bytes
+
+
+def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: float = 0.02,
+                      fuse_qkv: bool = True) -> Dict[str, Weight]:
+    import torch
+
+    device = torch.device("cuda", rt.device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    stream = torch.cuda.ExternalStream(rt.stream.value, device=device) if rt.stream.value else torch.cuda.current_stream(device)
+    shapes = config.linears()
+    biggest = max(max(n * k for _, n, k in shapes), 16 * 1024 * config.hidden)
+    numbers = torch.empty(biggest, dtype=torch.float32, device=device)
+    blocks = torch.empty(payload_bytes(config.element, biggest) + 16, dtype=torch.uint8, device=device)
+    weights: Dict[str, Weight] = {}
+
+    def make(n: int, k: int, dst=None) -> Weight:
+        with torch.cuda.stream(stream):
+            view = numbers[: n * k]
+            view.normal_(0.0, deviation, generator=gen)
+            rt.quantize_device(config.element, view.data_ptr(), n * k, blocks.data_ptr())
+            return rt.seal_device(config.element, n, k, blocks.data_ptr(), dst)
+
+    for layer in range(config.layers):
+        for name, n, k in shapes:
+            if fuse_qkv and name in ("attn_k", "attn_v"):
+                continue
+            if fuse_qkv and name == "attn_q":
+                parts = [config.query_width, config.key_width, config.key_width]
+                assert all(p % 16 == 0 for p in parts)
+                total = sum(parts)
+                base = rt.alloc(rt.sealed_bytes(config.element, total, k))
+                at = base
+                for p in parts:
+                    make(p, k, at)
+                    at += rt.sealed_bytes(config.element, p, k)
+                weights[f"blk.{layer}.attn_qkv.weight"] = Weight(base, config.element, 1, total, k, at - base)
+                continue
+            weights[f"blk.{layer}.{name}.weight"] = make(n, k)
+    # the head in slabs of rows so that the scratch stays small
+    k = config.hidden
+    total = config.vocab
+    base = rt.alloc(rt.sealed_bytes(config.element, total, k))
+    at, done = base, 0
+    while done < total:
+        rows = min(16 * 1024, total - done)
+        make(rows, k, at)
+        at += rt.sealed_bytes(config.element, rows, k)
+        done += rows
+    weights["output.weight"] = Weight(base, config.element, 1, total, k, at - base)
+    rt.sync()
+    del numbers, blocks
+    return weights
