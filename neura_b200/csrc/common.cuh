@@ -12,9 +12,9 @@ constexpr uint32_t kQ8Block = 32;       // crates/neura-abi/src/element.rs:35
 constexpr uint32_t kQ8Bytes = 34;       // element.rs:155-158
 constexpr uint32_t kSuperBlock = 256;   // element.rs:36
 constexpr uint32_t kQ4kBytes = 144;     // element.rs:159-162
-constexpr uint32_t kTileRows = 16;      // rows of one MMA tile (m16n8k32)
-constexpr uint32_t kQ4kUnit = kTileRows * kQ4kBytes;  // 2304 B: one tile x one super-block
-constexpr uint32_t kQ8Unit = kTileRows * kQ8Bytes;    // 544 B: one tile x one block
+constexpr uint32_t kTileRows = 32;      // rows of one tile of the sealed layout: two m16n8k32 MMA tiles
+constexpr uint32_t kQ4kUnit = 16 * kQ4kBytes;  // 2304 B: 16 rows x one super-block (half a unit)
+constexpr uint32_t kQ8Unit = 16 * kQ8Bytes;    // 544 B: 16 rows x one block (half a unit)
 
 // Fused epilogue, passed by value to kernels.
 struct Chain {

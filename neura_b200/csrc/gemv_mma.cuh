@@ -5,25 +5,38 @@
 // This stands in for template_run_matmul_folded and its per-format dots
 // (crates/neura-kernel/src/task/matmul.rs:376-517, dot.rs:471-542, :583-619).
 //
-// Work split.  A "unit" is one 16-row tile x one block of K (a Q4_K super-block or a
+// Work split.  A "unit" is one 32-row tile x one block of K (a Q4_K super-block or a
 // Q8_0 block); units are contiguous in memory in (tile, block) order.  Every warp of
 // the grid takes one contiguous, equally long run of units, so all SMs stream the same
 // number of bytes whatever N and K are.  A run may start or end inside a tile; such a
 // tile is finished by the last of its contributing warps to arrive (a counter per
 // tile, no waiting), which adds the partial sums in warp order, so results do not
 // depend on timing.
+//
+// Data movement.  Each warp owns a ring of shared-memory stages that one lane fills
+// with bulk asynchronous copies (cp.async.bulk, completion on an mbarrier), several
+// stages ahead of the MMA work, so the bytes in flight per SM do not depend on
+// registers.  Waits on those barriers are bounded: a warp that gives up raises the
+// status word, drains its own copies and leaves.
 #pragma once
 #include "common.cuh"
 
 namespace nc {
 
+constexpr int kGemvWarps = 4;            // warps per CTA (they never synchronise with each other)
+constexpr uint32_t kQ4kStage = 2 * kQ4kUnit;       // one 32-row unit: 4608 B
+constexpr uint32_t kQ8Group = 4;                   // 32-row units per stage
+constexpr uint32_t kQ8Stage = kQ8Group * 2 * kQ8Unit;  // 4352 B
+constexpr unsigned long long kWaitNanos = 2000000000ull;  // a warp gives up on a copy after two seconds
+
 struct GemvParams {
     const uint8_t *w;     // tiled weights
-    const int8_t *dig;    // activation digit planes
+    const uint8_t *dig;   // activation digit planes
     const float *cs;      // digit scales
     float *out;
-    float *partial;       // [tile][slot][rows][16] split-tile partial sums
+    float *partial;       // [tile][slot][rows][32] split-tile partial sums
     unsigned int *counters;  // [tile], zero between launches
+    unsigned int *status;    // raised when a bounded wait ran out
     uint64_t out_stride;
     uint32_t n, rows, ncols;
     uint32_t upt;         // units per tile (blocks along K)
@@ -33,6 +46,14 @@ struct GemvParams {
     Chain chain;
 };
 
+// D = A * B with a zero accumulator (the zeros are immediates, not registers).
+__device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -40,12 +61,62 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_s8s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// ---- shared-memory ring plumbing ----------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ unsigned long long global_nanos() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for a stage with a time limit; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long start = global_nanos();
+    for (;;) {
+#pragma unroll 1
+        for (int tries = 0; tries < 64; ++tries)
+            if (mbar_try(bar, parity)) return true;
+        if (global_nanos() - start > kWaitNanos) return false;
+    }
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds4(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
 }
 
 // Which warp owns unit u under the (q, r) split.
@@ -54,28 +125,30 @@ __device__ __forceinline__ uint32_t owner_of(uint64_t u, uint32_t q, uint32_t r)
     return u < head ? (uint32_t)(u / (q + 1)) : r + (uint32_t)((u - head) / q);
 }
 
-// Ends a warp's stretch [first_blk, end_blk) of tile `tile`: either finishes the tile
-// or leaves a partial for the last contributor to add up.  acc holds, per 8-column
-// MMA tile, (row g, col 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).
+// Ends a warp's stretch [first_blk, end_blk) of the 32-row tile `tile`: either finishes the
+// tile or leaves a partial for the last contributor to add up.  acc[h] holds, for rows
+// 16h..16h+15 and per 8-column MMA tile, (row g, col 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).
 template <int NT>
-__device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[NT][4], float *patch, uint32_t warp,
-                                           uint32_t tile, uint32_t first_blk, uint32_t end_blk) {
+__device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][NT][4], float *patch, uint32_t warp,
+                                        uint32_t tile, uint32_t first_blk, uint32_t end_blk) {
     const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     constexpr int W = NT * 8 + 1;  // padded row of the per-warp patch
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        patch[g * W + nt * 8 + 2 * t] = acc[nt][0];
-        patch[g * W + nt * 8 + 2 * t + 1] = acc[nt][1];
-        patch[(g + 8) * W + nt * 8 + 2 * t] = acc[nt][2];
-        patch[(g + 8) * W + nt * 8 + 2 * t + 1] = acc[nt][3];
-        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-    }
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            patch[(16 * h + g) * W + nt * 8 + 2 * t] = acc[h][nt][0];
+            patch[(16 * h + g) * W + nt * 8 + 2 * t + 1] = acc[h][nt][1];
+            patch[(16 * h + g + 8) * W + nt * 8 + 2 * t] = acc[h][nt][2];
+            patch[(16 * h + g + 8) * W + nt * 8 + 2 * t + 1] = acc[h][nt][3];
+            acc[h][nt][0] = acc[h][nt][1] = acc[h][nt][2] = acc[h][nt][3] = 0.0f;
+        }
     __syncwarp();
-    const uint32_t cells = p.rows * 16;
+    const uint32_t cells = p.rows * 32;
     const bool whole = first_blk == 0 && end_blk == p.upt;
     if (whole) {
         for (uint32_t idx = lane; idx < cells; idx += 32) {
-            const uint32_t rr = idx & 15, b = idx >> 4, col = tile * 16 + rr;
+            const uint32_t rr = idx & 31, b = idx >> 5, col = tile * 32 + rr;
             const float v = (patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2];
             if (col < p.n) p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, v);
         }
@@ -85,7 +158,7 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[NT]
         const uint32_t count = last - first + 1, slot = warp - first;
         float *mine = p.partial + ((uint64_t)tile * p.maxp + slot) * cells;
         for (uint32_t idx = lane; idx < cells; idx += 32) {
-            const uint32_t rr = idx & 15, b = idx >> 4;
+            const uint32_t rr = idx & 31, b = idx >> 5;
             __stcg(mine + idx, (patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2]);
         }
         __threadfence();
@@ -97,7 +170,7 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[NT]
             __threadfence();
             const float *all = p.partial + (uint64_t)tile * p.maxp * cells;
             for (uint32_t idx = lane; idx < cells; idx += 32) {
-                const uint32_t rr = idx & 15, b = idx >> 4, col = tile * 16 + rr;
+                const uint32_t rr = idx & 31, b = idx >> 5, col = tile * 32 + rr;
                 float v = 0.0f;
                 for (uint32_t s = 0; s < count; ++s) v += __ldcg(all + (uint64_t)s * cells + idx);
                 if (col < p.n) p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, v);
@@ -108,198 +181,196 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[NT]
     __syncwarp();
 }
 
-// ---------------------------------------------------------------------------------
-// Q4_K
-// ---------------------------------------------------------------------------------
-struct Q4kRegs {
-    uint4 h0, h1;  // headers of rows g and g+8
-    uint4 q[4];    // nibble groups: (.x,.y) row g, (.z,.w) row g+8
-};
-
-__device__ __forceinline__ void q4k_load(Q4kRegs &regs, const uint8_t *unit, uint32_t lane) {
-    const uint32_t g = lane >> 2;
-    regs.h0 = ld_stream16(unit + g * 16);
-    regs.h1 = ld_stream16(unit + (g + 8) * 16);
-#pragma unroll
-    for (int G = 0; G < 4; ++G) regs.q[G] = ld_stream16(unit + 256 + G * 512 + lane * 16);
-}
-
+// ---- Q4_K: one 16-row half of a unit ---------------------------------------------------
+// dg[nt][i] holds the digit fragments of sub-blocks 2i (.x,.y) and 2i+1 (.z,.w).
 template <int NT>
-__device__ __forceinline__ void q4k_unit(const GemvParams &p, const Q4kRegs &regs, uint32_t sb, float (&acc)[NT][4]) {
-    const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+__device__ __forceinline__ void q4k_half(uint32_t half_addr, const uint4 (&dg)[NT][4], const float (&c)[NT][2],
+                                         float (&acc)[NT][4]) {
+    const uint32_t lane = threadIdx.x & 31, g = lane >> 2;
+    const uint4 h0 = lds16(half_addr + g * 16), h1 = lds16(half_addr + (g + 8) * 16);
+    uint4 q[4];
+#pragma unroll
+    for (int G = 0; G < 4; ++G) q[G] = lds16(half_addr + 256 + G * 512 + lane * 16);
     uint32_t sc0[2], mn0[2], sc1[2], mn1[2];
-    q4k_scales(regs.h0.y, regs.h0.z, regs.h0.w, sc0, mn0);
-    q4k_scales(regs.h1.y, regs.h1.z, regs.h1.w, sc1, mn1);
+    q4k_scales(h0.y, h0.z, h0.w, sc0, mn0);
+    q4k_scales(h1.y, h1.z, h1.w, sc1, mn1);
     int qa[NT][4], ma[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) qa[nt][i] = ma[nt][i] = 0;
-    const int8_t *dig = p.dig + ((uint64_t)sb * 8 * p.ncols + g) * 32 + t * 8;
 #pragma unroll
     for (int G = 0; G < 4; ++G) {
 #pragma unroll
         for (int seat = 0; seat < 2; ++seat) {
             const int sub = G * 2 + seat;
-            const uint32_t a0 = (regs.q[G].x >> (4 * seat)) & 0x0f0f0f0fu;
-            const uint32_t a2 = (regs.q[G].y >> (4 * seat)) & 0x0f0f0f0fu;
-            const uint32_t a1 = (regs.q[G].z >> (4 * seat)) & 0x0f0f0f0fu;
-            const uint32_t a3 = (regs.q[G].w >> (4 * seat)) & 0x0f0f0f0fu;
-            const int s0 = (int)((sc0[sub >> 2] >> (8 * (sub & 3))) & 0xffu);
-            const int s1 = (int)((sc1[sub >> 2] >> (8 * (sub & 3))) & 0xffu);
+            const uint32_t a0 = (q[G].x >> (4 * seat)) & 0x0f0f0f0fu;
+            const uint32_t a2 = (q[G].y >> (4 * seat)) & 0x0f0f0f0fu;
+            const uint32_t a1 = (q[G].z >> (4 * seat)) & 0x0f0f0f0fu;
+            const uint32_t a3 = (q[G].w >> (4 * seat)) & 0x0f0f0f0fu;
+            const int s0 = (int)__byte_perm(sc0[sub >> 2], 0u, 0x4440u + (sub & 3));
+            const int s1 = (int)__byte_perm(sc1[sub >> 2], 0u, 0x4440u + (sub & 3));
             // the sub-block's min, replicated over the four bytes of an A register
             const uint32_t m0 = __byte_perm(mn0[sub >> 2], 0u, 0x1111u * (sub & 3));
             const uint32_t m1 = __byte_perm(mn1[sub >> 2], 0u, 0x1111u * (sub & 3));
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                uint2 b = make_uint2(0u, 0u);
-                if (nt * 8 + g < p.ncols)
-                    b = __ldg(reinterpret_cast<const uint2 *>(dig + ((uint64_t)sub * p.ncols + nt * 8) * 32));
-                int d[4] = {0, 0, 0, 0};
-                mma_u8s8(d, a0, a1, a2, a3, b.x, b.y);
+                const uint32_t b0 = seat ? dg[nt][G].z : dg[nt][G].x;
+                const uint32_t b1 = seat ? dg[nt][G].w : dg[nt][G].y;
+                int d[4];
+                mma_u8s8_zero(d, a0, a1, a2, a3, b0, b1);
                 qa[nt][0] += d[0] * s0;
                 qa[nt][1] += d[1] * s0;
                 qa[nt][2] += d[2] * s1;
                 qa[nt][3] += d[3] * s1;
-                mma_u8s8(ma[nt], m0, m1, m0, m1, b.x, b.y);
+                mma_u8s8(ma[nt], m0, m1, m0, m1, b0, b1);
             }
         }
     }
     // value = (d*sc)*q - dmin*m  (ggml.rs:341-346)  ->  sum = d*sum(sc*q*x) - dmin*sum(m*x)
-    const float d0 = half_bits_to_float(regs.h0.x & 0xffffu), n0 = half_bits_to_float(regs.h0.x >> 16);
-    const float d1 = half_bits_to_float(regs.h1.x & 0xffffu), n1 = half_bits_to_float(regs.h1.x >> 16);
+    const float d0 = half_bits_to_float(h0.x & 0xffffu), n0 = half_bits_to_float(h0.x >> 16);
+    const float d1 = half_bits_to_float(h1.x & 0xffffu), n1 = half_bits_to_float(h1.x >> 16);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const uint32_t col = nt * 8 + 2 * t;
-        const float c0 = col < p.ncols ? __ldg(p.cs + (uint64_t)sb * p.ncols + col) : 0.0f;
-        const float c1 = col + 1 < p.ncols ? __ldg(p.cs + (uint64_t)sb * p.ncols + col + 1) : 0.0f;
-        acc[nt][0] = fmaf(d0 * (float)qa[nt][0] - n0 * (float)ma[nt][0], c0, acc[nt][0]);
-        acc[nt][1] = fmaf(d0 * (float)qa[nt][1] - n0 * (float)ma[nt][1], c1, acc[nt][1]);
-        acc[nt][2] = fmaf(d1 * (float)qa[nt][2] - n1 * (float)ma[nt][2], c0, acc[nt][2]);
-        acc[nt][3] = fmaf(d1 * (float)qa[nt][3] - n1 * (float)ma[nt][3], c1, acc[nt][3]);
+        acc[nt][0] = fmaf(d0 * (float)qa[nt][0] - n0 * (float)ma[nt][0], c[nt][0], acc[nt][0]);
+        acc[nt][1] = fmaf(d0 * (float)qa[nt][1] - n0 * (float)ma[nt][1], c[nt][1], acc[nt][1]);
+        acc[nt][2] = fmaf(d1 * (float)qa[nt][2] - n1 * (float)ma[nt][2], c[nt][0], acc[nt][2]);
+        acc[nt][3] = fmaf(d1 * (float)qa[nt][3] - n1 * (float)ma[nt][3], c[nt][1], acc[nt][3]);
     }
 }
 
+// ---- Q8_0: one 16-row half of a unit ---------------------------------------------------
 template <int NT>
-__global__ void __launch_bounds__(256) gemv_q4k_kernel(const __grid_constant__ GemvParams p) {
-    extern __shared__ float patches[];
-    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const uint32_t warp = blockIdx.x * (blockDim.x >> 5) + wib;
-    if (warp >= p.nwarps) return;
-    float *patch = patches + wib * 16 * (NT * 8 + 1);
-    const uint64_t u0 = (uint64_t)warp * p.q + min(warp, p.r);
-    const uint64_t u1 = u0 + p.q + (warp < p.r ? 1u : 0u);
-    uint32_t tile = (uint32_t)(u0 / p.upt), blk = (uint32_t)(u0 % p.upt), first_blk = blk;
-    float acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-    const uint8_t *unit = p.w + u0 * kQ4kUnit;
-    Q4kRegs bufa, bufb;
-    q4k_load(bufa, unit, lane);
-    for (uint64_t u = u0; u < u1; u += 2) {
-        if (u + 1 < u1) q4k_load(bufb, unit + kQ4kUnit, lane);
-        q4k_unit<NT>(p, bufa, blk, acc);
-        if (++blk == p.upt || u + 1 == u1) {
-            flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk);
-            if (blk == p.upt) { blk = 0; ++tile; }
-            first_blk = blk;
-        }
-        if (u + 1 < u1) {
-            if (u + 2 < u1) q4k_load(bufa, unit + 2 * kQ4kUnit, lane);
-            q4k_unit<NT>(p, bufb, blk, acc);
-            if (++blk == p.upt || u + 2 == u1) {
-                flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk);
-                if (blk == p.upt) { blk = 0; ++tile; }
-                first_blk = blk;
-            }
-        }
-        unit += 2 * kQ4kUnit;
-    }
-}
-
-// ---------------------------------------------------------------------------------
-// Q8_0: four blocks of K per step
-// ---------------------------------------------------------------------------------
-constexpr int kQ8Group = 4;
-
-struct Q8Regs {
-    uint4 q[kQ8Group];      // (.x,.y) row g, (.z,.w) row g+8
-    uint32_t d[kQ8Group];   // fp16 scales of rows g (low half) and g+8 (high half)
-};
-
-// Loads the group of units starting at `u`; units past `last` (the matrix's final
-// unit) are clamped onto it, so every lane register is defined by an in-bounds load.
-__device__ __forceinline__ void q8_load(Q8Regs &regs, const uint8_t *w, uint64_t u, uint64_t last, uint32_t lane) {
-#pragma unroll
-    for (int i = 0; i < kQ8Group; ++i) {
-        const uint8_t *unit = w + min(u + i, last) * kQ8Unit;
-        regs.q[i] = ld_stream16(unit + lane * 16);
-        regs.d[i] = ld_stream4(unit + 512 + (lane >> 2) * 4);
-    }
-}
-
-template <int NT>
-__device__ __forceinline__ void q8_unit(const GemvParams &p, const uint4 &q, uint32_t dd, uint32_t blk,
+__device__ __forceinline__ void q8_half(uint32_t half_addr, const uint2 (&dg)[NT], const float (&c)[NT][2],
                                         float (&acc)[NT][4]) {
-    const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t lane = threadIdx.x & 31, g = lane >> 2;
+    const uint4 q = lds16(half_addr + lane * 16);   // (.x,.y) row g, (.z,.w) row g+8
+    const uint32_t dd = lds4(half_addr + 512 + g * 4);
     const float d0 = half_bits_to_float(dd & 0xffffu), d1 = half_bits_to_float(dd >> 16);
-    const int8_t *dig = p.dig + ((uint64_t)blk * p.ncols + g) * 32 + t * 8;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        uint2 b = make_uint2(0u, 0u);
-        if (nt * 8 + g < p.ncols) b = __ldg(reinterpret_cast<const uint2 *>(dig + nt * 8 * 32));
-        int d[4] = {0, 0, 0, 0};
-        mma_s8s8(d, q.x, q.z, q.y, q.w, b.x, b.y);
-        const uint32_t col = nt * 8 + 2 * t;
-        const float c0 = col < p.ncols ? __ldg(p.cs + (uint64_t)blk * p.ncols + col) : 0.0f;
-        const float c1 = col + 1 < p.ncols ? __ldg(p.cs + (uint64_t)blk * p.ncols + col + 1) : 0.0f;
-        acc[nt][0] = fmaf((float)d[0], d0 * c0, acc[nt][0]);
-        acc[nt][1] = fmaf((float)d[1], d0 * c1, acc[nt][1]);
-        acc[nt][2] = fmaf((float)d[2], d1 * c0, acc[nt][2]);
-        acc[nt][3] = fmaf((float)d[3], d1 * c1, acc[nt][3]);
+        int d[4];
+        mma_s8s8_zero(d, q.x, q.z, q.y, q.w, dg[nt].x, dg[nt].y);
+        acc[nt][0] = fmaf((float)d[0], d0 * c[nt][0], acc[nt][0]);
+        acc[nt][1] = fmaf((float)d[1], d0 * c[nt][1], acc[nt][1]);
+        acc[nt][2] = fmaf((float)d[2], d1 * c[nt][0], acc[nt][2]);
+        acc[nt][3] = fmaf((float)d[3], d1 * c[nt][1], acc[nt][3]);
     }
 }
 
-template <int NT>
-__global__ void __launch_bounds__(256) gemv_q8_0_kernel(const __grid_constant__ GemvParams p) {
-    extern __shared__ float patches[];
-    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const uint32_t warp = blockIdx.x * (blockDim.x >> 5) + wib;
+// ---- the streaming kernel ----------------------------------------------------------------
+template <bool Q4K, int NT, int STAGES>
+__global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
+    constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
+    constexpr uint32_t kUnit = Q4K ? kQ4kStage : 2 * kQ8Unit;  // bytes of one 32-row unit
+    constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;            // units per stage
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t warp = blockIdx.x * kGemvWarps + wib;
     if (warp >= p.nwarps) return;
-    float *patch = patches + wib * 16 * (NT * 8 + 1);
+    const uint32_t ring = smem_addr(smem) + wib * STAGES * kStage;
+    const uint32_t bars = smem_addr(smem) + kGemvWarps * STAGES * kStage + wib * STAGES * 8;
+    float *patch = reinterpret_cast<float *>(smem + kGemvWarps * STAGES * (kStage + 8)) + wib * 32 * (NT * 8 + 1);
+
     const uint64_t u0 = (uint64_t)warp * p.q + min(warp, p.r);
-    const uint64_t u1 = u0 + p.q + (warp < p.r ? 1u : 0u);
+    const uint32_t units = p.q + (warp < p.r ? 1u : 0u);
+    const uint32_t steps = (units + kGroup - 1) / kGroup;
+    const uint8_t *src = p.w + u0 * kUnit;
+    const uint64_t bytes = (uint64_t)units * kUnit;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(bars + s * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            if ((uint32_t)s < steps) {
+                const uint64_t at = (uint64_t)s * kStage;
+                const uint32_t len = (uint32_t)min((uint64_t)kStage, bytes - at);
+                mbar_expect(bars + s * 8, len);
+                bulk_load(ring + s * kStage, src + at, len, bars + s * 8);
+            }
+        }
+    }
+    __syncwarp();
+
     uint32_t tile = (uint32_t)(u0 / p.upt), blk = (uint32_t)(u0 % p.upt), first_blk = blk;
-    float acc[NT][4];
+    float acc[2][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-    const uint64_t last = (uint64_t)((p.n + 15) / 16) * p.upt - 1;
-    Q8Regs bufa, bufb;
-    q8_load(bufa, p.w, u0, last, lane);
-    for (uint64_t u = u0; u < u1; u += 2 * kQ8Group) {
-        q8_load(bufb, p.w, u + kQ8Group, last, lane);
+    for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int i = 0; i < kQ8Group; ++i) {
-            if (u + i < u1) {
-                q8_unit<NT>(p, bufa.q[i], bufa.d[i], blk, acc);
-                if (++blk == p.upt || u + i + 1 == u1) {
+        for (int nt = 0; nt < NT; ++nt) acc[h][nt][0] = acc[h][nt][1] = acc[h][nt][2] = acc[h][nt][3] = 0.0f;
+
+    uint32_t stage = 0, parity = 0, done = 0, step_failed = 0;
+    bool alive = true;
+    for (uint32_t step = 0; step < steps; ++step) {
+        if (!mbar_wait(bars + stage * 8, parity)) {
+            alive = false;
+            step_failed = step;
+            break;
+        }
+        const uint32_t buf = ring + stage * kStage;
+#pragma unroll
+        for (uint32_t j = 0; j < kGroup; ++j) {
+            if (done < units) {
+                float c[NT][2];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const uint32_t col = nt * 8 + 2 * t;
+                    c[nt][0] = col < p.ncols ? __ldg(p.cs + (uint64_t)blk * p.ncols + col) : 0.0f;
+                    c[nt][1] = col + 1 < p.ncols ? __ldg(p.cs + (uint64_t)blk * p.ncols + col + 1) : 0.0f;
+                }
+                if constexpr (Q4K) {
+                    uint4 dg[NT][4];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint32_t col = nt * 8 + g;
+                        const uint4 *from = reinterpret_cast<const uint4 *>(
+                            p.dig + (((uint64_t)blk * p.ncols + col) * 4 + t) * 64);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dg[nt][i] = col < p.ncols ? __ldg(from + i) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    q4k_half<NT>(buf, dg, c, acc[0]);
+                    q4k_half<NT>(buf + kQ4kUnit, dg, c, acc[1]);
+                } else {
+                    uint2 dg[NT];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint32_t col = nt * 8 + g;
+                        dg[nt] = col < p.ncols
+                            ? __ldg(reinterpret_cast<const uint2 *>(p.dig + ((uint64_t)blk * p.ncols + col) * 32 + t * 8))
+                            : make_uint2(0u, 0u);
+                    }
+                    q8_half<NT>(buf + j * 2 * kQ8Unit, dg, c, acc[0]);
+                    q8_half<NT>(buf + j * 2 * kQ8Unit + kQ8Unit, dg, c, acc[1]);
+                }
+                ++done;
+                if (++blk == p.upt || done == units) {
                     flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk);
                     if (blk == p.upt) { blk = 0; ++tile; }
                     first_blk = blk;
                 }
             }
         }
-        q8_load(bufa, p.w, u + 2 * kQ8Group, last, lane);
-#pragma unroll
-        for (int i = 0; i < kQ8Group; ++i) {
-            if (u + kQ8Group + i < u1) {
-                q8_unit<NT>(p, bufb.q[i], bufb.d[i], blk, acc);
-                if (++blk == p.upt || u + kQ8Group + i + 1 == u1) {
-                    flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk);
-                    if (blk == p.upt) { blk = 0; ++tile; }
-                    first_blk = blk;
-                }
-            }
+        __syncwarp();  // every lane has read this stage: it may be refilled
+        if (lane == 0 && step + STAGES < steps) {
+            const uint64_t at = (uint64_t)(step + STAGES) * kStage;
+            const uint32_t len = (uint32_t)min((uint64_t)kStage, bytes - at);
+            mbar_expect(bars + stage * 8, len);
+            bulk_load(buf, src + at, len, bars + stage * 8);
+        }
+        if (++stage == STAGES) { stage = 0; parity ^= 1u; }
+    }
+    if (!alive) {
+        // a copy never landed: say so, then give the copies still in flight a bounded time to
+        // land before the shared memory is handed back
+        if (lane == 0) atomicOr(p.status, 1u);
+        const uint32_t pending = min((uint32_t)STAGES, steps - step_failed);
+        for (uint32_t s = 0; s < pending; ++s) {
+            mbar_wait(bars + stage * 8, parity);
+            if (++stage == STAGES) { stage = 0; parity ^= 1u; }
         }
     }
 }

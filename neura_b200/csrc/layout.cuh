@@ -1,18 +1,20 @@
 // Weight layouts: the verbatim GGUF order, the tiled order the MMA kernels stream,
 // the seal kernel that turns the first into the second, and the bit-exact dequantiser.
 //
-// Tiled layout (NC_LAYOUT_TILED).  Rows are grouped in tiles of 16 (padded with zero
+// Tiled layout (NC_LAYOUT_TILED).  Rows are grouped in tiles of 32 (padded with zero
 // rows); a tile's blocks follow each other along K, tile after tile, so the whole
-// matrix is one contiguous stream of "units":
-//   Q4_K unit = 16 rows x 1 super-block = 2304 B
+// matrix is one contiguous stream of units of 32 rows x 1 block.  A unit is two halves
+// of 16 rows (rows 0-15, then rows 16-31), each laid out for one m16n8k32 MMA tile:
+//   Q4_K half = 16 rows x 1 super-block = 2304 B
 //     [0, 256)    16 headers of 16 B (d, dmin, 12 scale bytes), row i at 16*i
 //     [256, 2304) 4 nibble groups x 32 lanes x 16 B; lane (g = lane/4, t = lane%4) of
 //                 group G holds bytes [16+32G+8t, +8) of row g, then the same of row g+8
-//   Q8_0 unit = 16 rows x 1 block = 544 B
+//   Q8_0 half = 16 rows x 1 block = 544 B
 //     [0, 512)    32 lanes x 16 B: quants [8t, +8) of row g, then of row g+8
 //     [512, 544)  8 pairs of fp16 scales: (row g, row g+8) at 512 + 4g
-// A warp therefore fetches each unit with fully coalesced 16-byte loads and every lane
-// receives exactly the A-fragment bytes of mma.m16n8k32 (rows g and g+8, eight K values).
+// A unit is one contiguous run of bytes (a bulk copy moves it), and once it sits in
+// shared memory every lane reads exactly the A-fragment bytes of mma.m16n8k32 (rows g
+// and g+8, eight K values) with conflict-free 16-byte loads.
 #pragma once
 #include "common.cuh"
 
@@ -28,16 +30,16 @@ __device__ __forceinline__ uint32_t weight_byte(const WeightView &w, uint32_t ro
     if (w.element == NC_ELEMENT_Q4K) {
         const uint32_t nsb = w.k / kSuperBlock;
         if (w.layout == NC_LAYOUT_GGUF) return w.data[((uint64_t)row * nsb + blk) * kQ4kBytes + o];
-        const uint32_t tile = row / 16, rr = row % 16, g = rr % 8, hi = rr / 8;
-        const uint64_t unit = ((uint64_t)tile * nsb + blk) * kQ4kUnit;
+        const uint32_t tile = row / 32, half = (row % 32) / 16, rr = row % 16, g = rr % 8, hi = rr / 8;
+        const uint64_t unit = (((uint64_t)tile * nsb + blk) * 2 + half) * kQ4kUnit;
         if (o < 16) return w.data[unit + rr * 16 + o];
         const uint32_t qo = o - 16, G = qo / 32, r32 = qo % 32, t = r32 / 8, i = r32 % 8;
         return w.data[unit + 256 + G * 512 + (g * 4 + t) * 16 + hi * 8 + i];
     }
     const uint32_t nblk = w.k / kQ8Block;
     if (w.layout == NC_LAYOUT_GGUF) return w.data[((uint64_t)row * nblk + blk) * kQ8Bytes + o];
-    const uint32_t tile = row / 16, rr = row % 16, g = rr % 8, hi = rr / 8;
-    const uint64_t unit = ((uint64_t)tile * nblk + blk) * kQ8Unit;
+    const uint32_t tile = row / 32, half = (row % 32) / 16, rr = row % 16, g = rr % 8, hi = rr / 8;
+    const uint64_t unit = (((uint64_t)tile * nblk + blk) * 2 + half) * kQ8Unit;
     if (o < 2) return w.data[unit + 512 + g * 4 + hi * 2 + o];
     const uint32_t qo = o - 2, t = qo / 8, i = qo % 8;
     return w.data[unit + (g * 4 + t) * 16 + hi * 8 + i];
@@ -88,8 +90,8 @@ __global__ void dequant_kernel(WeightView w, float *out) {
 __global__ void seal_q4k_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, uint32_t nsb, uint64_t granules) {
     for (uint64_t d = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; d < granules;
          d += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t unit = d / 288;
-        const uint32_t within = (uint32_t)(d % 288);
+        const uint64_t unit = d / 576;
+        const uint32_t half = (uint32_t)(d % 576) / 288, within = (uint32_t)(d % 288);
         const uint32_t tile = (uint32_t)(unit / nsb), sb = (uint32_t)(unit % nsb);
         uint32_t rr, o;
         if (within < 32) {
@@ -100,7 +102,7 @@ __global__ void seal_q4k_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, u
             rr = lane / 4 + 8 * hi;
             o = 16 + 32 * G + 8 * (lane % 4);
         }
-        const uint32_t row = tile * 16 + rr;
+        const uint32_t row = tile * 32 + half * 16 + rr;
         uint2 v = make_uint2(0u, 0u);
         if (row < n) v = *reinterpret_cast<const uint2 *>(gguf + ((uint64_t)row * nsb + sb) * kQ4kBytes + o);
         *reinterpret_cast<uint2 *>(dst + d * 8) = v;
@@ -111,8 +113,8 @@ __global__ void seal_q4k_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, u
 __global__ void seal_q8_0_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, uint32_t nblk, uint64_t granules) {
     for (uint64_t d = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; d < granules;
          d += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t unit = d / 272;
-        const uint32_t within = (uint32_t)(d % 272);
+        const uint64_t unit = d / 544;
+        const uint32_t half = (uint32_t)(d % 544) / 272, within = (uint32_t)(d % 272);
         const uint32_t tile = (uint32_t)(unit / nblk), blk = (uint32_t)(unit % nblk);
         uint32_t rr, o;
         if (within < 256) {
@@ -124,7 +126,7 @@ __global__ void seal_q8_0_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, 
             rr = s / 2 + 8 * (s % 2);
             o = 0;
         }
-        const uint32_t row = tile * 16 + rr;
+        const uint32_t row = tile * 32 + half * 16 + rr;
         unsigned short v = 0;
         if (row < n)
             v = *reinterpret_cast<const unsigned short *>(gguf + ((uint64_t)row * nblk + blk) * kQ8Bytes + o);

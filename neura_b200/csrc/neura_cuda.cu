@@ -43,6 +43,7 @@ int32_t cuda_refuse(cudaError_t e, const char *what) {
 
 constexpr int32_t kBadArgument = -1;
 constexpr int32_t kBadState = -2;
+constexpr int32_t kDeviceRefusal = -3;
 constexpr uint32_t kMaxRowsPerPass = 16;  // activation rows one GEMV launch carries
 
 struct Region {
@@ -55,7 +56,7 @@ struct Region {
 struct nc_context {
     int device = 0;
     int sms = 0;
-    Region dig, cs, partial, counters, stage_x, stage_out;
+    Region dig, cs, partial, counters, status, stage_x, stage_out;
     uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
     uint64_t launches = 0;
     bool capturing = false;
@@ -103,42 +104,57 @@ GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t
     plan.ntiles = (n + kTileRows - 1) / kTileRows;
     plan.upt = k / block_elements(element);
     const uint64_t units = (uint64_t)plan.ntiles * plan.upt;
-    const uint64_t least = element == NC_ELEMENT_Q4K ? 2 : 8;  // units a warp should at least stream
-    uint64_t warps = (uint64_t)ctx->sms * resident_blocks_per_sm * 8;
+    const uint64_t least = element == NC_ELEMENT_Q4K ? 2 : 8;  // 32-row units a warp should at least stream
+    uint64_t warps = (uint64_t)ctx->sms * resident_blocks_per_sm * kGemvWarps;
     if (warps > units / least) warps = units / least;
     if (warps < 1) warps = 1;
     plan.nwarps = (uint32_t)warps;
     plan.q = (uint32_t)(units / warps);
     plan.r = (uint32_t)(units % warps);
     plan.maxp = (plan.upt + plan.q - 1) / plan.q + 1;
-    plan.blocks = (plan.nwarps + 7) / 8;
+    plan.blocks = (plan.nwarps + kGemvWarps - 1) / kGemvWarps;
     return plan;
 }
 
-template <int NT>
-int32_t launch_gemv(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
-    auto kernel = element == NC_ELEMENT_Q4K ? gemv_q4k_kernel<NT> : gemv_q8_0_kernel<NT>;
-    const size_t smem = 8 * 16 * (NT * 8 + 1) * sizeof(float);
-    int resident = 0;
-    NC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, 256, smem));
-    if (resident < 1) return refuse(kBadState, "the product kernel does not fit an SM");
-    if (resident > 4) resident = 4;
-    const GemvPlan plan = plan_gemv(ctx, element, n, k, resident);
-    const uint64_t cells = (uint64_t)p.rows * 16;
+constexpr int kStages = 3;
+
+template <bool Q4K, int NT>
+int32_t launch_gemv_as(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
+    auto kernel = gemv_stream_kernel<Q4K, NT, kStages>;
+    constexpr size_t stage = Q4K ? kQ4kStage : kQ8Stage;
+    constexpr size_t smem = kGemvWarps * kStages * (stage + 8) + kGemvWarps * 32 * (NT * 8 + 1) * sizeof(float);
+    static int resident[16] = {0};  // per device, filled on first use
+    if (resident[ctx->device & 15] == 0) {
+        NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int blocks = 0;
+        NC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kGemvWarps * 32, smem));
+        if (blocks < 1) return refuse(kBadState, "the product kernel does not fit an SM");
+        resident[ctx->device & 15] = blocks;
+    }
+    const GemvPlan plan = plan_gemv(ctx, element, n, k, resident[ctx->device & 15]);
+    const uint64_t cells = (uint64_t)p.rows * kTileRows;
     int32_t rc;
     if ((rc = ensure(ctx, ctx->partial, (uint64_t)plan.ntiles * plan.maxp * cells * sizeof(float), false))) return rc;
     if ((rc = ensure(ctx, ctx->counters, (uint64_t)plan.ntiles * sizeof(unsigned int), true))) return rc;
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
     p.partial = (float *)ctx->partial.ptr;
     p.counters = (unsigned int *)ctx->counters.ptr;
+    p.status = (unsigned int *)ctx->status.ptr;
     p.upt = plan.upt;
     p.nwarps = plan.nwarps;
     p.q = plan.q;
     p.r = plan.r;
     p.maxp = plan.maxp;
-    kernel<<<plan.blocks, 256, smem, stream>>>(p);
+    kernel<<<plan.blocks, kGemvWarps * 32, smem, stream>>>(p);
     ctx->launches++;
     NC_CUDA(cudaGetLastError());
     return 0;
+}
+
+template <int NT>
+int32_t launch_gemv(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
+    return element == NC_ELEMENT_Q4K ? launch_gemv_as<true, NT>(ctx, stream, element, p, n, k)
+                                     : launch_gemv_as<false, NT>(ctx, stream, element, p, n, k);
 }
 
 int32_t check_weight(const nc_weight *w) {
@@ -153,6 +169,17 @@ int32_t check_weight(const nc_weight *w) {
     if ((uintptr_t)w->data_dev % 16)
         return refuse(kBadArgument, "a weight starts on a 16-byte boundary");
     return 0;
+}
+
+// The device status word (the reference's refusal word, crates/neura-kernel/src/substrate.rs:93-100):
+// read after a synchronisation, non-zero when a kernel gave up on a bounded wait.
+int32_t check_status(nc_context *ctx) {
+    if (!ctx->status.ptr) return 0;
+    unsigned int word = 0;
+    NC_CUDA(cudaMemcpy(&word, ctx->status.ptr, sizeof word, cudaMemcpyDeviceToHost));
+    if (word == 0) return 0;
+    NC_CUDA(cudaMemset(ctx->status.ptr, 0, sizeof word));
+    return refuse(kDeviceRefusal, "a kernel gave up waiting for its own copies (status %u); its output is not valid", word);
 }
 
 }  // namespace
@@ -185,7 +212,7 @@ int32_t neura_cuda_open(int32_t device, nc_context **out) {
 int32_t neura_cuda_close(nc_context *ctx) {
     if (!ctx) return 0;
     cudaSetDevice(ctx->device);
-    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->partial, &ctx->counters, &ctx->stage_x, &ctx->stage_out})
+    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
     return 0;
@@ -248,7 +275,7 @@ int32_t neura_cuda_read(nc_context *ctx, void *stream, void *dst_host, const voi
 int32_t neura_cuda_sync(nc_context *ctx, void *stream) {
     if (!ctx) return refuse(kBadArgument, "sync needs a context");
     NC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    return 0;
+    return check_status(ctx);
 }
 
 int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k) {
@@ -264,13 +291,14 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     const uint32_t ntiles = (n + kTileRows - 1) / kTileRows;
     for (uint32_t element : {NC_ELEMENT_Q8_0, NC_ELEMENT_Q4K}) {
         if (k % block_elements(element)) continue;
-        for (int resident = 1; resident <= 4; ++resident) {
+        for (int resident = 1; resident <= 8; ++resident) {
             const GemvPlan plan = plan_gemv(ctx, element, n, k, resident);
-            if ((rc = ensure(ctx, ctx->partial, (uint64_t)plan.ntiles * plan.maxp * pass * 16 * sizeof(float), false)))
+            if ((rc = ensure(ctx, ctx->partial, (uint64_t)plan.ntiles * plan.maxp * pass * kTileRows * sizeof(float), false)))
                 return rc;
         }
     }
     if ((rc = ensure(ctx, ctx->counters, (uint64_t)ntiles * sizeof(unsigned int), true))) return rc;
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
     if ((rc = ensure(ctx, ctx->stage_x, (uint64_t)rows * k * sizeof(float), false))) return rc;
     if ((rc = ensure(ctx, ctx->stage_out, (uint64_t)rows * n * sizeof(float), false))) return rc;
     return 0;
@@ -390,7 +418,7 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     GemvParams p;
     memset(&p, 0, sizeof p);
     p.w = (const uint8_t *)w->data_dev;
-    p.dig = (const int8_t *)ctx->dig.ptr;
+    p.dig = (const uint8_t *)ctx->dig.ptr;
     p.cs = (const float *)ctx->cs.ptr;
     p.out = out_dev;
     p.out_stride = out_stride;
@@ -452,7 +480,7 @@ int32_t neura_cuda_linear_host(nc_context *ctx, void *stream_, const nc_weight *
         return rc;
     NC_CUDA(cudaMemcpyAsync(out_host, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, stream));
     NC_CUDA(cudaStreamSynchronize(stream));
-    return 0;
+    return check_status(ctx);
 }
 
 uint64_t neura_cuda_launches(const nc_context *ctx) { return ctx ? ctx->launches : 0; }

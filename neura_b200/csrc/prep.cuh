@@ -10,8 +10,10 @@
 // products are exact, so the result differs from a sequential f32 sum only by the
 // 2^-23 (relative to the granule's peak) rounding of v and by f32 accumulation order.
 //
-//   dig[kb][col][32]   int8, kb = 32-element block of K, col = 3*row + digit, natural element order
-//   cs[gi][col]        f32 2^-s * 256^digit, gi = exponent granule of K
+//   granule 32  (Q8_0): dig[kb][col][32]        int8, kb = 32-element block of K, col = 3*row + digit
+//   granule 256 (Q4_K): dig[sb][col][t][sub][8] int8, sb = super-block of K, sub = its 32-block,
+//                       t = which eight elements of that block (so an MMA lane's 64 bytes are contiguous)
+//   cs[gi][col]         f32 2^-s * 256^digit, gi = exponent granule of K
 #pragma once
 #include "common.cuh"
 
@@ -98,8 +100,10 @@ __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
             const uint32_t col = row * 3 + j;
-            *reinterpret_cast<uint2 *>(p.dig + ((uint64_t)kb * p.ncols + col) * 32 + (lane & 3) * 8) =
-                make_uint2(d[j][0], d[j][1]);
+            const uint64_t at = p.granule == 256
+                ? ((((uint64_t)chunk * p.ncols + col) * 4 + (lane & 3)) * 8 + (lane >> 2)) * 8
+                : ((uint64_t)kb * p.ncols + col) * 32 + (lane & 3) * 8;
+            *reinterpret_cast<uint2 *>(p.dig + at) = make_uint2(d[j][0], d[j][1]);
         }
         const bool writes = p.granule == 256 ? lane == 0 : (lane & 3) == 0;
         if (writes) {

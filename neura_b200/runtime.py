@@ -192,7 +192,7 @@ class Runtime:
 
     def seal_device(self, element: int, n: int, k: int, gguf_ptr: int, dst: Optional[int] = None) -> Weight:
         """Seals a GGUF tensor already on the device; into ``dst`` if given (a caller that lays
-        several tensors of the same ``k`` end to end, each a multiple of 16 rows, gets one
+        several tensors of the same ``k`` end to end, each a multiple of 32 rows, gets one
         weight of their rows stacked, e.g. q, k and v)."""
         nbytes = self.sealed_bytes(element, n, k)
         if dst is None:

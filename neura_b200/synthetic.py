@@ -36,7 +36,7 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
                 continue
             if fuse_qkv and name == "attn_q":
                 parts = [config.query_width, config.key_width, config.key_width]
-                assert all(p % 16 == 0 for p in parts)
+                assert all(p % 32 == 0 for p in parts)
                 total = sum(parts)
                 base = rt.alloc(rt.sealed_bytes(config.element, total, k))
                 at = base
