@@ -259,13 +259,51 @@ __device__ __forceinline__ void q8_half(uint32_t half_addr, const uint2 (&dg)[NT
 }
 
 // ---- the streaming kernel ----------------------------------------------------------------
+// Activation fragments of one stage (kGroup units): B operands of the MMAs and the digit scales.
+template <bool Q4K, int NT>
+struct StageFrags {
+    static constexpr int kUnits = Q4K ? 1 : (int)kQ8Group;
+    uint4 wide[Q4K ? NT : 1][4];          // Q4_K: sub-blocks 2i (.x,.y) and 2i+1 (.z,.w) of 8-column tile nt
+    uint2 narrow[Q4K ? 1 : kUnits][NT];   // Q8_0: one block per unit
+    float c[kUnits][NT][2];
+};
+
+template <bool Q4K, int NT>
+__device__ __forceinline__ void load_frags(StageFrags<Q4K, NT> &f, const GemvParams &p, uint32_t blk, uint32_t have) {
+    const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int j = 0; j < StageFrags<Q4K, NT>::kUnits; ++j) {
+        // units past the warp's run read the fragments of its last block; nothing uses them
+        const uint32_t at = (uint32_t)j < have ? blk : (blk == 0 ? p.upt - 1 : blk - 1);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t col = nt * 8 + 2 * t;
+            f.c[j][nt][0] = col < p.ncols ? __ldg(p.cs + (uint64_t)at * p.ncols + col) : 0.0f;
+            f.c[j][nt][1] = col + 1 < p.ncols ? __ldg(p.cs + (uint64_t)at * p.ncols + col + 1) : 0.0f;
+            const uint32_t mine = nt * 8 + g;
+            if constexpr (Q4K) {
+                const uint4 *from =
+                    reinterpret_cast<const uint4 *>(p.dig + (((uint64_t)at * p.ncols + mine) * 4 + t) * 64);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    f.wide[nt][i] = mine < p.ncols ? __ldg(from + i) : make_uint4(0u, 0u, 0u, 0u);
+            } else {
+                f.narrow[j][nt] = mine < p.ncols
+                    ? __ldg(reinterpret_cast<const uint2 *>(p.dig + ((uint64_t)at * p.ncols + mine) * 32 + t * 8))
+                    : make_uint2(0u, 0u);
+            }
+        }
+        if ((uint32_t)j < have && ++blk == p.upt) blk = 0;
+    }
+}
+
 template <bool Q4K, int NT, int STAGES>
 __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
     constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
     constexpr uint32_t kUnit = Q4K ? kQ4kStage : 2 * kQ8Unit;  // bytes of one 32-row unit
     constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;            // units per stage
     extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const uint32_t warp = blockIdx.x * kGemvWarps + wib;
     if (warp >= p.nwarps) return;
     const uint32_t ring = smem_addr(smem) + wib * STAGES * kStage;
@@ -278,6 +316,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __gr
     const uint8_t *src = p.w + u0 * kUnit;
     const uint64_t bytes = (uint64_t)units * kUnit;
 
+    // The weights do not depend on the kernel before this one: start streaming them at once.
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) mbar_init(bars + s * 8, 1);
@@ -294,6 +333,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __gr
         }
     }
     __syncwarp();
+    // Programmatic dependent launch: let the next kernel of the stream start its own
+    // prologue, then wait until the kernel before this one (the activation staging) is
+    // complete and visible.  Both are no-ops in a plain launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     uint32_t tile = (uint32_t)(u0 / p.upt), blk = (uint32_t)(u0 % p.upt), first_blk = blk;
     float acc[2][NT][4];
@@ -302,9 +346,14 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __gr
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[h][nt][0] = acc[h][nt][1] = acc[h][nt][2] = acc[h][nt][3] = 0.0f;
 
+    StageFrags<Q4K, NT> now, next;
+    load_frags<Q4K, NT>(now, p, blk, min(units, kGroup));
     uint32_t stage = 0, parity = 0, done = 0, step_failed = 0;
     bool alive = true;
     for (uint32_t step = 0; step < steps; ++step) {
+        // fragments of the following stage travel while this one is multiplied
+        const uint32_t ahead = done + kGroup;
+        if (ahead < units) load_frags<Q4K, NT>(next, p, (blk + kGroup) % p.upt, min(units - ahead, kGroup));
         if (!mbar_wait(bars + stage * 8, parity)) {
             alive = false;
             step_failed = step;
@@ -314,37 +363,12 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __gr
 #pragma unroll
         for (uint32_t j = 0; j < kGroup; ++j) {
             if (done < units) {
-                float c[NT][2];
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const uint32_t col = nt * 8 + 2 * t;
-                    c[nt][0] = col < p.ncols ? __ldg(p.cs + (uint64_t)blk * p.ncols + col) : 0.0f;
-                    c[nt][1] = col + 1 < p.ncols ? __ldg(p.cs + (uint64_t)blk * p.ncols + col + 1) : 0.0f;
-                }
                 if constexpr (Q4K) {
-                    uint4 dg[NT][4];
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const uint32_t col = nt * 8 + g;
-                        const uint4 *from = reinterpret_cast<const uint4 *>(
-                            p.dig + (((uint64_t)blk * p.ncols + col) * 4 + t) * 64);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            dg[nt][i] = col < p.ncols ? __ldg(from + i) : make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    q4k_half<NT>(buf, dg, c, acc[0]);
-                    q4k_half<NT>(buf + kQ4kUnit, dg, c, acc[1]);
+                    q4k_half<NT>(buf, now.wide, now.c[0], acc[0]);
+                    q4k_half<NT>(buf + kQ4kUnit, now.wide, now.c[0], acc[1]);
                 } else {
-                    uint2 dg[NT];
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const uint32_t col = nt * 8 + g;
-                        dg[nt] = col < p.ncols
-                            ? __ldg(reinterpret_cast<const uint2 *>(p.dig + ((uint64_t)blk * p.ncols + col) * 32 + t * 8))
-                            : make_uint2(0u, 0u);
-                    }
-                    q8_half<NT>(buf + j * 2 * kQ8Unit, dg, c, acc[0]);
-                    q8_half<NT>(buf + j * 2 * kQ8Unit + kQ8Unit, dg, c, acc[1]);
+                    q8_half<NT>(buf + j * 2 * kQ8Unit, now.narrow[j], now.c[j], acc[0]);
+                    q8_half<NT>(buf + j * 2 * kQ8Unit + kQ8Unit, now.narrow[j], now.c[j], acc[1]);
                 }
                 ++done;
                 if (++blk == p.upt || done == units) {
@@ -362,6 +386,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __gr
             bulk_load(buf, src + at, len, bars + stage * 8);
         }
         if (++stage == STAGES) { stage = 0; parity ^= 1u; }
+        now = next;
     }
     if (!alive) {
         // a copy never landed: say so, then give the copies still in flight a bounded time to

@@ -116,7 +116,26 @@ GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t
     return plan;
 }
 
-constexpr int kStages = 3;
+constexpr int kStages = 2;
+
+// Launches with the programmatic-stream-serialization attribute, so that a kernel's
+// prologue (for the product: its first weight copies) overlaps the tail of the kernel
+// before it; the kernels order themselves with griddepcontrol.wait.
+template <typename Params>
+cudaError_t launch_dependent(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             const Params &params) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, params);
+}
 
 template <bool Q4K, int NT>
 int32_t launch_gemv_as(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
@@ -145,9 +164,8 @@ int32_t launch_gemv_as(nc_context *ctx, cudaStream_t stream, uint32_t element, G
     p.q = plan.q;
     p.r = plan.r;
     p.maxp = plan.maxp;
-    kernel<<<plan.blocks, kGemvWarps * 32, smem, stream>>>(p);
+    NC_CUDA(launch_dependent(kernel, dim3(plan.blocks), dim3(kGemvWarps * 32), smem, stream, p));
     ctx->launches++;
-    NC_CUDA(cudaGetLastError());
     return 0;
 }
 
@@ -390,9 +408,9 @@ int32_t neura_cuda_stage(nc_context *ctx, void *stream_, const float *x_dev, uin
     prep.granule = element == NC_ELEMENT_Q4K ? 256 : 32;
     prep.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
     const uint64_t prep_warps = (uint64_t)rows * (kpad / 256);
-    prep_kernel<<<(unsigned int)((prep_warps + 3) / 4), 128, 0, (cudaStream_t)stream_>>>(prep);
+    NC_CUDA(launch_dependent(prep_kernel, dim3((unsigned int)((prep_warps + 3) / 4)), dim3(128), 0,
+                             (cudaStream_t)stream_, prep));
     ctx->launches++;
-    NC_CUDA(cudaGetLastError());
     ctx->staged_rows = rows;
     ctx->staged_k = k;
     ctx->staged_granule = prep.granule;

@@ -31,6 +31,10 @@ struct PrepParams {
 
 // One warp per (row, 256-element chunk): lane l owns elements [8l, 8l+8) of the chunk.
 __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
+    // Programmatic dependent launch: the product that follows may start fetching its
+    // weights now; the activations this kernel reads must be complete first.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t chunks = (p.k + 255) / 256;
     const uint64_t total = (uint64_t)p.rows * chunks;
