@@ -154,6 +154,23 @@ int32_t neura_cuda_stage(nc_context *ctx, void *stream, const float *x_dev, uint
 int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev,
                                  uint64_t out_stride, const nc_step *chain, uint32_t n_steps);
 
+/* No counterpart in the reference.  neura_cuda_linear for callers that may not touch the
+ * device allocator: a game loop stepping generation under a frame budget (where a
+ * cudaMalloc, or the device-wide wait a cudaFree implies, would blow the frame), or a host
+ * engine that owns all device memory and admits no third-party allocation.  Same result as
+ * neura_cuda_linear, but every byte of scratch comes from one fixed 16 MiB array inside the
+ * library image (each GPU that loads the library holds it until exit) and the call makes no
+ * cudaMalloc, cudaFree or other allocating call.
+ *  - limits: 1 to 4 rows, w->k <= 32768, w->n <= 262144; anything larger is refused with a
+ *    sentence in neura_cuda_last_error();
+ *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress):
+ *    make that first call outside any stream capture;
+ *  - all calls on a device share the array: two calls whose kernels can overlap on the GPU
+ *    (different streams without an ordering between them) race; order them. */
+int32_t neura_cuda_linear_static(nc_context *ctx, void *stream, const nc_weight *w, const float *x_dev,
+                                 uint32_t rows, uint64_t x_stride, float *out_dev, uint64_t out_stride,
+                                 const nc_step *chain, uint32_t n_steps);
+
 /* The same product called the way Runtime::{write, run, read} are (runtime.rs:1020,833,1064):
  * activations come from and results return to host memory; blocks until done. */
 int32_t neura_cuda_linear_host(nc_context *ctx, void *stream, const nc_weight *w, const float *x_host,

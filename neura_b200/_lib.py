@@ -15,7 +15,7 @@ SYMBOLS = [
     "neura_cuda_weight_seal", "neura_cuda_dequant", "neura_cuda_quantize", "neura_cuda_linear",
     "neura_cuda_linear_host", "neura_cuda_launches", "neura_cuda_stage", "neura_cuda_linear_staged",
     "neura_cuda_capture_begin", "neura_cuda_capture_end", "neura_cuda_program_run", "neura_cuda_program_free",
-    "neura_cuda_stream_create", "neura_cuda_stream_destroy",
+    "neura_cuda_stream_create", "neura_cuda_stream_destroy", "neura_cuda_linear_static",
 ]
 
 
@@ -83,6 +83,7 @@ def load() -> ctypes.CDLL:
         "neura_cuda_program_free": (i32, [p, p]),
         "neura_cuda_stream_create": (i32, [p, pp]),
         "neura_cuda_stream_destroy": (i32, [p, p]),
+        "neura_cuda_linear_static": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, u64, p, u64, ctypes.POINTER(NcStep), u32]),
     }
     for name in SYMBOLS:
         fn = getattr(lib, name)  # raises AttributeError if the library does not export it

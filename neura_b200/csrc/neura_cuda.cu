@@ -501,6 +501,129 @@ int32_t neura_cuda_linear_host(nc_context *ctx, void *stream_, const nc_weight *
     return check_status(ctx);
 }
 
+// ---------------------------------------------------------------------------------------
+// The product for callers that must not allocate.
+//
+// Everything neura_cuda_linear keeps in scratch that it may have to cudaMalloc (digit
+// planes, digit scales, split-tile partial sums, tile counters, the status word) lives
+// here in one fixed array inside the library image.  Every GPU whose context loads the
+// library carries these 16 MiB until the process exits.
+// ---------------------------------------------------------------------------------------
+constexpr uint64_t kStaticScratchBytes = 16ull << 20;
+constexpr uint32_t kStaticMaxRows = 4;
+constexpr uint32_t kStaticMaxK = 32768;
+constexpr uint32_t kStaticMaxN = 262144;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// `g_static_scratch` names a host-side shadow in host code, not device memory: the device
+// address has to be asked for, once per device, with that device current.
+static unsigned char *g_static_scratch_dev[64] = {nullptr};
+
+int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_dev,
+                                 uint32_t rows, uint64_t x_stride, float *out_dev, uint64_t out_stride,
+                                 const nc_step *chain, uint32_t n_steps) {
+    if (!ctx || !x_dev || !out_dev) return refuse(kBadArgument, "a product needs a context, activations and an output");
+    int32_t rc;
+    if ((rc = check_weight(w))) return rc;
+    if (w->layout != NC_LAYOUT_TILED)
+        return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order");
+    if (rows == 0 || rows > kStaticMaxRows || w->k > kStaticMaxK || w->n > kStaticMaxN)
+        return refuse(kBadArgument,
+                      "the allocation-free product holds scratch for at most %u rows against a [%u, %u] weight; "
+                      "%u rows against [%u, %u] need neura_cuda_linear",
+                      kStaticMaxRows, kStaticMaxN, kStaticMaxK, rows, w->n, w->k);
+    if (x_stride < w->k || out_stride < w->n)
+        return refuse(kBadArgument, "rows of %u activations and %u outputs overlap at strides %llu and %llu", w->k, w->n,
+                      (unsigned long long)x_stride, (unsigned long long)out_stride);
+    if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
+        return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
+    if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    if (ctx->device < 0 || ctx->device >= 64) return refuse(kBadState, "device %d is outside the table of scratch addresses", ctx->device);
+    cudaStream_t stream = (cudaStream_t)stream_;
+
+    // one-time set-up per device (the first call on a device; make it before any stream capture)
+    if (!g_static_scratch_dev[ctx->device]) {
+        NC_CUDA(cudaSetDevice(ctx->device));
+        unsigned char *address = nullptr;
+        NC_CUDA(cudaGetSymbolAddress((void **)&address, g_static_scratch));
+        if (!address) return refuse(kBadState, "the static scratch has no address on device %d", ctx->device);
+        g_static_scratch_dev[ctx->device] = address;
+    }
+    unsigned char *base = g_static_scratch_dev[ctx->device];
+
+    // carve: [status 256][counters][digit scales][digit planes][partial sums ...]
+    const uint32_t ncols = rows * 3;
+    const uint64_t kpad = ((uint64_t)w->k + 255) / 256 * 256;
+    const uint64_t counters_bytes = (uint64_t)(kStaticMaxN / kTileRows) * sizeof(unsigned int);
+    const uint64_t cs_bytes = (uint64_t)(kStaticMaxK / 32) * kStaticMaxRows * 3 * sizeof(float);
+    const uint64_t dig_bytes = (uint64_t)kStaticMaxK * kStaticMaxRows * 3;
+    unsigned int *status = (unsigned int *)base;
+    unsigned int *counters = (unsigned int *)(base + 256);
+    float *cs = (float *)(base + 256 + counters_bytes);
+    uint8_t *dig = base + 256 + counters_bytes + cs_bytes;
+    float *partial = (float *)(base + 256 + counters_bytes + cs_bytes + dig_bytes);
+    const uint64_t partial_room = kStaticScratchBytes - (256 + counters_bytes + cs_bytes + dig_bytes);
+
+    const bool q4k = w->element == NC_ELEMENT_Q4K;
+    const int nt = (int)((ncols + 7) / 8);  // 1 or 2 for up to four rows
+    void (*kernel)(GemvParams) = q4k ? (nt == 1 ? gemv_stream_kernel<true, 1, kStages> : gemv_stream_kernel<true, 2, kStages>)
+                                     : (nt == 1 ? gemv_stream_kernel<false, 1, kStages> : gemv_stream_kernel<false, 2, kStages>);
+    const size_t stage = q4k ? kQ4kStage : kQ8Stage;
+    const size_t smem = kGemvWarps * kStages * (stage + 8) + kGemvWarps * 32 * (nt * 8 + 1) * sizeof(float);
+    NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int resident = 0;
+    NC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kGemvWarps * 32, smem));
+    if (resident < 1) return refuse(kBadState, "the product kernel does not fit an SM");
+    const GemvPlan plan = plan_gemv(ctx, w->element, w->n, w->k, resident);
+    const uint64_t partial_need = (uint64_t)plan.ntiles * plan.maxp * rows * kTileRows * sizeof(float);
+    if (partial_need > partial_room)
+        return refuse(kBadArgument, "this product splits into %llu bytes of partial sums and the static scratch holds %llu",
+                      (unsigned long long)partial_need, (unsigned long long)partial_room);
+
+    // the array keeps whatever the last call left: the counters and the status word start at zero
+    NC_CUDA(cudaMemsetAsync(base, 0, 256 + counters_bytes, stream));
+
+    PrepParams prep;
+    prep.x = x_dev;
+    prep.x_stride = x_stride;
+    prep.dig = (int8_t *)dig;
+    prep.cs = cs;
+    prep.rows = rows;
+    prep.k = w->k;
+    prep.ncols = ncols;
+    prep.granule = q4k ? 256 : 32;
+    prep.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
+    const uint64_t prep_warps = (uint64_t)rows * (kpad / 256);
+    prep_kernel<<<(unsigned int)((prep_warps + 3) / 4), 128, 0, stream>>>(prep);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+
+    GemvParams p;
+    memset(&p, 0, sizeof p);
+    p.w = (const uint8_t *)w->data_dev;
+    p.dig = dig;
+    p.cs = cs;
+    p.out = out_dev;
+    p.partial = partial;
+    p.counters = counters;
+    p.status = status;
+    p.out_stride = out_stride;
+    p.n = w->n;
+    p.rows = rows;
+    p.ncols = ncols;
+    p.upt = plan.upt;
+    p.nwarps = plan.nwarps;
+    p.q = plan.q;
+    p.r = plan.r;
+    p.maxp = plan.maxp;
+    p.chain.n = n_steps;
+    for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
+    kernel<<<plan.blocks, kGemvWarps * 32, smem, stream>>>(p);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+    return 0;
+}
+
 uint64_t neura_cuda_launches(const nc_context *ctx) { return ctx ? ctx->launches : 0; }
 
 int32_t neura_cuda_capture_begin(nc_context *ctx, void *stream) {

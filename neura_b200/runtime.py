@@ -258,6 +258,18 @@ class Runtime:
         _check(self._lib.neura_cuda_linear(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(x.ptr), rows,
                                            x.shape[-1], ctypes.c_void_p(out.ptr), out.shape[-1], arr, count))
 
+    def linear_static(self, weight: Weight, x: DeviceTensor, out: DeviceTensor,
+                      chain: Optional[Sequence[Step]] = None, rows: Optional[int] = None) -> None:
+        """``linear`` for callers that may not allocate on the device (a frame-budgeted game
+        loop, a host engine that owns the device heap): up to 4 rows, scratch from a fixed
+        array inside the library instead of the context's growable regions."""
+        rows = rows if rows is not None else x.rows
+        arr, count = self._steps(chain, weight.n)
+        rec = weight.record()
+        _check(self._lib.neura_cuda_linear_static(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(x.ptr),
+                                                  rows, x.shape[-1], ctypes.c_void_p(out.ptr), out.shape[-1], arr,
+                                                  count))
+
     def stage(self, x: DeviceTensor, element: int, rows: Optional[int] = None, k: Optional[int] = None) -> None:
         """First half of ``linear``: rewrites up to 16 activation rows for the MMA kernels."""
         rows = rows if rows is not None else x.rows
