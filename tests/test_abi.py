@@ -1,0 +1,76 @@
+"""The C ABI without a GPU: the library builds, loads and exports what the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from neura_b200 import _lib, build
+
+    build.build()
+    return _lib.load()
+
+
+def declared_symbols():
+    with open(os.path.join(ROOT, "include", "neura_cuda.h")) as fh:
+        text = fh.read()
+    return sorted(set(re.findall(r"\b(neura_cuda_\w+)\s*\(", text)))
+
+
+def test_every_declared_entry_point_is_exported(lib):
+    from neura_b200 import _lib
+
+    names = declared_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in neura_cuda.h but not exported"
+    assert sorted(_lib.SYMBOLS) == names, "the ctypes table and the header disagree"
+
+
+def test_geometry_entry_points_need_no_device(lib):
+    assert lib.neura_cuda_payload_bytes(8, 32) == 34
+    assert lib.neura_cuda_payload_bytes(9, 256) == 144
+    assert lib.neura_cuda_payload_bytes(9, 18944 * 3584) == 38191104
+    assert lib.neura_cuda_payload_bytes(0, 10) == 40
+    assert lib.neura_cuda_payload_bytes(12, 256) == 0          # Q3_K is not on this path
+    # sealing pads rows to tiles of 32 and keeps the block bytes
+    assert lib.neura_cuda_sealed_bytes(9, 18944, 3584) == 38191104
+    assert lib.neura_cuda_sealed_bytes(9, 33, 256) == 64 * 144
+    assert lib.neura_cuda_sealed_bytes(8, 4864, 896) == 4630528
+    assert lib.neura_cuda_sealed_bytes(9, 16, 200) == 0
+
+
+def test_open_without_a_gpu_is_an_error_not_a_fallback(lib):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    handle = ctypes.c_void_p()
+    code = lib.neura_cuda_open(0, ctypes.byref(handle))
+    assert code != 0 and not handle.value
+    assert lib.neura_cuda_last_error()
+
+
+def test_the_package_has_no_cpu_path():
+    import neura_b200
+
+    with pytest.raises(neura_b200.NeuraCudaError):
+        import torch
+
+        if torch.cuda.is_available():
+            raise neura_b200.NeuraCudaError(0, "skipped: a GPU is present")
+        neura_b200.Runtime(0)
+
+
+def test_model_shapes_count_the_bytes_the_baseline_names():
+    from neura_b200 import qwen
+
+    assert qwen.QWEN25_32B_Q4K.weight_elements() == 31984189440
+    assert qwen.QWEN25_32B_Q4K.weight_bytes() == 17991106560
+    assert qwen.QWEN25_05B_Q8.weight_elements() == 493961216
+    assert qwen.QWEN25_05B_Q8.weight_bytes() == 524833792

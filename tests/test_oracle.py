@@ -1,0 +1,230 @@
+"""The CPU oracle against what the reference pins for this path (no GPU needed)."""
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "blocks.npz")
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def test_block_byte_counts_follow_the_abi(oracle):
+    # crates/neura-abi/tests/layout.rs:148-158 pins 32 -> 34 bytes and 256 -> 144 bytes
+    assert oracle.payload_bytes(oracle.Q8_0, 32) == 34
+    assert oracle.payload_bytes(oracle.Q8_0, 33) == 68
+    assert oracle.payload_bytes(oracle.Q4K, 256) == 144
+    assert oracle.payload_bytes(oracle.Q4K, 257) == 288
+    assert oracle.payload_bytes(oracle.Q8_0, 4864 * 896) == 4630528       # config 1
+    assert oracle.payload_bytes(oracle.Q4K, 18944 * 3584) == 38191104     # config 2
+    # pack() pads its bytes to whole 4-byte words (ggml.rs:17-18)
+    assert oracle.pack(oracle.Q8_0, np.ones(32, np.float32)).size == 36
+
+
+def test_half_conversion_is_ieee_round_to_nearest_even(oracle):
+    lib = oracle.lib()
+    halves = np.arange(65536, dtype=np.uint16)
+    expected = halves.view(np.float16).astype(np.float32)
+    got = np.array([lib.nro_f16_to_f32(int(h)) for h in halves], dtype=np.float32)
+    same = (bits(got) == bits(expected)) | (np.isnan(got) & np.isnan(expected))
+    assert same.all()
+    rng = np.random.default_rng(0)
+    values = (rng.standard_normal(20000) * 10.0 ** rng.integers(-9, 6, 20000)).astype(np.float32)
+    values = np.concatenate([values, np.array([0.0, -0.0, 65504, 65519.99, 65520, 5.96e-8, 2.98e-8, 2.9802322e-8,
+                                               6.1e-5, 6.0975552e-05, np.inf, -np.inf], dtype=np.float32)])
+    with np.errstate(over="ignore"):
+        want = values.astype(np.float16).view(np.uint16)
+    have = np.array([lib.nro_f32_to_f16(float(v)) for v in values], dtype=np.uint16)
+    assert np.array_equal(want, have)
+    # the one half the reference's own tests name: f16(0.25) (crates/neura-precision/tests/format.rs:232-234)
+    assert lib.nro_f32_to_f16(0.25) == 0x3400
+
+
+def test_bfloat16_rounds_to_nearest_even(oracle):
+    lib = oracle.lib()
+    # crates/neura-precision/src/lib.rs:325-329
+    assert lib.nro_bf16_rne(1.0) == 0x3F80
+    assert lib.nro_bf16_rne(float(np.float32(1.00390625))) == 0x3F80      # tie -> even (down)
+    assert lib.nro_bf16_rne(float(np.float32(1.01171875))) == 0x3F82      # tie -> even (up)
+    assert lib.nro_bf16_rne(float(np.float32(1.005))) == 0x3F81
+
+
+def test_the_prng_is_xorshift32_13_17_5(oracle):
+    # crates/neura-graph/src/init.rs:86-91, seeded seed|1 (tests/support/mod.rs:41-48)
+    state = 23 | 1
+    expected = []
+    for _ in range(16):
+        state ^= (state << 13) & 0xFFFFFFFF
+        state ^= state >> 17
+        state ^= (state << 5) & 0xFFFFFFFF
+        expected.append(np.float32(-1.0) + np.float32(2.0) * (np.float32(state >> 8) / np.float32(1 << 24)))
+    assert np.array_equal(bits(oracle.random(16, 23)), bits(np.array(expected, dtype=np.float32)))
+    # an even seed and the odd seed above it draw the same stream
+    assert np.array_equal(oracle.random(8, 22), oracle.random(8, 23))
+    normal = oracle.Stream(23).normal(20000)
+    assert abs(float(normal.mean())) < 0.03 and abs(float(normal.std()) - 1.0) < 0.03
+
+
+def ggml_q4k_reference(field: np.ndarray) -> np.ndarray:
+    """The published GGML Q4_K walk (dequantize_row_q4_K), written independently of the oracle."""
+    d = np.frombuffer(field[0:2].tobytes(), dtype=np.float16)[0].astype(np.float32)
+    dmin = np.frombuffer(field[2:4].tobytes(), dtype=np.float16)[0].astype(np.float32)
+    scales = field[4:16].astype(np.uint32)
+    qs = field[16:144]
+    out = []
+
+    def scale_min(j):
+        if j < 4:
+            return scales[j] & 63, scales[j + 4] & 63
+        return (scales[j + 4] & 0xF) | ((scales[j - 4] >> 6) << 4), (scales[j + 4] >> 4) | ((scales[j] >> 6) << 4)
+
+    for group in range(4):
+        chunk = qs[32 * group: 32 * group + 32]
+        sc1, m1 = scale_min(2 * group)
+        sc2, m2 = scale_min(2 * group + 1)
+        d1, min1 = np.float32(d * np.float32(sc1)), np.float32(dmin * np.float32(m1))
+        d2, min2 = np.float32(d * np.float32(sc2)), np.float32(dmin * np.float32(m2))
+        out.extend(np.float32(d1 * np.float32(q & 0xF)) - min1 for q in chunk)
+        out.extend(np.float32(d2 * np.float32(q >> 4)) - min2 for q in chunk)
+    return np.array(out, dtype=np.float32)
+
+
+def test_the_q4k_walk_agrees_across_three_restatements(oracle):
+    # ggml.rs:336-350 (unpack), fetch.rs:256-267 (device scalar fetch), and the published GGML layout
+    rng = np.random.default_rng(7)
+    for _ in range(8):
+        field = rng.integers(0, 256, 144, dtype=np.uint8)
+        field[0:2] = np.frombuffer(np.float16(rng.uniform(0.001, 0.1)).tobytes(), dtype=np.uint8)
+        field[2:4] = np.frombuffer(np.float16(rng.uniform(0.001, 0.1)).tobytes(), dtype=np.uint8)
+        walked = oracle.unpack(oracle.Q4K, 256, field)
+        fetched = np.array([oracle.fetch(oracle.Q4K, field, i) for i in range(256)], dtype=np.float32)
+        assert np.array_equal(bits(walked), bits(fetched))
+        assert np.array_equal(bits(walked), bits(ggml_q4k_reference(field)))
+
+
+def test_the_q8_0_walk_agrees_across_restatements(oracle):
+    rng = np.random.default_rng(8)
+    field = rng.integers(0, 256, 34 * 3, dtype=np.uint8)
+    for b in range(3):
+        field[34 * b: 34 * b + 2] = np.frombuffer(np.float16(rng.uniform(0.001, 0.1)).tobytes(), dtype=np.uint8)
+    walked = oracle.unpack(oracle.Q8_0, 96, field)
+    fetched = np.array([oracle.fetch(oracle.Q8_0, field, i) for i in range(96)], dtype=np.float32)
+    assert np.array_equal(bits(walked), bits(fetched))
+    for b in range(3):
+        d = np.frombuffer(field[34 * b: 34 * b + 2].tobytes(), dtype=np.float16)[0].astype(np.float32)
+        q = field[34 * b + 2: 34 * b + 34].view(np.int8).astype(np.float32)
+        assert np.array_equal(bits(walked[32 * b: 32 * b + 32]), bits(q * d))
+
+
+def test_six_bit_scales_survive_their_packing(oracle):
+    # put_scale_min_k4 / scale_min_k4 (ggml.rs:127-147): every sub-block keeps its own pair
+    w = np.zeros(256, dtype=np.float32)
+    for sub in range(8):
+        w[32 * sub: 32 * sub + 32] = np.linspace(-(sub + 1) * 0.01, (8 - sub) * 0.02, 32)
+    field = oracle.pack(oracle.Q4K, w)[:144]
+    back = oracle.unpack(oracle.Q4K, 256, field)
+    for sub in range(8):
+        span = w[32 * sub: 32 * sub + 32]
+        step = (span.max() - min(0.0, span.min())) / 15.0
+        assert np.abs(back[32 * sub: 32 * sub + 32] - span).max() <= step * 0.75 + 2e-3
+
+
+def test_round_trips_stay_within_half_a_step(oracle):
+    w = oracle.Stream(23).normal(64 * 256, 0.0, 0.02)
+    back = oracle.unpack(oracle.Q8_0, w.size, oracle.pack(oracle.Q8_0, w))
+    for b in range(w.size // 32):
+        block = w[32 * b: 32 * b + 32]
+        quantum = np.abs(block).max() / 127.0
+        # codes are taken with the f32 quantum and decoded with its fp16 rounding: 0.5 + 127 * 2^-11 steps
+        assert np.abs(back[32 * b: 32 * b + 32] - block).max() <= quantum * 0.57 + 1e-7
+    back = oracle.unpack(oracle.Q4K, w.size, oracle.pack(oracle.Q4K, w))
+    assert np.abs(back - w).max() < 0.02 * 0.35
+
+
+def test_zero_blocks_and_short_tails(oracle):
+    zeros = np.zeros(256, dtype=np.float32)
+    for element in (oracle.Q8_0, oracle.Q4K):
+        packed = oracle.pack(element, zeros)
+        assert np.array_equal(oracle.unpack(element, 256, packed), zeros)
+    # the last block is padded with zeros (ggml.rs:12-15) and unpack truncates (ggml.rs:36)
+    w = oracle.random(40, 5)
+    packed = oracle.pack(oracle.Q8_0, w)
+    assert packed.size == 68
+    assert oracle.unpack(oracle.Q8_0, 40, packed).size == 40
+    assert np.all(packed[34 + 2 + 8: 68] == 0)
+    with pytest.raises(ValueError):
+        oracle.unpack(oracle.Q8_0, 80, packed)   # fewer bytes than the shape packs (ggml.rs:25-30)
+
+
+def test_the_product_is_the_reference_tests_loop(oracle):
+    n, k, rows = 24, 512, 3
+    w = oracle.random(n * k, 23).reshape(n, k)
+    x = oracle.random(rows * k, 29).reshape(rows, k)
+    for element in (oracle.Q8_0, oracle.Q4K):
+        packed = oracle.pack_rows(element, w)
+        weight = oracle.unpack(element, n * k, packed).reshape(n, k)
+        expected = np.zeros((rows, n), dtype=np.float32)
+        for r in range(rows):          # crates/neura-runtime/tests/runtime.rs:72-83
+            for c in range(n):
+                total = np.float32(0.0)
+                for s in range(k):
+                    total = np.float32(total + np.float32(weight[c, s] * x[r, s]))
+                expected[r, c] = total
+        got = oracle.linear(element, packed, n, k, x)
+        assert np.array_equal(bits(got), bits(expected))
+        assert np.array_equal(bits(oracle.linear(element, packed, n, k, x, threads=4)), bits(expected))
+        assert np.array_equal(bits(oracle.matmul_f32(weight, x)), bits(expected))
+        assert np.abs(got - (weight.astype(np.float64) @ x.astype(np.float64).T).T).max() < 1e-3
+
+
+def test_the_chain_applies_ops_in_order_with_broadcast_operands(oracle):
+    n, k, rows = 16, 256, 2
+    w = oracle.random(n * k, 3).reshape(n, k)
+    x = oracle.random(rows * k, 4).reshape(rows, k)
+    packed = oracle.pack_rows(oracle.Q4K, w)
+    plain = oracle.linear(oracle.Q4K, packed, n, k, x)
+    bias = oracle.random(n, 5)
+    gate = oracle.random(rows * n, 6).reshape(rows, n)
+    got = oracle.linear(oracle.Q4K, packed, n, k, x, chain=[(oracle.ADD, bias), (oracle.SILU, None),
+                                                            (oracle.MUL, gate), (oracle.SUB, gate, True)])
+    y = plain + bias
+    y = y * (np.float32(1.0) / (np.float32(1.0) + np.exp(-y, dtype=np.float32)))
+    y = gate - y * gate
+    assert np.abs(got - y).max() < 1e-5
+    assert oracle.op_apply(oracle.SIGMOID, 0.0) == 0.5
+    assert oracle.op_apply(oracle.MAXIMUM, 1.0, 2.0) == 2.0
+
+
+def test_bf16_product_rounds_both_operands_first(oracle):
+    n, k = 8, 256
+    w = oracle.Stream(1).normal(n * k, 0.0, 0.02).reshape(n, k)
+    x = oracle.Stream(2).normal(k).reshape(1, k)
+    packed = oracle.pack_rows(oracle.Q4K, w)
+    weight = oracle.unpack(oracle.Q4K, n * k, packed).reshape(n, k)
+
+    def bf16(a):
+        b = bits(a).astype(np.uint64)
+        return (((b + 0x7FFF + ((b >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+    expected = (bf16(weight).astype(np.float64) @ bf16(x).astype(np.float64).T).T
+    got = oracle.linear(oracle.Q4K, packed, n, k, x, bf16=True)
+    assert np.abs(got - expected).max() < 1e-4
+
+
+def test_golden_vectors_still_hold(oracle):
+    golden = np.load(GOLDEN)
+    assert np.array_equal(bits(oracle.random(64, 23)), bits(golden["uniform_seed23"]))
+    assert np.allclose(oracle.Stream(23).normal(64, 0.0, 0.02), golden["normal_seed23"], rtol=0, atol=1e-8)
+    for name, element in (("q8_0", oracle.Q8_0), ("q4k", oracle.Q4K)):
+        w, packed = golden[f"{name}_weight"], golden[f"{name}_packed"]
+        n, k = w.shape
+        assert np.array_equal(oracle.pack_rows(element, w), packed)
+        assert np.array_equal(bits(oracle.unpack(element, n * k, packed)), bits(golden[f"{name}_unpacked"].reshape(-1)))
+        x = golden[f"{name}_x"]
+        assert np.array_equal(bits(oracle.linear(element, packed, n, k, x)), bits(golden[f"{name}_product"]))
+        chain = [(oracle.ADD, golden[f"{name}_bias"]), (oracle.SILU, None)]
+        assert np.allclose(oracle.linear(element, packed, n, k, x, chain=chain), golden[f"{name}_chain"], rtol=0, atol=1e-6)
+    assert np.array_equal(oracle.pack_rows(oracle.Q8_0, golden["edge_weight"]), golden["edge_q8_0"])
+    assert np.array_equal(oracle.pack_rows(oracle.Q4K, golden["edge_weight"]), golden["edge_q4k"])
