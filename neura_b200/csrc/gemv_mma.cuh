@@ -33,6 +33,7 @@ struct GemvParams {
     const uint8_t *w;     // tiled weights
     const uint8_t *dig;   // activation digit planes
     const float *cs;      // digit scales
+    const uint8_t *sums;  // Q4_K: MMA fragments of the per-sub-block digit sums
     float *out;
     float *partial;       // [tile][slot][rows][32] split-tile partial sums
     unsigned int *counters;  // [tile], zero between launches
@@ -119,10 +120,10 @@ __device__ __forceinline__ uint32_t lds4(uint32_t addr) {
     return v;
 }
 
-// Which warp owns unit u under the (q, r) split.
-__device__ __forceinline__ uint32_t owner_of(uint64_t u, uint32_t q, uint32_t r) {
-    const uint64_t head = (uint64_t)r * (q + 1);
-    return u < head ? (uint32_t)(u / (q + 1)) : r + (uint32_t)((u - head) / q);
+// Which warp owns unit u under the (q, r) split (the host keeps the unit count below 2^32).
+__device__ __forceinline__ uint32_t owner_of(uint32_t u, uint32_t q, uint32_t r) {
+    const uint32_t head = r * (q + 1);
+    return u < head ? u / (q + 1) : r + (u - head) / q;
 }
 
 // Ends a warp's stretch [first_blk, end_blk) of the 32-row tile `tile`: either finishes the
@@ -153,7 +154,7 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
             if (col < p.n) p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, v);
         }
     } else {
-        const uint64_t base = (uint64_t)tile * p.upt;
+        const uint32_t base = tile * p.upt;
         const uint32_t first = owner_of(base, p.q, p.r), last = owner_of(base + p.upt - 1, p.q, p.r);
         const uint32_t count = last - first + 1, slot = warp - first;
         float *mine = p.partial + ((uint64_t)tile * p.maxp + slot) * cells;
@@ -161,13 +162,17 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
             const uint32_t rr = idx & 31, b = idx >> 5;
             __stcg(mine + idx, (patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2]);
         }
-        __threadfence();
+        // the warp's stores are ordered before lane 0's fence by the warp barrier, and the fence
+        // makes them visible to the GPU before the arrival is counted
         __syncwarp();
         unsigned int seen = 0;
-        if (lane == 0) seen = atomicAdd(p.counters + tile, 1u);
+        if (lane == 0) {
+            __threadfence();
+            seen = atomicAdd(p.counters + tile, 1u);
+            __threadfence();
+        }
         seen = __shfl_sync(0xffffffffu, seen, 0);
         if (seen == count - 1) {
-            __threadfence();
             const float *all = p.partial + (uint64_t)tile * p.maxp * cells;
             for (uint32_t idx = lane; idx < cells; idx += 32) {
                 const uint32_t rr = idx & 31, b = idx >> 5, col = tile * 32 + rr;
@@ -182,11 +187,18 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
 }
 
 // ---- Q4_K: one 16-row half of a unit ---------------------------------------------------
-// dg[nt][i] holds the digit fragments of sub-blocks 2i (.x,.y) and 2i+1 (.z,.w).
+// dg[nt][i] holds the digit fragments of sub-blocks 2i (.x,.y) and 2i+1 (.z,.w); sf[nt] the
+// fragments of the per-sub-block digit sums, low byte (.x,.y) and high byte (.z,.w).
+//
+// Low nibbles are used as they are and high nibbles in place (16 * q, no shift), so the two
+// kinds are summed apart and joined as 16 * low + high with the 1/16 folded into d.
+// The min term sum_k m * x_k = m * (sum of the sub-block's digits) takes two MMAs for the whole
+// super-block: K slot 4t holds sub-block t (and 16 + 4t sub-block 4 + t), A = the 6-bit mins,
+// B = the low and the high byte of the digit sums (prep.cuh).
 template <int NT>
-__device__ __forceinline__ void q4k_half(uint32_t half_addr, const uint4 (&dg)[NT][4], const float (&c)[NT][2],
-                                         float (&acc)[NT][4]) {
-    const uint32_t lane = threadIdx.x & 31, g = lane >> 2;
+__device__ __forceinline__ void q4k_half(uint32_t half_addr, const uint4 (&dg)[NT][4], const uint4 (&sf)[NT],
+                                         const float (&c)[NT][2], float (&acc)[NT][4]) {
+    const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint4 h0 = lds16(half_addr + g * 16), h1 = lds16(half_addr + (g + 8) * 16);
     uint4 q[4];
 #pragma unroll
@@ -194,48 +206,66 @@ __device__ __forceinline__ void q4k_half(uint32_t half_addr, const uint4 (&dg)[N
     uint32_t sc0[2], mn0[2], sc1[2], mn1[2];
     q4k_scales(h0.y, h0.z, h0.w, sc0, mn0);
     q4k_scales(h1.y, h1.z, h1.w, sc1, mn1);
-    int qa[NT][4], ma[NT][4];
+    int lo[NT][4], hi[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) qa[nt][i] = ma[nt][i] = 0;
+        for (int i = 0; i < 4; ++i) lo[nt][i] = hi[nt][i] = 0;
 #pragma unroll
     for (int G = 0; G < 4; ++G) {
-#pragma unroll
-        for (int seat = 0; seat < 2; ++seat) {
-            const int sub = G * 2 + seat;
-            const uint32_t a0 = (q[G].x >> (4 * seat)) & 0x0f0f0f0fu;
-            const uint32_t a2 = (q[G].y >> (4 * seat)) & 0x0f0f0f0fu;
-            const uint32_t a1 = (q[G].z >> (4 * seat)) & 0x0f0f0f0fu;
-            const uint32_t a3 = (q[G].w >> (4 * seat)) & 0x0f0f0f0fu;
+        {
+            const int sub = G * 2;
             const int s0 = (int)__byte_perm(sc0[sub >> 2], 0u, 0x4440u + (sub & 3));
             const int s1 = (int)__byte_perm(sc1[sub >> 2], 0u, 0x4440u + (sub & 3));
-            // the sub-block's min, replicated over the four bytes of an A register
-            const uint32_t m0 = __byte_perm(mn0[sub >> 2], 0u, 0x1111u * (sub & 3));
-            const uint32_t m1 = __byte_perm(mn1[sub >> 2], 0u, 0x1111u * (sub & 3));
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint32_t b0 = seat ? dg[nt][G].z : dg[nt][G].x;
-                const uint32_t b1 = seat ? dg[nt][G].w : dg[nt][G].y;
                 int d[4];
-                mma_u8s8_zero(d, a0, a1, a2, a3, b0, b1);
-                qa[nt][0] += d[0] * s0;
-                qa[nt][1] += d[1] * s0;
-                qa[nt][2] += d[2] * s1;
-                qa[nt][3] += d[3] * s1;
-                mma_u8s8(ma[nt], m0, m1, m0, m1, b0, b1);
+                mma_u8s8_zero(d, q[G].x & 0x0f0f0f0fu, q[G].z & 0x0f0f0f0fu, q[G].y & 0x0f0f0f0fu,
+                              q[G].w & 0x0f0f0f0fu, dg[nt][G].x, dg[nt][G].y);
+                lo[nt][0] += d[0] * s0;
+                lo[nt][1] += d[1] * s0;
+                lo[nt][2] += d[2] * s1;
+                lo[nt][3] += d[3] * s1;
+            }
+        }
+        {
+            const int sub = G * 2 + 1;
+            const int s0 = (int)__byte_perm(sc0[sub >> 2], 0u, 0x4440u + (sub & 3));
+            const int s1 = (int)__byte_perm(sc1[sub >> 2], 0u, 0x4440u + (sub & 3));
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                int d[4];
+                mma_u8s8_zero(d, q[G].x & 0xf0f0f0f0u, q[G].z & 0xf0f0f0f0u, q[G].y & 0xf0f0f0f0u,
+                              q[G].w & 0xf0f0f0f0u, dg[nt][G].z, dg[nt][G].w);
+                hi[nt][0] += d[0] * s0;
+                hi[nt][1] += d[1] * s0;
+                hi[nt][2] += d[2] * s1;
+                hi[nt][3] += d[3] * s1;
             }
         }
     }
+    // A of the min MMAs: byte 0 of each register is the min of this lane's sub-block; the other
+    // bytes meet zero bytes of B
+    const uint32_t a0 = mn0[0] >> (8 * t), a2 = mn0[1] >> (8 * t);
+    const uint32_t a1 = mn1[0] >> (8 * t), a3 = mn1[1] >> (8 * t);
     // value = (d*sc)*q - dmin*m  (ggml.rs:341-346)  ->  sum = d*sum(sc*q*x) - dmin*sum(m*x)
-    const float d0 = half_bits_to_float(h0.x & 0xffffu), n0 = half_bits_to_float(h0.x >> 16);
-    const float d1 = half_bits_to_float(h1.x & 0xffffu), n1 = half_bits_to_float(h1.x >> 16);
+    const float d0 = half_bits_to_float(h0.x & 0xffffu) * 0.0625f, n0 = half_bits_to_float(h0.x >> 16);
+    const float d1 = half_bits_to_float(h1.x & 0xffffu) * 0.0625f, n1 = half_bits_to_float(h1.x >> 16);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        acc[nt][0] = fmaf(d0 * (float)qa[nt][0] - n0 * (float)ma[nt][0], c[nt][0], acc[nt][0]);
-        acc[nt][1] = fmaf(d0 * (float)qa[nt][1] - n0 * (float)ma[nt][1], c[nt][1], acc[nt][1]);
-        acc[nt][2] = fmaf(d1 * (float)qa[nt][2] - n1 * (float)ma[nt][2], c[nt][0], acc[nt][2]);
-        acc[nt][3] = fmaf(d1 * (float)qa[nt][3] - n1 * (float)ma[nt][3], c[nt][1], acc[nt][3]);
+        int ml[4], mh[4];
+        mma_u8s8_zero(ml, a0, a1, a2, a3, sf[nt].x, sf[nt].y);
+        mma_u8s8_zero(mh, a0, a1, a2, a3, sf[nt].z, sf[nt].w);
+        float qf[4], mf[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            qf[i] = (float)(lo[nt][i] * 16 + hi[nt][i]);
+            mf[i] = (float)(mh[i] * 256 + ml[i]);
+        }
+        acc[nt][0] = fmaf(d0 * qf[0] - n0 * mf[0], c[nt][0], acc[nt][0]);
+        acc[nt][1] = fmaf(d0 * qf[1] - n0 * mf[1], c[nt][1], acc[nt][1]);
+        acc[nt][2] = fmaf(d1 * qf[2] - n1 * mf[2], c[nt][0], acc[nt][2]);
+        acc[nt][3] = fmaf(d1 * qf[3] - n1 * mf[3], c[nt][1], acc[nt][3]);
     }
 }
 
@@ -264,41 +294,106 @@ template <bool Q4K, int NT>
 struct StageFrags {
     static constexpr int kUnits = Q4K ? 1 : (int)kQ8Group;
     uint4 wide[Q4K ? NT : 1][4];          // Q4_K: sub-blocks 2i (.x,.y) and 2i+1 (.z,.w) of 8-column tile nt
+    uint4 sums[Q4K ? NT : 1];             // Q4_K: digit sums per sub-block, low and high byte
     uint2 narrow[Q4K ? 1 : kUnits][NT];   // Q8_0: one block per unit
     float c[kUnits][NT][2];
 };
 
+// Loads the fragments of the `have` units that start at block `blk` of K (wrapping at the tile end).
 template <bool Q4K, int NT>
 __device__ __forceinline__ void load_frags(StageFrags<Q4K, NT> &f, const GemvParams &p, uint32_t blk, uint32_t have) {
     const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int j = 0; j < StageFrags<Q4K, NT>::kUnits; ++j) {
-        // units past the warp's run read the fragments of its last block; nothing uses them
-        const uint32_t at = (uint32_t)j < have ? blk : (blk == 0 ? p.upt - 1 : blk - 1);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const uint32_t col = nt * 8 + 2 * t;
-            f.c[j][nt][0] = col < p.ncols ? __ldg(p.cs + (uint64_t)at * p.ncols + col) : 0.0f;
-            f.c[j][nt][1] = col + 1 < p.ncols ? __ldg(p.cs + (uint64_t)at * p.ncols + col + 1) : 0.0f;
+            f.c[j][nt][0] = col < p.ncols ? __ldg(p.cs + blk * p.ncols + col) : 0.0f;
+            f.c[j][nt][1] = col + 1 < p.ncols ? __ldg(p.cs + blk * p.ncols + col + 1) : 0.0f;
             const uint32_t mine = nt * 8 + g;
+            const bool live = mine < p.ncols;
             if constexpr (Q4K) {
-                const uint4 *from =
-                    reinterpret_cast<const uint4 *>(p.dig + (((uint64_t)at * p.ncols + mine) * 4 + t) * 64);
+                const uint32_t entry = (blk * p.ncols + mine) * 4 + t;
+                const uint4 *from = reinterpret_cast<const uint4 *>(p.dig) + entry * 4u;
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    f.wide[nt][i] = mine < p.ncols ? __ldg(from + i) : make_uint4(0u, 0u, 0u, 0u);
+                for (int i = 0; i < 4; ++i) f.wide[nt][i] = live ? __ldg(from + i) : make_uint4(0u, 0u, 0u, 0u);
+                f.sums[nt] = live ? __ldg(reinterpret_cast<const uint4 *>(p.sums) + entry) : make_uint4(0u, 0u, 0u, 0u);
             } else {
-                f.narrow[j][nt] = mine < p.ncols
-                    ? __ldg(reinterpret_cast<const uint2 *>(p.dig + ((uint64_t)at * p.ncols + mine) * 32 + t * 8))
+                f.narrow[j][nt] = live
+                    ? __ldg(reinterpret_cast<const uint2 *>(p.dig + (blk * p.ncols + mine) * 32u + t * 8u))
                     : make_uint2(0u, 0u);
             }
         }
-        if ((uint32_t)j < have && ++blk == p.upt) blk = 0;
+        // units past the warp's run re-read its last block; nothing uses them
+        if ((uint32_t)(j + 1) < have && ++blk == p.upt) blk = 0;
     }
 }
 
 template <bool Q4K, int NT, int STAGES>
-__global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
+struct GemvWarp {
+    static constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
+    static constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;
+    const GemvParams &p;
+    uint32_t ring, bars;
+    float *patch;
+    const uint8_t *src;
+    uint64_t bytes;
+    uint32_t warp, units, steps;
+    uint32_t tile, blk, first_blk, done;
+    float acc[2][NT][4];
+
+    // Unit J of the stage at `buf`.
+    template <int J>
+    __device__ __forceinline__ void unit(uint32_t buf, const StageFrags<Q4K, NT> &f) {
+        if (done >= units) return;
+        if constexpr (Q4K) {
+            q4k_half<NT>(buf, f.wide, f.sums, f.c[0], acc[0]);
+            q4k_half<NT>(buf + kQ4kUnit, f.wide, f.sums, f.c[0], acc[1]);
+        } else {
+            q8_half<NT>(buf + J * 2 * kQ8Unit, f.narrow[J], f.c[J], acc[0]);
+            q8_half<NT>(buf + J * 2 * kQ8Unit + kQ8Unit, f.narrow[J], f.c[J], acc[1]);
+        }
+        ++done;
+        if (++blk == p.upt || done == units) {
+            flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk);
+            if (blk == p.upt) { blk = 0; ++tile; }
+            first_blk = blk;
+        }
+    }
+
+    // One stage: wait for its bytes, multiply, finish tiles that end in it, refill it.
+    // Returns false when the bounded wait ran out.
+    __device__ __forceinline__ bool run(uint32_t step, const StageFrags<Q4K, NT> &f) {
+        const uint32_t stage = step % STAGES, parity = (step / STAGES) & 1u;
+        if (!mbar_wait(bars + stage * 8, parity)) return false;
+        const uint32_t buf = ring + stage * kStage;
+        unit<0>(buf, f);
+        if constexpr (kGroup > 1) {
+            unit<1>(buf, f);
+            unit<2>(buf, f);
+            unit<3>(buf, f);
+        }
+        __syncwarp();  // every lane has read this stage: it may be refilled
+        if ((threadIdx.x & 31) == 0 && step + STAGES < steps) {
+            const uint64_t at = (uint64_t)(step + STAGES) * kStage;
+            const uint32_t len = (uint32_t)min((uint64_t)kStage, bytes - at);
+            mbar_expect(bars + stage * 8, len);
+            bulk_load(buf, src + at, len, bars + stage * 8);
+        }
+        return true;
+    }
+
+    // The block of K at which the stage after the current one starts.
+    __device__ __forceinline__ uint32_t block_after(uint32_t from) const {
+        uint32_t next = from + kGroup;
+        while (next >= p.upt) next -= p.upt;
+        return next;
+    }
+};
+
+template <bool Q4K, int NT, int STAGES>
+__global__ void __launch_bounds__(kGemvWarps * 32, NT <= 1 ? 4 : 1) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
+    static_assert(STAGES == 2 && kQ8Group == 4, "a pair of steps is unrolled by hand, and so are the four units of a Q8_0 stage");
     constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
     constexpr uint32_t kUnit = Q4K ? kQ4kStage : 2 * kQ8Unit;  // bytes of one 32-row unit
     constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;            // units per stage
@@ -306,29 +401,30 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __gr
     const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const uint32_t warp = blockIdx.x * kGemvWarps + wib;
     if (warp >= p.nwarps) return;
-    const uint32_t ring = smem_addr(smem) + wib * STAGES * kStage;
-    const uint32_t bars = smem_addr(smem) + kGemvWarps * STAGES * kStage + wib * STAGES * 8;
-    float *patch = reinterpret_cast<float *>(smem + kGemvWarps * STAGES * (kStage + 8)) + wib * 32 * (NT * 8 + 1);
-
-    const uint64_t u0 = (uint64_t)warp * p.q + min(warp, p.r);
-    const uint32_t units = p.q + (warp < p.r ? 1u : 0u);
-    const uint32_t steps = (units + kGroup - 1) / kGroup;
-    const uint8_t *src = p.w + u0 * kUnit;
-    const uint64_t bytes = (uint64_t)units * kUnit;
+    GemvWarp<Q4K, NT, STAGES> w{p};
+    w.ring = smem_addr(smem) + wib * STAGES * kStage;
+    w.bars = smem_addr(smem) + kGemvWarps * STAGES * kStage + wib * STAGES * 8;
+    w.patch = reinterpret_cast<float *>(smem + kGemvWarps * STAGES * (kStage + 8)) + wib * 32 * (NT * 8 + 1);
+    const uint32_t u0 = warp * p.q + min(warp, p.r);
+    w.warp = warp;
+    w.units = p.q + (warp < p.r ? 1u : 0u);
+    w.steps = (w.units + kGroup - 1) / kGroup;
+    w.src = p.w + (uint64_t)u0 * kUnit;
+    w.bytes = (uint64_t)w.units * kUnit;
 
     // The weights do not depend on the kernel before this one: start streaming them at once.
     if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(bars + s * 8, 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(w.bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
-            if ((uint32_t)s < steps) {
+            if ((uint32_t)s < w.steps) {
                 const uint64_t at = (uint64_t)s * kStage;
-                const uint32_t len = (uint32_t)min((uint64_t)kStage, bytes - at);
-                mbar_expect(bars + s * 8, len);
-                bulk_load(ring + s * kStage, src + at, len, bars + s * 8);
+                const uint32_t len = (uint32_t)min((uint64_t)kStage, w.bytes - at);
+                mbar_expect(w.bars + s * 8, len);
+                bulk_load(w.ring + s * kStage, w.src + at, len, w.bars + s * 8);
             }
         }
     }
@@ -339,64 +435,36 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_stream_kernel(const __gr
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    uint32_t tile = (uint32_t)(u0 / p.upt), blk = (uint32_t)(u0 % p.upt), first_blk = blk;
-    float acc[2][NT][4];
+    w.tile = u0 / p.upt;
+    w.blk = u0 % p.upt;
+    w.first_blk = w.blk;
+    w.done = 0;
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) acc[h][nt][0] = acc[h][nt][1] = acc[h][nt][2] = acc[h][nt][3] = 0.0f;
+        for (int nt = 0; nt < NT; ++nt) w.acc[h][nt][0] = w.acc[h][nt][1] = w.acc[h][nt][2] = w.acc[h][nt][3] = 0.0f;
 
-    StageFrags<Q4K, NT> now, next;
-    load_frags<Q4K, NT>(now, p, blk, min(units, kGroup));
-    uint32_t stage = 0, parity = 0, done = 0, step_failed = 0;
-    bool alive = true;
-    for (uint32_t step = 0; step < steps; ++step) {
-        // fragments of the following stage travel while this one is multiplied
-        const uint32_t ahead = done + kGroup;
-        if (ahead < units) load_frags<Q4K, NT>(next, p, (blk + kGroup) % p.upt, min(units - ahead, kGroup));
-        if (!mbar_wait(bars + stage * 8, parity)) {
-            alive = false;
-            step_failed = step;
-            break;
+    // Two fragment sets take turns: the set of the following stage travels while this one is multiplied.
+    StageFrags<Q4K, NT> even, odd;
+    load_frags<Q4K, NT>(even, p, w.blk, min(w.units, kGroup));
+    uint32_t failed = 0xffffffffu;
+    for (uint32_t step = 0; step < w.steps; step += 2) {
+        const bool second = step + 1 < w.steps;
+        if (second) load_frags<Q4K, NT>(odd, p, w.block_after(w.blk), min(w.units - (step + 1) * kGroup, kGroup));
+        if (!w.run(step, even)) { failed = step; break; }
+        if (second) {
+            if (step + 2 < w.steps)
+                load_frags<Q4K, NT>(even, p, w.block_after(w.blk), min(w.units - (step + 2) * kGroup, kGroup));
+            if (!w.run(step + 1, odd)) { failed = step + 1; break; }
         }
-        const uint32_t buf = ring + stage * kStage;
-#pragma unroll
-        for (uint32_t j = 0; j < kGroup; ++j) {
-            if (done < units) {
-                if constexpr (Q4K) {
-                    q4k_half<NT>(buf, now.wide, now.c[0], acc[0]);
-                    q4k_half<NT>(buf + kQ4kUnit, now.wide, now.c[0], acc[1]);
-                } else {
-                    q8_half<NT>(buf + j * 2 * kQ8Unit, now.narrow[j], now.c[j], acc[0]);
-                    q8_half<NT>(buf + j * 2 * kQ8Unit + kQ8Unit, now.narrow[j], now.c[j], acc[1]);
-                }
-                ++done;
-                if (++blk == p.upt || done == units) {
-                    flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk);
-                    if (blk == p.upt) { blk = 0; ++tile; }
-                    first_blk = blk;
-                }
-            }
-        }
-        __syncwarp();  // every lane has read this stage: it may be refilled
-        if (lane == 0 && step + STAGES < steps) {
-            const uint64_t at = (uint64_t)(step + STAGES) * kStage;
-            const uint32_t len = (uint32_t)min((uint64_t)kStage, bytes - at);
-            mbar_expect(bars + stage * 8, len);
-            bulk_load(buf, src + at, len, bars + stage * 8);
-        }
-        if (++stage == STAGES) { stage = 0; parity ^= 1u; }
-        now = next;
     }
-    if (!alive) {
+    if (failed != 0xffffffffu) {
         // a copy never landed: say so, then give the copies still in flight a bounded time to
         // land before the shared memory is handed back
         if (lane == 0) atomicOr(p.status, 1u);
-        const uint32_t pending = min((uint32_t)STAGES, steps - step_failed);
-        for (uint32_t s = 0; s < pending; ++s) {
-            mbar_wait(bars + stage * 8, parity);
-            if (++stage == STAGES) { stage = 0; parity ^= 1u; }
-        }
+        const uint32_t pending = min((uint32_t)STAGES, w.steps - failed);
+        for (uint32_t s = 0; s < pending; ++s)
+            mbar_wait(w.bars + ((failed + s) % STAGES) * 8, ((failed + s) / STAGES) & 1u);
     }
 }
 

@@ -56,7 +56,7 @@ struct Region {
 struct nc_context {
     int device = 0;
     int sms = 0;
-    Region dig, cs, partial, counters, status, stage_x, stage_out;
+    Region dig, cs, sums, partial, counters, status, stage_x, stage_out;
     uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
     uint64_t launches = 0;
     bool capturing = false;
@@ -103,7 +103,7 @@ GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t
     GemvPlan plan;
     plan.ntiles = (n + kTileRows - 1) / kTileRows;
     plan.upt = k / block_elements(element);
-    const uint64_t units = (uint64_t)plan.ntiles * plan.upt;
+    const uint64_t units = (uint64_t)plan.ntiles * plan.upt;  // below 2^32: n and k are 32-bit, units = n*k/8192 at most
     const uint64_t least = element == NC_ELEMENT_Q4K ? 2 : 8;  // 32-row units a warp should at least stream
     uint64_t warps = (uint64_t)ctx->sms * resident_blocks_per_sm * kGemvWarps;
     if (warps > units / least) warps = units / least;
@@ -230,7 +230,7 @@ int32_t neura_cuda_open(int32_t device, nc_context **out) {
 int32_t neura_cuda_close(nc_context *ctx) {
     if (!ctx) return 0;
     cudaSetDevice(ctx->device);
-    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out})
+    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
     return 0;
@@ -304,6 +304,7 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     int32_t rc;
     if ((rc = ensure(ctx, ctx->dig, kpad * 3 * pass, false))) return rc;
     if ((rc = ensure(ctx, ctx->cs, kpad / 32 * 3 * pass * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->sums, kpad / 256 * 3 * pass * 64, false))) return rc;
     // partial sums: the widest split is one unit per warp and two warps per tile ... bounded by the
     // plan for the narrowest block (32), computed with the resident grid of the largest kernel
     const uint32_t ntiles = (n + kTileRows - 1) / kTileRows;
@@ -397,11 +398,13 @@ int32_t neura_cuda_stage(nc_context *ctx, void *stream_, const float *x_dev, uin
     int32_t rc;
     if ((rc = ensure(ctx, ctx->dig, kpad * ncols, false))) return rc;
     if ((rc = ensure(ctx, ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->sums, kpad / 256 * ncols * 64, false))) return rc;
     PrepParams prep;
     prep.x = x_dev;
     prep.x_stride = x_stride;
     prep.dig = (int8_t *)ctx->dig.ptr;
     prep.cs = (float *)ctx->cs.ptr;
+    prep.sums = (uint32_t *)ctx->sums.ptr;
     prep.rows = rows;
     prep.k = k;
     prep.ncols = ncols;
@@ -438,6 +441,7 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     p.w = (const uint8_t *)w->data_dev;
     p.dig = (const uint8_t *)ctx->dig.ptr;
     p.cs = (const float *)ctx->cs.ptr;
+    p.sums = (const uint8_t *)ctx->sums.ptr;
     p.out = out_dev;
     p.out_stride = out_stride;
     p.n = w->n;
@@ -557,12 +561,14 @@ int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight
     const uint64_t counters_bytes = (uint64_t)(kStaticMaxN / kTileRows) * sizeof(unsigned int);
     const uint64_t cs_bytes = (uint64_t)(kStaticMaxK / 32) * kStaticMaxRows * 3 * sizeof(float);
     const uint64_t dig_bytes = (uint64_t)kStaticMaxK * kStaticMaxRows * 3;
+    const uint64_t sums_bytes = (uint64_t)(kStaticMaxK / 256) * kStaticMaxRows * 3 * 64;
     unsigned int *status = (unsigned int *)base;
     unsigned int *counters = (unsigned int *)(base + 256);
     float *cs = (float *)(base + 256 + counters_bytes);
     uint8_t *dig = base + 256 + counters_bytes + cs_bytes;
-    float *partial = (float *)(base + 256 + counters_bytes + cs_bytes + dig_bytes);
-    const uint64_t partial_room = kStaticScratchBytes - (256 + counters_bytes + cs_bytes + dig_bytes);
+    uint32_t *sums = (uint32_t *)(base + 256 + counters_bytes + cs_bytes + dig_bytes);
+    float *partial = (float *)(base + 256 + counters_bytes + cs_bytes + dig_bytes + sums_bytes);
+    const uint64_t partial_room = kStaticScratchBytes - (256 + counters_bytes + cs_bytes + dig_bytes + sums_bytes);
 
     const bool q4k = w->element == NC_ELEMENT_Q4K;
     const int nt = (int)((ncols + 7) / 8);  // 1 or 2 for up to four rows
@@ -588,6 +594,7 @@ int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight
     prep.x_stride = x_stride;
     prep.dig = (int8_t *)dig;
     prep.cs = cs;
+    prep.sums = sums;
     prep.rows = rows;
     prep.k = w->k;
     prep.ncols = ncols;
@@ -603,6 +610,7 @@ int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight
     p.w = (const uint8_t *)w->data_dev;
     p.dig = dig;
     p.cs = cs;
+    p.sums = (const uint8_t *)sums;
     p.out = out_dev;
     p.partial = partial;
     p.counters = counters;

@@ -14,6 +14,10 @@
 //   granule 256 (Q4_K): dig[sb][col][t][sub][8] int8, sb = super-block of K, sub = its 32-block,
 //                       t = which eight elements of that block (so an MMA lane's 64 bytes are contiguous)
 //   cs[gi][col]         f32 2^-s * 256^digit, gi = exponent granule of K
+//   granule 256 only:   sums[sb][col][t][4] u32: the B fragments of the two MMAs that take the Q4_K min
+//                       term.  S = sum of a sub-block's 32 digits (|S| <= 4096) = S0 + 256 S1 in int8
+//                       bytes; word 0 holds S0 of sub-block t in its low byte, word 1 S0 of sub-block
+//                       4 + t, words 2 and 3 the same for S1; the other bytes are zero.
 #pragma once
 #include "common.cuh"
 
@@ -24,6 +28,7 @@ struct PrepParams {
     uint64_t x_stride;
     int8_t *dig;
     float *cs;
+    uint32_t *sums;     // granule 256 only: [sb][col][t] x {low b0, low b1, high b0, high b1}, see below
     uint32_t rows, k, ncols;
     uint32_t granule;   // 256 or 32
     uint32_t vector;    // 1: rows start 16-byte aligned, so a lane may fetch float4
@@ -89,6 +94,7 @@ __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
         if (!live) continue;
         const float up = ldexpf(1.0f, s);
         uint32_t d[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+        int total[3] = {0, 0, 0};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             int q = finite ? __float2int_rn(v[i] * up) : 0;
@@ -96,6 +102,9 @@ __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
             q = (q - d0) >> 8;
             const int d1 = (int)(int8_t)(q & 255);
             const int d2 = (q - d1) >> 8;
+            total[0] += d0;
+            total[1] += d1;
+            total[2] += d2;
             d[0][i >> 2] |= (uint32_t)(d0 & 255) << (8 * (i & 3));
             d[1][i >> 2] |= (uint32_t)(d1 & 255) << (8 * (i & 3));
             d[2][i >> 2] |= (uint32_t)(d2 & 255) << (8 * (i & 3));
@@ -108,6 +117,22 @@ __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
                 ? ((((uint64_t)chunk * p.ncols + col) * 4 + (lane & 3)) * 8 + (lane >> 2)) * 8
                 : ((uint64_t)kb * p.ncols + col) * 32 + (lane & 3) * 8;
             *reinterpret_cast<uint2 *>(p.dig + at) = make_uint2(d[j][0], d[j][1]);
+        }
+        if (p.granule == 256) {
+            // (no lane has left the loop body: the chunks of a 256-granule are whole)
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                int s = total[j];
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                if ((lane & 3) == 0) {
+                    const uint32_t sub = lane >> 2, col = row * 3 + j;
+                    const int s0 = (int)(int8_t)(s & 255), s1 = (s - s0) >> 8;
+                    uint32_t *entry = p.sums + (((uint64_t)chunk * p.ncols + col) * 4 + (sub & 3)) * 4 + (sub >> 2);
+                    entry[0] = (uint32_t)(s0 & 255);
+                    entry[2] = (uint32_t)(s1 & 255);
+                }
+            }
         }
         const bool writes = p.granule == 256 ? lane == 0 : (lane & 3) == 0;
         if (writes) {
