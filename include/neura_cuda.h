@@ -154,6 +154,49 @@ int32_t neura_cuda_stage(nc_context *ctx, void *stream, const float *x_dev, uint
 int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev,
                                  uint64_t out_stride, const nc_step *chain, uint32_t n_steps);
 
+/* ---- the steps either side of the products in a decoder layer (one new row per sequence) ---- */
+
+/* rms_norm (crates/neura-decoder/src/op.rs:3-5 -> crates/neura-kernel/src/task/norm.rs:55-131):
+ *   y = x / sqrt(mean(x^2) + floor) * weight
+ * fused with neura_cuda_stage of y for weights of block format `element`, so that the products
+ * that follow (q/k/v, gate/up, the head) take neura_cuda_linear_staged directly.  `weight_dev`
+ * may be NULL; `normed_dev`, when not NULL, also receives y as f32. */
+int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                                  uint32_t k, const float *weight_dev, float floor, uint32_t element,
+                                  float *normed_dev, uint64_t normed_stride);
+
+/* rope over the full head width (crates/neura-decoder/src/rope.rs:3-12 -> crates/neura-kernel/src/task/rope.rs:48-122,
+ * half rotation, angle = position * base^(-2c/width)) applied in place to the query and key parts of
+ * fused q|k|v rows, then Cache::write (crates/neura-decoder/src/cache.rs:267-310): the turned key and
+ * the value of sequence b go to slot position_dev[b] of keys/values [batch][key_heads][capacity][width]. */
+int32_t neura_cuda_rope_cache(nc_context *ctx, void *stream, float *qkv_dev, uint64_t row_stride,
+                              const uint32_t *position_dev, float base, uint32_t batch, uint32_t heads,
+                              uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
+                              float *values_dev);
+
+/* Cache::attend (crates/neura-decoder/src/cache.rs:311-406 -> crates/neura-kernel/src/task/attention.rs:309-617):
+ * causal grouped-query attention of the new row of each sequence over slots 0..position_dev[b];
+ * query head h reads key head h / (heads / key_heads); f32 throughout. */
+int32_t neura_cuda_attend(nc_context *ctx, void *stream, const float *q_dev, uint64_t q_stride, const float *keys_dev,
+                          const float *values_dev, const uint32_t *position_dev, float scale, uint32_t batch,
+                          uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
+                          uint64_t out_stride);
+
+/* Sampling::Greedy -> graph.argmax (crates/neura-generate/src/sampling.rs:79-81,
+ * crates/neura-kernel/src/task/choice.rs:46-52): the lowest index wins a tie. */
+int32_t neura_cuda_argmax(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint32_t width,
+                          uint64_t stride, uint32_t *out_dev);
+
+/* graph.gather of a quantised embedding table (crates/neura-kernel/src/task/select.rs:29-49 with
+ * fetch_q8_0 / fetch_q4_k, fetch.rs:236-267): out[r] = dequantised row tokens_dev[r], bit-exact;
+ * the table may be in either layout (a tied head is sealed). */
+int32_t neura_cuda_embed(nc_context *ctx, void *stream, const nc_weight *table, const uint32_t *tokens_dev,
+                         uint32_t rows, float *out_dev, uint64_t out_stride);
+
+/* cursor += by for every sequence (Batch::step's advance, crates/neura-generate/src/batch.rs:1716-1725),
+ * on the device so that a recorded decode step replays without host writes. */
+int32_t neura_cuda_advance(nc_context *ctx, void *stream, uint32_t *position_dev, uint32_t rows, uint32_t by);
+
 /* No counterpart in the reference.  neura_cuda_linear for callers that may not touch the
  * device allocator: a game loop stepping generation under a frame budget (where a
  * cudaMalloc, or the device-wide wait a cudaFree implies, would blow the frame), or a host

@@ -45,45 +45,39 @@ __device__ __forceinline__ uint32_t weight_byte(const WeightView &w, uint32_t ro
     return w.data[unit + (g * 4 + t) * 16 + hi * 8 + i];
 }
 
-// unpack: q8_0_values / q4_k_values (crates/neura-precision/src/ggml.rs:211-216, :336-350).
-// Each product is rounded to f32 on its own (no fma), which is what makes it bit-exact.
+// One element of unpack: q8_0_values / q4_k_values (crates/neura-precision/src/ggml.rs:211-216,
+// :336-350).  Each product is rounded to f32 on its own (no fma), which is what makes it bit-exact.
+__device__ __forceinline__ float dequant_at(const WeightView &w, uint32_t row, uint32_t at) {
+    if (w.element == NC_ELEMENT_Q8_0) {
+        const uint32_t blk = at / kQ8Block, lane = at % kQ8Block;
+        const float quantum = half_bits_to_float(weight_byte(w, row, blk, 0) | (weight_byte(w, row, blk, 1) << 8));
+        return __fmul_rn((float)(int8_t)weight_byte(w, row, blk, 2 + lane), quantum);
+    }
+    const uint32_t blk = at / kSuperBlock, within = at % kSuperBlock;
+    const uint32_t group = within / 64, seat = (within % 64) / 32, lane = within % 32;
+    const uint32_t sub = group * 2 + seat;
+    const float scale = half_bits_to_float(weight_byte(w, row, blk, 0) | (weight_byte(w, row, blk, 1) << 8));
+    const float min = half_bits_to_float(weight_byte(w, row, blk, 2) | (weight_byte(w, row, blk, 3) << 8));
+    uint32_t code, offset;  // scale_min_k4, ggml.rs:127-136
+    if (sub < 4) {
+        code = weight_byte(w, row, blk, 4 + sub) & 63u;
+        offset = weight_byte(w, row, blk, 4 + sub + 4) & 63u;
+    } else {
+        code = (weight_byte(w, row, blk, 4 + sub + 4) & 0x0fu) | ((weight_byte(w, row, blk, 4 + sub - 4) >> 6) << 4);
+        offset = (weight_byte(w, row, blk, 4 + sub + 4) >> 4) | ((weight_byte(w, row, blk, 4 + sub) >> 6) << 4);
+    }
+    const uint32_t packed = weight_byte(w, row, blk, 16 + group * 32 + lane);
+    const uint32_t quant = seat ? packed >> 4 : packed & 0x0fu;
+    const float quantum = __fmul_rn(scale, (float)code);
+    const float low = __fmul_rn(min, (float)offset);
+    return __fsub_rn(__fmul_rn(quantum, (float)quant), low);
+}
+
 __global__ void dequant_kernel(WeightView w, float *out) {
     const uint64_t total = (uint64_t)w.n * w.k;
     for (uint64_t e = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; e < total;
-         e += (uint64_t)gridDim.x * blockDim.x) {
-        const uint32_t row = (uint32_t)(e / w.k), at = (uint32_t)(e % w.k);
-        float value;
-        if (w.element == NC_ELEMENT_Q8_0) {
-            const uint32_t blk = at / kQ8Block, lane = at % kQ8Block;
-            const float quantum =
-                half_bits_to_float(weight_byte(w, row, blk, 0) | (weight_byte(w, row, blk, 1) << 8));
-            value = __fmul_rn((float)(int8_t)weight_byte(w, row, blk, 2 + lane), quantum);
-        } else {
-            const uint32_t blk = at / kSuperBlock, within = at % kSuperBlock;
-            const uint32_t group = within / 64, seat = (within % 64) / 32, lane = within % 32;
-            const uint32_t sub = group * 2 + seat;
-            const float scale =
-                half_bits_to_float(weight_byte(w, row, blk, 0) | (weight_byte(w, row, blk, 1) << 8));
-            const float min =
-                half_bits_to_float(weight_byte(w, row, blk, 2) | (weight_byte(w, row, blk, 3) << 8));
-            uint32_t code, offset;  // scale_min_k4, ggml.rs:127-136
-            if (sub < 4) {
-                code = weight_byte(w, row, blk, 4 + sub) & 63u;
-                offset = weight_byte(w, row, blk, 4 + sub + 4) & 63u;
-            } else {
-                code = (weight_byte(w, row, blk, 4 + sub + 4) & 0x0fu) |
-                       ((weight_byte(w, row, blk, 4 + sub - 4) >> 6) << 4);
-                offset = (weight_byte(w, row, blk, 4 + sub + 4) >> 4) |
-                         ((weight_byte(w, row, blk, 4 + sub) >> 6) << 4);
-            }
-            const uint32_t packed = weight_byte(w, row, blk, 16 + group * 32 + lane);
-            const uint32_t quant = seat ? packed >> 4 : packed & 0x0fu;
-            const float quantum = __fmul_rn(scale, (float)code);
-            const float low = __fmul_rn(min, (float)offset);
-            value = __fsub_rn(__fmul_rn(quantum, (float)quant), low);
-        }
-        out[e] = value;
-    }
+         e += (uint64_t)gridDim.x * blockDim.x)
+        out[e] = dequant_at(w, (uint32_t)(e / w.k), (uint32_t)(e % w.k));
 }
 
 // GGUF -> tiled, Q4_K, one 8-byte granule per thread step.

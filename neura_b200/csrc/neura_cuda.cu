@@ -7,6 +7,7 @@
 #include <string>
 
 #include "common.cuh"
+#include "decoder_ops.cuh"
 #include "gemv_mma.cuh"
 #include "layout.cuh"
 #include "prep.cuh"
@@ -121,9 +122,9 @@ constexpr int kStages = 2;
 // Launches with the programmatic-stream-serialization attribute, so that a kernel's
 // prologue (for the product: its first weight copies) overlaps the tail of the kernel
 // before it; the kernels order themselves with griddepcontrol.wait.
-template <typename Params>
-cudaError_t launch_dependent(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             const Params &params) {
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args &&...args) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
@@ -134,7 +135,7 @@ cudaError_t launch_dependent(void (*kernel)(Params), dim3 grid, dim3 block, size
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, kernel, params);
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
 template <bool Q4K, int NT>
@@ -503,6 +504,117 @@ int32_t neura_cuda_linear_host(nc_context *ctx, void *stream_, const nc_weight *
     NC_CUDA(cudaMemcpyAsync(out_host, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, stream));
     NC_CUDA(cudaStreamSynchronize(stream));
     return check_status(ctx);
+}
+
+int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                                  uint32_t k, const float *weight_dev, float floor, uint32_t element,
+                                  float *normed_dev, uint64_t normed_stride) {
+    if (!ctx || !x_dev) return refuse(kBadArgument, "a norm needs a context and a row to norm");
+    const uint32_t per = block_elements(element);
+    if (!per || !k || k % per)
+        return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
+    if (rows == 0 || rows > kMaxRowsPerPass)
+        return refuse(kBadArgument, "one staging holds 1 to %u rows, not %u", kMaxRowsPerPass, rows);
+    if (x_stride < k || (normed_dev && normed_stride < k))
+        return refuse(kBadArgument, "rows of %u numbers overlap at the strides given", k);
+    if ((uintptr_t)x_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
+    const uint32_t ncols = rows * 3;
+    int32_t rc;
+    if ((rc = ensure(ctx, ctx->dig, kpad * ncols, false))) return rc;
+    if ((rc = ensure(ctx, ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->sums, kpad / 256 * ncols * 64, false))) return rc;
+    NormStageParams p;
+    p.prep.x = x_dev;
+    p.prep.x_stride = x_stride;
+    p.prep.dig = (int8_t *)ctx->dig.ptr;
+    p.prep.cs = (float *)ctx->cs.ptr;
+    p.prep.sums = (uint32_t *)ctx->sums.ptr;
+    p.prep.rows = rows;
+    p.prep.k = k;
+    p.prep.ncols = ncols;
+    p.prep.granule = element == NC_ELEMENT_Q4K ? 256 : 32;
+    p.prep.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
+    p.weight = weight_dev;
+    p.normed = normed_dev;
+    p.normed_stride = normed_stride;
+    p.floor = floor;
+    NC_CUDA(launch_dependent(rms_norm_stage_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream_, p));
+    ctx->launches++;
+    ctx->staged_rows = rows;
+    ctx->staged_k = k;
+    ctx->staged_granule = p.prep.granule;
+    return 0;
+}
+
+int32_t neura_cuda_rope_cache(nc_context *ctx, void *stream_, float *qkv_dev, uint64_t row_stride,
+                              const uint32_t *position_dev, float base, uint32_t batch, uint32_t heads,
+                              uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
+                              float *values_dev) {
+    if (!ctx || !qkv_dev || !position_dev || !keys_dev || !values_dev)
+        return refuse(kBadArgument, "rope needs a context, the q|k|v rows, their positions and a cache");
+    if (!batch || !heads || !key_heads || !width || width % 2 || !capacity)
+        return refuse(kBadArgument, "a rotation of %u heads of width %u over %u slots turns nothing", heads, width, capacity);
+    if (row_stride < (uint64_t)(heads + 2 * key_heads) * width)
+        return refuse(kBadArgument, "a q|k|v row of %u numbers overlaps at stride %llu", (heads + 2 * key_heads) * width,
+                      (unsigned long long)row_stride);
+    RopeCacheParams p{qkv_dev, row_stride, position_dev, keys_dev, values_dev, base, batch, heads, key_heads, width, capacity};
+    const uint32_t work = batch * ((heads + key_heads) * (width / 2) + key_heads * width);
+    NC_CUDA(launch_dependent(rope_cache_kernel, dim3((work + 255) / 256), dim3(256), 0, (cudaStream_t)stream_, p));
+    ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, uint64_t q_stride, const float *keys_dev,
+                          const float *values_dev, const uint32_t *position_dev, float scale, uint32_t batch,
+                          uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
+                          uint64_t out_stride) {
+    if (!ctx || !q_dev || !keys_dev || !values_dev || !position_dev || !out_dev)
+        return refuse(kBadArgument, "attention needs a context, queries, a cache, positions and an output");
+    if (!batch || !heads || !key_heads || heads % key_heads || !width || !capacity)
+        return refuse(kBadArgument, "%u query heads do not share %u key heads", heads, key_heads);
+    const size_t smem = ((size_t)capacity + 8) * sizeof(float);
+    if (smem > 200 * 1024) return refuse(kBadArgument, "a cache of %u slots does not fit the attention kernel's shared memory", capacity);
+    static bool raised[64] = {false};
+    if (smem > 48 * 1024 && !raised[ctx->device & 63]) {
+        NC_CUDA(cudaFuncSetAttribute(attend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised[ctx->device & 63] = true;
+    }
+    AttendParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride, scale,
+                   batch, heads, key_heads, width, capacity};
+    NC_CUDA(launch_dependent(attend_kernel, dim3(batch * heads), dim3(128), smem, (cudaStream_t)stream_, p));
+    ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_argmax(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint32_t width,
+                          uint64_t stride, uint32_t *out_dev) {
+    if (!ctx || !x_dev || !out_dev || !rows || !width) return refuse(kBadArgument, "argmax needs a context, rows and an output");
+    if (stride < width) return refuse(kBadArgument, "rows of %u numbers overlap at stride %llu", width, (unsigned long long)stride);
+    NC_CUDA(launch_dependent(argmax_kernel, dim3(rows), dim3(1024), 0, (cudaStream_t)stream_, x_dev, stride, width, out_dev));
+    ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_embed(nc_context *ctx, void *stream_, const nc_weight *table, const uint32_t *tokens_dev,
+                         uint32_t rows, float *out_dev, uint64_t out_stride) {
+    if (!ctx || !tokens_dev || !out_dev || !rows) return refuse(kBadArgument, "a gather needs a context, tokens and an output");
+    int32_t rc;
+    if ((rc = check_weight(table))) return rc;
+    if (out_stride < table->k) return refuse(kBadArgument, "rows of %u numbers overlap at stride %llu", table->k, (unsigned long long)out_stride);
+    WeightView view{(const uint8_t *)table->data_dev, table->element, table->layout, table->n, table->k};
+    const uint32_t work = rows * table->k;
+    NC_CUDA(launch_dependent(embed_kernel, dim3((work + 255) / 256), dim3(256), 0, (cudaStream_t)stream_, view, tokens_dev,
+                             rows, out_dev, out_stride));
+    ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_advance(nc_context *ctx, void *stream_, uint32_t *position_dev, uint32_t rows, uint32_t by) {
+    if (!ctx || !position_dev || !rows) return refuse(kBadArgument, "advance needs a context and positions");
+    NC_CUDA(launch_dependent(advance_kernel, dim3((rows + 127) / 128), dim3(128), 0, (cudaStream_t)stream_, position_dev, rows, by));
+    ctx->launches++;
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -34,6 +34,114 @@ struct PrepParams {
     uint32_t vector;    // 1: rows start 16-byte aligned, so a lane may fetch float4
 };
 
+// Digitises one 256-element chunk of row `row` held by a warp: lane l owns v[0..8) =
+// elements [8l, 8l+8) of the chunk; `live` says whether those elements exist (k is a
+// multiple of 32, so a lane is live or dead as a whole).  All 32 lanes must call.
+__device__ __forceinline__ void stage_chunk(const PrepParams &p, uint32_t row, uint32_t chunk, const float (&v)[8],
+                                            bool live) {
+    const uint32_t lane = threadIdx.x & 31;
+    float peak = 0.0f;
+    bool odd = false;  // an inf or a nan among this lane's numbers
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            peak = fmaxf(peak, fabsf(v[i]));
+            odd |= !(fabsf(v[i]) <= 3.0e38f);
+        }
+    }
+    // granule peak: 4 lanes share a 32-block, the warp shares the 256-chunk
+    peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 1));
+    peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 2));
+    if (p.granule == 256) {
+        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 4));
+        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 8));
+        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 16));
+    }
+    // peak < 2^e  ->  |x * 2^(22-e)| < 2^22
+    int s = 0;
+    float unscale = 1.0f;
+    const uint32_t vote = __ballot_sync(0xffffffffu, odd);
+    const bool finite = p.granule == 256 ? vote == 0u : ((vote >> (lane & ~3u)) & 0xfu) == 0u;
+    if (peak > 0.0f && finite) {
+        int e;
+        frexpf(peak, &e);
+        s = min(max(22 - e, -100), 120);
+        unscale = ldexpf(1.0f, -s);
+    }
+    if (!finite) unscale = __int_as_float(0x7fc00000);  // the product of this granule reads as nan
+    const float up = ldexpf(1.0f, s);
+    uint32_t d[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+    int total[3] = {0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int q = (finite && live) ? __float2int_rn(v[i] * up) : 0;
+        const int d0 = (int)(int8_t)(q & 255);
+        q = (q - d0) >> 8;
+        const int d1 = (int)(int8_t)(q & 255);
+        const int d2 = (q - d1) >> 8;
+        total[0] += d0;
+        total[1] += d1;
+        total[2] += d2;
+        d[0][i >> 2] |= (uint32_t)(d0 & 255) << (8 * (i & 3));
+        d[1][i >> 2] |= (uint32_t)(d1 & 255) << (8 * (i & 3));
+        d[2][i >> 2] |= (uint32_t)(d2 & 255) << (8 * (i & 3));
+    }
+    const uint32_t kb = chunk * 8 + (lane >> 2);
+    if (p.granule == 256) {
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            int sum = total[j];
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((lane & 3) == 0) {
+                const uint32_t sub = lane >> 2, col = row * 3 + j;
+                const int s0 = (int)(int8_t)(sum & 255), s1 = (sum - s0) >> 8;
+                uint32_t *entry = p.sums + (((uint64_t)chunk * p.ncols + col) * 4 + (sub & 3)) * 4 + (sub >> 2);
+                entry[0] = (uint32_t)(s0 & 255);
+                entry[2] = (uint32_t)(s1 & 255);
+            }
+        }
+    }
+    if (!live) return;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        const uint32_t col = row * 3 + j;
+        const uint64_t at = p.granule == 256
+            ? ((((uint64_t)chunk * p.ncols + col) * 4 + (lane & 3)) * 8 + (lane >> 2)) * 8
+            : ((uint64_t)kb * p.ncols + col) * 32 + (lane & 3) * 8;
+        *reinterpret_cast<uint2 *>(p.dig + at) = make_uint2(d[j][0], d[j][1]);
+    }
+    const bool writes = p.granule == 256 ? lane == 0 : (lane & 3) == 0;
+    if (writes) {
+        const uint32_t gi = p.granule == 256 ? chunk : kb;
+        float c = unscale;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            p.cs[(uint64_t)gi * p.ncols + row * 3 + j] = c;
+            c *= 256.0f;
+        }
+    }
+}
+
+// Fetches a lane's eight numbers of a chunk.
+__device__ __forceinline__ void load_chunk(const PrepParams &p, uint32_t row, uint32_t at, bool live, float (&v)[8]) {
+    if (live) {
+        const float *from = p.x + (uint64_t)row * p.x_stride + at;
+        if (p.vector) {
+            const float4 a = *reinterpret_cast<const float4 *>(from);
+            const float4 b = *reinterpret_cast<const float4 *>(from + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = from[i];
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+}
+
 // One warp per (row, 256-element chunk): lane l owns elements [8l, 8l+8) of the chunk.
 __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
     // Programmatic dependent launch: the product that follows may start fetching its
@@ -47,103 +155,58 @@ __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
     for (uint64_t w = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total; w += warps) {
         const uint32_t row = (uint32_t)(w / chunks), chunk = (uint32_t)(w % chunks);
         const uint32_t at = chunk * 256 + lane * 8;
-        const bool live = at < p.k;  // k is a multiple of 32, so a lane is live or dead as a whole
+        const bool live = at < p.k;
         float v[8];
-        float peak = 0.0f;
-        bool odd = false;  // an inf or a nan among this lane's numbers
+        load_chunk(p, row, at, live, v);
+        stage_chunk(p, row, chunk, v, live);
+    }
+}
+
+// rms_norm (crates/neura-kernel/src/task/norm.rs:55-131, op = NORM_RMS) fused with the staging
+// of its result: one CTA per row computes scale = 1 / sqrt(mean(x^2) + floor), then its warps
+// digitise x * scale * weight chunk by chunk.  `normed`, when not null, also receives the f32 row.
+struct NormStageParams {
+    PrepParams prep;
+    const float *weight;  // [k] or null
+    float *normed;        // [rows][normed_stride] or null
+    uint64_t normed_stride;
+    float floor;
+};
+
+__global__ void __launch_bounds__(256) rms_norm_stage_kernel(const __grid_constant__ NormStageParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float partial[8];
+    __shared__ float scale_shared;
+    const uint32_t row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *x = p.prep.x + (uint64_t)row * p.prep.x_stride;
+    float square = 0.0f;
+    for (uint32_t c = threadIdx.x; c < p.prep.k; c += blockDim.x) square = fmaf(x[c], x[c], square);
+    for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+    if (lane == 0) partial[warp] = square;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) total += partial[w];
+        scale_shared = 1.0f / sqrtf(total / (float)p.prep.k + p.floor);
+    }
+    __syncthreads();
+    const float scale = scale_shared;
+    const uint32_t chunks = (p.prep.k + 255) / 256;
+    for (uint32_t chunk = warp; chunk < chunks; chunk += (blockDim.x >> 5)) {
+        const uint32_t at = chunk * 256 + lane * 8;
+        const bool live = at < p.prep.k;
+        float v[8];
+        load_chunk(p.prep, row, at, live, v);
         if (live) {
-            const float *from = p.x + (uint64_t)row * p.x_stride + at;
-            if (p.vector) {
-                const float4 a = *reinterpret_cast<const float4 *>(from);
-                const float4 b = *reinterpret_cast<const float4 *>(from + 4);
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = from[i];
-            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                peak = fmaxf(peak, fabsf(v[i]));
-                odd |= !(fabsf(v[i]) <= 3.0e38f);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-        }
-        // granule peak: 4 lanes share a 32-block, the warp shares the 256-chunk
-        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 1));
-        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 2));
-        if (p.granule == 256) {
-            peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 4));
-            peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 8));
-            peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 16));
-        }
-        // peak < 2^e  ->  |x * 2^(22-e)| < 2^22
-        int s = 0;
-        float unscale = 1.0f;
-        const uint32_t vote = __ballot_sync(0xffffffffu, odd);
-        const bool finite = p.granule == 256 ? vote == 0u : ((vote >> (lane & ~3u)) & 0xfu) == 0u;
-        if (peak > 0.0f && finite) {
-            int e;
-            frexpf(peak, &e);
-            s = min(max(22 - e, -100), 120);
-            unscale = ldexpf(1.0f, -s);
-        }
-        if (!finite) unscale = __int_as_float(0x7fc00000);  // the product of this granule reads as nan
-        if (!live) continue;
-        const float up = ldexpf(1.0f, s);
-        uint32_t d[3][2] = {{0, 0}, {0, 0}, {0, 0}};
-        int total[3] = {0, 0, 0};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            int q = finite ? __float2int_rn(v[i] * up) : 0;
-            const int d0 = (int)(int8_t)(q & 255);
-            q = (q - d0) >> 8;
-            const int d1 = (int)(int8_t)(q & 255);
-            const int d2 = (q - d1) >> 8;
-            total[0] += d0;
-            total[1] += d1;
-            total[2] += d2;
-            d[0][i >> 2] |= (uint32_t)(d0 & 255) << (8 * (i & 3));
-            d[1][i >> 2] |= (uint32_t)(d1 & 255) << (8 * (i & 3));
-            d[2][i >> 2] |= (uint32_t)(d2 & 255) << (8 * (i & 3));
-        }
-        const uint32_t kb = chunk * 8 + (lane >> 2);
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            const uint32_t col = row * 3 + j;
-            const uint64_t at = p.granule == 256
-                ? ((((uint64_t)chunk * p.ncols + col) * 4 + (lane & 3)) * 8 + (lane >> 2)) * 8
-                : ((uint64_t)kb * p.ncols + col) * 32 + (lane & 3) * 8;
-            *reinterpret_cast<uint2 *>(p.dig + at) = make_uint2(d[j][0], d[j][1]);
-        }
-        if (p.granule == 256) {
-            // (no lane has left the loop body: the chunks of a 256-granule are whole)
-#pragma unroll
-            for (int j = 0; j < 3; ++j) {
-                int s = total[j];
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                if ((lane & 3) == 0) {
-                    const uint32_t sub = lane >> 2, col = row * 3 + j;
-                    const int s0 = (int)(int8_t)(s & 255), s1 = (s - s0) >> 8;
-                    uint32_t *entry = p.sums + (((uint64_t)chunk * p.ncols + col) * 4 + (sub & 3)) * 4 + (sub >> 2);
-                    entry[0] = (uint32_t)(s0 & 255);
-                    entry[2] = (uint32_t)(s1 & 255);
-                }
+                v[i] = v[i] * scale;
+                if (p.weight) v[i] = v[i] * p.weight[at + i];
+                if (p.normed) p.normed[(uint64_t)row * p.normed_stride + at + i] = v[i];
             }
         }
-        const bool writes = p.granule == 256 ? lane == 0 : (lane & 3) == 0;
-        if (writes) {
-            const uint32_t gi = p.granule == 256 ? chunk : kb;
-            float c = unscale;
-#pragma unroll
-            for (int j = 0; j < 3; ++j) {
-                p.cs[(uint64_t)gi * p.ncols + row * 3 + j] = c;
-                c *= 256.0f;
-            }
-        }
+        stage_chunk(p.prep, row, chunk, v, live);
     }
 }
 

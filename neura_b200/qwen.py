@@ -125,3 +125,100 @@ class LinearStack:
 
     def launches_per_token(self) -> int:
         return self.config.layers * 9 + 2
+
+
+class Decoder:
+    """A Qwen2.5-shaped decoder stepping one token per sequence (greedy), on the device.
+
+    Layer wiring after examples/qwen/attention.rs:98-153 and mlp.rs:29-36 without the
+    Qwen3.5 extras (no q/k norms, no attention gate, RoPE over the full head width);
+    the step is Batch::answer (crates/neura-generate/src/batch.rs:1646-1725): token ids and
+    cursors stay on the device, so one recorded program replays per token.
+
+    ``weights``: "token_embd.weight" (any layout; the sealed head when tied), "output.weight",
+    per layer "blk.N.attn_qkv.weight" (q, k, v rows stacked), "blk.N.attn_output.weight",
+    "blk.N.ffn_gate.weight", "blk.N.ffn_up.weight", "blk.N.ffn_down.weight".
+    ``norms``: "blk.N.attn_norm.weight", "blk.N.ffn_norm.weight", "output_norm.weight" (f32 [hidden]).
+    """
+
+    def __init__(self, rt: Runtime, config: Config, weights: Dict[str, Weight], norms: Dict[str, DeviceTensor],
+                 batch: int = 1, capacity: int = 640):
+        if batch > 16:
+            raise ValueError("one decode step carries at most 16 sequences")
+        self.rt, self.config, self.weights, self.norms = rt, config, weights, norms
+        self.batch, self.capacity = batch, capacity
+        c = config
+        self.tokens = rt.tensor_u32(batch)
+        self.position = rt.tensor_u32(batch)
+        self.hidden = rt.tensor(batch, c.hidden)
+        self.qkv = rt.tensor(batch, c.query_width + 2 * c.key_width)
+        self.attended = rt.tensor(batch, c.query_width)
+        self.gate = rt.tensor(batch, c.feed_forward)
+        self.held = rt.tensor(batch, c.feed_forward)
+        self.logits = rt.tensor(batch, c.vocab)
+        cache = batch * c.key_heads * capacity * c.head_width
+        self.keys = [rt.tensor(cache) for _ in range(c.layers)]
+        self.values = [rt.tensor(cache) for _ in range(c.layers)]
+        rt.reserve(batch, max(c.vocab, c.feed_forward), max(c.hidden, c.feed_forward, c.query_width))
+        self.program: Optional[int] = None
+        self.scale = 1.0 / float(c.head_width) ** 0.5
+
+    def step(self) -> None:
+        rt, c, w, n = self.rt, self.config, self.weights, self.norms
+        rt.embed(w["token_embd.weight"], self.tokens, self.hidden)
+        for layer in range(c.layers):
+            at = lambda name: f"blk.{layer}.{name}.weight"  # noqa: E731
+            rt.rms_norm_stage(self.hidden, n[at("attn_norm")], c.floor, c.element)
+            rt.linear_staged(w[at("attn_qkv")], self.qkv)
+            rt.rope_cache(self.qkv, self.position, c.rope_base, c.heads, c.key_heads, c.head_width, self.capacity,
+                          self.keys[layer], self.values[layer])
+            rt.attend(self.qkv, self.keys[layer], self.values[layer], self.position, self.scale, c.heads,
+                      c.key_heads, c.head_width, self.capacity, self.attended)
+            rt.stage(self.attended, c.element)
+            rt.linear_staged(w[at("attn_output")], self.hidden, [Step(ADD, self.hidden)])
+            rt.rms_norm_stage(self.hidden, n[at("ffn_norm")], c.floor, c.element)
+            rt.linear_staged(w[at("ffn_gate")], self.gate, [Step(SILU)])
+            rt.linear_staged(w[at("ffn_up")], self.held, [Step(MUL, self.gate)])
+            rt.stage(self.held, c.element)
+            rt.linear_staged(w[at("ffn_down")], self.hidden, [Step(ADD, self.hidden)])
+        rt.rms_norm_stage(self.hidden, n["output_norm.weight"], c.floor, c.element)
+        rt.linear_staged(w["output.weight"], self.logits)
+        rt.argmax(self.logits, self.tokens)
+        rt.advance(self.position, 1)
+
+    def launches_per_token(self) -> int:
+        return self.config.layers * 11 + 5
+
+    def record(self) -> int:
+        self.rt.capture_begin()
+        self.step()
+        self.program = self.rt.capture_end()
+        return self.program
+
+    def reset(self) -> None:
+        import numpy as np
+
+        self.rt.write(self.position, np.zeros(self.batch, dtype=np.uint32))
+
+    def run_token(self) -> None:
+        if self.program is None:
+            self.step()
+        else:
+            self.rt.run(self.program)
+
+    def generate(self, prompts, steps: int):
+        """Feeds ``prompts`` [batch, length] one token at a time (every step attends to all the
+        tokens before it), then decodes ``steps`` tokens greedily.  Returns [batch, steps] ids."""
+        import numpy as np
+
+        prompts = np.ascontiguousarray(prompts, dtype=np.uint32).reshape(self.batch, -1)
+        self.reset()
+        out = np.zeros((self.batch, steps), dtype=np.uint32)
+        for at in range(prompts.shape[1]):
+            self.rt.write(self.tokens, prompts[:, at].copy())
+            self.run_token()
+        out[:, 0] = self.rt.read(self.tokens, dtype=np.uint32)
+        for at in range(1, steps):
+            self.run_token()
+            out[:, at] = self.rt.read(self.tokens, dtype=np.uint32)
+        return out

@@ -285,6 +285,72 @@ class Runtime:
             self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(out_ptr if out_ptr is not None else out.ptr),
             out_stride if out_stride is not None else out.shape[-1], arr, count))
 
+    # -- the steps either side of the products ---------------------------------------
+    def tensor_u32(self, count: int) -> DeviceTensor:
+        return DeviceTensor(self.alloc(count * 4), count * 4, (count,))
+
+    def rms_norm_stage(self, x: DeviceTensor, weight: Optional[DeviceTensor], floor: float, element: int,
+                       normed: Optional[DeviceTensor] = None, rows: Optional[int] = None,
+                       k: Optional[int] = None) -> None:
+        """decoder::rms (crates/neura-decoder/src/op.rs:3-5) fused with ``stage`` of its result."""
+        rows = rows if rows is not None else x.rows
+        k = k if k is not None else x.shape[-1]
+        _check(self._lib.neura_cuda_rms_norm_stage(
+            self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1], k,
+            ctypes.c_void_p(weight.ptr) if weight is not None else None, floor, element,
+            ctypes.c_void_p(normed.ptr) if normed is not None else None,
+            normed.shape[-1] if normed is not None else 0))
+
+    def rope_cache(self, qkv: DeviceTensor, position: DeviceTensor, base: float, heads: int, key_heads: int,
+                   width: int, capacity: int, keys: DeviceTensor, values: DeviceTensor,
+                   batch: Optional[int] = None) -> None:
+        """decoder::partial over the full width + Cache::write (crates/neura-decoder/src/rope.rs:3-12, cache.rs:267-310)."""
+        batch = batch if batch is not None else qkv.rows
+        _check(self._lib.neura_cuda_rope_cache(self._ctx, self.stream, ctypes.c_void_p(qkv.ptr), qkv.shape[-1],
+                                               ctypes.c_void_p(position.ptr), base, batch, heads, key_heads, width,
+                                               capacity, ctypes.c_void_p(keys.ptr), ctypes.c_void_p(values.ptr)))
+
+    def attend(self, q: DeviceTensor, keys: DeviceTensor, values: DeviceTensor, position: DeviceTensor, scale: float,
+               heads: int, key_heads: int, width: int, capacity: int, out: DeviceTensor,
+               batch: Optional[int] = None) -> None:
+        """Cache::attend (crates/neura-decoder/src/cache.rs:311-406) for one new row per sequence."""
+        batch = batch if batch is not None else q.rows
+        _check(self._lib.neura_cuda_attend(self._ctx, self.stream, ctypes.c_void_p(q.ptr), q.shape[-1],
+                                           ctypes.c_void_p(keys.ptr), ctypes.c_void_p(values.ptr),
+                                           ctypes.c_void_p(position.ptr), scale, batch, heads, key_heads, width,
+                                           capacity, ctypes.c_void_p(out.ptr), out.shape[-1]))
+
+    def argmax(self, x: DeviceTensor, out: DeviceTensor, rows: Optional[int] = None) -> None:
+        rows = rows if rows is not None else x.rows
+        _check(self._lib.neura_cuda_argmax(self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1],
+                                           x.shape[-1], ctypes.c_void_p(out.ptr)))
+
+    def embed(self, table: Weight, tokens: DeviceTensor, out: DeviceTensor, rows: Optional[int] = None) -> None:
+        rows = rows if rows is not None else out.rows
+        rec = table.record()
+        _check(self._lib.neura_cuda_embed(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(tokens.ptr), rows,
+                                          ctypes.c_void_p(out.ptr), out.shape[-1]))
+
+    def advance(self, position: DeviceTensor, by: int = 1) -> None:
+        _check(self._lib.neura_cuda_advance(self._ctx, self.stream, ctypes.c_void_p(position.ptr), position.shape[0], by))
+
+    def load_stacked(self, element: int, k: int, parts: Sequence[tuple]) -> Weight:
+        """Several GGUF tensors of the same ``k`` sealed end to end as one weight of their rows
+        stacked (q, k and v share their activations, so one product serves all three).
+        ``parts`` = [(n, gguf_bytes), ...], every n a multiple of 32."""
+        total = sum(n for n, _ in parts)
+        base = self.alloc(self.sealed_bytes(element, total, k))
+        at = base
+        for n, data in parts:
+            if n % 32:
+                raise NeuraCudaError(-1, f"a stacked part of {n} rows does not fill tiles of 32")
+            raw = self.load(element, n, k, data, seal=False)
+            self.seal_device(element, n, k, raw.ptr, at)
+            self.sync()
+            self.free(raw.ptr)
+            at += self.sealed_bytes(element, n, k)
+        return Weight(base, element, LAYOUT_TILED, total, k, at - base)
+
     # -- recorded programs --------------------------------------------------------
     def new_stream(self) -> int:
         out = ctypes.c_void_p()

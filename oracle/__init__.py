@@ -74,6 +74,11 @@ def lib() -> ctypes.CDLL:
         for name in ("nro_linear", "nro_linear_bf16"):
             getattr(_lib, name).argtypes = [u32, p, u64, u64, p, u64, u64, p, u64, p, u32, ctypes.c_int]
         _lib.nro_matmul_f32.argtypes = [p, u64, u64, p, u64, p, ctypes.c_int]
+        _lib.nro_rms_norm.argtypes = [p, p, f32, u64, u64, p]
+        _lib.nro_rope.argtypes = [p, p, f32, u64, u64, u64]
+        _lib.nro_attend.argtypes = [p, p, p, p, f32, u64, u64, u64, u64, u64, p]
+        _lib.nro_argmax.argtypes = [p, u64, u64, p]
+        _lib.nro_embed.argtypes = [u32, p, u64, p, u64, p]
     return _lib
 
 
@@ -195,4 +200,53 @@ def matmul_f32(weight: np.ndarray, x: np.ndarray, threads: int = 1) -> np.ndarra
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, k)
     out = np.empty((x.shape[0], n), dtype=np.float32)
     lib().nro_matmul_f32(_ptr(weight), n, k, _ptr(x), x.shape[0], _ptr(out), threads)
+    return out
+
+
+def rms_norm(x: np.ndarray, weight: np.ndarray | None, floor: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, width = x.reshape(-1, x.shape[-1]).shape
+    out = np.empty_like(x)
+    w = None if weight is None else np.ascontiguousarray(weight, dtype=np.float32)
+    lib().nro_rms_norm(_ptr(x), None if w is None else _ptr(w), floor, rows, width, _ptr(out))
+    return out
+
+
+def rope(x: np.ndarray, position: np.ndarray, base: float) -> np.ndarray:
+    """x [rows, heads, width] turned in place semantics (a copy is returned)."""
+    out = np.array(x, dtype=np.float32, order="C", copy=True)
+    rows, heads, width = out.shape
+    pos = np.ascontiguousarray(position, dtype=np.uint32)
+    lib().nro_rope(_ptr(out), _ptr(pos), base, rows, heads, width)
+    return out
+
+
+def attend(q: np.ndarray, keys: np.ndarray, values: np.ndarray, count: np.ndarray, scale: float) -> np.ndarray:
+    """q [batch, heads, width]; keys/values [batch, key_heads, capacity, width]; count[b] live positions."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    keys = np.ascontiguousarray(keys, dtype=np.float32)
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    batch, heads, width = q.shape
+    _, key_heads, capacity, _ = keys.shape
+    cnt = np.ascontiguousarray(count, dtype=np.uint32)
+    out = np.empty_like(q)
+    lib().nro_attend(_ptr(q), _ptr(keys), _ptr(values), _ptr(cnt), scale, batch, heads, key_heads, capacity, width,
+                     _ptr(out))
+    return out
+
+
+def argmax(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, width = x.reshape(-1, x.shape[-1]).shape
+    out = np.empty(rows, dtype=np.uint32)
+    lib().nro_argmax(_ptr(x), rows, width, _ptr(out))
+    return out
+
+
+def embed(element: int, packed: np.ndarray, width: int, tokens: np.ndarray) -> np.ndarray:
+    tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+    out = np.empty((tokens.size, width), dtype=np.float32)
+    if lib().nro_embed(element, _ptr(np.ascontiguousarray(packed, dtype=np.uint8)), width, _ptr(tokens), tokens.size,
+                       _ptr(out)):
+        raise ValueError("the oracle refused the gather")
     return out

@@ -517,3 +517,104 @@ int nro_matmul_f32(const float *weight, uint64_t n, uint64_t k, const float *x, 
     product_job job = {NRO_SINGLE, NULL, weight, x, out, rows, n, k, k, n, NULL, 0, 0, 0, 0};
     return run_product(job, threads);
 }
+
+/* ------------------------------------------------------------------ */
+/* The steps either side of the products in a decoder layer.          */
+/* ------------------------------------------------------------------ */
+
+/* rms_norm: crates/neura-kernel/src/task/norm.rs:55-131 with op = NORM_RMS:
+ * scale = 1 / sqrt(mean(x^2) + floor); out = x * scale * weight.
+ * (composed form in crates/neura-runtime/tests/norm.rs:21-26) */
+void nro_rms_norm(const float *x, const float *weight, float floor, uint64_t rows, uint64_t width, float *out) {
+    for (uint64_t r = 0; r < rows; ++r) {
+        const float *row = x + r * width;
+        float square = 0.0f;
+        for (uint64_t c = 0; c < width; ++c) square = square + row[c] * row[c];
+        float scale = 1.0f / sqrtf(square / (float)width + floor);
+        for (uint64_t c = 0; c < width; ++c) {
+            float result = row[c] * scale;
+            if (weight) result = result * weight[c];
+            out[r * width + c] = result;
+        }
+    }
+}
+
+/* rope: crates/neura-kernel/src/task/rope.rs:48-122 (half rotation), CPU form in
+ * crates/neura-runtime/tests/runtime.rs:468-494.  x is [rows][heads][width]; every head of
+ * row r turns by position[r]. */
+void nro_rope(float *x, const uint32_t *position, float base, uint64_t rows, uint64_t heads, uint64_t width) {
+    uint64_t half = width / 2;
+    for (uint64_t r = 0; r < rows; ++r) {
+        for (uint64_t h = 0; h < heads; ++h) {
+            float *v = x + (r * heads + h) * width;
+            for (uint64_t c = 0; c < half; ++c) {
+                float angle = (float)position[r] * powf(base, -2.0f * (float)c / (float)width);
+                float cosine = cosf(angle), sine = sinf(angle);
+                float low = v[c], high = v[c + half];
+                v[c] = low * cosine - high * sine;
+                v[c + half] = high * cosine + low * sine;
+            }
+        }
+    }
+}
+
+/* Causal grouped-query attention of one new row per sequence over its cache:
+ * crates/neura-runtime/tests/support/attention.rs:71-109 (softmax(q.k * scale) v, query head h
+ * reads key head h / (heads / key_heads), attention.rs:19-27), in f32 like the device
+ * (crates/neura-kernel/src/task/attention.rs:309-617).
+ *   q      [batch][heads][width]
+ *   keys   [batch][key_heads][capacity][width]   (positions 0..count[b]-1 are live)
+ *   out    [batch][heads][width] */
+void nro_attend(const float *q, const float *keys, const float *values, const uint32_t *count, float scale,
+                uint64_t batch, uint64_t heads, uint64_t key_heads, uint64_t capacity, uint64_t width, float *out) {
+    uint64_t group = heads / key_heads;
+    float *logits = (float *)malloc(capacity * sizeof(float));
+    for (uint64_t b = 0; b < batch; ++b) {
+        for (uint64_t h = 0; h < heads; ++h) {
+            const float *query = q + (b * heads + h) * width;
+            const float *k = keys + ((b * key_heads + h / group) * capacity) * width;
+            const float *v = values + ((b * key_heads + h / group) * capacity) * width;
+            float largest = -INFINITY;
+            for (uint64_t p = 0; p < count[b]; ++p) {
+                float total = 0.0f;
+                for (uint64_t d = 0; d < width; ++d) total = total + query[d] * k[p * width + d];
+                logits[p] = total * scale;
+                if (logits[p] > largest) largest = logits[p];
+            }
+            float total = 0.0f;
+            for (uint64_t p = 0; p < count[b]; ++p) {
+                logits[p] = expf(logits[p] - largest);
+                total = total + logits[p];
+            }
+            for (uint64_t d = 0; d < width; ++d) {
+                float sum = 0.0f;
+                for (uint64_t p = 0; p < count[b]; ++p) sum = sum + logits[p] * v[p * width + d];
+                out[(b * heads + h) * width + d] = sum / total;
+            }
+        }
+    }
+    free(logits);
+}
+
+/* argmax with the lowest index winning a tie: choice_precedes,
+ * crates/neura-kernel/src/task/choice.rs:46-52 */
+void nro_argmax(const float *x, uint64_t rows, uint64_t width, uint32_t *out) {
+    for (uint64_t r = 0; r < rows; ++r) {
+        uint32_t best = 0;
+        for (uint64_t c = 1; c < width; ++c)
+            if (x[r * width + c] > x[r * width + best]) best = (uint32_t)c;
+        out[r] = best;
+    }
+}
+
+/* gather of a quantised table row: run_gather (crates/neura-kernel/src/task/select.rs:29-49)
+ * over fetch (fetch.rs) = the dequantised row. */
+int nro_embed(uint32_t element, const uint8_t *packed, uint64_t width, const uint32_t *tokens, uint64_t rows,
+              float *out) {
+    uint32_t per, bytes;
+    if (nro_block(element, &per, &bytes) || width % per) return -1;
+    uint64_t row_bytes = width / per * bytes;
+    for (uint64_t r = 0; r < rows; ++r)
+        nro_unpack(element, width, packed + (uint64_t)tokens[r] * row_bytes, out + r * width);
+    return 0;
+}

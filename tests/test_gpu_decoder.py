@@ -1,0 +1,156 @@
+"""The decoder step and its parts against the CPU oracle (needs a B200)."""
+import numpy as np
+import pytest
+
+import neura_b200 as nb
+from neura_b200 import qwen
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def test_embedding_rows_are_the_dequantised_table_rows(runtime, oracle):
+    for element, width in ((nb.Q8_0, 896), (nb.Q4K, 1024)):
+        vocab = 320
+        table = oracle.Stream(3).normal(vocab * width, 0.0, 0.02).reshape(vocab, width)
+        packed = oracle.pack_rows(element, table)
+        tokens = np.array([0, 5, 319, 64, 5], dtype=np.uint32)
+        expected = oracle.embed(element, packed, width, tokens)
+        tok = runtime.tensor_u32(tokens.size)
+        runtime.write(tok, tokens)
+        out = runtime.tensor(tokens.size, width)
+        for seal in (False, True):
+            runtime.embed(runtime.load(element, vocab, width, packed, seal=seal), tok, out)
+            assert np.array_equal(bits(runtime.read(out)), bits(expected))
+
+
+def test_rms_norm_matches_and_its_staging_feeds_the_product(runtime, oracle):
+    rows, k, n = 3, 1024, 96
+    x = oracle.Stream(5).normal(rows * k).reshape(rows, k) * 3.0
+    weight = oracle.Stream(6).uniform(k, 0.5, 1.5)
+    expected = oracle.rms_norm(x, weight, 1e-6)
+    xd, wd, nd = runtime.tensor(rows, k), runtime.tensor(k), runtime.tensor(rows, k)
+    runtime.write(xd, x)
+    runtime.write(wd, weight)
+    w = oracle.Stream(7).normal(n * k, 0.0, 0.02).reshape(n, k)
+    for element in (nb.Q4K, nb.Q8_0):
+        packed = oracle.pack_rows(element, w)
+        runtime.rms_norm_stage(xd, wd, 1e-6, element, normed=nd)
+        assert np.abs(runtime.read(nd) - expected).max() <= 2e-6 * np.abs(expected).max()
+        out = runtime.tensor(rows, n)
+        runtime.linear_staged(runtime.load(element, n, k, packed), out)
+        want = oracle.linear(element, packed, n, k, expected)
+        assert np.abs(runtime.read(out) - want).max() <= 1e-3 * np.sqrt(np.mean(want ** 2))
+
+
+def test_rope_and_cache_write(runtime, oracle):
+    batch, heads, key_heads, width, capacity = 3, 4, 2, 64, 32
+    row = (heads + 2 * key_heads) * width
+    qkv = oracle.Stream(8).normal(batch * row).reshape(batch, row)
+    position = np.array([0, 7, 31], dtype=np.uint32)
+    qd, pd = runtime.tensor(batch, row), runtime.tensor_u32(batch)
+    keys = runtime.tensor(batch * key_heads * capacity * width)
+    values = runtime.tensor(batch * key_heads * capacity * width)
+    runtime.write(qd, qkv)
+    runtime.write(pd, position)
+    runtime.write(keys, np.zeros(keys.shape, np.float32))
+    runtime.write(values, np.zeros(values.shape, np.float32))
+    runtime.rope_cache(qd, pd, 1e6, heads, key_heads, width, capacity, keys, values)
+    got = runtime.read(qd)
+    q = oracle.rope(qkv[:, : heads * width].reshape(batch, heads, width), position, 1e6)
+    k = oracle.rope(qkv[:, heads * width: (heads + key_heads) * width].reshape(batch, key_heads, width), position, 1e6)
+    assert np.abs(got[:, : heads * width] - q.reshape(batch, -1)).max() <= 2e-5
+    assert np.abs(got[:, heads * width: (heads + key_heads) * width] - k.reshape(batch, -1)).max() <= 2e-5
+    kc = runtime.read(keys).reshape(batch, key_heads, capacity, width)
+    vc = runtime.read(values).reshape(batch, key_heads, capacity, width)
+    v = qkv[:, (heads + key_heads) * width:].reshape(batch, key_heads, width)
+    for b in range(batch):
+        assert np.abs(kc[b, :, position[b]] - k[b]).max() <= 2e-5
+        assert np.array_equal(bits(vc[b, :, position[b]]), bits(v[b]))
+        untouched = np.delete(kc[b], position[b], axis=1)
+        assert not untouched.any()
+
+
+def test_attention_over_the_cache(runtime, oracle):
+    batch, heads, key_heads, width, capacity = 2, 6, 2, 64, 96
+    q = oracle.Stream(9).normal(batch * heads * width).reshape(batch, heads, width)
+    keys = oracle.Stream(10).normal(batch * key_heads * capacity * width).reshape(batch, key_heads, capacity, width)
+    values = oracle.Stream(11).normal(keys.size).reshape(keys.shape)
+    position = np.array([0, 70], dtype=np.uint32)
+    expected = oracle.attend(q, keys, values, position + 1, 0.125)
+    qd, out = runtime.tensor(batch, heads * width), runtime.tensor(batch, heads * width)
+    kd, vd, pd = runtime.tensor(keys.size), runtime.tensor(values.size), runtime.tensor_u32(batch)
+    runtime.write(qd, q.reshape(batch, -1))
+    runtime.write(kd, keys.reshape(-1))
+    runtime.write(vd, values.reshape(-1))
+    runtime.write(pd, position)
+    runtime.attend(qd, kd, vd, pd, 0.125, heads, key_heads, width, capacity, out)
+    assert np.abs(runtime.read(out) - expected.reshape(batch, -1)).max() <= 1e-5
+
+
+def test_argmax_takes_the_lowest_index_on_ties(runtime, oracle):
+    x = oracle.Stream(12).normal(3 * 5000).reshape(3, 5000)
+    x[0, 4000] = x[0, 17] = 9.0
+    x[1, 4999] = 8.0
+    x[2] = -1.0
+    xd, out = runtime.tensor(3, 5000), runtime.tensor_u32(3)
+    runtime.write(xd, x)
+    runtime.argmax(xd, out)
+    assert list(runtime.read(out, dtype=np.uint32)) == [17, 4999, 0]
+    assert list(oracle.argmax(x)) == [17, 4999, 0]
+
+
+def load_model(rt, config, packed, norms):
+    weights, dnorms = {}, {}
+    c = config
+    for layer in range(c.layers):
+        name = lambda part: f"blk.{layer}.{part}.weight"  # noqa: E731
+        weights[name("attn_qkv")] = rt.load_stacked(c.element, c.hidden, [
+            (c.query_width, packed[name("attn_q")]), (c.key_width, packed[name("attn_k")]),
+            (c.key_width, packed[name("attn_v")])])
+        for part, n, k in c.linears()[3:]:
+            weights[name(part)] = rt.load(c.element, n, k, packed[name(part)])
+    weights["output.weight"] = rt.load(c.element, c.vocab, c.hidden, packed["output.weight"])
+    if c.tied_head:
+        weights["token_embd.weight"] = weights["output.weight"]
+    else:
+        weights["token_embd.weight"] = rt.load(c.element, c.vocab, c.hidden, packed["token_embd.weight"], seal=False)
+    for key, value in norms.items():
+        dnorms[key] = rt.tensor(value.size)
+        rt.write(dnorms[key], value)
+    return weights, dnorms
+
+
+SMALL = {
+    "q8_0": qwen.Config("tiny-q8_0", 2, 896, 14, 2, 64, 4864, 2048, nb.Q8_0, tied_head=True),
+    "q4_k": qwen.Config("tiny-q4_k", 2, 1024, 8, 2, 128, 2816, 2048, nb.Q4K),
+}
+
+
+@pytest.mark.parametrize("name,batch", [("q8_0", 1), ("q4_k", 1), ("q4_k", 3)])
+def test_greedy_tokens_match_the_oracle_for_64_steps(oracle, name, batch):
+    from oracle.decoder import OracleDecoder, synthetic_model
+
+    config = SMALL[name]
+    packed, norms = synthetic_model(config, seed=23)
+    prompts = (oracle.Stream(29).uniform(batch * 16, 0.0, 1.0) * config.vocab).astype(np.uint32).reshape(batch, 16)
+    want, margins = OracleDecoder(config, packed, norms, batch=batch, capacity=96).generate(prompts, 64)
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weights, dnorms = load_model(rt, config, packed, norms)
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=96)
+        eager = decoder.generate(prompts, 64)
+        decoder.record()
+        replayed = decoder.generate(prompts, 64)
+    finally:
+        rt.close()
+    assert np.array_equal(eager, replayed), "a recorded step decodes what the eager step decodes"
+    differs = np.argwhere(eager != want)
+    if differs.size:
+        b, at = differs[0]
+        pytest.fail(f"sequence {b} leaves the oracle at step {at}: {eager[b, at]} for {want[b, at]}, "
+                    f"the oracle's margin there is {margins[b, at]:.3e}")
