@@ -3,9 +3,9 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-One step = one decoded token's pass over every Q4_K projection of a Qwen2.5-32B-shaped
-decoder (64 layers of q/k/v, output, gate, up, down, then the head: 17.99 GB of GGUF
-blocks, far larger than L2, so every step streams them from HBM).  Prints ONE JSON line.
+One step = one greedily decoded token of a random-init Qwen2.5-32B-shaped decoder with Q4_K
+projections (64 layers; 17.99 GB of GGUF blocks per token, far larger than L2, so every step
+streams them from HBM) after a 512-token random prompt.  Prints ONE JSON line.
 With N > 1 (launched under torchrun) every rank runs the same model on its own GPU.
 """
 from __future__ import annotations
@@ -115,7 +115,7 @@ def cpu_baseline(config, seconds: float = 12.0):
     x = oracle.Stream(29).normal(k).reshape(1, k)
     oracle.linear(config.element, packed, n, k, x, threads=cores)  # warm-up
     runs, spent = 0, 0.0
-    while spent < seconds and runs < 64:
+    while spent < seconds and runs < 4096:
         t0 = time.perf_counter()
         oracle.linear(config.element, packed, n, k, x, threads=cores)
         spent += time.perf_counter() - t0
@@ -183,32 +183,35 @@ def run_ours(args):
 
     import neura_b200 as nb
     from neura_b200 import qwen
-    from neura_b200.synthetic import synthetic_weights
+    from neura_b200.synthetic import synthetic_norms, synthetic_weights
 
     config = workload_config(args.workload)
     rows = args.batch
+    warmup = max(3, args.warmup)
+    capacity = args.prompt + 2 * (warmup + args.steps) + 8
     rt = nb.Runtime(local)
     rt.use_stream(rt.new_stream())
     tstream = torch.cuda.ExternalStream(rt.stream.value, device=torch.device("cuda", local))
     weights = synthetic_weights(rt, config, seed=23 + rank)
-    stack = qwen.LinearStack(rt, config, weights, rows=rows)
+    norms = synthetic_norms(rt, config)
+    decoder = qwen.Decoder(rt, config, weights, norms, batch=rows, capacity=capacity)
 
-    # pinned host buffers of the end-to-end path: the token's input activations in, logits out
-    x_host = torch.randn(rows, config.hidden, generator=torch.Generator().manual_seed(29)).pin_memory()
-    top_host = torch.empty(rows, config.vocab, dtype=torch.float32).pin_memory()
-    h2d, d2h = x_host.numel() * 4, top_host.numel() * 4
-
-    def write_input():
-        rt._lib.neura_cuda_write(rt._ctx, rt.stream, stack.hidden.ptr, x_host.data_ptr(), h2d)
-
-    def read_output():
-        rt._lib.neura_cuda_read(rt._ctx, rt.stream, top_host.data_ptr(), stack.logits.ptr, d2h)
-
-    write_input()
-    stack.token()          # eager once: sizes every scratch region before recording
+    # the prompt: random token ids, fed one position at a time through the decode step
+    prompts = np.random.default_rng(29).integers(0, config.vocab, (rows, args.prompt), dtype=np.uint32)
+    decoder.reset()
+    rt.write(decoder.tokens, prompts[:, 0].copy())
+    decoder.step()          # eager once: sizes every scratch region before recording
     rt.sync()
-    program = stack.record()
-    launches0 = rt.launches
+    decoder.record()
+    launches_per_token = decoder.launches_per_token()
+    for at in range(1, args.prompt):
+        rt.write(decoder.tokens, prompts[:, at].copy())
+        decoder.run_token()
+    rt.sync()
+
+    # pinned host buffers of the end-to-end path: token ids in, token ids out
+    ids_host = torch.zeros(rows, dtype=torch.int32).pin_memory()
+    h2d = d2h = rows * 4
 
     def barrier():
         rt.sync()
@@ -216,33 +219,33 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident throughput -------------------------------------------------
-    for _ in range(max(3, args.warmup)):
-        write_input()
-        rt.run(program)
+    # ---- device-resident throughput: ids and cursors stay on the device --------------
+    for _ in range(warmup):
+        decoder.run_token()
     barrier()
+    launches0 = rt.launches
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         time.sleep(0.15)
         start.record(tstream)
         for _ in range(args.steps):
-            rt.run(program)
+            decoder.run_token()
         stop.record(tstream)
         barrier()
         time.sleep(0.15)
     ms = start.elapsed_time(stop)
-    launches = rt.launches - launches0 - max(3, args.warmup) * stack.launches_per_token()
+    launches = rt.launches - launches0
     clock_summary = clocks.summary()
 
-    # ---- end to end: host buffers in and out every step -------------------------------
+    # ---- end to end: the host loop of Batch::step — write ids, run, read ids ---------------
+    rt._lib.neura_cuda_read(rt._ctx, rt.stream, ids_host.data_ptr(), decoder.tokens.ptr, d2h)
     barrier()
     t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = args.steps
     t_start.record(tstream)
-    for _ in range(e2e_steps):
-        write_input()
-        rt.run(program)
-        read_output()
+    for _ in range(args.steps):
+        rt._lib.neura_cuda_write(rt._ctx, rt.stream, decoder.tokens.ptr, ids_host.data_ptr(), h2d)
+        decoder.run_token()
+        rt._lib.neura_cuda_read(rt._ctx, rt.stream, ids_host.data_ptr(), decoder.tokens.ptr, d2h)
         rt.sync()
     t_stop.record(tstream)
     barrier()
@@ -251,16 +254,18 @@ def run_ours(args):
     # ---- roofline of the dominant kernel (the Q4_K product), timed on its own ----------
     peak, peak_kind = measured_peaks()
     name, n, k = "ffn_up", config.feed_forward, config.hidden
-    rt.stage(stack.hidden, config.element)
+    rt.stage(decoder.hidden, config.element)
     reps = 4
     r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for layer in range(config.layers):
-        rt.linear_staged(weights[f"blk.{layer}.{name}.weight"], stack.held)
+    rt.capture_begin()
+    for layer in range(config.layers):  # 64 different matrices: 5 GB between reuses, L2 holds none of it
+        rt.linear_staged(weights[f"blk.{layer}.{name}.weight"], decoder.held)
+    sweep = rt.capture_end()
+    rt.run(sweep)
     rt.sync()
     r0.record(tstream)
     for _ in range(reps):
-        for layer in range(config.layers):  # 64 different matrices: 5 GB between reuses, L2 holds none of it
-            rt.linear_staged(weights[f"blk.{layer}.{name}.weight"], stack.held)
+        rt.run(sweep)
     r1.record(tstream)
     rt.sync()
     kernel_ms = r0.elapsed_time(r1) / (reps * config.layers)
@@ -275,21 +280,24 @@ def run_ours(args):
         tokens = rows * args.steps * world
         line = {
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": config.name, "batch": rows, "part": "projections and head of every layer "
-                       "(norms, RoPE and attention not yet in the step)", "parallelism": f"replicas x{world}",
-                       "l2": "inputs larger than L2 (17.99 GB of weights per step)",
+            "config": {"workload": f"{config.name} decode: {config.layers} layers, hidden {config.hidden}, "
+                                   f"{config.heads}/{config.key_heads} heads x {config.head_width}, ff {config.feed_forward}, "
+                                   f"vocab {config.vocab}; {args.prompt}-token random prompt, greedy",
+                       "batch": rows, "parallelism": f"replicas x{world}",
+                       "l2": f"inputs larger than L2 ({config.weight_bytes() / 1e9:.2f} GB of weights per step)",
                        "weight_bytes_per_token": config.weight_bytes()},
             "clocks": clock_summary,
-            "e2e": {"value": rows * e2e_steps * world / (e2e_ms * 1e-3), "unit": UNIT,
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": f"gemv_q4k_kernel<NT> on [{n}x{k}] at batch {rows}",
+                         "kernel": f"gemv_stream_kernel<Q4_K> on [{n}x{k}] at batch {rows}",
                          "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
-                         "step_gbs": config.weight_bytes() / (ms / args.steps * 1e-3) / 1e9},
+                         "step_gbs": config.weight_bytes() / (ms / args.steps * 1e-3) / 1e9,
+                         "launches_per_token": launches_per_token},
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(config)
@@ -307,6 +315,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="qwen2.5-32b-q4_k")
     parser.add_argument("--batch", type=int, default=1)
+    parser.add_argument("--prompt", type=int, default=512)
     parser.add_argument("--no-cpu", action="store_true")
     args = parser.parse_args()
     if args.impl == "reference":

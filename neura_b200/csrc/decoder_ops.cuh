@@ -56,64 +56,138 @@ __global__ void rope_cache_kernel(const __grid_constant__ RopeCacheParams p) {
 
 // Cache::attend for one new row per sequence (crates/neura-decoder/src/cache.rs:311-406 over
 // crates/neura-kernel/src/task/attention.rs:309-617): softmax(q.k * scale) v with query head h
-// reading key head h / (heads / key_heads).  One CTA per (sequence, query head); positions
-// 0..count[b]-1 are live (count = position + 1 after the write).
+// reading key head h / (heads / key_heads); positions 0..position[b] are live.
+//
+// One CTA per (sequence, key head, split of the positions): the query heads that share the key
+// head are served together, so keys and values are read once.  Each CTA leaves, per query head,
+// its partial (largest logit, sum of exponentials, weighted values); the last CTA of a
+// (sequence, key head) to arrive merges the splits in order (the reference's key-split attention
+// with its AttentionFold merge, crates/neura-abi/src/kind.rs:638-645).
+constexpr uint32_t kAttendMaxGroup = 8;    // query heads per key head
+constexpr uint32_t kAttendMaxChunk = 128;  // positions one CTA takes
+
 struct AttendParams {
     const float *q;           // [batch][q_stride], head h at h*width
     uint64_t q_stride;
-    const float *keys, *values;
-    const uint32_t *position; // count = position[b] + 1
+    const float *keys, *values;   // [batch][key_heads][capacity][width]
+    const uint32_t *position;
     float *out;               // [batch][out_stride]
     uint64_t out_stride;
+    float *partial;           // [batch][heads][splits][width + 2]
+    unsigned int *counters;   // [batch][key_heads], zero between launches
     float scale;
-    uint32_t batch, heads, key_heads, width, capacity;
+    uint32_t batch, heads, key_heads, width, capacity, splits;
 };
 
 __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ AttendParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    extern __shared__ float shared[];   // [capacity] logits, then [4] reduction slots
-    float *logits = shared;
-    float *slots = shared + p.capacity;
-    const uint32_t b = blockIdx.x / p.heads, h = blockIdx.x % p.heads;
+    extern __shared__ float shared[];
+    const uint32_t group = p.heads / p.key_heads;
+    float *qs = shared;                                  // [group][width]
+    float *logits = qs + group * p.width;                // [group][kAttendMaxChunk]
+    float *stats = logits + group * kAttendMaxChunk;     // [group][2]: largest, sum
+    __shared__ unsigned int arrived;
+    const uint32_t split = blockIdx.x % p.splits;
+    const uint32_t kh = (blockIdx.x / p.splits) % p.key_heads;
+    const uint32_t b = blockIdx.x / (p.splits * p.key_heads);
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const uint32_t count = min(p.position[b] + 1, p.capacity);
-    const uint32_t kh = h / (p.heads / p.key_heads);
-    const float *q = p.q + (uint64_t)b * p.q_stride + (uint64_t)h * p.width;
+    const uint32_t chunk = min((count + p.splits - 1) / p.splits, kAttendMaxChunk);
+    // (the host sizes `splits` so that capacity / splits <= kAttendMaxChunk)
+    const uint32_t first = min(split * chunk, count), last = min(first + chunk, count);
     const float *k = p.keys + ((uint64_t)b * p.key_heads + kh) * p.capacity * p.width;
     const float *v = p.values + ((uint64_t)b * p.key_heads + kh) * p.capacity * p.width;
-    // scores: one warp per position, lanes across the head width
-    float largest = -INFINITY;
-    for (uint32_t pos = warp; pos < count; pos += warps) {
-        float total = 0.0f;
-        for (uint32_t d = lane; d < p.width; d += 32) total = fmaf(q[d], k[(uint64_t)pos * p.width + d], total);
-        for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-        total *= p.scale;
-        if (lane == 0) logits[pos] = total;
-        largest = fmaxf(largest, total);
+    for (uint32_t i = threadIdx.x; i < group * p.width; i += blockDim.x)
+        qs[i] = p.q[(uint64_t)b * p.q_stride + (uint64_t)(kh * group) * p.width + i];
+    __syncthreads();
+    // logits of this split: one warp per position, lanes across the head width
+    for (uint32_t pos = first + warp; pos < last; pos += warps) {
+        float acc[kAttendMaxGroup];
+#pragma unroll
+        for (uint32_t g = 0; g < kAttendMaxGroup; ++g) acc[g] = 0.0f;
+        for (uint32_t d = lane; d < p.width; d += 32) {
+            const float kv = k[(uint64_t)pos * p.width + d];
+#pragma unroll
+            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                if (g < group) acc[g] = fmaf(qs[g * p.width + d], kv, acc[g]);
+        }
+#pragma unroll
+        for (uint32_t g = 0; g < kAttendMaxGroup; ++g) {
+            if (g < group) {
+                float total = acc[g];
+                for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                if (lane == 0) logits[g * kAttendMaxChunk + (pos - first)] = total * p.scale;
+            }
+        }
     }
-    if (lane == 0) slots[warp] = largest;
     __syncthreads();
-    largest = slots[0];
-    for (uint32_t w = 1; w < warps; ++w) largest = fmaxf(largest, slots[w]);
-    __syncthreads();
-    float sum = 0.0f;
-    for (uint32_t pos = threadIdx.x; pos < count; pos += blockDim.x) {
-        const float e = expf(logits[pos] - largest);
-        logits[pos] = e;
-        sum += e;
+    // per query head: largest logit and sum of exponentials of the split (one warp per head)
+    for (uint32_t g = warp; g < group; g += warps) {
+        float largest = -INFINITY;
+        for (uint32_t i = lane; i < last - first; i += 32) largest = fmaxf(largest, logits[g * kAttendMaxChunk + i]);
+        for (int o = 16; o; o >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+        float sum = 0.0f;
+        for (uint32_t i = lane; i < last - first; i += 32) {
+            const float e = expf(logits[g * kAttendMaxChunk + i] - largest);
+            logits[g * kAttendMaxChunk + i] = e;
+            sum += e;
+        }
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) { stats[g * 2] = largest; stats[g * 2 + 1] = sum; }
     }
-    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) slots[warp] = sum;
     __syncthreads();
-    float total = 0.0f;
-    for (uint32_t w = 0; w < warps; ++w) total += slots[w];
-    // weighted sum of the values: one thread per channel, coalesced across the head width
+    // weighted values: one thread per channel, every value row read once for all the group's heads
     for (uint32_t d = threadIdx.x; d < p.width; d += blockDim.x) {
-        float acc = 0.0f;
-        for (uint32_t pos = 0; pos < count; ++pos) acc = fmaf(logits[pos], v[(uint64_t)pos * p.width + d], acc);
-        p.out[(uint64_t)b * p.out_stride + (uint64_t)h * p.width + d] = acc / total;
+        float acc[kAttendMaxGroup];
+#pragma unroll
+        for (uint32_t g = 0; g < kAttendMaxGroup; ++g) acc[g] = 0.0f;
+        for (uint32_t pos = first; pos < last; ++pos) {
+            const float value = v[(uint64_t)pos * p.width + d];
+#pragma unroll
+            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                if (g < group) acc[g] = fmaf(logits[g * kAttendMaxChunk + (pos - first)], value, acc[g]);
+        }
+#pragma unroll
+        for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+            if (g < group)
+                __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (p.width + 2) + d, acc[g]);
     }
+    if (threadIdx.x < group * 2) {
+        const uint32_t g = threadIdx.x / 2, which = threadIdx.x % 2;
+        __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (p.width + 2) + p.width + which,
+               stats[g * 2 + which]);
+    }
+    // the last split of this (sequence, key head) to arrive merges them all, in split order
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        arrived = atomicAdd(p.counters + b * p.key_heads + kh, 1u);
+        __threadfence();
+    }
+    __syncthreads();
+    if (arrived != p.splits - 1) return;
+    for (uint32_t g = 0; g < group; ++g) {
+        const float *mine = p.partial + ((uint64_t)b * p.heads + kh * group + g) * p.splits * (p.width + 2);
+        float largest = -INFINITY;
+        for (uint32_t s = 0; s < p.splits; ++s) largest = fmaxf(largest, __ldcg(mine + s * (p.width + 2) + p.width));
+        float total = 0.0f;
+        for (uint32_t s = 0; s < p.splits; ++s) {
+            const float m = __ldcg(mine + s * (p.width + 2) + p.width);
+            const float factor = m == -INFINITY ? 0.0f : expf(m - largest);
+            total = fmaf(__ldcg(mine + s * (p.width + 2) + p.width + 1), factor, total);
+        }
+        for (uint32_t d = threadIdx.x; d < p.width; d += blockDim.x) {
+            float acc = 0.0f;
+            for (uint32_t s = 0; s < p.splits; ++s) {
+                const float m = __ldcg(mine + s * (p.width + 2) + p.width);
+                const float factor = m == -INFINITY ? 0.0f : expf(m - largest);
+                acc = fmaf(__ldcg(mine + s * (p.width + 2) + d), factor, acc);
+            }
+            p.out[(uint64_t)b * p.out_stride + (uint64_t)(kh * group + g) * p.width + d] = acc / total;
+        }
+    }
+    if (threadIdx.x == 0) p.counters[b * p.key_heads + kh] = 0u;
 }
 
 // argmax, the lowest index winning a tie (choice_precedes, crates/neura-kernel/src/task/choice.rs:46-52).

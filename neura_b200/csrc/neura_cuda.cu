@@ -57,7 +57,7 @@ struct Region {
 struct nc_context {
     int device = 0;
     int sms = 0;
-    Region dig, cs, sums, partial, counters, status, stage_x, stage_out;
+    Region dig, cs, sums, partial, counters, status, stage_x, stage_out, attend_partial, attend_counters;
     uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
     uint64_t launches = 0;
     bool capturing = false;
@@ -231,7 +231,7 @@ int32_t neura_cuda_open(int32_t device, nc_context **out) {
 int32_t neura_cuda_close(nc_context *ctx) {
     if (!ctx) return 0;
     cudaSetDevice(ctx->device);
-    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out})
+    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
     return 0;
@@ -573,16 +573,20 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, ui
         return refuse(kBadArgument, "attention needs a context, queries, a cache, positions and an output");
     if (!batch || !heads || !key_heads || heads % key_heads || !width || !capacity)
         return refuse(kBadArgument, "%u query heads do not share %u key heads", heads, key_heads);
-    const size_t smem = ((size_t)capacity + 8) * sizeof(float);
-    if (smem > 200 * 1024) return refuse(kBadArgument, "a cache of %u slots does not fit the attention kernel's shared memory", capacity);
-    static bool raised[64] = {false};
-    if (smem > 48 * 1024 && !raised[ctx->device & 63]) {
-        NC_CUDA(cudaFuncSetAttribute(attend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        raised[ctx->device & 63] = true;
-    }
-    AttendParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride, scale,
-                   batch, heads, key_heads, width, capacity};
-    NC_CUDA(launch_dependent(attend_kernel, dim3(batch * heads), dim3(128), smem, (cudaStream_t)stream_, p));
+    const uint32_t group = heads / key_heads;
+    if (group > kAttendMaxGroup)
+        return refuse(kBadArgument, "%u query heads per key head are more than the %u the attention kernel serves together",
+                      group, kAttendMaxGroup);
+    const uint32_t splits = (capacity + 63) / 64;  // at most 64 <= kAttendMaxChunk positions per CTA
+    const size_t smem = ((size_t)group * width + (size_t)group * kAttendMaxChunk + (size_t)group * 2) * sizeof(float);
+    if (smem > 48 * 1024) return refuse(kBadArgument, "heads of width %u do not fit the attention kernel's shared memory", width);
+    int32_t rc;
+    if ((rc = ensure(ctx, ctx->attend_partial, (uint64_t)batch * heads * splits * (width + 2) * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->attend_counters, (uint64_t)batch * key_heads * sizeof(unsigned int), true))) return rc;
+    AttendParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride,
+                   (float *)ctx->attend_partial.ptr, (unsigned int *)ctx->attend_counters.ptr, scale,
+                   batch, heads, key_heads, width, capacity, splits};
+    NC_CUDA(launch_dependent(attend_kernel, dim3(batch * key_heads * splits), dim3(128), smem, (cudaStream_t)stream_, p));
     ctx->launches++;
     return 0;
 }

@@ -10,7 +10,7 @@ from .runtime import Runtime, Weight, payload_bytes
 
 
 def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: float = 0.02,
-                      fuse_qkv: bool = True) -> Dict[str, Weight]:
+                      fuse_qkv: bool = True, with_embedding: bool = True) -> Dict[str, Weight]:
     import torch
 
     device = torch.device("cuda", rt.device)
@@ -57,6 +57,36 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
         at += rt.sealed_bytes(config.element, rows, k)
         done += rows
     weights["output.weight"] = Weight(base, config.element, 1, total, k, at - base)
+    if with_embedding:
+        if config.tied_head:
+            weights["token_embd.weight"] = weights["output.weight"]
+        else:  # a table of its own, kept in GGUF order (only rows are gathered from it)
+            row_bytes = payload_bytes(config.element, k)
+            table = rt.alloc(row_bytes * total)
+            done = 0
+            with torch.cuda.stream(stream):
+                while done < total:
+                    rows = min(16 * 1024, total - done)
+                    view = numbers[: rows * k]
+                    view.normal_(0.0, deviation, generator=gen)
+                    rt.quantize_device(config.element, view.data_ptr(), rows * k, table + done * row_bytes)
+                    done += rows
+            weights["token_embd.weight"] = Weight(table, config.element, 0, total, k, row_bytes * total)
     rt.sync()
     del numbers, blocks
     return weights
+
+
+def synthetic_norms(rt: Runtime, config: Config):
+    """RMSNorm weights of 1, as a random-init model has them."""
+    import numpy as np
+
+    ones = np.ones(config.hidden, dtype=np.float32)
+    norms = {}
+    names = ["output_norm.weight"]
+    for layer in range(config.layers):
+        names += [f"blk.{layer}.attn_norm.weight", f"blk.{layer}.ffn_norm.weight"]
+    for name in names:
+        norms[name] = rt.tensor(config.hidden)
+        rt.write(norms[name], ones)
+    return norms
