@@ -64,7 +64,8 @@ __global__ void rope_cache_kernel(const __grid_constant__ RopeCacheParams p) {
 // (sequence, key head) to arrive merges the splits in order (the reference's key-split attention
 // with its AttentionFold merge, crates/neura-abi/src/kind.rs:638-645).
 constexpr uint32_t kAttendMaxGroup = 8;    // query heads per key head
-constexpr uint32_t kAttendMaxChunk = 128;  // positions one CTA takes
+constexpr uint32_t kAttendTile = 64;       // positions one CTA takes
+constexpr uint32_t kAttendMaxChunk = 64;   // row length of the per-head logit and merge tables (>= tile, >= splits)
 
 struct AttendParams {
     const float *q;           // [batch][q_stride], head h at h*width
@@ -79,45 +80,65 @@ struct AttendParams {
     uint32_t batch, heads, key_heads, width, capacity, splits;
 };
 
+__device__ __forceinline__ void copy16_async(void *dst_shared, const void *src_global) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)),
+                 "l"(src_global)
+                 : "memory");
+}
+
+// WIDTH is the head width (64 or 128).  The split's keys and values (contiguous in the cache)
+// are copied to shared memory with asynchronous 16-byte copies, all in flight at once, so the
+// cache costs one memory round trip per CTA.
+template <uint32_t WIDTH>
 __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ AttendParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    extern __shared__ float shared[];
+    extern __shared__ __align__(16) float shared[];
     const uint32_t group = p.heads / p.key_heads;
-    float *qs = shared;                                  // [group][width]
-    float *logits = qs + group * p.width;                // [group][kAttendMaxChunk]
-    float *stats = logits + group * kAttendMaxChunk;     // [group][2]: largest, sum
+    float *ks = shared;                                  // [kAttendTile][WIDTH]
+    float *vs = ks + kAttendTile * WIDTH;                // [kAttendTile][WIDTH]
+    float *qs = vs + kAttendTile * WIDTH;                // [group][WIDTH]
+    float *logits = qs + kAttendMaxGroup * WIDTH;        // [group][kAttendMaxChunk]
+    float *stats = logits + kAttendMaxGroup * kAttendMaxChunk;  // [group][2]: largest, sum
     __shared__ unsigned int arrived;
     const uint32_t split = blockIdx.x % p.splits;
     const uint32_t kh = (blockIdx.x / p.splits) % p.key_heads;
     const uint32_t b = blockIdx.x / (p.splits * p.key_heads);
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const uint32_t count = min(p.position[b] + 1, p.capacity);
-    const uint32_t chunk = min((count + p.splits - 1) / p.splits, kAttendMaxChunk);
-    // (the host sizes `splits` so that capacity / splits <= kAttendMaxChunk)
-    const uint32_t first = min(split * chunk, count), last = min(first + chunk, count);
-    const float *k = p.keys + ((uint64_t)b * p.key_heads + kh) * p.capacity * p.width;
-    const float *v = p.values + ((uint64_t)b * p.key_heads + kh) * p.capacity * p.width;
-    for (uint32_t i = threadIdx.x; i < group * p.width; i += blockDim.x)
-        qs[i] = p.q[(uint64_t)b * p.q_stride + (uint64_t)(kh * group) * p.width + i];
+    const uint32_t chunk = min((count + p.splits - 1) / p.splits, kAttendTile);
+    // (the host sizes `splits` so that capacity / splits <= kAttendTile)
+    const uint32_t first = min(split * chunk, count), last = min(first + chunk, count), held = last - first;
+    const float *k = p.keys + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
+    const float *v = p.values + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
+    for (uint32_t i = threadIdx.x; i < held * (WIDTH / 4); i += blockDim.x) {
+        copy16_async(ks + i * 4, k + i * 4);
+        copy16_async(vs + i * 4, v + i * 4);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (uint32_t i = threadIdx.x; i < group * WIDTH; i += blockDim.x)
+        qs[i] = p.q[(uint64_t)b * p.q_stride + (uint64_t)(kh * group) * WIDTH + i];
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     // logits of this split: one warp per position, lanes across the head width
-    for (uint32_t pos = first + warp; pos < last; pos += warps) {
-        float acc[kAttendMaxGroup];
+    constexpr uint32_t PER = WIDTH / 32;
+    float qr[kAttendMaxGroup][PER];
 #pragma unroll
-        for (uint32_t g = 0; g < kAttendMaxGroup; ++g) acc[g] = 0.0f;
-        for (uint32_t d = lane; d < p.width; d += 32) {
-            const float kv = k[(uint64_t)pos * p.width + d];
+    for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
 #pragma unroll
-            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
-                if (g < group) acc[g] = fmaf(qs[g * p.width + d], kv, acc[g]);
-        }
+        for (uint32_t i = 0; i < PER; ++i) qr[g][i] = g < group ? qs[g * WIDTH + lane * PER + i] : 0.0f;
+    for (uint32_t pos = warp; pos < held; pos += warps) {
+        float kv[PER];
+#pragma unroll
+        for (uint32_t i = 0; i < PER; ++i) kv[i] = ks[pos * WIDTH + lane * PER + i];
 #pragma unroll
         for (uint32_t g = 0; g < kAttendMaxGroup; ++g) {
             if (g < group) {
-                float total = acc[g];
+                float total = 0.0f;
+#pragma unroll
+                for (uint32_t i = 0; i < PER; ++i) total = fmaf(qr[g][i], kv[i], total);
                 for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-                if (lane == 0) logits[g * kAttendMaxChunk + (pos - first)] = total * p.scale;
+                if (lane == 0) logits[g * kAttendMaxChunk + pos] = total * p.scale;
             }
         }
     }
@@ -125,10 +146,10 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     // per query head: largest logit and sum of exponentials of the split (one warp per head)
     for (uint32_t g = warp; g < group; g += warps) {
         float largest = -INFINITY;
-        for (uint32_t i = lane; i < last - first; i += 32) largest = fmaxf(largest, logits[g * kAttendMaxChunk + i]);
+        for (uint32_t i = lane; i < held; i += 32) largest = fmaxf(largest, logits[g * kAttendMaxChunk + i]);
         for (int o = 16; o; o >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
         float sum = 0.0f;
-        for (uint32_t i = lane; i < last - first; i += 32) {
+        for (uint32_t i = lane; i < held; i += 32) {
             const float e = expf(logits[g * kAttendMaxChunk + i] - largest);
             logits[g * kAttendMaxChunk + i] = e;
             sum += e;
@@ -138,24 +159,24 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     }
     __syncthreads();
     // weighted values: one thread per channel, every value row read once for all the group's heads
-    for (uint32_t d = threadIdx.x; d < p.width; d += blockDim.x) {
+    for (uint32_t d = threadIdx.x; d < WIDTH; d += blockDim.x) {
         float acc[kAttendMaxGroup];
 #pragma unroll
         for (uint32_t g = 0; g < kAttendMaxGroup; ++g) acc[g] = 0.0f;
-        for (uint32_t pos = first; pos < last; ++pos) {
-            const float value = v[(uint64_t)pos * p.width + d];
+        for (uint32_t pos = 0; pos < held; ++pos) {
+            const float value = vs[pos * WIDTH + d];
 #pragma unroll
             for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
-                if (g < group) acc[g] = fmaf(logits[g * kAttendMaxChunk + (pos - first)], value, acc[g]);
+                if (g < group) acc[g] = fmaf(logits[g * kAttendMaxChunk + pos], value, acc[g]);
         }
 #pragma unroll
         for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
             if (g < group)
-                __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (p.width + 2) + d, acc[g]);
+                __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (WIDTH + 2) + d, acc[g]);
     }
     if (threadIdx.x < group * 2) {
         const uint32_t g = threadIdx.x / 2, which = threadIdx.x % 2;
-        __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (p.width + 2) + p.width + which,
+        __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (WIDTH + 2) + WIDTH + which,
                stats[g * 2 + which]);
     }
     // the last split of this (sequence, key head) to arrive merges them all, in split order
@@ -167,60 +188,104 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     }
     __syncthreads();
     if (arrived != p.splits - 1) return;
-    for (uint32_t g = 0; g < group; ++g) {
-        const float *mine = p.partial + ((uint64_t)b * p.heads + kh * group + g) * p.splits * (p.width + 2);
+    // merge: every load of a phase is issued before its first use, so each phase costs one round trip
+    float *factor = logits;   // [group][splits], reusing the logits area (splits <= kAttendMaxChunk)
+    float *totals = stats;    // [group]
+    const float *mine = p.partial + ((uint64_t)b * p.heads + kh * group) * p.splits * (p.width + 2);
+    for (uint32_t i = threadIdx.x; i < group * p.splits; i += blockDim.x)
+        factor[(i / p.splits) * kAttendMaxChunk + i % p.splits] = __ldcg(mine + (uint64_t)i * (p.width + 2) + p.width);
+    __syncthreads();
+    for (uint32_t g = warp; g < group; g += warps) {
         float largest = -INFINITY;
-        for (uint32_t s = 0; s < p.splits; ++s) largest = fmaxf(largest, __ldcg(mine + s * (p.width + 2) + p.width));
+        for (uint32_t s = lane; s < p.splits; s += 32) largest = fmaxf(largest, factor[g * kAttendMaxChunk + s]);
+        for (int o = 16; o; o >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
         float total = 0.0f;
-        for (uint32_t s = 0; s < p.splits; ++s) {
-            const float m = __ldcg(mine + s * (p.width + 2) + p.width);
-            const float factor = m == -INFINITY ? 0.0f : expf(m - largest);
-            total = fmaf(__ldcg(mine + s * (p.width + 2) + p.width + 1), factor, total);
+        for (uint32_t s = lane; s < p.splits; s += 32) {
+            const float m = factor[g * kAttendMaxChunk + s];
+            const float f = m == -INFINITY ? 0.0f : expf(m - largest);
+            factor[g * kAttendMaxChunk + s] = f;
+            total = fmaf(__ldcg(mine + ((uint64_t)g * p.splits + s) * (p.width + 2) + p.width + 1), f, total);
         }
-        for (uint32_t d = threadIdx.x; d < p.width; d += blockDim.x) {
-            float acc = 0.0f;
-            for (uint32_t s = 0; s < p.splits; ++s) {
-                const float m = __ldcg(mine + s * (p.width + 2) + p.width);
-                const float factor = m == -INFINITY ? 0.0f : expf(m - largest);
-                acc = fmaf(__ldcg(mine + s * (p.width + 2) + d), factor, acc);
-            }
-            p.out[(uint64_t)b * p.out_stride + (uint64_t)(kh * group + g) * p.width + d] = acc / total;
+        for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if (lane == 0) totals[g] = total;
+    }
+    __syncthreads();
+    for (uint32_t item = threadIdx.x; item < group * p.width; item += blockDim.x) {
+        const uint32_t g = item / p.width, d = item % p.width;
+        const float *from = mine + (uint64_t)g * p.splits * (p.width + 2) + d;
+        float acc = 0.0f;
+        for (uint32_t s = 0; s < p.splits; s += 8) {
+            float part[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) part[u] = s + u < p.splits ? __ldcg(from + (uint64_t)(s + u) * (p.width + 2)) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (s + u < p.splits) acc = fmaf(part[u], factor[g * kAttendMaxChunk + s + u], acc);
         }
+        p.out[(uint64_t)b * p.out_stride + (uint64_t)(kh * group + g) * p.width + d] = acc / totals[g];
     }
     if (threadIdx.x == 0) p.counters[b * p.key_heads + kh] = 0u;
 }
 
 // argmax, the lowest index winning a tie (choice_precedes, crates/neura-kernel/src/task/choice.rs:46-52).
-// One CTA per row.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float *x, uint64_t stride, uint32_t width, uint32_t *out) {
+// A row is shared by `slices` CTAs; the last of them to arrive merges their candidates.
+struct ArgmaxParams {
+    const float *x;
+    uint64_t stride;
+    uint32_t width, slices;
+    uint32_t *out;
+    float *slice_value;          // [rows][slices]
+    uint32_t *slice_index;       // [rows][slices]
+    unsigned int *counters;      // [rows], zero between launches
+};
+
+__device__ __forceinline__ void argmax_take(float &value, uint32_t &index, float other, uint32_t other_index) {
+    if (other > value || (other == value && other_index < index)) { value = other; index = other_index; }
+}
+
+__global__ void __launch_bounds__(256) argmax_kernel(const __grid_constant__ ArgmaxParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ float best_value[32];
-    __shared__ uint32_t best_index[32];
-    const float *row = x + (uint64_t)blockIdx.x * stride;
+    __shared__ float best_value[8];
+    __shared__ uint32_t best_index[8];
+    __shared__ unsigned int arrived;
+    const uint32_t row = blockIdx.x / p.slices, slice = blockIdx.x % p.slices;
+    const float *x = p.x + (uint64_t)row * p.stride;
+    const uint32_t per = (p.width + p.slices - 1) / p.slices;
+    const uint32_t first = slice * per, last = min(first + per, p.width);
     float value = -INFINITY;
     uint32_t index = 0xffffffffu;
-    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
-        const float other = row[c];
-        if (other > value || (other == value && c < index)) { value = other; index = c; }
+    for (uint32_t c = first + threadIdx.x; c < last; c += blockDim.x * 8) {   // eight loads in flight per thread
+        float other[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) other[u] = c + u * blockDim.x < last ? x[c + u * blockDim.x] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) argmax_take(value, index, other[u], c + u * blockDim.x);
     }
-    for (int o = 16; o; o >>= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, value, o);
-        const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, o);
-        if (other > value || (other == value && other_index < index)) { value = other; index = other_index; }
-    }
+    for (int o = 16; o; o >>= 1)
+        argmax_take(value, index, __shfl_xor_sync(0xffffffffu, value, o), __shfl_xor_sync(0xffffffffu, index, o));
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { best_value[warp] = value; best_index[warp] = index; }
     __syncthreads();
-    if (warp == 0) {
-        value = lane < (blockDim.x >> 5) ? best_value[lane] : -INFINITY;
-        index = lane < (blockDim.x >> 5) ? best_index[lane] : 0xffffffffu;
-        for (int o = 16; o; o >>= 1) {
-            const float other = __shfl_xor_sync(0xffffffffu, value, o);
-            const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, o);
-            if (other > value || (other == value && other_index < index)) { value = other; index = other_index; }
-        }
-        if (lane == 0) out[blockIdx.x] = index == 0xffffffffu ? 0u : index;
+    if (threadIdx.x == 0) {
+        for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) argmax_take(value, index, best_value[w], best_index[w]);
+        __stcg(p.slice_value + row * p.slices + slice, value);
+        __stcg(p.slice_index + row * p.slices + slice, index);
+        __threadfence();
+        arrived = atomicAdd(p.counters + row, 1u);
+        __threadfence();
+    }
+    __syncthreads();
+    if (arrived != p.slices - 1 || warp != 0) return;
+    value = -INFINITY;
+    index = 0xffffffffu;
+    for (uint32_t s = lane; s < p.slices; s += 32)
+        argmax_take(value, index, __ldcg(p.slice_value + row * p.slices + s), __ldcg(p.slice_index + row * p.slices + s));
+    for (int o = 16; o; o >>= 1)
+        argmax_take(value, index, __shfl_xor_sync(0xffffffffu, value, o), __shfl_xor_sync(0xffffffffu, index, o));
+    if (lane == 0) {
+        p.out[row] = index == 0xffffffffu ? 0u : index;
+        p.counters[row] = 0u;
     }
 }
 

@@ -57,7 +57,7 @@ struct Region {
 struct nc_context {
     int device = 0;
     int sms = 0;
-    Region dig, cs, sums, partial, counters, status, stage_x, stage_out, attend_partial, attend_counters;
+    Region dig, cs, sums, partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch;
     uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
     uint64_t launches = 0;
     bool capturing = false;
@@ -231,7 +231,7 @@ int32_t neura_cuda_open(int32_t device, nc_context **out) {
 int32_t neura_cuda_close(nc_context *ctx) {
     if (!ctx) return 0;
     cudaSetDevice(ctx->device);
-    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters})
+    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
     return 0;
@@ -577,16 +577,27 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, ui
     if (group > kAttendMaxGroup)
         return refuse(kBadArgument, "%u query heads per key head are more than the %u the attention kernel serves together",
                       group, kAttendMaxGroup);
-    const uint32_t splits = (capacity + 63) / 64;  // at most 64 <= kAttendMaxChunk positions per CTA
-    const size_t smem = ((size_t)group * width + (size_t)group * kAttendMaxChunk + (size_t)group * 2) * sizeof(float);
-    if (smem > 48 * 1024) return refuse(kBadArgument, "heads of width %u do not fit the attention kernel's shared memory", width);
+    if (width != 64 && width != 128)
+        return refuse(kBadArgument, "the attention kernel is built for heads of width 64 and 128, not %u", width);
+    if (capacity > 64 * kAttendTile)
+        return refuse(kBadArgument, "a cache of %u slots is more than the %u the attention kernel splits", capacity,
+                      64 * kAttendTile);
+    const uint32_t splits = (capacity + kAttendTile - 1) / kAttendTile;  // <= 64, and <= kAttendTile positions per CTA
+    const size_t smem = ((size_t)2 * kAttendTile * width + (size_t)kAttendMaxGroup * width +
+                         (size_t)kAttendMaxGroup * kAttendMaxChunk + (size_t)kAttendMaxGroup * 2) * sizeof(float);
+    auto kernel = width == 128 ? attend_kernel<128> : attend_kernel<64>;
+    static bool raised[64][2] = {{false}};
+    if (!raised[ctx->device & 63][width == 128]) {
+        NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        raised[ctx->device & 63][width == 128] = true;
+    }
     int32_t rc;
     if ((rc = ensure(ctx, ctx->attend_partial, (uint64_t)batch * heads * splits * (width + 2) * sizeof(float), false))) return rc;
     if ((rc = ensure(ctx, ctx->attend_counters, (uint64_t)batch * key_heads * sizeof(unsigned int), true))) return rc;
     AttendParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride,
                    (float *)ctx->attend_partial.ptr, (unsigned int *)ctx->attend_counters.ptr, scale,
                    batch, heads, key_heads, width, capacity, splits};
-    NC_CUDA(launch_dependent(attend_kernel, dim3(batch * key_heads * splits), dim3(128), smem, (cudaStream_t)stream_, p));
+    NC_CUDA(launch_dependent(kernel, dim3(batch * key_heads * splits), dim3(128), smem, (cudaStream_t)stream_, p));
     ctx->launches++;
     return 0;
 }
@@ -595,7 +606,19 @@ int32_t neura_cuda_argmax(nc_context *ctx, void *stream_, const float *x_dev, ui
                           uint64_t stride, uint32_t *out_dev) {
     if (!ctx || !x_dev || !out_dev || !rows || !width) return refuse(kBadArgument, "argmax needs a context, rows and an output");
     if (stride < width) return refuse(kBadArgument, "rows of %u numbers overlap at stride %llu", width, (unsigned long long)stride);
-    NC_CUDA(launch_dependent(argmax_kernel, dim3(rows), dim3(1024), 0, (cudaStream_t)stream_, x_dev, stride, width, out_dev));
+    const uint32_t slices = width >= 8192 ? 64 : 1;
+    int32_t rc;
+    if ((rc = ensure(ctx, ctx->argmax_scratch, (uint64_t)rows * slices * 8 + (uint64_t)rows * 4 + 256, true))) return rc;
+    ArgmaxParams p;
+    p.x = x_dev;
+    p.stride = stride;
+    p.width = width;
+    p.slices = slices;
+    p.out = out_dev;
+    p.counters = (unsigned int *)ctx->argmax_scratch.ptr;
+    p.slice_value = (float *)((unsigned char *)ctx->argmax_scratch.ptr + (((uint64_t)rows * 4 + 255) / 256) * 256);
+    p.slice_index = (uint32_t *)(p.slice_value + (uint64_t)rows * slices);
+    NC_CUDA(launch_dependent(argmax_kernel, dim3(rows * slices), dim3(256), 0, (cudaStream_t)stream_, p));
     ctx->launches++;
     return 0;
 }

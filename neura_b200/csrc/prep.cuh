@@ -173,40 +173,72 @@ struct NormStageParams {
     float floor;
 };
 
+constexpr uint32_t kNormChunksPerWarp = 4;   // 8 warps x 4 chunks x 256 = rows of up to 8192 stay in registers
+
 __global__ void __launch_bounds__(256) rms_norm_stage_kernel(const __grid_constant__ NormStageParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float partial[8];
     __shared__ float scale_shared;
-    const uint32_t row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float *x = p.prep.x + (uint64_t)row * p.prep.x_stride;
+    const uint32_t row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const uint32_t chunks = (p.prep.k + 255) / 256;
+    const bool held = chunks <= warps * kNormChunksPerWarp;
+    // every load of the row is issued before the first use, so the row costs one memory round trip
+    float v[kNormChunksPerWarp][8];
     float square = 0.0f;
-    for (uint32_t c = threadIdx.x; c < p.prep.k; c += blockDim.x) square = fmaf(x[c], x[c], square);
+    if (held) {
+#pragma unroll
+        for (uint32_t i = 0; i < kNormChunksPerWarp; ++i) {
+            const uint32_t chunk = warp + i * warps, at = chunk * 256 + lane * 8;
+            load_chunk(p.prep, row, at, chunk < chunks && at < p.prep.k, v[i]);
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kNormChunksPerWarp; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) square = fmaf(v[i][j], v[i][j], square);
+    } else {
+        const float *x = p.prep.x + (uint64_t)row * p.prep.x_stride;
+        for (uint32_t c = threadIdx.x; c < p.prep.k; c += blockDim.x) square = fmaf(x[c], x[c], square);
+    }
     for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
     if (lane == 0) partial[warp] = square;
     __syncthreads();
     if (threadIdx.x == 0) {
         float total = 0.0f;
-        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) total += partial[w];
+        for (uint32_t w = 0; w < warps; ++w) total += partial[w];
         scale_shared = 1.0f / sqrtf(total / (float)p.prep.k + p.floor);
     }
     __syncthreads();
     const float scale = scale_shared;
-    const uint32_t chunks = (p.prep.k + 255) / 256;
-    for (uint32_t chunk = warp; chunk < chunks; chunk += (blockDim.x >> 5)) {
-        const uint32_t at = chunk * 256 + lane * 8;
-        const bool live = at < p.prep.k;
-        float v[8];
-        load_chunk(p.prep, row, at, live, v);
-        if (live) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                v[i] = v[i] * scale;
-                if (p.weight) v[i] = v[i] * p.weight[at + i];
-                if (p.normed) p.normed[(uint64_t)row * p.normed_stride + at + i] = v[i];
+    for (uint32_t i = 0; i < kNormChunksPerWarp; ++i) {
+        for (uint32_t chunk = warp + i * warps; chunk < chunks; chunk += held ? chunks : warps * kNormChunksPerWarp) {
+            const uint32_t at = chunk * 256 + lane * 8;
+            const bool live = at < p.prep.k;
+            float w[8];
+            if (held) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j] = v[i][j];
+            } else {
+                load_chunk(p.prep, row, at, live, w);
             }
+            if (live) {
+                float gain[8];
+                if (p.weight) {
+                    const float4 a = *reinterpret_cast<const float4 *>(p.weight + at);
+                    const float4 c = *reinterpret_cast<const float4 *>(p.weight + at + 4);
+                    gain[0] = a.x; gain[1] = a.y; gain[2] = a.z; gain[3] = a.w;
+                    gain[4] = c.x; gain[5] = c.y; gain[6] = c.z; gain[7] = c.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    w[j] = w[j] * scale;
+                    if (p.weight) w[j] = w[j] * gain[j];
+                    if (p.normed) p.normed[(uint64_t)row * p.normed_stride + at + j] = w[j];
+                }
+            }
+            stage_chunk(p.prep, row, chunk, w, live);
         }
-        stage_chunk(p.prep, row, chunk, v, live);
     }
 }
 
