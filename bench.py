@@ -6,7 +6,8 @@
 One step = one greedily decoded token of a random-init Qwen2.5-32B-shaped decoder with Q4_K
 projections (64 layers; 17.99 GB of GGUF blocks per token, far larger than L2, so every step
 streams them from HBM) after a 512-token random prompt.  Prints ONE JSON line.
-With N > 1 (launched under torchrun) every rank runs the same model on its own GPU.
+With N > 1 (launched under torchrun) the model is split tensor-parallel over the N GPUs: q/k/v, gate, up
+and the head by rows, attention output and down by K with one NCCL all-reduce each.
 """
 from __future__ import annotations
 
@@ -192,9 +193,15 @@ def run_ours(args):
     rt = nb.Runtime(local)
     rt.use_stream(rt.new_stream())
     tstream = torch.cuda.ExternalStream(rt.stream.value, device=torch.device("cuda", local))
-    weights = synthetic_weights(rt, config, seed=23 + rank)
+    shard = comm = None
+    if world > 1:  # tensor parallel: one model split over the ranks
+        from neura_b200 import parallel
+
+        shard = parallel.Shard(config, world, rank)
+        comm = parallel.TorchComm(world, rank, device=torch.device("cuda", local), stream=tstream)
+    weights = synthetic_weights(rt, config, seed=23 + rank, shard=shard)
     norms = synthetic_norms(rt, config)
-    decoder = qwen.Decoder(rt, config, weights, norms, batch=rows, capacity=capacity)
+    decoder = qwen.Decoder(rt, config, weights, norms, batch=rows, capacity=capacity, shard=shard, comm=comm)
 
     # the prompt: random token ids, fed one position at a time through the decode step
     prompts = np.random.default_rng(29).integers(0, config.vocab, (rows, args.prompt), dtype=np.uint32)
@@ -253,7 +260,7 @@ def run_ours(args):
 
     # ---- roofline of the dominant kernel (the Q4_K product), timed on its own ----------
     peak, peak_kind = measured_peaks()
-    name, n, k = "ffn_up", config.feed_forward, config.hidden
+    name, n, k = "ffn_up", decoder.feed_forward, config.hidden
     rt.stage(decoder.hidden, config.element)
     reps = 4
     r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -277,15 +284,15 @@ def run_ours(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(times[0]), float(times[1])
     if rank == 0:
-        tokens = rows * args.steps * world
+        tokens = rows * args.steps  # the ranks decode the same sequences together
         line = {
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{config.name} decode: {config.layers} layers, hidden {config.hidden}, "
                                    f"{config.heads}/{config.key_heads} heads x {config.head_width}, ff {config.feed_forward}, "
                                    f"vocab {config.vocab}; {args.prompt}-token random prompt, greedy",
-                       "batch": rows, "parallelism": f"replicas x{world}",
+                       "batch": rows, "parallelism": f"tp{world}" if world > 1 else "single GPU",
                        "l2": f"inputs larger than L2 ({config.weight_bytes() / 1e9:.2f} GB of weights per step)",
                        "weight_bytes_per_token": config.weight_bytes()},
             "clocks": clock_summary,
@@ -296,15 +303,19 @@ def run_ours(args):
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
                          "kernel": f"gemv_stream_kernel<Q4_K> on [{n}x{k}] at batch {rows}",
                          "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
-                         "step_gbs": config.weight_bytes() / (ms / args.steps * 1e-3) / 1e9,
+                         "step_gbs_per_gpu": (shard.local_bytes_per_token() if shard else config.weight_bytes())
+                                             / (ms / args.steps * 1e-3) / 1e9,
                          "launches_per_token": launches_per_token},
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(config)
         print(json.dumps(line))
     if dist is not None:
+        # (no destroy_process_group: with NCCL kernels held in a recorded program it was seen to wait forever)
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main():

@@ -151,6 +151,12 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream, const nc_weight *w, con
  * neura_cuda_stage or neura_cuda_linear on the context. */
 int32_t neura_cuda_stage(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint64_t x_stride,
                          uint32_t k, uint32_t element);
+/* neura_cuda_stage for a row-parallel shard (no counterpart in the reference, which runs on one
+ * device): the rows hold elements [lo, hi) of the K axis of a weight of `k` columns and the rest of
+ * K is staged as zero.  A rank of a tensor-parallel group keeps the whole super-blocks that cover
+ * its K range and stages its activations at their offset inside them; lo and hi are multiples of 32. */
+int32_t neura_cuda_stage_window(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                                uint32_t k, uint32_t element, uint32_t lo, uint32_t hi);
 int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev,
                                  uint64_t out_stride, const nc_step *chain, uint32_t n_steps);
 
@@ -186,6 +192,12 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream, const float *q_dev, uin
  * crates/neura-kernel/src/task/choice.rs:46-52): the lowest index wins a tie. */
 int32_t neura_cuda_argmax(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint32_t width,
                           uint64_t stride, uint32_t *out_dev);
+
+/* The same over rows whose columns arrive in segments (the shares of a column-parallel head gathered
+ * from the ranks of a tensor-parallel group, no counterpart in the reference): column c of row r is
+ * x_dev[(c / segment) * segment_stride + r * stride + c % segment]. */
+int32_t neura_cuda_argmax_segments(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint32_t width,
+                                   uint64_t stride, uint32_t segment, uint64_t segment_stride, uint32_t *out_dev);
 
 /* graph.gather of a quantised embedding table (crates/neura-kernel/src/task/select.rs:29-49 with
  * fetch_q8_0 / fetch_q4_k, fetch.rs:236-267): out[r] = dequantised row tokens_dev[r], bit-exact;

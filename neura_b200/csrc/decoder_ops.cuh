@@ -231,7 +231,9 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
 // A row is shared by `slices` CTAs; the last of them to arrive merges their candidates.
 struct ArgmaxParams {
     const float *x;
-    uint64_t stride;
+    uint64_t stride;             // between rows
+    uint64_t segment_stride;     // column c of a row lives at (c / segment) * segment_stride + c % segment
+    uint32_t segment;            // (a row gathered from several ranks is split in segments; else segment = width)
     uint32_t width, slices;
     uint32_t *out;
     float *slice_value;          // [rows][slices]
@@ -258,7 +260,10 @@ __global__ void __launch_bounds__(256) argmax_kernel(const __grid_constant__ Arg
     for (uint32_t c = first + threadIdx.x; c < last; c += blockDim.x * 8) {   // eight loads in flight per thread
         float other[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) other[u] = c + u * blockDim.x < last ? x[c + u * blockDim.x] : -INFINITY;
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t at = c + u * blockDim.x;
+            other[u] = at < last ? x[(uint64_t)(at / p.segment) * p.segment_stride + at % p.segment] : -INFINITY;
+        }
 #pragma unroll
         for (int u = 0; u < 8; ++u) argmax_take(value, index, other[u], c + u * blockDim.x);
     }

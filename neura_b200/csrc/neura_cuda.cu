@@ -384,15 +384,18 @@ int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, con
     return 0;
 }
 
-int32_t neura_cuda_stage(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
-                         uint32_t k, uint32_t element) {
+int32_t neura_cuda_stage_window(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                                uint32_t k, uint32_t element, uint32_t lo, uint32_t hi) {
     if (!ctx || !x_dev) return refuse(kBadArgument, "staging needs a context and activations");
     const uint32_t per = block_elements(element);
     if (!per || !k || k % per)
         return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
     if (rows == 0 || rows > kMaxRowsPerPass)
         return refuse(kBadArgument, "one staging holds 1 to %u rows, not %u", kMaxRowsPerPass, rows);
-    if (x_stride < k) return refuse(kBadArgument, "rows of %u activations overlap at stride %llu", k, (unsigned long long)x_stride);
+    if (lo >= hi || hi > k || lo % 32 || hi % 32)
+        return refuse(kBadArgument, "a window [%u, %u) of %u activations starts and ends on multiples of 32 inside them", lo, hi, k);
+    if (x_stride < hi - lo)
+        return refuse(kBadArgument, "rows of %u activations overlap at stride %llu", hi - lo, (unsigned long long)x_stride);
     if ((uintptr_t)x_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
     const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
     const uint32_t ncols = rows * 3;
@@ -411,6 +414,8 @@ int32_t neura_cuda_stage(nc_context *ctx, void *stream_, const float *x_dev, uin
     prep.ncols = ncols;
     prep.granule = element == NC_ELEMENT_Q4K ? 256 : 32;
     prep.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
+    prep.lo = lo;
+    prep.hi = hi;
     const uint64_t prep_warps = (uint64_t)rows * (kpad / 256);
     NC_CUDA(launch_dependent(prep_kernel, dim3((unsigned int)((prep_warps + 3) / 4)), dim3(128), 0,
                              (cudaStream_t)stream_, prep));
@@ -419,6 +424,13 @@ int32_t neura_cuda_stage(nc_context *ctx, void *stream_, const float *x_dev, uin
     ctx->staged_k = k;
     ctx->staged_granule = prep.granule;
     return 0;
+}
+
+int32_t neura_cuda_stage(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                         uint32_t k, uint32_t element) {
+    if (k == 0) return refuse(kBadArgument, "staging no activations stages nothing");
+    if (x_stride < k) return refuse(kBadArgument, "rows of %u activations overlap at stride %llu", k, (unsigned long long)x_stride);
+    return neura_cuda_stage_window(ctx, stream_, x_dev, rows, x_stride, k, element, 0, k);
 }
 
 int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight *w, float *out_dev,
@@ -535,6 +547,8 @@ int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x
     p.prep.ncols = ncols;
     p.prep.granule = element == NC_ELEMENT_Q4K ? 256 : 32;
     p.prep.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
+    p.prep.lo = 0;
+    p.prep.hi = k;
     p.weight = weight_dev;
     p.normed = normed_dev;
     p.normed_stride = normed_stride;
@@ -602,16 +616,18 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, ui
     return 0;
 }
 
-int32_t neura_cuda_argmax(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint32_t width,
-                          uint64_t stride, uint32_t *out_dev) {
+int32_t neura_cuda_argmax_segments(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint32_t width,
+                                   uint64_t stride, uint32_t segment, uint64_t segment_stride, uint32_t *out_dev) {
     if (!ctx || !x_dev || !out_dev || !rows || !width) return refuse(kBadArgument, "argmax needs a context, rows and an output");
-    if (stride < width) return refuse(kBadArgument, "rows of %u numbers overlap at stride %llu", width, (unsigned long long)stride);
+    if (!segment || width % segment) return refuse(kBadArgument, "rows of %u numbers do not split in segments of %u", width, segment);
     const uint32_t slices = width >= 8192 ? 64 : 1;
     int32_t rc;
     if ((rc = ensure(ctx, ctx->argmax_scratch, (uint64_t)rows * slices * 8 + (uint64_t)rows * 4 + 256, true))) return rc;
     ArgmaxParams p;
     p.x = x_dev;
     p.stride = stride;
+    p.segment = segment;
+    p.segment_stride = segment_stride;
     p.width = width;
     p.slices = slices;
     p.out = out_dev;
@@ -621,6 +637,12 @@ int32_t neura_cuda_argmax(nc_context *ctx, void *stream_, const float *x_dev, ui
     NC_CUDA(launch_dependent(argmax_kernel, dim3(rows * slices), dim3(256), 0, (cudaStream_t)stream_, p));
     ctx->launches++;
     return 0;
+}
+
+int32_t neura_cuda_argmax(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint32_t width,
+                          uint64_t stride, uint32_t *out_dev) {
+    if (stride < width) return refuse(kBadArgument, "rows of %u numbers overlap at stride %llu", width, (unsigned long long)stride);
+    return neura_cuda_argmax_segments(ctx, stream_, x_dev, rows, width, stride, width, 0, out_dev);
 }
 
 int32_t neura_cuda_embed(nc_context *ctx, void *stream_, const nc_weight *table, const uint32_t *tokens_dev,
@@ -739,6 +761,8 @@ int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight
     prep.ncols = ncols;
     prep.granule = q4k ? 256 : 32;
     prep.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0) ? 1u : 0u;
+    prep.lo = 0;
+    prep.hi = w->k;
     const uint64_t prep_warps = (uint64_t)rows * (kpad / 256);
     prep_kernel<<<(unsigned int)((prep_warps + 3) / 4), 128, 0, stream>>>(prep);
     ctx->launches++;

@@ -32,6 +32,7 @@ struct PrepParams {
     uint32_t rows, k, ncols;
     uint32_t granule;   // 256 or 32
     uint32_t vector;    // 1: rows start 16-byte aligned, so a lane may fetch float4
+    uint32_t lo, hi;    // the activations are elements [lo, hi) of K (multiples of 32); the rest of K reads as zero
 };
 
 // Digitises one 256-element chunk of row `row` held by a warp: lane l owns v[0..8) =
@@ -125,8 +126,8 @@ __device__ __forceinline__ void stage_chunk(const PrepParams &p, uint32_t row, u
 
 // Fetches a lane's eight numbers of a chunk.
 __device__ __forceinline__ void load_chunk(const PrepParams &p, uint32_t row, uint32_t at, bool live, float (&v)[8]) {
-    if (live) {
-        const float *from = p.x + (uint64_t)row * p.x_stride + at;
+    if (live && at >= p.lo && at < p.hi) {
+        const float *from = p.x + (uint64_t)row * p.x_stride + (at - p.lo);
         if (p.vector) {
             const float4 a = *reinterpret_cast<const float4 *>(from);
             const float4 b = *reinterpret_cast<const float4 *>(from + 4);

@@ -1,0 +1,194 @@
+"""Tensor-parallel sharding of the decoder's projections over the GPUs of one box.
+
+The reference runs on one device; this split has no counterpart there and is checked against
+the single-device result.  Column-parallel projections (q/k/v, gate, up, the head) split their
+rows (output features): a rank's share is a contiguous run of GGUF rows, so no block is cut.
+Row-parallel projections (attention output, down) split K; a rank keeps the whole Q4_K
+super-blocks (or Q8_0 blocks) that cover its K range, stages its activations at their offset
+inside them (the rest of K staged as zero, ``Runtime.stage_window``) and the ranks' partial
+products are summed by one all-reduce per projection.  The weights are quantised as whole
+rows first, so every rank dequantises exactly the values the single-device model does.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Tuple
+
+import numpy as np
+
+from .qwen import Config
+from .runtime import Q4K, Q8_0, payload_bytes
+
+_BLOCK = {Q8_0: (32, 34), Q4K: (256, 144)}
+
+
+@dataclass(frozen=True)
+class Window:
+    """A rank's share of a K axis: elements [lo, hi) of the padded local axis of ``k`` columns,
+    which are blocks [first_block, first_block + k / block) of the full axis."""
+    k: int
+    lo: int
+    hi: int
+    first_block: int
+
+
+@dataclass(frozen=True)
+class Shard:
+    config: Config
+    world: int
+    rank: int
+
+    def __post_init__(self):
+        c, w = self.config, self.world
+        if c.heads % w or c.key_heads % w or c.feed_forward % w or c.vocab % w:
+            raise ValueError(f"{c.name} does not split evenly over {w} ranks "
+                             f"({c.heads}/{c.key_heads} heads, ff {c.feed_forward}, vocab {c.vocab})")
+        for width in (c.feed_forward // w, c.vocab // w, c.key_width // w):
+            if width % 32:
+                raise ValueError(f"a share of {width} rows does not fill tiles of 32")
+        if (c.query_width // w) % 32 or (c.feed_forward // w) % 32:
+            raise ValueError("a share of a K axis starts on a multiple of 32")
+
+    # -- shapes of the local model ---------------------------------------------------
+    @property
+    def heads(self) -> int:
+        return self.config.heads // self.world
+
+    @property
+    def key_heads(self) -> int:
+        return self.config.key_heads // self.world
+
+    @property
+    def query_width(self) -> int:
+        return self.heads * self.config.head_width
+
+    @property
+    def key_width(self) -> int:
+        return self.key_heads * self.config.head_width
+
+    @property
+    def feed_forward(self) -> int:
+        return self.config.feed_forward // self.world
+
+    @property
+    def vocab(self) -> int:
+        return self.config.vocab // self.world
+
+    def rows(self, n: int) -> Tuple[int, int]:
+        """The run of rows [n0, n1) of a column-parallel projection of ``n`` rows."""
+        share = n // self.world
+        return self.rank * share, (self.rank + 1) * share
+
+    def window(self, k: int) -> Window:
+        """The share of a row-parallel projection's K axis of ``k`` columns."""
+        per = _BLOCK[self.config.element][0]
+        share = k // self.world
+        k0, k1 = self.rank * share, (self.rank + 1) * share
+        b0, b1 = k0 // per, (k1 + per - 1) // per
+        return Window((b1 - b0) * per, k0 - b0 * per, k1 - b0 * per, b0)
+
+    # -- slicing GGUF tensors ------------------------------------------------------------
+    def slice_rows(self, packed: np.ndarray, n: int, k: int, share_of: int = None) -> np.ndarray:
+        """Rows [n0, n1) of a GGUF [n, k] tensor (a contiguous run of its bytes)."""
+        n0, n1 = self.rows(n)
+        row = payload_bytes(self.config.element, k)
+        return np.ascontiguousarray(packed, dtype=np.uint8)[n0 * row: n1 * row]
+
+    def slice_columns(self, packed: np.ndarray, n: int, k: int) -> np.ndarray:
+        """The whole blocks that cover this rank's share of K, for every row of a GGUF [n, k] tensor."""
+        per, size = _BLOCK[self.config.element]
+        window = self.window(k)
+        blocks = np.ascontiguousarray(packed, dtype=np.uint8)[: n * (k // per) * size].reshape(n, k // per, size)
+        return np.ascontiguousarray(blocks[:, window.first_block: window.first_block + window.k // per]).reshape(-1)
+
+    def local_bytes_per_token(self) -> int:
+        """GGUF bytes this rank streams per decoded token (projections and its share of the head)."""
+        c = self.config
+        e = c.element
+        per_layer = (payload_bytes(e, (self.query_width + 2 * self.key_width) * c.hidden)
+                     + payload_bytes(e, c.hidden * self.window(c.query_width).k)
+                     + 2 * payload_bytes(e, self.feed_forward * c.hidden)
+                     + payload_bytes(e, c.hidden * self.window(c.feed_forward).k))
+        return c.layers * per_layer + payload_bytes(e, self.vocab * c.hidden)
+
+
+class TorchComm:
+    """The two exchanges of a tensor-parallel decode step over torch.distributed (NCCL on the
+    GPUs, gloo in the CPU tests), enqueued on the runtime's stream."""
+
+    def __init__(self, world: int, rank: int, device=None, stream=None):
+        import torch
+        import torch.distributed as dist
+
+        self.torch, self.dist = torch, dist
+        self.world, self.rank, self.device, self.stream = world, rank, device, stream
+        self.views: Dict[int, object] = {}
+
+    def view(self, ptr: int, count: int):
+        """A torch view of ``count`` f32 at a device pointer this process owns."""
+        key = (ptr, count)
+        if key not in self.views:
+            torch = self.torch
+
+            class _Span:
+                __cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3}
+
+            self.views[key] = torch.as_tensor(_Span(), device=self.device)
+        return self.views[key]
+
+    def all_reduce(self, ptr: int, count: int) -> None:
+        tensor = self.view(ptr, count)
+        with self.torch.cuda.stream(self.stream):
+            self.dist.all_reduce(tensor)
+
+    def all_gather(self, dst_ptr: int, src_ptr: int, count: int) -> None:
+        """dst [world][count] <- every rank's src [count]."""
+        dst, src = self.view(dst_ptr, count * self.world), self.view(src_ptr, count)
+        with self.torch.cuda.stream(self.stream):
+            self.dist.all_gather_into_tensor(dst, src)
+
+
+def load_decoder_weights(rt, config: Config, packed: Dict[str, np.ndarray], norms: Dict[str, np.ndarray],
+                         shard: Shard = None):
+    """Runtime::load for a whole decoder: pours the GGUF tensors of ``packed`` (named as a Qwen GGUF
+    names them: token_embd.weight, output.weight, blk.N.attn_q/k/v/output.weight, blk.N.ffn_gate/up/
+    down.weight) into sealed device weights, the rank's shares only when ``shard`` is given.
+    Returns (weights, norms) as ``qwen.Decoder`` takes them."""
+    c = config
+    e = c.element
+    weights, device_norms = {}, {}
+
+    def rows_of(name: str, n: int, k: int):
+        data = packed[name]
+        if shard is None:
+            return n, data
+        return n // shard.world, shard.slice_rows(data, n, k)
+
+    def columns_of(name: str, n: int, k: int):
+        data = packed[name]
+        if shard is None:
+            return k, data
+        return shard.window(k).k, shard.slice_columns(data, n, k)
+
+    for layer in range(c.layers):
+        name = lambda part: f"blk.{layer}.{part}.weight"  # noqa: E731
+        parts = [rows_of(name("attn_q"), c.query_width, c.hidden), rows_of(name("attn_k"), c.key_width, c.hidden),
+                 rows_of(name("attn_v"), c.key_width, c.hidden)]
+        weights[name("attn_qkv")] = rt.load_stacked(e, c.hidden, parts)
+        k, data = columns_of(name("attn_output"), c.hidden, c.query_width)
+        weights[name("attn_output")] = rt.load(e, c.hidden, k, data)
+        for part in ("ffn_gate", "ffn_up"):
+            n, data = rows_of(name(part), c.feed_forward, c.hidden)
+            weights[name(part)] = rt.load(e, n, c.hidden, data)
+        k, data = columns_of(name("ffn_down"), c.hidden, c.feed_forward)
+        weights[name("ffn_down")] = rt.load(e, c.hidden, k, data)
+    n, data = rows_of("output.weight", c.vocab, c.hidden)
+    weights["output.weight"] = rt.load(e, n, c.hidden, data)
+    if c.tied_head and shard is None:
+        weights["token_embd.weight"] = weights["output.weight"]
+    else:  # every rank gathers from the whole table, kept in GGUF order
+        weights["token_embd.weight"] = rt.load(e, c.vocab, c.hidden, packed["token_embd.weight"], seal=False)
+    for key, value in norms.items():
+        device_norms[key] = rt.tensor(value.size)
+        rt.write(device_norms[key], value)
+    return weights, device_norms

@@ -142,26 +142,57 @@ class Decoder:
     """
 
     def __init__(self, rt: Runtime, config: Config, weights: Dict[str, Weight], norms: Dict[str, DeviceTensor],
-                 batch: int = 1, capacity: int = 640):
+                 batch: int = 1, capacity: int = 640, shard=None, comm=None):
+        """``shard`` (parallel.Shard) and ``comm`` (parallel.TorchComm) make this one rank of a
+        tensor-parallel group: ``weights`` then hold the rank's shares (q/k/v, gate, up and head
+        rows; the K blocks of attention output and down that cover its window)."""
         if batch > 16:
             raise ValueError("one decode step carries at most 16 sequences")
+        if (shard is None) != (comm is None):
+            raise ValueError("a tensor-parallel rank needs both its shard and its communicator")
         self.rt, self.config, self.weights, self.norms = rt, config, weights, norms
-        self.batch, self.capacity = batch, capacity
+        self.batch, self.capacity, self.shard, self.comm = batch, capacity, shard, comm
         c = config
+        world = shard.world if shard else 1
+        self.heads, self.key_heads = c.heads // world, c.key_heads // world
+        self.query_width, self.key_width = self.heads * c.head_width, self.key_heads * c.head_width
+        self.feed_forward, self.vocab = c.feed_forward // world, c.vocab // world
         self.tokens = rt.tensor_u32(batch)
         self.position = rt.tensor_u32(batch)
         self.hidden = rt.tensor(batch, c.hidden)
-        self.qkv = rt.tensor(batch, c.query_width + 2 * c.key_width)
-        self.attended = rt.tensor(batch, c.query_width)
-        self.gate = rt.tensor(batch, c.feed_forward)
-        self.held = rt.tensor(batch, c.feed_forward)
-        self.logits = rt.tensor(batch, c.vocab)
-        cache = batch * c.key_heads * capacity * c.head_width
+        self.qkv = rt.tensor(batch, self.query_width + 2 * self.key_width)
+        self.attended = rt.tensor(batch, self.query_width)
+        self.gate = rt.tensor(batch, self.feed_forward)
+        self.held = rt.tensor(batch, self.feed_forward)
+        self.logits = rt.tensor(batch, self.vocab)
+        self.gathered = rt.tensor(world, batch, self.vocab) if shard else None
+        cache = batch * self.key_heads * capacity * c.head_width
         self.keys = [rt.tensor(cache) for _ in range(c.layers)]
         self.values = [rt.tensor(cache) for _ in range(c.layers)]
-        rt.reserve(batch, max(c.vocab, c.feed_forward), max(c.hidden, c.feed_forward, c.query_width))
+        widest_k = max(c.hidden, self.window(c.feed_forward)[0], self.window(c.query_width)[0])
+        rt.reserve(batch, max(self.vocab, self.feed_forward, c.hidden), widest_k)
         self.program: Optional[int] = None
         self.scale = 1.0 / float(c.head_width) ** 0.5
+
+    def window(self, k: int):
+        """(local K, lo, hi) of a row-parallel projection over a K axis of ``k``."""
+        if self.shard is None:
+            return k, 0, k
+        w = self.shard.window(k)
+        return w.k, w.lo, w.hi
+
+    def _row_parallel(self, x: DeviceTensor, weight: Weight, k: int) -> None:
+        """hidden += W x over this rank's share of K, summed over the ranks."""
+        rt, c = self.rt, self.config
+        local, lo, hi = self.window(k)
+        if self.shard is None:
+            rt.stage(x, c.element)
+            rt.linear_staged(weight, self.hidden, [Step(ADD, self.hidden)])
+            return
+        rt.stage_window(x, c.element, local, lo, hi)
+        # rank 0 carries the residual, so the sum over the ranks is hidden + W x on every rank
+        rt.linear_staged(weight, self.hidden, [Step(ADD, self.hidden)] if self.shard.rank == 0 else None)
+        self.comm.all_reduce(self.hidden.ptr, self.batch * c.hidden)
 
     def step(self) -> None:
         rt, c, w, n = self.rt, self.config, self.weights, self.norms
@@ -170,20 +201,23 @@ class Decoder:
             at = lambda name: f"blk.{layer}.{name}.weight"  # noqa: E731
             rt.rms_norm_stage(self.hidden, n[at("attn_norm")], c.floor, c.element)
             rt.linear_staged(w[at("attn_qkv")], self.qkv)
-            rt.rope_cache(self.qkv, self.position, c.rope_base, c.heads, c.key_heads, c.head_width, self.capacity,
-                          self.keys[layer], self.values[layer])
-            rt.attend(self.qkv, self.keys[layer], self.values[layer], self.position, self.scale, c.heads,
-                      c.key_heads, c.head_width, self.capacity, self.attended)
-            rt.stage(self.attended, c.element)
-            rt.linear_staged(w[at("attn_output")], self.hidden, [Step(ADD, self.hidden)])
+            rt.rope_cache(self.qkv, self.position, c.rope_base, self.heads, self.key_heads, c.head_width,
+                          self.capacity, self.keys[layer], self.values[layer])
+            rt.attend(self.qkv, self.keys[layer], self.values[layer], self.position, self.scale, self.heads,
+                      self.key_heads, c.head_width, self.capacity, self.attended)
+            self._row_parallel(self.attended, w[at("attn_output")], c.query_width)
             rt.rms_norm_stage(self.hidden, n[at("ffn_norm")], c.floor, c.element)
             rt.linear_staged(w[at("ffn_gate")], self.gate, [Step(SILU)])
             rt.linear_staged(w[at("ffn_up")], self.held, [Step(MUL, self.gate)])
-            rt.stage(self.held, c.element)
-            rt.linear_staged(w[at("ffn_down")], self.hidden, [Step(ADD, self.hidden)])
+            self._row_parallel(self.held, w[at("ffn_down")], c.feed_forward)
         rt.rms_norm_stage(self.hidden, n["output_norm.weight"], c.floor, c.element)
         rt.linear_staged(w["output.weight"], self.logits)
-        rt.argmax(self.logits, self.tokens)
+        if self.shard is None:
+            rt.argmax(self.logits, self.tokens)
+        else:
+            self.comm.all_gather(self.gathered.ptr, self.logits.ptr, self.batch * self.vocab)
+            rt.argmax_segments(self.gathered.ptr, self.batch, c.vocab, self.vocab, self.vocab,
+                               self.batch * self.vocab, self.tokens)
         rt.advance(self.position, 1)
 
     def launches_per_token(self) -> int:

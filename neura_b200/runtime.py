@@ -276,6 +276,12 @@ class Runtime:
         k = k if k is not None else x.shape[-1]
         _check(self._lib.neura_cuda_stage(self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1], k, element))
 
+    def stage_window(self, x: DeviceTensor, element: int, k: int, lo: int, hi: int, rows: Optional[int] = None) -> None:
+        """``stage`` for a row-parallel shard: ``x`` holds elements [lo, hi) of a K axis of ``k``."""
+        rows = rows if rows is not None else x.rows
+        _check(self._lib.neura_cuda_stage_window(self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1], k,
+                                                 element, lo, hi))
+
     def linear_staged(self, weight: Weight, out: DeviceTensor, chain: Optional[Sequence[Step]] = None,
                       out_ptr: Optional[int] = None, out_stride: Optional[int] = None) -> None:
         """Second half of ``linear``: the staged rows times ``weight``."""
@@ -324,6 +330,12 @@ class Runtime:
         rows = rows if rows is not None else x.rows
         _check(self._lib.neura_cuda_argmax(self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1],
                                            x.shape[-1], ctypes.c_void_p(out.ptr)))
+
+    def argmax_segments(self, x_ptr: int, rows: int, width: int, stride: int, segment: int, segment_stride: int,
+                        out: DeviceTensor) -> None:
+        """argmax over rows gathered in segments from the ranks of a tensor-parallel group."""
+        _check(self._lib.neura_cuda_argmax_segments(self._ctx, self.stream, ctypes.c_void_p(x_ptr), rows, width, stride,
+                                                    segment, segment_stride, ctypes.c_void_p(out.ptr)))
 
     def embed(self, table: Weight, tokens: DeviceTensor, out: DeviceTensor, rows: Optional[int] = None) -> None:
         rows = rows if rows is not None else out.rows

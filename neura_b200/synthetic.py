@@ -10,7 +10,9 @@ from .runtime import Runtime, Weight, payload_bytes
 
 
 def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: float = 0.02,
-                      fuse_qkv: bool = True, with_embedding: bool = True) -> Dict[str, Weight]:
+                      fuse_qkv: bool = True, with_embedding: bool = True, shard=None) -> Dict[str, Weight]:
+    """``shard`` (parallel.Shard): make only that rank's shares, in the shapes a sharded load gives
+    (the values are fresh random numbers, not slices of one model: the benchmark needs the bytes)."""
     import torch
 
     device = torch.device("cuda", rt.device)
@@ -18,6 +20,16 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
     gen.manual_seed(seed)
     stream = torch.cuda.ExternalStream(rt.stream.value, device=device) if rt.stream.value else torch.cuda.current_stream(device)
     shapes = config.linears()
+    vocab = config.vocab
+    if shard is not None:
+        qw, kw = shard.query_width, shard.key_width
+        shapes = [("attn_q", qw, config.hidden), ("attn_k", kw, config.hidden), ("attn_v", kw, config.hidden),
+                  ("attn_output", config.hidden, shard.window(config.query_width).k),
+                  ("ffn_gate", shard.feed_forward, config.hidden), ("ffn_up", shard.feed_forward, config.hidden),
+                  ("ffn_down", config.hidden, shard.window(config.feed_forward).k)]
+        vocab = shard.vocab
+    else:
+        qw, kw = config.query_width, config.key_width
     biggest = max(max(n * k for _, n, k in shapes), 16 * 1024 * config.hidden)
     numbers = torch.empty(biggest, dtype=torch.float32, device=device)
     blocks = torch.empty(payload_bytes(config.element, biggest) + 16, dtype=torch.uint8, device=device)
@@ -35,7 +47,7 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
             if fuse_qkv and name in ("attn_k", "attn_v"):
                 continue
             if fuse_qkv and name == "attn_q":
-                parts = [config.query_width, config.key_width, config.key_width]
+                parts = [qw, kw, kw]
                 assert all(p % 32 == 0 for p in parts)
                 total = sum(parts)
                 base = rt.alloc(rt.sealed_bytes(config.element, total, k))
@@ -48,7 +60,7 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
             weights[f"blk.{layer}.{name}.weight"] = make(n, k)
     # the head in slabs of rows so that the scratch stays small
     k = config.hidden
-    total = config.vocab
+    total = vocab
     base = rt.alloc(rt.sealed_bytes(config.element, total, k))
     at, done = base, 0
     while done < total:
@@ -58,9 +70,10 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
         done += rows
     weights["output.weight"] = Weight(base, config.element, 1, total, k, at - base)
     if with_embedding:
-        if config.tied_head:
+        if config.tied_head and shard is None:
             weights["token_embd.weight"] = weights["output.weight"]
         else:  # a table of its own, kept in GGUF order (only rows are gathered from it)
+            total = config.vocab
             row_bytes = payload_bytes(config.element, k)
             table = rt.alloc(row_bytes * total)
             done = 0

@@ -104,24 +104,9 @@ def test_argmax_takes_the_lowest_index_on_ties(runtime, oracle):
 
 
 def load_model(rt, config, packed, norms):
-    weights, dnorms = {}, {}
-    c = config
-    for layer in range(c.layers):
-        name = lambda part: f"blk.{layer}.{part}.weight"  # noqa: E731
-        weights[name("attn_qkv")] = rt.load_stacked(c.element, c.hidden, [
-            (c.query_width, packed[name("attn_q")]), (c.key_width, packed[name("attn_k")]),
-            (c.key_width, packed[name("attn_v")])])
-        for part, n, k in c.linears()[3:]:
-            weights[name(part)] = rt.load(c.element, n, k, packed[name(part)])
-    weights["output.weight"] = rt.load(c.element, c.vocab, c.hidden, packed["output.weight"])
-    if c.tied_head:
-        weights["token_embd.weight"] = weights["output.weight"]
-    else:
-        weights["token_embd.weight"] = rt.load(c.element, c.vocab, c.hidden, packed["token_embd.weight"], seal=False)
-    for key, value in norms.items():
-        dnorms[key] = rt.tensor(value.size)
-        rt.write(dnorms[key], value)
-    return weights, dnorms
+    from neura_b200.parallel import load_decoder_weights
+
+    return load_decoder_weights(rt, config, packed, norms)
 
 
 SMALL = {
