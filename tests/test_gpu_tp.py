@@ -1,0 +1,27 @@
+"""Tensor-parallel decoding on the GPUs of this box (skipped with fewer than two)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def gpus() -> int:
+    import torch
+
+    return torch.cuda.device_count()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_a_split_model_decodes_the_oracles_tokens(world):
+    if gpus() < world:
+        pytest.skip(f"{world} GPUs are not here")
+    env = dict(os.environ, TP_CHECK_LIMIT="150", NCCL_NVLS_ENABLE="0")
+    run = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+         "127.0.0.1", "--master-port", str(29540 + world), os.path.join(ROOT, "tests", "tp_decode_check.py")],
+        capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert run.returncode == 0 and f"tp{world}: 64 greedy tokens" in run.stdout, run.stdout[-2000:] + run.stderr[-2000:]
