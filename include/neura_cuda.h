@@ -35,7 +35,8 @@ extern "C" {
 
 /* How the blocks of a weight tensor are laid out in device memory. */
 #define NC_LAYOUT_GGUF 0u   /* verbatim GGUF: row after row, blocks in order (what store.rs:131-135 copies) */
-#define NC_LAYOUT_TILED 1u  /* neura_cuda_weight_seal output: same bytes, permuted per 16-row tile for the MMA kernels */
+#define NC_LAYOUT_TILED 1u  /* neura_cuda_weight_seal output: same bytes, permuted per 32-row tile for the MMA kernels */
+#define NC_LAYOUT_TILED_PAIR 2u /* neura_cuda_weight_seal_pair output: two [n, k] tensors, 16 rows of each per tile */
 
 /* Pointwise op codes of the fused epilogue: neura-pointwise declaration order
  * (crates/neura-pointwise/src/op.rs:141-170). */
@@ -123,6 +124,15 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
  * neura_cuda_sealed_bytes().  Dequantised values are unchanged bit for bit. */
 int32_t neura_cuda_weight_seal(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k,
                                const void *gguf_dev, void *dst_dev);
+
+/* The gate and up projections of an MLP sealed as one weight (examples/qwen/mlp.rs:31-33:
+ * `mul(silu(matmul(x, gate)), matmul(x, up))`).  A product with the result (layout
+ * NC_LAYOUT_TILED_PAIR, n = rows of each tensor) writes out[c] = chain(silu(gate_c . x) * (up_c . x)):
+ * both tensors are streamed once by one kernel and the SwiGLU costs no pass of its own.
+ * `dst_dev` holds neura_cuda_sealed_pair_bytes(). */
+uint64_t neura_cuda_sealed_pair_bytes(uint32_t element, uint32_t n, uint32_t k);
+int32_t neura_cuda_weight_seal_pair(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k,
+                                    const void *gate_gguf_dev, const void *up_gguf_dev, void *dst_dev);
 
 /* unpack (crates/neura-precision/src/ggml.rs:22-38, q8_0_values :211-216,
  * q4_k_values :336-350): out_dev[n*k] f32, bit-exact, for either layout. */

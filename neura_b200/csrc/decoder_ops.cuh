@@ -95,8 +95,9 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(16) float shared[];
     const uint32_t group = p.heads / p.key_heads;
-    float *ks = shared;                                  // [kAttendTile][WIDTH]
-    float *vs = ks + kAttendTile * WIDTH;                // [kAttendTile][WIDTH]
+    constexpr uint32_t KROW = WIDTH + 4;                 // padded key row: float4 reads of 8 rows hit 32 banks
+    float *ks = shared;                                  // [kAttendTile][KROW]
+    float *vs = ks + kAttendTile * KROW;                 // [kAttendTile][WIDTH]
     float *qs = vs + kAttendTile * WIDTH;                // [group][WIDTH]
     float *logits = qs + kAttendMaxGroup * WIDTH;        // [group][kAttendMaxChunk]
     float *stats = logits + kAttendMaxGroup * kAttendMaxChunk;  // [group][2]: largest, sum
@@ -112,7 +113,8 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     const float *k = p.keys + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
     const float *v = p.values + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
     for (uint32_t i = threadIdx.x; i < held * (WIDTH / 4); i += blockDim.x) {
-        copy16_async(ks + i * 4, k + i * 4);
+        const uint32_t row = i / (WIDTH / 4), quad = i % (WIDTH / 4);
+        copy16_async(ks + row * KROW + quad * 4, k + i * 4);
         copy16_async(vs + i * 4, v + i * 4);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -120,27 +122,21 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
         qs[i] = p.q[(uint64_t)b * p.q_stride + (uint64_t)(kh * group) * WIDTH + i];
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    // logits of this split: one warp per position, lanes across the head width
-    constexpr uint32_t PER = WIDTH / 32;
-    float qr[kAttendMaxGroup][PER];
-#pragma unroll
-    for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
-#pragma unroll
-        for (uint32_t i = 0; i < PER; ++i) qr[g][i] = g < group ? qs[g * WIDTH + lane * PER + i] : 0.0f;
-    for (uint32_t pos = warp; pos < held; pos += warps) {
-        float kv[PER];
-#pragma unroll
-        for (uint32_t i = 0; i < PER; ++i) kv[i] = ks[pos * WIDTH + lane * PER + i];
-#pragma unroll
-        for (uint32_t g = 0; g < kAttendMaxGroup; ++g) {
-            if (g < group) {
-                float total = 0.0f;
-#pragma unroll
-                for (uint32_t i = 0; i < PER; ++i) total = fmaf(qr[g][i], kv[i], total);
-                for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-                if (lane == 0) logits[g * kAttendMaxChunk + pos] = total * p.scale;
-            }
+    // logits of this split: one thread per (query head, position), the whole dot product in registers
+    for (uint32_t item = threadIdx.x; item < group * held; item += blockDim.x) {
+        const uint32_t g = item / held, pos = item % held;
+        const float4 *kr = reinterpret_cast<const float4 *>(ks + pos * KROW);
+        const float4 *qr = reinterpret_cast<const float4 *>(qs + g * WIDTH);
+        float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f, t3 = 0.0f;
+#pragma unroll 8
+        for (uint32_t c = 0; c < WIDTH / 4; ++c) {
+            const float4 a = kr[c], q4 = qr[c];
+            t0 = fmaf(a.x, q4.x, t0);
+            t1 = fmaf(a.y, q4.y, t1);
+            t2 = fmaf(a.z, q4.z, t2);
+            t3 = fmaf(a.w, q4.w, t3);
         }
+        logits[g * kAttendMaxChunk + pos] = ((t0 + t1) + (t2 + t3)) * p.scale;
     }
     __syncthreads();
     // per query head: largest logit and sum of exponentials of the split (one warp per head)

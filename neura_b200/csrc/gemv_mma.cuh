@@ -44,6 +44,8 @@ struct GemvParams {
     uint32_t nwarps;      // warps that take work
     uint32_t q, r;        // every warp takes q units, the first r one more
     uint32_t maxp;        // slots per tile in `partial`
+    uint32_t pair;        // 1: a tile is 16 rows of one matrix over the same 16 rows of a second one, and
+                          //    output c is silu(first row c) * (second row c): the SwiGLU of a gate and an up projection
     Chain chain;
 };
 
@@ -147,7 +149,15 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
     __syncwarp();
     const uint32_t cells = p.rows * 32;
     const bool whole = first_blk == 0 && end_blk == p.upt;
-    if (whole) {
+    if (whole && p.pair) {
+        for (uint32_t idx = lane; idx < p.rows * 16; idx += 32) {
+            const uint32_t rr = idx & 15, b = idx >> 4, col = tile * 16 + rr, up = rr + 16;
+            const float gate = (patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2];
+            const float other = (patch[up * W + 3 * b] + patch[up * W + 3 * b + 1]) + patch[up * W + 3 * b + 2];
+            if (col < p.n)
+                p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, gate * sigmoid_f(gate) * other);
+        }
+    } else if (whole) {
         for (uint32_t idx = lane; idx < cells; idx += 32) {
             const uint32_t rr = idx & 31, b = idx >> 5, col = tile * 32 + rr;
             const float v = (patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2];
@@ -172,7 +182,20 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
             __threadfence();
         }
         seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (seen == count - 1) {
+        if (seen == count - 1 && p.pair) {
+            const float *all = p.partial + (uint64_t)tile * p.maxp * cells;
+            for (uint32_t idx = lane; idx < p.rows * 16; idx += 32) {
+                const uint32_t rr = idx & 15, b = idx >> 4, col = tile * 16 + rr;
+                float gate = 0.0f, other = 0.0f;
+                for (uint32_t s = 0; s < count; ++s) {
+                    gate += __ldcg(all + (uint64_t)s * cells + b * 32 + rr);
+                    other += __ldcg(all + (uint64_t)s * cells + b * 32 + rr + 16);
+                }
+                if (col < p.n)
+                    p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, gate * sigmoid_f(gate) * other);
+            }
+            if (lane == 0) p.counters[tile] = 0u;
+        } else if (seen == count - 1) {
             const float *all = p.partial + (uint64_t)tile * p.maxp * cells;
             for (uint32_t idx = lane; idx < cells; idx += 32) {
                 const uint32_t rr = idx & 31, b = idx >> 5, col = tile * 32 + rr;

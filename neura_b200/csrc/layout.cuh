@@ -81,7 +81,10 @@ __global__ void dequant_kernel(WeightView w, float *out) {
 }
 
 // GGUF -> tiled, Q4_K, one 8-byte granule per thread step.
-__global__ void seal_q4k_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, uint32_t nsb, uint64_t granules) {
+// With `second` not null the output pairs two matrices: half 0 of tile T holds rows [16T, 16T+16) of
+// `gguf`, half 1 the same rows of `second` (n counts the rows of each).
+__global__ void seal_q4k_kernel(const uint8_t *gguf, const uint8_t *second, uint8_t *dst, uint32_t n, uint32_t nsb,
+                                uint64_t granules) {
     for (uint64_t d = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; d < granules;
          d += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t unit = d / 576;
@@ -96,15 +99,17 @@ __global__ void seal_q4k_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, u
             rr = lane / 4 + 8 * hi;
             o = 16 + 32 * G + 8 * (lane % 4);
         }
-        const uint32_t row = tile * 32 + half * 16 + rr;
+        const uint32_t row = second ? tile * 16 + rr : tile * 32 + half * 16 + rr;
+        const uint8_t *from = second && half ? second : gguf;
         uint2 v = make_uint2(0u, 0u);
-        if (row < n) v = *reinterpret_cast<const uint2 *>(gguf + ((uint64_t)row * nsb + sb) * kQ4kBytes + o);
+        if (row < n) v = *reinterpret_cast<const uint2 *>(from + ((uint64_t)row * nsb + sb) * kQ4kBytes + o);
         *reinterpret_cast<uint2 *>(dst + d * 8) = v;
     }
 }
 
 // GGUF -> tiled, Q8_0, one 2-byte granule per thread step (34-byte blocks are only 2-byte aligned).
-__global__ void seal_q8_0_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, uint32_t nblk, uint64_t granules) {
+__global__ void seal_q8_0_kernel(const uint8_t *gguf, const uint8_t *second, uint8_t *dst, uint32_t n, uint32_t nblk,
+                                 uint64_t granules) {
     for (uint64_t d = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; d < granules;
          d += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t unit = d / 544;
@@ -120,10 +125,11 @@ __global__ void seal_q8_0_kernel(const uint8_t *gguf, uint8_t *dst, uint32_t n, 
             rr = s / 2 + 8 * (s % 2);
             o = 0;
         }
-        const uint32_t row = tile * 32 + half * 16 + rr;
+        const uint32_t row = second ? tile * 16 + rr : tile * 32 + half * 16 + rr;
+        const uint8_t *from = second && half ? second : gguf;
         unsigned short v = 0;
         if (row < n)
-            v = *reinterpret_cast<const unsigned short *>(gguf + ((uint64_t)row * nblk + blk) * kQ8Bytes + o);
+            v = *reinterpret_cast<const unsigned short *>(from + ((uint64_t)row * nblk + blk) * kQ8Bytes + o);
         *reinterpret_cast<unsigned short *>(dst + d * 2) = v;
     }
 }

@@ -324,27 +324,46 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     return 0;
 }
 
-int32_t neura_cuda_weight_seal(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k,
-                               const void *gguf_dev, void *dst_dev) {
+static int32_t seal_any(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k, const void *gguf_dev,
+                        const void *second_dev, void *dst_dev) {
     if (!ctx || !gguf_dev || !dst_dev) return refuse(kBadArgument, "seal needs a context, a source and a destination");
     const uint32_t per = block_elements(element);
     if (!per || !n || !k || k % per)
         return refuse(kBadArgument, "a [%u, %u] tensor of element %u is not whole blocks this path seals", n, k, element);
-    if ((uintptr_t)gguf_dev % (element == NC_ELEMENT_Q4K ? 8 : 2) || (uintptr_t)dst_dev % 16)
+    const uintptr_t align = element == NC_ELEMENT_Q4K ? 8 : 2;
+    if ((uintptr_t)gguf_dev % align || (uintptr_t)second_dev % align || (uintptr_t)dst_dev % 16)
         return refuse(kBadArgument, "seal reads an 8-byte aligned tensor and writes a 16-byte aligned one");
-    const uint64_t bytes = neura_cuda_sealed_bytes(element, n, k);
+    const uint64_t bytes = second_dev ? neura_cuda_sealed_pair_bytes(element, n, k) : neura_cuda_sealed_bytes(element, n, k);
     const uint64_t granules = element == NC_ELEMENT_Q4K ? bytes / 8 : bytes / 2;
     const uint64_t want = (granules + 255) / 256;
     const unsigned int blocks = (unsigned int)(want < (uint64_t)ctx->sms * 32 ? want : (uint64_t)ctx->sms * 32);
     if (element == NC_ELEMENT_Q4K)
-        seal_q4k_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)gguf_dev, (uint8_t *)dst_dev, n,
-                                                                  k / per, granules);
+        seal_q4k_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)gguf_dev, (const uint8_t *)second_dev,
+                                                                  (uint8_t *)dst_dev, n, k / per, granules);
     else
-        seal_q8_0_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)gguf_dev, (uint8_t *)dst_dev, n,
-                                                                   k / per, granules);
+        seal_q8_0_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)gguf_dev, (const uint8_t *)second_dev,
+                                                                   (uint8_t *)dst_dev, n, k / per, granules);
     ctx->launches++;
     NC_CUDA(cudaGetLastError());
     return 0;
+}
+
+uint64_t neura_cuda_sealed_pair_bytes(uint32_t element, uint32_t n, uint32_t k) {
+    const uint32_t per = block_elements(element);
+    if (!per || k % per) return 0;
+    const uint64_t tiles = ((uint64_t)n + 15) / 16;
+    return tiles * 32 * (k / per) * block_bytes(element);
+}
+
+int32_t neura_cuda_weight_seal(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k,
+                               const void *gguf_dev, void *dst_dev) {
+    return seal_any(ctx, stream, element, n, k, gguf_dev, nullptr, dst_dev);
+}
+
+int32_t neura_cuda_weight_seal_pair(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k,
+                                    const void *gate_gguf_dev, const void *up_gguf_dev, void *dst_dev) {
+    if (!up_gguf_dev) return refuse(kBadArgument, "a pair seals two tensors");
+    return seal_any(ctx, stream, element, n, k, gate_gguf_dev, up_gguf_dev, dst_dev);
 }
 
 int32_t neura_cuda_dequant(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev) {
@@ -352,7 +371,7 @@ int32_t neura_cuda_dequant(nc_context *ctx, void *stream, const nc_weight *w, fl
     int32_t rc;
     if ((rc = check_weight(w))) return rc;
     if (w->layout != NC_LAYOUT_GGUF && w->layout != NC_LAYOUT_TILED)
-        return refuse(kBadArgument, "layout %u is neither the GGUF nor the tiled order", w->layout);
+        return refuse(kBadArgument, "layout %u is neither the GGUF nor the tiled order (a sealed pair is dequantised from its two sources)", w->layout);
     WeightView view{(const uint8_t *)w->data_dev, w->element, w->layout, w->n, w->k};
     const uint64_t total = (uint64_t)w->n * w->k;
     const uint64_t want = (total + 255) / 256;
@@ -438,8 +457,11 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     if (!ctx || !out_dev) return refuse(kBadArgument, "a product needs a context and an output");
     int32_t rc;
     if ((rc = check_weight(w))) return rc;
-    if (w->layout != NC_LAYOUT_TILED)
+    if (w->layout != NC_LAYOUT_TILED && w->layout != NC_LAYOUT_TILED_PAIR)
         return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order");
+    const bool pair = w->layout == NC_LAYOUT_TILED_PAIR;
+    // a pair is planned as the matrix of both tensors' rows, 16 of each per 32-row tile
+    const uint32_t plan_n = pair ? (w->n + 15) / 16 * 32 : w->n;
     const uint32_t granule = w->element == NC_ELEMENT_Q4K ? 256 : 32;
     if (!ctx->staged_rows || ctx->staged_k != w->k || ctx->staged_granule != granule)
         return refuse(kBadArgument, "the staged activations (%u rows of %u for blocks of %u) do not fit a [%u, %u] weight of element %u",
@@ -460,16 +482,17 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     p.n = w->n;
     p.rows = ctx->staged_rows;
     p.ncols = ctx->staged_rows * 3;
+    p.pair = pair ? 1u : 0u;
     p.chain.n = n_steps;
     for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
     cudaStream_t stream = (cudaStream_t)stream_;
     switch ((p.ncols + 7) / 8) {
-    case 1: return launch_gemv<1>(ctx, stream, w->element, p, w->n, w->k);
-    case 2: return launch_gemv<2>(ctx, stream, w->element, p, w->n, w->k);
-    case 3: return launch_gemv<3>(ctx, stream, w->element, p, w->n, w->k);
-    case 4: return launch_gemv<4>(ctx, stream, w->element, p, w->n, w->k);
-    case 5: return launch_gemv<5>(ctx, stream, w->element, p, w->n, w->k);
-    default: return launch_gemv<6>(ctx, stream, w->element, p, w->n, w->k);
+    case 1: return launch_gemv<1>(ctx, stream, w->element, p, plan_n, w->k);
+    case 2: return launch_gemv<2>(ctx, stream, w->element, p, plan_n, w->k);
+    case 3: return launch_gemv<3>(ctx, stream, w->element, p, plan_n, w->k);
+    case 4: return launch_gemv<4>(ctx, stream, w->element, p, plan_n, w->k);
+    case 5: return launch_gemv<5>(ctx, stream, w->element, p, plan_n, w->k);
+    default: return launch_gemv<6>(ctx, stream, w->element, p, plan_n, w->k);
     }
 }
 
@@ -597,7 +620,7 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, ui
         return refuse(kBadArgument, "a cache of %u slots is more than the %u the attention kernel splits", capacity,
                       64 * kAttendTile);
     const uint32_t splits = (capacity + kAttendTile - 1) / kAttendTile;  // <= 64, and <= kAttendTile positions per CTA
-    const size_t smem = ((size_t)2 * kAttendTile * width + (size_t)kAttendMaxGroup * width +
+    const size_t smem = ((size_t)kAttendTile * (2 * width + 4) + (size_t)kAttendMaxGroup * width +
                          (size_t)kAttendMaxGroup * kAttendMaxChunk + (size_t)kAttendMaxGroup * 2) * sizeof(float);
     auto kernel = width == 128 ? attend_kernel<128> : attend_kernel<64>;
     static bool raised[64][2] = {{false}};

@@ -149,7 +149,7 @@ class TorchComm:
 
 
 def load_decoder_weights(rt, config: Config, packed: Dict[str, np.ndarray], norms: Dict[str, np.ndarray],
-                         shard: Shard = None):
+                         shard: Shard = None, pair_mlp: bool = True):
     """Runtime::load for a whole decoder: pours the GGUF tensors of ``packed`` (named as a Qwen GGUF
     names them: token_embd.weight, output.weight, blk.N.attn_q/k/v/output.weight, blk.N.ffn_gate/up/
     down.weight) into sealed device weights, the rank's shares only when ``shard`` is given.
@@ -177,9 +177,13 @@ def load_decoder_weights(rt, config: Config, packed: Dict[str, np.ndarray], norm
         weights[name("attn_qkv")] = rt.load_stacked(e, c.hidden, parts)
         k, data = columns_of(name("attn_output"), c.hidden, c.query_width)
         weights[name("attn_output")] = rt.load(e, c.hidden, k, data)
-        for part in ("ffn_gate", "ffn_up"):
-            n, data = rows_of(name(part), c.feed_forward, c.hidden)
-            weights[name(part)] = rt.load(e, n, c.hidden, data)
+        n, gate = rows_of(name("ffn_gate"), c.feed_forward, c.hidden)
+        n, up = rows_of(name("ffn_up"), c.feed_forward, c.hidden)
+        if pair_mlp:
+            weights[name("ffn_gate_up")] = rt.load_pair(e, n, c.hidden, gate, up)
+        else:
+            weights[name("ffn_gate")] = rt.load(e, n, c.hidden, gate)
+            weights[name("ffn_up")] = rt.load(e, n, c.hidden, up)
         k, data = columns_of(name("ffn_down"), c.hidden, c.feed_forward)
         weights[name("ffn_down")] = rt.load(e, c.hidden, k, data)
     n, data = rows_of("output.weight", c.vocab, c.hidden)

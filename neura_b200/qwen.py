@@ -207,8 +207,11 @@ class Decoder:
                       self.key_heads, c.head_width, self.capacity, self.attended)
             self._row_parallel(self.attended, w[at("attn_output")], c.query_width)
             rt.rms_norm_stage(self.hidden, n[at("ffn_norm")], c.floor, c.element)
-            rt.linear_staged(w[at("ffn_gate")], self.gate, [Step(SILU)])
-            rt.linear_staged(w[at("ffn_up")], self.held, [Step(MUL, self.gate)])
+            if at("ffn_gate_up") in w:   # gate and up sealed as a pair: one product, SwiGLU in its epilogue
+                rt.linear_staged(w[at("ffn_gate_up")], self.held)
+            else:
+                rt.linear_staged(w[at("ffn_gate")], self.gate, [Step(SILU)])
+                rt.linear_staged(w[at("ffn_up")], self.held, [Step(MUL, self.gate)])
             self._row_parallel(self.held, w[at("ffn_down")], c.feed_forward)
         rt.rms_norm_stage(self.hidden, n["output_norm.weight"], c.floor, c.element)
         rt.linear_staged(w["output.weight"], self.logits)
@@ -221,7 +224,8 @@ class Decoder:
         rt.advance(self.position, 1)
 
     def launches_per_token(self) -> int:
-        return self.config.layers * 11 + 5
+        paired = "blk.0.ffn_gate_up.weight" in self.weights
+        return self.config.layers * (10 if paired else 11) + 5
 
     def record(self) -> int:
         self.rt.capture_begin()

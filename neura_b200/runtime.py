@@ -21,7 +21,7 @@ from . import _lib
 from ._lib import NcStep, NcWeight
 
 SINGLE, BFLOAT16, Q8_0, Q4K = 0, 2, 8, 9
-LAYOUT_GGUF, LAYOUT_TILED = 0, 1
+LAYOUT_GGUF, LAYOUT_TILED, LAYOUT_TILED_PAIR = 0, 1, 2
 
 # neura-pointwise op codes (crates/neura-pointwise/src/op.rs:141-170)
 ADD, MUL, SUB, DIV, MAXIMUM, MINIMUM, RELU, SQRT, RECIP, EXP = range(10)
@@ -200,6 +200,24 @@ class Runtime:
         _check(self._lib.neura_cuda_weight_seal(self._ctx, self.stream, element, n, k,
                                                 ctypes.c_void_p(gguf_ptr), ctypes.c_void_p(dst)))
         return Weight(dst, element, LAYOUT_TILED, n, k, nbytes)
+
+    def seal_pair_device(self, element: int, n: int, k: int, gate_ptr: int, up_ptr: int) -> Weight:
+        """Seals the gate and up tensors of an MLP (both GGUF [n, k], on the device) as one paired weight."""
+        nbytes = int(self._lib.neura_cuda_sealed_pair_bytes(element, n, k))
+        dst = self.alloc(nbytes)
+        _check(self._lib.neura_cuda_weight_seal_pair(self._ctx, self.stream, element, n, k, ctypes.c_void_p(gate_ptr),
+                                                     ctypes.c_void_p(up_ptr), ctypes.c_void_p(dst)))
+        return Weight(dst, element, LAYOUT_TILED_PAIR, n, k, nbytes)
+
+    def load_pair(self, element: int, n: int, k: int, gate_bytes: np.ndarray, up_bytes: np.ndarray) -> Weight:
+        """``load`` for the gate and up projections of an MLP: a product with the result is silu(gate x) * (up x)."""
+        gate = self.load(element, n, k, gate_bytes, seal=False)
+        up = self.load(element, n, k, up_bytes, seal=False)
+        weight = self.seal_pair_device(element, n, k, gate.ptr, up.ptr)
+        self.sync()
+        self.free(gate.ptr)
+        self.free(up.ptr)
+        return weight
 
     def quantize_device(self, element: int, src_ptr: int, elements: int, dst_ptr: int) -> None:
         _check(self._lib.neura_cuda_quantize(self._ctx, self.stream, element, ctypes.c_void_p(src_ptr), elements,

@@ -57,6 +57,21 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
                     at += rt.sealed_bytes(config.element, p, k)
                 weights[f"blk.{layer}.attn_qkv.weight"] = Weight(base, config.element, 1, total, k, at - base)
                 continue
+            if name == "ffn_gate":   # gate and up sealed as a pair
+                with torch.cuda.stream(stream):
+                    both = torch.empty(2 * payload_bytes(config.element, n * k) + 32, dtype=torch.uint8, device=device)
+                    half = (payload_bytes(config.element, n * k) + 15) // 16 * 16
+                    for part in range(2):
+                        view = numbers[: n * k]
+                        view.normal_(0.0, deviation, generator=gen)
+                        rt.quantize_device(config.element, view.data_ptr(), n * k, both.data_ptr() + part * half)
+                    weights[f"blk.{layer}.ffn_gate_up.weight"] = rt.seal_pair_device(
+                        config.element, n, k, both.data_ptr(), both.data_ptr() + half)
+                    rt.sync()
+                    del both
+                continue
+            if name == "ffn_up":
+                continue
             weights[f"blk.{layer}.{name}.weight"] = make(n, k)
     # the head in slabs of rows so that the scratch stays small
     k = config.hidden

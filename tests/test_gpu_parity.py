@@ -162,3 +162,21 @@ def test_device_packer_keeps_the_sign_of_a_zero_extreme(runtime, oracle):
     w[5, 255] = -0.0
     packed = oracle.pack_rows(nb.Q4K, w)
     assert np.array_equal(runtime.quantize(nb.Q4K, w), packed)
+
+
+@pytest.mark.parametrize("element", ELEMENTS)
+@pytest.mark.parametrize("n,k,rows", [(48, 512, 1), (1000, 1024, 3), (27, 256, 2)])
+def test_a_sealed_gate_up_pair_is_the_swiglu_of_the_two_products(runtime, oracle, element, n, k, rows):
+    # examples/qwen/mlp.rs:31-33: mul(silu(matmul(x, gate)), matmul(x, up))
+    gate = oracle.Stream(51).normal(n * k, 0.0, 0.05).reshape(n, k)
+    up = oracle.Stream(53).normal(n * k, 0.0, 0.05).reshape(n, k)
+    pg, pu = oracle.pack_rows(element, gate), oracle.pack_rows(element, up)
+    x = oracle.Stream(57).normal(rows * k).reshape(rows, k)
+    silu = oracle.linear(element, pg, n, k, x, chain=[(oracle.SILU, None)])
+    expected = oracle.linear(element, pu, n, k, x, chain=[(oracle.MUL, silu)])
+    pair = runtime.load_pair(element, n, k, pg, pu)
+    assert pair.layout == nb.LAYOUT_TILED_PAIR
+    xd, od = runtime.tensor(rows, k), runtime.tensor(rows, n)
+    runtime.write(xd, x)
+    runtime.linear(pair, xd, od)
+    assert_close(runtime.read(od), expected, f"pair element {element} [{n},{k}] rows {rows}")
