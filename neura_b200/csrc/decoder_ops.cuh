@@ -2,6 +2,8 @@
 // grouped-query attention of one new row over the cache, argmax, and the gather of a
 // quantised embedding row.  (rms_norm lives in prep.cuh, fused with the activation staging.)
 #pragma once
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "layout.cuh"
 
@@ -64,8 +66,8 @@ __global__ void rope_cache_kernel(const __grid_constant__ RopeCacheParams p) {
 // (sequence, key head) to arrive merges the splits in order (the reference's key-split attention
 // with its AttentionFold merge, crates/neura-abi/src/kind.rs:638-645).
 constexpr uint32_t kAttendMaxGroup = 8;    // query heads per key head
-constexpr uint32_t kAttendTile = 64;       // positions one CTA takes
-constexpr uint32_t kAttendMaxChunk = 64;   // row length of the per-head logit and merge tables (>= tile, >= splits)
+constexpr uint32_t kAttendMaxChunk = 128;  // row length of the per-head logit and merge tables (>= tile, >= splits)
+constexpr uint32_t kAttendMaxCluster = 8;  // splits that merge through distributed shared memory
 
 struct AttendParams {
     const float *q;           // [batch][q_stride], head h at h*width
@@ -89,16 +91,20 @@ __device__ __forceinline__ void copy16_async(void *dst_shared, const void *src_g
 // WIDTH is the head width (64 or 128).  The split's keys and values (contiguous in the cache)
 // are copied to shared memory with asynchronous 16-byte copies, all in flight at once, so the
 // cache costs one memory round trip per CTA.
-template <uint32_t WIDTH>
+// TILE is the number of positions one CTA takes (64 or 128).  With CLUSTER the splits of one
+// (sequence, key head) form a thread-block cluster and merge their partials through distributed
+// shared memory behind a cluster barrier; otherwise they merge through global memory, the last
+// CTA to arrive doing the work.
+template <uint32_t WIDTH, uint32_t TILE, bool CLUSTER>
 __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ AttendParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(16) float shared[];
     const uint32_t group = p.heads / p.key_heads;
     constexpr uint32_t KROW = WIDTH + 4;                 // padded key row: float4 reads of 8 rows hit 32 banks
-    float *ks = shared;                                  // [kAttendTile][KROW]
-    float *vs = ks + kAttendTile * KROW;                 // [kAttendTile][WIDTH]
-    float *qs = vs + kAttendTile * WIDTH;                // [group][WIDTH]
+    float *ks = shared;                                  // [TILE][KROW]
+    float *vs = ks + TILE * KROW;                 // [TILE][WIDTH]
+    float *qs = vs + TILE * WIDTH;                // [group][WIDTH]
     float *logits = qs + kAttendMaxGroup * WIDTH;        // [group][kAttendMaxChunk]
     float *stats = logits + kAttendMaxGroup * kAttendMaxChunk;  // [group][2]: largest, sum
     __shared__ unsigned int arrived;
@@ -107,8 +113,8 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     const uint32_t b = blockIdx.x / (p.splits * p.key_heads);
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const uint32_t count = min(p.position[b] + 1, p.capacity);
-    const uint32_t chunk = min((count + p.splits - 1) / p.splits, kAttendTile);
-    // (the host sizes `splits` so that capacity / splits <= kAttendTile)
+    const uint32_t chunk = min((count + p.splits - 1) / p.splits, TILE);
+    // (the host sizes `splits` so that capacity / splits <= TILE)
     const uint32_t first = min(split * chunk, count), last = min(first + chunk, count), held = last - first;
     const float *k = p.keys + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
     const float *v = p.values + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
@@ -165,10 +171,40 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
             for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
                 if (g < group) acc[g] = fmaf(logits[g * kAttendMaxChunk + pos], value, acc[g]);
         }
+        if constexpr (CLUSTER) {
+            // (every thread of the CTA is past the logits phase, which was the last reader of the key tile)
 #pragma unroll
-        for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
-            if (g < group)
-                __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (WIDTH + 2) + d, acc[g]);
+            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                if (g < group) ks[g * WIDTH + d] = acc[g];
+        } else {
+#pragma unroll
+            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                if (g < group)
+                    __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (WIDTH + 2) + d, acc[g]);
+        }
+    }
+    if constexpr (CLUSTER) {
+        // every split's partial sits in its CTA's shared memory; each CTA merges a slice of the channels
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const uint32_t per = (WIDTH + p.splits - 1) / p.splits;
+        const uint32_t d0 = min(split * per, WIDTH), d1 = min(d0 + per, WIDTH);
+        for (uint32_t item = threadIdx.x; item < group * (d1 - d0); item += blockDim.x) {
+            const uint32_t g = item / (d1 - d0), d = d0 + item % (d1 - d0);
+            float largest = -INFINITY;
+            for (uint32_t s2 = 0; s2 < p.splits; ++s2) largest = fmaxf(largest, cluster.map_shared_rank(stats, s2)[g * 2]);
+            float total = 0.0f, acc = 0.0f;
+            for (uint32_t s2 = 0; s2 < p.splits; ++s2) {
+                const float m = cluster.map_shared_rank(stats, s2)[g * 2];
+                const float f = m == -INFINITY ? 0.0f : expf(m - largest);
+                total = fmaf(cluster.map_shared_rank(stats, s2)[g * 2 + 1], f, total);
+                acc = fmaf(cluster.map_shared_rank(ks, s2)[g * WIDTH + d], f, acc);
+            }
+            p.out[(uint64_t)b * p.out_stride + (uint64_t)(kh * group + g) * WIDTH + d] = acc / total;
+        }
+        cluster.sync();   // no CTA leaves while its shared memory may still be read
+        return;
     }
     if (threadIdx.x < group * 2) {
         const uint32_t g = threadIdx.x / 2, which = threadIdx.x % 2;
@@ -185,11 +221,14 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     __syncthreads();
     if (arrived != p.splits - 1) return;
     // merge: every load of a phase is issued before its first use, so each phase costs one round trip
-    float *factor = logits;   // [group][splits], reusing the logits area (splits <= kAttendMaxChunk)
-    float *totals = stats;    // [group]
+    float *factor = logits;                    // [group][splits] (splits <= kAttendMaxChunk)
+    float *sums = ks;                          // [group][splits], the key tile is no longer needed
+    float *totals = stats;                     // [group]
     const float *mine = p.partial + ((uint64_t)b * p.heads + kh * group) * p.splits * (p.width + 2);
-    for (uint32_t i = threadIdx.x; i < group * p.splits; i += blockDim.x)
+    for (uint32_t i = threadIdx.x; i < group * p.splits; i += blockDim.x) {
         factor[(i / p.splits) * kAttendMaxChunk + i % p.splits] = __ldcg(mine + (uint64_t)i * (p.width + 2) + p.width);
+        sums[(i / p.splits) * kAttendMaxChunk + i % p.splits] = __ldcg(mine + (uint64_t)i * (p.width + 2) + p.width + 1);
+    }
     __syncthreads();
     for (uint32_t g = warp; g < group; g += warps) {
         float largest = -INFINITY;
@@ -200,25 +239,35 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
             const float m = factor[g * kAttendMaxChunk + s];
             const float f = m == -INFINITY ? 0.0f : expf(m - largest);
             factor[g * kAttendMaxChunk + s] = f;
-            total = fmaf(__ldcg(mine + ((uint64_t)g * p.splits + s) * (p.width + 2) + p.width + 1), f, total);
+            total = fmaf(sums[g * kAttendMaxChunk + s], f, total);
         }
         for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         if (lane == 0) totals[g] = total;
     }
     __syncthreads();
-    for (uint32_t item = threadIdx.x; item < group * p.width; item += blockDim.x) {
-        const uint32_t g = item / p.width, d = item % p.width;
-        const float *from = mine + (uint64_t)g * p.splits * (p.width + 2) + d;
-        float acc = 0.0f;
+    // one thread per channel; the partial rows of eight splits of every head of the group travel together
+    for (uint32_t d = threadIdx.x; d < p.width; d += blockDim.x) {
+        float acc[kAttendMaxGroup];
+#pragma unroll
+        for (uint32_t g = 0; g < kAttendMaxGroup; ++g) acc[g] = 0.0f;
         for (uint32_t s = 0; s < p.splits; s += 8) {
-            float part[8];
+            float part[kAttendMaxGroup][8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) part[u] = s + u < p.splits ? __ldcg(from + (uint64_t)(s + u) * (p.width + 2)) : 0.0f;
+            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (s + u < p.splits) acc = fmaf(part[u], factor[g * kAttendMaxChunk + s + u], acc);
+                for (int u = 0; u < 8; ++u)
+                    part[g][u] = (g < group && s + u < p.splits)
+                        ? __ldcg(mine + ((uint64_t)g * p.splits + s + u) * (p.width + 2) + d) : 0.0f;
+#pragma unroll
+            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (g < group && s + u < p.splits) acc[g] = fmaf(part[g][u], factor[g * kAttendMaxChunk + s + u], acc[g]);
         }
-        p.out[(uint64_t)b * p.out_stride + (uint64_t)(kh * group + g) * p.width + d] = acc / totals[g];
+#pragma unroll
+        for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+            if (g < group)
+                p.out[(uint64_t)b * p.out_stride + (uint64_t)(kh * group + g) * p.width + d] = acc[g] / totals[g];
     }
     if (threadIdx.x == 0) p.counters[b * p.key_heads + kh] = 0u;
 }

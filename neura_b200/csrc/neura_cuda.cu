@@ -616,25 +616,54 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, ui
                       group, kAttendMaxGroup);
     if (width != 64 && width != 128)
         return refuse(kBadArgument, "the attention kernel is built for heads of width 64 and 128, not %u", width);
-    if (capacity > 64 * kAttendTile)
-        return refuse(kBadArgument, "a cache of %u slots is more than the %u the attention kernel splits", capacity,
-                      64 * kAttendTile);
-    const uint32_t splits = (capacity + kAttendTile - 1) / kAttendTile;  // <= 64, and <= kAttendTile positions per CTA
-    const size_t smem = ((size_t)kAttendTile * (2 * width + 4) + (size_t)kAttendMaxGroup * width +
+    if (capacity > 64 * 128)
+        return refuse(kBadArgument, "a cache of %u slots is more than the %u the attention kernel splits", capacity, 64 * 128);
+    // up to 8 splits merge inside a thread-block cluster; longer caches merge through global memory
+    const uint32_t tile = capacity <= kAttendMaxCluster * 64 ? 64 : 128;
+    const uint32_t splits = (capacity + tile - 1) / tile;
+    const bool cluster = splits <= kAttendMaxCluster;
+    const size_t smem = ((size_t)tile * (2 * width + 4) + (size_t)kAttendMaxGroup * width +
                          (size_t)kAttendMaxGroup * kAttendMaxChunk + (size_t)kAttendMaxGroup * 2) * sizeof(float);
-    auto kernel = width == 128 ? attend_kernel<128> : attend_kernel<64>;
-    static bool raised[64][2] = {{false}};
-    if (!raised[ctx->device & 63][width == 128]) {
+    void (*kernel)(AttendParams);
+    const int which = (width == 128 ? 4 : 0) + (tile == 128 ? 2 : 0) + (cluster ? 1 : 0);
+    switch (which) {
+    case 0: kernel = attend_kernel<64, 64, false>; break;
+    case 1: kernel = attend_kernel<64, 64, true>; break;
+    case 2: kernel = attend_kernel<64, 128, false>; break;
+    case 3: kernel = attend_kernel<64, 128, true>; break;
+    case 4: kernel = attend_kernel<128, 64, false>; break;
+    case 5: kernel = attend_kernel<128, 64, true>; break;
+    case 6: kernel = attend_kernel<128, 128, false>; break;
+    default: kernel = attend_kernel<128, 128, true>; break;
+    }
+    static bool raised[64][8] = {{false}};
+    if (!raised[ctx->device & 63][which]) {
         NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        raised[ctx->device & 63][width == 128] = true;
+        raised[ctx->device & 63][which] = true;
     }
     int32_t rc;
-    if ((rc = ensure(ctx, ctx->attend_partial, (uint64_t)batch * heads * splits * (width + 2) * sizeof(float), false))) return rc;
-    if ((rc = ensure(ctx, ctx->attend_counters, (uint64_t)batch * key_heads * sizeof(unsigned int), true))) return rc;
+    if (!cluster) {
+        if ((rc = ensure(ctx, ctx->attend_partial, (uint64_t)batch * heads * splits * (width + 2) * sizeof(float), false))) return rc;
+        if ((rc = ensure(ctx, ctx->attend_counters, (uint64_t)batch * key_heads * sizeof(unsigned int), true))) return rc;
+    }
     AttendParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride,
                    (float *)ctx->attend_partial.ptr, (unsigned int *)ctx->attend_counters.ptr, scale,
                    batch, heads, key_heads, width, capacity, splits};
-    NC_CUDA(launch_dependent(kernel, dim3(batch * key_heads * splits), dim3(128), smem, (cudaStream_t)stream_, p));
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(batch * key_heads * splits);
+    config.blockDim = dim3(128);
+    config.dynamicSmemBytes = smem;
+    config.stream = (cudaStream_t)stream_;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = splits;
+    attribute[1].val.clusterDim.y = 1;
+    attribute[1].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = cluster ? 2 : 1;
+    NC_CUDA(cudaLaunchKernelEx(&config, kernel, p));
     ctx->launches++;
     return 0;
 }

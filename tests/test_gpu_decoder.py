@@ -74,12 +74,17 @@ def test_rope_and_cache_write(runtime, oracle):
         assert not untouched.any()
 
 
-def test_attention_over_the_cache(runtime, oracle):
-    batch, heads, key_heads, width, capacity = 2, 6, 2, 64, 96
+@pytest.mark.parametrize("heads,key_heads,width,capacity,positions", [
+    (6, 2, 64, 96, (0, 70)),        # two splits in one cluster
+    (10, 2, 128, 600, (599, 301)),  # five splits of 128 in one cluster
+    (4, 4, 128, 1100, (1099, 5)),   # nine splits: merged through global memory
+])
+def test_attention_over_the_cache(runtime, oracle, heads, key_heads, width, capacity, positions):
+    batch = 2
     q = oracle.Stream(9).normal(batch * heads * width).reshape(batch, heads, width)
     keys = oracle.Stream(10).normal(batch * key_heads * capacity * width).reshape(batch, key_heads, capacity, width)
     values = oracle.Stream(11).normal(keys.size).reshape(keys.shape)
-    position = np.array([0, 70], dtype=np.uint32)
+    position = np.array(positions, dtype=np.uint32)
     expected = oracle.attend(q, keys, values, position + 1, 0.125)
     qd, out = runtime.tensor(batch, heads * width), runtime.tensor(batch, heads * width)
     kd, vd, pd = runtime.tensor(keys.size), runtime.tensor(values.size), runtime.tensor_u32(batch)
