@@ -152,6 +152,16 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream, const nc_weight *w, con
                           uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
                           uint32_t n_steps);
 
+/* The tensor path, template_run_matmul_cooperative (crates/neura-kernel/src/task/matmul.rs:1344-1565),
+ * for prefill: many rows at once.  The f32 activations are rounded to bf16 (round to nearest even,
+ * crates/neura-precision/src/lib.rs:325-329), the Q4K weight is dequantised exactly and rounded to
+ * bf16 tile by tile in shared memory, products accumulate in f32 (tcgen05 MMAs into tensor memory):
+ *   out[r*out_stride + c] = chain(sum_k bf16(W[c][k]) * bf16(x[r*x_stride + k]))
+ * Needs a sealed (NC_LAYOUT_TILED) Q4K weight; any number of rows. */
+int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream, const nc_weight *w, const float *x_dev, uint32_t rows,
+                               uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
+                               uint32_t n_steps);
+
 /* The two halves of neura_cuda_linear, for callers that feed several weights with the
  * same activations (q/k/v, gate/up: examples/qwen/attention.rs:106-125, mlp.rs:31-32).
  * neura_cuda_stage rewrites up to 16 rows of f32 activations into the context's

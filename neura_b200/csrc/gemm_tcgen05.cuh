@@ -1,0 +1,250 @@
+// Prefill product on the 5th-generation tensor cores: out[M][N] = chain(X[M][K] . W[N][K]^T) with
+// Q4_K weights dequantised to bf16 tiles in shared memory, bf16 activations, f32 accumulation in
+// tensor memory (tcgen05.mma, kind::f16).
+//
+// This stands in for the reference's tensor path, template_run_matmul_cooperative
+// (crates/neura-kernel/src/task/matmul.rs:1344-1565), which converts both operands to 16-bit
+// floats in shared memory and multiplies them with cooperative-matrix MMAs into f32.
+//
+// One CTA computes a 128 (rows of X) x 256 (rows of W) tile of the output.  K advances in steps
+// of 64 (one 128-byte swizzle atom of bf16).  Warps 0-3 are producers: for every step they copy
+// the X tile (asynchronous 16-byte copies, swizzled) and dequantise a quarter super-block of 256
+// weight rows into the W tile; warp 4 issues the MMAs; the tiles cycle through a ring of stages
+// guarded by mbarriers (full: producers -> MMA, empty: tcgen05.commit -> producers).  When K is
+// exhausted the four producer warps read the accumulator out of tensor memory (tcgen05.ld), apply
+// the fused chain and store f32.  Every wait is bounded; a wait that runs out raises the status
+// word, and the CTA still frees its tensor memory before it leaves.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "gemv_mma.cuh"
+
+namespace nc {
+
+constexpr uint32_t kGemmBM = 128, kGemmBN = 256, kGemmBK = 64, kGemmStages = 4;
+constexpr uint32_t kGemmABytes = kGemmBM * kGemmBK * 2;   // 16 KiB
+constexpr uint32_t kGemmBBytes = kGemmBN * kGemmBK * 2;   // 32 KiB
+constexpr uint32_t kGemmStageBytes = kGemmABytes + kGemmBBytes;
+constexpr uint32_t kGemmTmemCols = 256;                   // 128 lanes x 256 f32 columns
+constexpr uint32_t kGemmThreads = 160;                    // 4 producer/epilogue warps + the MMA warp
+constexpr uint32_t kGemmSmem = kGemmStages * kGemmStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+
+struct GemmParams {
+    const uint8_t *w;            // tiled Q4_K weights
+    const __nv_bfloat16 *x;      // [m][k] bf16 activations
+    float *out;                  // [m][out_stride]
+    uint64_t out_stride;
+    uint32_t m, n, k;
+    uint32_t units32;            // 32-row units along N the sealed weight holds
+    unsigned int *status;
+    Chain chain;
+};
+
+// f32 -> bf16 with round-to-nearest-even (crates/neura-precision/src/lib.rs:325-329).
+__global__ void to_bf16_kernel(const float *x, uint64_t x_stride, uint32_t rows, uint32_t k, __nv_bfloat16 *out) {
+    const uint64_t total = (uint64_t)rows * k;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16_rn(x[(i / k) * x_stride + i % k]);
+}
+
+// ---- tcgen05 plumbing -------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// The barrier is told when this thread's asynchronous copies issued so far have landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void sts16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, swizzled in
+// 128-byte atoms: groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((address & 0x3ffffu) >> 4);   // start address
+    desc |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzled K-major tiles)
+    desc |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: 8 rows x 128 bytes
+    desc |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+    desc |= (uint64_t)2 << 61;                        // 128-byte swizzle
+    return desc;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M x N.
+__device__ __forceinline__ uint32_t instruction_descriptor(uint32_t m, uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// 32 lanes x 32 columns of f32 out of tensor memory: thread i of the warp gets lane i's 32 columns.
+__device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(address)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- dequantising a quarter super-block of one weight row into two 16-byte chunks of bf16 -------
+// `w0`, `w1`: the eight quant bytes [8t, 8t+8) of nibble group G of the row; low nibbles are
+// elements 8t.. of sub-block 2G, high nibbles the same elements of sub-block 2G+1.
+// value = (d*sc)*q - dmin*m rounded to f32 as q4_k_values does (crates/neura-precision/src/ggml.rs:341-346):
+// d*sc, dmin*m and (d*sc)*q are exact in f32 (11 x 6 x 4 significant bits), so one fused
+// multiply-subtract rounds exactly where the reference's separate operations round; then bf16 RNE.
+__device__ __forceinline__ uint32_t bf16_pair(float quantum, float low, uint32_t bytes, uint32_t lane_a, uint32_t lane_b) {
+    const float a = __uint_as_float(__byte_perm(bytes, 0x4b000000u, 0x7650u | lane_a)) - 8388608.0f;
+    const float b = __uint_as_float(__byte_perm(bytes, 0x4b000000u, 0x7650u | lane_b)) - 8388608.0f;
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(fmaf(quantum, a, -low), fmaf(quantum, b, -low));
+    return *reinterpret_cast<const uint32_t *>(&pair);
+}
+
+__device__ __forceinline__ void dequant_row_quarter(uint32_t tile, uint32_t row, uint32_t t, uint32_t G, uint32_t w0,
+                                                    uint32_t w1, const uint4 &header) {
+    uint32_t sc[2], mn[2];
+    q4k_scales(header.y, header.z, header.w, sc, mn);
+    const float d = half_bits_to_float(header.x & 0xffffu), dmin = half_bits_to_float(header.x >> 16);
+    const uint32_t sub = 2 * G;
+    const float quantum_lo = d * (float)((sc[sub >> 2] >> (8 * (sub & 3))) & 0xffu);
+    const float low_lo = dmin * (float)((mn[sub >> 2] >> (8 * (sub & 3))) & 0xffu);
+    const float quantum_hi = d * (float)((sc[(sub + 1) >> 2] >> (8 * ((sub + 1) & 3))) & 0xffu);
+    const float low_hi = dmin * (float)((mn[(sub + 1) >> 2] >> (8 * ((sub + 1) & 3))) & 0xffu);
+    const uint32_t lo0 = w0 & 0x0f0f0f0fu, lo1 = w1 & 0x0f0f0f0fu;
+    const uint32_t hi0 = (w0 >> 4) & 0x0f0f0f0fu, hi1 = (w1 >> 4) & 0x0f0f0f0fu;
+    const uint32_t at = tile + row * 128;
+    sts16(at + ((t ^ (row & 7)) << 4), bf16_pair(quantum_lo, low_lo, lo0, 0, 1), bf16_pair(quantum_lo, low_lo, lo0, 2, 3),
+          bf16_pair(quantum_lo, low_lo, lo1, 0, 1), bf16_pair(quantum_lo, low_lo, lo1, 2, 3));
+    sts16(at + (((4 + t) ^ (row & 7)) << 4), bf16_pair(quantum_hi, low_hi, hi0, 0, 1), bf16_pair(quantum_hi, low_hi, hi0, 2, 3),
+          bf16_pair(quantum_hi, low_hi, hi1, 0, 1), bf16_pair(quantum_hi, low_hi, hi1, 2, 3));
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t gemm_raw[];
+    const uint32_t base = (smem_addr(gemm_raw) + 1023u) & ~1023u;   // swizzle atoms want 1024-byte alignment
+    const uint32_t bars = base + kGemmStages * kGemmStageBytes;
+    const uint32_t full = bars, empty = bars + 8 * kGemmStages, accum = bars + 16 * kGemmStages;
+    const uint32_t slot = accum + 8;
+    __shared__ uint32_t failed;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t m0 = blockIdx.y * kGemmBM, n0 = blockIdx.x * kGemmBN;
+    const uint32_t ksteps = p.k / kGemmBK, nsb = p.k / kSuperBlock;
+
+    if (tid == 0) {
+        failed = 0;
+        for (uint32_t s = 0; s < kGemmStages; ++s) {
+            mbar_init(full + 8 * s, 256);   // 128 producer arrivals + 128 arrivals of their asynchronous copies
+            mbar_init(empty + 8 * s, 1);    // one tcgen05.commit
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) tmem_alloc(slot, kGemmTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = lds4(slot);
+    // the bf16 activations are written by the kernel before this one
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp < 4) {
+        // ---------------- producers ----------------
+        const uint32_t g = lane >> 2, t = lane & 3, half = warp & 1;
+        bool alive = true;
+        for (uint32_t it = 0; it < ksteps && alive; ++it) {
+            const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
+            if (!mbar_wait(empty + 8 * s, parity ^ 1u)) { alive = false; break; }
+            const uint32_t a_tile = base + s * kGemmStageBytes, b_tile = a_tile + kGemmABytes;
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) {
+                const uint32_t idx = tid + 128 * j, row = idx >> 3, c = idx & 7, gm = m0 + row;
+                const bool inside = gm < p.m;
+                const __nv_bfloat16 *src = p.x + (uint64_t)(inside ? gm : 0) * p.k + it * kGemmBK + c * 8;
+                cp_async_16(a_tile + row * 128 + ((c ^ (row & 7)) << 4), src, inside ? 16u : 0u);
+            }
+            cp_async_arrive(full + 8 * s);
+            const uint32_t sb = it >> 2, G = it & 3;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t uu = (warp >> 1) + 2 * j, unit = n0 / 32 + uu;
+                uint4 q = make_uint4(0u, 0u, 0u, 0u), h0 = q, h1 = q;
+                if (unit < p.units32) {
+                    const uint8_t *from = p.w + (((uint64_t)unit * nsb + sb) * 2 + half) * kQ4kUnit;
+                    q = ld_stream16(from + 256 + G * 512 + lane * 16);
+                    h0 = ld_stream16(from + g * 16);
+                    h1 = ld_stream16(from + (g + 8) * 16);
+                }
+                const uint32_t row = uu * 32 + half * 16 + g;
+                dequant_row_quarter(b_tile, row, t, G, q.x, q.y, h0);
+                dequant_row_quarter(b_tile, row + 8, t, G, q.z, q.w, h1);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tile through the async proxy
+            mbar_arrive(full + 8 * s);
+        }
+        if (!alive) failed = 1;
+        // ---------------- epilogue ----------------
+        if (alive && mbar_wait(accum, 0)) {
+            tc_fence_after();
+            const uint32_t row = m0 + warp * 32 + lane;
+            for (uint32_t c0 = 0; c0 < kGemmBN; c0 += 32) {
+                uint32_t r[32];
+                tmem_load_32(tmem + ((warp * 32) << 16) + c0, r);
+                if (row < p.m) {
+                    float *to = p.out + (uint64_t)row * p.out_stride + n0 + c0;
+#pragma unroll
+                    for (uint32_t i = 0; i < 32; ++i)
+                        if (n0 + c0 + i < p.n) to[i] = chained(p.chain, row, n0 + c0 + i, __uint_as_float(r[i]));
+                }
+            }
+        } else {
+            failed = 1;
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issue ----------------
+        const uint32_t idesc = instruction_descriptor(kGemmBM, kGemmBN);
+        bool alive = true;
+        for (uint32_t it = 0; it < ksteps; ++it) {
+            const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
+            if (!mbar_wait(full + 8 * s, parity)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t a_tile = base + s * kGemmStageBytes;
+            const uint64_t desc_a = smem_descriptor(a_tile), desc_b = smem_descriptor(a_tile + kGemmABytes);
+#pragma unroll
+            for (uint32_t kk = 0; kk < kGemmBK / 16; ++kk)   // 16 bf16 = 32 bytes further along K inside the swizzle atom
+                tc_mma_bf16(tmem, desc_a + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
+            tc_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
+        }
+        if (alive) tc_commit(accum);
+        else failed = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (failed && tid == 0) atomicOr(p.status, 2u);
+    if (warp == 4) tmem_free(tmem, kGemmTmemCols);
+}
+
+}  // namespace nc

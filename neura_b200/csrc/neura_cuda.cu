@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "decoder_ops.cuh"
+#include "gemm_tcgen05.cuh"
 #include "gemv_mma.cuh"
 #include "layout.cuh"
 #include "prep.cuh"
@@ -57,7 +58,7 @@ struct Region {
 struct nc_context {
     int device = 0;
     int sms = 0;
-    Region dig, cs, sums, partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch;
+    Region dig, cs, sums, partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch, x_bf16;
     uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
     uint64_t launches = 0;
     bool capturing = false;
@@ -231,7 +232,7 @@ int32_t neura_cuda_open(int32_t device, nc_context **out) {
 int32_t neura_cuda_close(nc_context *ctx) {
     if (!ctx) return 0;
     cudaSetDevice(ctx->device);
-    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch})
+    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
     return 0;
@@ -519,6 +520,55 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, co
                                            n_steps)))
             return rc;
     }
+    return 0;
+}
+
+int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_dev, uint32_t rows,
+                               uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
+                               uint32_t n_steps) {
+    if (!ctx || !x_dev || !out_dev) return refuse(kBadArgument, "a product needs a context, activations and an output");
+    int32_t rc;
+    if ((rc = check_weight(w))) return rc;
+    if (w->element != NC_ELEMENT_Q4K || w->layout != NC_LAYOUT_TILED)
+        return refuse(kBadArgument, "the tensor-core product takes a sealed Q4K weight (element %u, layout %u given)",
+                      w->element, w->layout);
+    if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
+    if (x_stride < w->k || out_stride < w->n)
+        return refuse(kBadArgument, "rows of %u activations and %u outputs overlap at strides %llu and %llu", w->k, w->n,
+                      (unsigned long long)x_stride, (unsigned long long)out_stride);
+    if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
+        return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
+    if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    if ((rc = ensure(ctx, ctx->x_bf16, (uint64_t)rows * w->k * 2, false))) return rc;
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const uint64_t total = (uint64_t)rows * w->k;
+    const uint64_t want = (total + 255) / 256;
+    const unsigned int blocks = (unsigned int)(want < (uint64_t)ctx->sms * 16 ? want : (uint64_t)ctx->sms * 16);
+    to_bf16_kernel<<<blocks, 256, 0, stream>>>(x_dev, x_stride, rows, w->k, (__nv_bfloat16 *)ctx->x_bf16.ptr);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
+    static bool raised[64] = {false};
+    if (!raised[ctx->device & 63]) {
+        NC_CUDA(cudaFuncSetAttribute(gemm_q4k_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+        raised[ctx->device & 63] = true;
+    }
+    GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.w = (const uint8_t *)w->data_dev;
+    p.x = (const __nv_bfloat16 *)ctx->x_bf16.ptr;
+    p.out = out_dev;
+    p.out_stride = out_stride;
+    p.m = rows;
+    p.n = w->n;
+    p.k = w->k;
+    p.units32 = (w->n + 31) / 32;
+    p.status = (unsigned int *)ctx->status.ptr;
+    p.chain.n = n_steps;
+    for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
+    NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((w->n + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM),
+                             dim3(kGemmThreads), kGemmSmem, stream, p));
+    ctx->launches++;
     return 0;
 }
 

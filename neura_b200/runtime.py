@@ -276,6 +276,15 @@ class Runtime:
         _check(self._lib.neura_cuda_linear(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(x.ptr), rows,
                                            x.shape[-1], ctypes.c_void_p(out.ptr), out.shape[-1], arr, count))
 
+    def linear_bf16(self, weight: Weight, x: DeviceTensor, out: DeviceTensor,
+                    chain: Optional[Sequence[Step]] = None, rows: Optional[int] = None) -> None:
+        """The prefill product on the tensor cores: bf16 operands, f32 accumulation (asynchronous)."""
+        rows = rows if rows is not None else x.rows
+        arr, count = self._steps(chain, weight.n)
+        rec = weight.record()
+        _check(self._lib.neura_cuda_linear_bf16(self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(x.ptr), rows,
+                                                x.shape[-1], ctypes.c_void_p(out.ptr), out.shape[-1], arr, count))
+
     def linear_static(self, weight: Weight, x: DeviceTensor, out: DeviceTensor,
                       chain: Optional[Sequence[Step]] = None, rows: Optional[int] = None) -> None:
         """``linear`` for callers that may not allocate on the device (a frame-budgeted game

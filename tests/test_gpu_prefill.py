@@ -1,0 +1,57 @@
+"""The tensor-core prefill product against the CPU oracle (needs a B200)."""
+import numpy as np
+import pytest
+
+import neura_b200 as nb
+
+pytestmark = pytest.mark.gpu
+
+# both sides round the dequantised weights and the activations to bf16 the same way, so what is left
+# is the order of the f32 accumulation: 1e-3 of the output's rms is the north star's bar
+REL_TOL = 1e-3
+
+
+def check(runtime, oracle, m, n, k, chain=False, seed=61):
+    w = oracle.Stream(seed).normal(n * k, 0.0, 0.02).reshape(n, k)
+    packed = oracle.pack_rows(nb.Q4K, w)
+    x = oracle.Stream(seed + 2).normal(m * k).reshape(m, k)
+    weight = runtime.load(nb.Q4K, n, k, packed)
+    xd, od = runtime.tensor(m, k), runtime.tensor(m, n)
+    runtime.write(xd, x)
+    steps, ochain = None, None
+    if chain:
+        bias = oracle.Stream(seed + 4).normal(n)
+        bd = runtime.tensor(n)
+        runtime.write(bd, bias)
+        steps, ochain = [nb.Step(nb.ADD, bd), nb.Step(nb.SILU)], [(oracle.ADD, bias), (oracle.SILU, None)]
+    runtime.linear_bf16(weight, xd, od, steps)
+    got = runtime.read(od)
+    want = oracle.linear(nb.Q4K, packed, n, k, x, chain=ochain, threads=8, bf16=True)
+    scale = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    worst = float(np.abs(got - want).max())
+    assert worst <= REL_TOL * scale, f"[{m}x{k}] x [{n}x{k}]: |diff| {worst:.3e} against rms {scale:.3e}"
+    for ptr in (xd.ptr, od.ptr, weight.ptr):
+        runtime.free(ptr)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (128, 256, 1024), (256, 512, 512), (200, 300, 768), (1, 33, 256),
+                                   (130, 5, 256)])
+def test_prefill_product_matches_the_bf16_oracle(runtime, oracle, m, n, k):
+    check(runtime, oracle, m, n, k)
+
+
+def test_prefill_product_applies_the_fused_chain(runtime, oracle):
+    check(runtime, oracle, 96, 320, 512, chain=True)
+
+
+def test_prefill_product_at_the_benchmark_depth_on_a_slice_of_its_width(runtime, oracle):
+    # config 4 is [2048 x 3584] x [18944 x 3584]; the oracle takes a slice of that in seconds
+    check(runtime, oracle, 64, 512, 3584)
+
+
+def test_prefill_refuses_what_it_does_not_multiply(runtime, oracle):
+    w = oracle.Stream(3).normal(32 * 256, 0.0, 0.02).reshape(32, 256)
+    q8 = runtime.load(nb.Q8_0, 32, 256, oracle.pack_rows(nb.Q8_0, w))
+    xd, od = runtime.tensor(4, 256), runtime.tensor(4, 32)
+    with pytest.raises(nb.NeuraCudaError, match="Q4K"):
+        runtime.linear_bf16(q8, xd, od)
