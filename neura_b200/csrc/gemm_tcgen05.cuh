@@ -6,15 +6,18 @@
 // (crates/neura-kernel/src/task/matmul.rs:1344-1565), which converts both operands to 16-bit
 // floats in shared memory and multiplies them with cooperative-matrix MMAs into f32.
 //
-// One CTA computes a 128 (rows of X) x 256 (rows of W) tile of the output.  K advances in steps
-// of 64 (one 128-byte swizzle atom of bf16).  Warps 0-3 are producers: for every step they copy
-// the X tile (asynchronous 16-byte copies, swizzled) and dequantise a quarter super-block of 256
-// weight rows into the W tile; warp 4 issues the MMAs; the tiles cycle through a ring of stages
+// One CTA computes a 256 (rows of X) x 256 (rows of W) tile of the output as two 128 x 256
+// accumulators, so a dequantised weight tile feeds two MMAs.  K advances in steps of 64 (one
+// 128-byte swizzle atom of bf16).  For every step one thread asks the tensor memory accelerator
+// for the X tile (cp.async.bulk.tensor, 128-byte swizzle, rows past M zero-filled) and warps 0-15
+// dequantise a quarter super-block of 256 weight rows into the W tile (the raw blocks of the next
+// step are fetched while this one is dequantised); warp 16 issues the MMAs; the tiles cycle through a ring of stages
 // guarded by mbarriers (full: producers -> MMA, empty: tcgen05.commit -> producers).  When K is
-// exhausted the four producer warps read the accumulator out of tensor memory (tcgen05.ld), apply
+// exhausted the producer warps read the accumulator out of tensor memory (tcgen05.ld), apply
 // the fused chain and store f32.  Every wait is bounded; a wait that runs out raises the status
 // word, and the CTA still frees its tensor memory before it leaves.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -22,15 +25,17 @@
 
 namespace nc {
 
-constexpr uint32_t kGemmBM = 128, kGemmBN = 256, kGemmBK = 64, kGemmStages = 4;
-constexpr uint32_t kGemmABytes = kGemmBM * kGemmBK * 2;   // 16 KiB
+constexpr uint32_t kGemmBM = 256, kGemmBN = 256, kGemmBK = 64, kGemmStages = 3;
+constexpr uint32_t kGemmABytes = kGemmBM * kGemmBK * 2;   // 32 KiB: two 128-row MMA operands
 constexpr uint32_t kGemmBBytes = kGemmBN * kGemmBK * 2;   // 32 KiB
 constexpr uint32_t kGemmStageBytes = kGemmABytes + kGemmBBytes;
-constexpr uint32_t kGemmTmemCols = 256;                   // 128 lanes x 256 f32 columns
-constexpr uint32_t kGemmThreads = 160;                    // 4 producer/epilogue warps + the MMA warp
+constexpr uint32_t kGemmTmemCols = 512;                   // two accumulators of 128 lanes x 256 f32 columns
+constexpr uint32_t kGemmProducers = 512;                  // 16 producer/epilogue warps
+constexpr uint32_t kGemmThreads = kGemmProducers + 32;    // ... + the MMA warp
 constexpr uint32_t kGemmSmem = kGemmStages * kGemmStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 
 struct GemmParams {
+    CUtensorMap x_map;           // the bf16 activations as a 2-D tensor [m][k], boxes of 256 rows x 64 columns
     const uint8_t *w;            // tiled Q4_K weights
     const __nv_bfloat16 *x;      // [m][k] bf16 activations
     float *out;                  // [m][out_stride]
@@ -123,23 +128,61 @@ __device__ __forceinline__ uint32_t bf16_pair(float quantum, float low, uint32_t
     return *reinterpret_cast<const uint32_t *>(&pair);
 }
 
+// The 6-bit scale and min of sub-blocks 2G and 2G+1 out of the twelve scale bytes (y = bytes 0-3,
+// z = 4-7, w = 8-11; scale_min_k4, crates/neura-precision/src/ggml.rs:127-136).
+__device__ __forceinline__ void quarter_scales(const uint4 &header, uint32_t G, float (&quantum)[2], float (&low)[2]) {
+    const float d = half_bits_to_float(header.x & 0xffffu), dmin = half_bits_to_float(header.x >> 16);
+    const uint32_t shift = 16 * (G & 1);   // sub-blocks 2G, 2G+1 sit in bytes 2(G&1), 2(G&1)+1 of their words
+    uint32_t sc, mn;                       // two bytes each: the pair of this quarter
+    if (G < 2) {
+        sc = (header.y >> shift) & 0x3f3fu;
+        mn = (header.z >> shift) & 0x3f3fu;
+    } else {
+        sc = ((header.w >> shift) & 0x0f0fu) | ((((header.y >> shift) >> 6) & 0x0303u) << 4);
+        mn = (((header.w >> shift) >> 4) & 0x0f0fu) | ((((header.z >> shift) >> 6) & 0x0303u) << 4);
+    }
+    quantum[0] = d * (float)(sc & 0xffu);
+    quantum[1] = d * (float)(sc >> 8);
+    low[0] = dmin * (float)(mn & 0xffu);
+    low[1] = dmin * (float)(mn >> 8);
+}
+
 __device__ __forceinline__ void dequant_row_quarter(uint32_t tile, uint32_t row, uint32_t t, uint32_t G, uint32_t w0,
                                                     uint32_t w1, const uint4 &header) {
-    uint32_t sc[2], mn[2];
-    q4k_scales(header.y, header.z, header.w, sc, mn);
-    const float d = half_bits_to_float(header.x & 0xffffu), dmin = half_bits_to_float(header.x >> 16);
-    const uint32_t sub = 2 * G;
-    const float quantum_lo = d * (float)((sc[sub >> 2] >> (8 * (sub & 3))) & 0xffu);
-    const float low_lo = dmin * (float)((mn[sub >> 2] >> (8 * (sub & 3))) & 0xffu);
-    const float quantum_hi = d * (float)((sc[(sub + 1) >> 2] >> (8 * ((sub + 1) & 3))) & 0xffu);
-    const float low_hi = dmin * (float)((mn[(sub + 1) >> 2] >> (8 * ((sub + 1) & 3))) & 0xffu);
+    float quantum[2], low[2];
+    quarter_scales(header, G, quantum, low);
     const uint32_t lo0 = w0 & 0x0f0f0f0fu, lo1 = w1 & 0x0f0f0f0fu;
     const uint32_t hi0 = (w0 >> 4) & 0x0f0f0f0fu, hi1 = (w1 >> 4) & 0x0f0f0f0fu;
     const uint32_t at = tile + row * 128;
-    sts16(at + ((t ^ (row & 7)) << 4), bf16_pair(quantum_lo, low_lo, lo0, 0, 1), bf16_pair(quantum_lo, low_lo, lo0, 2, 3),
-          bf16_pair(quantum_lo, low_lo, lo1, 0, 1), bf16_pair(quantum_lo, low_lo, lo1, 2, 3));
-    sts16(at + (((4 + t) ^ (row & 7)) << 4), bf16_pair(quantum_hi, low_hi, hi0, 0, 1), bf16_pair(quantum_hi, low_hi, hi0, 2, 3),
-          bf16_pair(quantum_hi, low_hi, hi1, 0, 1), bf16_pair(quantum_hi, low_hi, hi1, 2, 3));
+    sts16(at + ((t ^ (row & 7)) << 4), bf16_pair(quantum[0], low[0], lo0, 0, 1), bf16_pair(quantum[0], low[0], lo0, 2, 3),
+          bf16_pair(quantum[0], low[0], lo1, 0, 1), bf16_pair(quantum[0], low[0], lo1, 2, 3));
+    sts16(at + (((4 + t) ^ (row & 7)) << 4), bf16_pair(quantum[1], low[1], hi0, 0, 1), bf16_pair(quantum[1], low[1], hi0, 2, 3),
+          bf16_pair(quantum[1], low[1], hi1, 0, 1), bf16_pair(quantum[1], low[1], hi1, 2, 3));
+}
+
+struct RawQuarter {   // what one producer thread fetches for one k-step: 16 rows' lane of one unit half
+    uint4 q, h0, h1;
+};
+
+// Warp w of the 16 producers owns half (w & 1) of 32-row unit (w >> 1) of the 256-row W tile.
+__device__ __forceinline__ void fetch_quarter(RawQuarter &raw, const GemmParams &p, uint32_t n0, uint32_t it, uint32_t warp,
+                                              uint32_t lane) {
+    const uint32_t nsb = p.k / kSuperBlock, sb = it >> 2, G = it & 3, g = lane >> 2, half = warp & 1;
+    const uint32_t unit = n0 / 32 + (warp >> 1);
+    raw.q = raw.h0 = raw.h1 = make_uint4(0u, 0u, 0u, 0u);
+    if (unit < p.units32) {
+        const uint8_t *from = p.w + (((uint64_t)unit * nsb + sb) * 2 + half) * kQ4kUnit;
+        raw.q = ld_stream16(from + 256 + G * 512 + lane * 16);
+        raw.h0 = ld_stream16(from + g * 16);
+        raw.h1 = ld_stream16(from + (g + 8) * 16);
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const __grid_constant__ GemmParams p) {
@@ -151,18 +194,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
     __shared__ uint32_t failed;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t m0 = blockIdx.y * kGemmBM, n0 = blockIdx.x * kGemmBN;
-    const uint32_t ksteps = p.k / kGemmBK, nsb = p.k / kSuperBlock;
+    const uint32_t ksteps = p.k / kGemmBK;
+    constexpr uint32_t kMmaWarp = kGemmProducers / 32;
 
     if (tid == 0) {
         failed = 0;
         for (uint32_t s = 0; s < kGemmStages; ++s) {
-            mbar_init(full + 8 * s, 256);   // 128 producer arrivals + 128 arrivals of their asynchronous copies
-            mbar_init(empty + 8 * s, 1);    // one tcgen05.commit
+            mbar_init(full + 8 * s, kGemmProducers / 32 + 1);   // every producer warp arrives, and the thread that asks for the X tile
+            mbar_init(empty + 8 * s, 1);                   // one tcgen05.commit
         }
         mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) tmem_alloc(slot, kGemmTmemCols);
+    if (warp == kMmaWarp) tmem_alloc(slot, kGemmTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -171,48 +215,46 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    if (warp < 4) {
+    if (warp < kMmaWarp) {
         // ---------------- producers ----------------
         const uint32_t g = lane >> 2, t = lane & 3, half = warp & 1;
         bool alive = true;
-        for (uint32_t it = 0; it < ksteps && alive; ++it) {
-            const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
-            if (!mbar_wait(empty + 8 * s, parity ^ 1u)) { alive = false; break; }
-            const uint32_t a_tile = base + s * kGemmStageBytes, b_tile = a_tile + kGemmABytes;
+        // the raw blocks travel three steps ahead of their use (a miss to HBM takes longer than one step)
+        RawQuarter raw[4];
 #pragma unroll
-            for (uint32_t j = 0; j < 8; ++j) {
-                const uint32_t idx = tid + 128 * j, row = idx >> 3, c = idx & 7, gm = m0 + row;
-                const bool inside = gm < p.m;
-                const __nv_bfloat16 *src = p.x + (uint64_t)(inside ? gm : 0) * p.k + it * kGemmBK + c * 8;
-                cp_async_16(a_tile + row * 128 + ((c ^ (row & 7)) << 4), src, inside ? 16u : 0u);
-            }
-            cp_async_arrive(full + 8 * s);
-            const uint32_t sb = it >> 2, G = it & 3;
+        for (uint32_t j = 0; j < 3; ++j)
+            if (j < ksteps) fetch_quarter(raw[j], p, n0, j, warp, lane);
+        for (uint32_t it0 = 0; it0 < ksteps && alive; it0 += 4) {
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
-                const uint32_t uu = (warp >> 1) + 2 * j, unit = n0 / 32 + uu;
-                uint4 q = make_uint4(0u, 0u, 0u, 0u), h0 = q, h1 = q;
-                if (unit < p.units32) {
-                    const uint8_t *from = p.w + (((uint64_t)unit * nsb + sb) * 2 + half) * kQ4kUnit;
-                    q = ld_stream16(from + 256 + G * 512 + lane * 16);
-                    h0 = ld_stream16(from + g * 16);
-                    h1 = ld_stream16(from + (g + 8) * 16);
+                const uint32_t it = it0 + j;
+                if (it >= ksteps || !alive) break;
+                const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
+                if (it + 3 < ksteps) fetch_quarter(raw[(j + 3) & 3], p, n0, it + 3, warp, lane);
+                if (!mbar_wait(empty + 8 * s, parity ^ 1u)) { alive = false; break; }
+                const uint32_t a_tile = base + s * kGemmStageBytes, b_tile = a_tile + kGemmABytes;
+                if (tid == 0) {   // x (columns) is a multiple of 64 bf16 = 128 bytes: the 16-byte rule of the copy holds
+                    mbar_expect(full + 8 * s, kGemmABytes);
+                    tma_load_2d(a_tile, &p.x_map, it * kGemmBK, m0, full + 8 * s);
                 }
-                const uint32_t row = uu * 32 + half * 16 + g;
-                dequant_row_quarter(b_tile, row, t, G, q.x, q.y, h0);
-                dequant_row_quarter(b_tile, row + 8, t, G, q.z, q.w, h1);
+                const uint32_t G = it & 3;
+                const uint32_t row = (warp >> 1) * 32 + half * 16 + g;
+                dequant_row_quarter(b_tile, row, t, G, raw[j].q.x, raw[j].q.y, raw[j].h0);
+                dequant_row_quarter(b_tile, row + 8, t, G, raw[j].q.z, raw[j].q.w, raw[j].h1);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tile through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full + 8 * s);   // one arrival per warp: 512 arrivals on one barrier word would queue up
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tile through the async proxy
-            mbar_arrive(full + 8 * s);
         }
         if (!alive) failed = 1;
-        // ---------------- epilogue ----------------
+        // ---------------- epilogue: warp w reads lanes 32 (w % 4).. of accumulator (w / 4) % 2, column half w / 8 ----------------
         if (alive && mbar_wait(accum, 0)) {
             tc_fence_after();
-            const uint32_t row = m0 + warp * 32 + lane;
-            for (uint32_t c0 = 0; c0 < kGemmBN; c0 += 32) {
+            const uint32_t which = (warp >> 2) & 1, lanes = (warp & 3) * 32, columns = (warp >> 3) * (kGemmBN / 2);
+            const uint32_t row = m0 + which * 128 + lanes + lane;
+            for (uint32_t c0 = columns; c0 < columns + kGemmBN / 2; c0 += 32) {
                 uint32_t r[32];
-                tmem_load_32(tmem + ((warp * 32) << 16) + c0, r);
+                tmem_load_32(tmem + (lanes << 16) + which * kGemmBN + c0, r);
                 if (row < p.m) {
                     float *to = p.out + (uint64_t)row * p.out_stride + n0 + c0;
 #pragma unroll
@@ -225,17 +267,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
         }
     } else if (lane == 0) {
         // ---------------- MMA issue ----------------
-        const uint32_t idesc = instruction_descriptor(kGemmBM, kGemmBN);
+        const uint32_t idesc = instruction_descriptor(128, kGemmBN);
         bool alive = true;
         for (uint32_t it = 0; it < ksteps; ++it) {
             const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
             if (!mbar_wait(full + 8 * s, parity)) { alive = false; break; }
             tc_fence_after();
             const uint32_t a_tile = base + s * kGemmStageBytes;
-            const uint64_t desc_a = smem_descriptor(a_tile), desc_b = smem_descriptor(a_tile + kGemmABytes);
+            const uint64_t desc_a0 = smem_descriptor(a_tile), desc_a1 = smem_descriptor(a_tile + kGemmABytes / 2);
+            const uint64_t desc_b = smem_descriptor(a_tile + kGemmABytes);
 #pragma unroll
-            for (uint32_t kk = 0; kk < kGemmBK / 16; ++kk)   // 16 bf16 = 32 bytes further along K inside the swizzle atom
-                tc_mma_bf16(tmem, desc_a + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
+            for (uint32_t kk = 0; kk < kGemmBK / 16; ++kk) {   // 16 bf16 = 32 bytes further along K inside the swizzle atom
+                tc_mma_bf16(tmem, desc_a0 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
+                tc_mma_bf16(tmem + kGemmBN, desc_a1 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
+            }
             tc_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
         }
         if (alive) tc_commit(accum);
@@ -244,7 +289,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
     tc_fence_before();
     __syncthreads();
     if (failed && tid == 0) atomicOr(p.status, 2u);
-    if (warp == 4) tmem_free(tmem, kGemmTmemCols);
+    if (warp == kMmaWarp) tmem_free(tmem, kGemmTmemCols);
 }
 
 }  // namespace nc

@@ -553,8 +553,29 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
         NC_CUDA(cudaFuncSetAttribute(gemm_q4k_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
         raised[ctx->device & 63] = true;
     }
+    // the tensor map of the bf16 activations, encoded by the driver (looked up, so the library links the runtime only)
+    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    if (!encode) {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        NC_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found));
+        if (!entry || found != cudaDriverEntryPointSuccess) return refuse(kBadState, "the driver does not offer cuTensorMapEncodeTiled");
+        encode = (encode_fn)entry;
+    }
     GemmParams p;
     memset(&p, 0, sizeof p);
+    {
+        const cuuint64_t dims[2] = {w->k, rows};
+        const cuuint64_t strides[1] = {(cuuint64_t)w->k * 2};
+        const cuuint32_t box[2] = {kGemmBK, kGemmBM}, steps[2] = {1, 1};
+        const CUresult made = encode(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ctx->x_bf16.ptr, dims, strides, box, steps,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (made != CUDA_SUCCESS) return refuse(kBadState, "cuTensorMapEncodeTiled refused the activations (%d)", (int)made);
+    }
     p.w = (const uint8_t *)w->data_dev;
     p.x = (const __nv_bfloat16 *)ctx->x_bf16.ptr;
     p.out = out_dev;
