@@ -7,7 +7,8 @@ One step = one greedily decoded token of a random-init Qwen2.5-32B-shaped decode
 projections (64 layers; 17.99 GB of GGUF blocks per token, far larger than L2, so every step
 streams them from HBM) after a 512-token random prompt.  Prints ONE JSON line.
 With N > 1 (launched under torchrun) the model is split tensor-parallel over the N GPUs: q/k/v, gate, up
-and the head by rows, attention output and down by K with one NCCL all-reduce each.
+and the head by rows, attention output and down by K with one all-reduce each (the library's own
+one-shot kernel over NVLink peer memory, or NCCL with --comm nccl).
 """
 from __future__ import annotations
 
@@ -198,7 +199,10 @@ def run_ours(args):
         from neura_b200 import parallel
 
         shard = parallel.Shard(config, world, rank)
-        comm = parallel.TorchComm(world, rank, device=torch.device("cuda", local), stream=tstream)
+        if args.comm == "peer":   # the library's one-shot all-reduce over NVLink peer memory
+            comm = parallel.PeerComm(rt, world, rank, rows * config.hidden, device=torch.device("cuda", local), stream=tstream)
+        else:
+            comm = parallel.TorchComm(world, rank, device=torch.device("cuda", local), stream=tstream)
     weights = synthetic_weights(rt, config, seed=23 + rank, shard=shard)
     norms = synthetic_norms(rt, config)
     decoder = qwen.Decoder(rt, config, weights, norms, batch=rows, capacity=capacity, shard=shard, comm=comm)
@@ -292,7 +296,7 @@ def run_ours(args):
             "config": {"workload": f"{config.name} decode: {config.layers} layers, hidden {config.hidden}, "
                                    f"{config.heads}/{config.key_heads} heads x {config.head_width}, ff {config.feed_forward}, "
                                    f"vocab {config.vocab}; {args.prompt}-token random prompt, greedy",
-                       "batch": rows, "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                       "batch": rows, "parallelism": f"tp{world} ({args.comm} all-reduce)" if world > 1 else "single GPU",
                        "l2": f"inputs larger than L2 ({config.weight_bytes() / 1e9:.2f} GB of weights per step)",
                        "weight_bytes_per_token": config.weight_bytes()},
             "clocks": clock_summary,
@@ -327,6 +331,7 @@ def main():
     parser.add_argument("--workload", default="qwen2.5-32b-q4_k")
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--prompt", type=int, default=512)
+    parser.add_argument("--comm", default="peer", choices=["peer", "nccl"])
     parser.add_argument("--no-cpu", action="store_true")
     args = parser.parse_args()
     if args.impl == "reference":

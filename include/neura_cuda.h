@@ -229,6 +229,24 @@ int32_t neura_cuda_embed(nc_context *ctx, void *stream, const nc_weight *table, 
  * on the device so that a recorded decode step replays without host writes. */
 int32_t neura_cuda_advance(nc_context *ctx, void *stream, uint32_t *position_dev, uint32_t rows, uint32_t by);
 
+/* ---- tensor-parallel exchange over NVLink peer memory (no counterpart in the reference, which runs on one device) ---- */
+
+/* A communicator of one process per GPU on one box.  neura_cuda_comm_create allocates this rank's
+ * buffer (room for all-reduces of up to `max_count` f32) and writes its 64-byte CUDA IPC handle to
+ * `handle_out`; the caller gathers the handles of all ranks (any host channel) and gives them, in
+ * rank order, to neura_cuda_comm_connect, which maps the peers' buffers. */
+typedef struct nc_comm nc_comm;
+int32_t neura_cuda_comm_create(nc_context *ctx, uint64_t max_count, nc_comm **out, void *handle_out);
+int32_t neura_cuda_comm_connect(nc_context *ctx, nc_comm *comm, uint32_t rank, uint32_t world, const void *handles);
+int32_t neura_cuda_comm_destroy(nc_context *ctx, nc_comm *comm);
+
+/* inout_dev[i] <- sum over the ranks of their inout_dev[i], added in rank order (every rank gets
+ * the same bits).  One kernel: the ranks' partial sums cross NVLink as plain peer loads, the only
+ * waiting is on the peers' sequence flags, bounded by a two-second timer; a rank that gives up
+ * leaves its input untouched and the next neura_cuda_sync returns the refusal.  Every rank must
+ * issue the same calls in the same order.  `count` is a multiple of 4, `inout_dev` 16-byte aligned. */
+int32_t neura_cuda_allreduce(nc_context *ctx, void *stream, nc_comm *comm, float *inout_dev, uint32_t count);
+
 /* No counterpart in the reference.  neura_cuda_linear for callers that may not touch the
  * device allocator: a game loop stepping generation under a frame budget (where a
  * cudaMalloc, or the device-wide wait a cudaFree implies, would blow the frame), or a host

@@ -18,7 +18,8 @@ SYMBOLS = [
     "neura_cuda_stream_create", "neura_cuda_stream_destroy", "neura_cuda_linear_static",
     "neura_cuda_rms_norm_stage", "neura_cuda_rope_cache", "neura_cuda_attend", "neura_cuda_argmax", "neura_cuda_embed",
     "neura_cuda_advance", "neura_cuda_stage_window", "neura_cuda_argmax_segments", "neura_cuda_sealed_pair_bytes",
-    "neura_cuda_weight_seal_pair", "neura_cuda_linear_bf16",
+    "neura_cuda_weight_seal_pair", "neura_cuda_linear_bf16", "neura_cuda_comm_create",
+    "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce",
 ]
 
 
@@ -96,6 +97,10 @@ def load() -> ctypes.CDLL:
         "neura_cuda_sealed_pair_bytes": (u64, [u32, u32, u32]),
         "neura_cuda_weight_seal_pair": (i32, [p, p, u32, u32, u32, p, p, p]),
         "neura_cuda_linear_bf16": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, u64, p, u64, ctypes.POINTER(NcStep), u32]),
+        "neura_cuda_comm_create": (i32, [p, u64, pp, p]),
+        "neura_cuda_comm_connect": (i32, [p, p, u32, u32, p]),
+        "neura_cuda_comm_destroy": (i32, [p, p]),
+        "neura_cuda_allreduce": (i32, [p, p, p, p, u32]),
         "neura_cuda_stage_window": (i32, [p, p, p, u32, u64, u32, u32, u32, u32]),
         "neura_cuda_linear_static": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, u64, p, u64, ctypes.POINTER(NcStep), u32]),
     }

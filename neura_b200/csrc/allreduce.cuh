@@ -1,0 +1,100 @@
+// One-shot all-reduce over NVLink peer memory for the row-parallel projections of a tensor-parallel
+// decode step (no counterpart in the reference, which runs on one device).
+//
+// Every rank owns a communication buffer that its peers map (CUDA IPC): a call counter, one flag
+// per sender and two slots of one partial per sender.  A call pushes the rank's partial sums into
+// its seat of every rank's slot (posted stores over NVLink; nothing is read remotely), then
+// publishes the call's sequence number in its flag at every rank (release, system scope), waits
+// until all senders' flags in its own memory show that number (local acquire loads, bounded by a
+// timer) and adds the seats in rank order, so every rank computes bit-identical sums.  Two slots
+// suffice: a rank can only reach call s+2 after every peer has published s+1, i.e. has finished
+// reading call s.  A wait that runs out raises the status word and leaves the input untouched.
+#pragma once
+#include "common.cuh"
+#include "gemv_mma.cuh"
+
+namespace nc {
+
+constexpr uint32_t kMaxRanks = 8;
+constexpr uint32_t kCommHeaderBytes = 256;   // [0] call counter, [64 + 4 r] flag of sender r
+
+struct AllreduceParams {
+    unsigned char *mine;                 // this rank's communication buffer
+    unsigned char *peer[kMaxRanks];      // every rank's buffer as mapped here (peer[rank] == mine)
+    float *inout;                        // [count]
+    uint64_t slot_bytes;                 // bytes of one sender's seat; a slot is world seats
+    uint32_t count, world, rank;
+    unsigned int *status;
+};
+
+__device__ __forceinline__ unsigned int load_acquire_sys(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void store_release_sys(unsigned int *p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 load_peer16(const float *p) {
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void store_peer16(float *p, float4 v) {
+    asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// One CTA; count is a multiple of 4.
+__global__ void __launch_bounds__(1024) allreduce_kernel(const __grid_constant__ AllreduceParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ unsigned int gave_up;
+    unsigned int *counter = reinterpret_cast<unsigned int *>(p.mine);
+    const unsigned int seq = *counter + 1u;
+    const uint64_t slot = (uint64_t)(seq & 1u) * p.world * p.slot_bytes;
+    if (threadIdx.x == 0) gave_up = 0u;
+    // push this rank's partial into its seat at every rank
+    for (uint32_t i = threadIdx.x * 4; i < p.count; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(p.inout + i);
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxRanks; ++r)
+            if (r < p.world)
+                store_peer16(reinterpret_cast<float *>(p.peer[r] + kCommHeaderBytes + slot + p.rank * p.slot_bytes) + i, v);
+    }
+    __syncthreads();   // orders every thread's stores before the fences below
+    if (threadIdx.x < p.world) {
+        __threadfence_system();
+        store_release_sys(reinterpret_cast<unsigned int *>(p.peer[threadIdx.x] + 64) + p.rank, seq);
+        const unsigned int *flag = reinterpret_cast<const unsigned int *>(p.mine + 64) + threadIdx.x;
+        const unsigned long long start = global_nanos();
+        // (flags only grow; a peer may already be one call ahead)
+        while ((int)(load_acquire_sys(flag) - seq) < 0) {
+            if (global_nanos() - start > kWaitNanos) { gave_up = 1u; break; }
+        }
+    }
+    __syncthreads();
+    if (gave_up) {
+        if (threadIdx.x == 0) atomicOr(p.status, 4u);
+        return;   // the counter stays: the next call repeats this sequence number
+    }
+    for (uint32_t i = threadIdx.x * 4; i < p.count; i += blockDim.x * 4) {
+        float4 part[kMaxRanks];
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxRanks; ++r)
+            if (r < p.world)
+                part[r] = load_peer16(reinterpret_cast<const float *>(p.mine + kCommHeaderBytes + slot + r * p.slot_bytes) + i);
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxRanks; ++r) {
+            if (r < p.world) {
+                sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w;
+            }
+        }
+        *reinterpret_cast<float4 *>(p.inout + i) = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *counter = seq;
+}
+
+}  // namespace nc

@@ -6,6 +6,7 @@
 #include <new>
 #include <string>
 
+#include "allreduce.cuh"
 #include "common.cuh"
 #include "decoder_ops.cuh"
 #include "gemm_tcgen05.cuh"
@@ -63,6 +64,15 @@ struct nc_context {
     uint64_t launches = 0;
     bool capturing = false;
     uint64_t capture_mark = 0;
+};
+
+struct nc_comm {
+    int device = 0;
+    unsigned char *mine = nullptr;
+    unsigned char *peer[kMaxRanks] = {nullptr};
+    uint64_t slot_bytes = 0, max_count = 0;
+    uint32_t world = 0, rank = 0;
+    bool connected = false;
 };
 
 struct nc_program {
@@ -786,6 +796,85 @@ int32_t neura_cuda_advance(nc_context *ctx, void *stream_, uint32_t *position_de
     if (!ctx || !position_dev || !rows) return refuse(kBadArgument, "advance needs a context and positions");
     NC_CUDA(launch_dependent(advance_kernel, dim3((rows + 127) / 128), dim3(128), 0, (cudaStream_t)stream_, position_dev, rows, by));
     ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_comm_create(nc_context *ctx, uint64_t max_count, nc_comm **out, void *handle_out) {
+    if (!ctx || !out || !handle_out || !max_count) return refuse(kBadArgument, "a communicator needs a context, a size and somewhere to put its handle");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    nc_comm *comm = new (std::nothrow) nc_comm();
+    if (!comm) return refuse(kBadState, "out of host memory");
+    comm->device = ctx->device;
+    comm->max_count = (max_count + 3) / 4 * 4;
+    comm->slot_bytes = (comm->max_count * sizeof(float) + 255) / 256 * 256;
+    const uint64_t bytes = kCommHeaderBytes + 2 * kMaxRanks * comm->slot_bytes;   // two slots of one seat per sender
+    cudaError_t e = cudaMalloc((void **)&comm->mine, bytes);
+    if (e == cudaSuccess) e = cudaMemset(comm->mine, 0, bytes);
+    cudaIpcMemHandle_t handle;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&handle, comm->mine);
+    if (e != cudaSuccess) {
+        if (comm->mine) cudaFree(comm->mine);
+        delete comm;
+        return cuda_refuse(e, "neura_cuda_comm_create");
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    memcpy(handle_out, &handle, sizeof handle);
+    *out = comm;
+    return 0;
+}
+
+int32_t neura_cuda_comm_connect(nc_context *ctx, nc_comm *comm, uint32_t rank, uint32_t world, const void *handles) {
+    if (!ctx || !comm || !handles) return refuse(kBadArgument, "connect needs a context, a communicator and the ranks' handles");
+    if (world < 2 || world > kMaxRanks || rank >= world)
+        return refuse(kBadArgument, "rank %u of %u is not a place in a group of 2 to %u", rank, world, kMaxRanks);
+    if (comm->connected) return refuse(kBadState, "this communicator is already connected");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    for (uint32_t r = 0; r < world; ++r) {
+        if (r == rank) {
+            comm->peer[r] = comm->mine;
+            continue;
+        }
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, (const unsigned char *)handles + 64 * r, sizeof handle);
+        NC_CUDA(cudaIpcOpenMemHandle((void **)&comm->peer[r], handle, cudaIpcMemLazyEnablePeerAccess));
+    }
+    comm->world = world;
+    comm->rank = rank;
+    comm->connected = true;
+    return 0;
+}
+
+int32_t neura_cuda_allreduce(nc_context *ctx, void *stream_, nc_comm *comm, float *inout_dev, uint32_t count) {
+    if (!ctx || !comm || !inout_dev || !count) return refuse(kBadArgument, "an all-reduce needs a context, a communicator and numbers");
+    if (!comm->connected) return refuse(kBadState, "the communicator is not connected to its peers");
+    if (count % 4 || count > comm->max_count || (uintptr_t)inout_dev % 16)
+        return refuse(kBadArgument, "an all-reduce takes a 16-byte aligned multiple of 4 numbers, at most %llu (got %u)",
+                      (unsigned long long)comm->max_count, count);
+    int32_t rc;
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
+    AllreduceParams p;
+    memset(&p, 0, sizeof p);
+    p.mine = comm->mine;
+    for (uint32_t r = 0; r < comm->world; ++r) p.peer[r] = comm->peer[r];
+    p.inout = inout_dev;
+    p.slot_bytes = comm->slot_bytes;
+    p.count = count;
+    p.world = comm->world;
+    p.rank = comm->rank;
+    p.status = (unsigned int *)ctx->status.ptr;
+    const unsigned int threads = count / 4 >= 1024 ? 1024 : ((count / 4 + 31) / 32 * 32 < 32 ? 32 : (count / 4 + 31) / 32 * 32);
+    NC_CUDA(launch_dependent(allreduce_kernel, dim3(1), dim3(threads), 0, (cudaStream_t)stream_, p));
+    ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_comm_destroy(nc_context *ctx, nc_comm *comm) {
+    if (!comm) return 0;
+    if (ctx) cudaSetDevice(ctx->device);
+    for (uint32_t r = 0; r < comm->world; ++r)
+        if (r != comm->rank && comm->peer[r]) cudaIpcCloseMemHandle(comm->peer[r]);
+    if (comm->mine) cudaFree(comm->mine);
+    delete comm;
     return 0;
 }
 

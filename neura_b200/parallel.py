@@ -196,3 +196,33 @@ def load_decoder_weights(rt, config: Config, packed: Dict[str, np.ndarray], norm
         device_norms[key] = rt.tensor(value.size)
         rt.write(device_norms[key], value)
     return weights, device_norms
+
+
+class PeerComm(TorchComm):
+    """The same exchanges with the all-reduce done by the library's own one-shot kernel over NVLink
+    peer memory (``neura_cuda_allreduce``); torch.distributed only carries the IPC handles at set-up
+    and the (rare) logits gather."""
+
+    def __init__(self, rt, world: int, rank: int, max_count: int, device=None, stream=None):
+        import ctypes
+
+        from .runtime import _check
+
+        super().__init__(world, rank, device=device, stream=stream)
+        self.rt = rt
+        handle = (ctypes.c_ubyte * 64)()
+        comm = ctypes.c_void_p()
+        _check(rt._lib.neura_cuda_comm_create(rt._ctx, max_count, ctypes.byref(comm), handle))
+        self.comm = comm
+        gathered = [None] * world
+        self.dist.all_gather_object(gathered, bytes(handle))
+        blob = (ctypes.c_ubyte * (64 * world)).from_buffer_copy(b"".join(gathered))
+        _check(rt._lib.neura_cuda_comm_connect(rt._ctx, comm, rank, world, blob))
+        self.dist.barrier()
+
+    def all_reduce(self, ptr: int, count: int) -> None:
+        import ctypes
+
+        from .runtime import _check
+
+        _check(self.rt._lib.neura_cuda_allreduce(self.rt._ctx, self.rt.stream, self.comm, ctypes.c_void_p(ptr), count))

@@ -41,7 +41,11 @@ def main() -> int:
     rt.use_stream(rt.new_stream())
     device = torch.device("cuda", local)
     shard = parallel.Shard(config, world, rank)
-    comm = parallel.TorchComm(world, rank, device=device, stream=torch.cuda.ExternalStream(rt.stream.value, device=device))
+    stream = torch.cuda.ExternalStream(rt.stream.value, device=device)
+    if os.environ.get("TP_COMM", "peer") == "peer":   # the library's own all-reduce over NVLink peer memory
+        comm = parallel.PeerComm(rt, world, rank, batch * config.hidden, device=device, stream=stream)
+    else:                                              # NCCL through torch.distributed
+        comm = parallel.TorchComm(world, rank, device=device, stream=stream)
     weights, dnorms = parallel.load_decoder_weights(rt, config, packed, norms, shard)
     decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=96, shard=shard, comm=comm)
     eager = decoder.generate(prompts, 64)
@@ -60,7 +64,8 @@ def main() -> int:
                   f"(oracle margin {margins[b, at]:.3e})")
             status = 1
         if status == 0:
-            print(f"tp{world}: 64 greedy tokens x {batch} sequences match the oracle, eager and recorded")
+            print(f"tp{world}: 64 greedy tokens x {batch} sequences match the oracle, eager and recorded "
+                  f"({type(comm).__name__})")
     flag = torch.tensor([status], device=device)
     dist.broadcast(flag, 0)
     rt.sync()
