@@ -283,6 +283,9 @@ def run_ours(args):
     algorithmic = 2 * nb.payload_bytes(config.element, n * k) + 4 * rows * k + 4 * rows * n
     achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
 
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel from the ncu capture
+    # summarised in profiles/decode_step_qwen32b_q4k_kernels.md (the full-size shape, batch 1, one GPU)
+    traffic = 163.4e6 if (config.name.startswith("qwen2.5-32b-q4_k") and rows == 1 and world == 1) else None
     times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=torch.device("cuda", local))
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -304,7 +307,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
                          "kernel": f"gemv_stream_kernel<Q4_K> on the paired gate|up [2x{n}x{k}] at batch {rows}",
                          "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
                          "step_gbs_per_gpu": (shard.local_bytes_per_token() if shard else config.weight_bytes())
