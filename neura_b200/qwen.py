@@ -244,6 +244,31 @@ class Decoder:
         else:
             self.rt.run(self.program)
 
+    def answer(self, tokens, cursors):
+        """One step with the planes' tokens and cursors given by the host, as Batch::answer writes
+        them (crates/neura-generate/src/batch.rs:1716-1725); returns the chosen ids [batch]."""
+        import numpy as np
+
+        self.rt.write(self.tokens, np.ascontiguousarray(tokens, dtype=np.uint32))
+        self.rt.write(self.position, np.ascontiguousarray(cursors, dtype=np.uint32))
+        self.run_token()
+        return self.rt.read(self.tokens, dtype=np.uint32)
+
+    @classmethod
+    def from_gguf(cls, rt: Runtime, source, batch: int = 1, capacity: int = 640, shard=None, comm=None,
+                  name: str = None) -> "Decoder":
+        """A decoder over the tensors of a GGUF (a path or a parsed ``gguf.Gguf``): the shapes from its
+        metadata (examples/qwen/config.rs:22-60), every projection poured and sealed
+        (Runtime::load, crates/neura-runtime/src/runtime.rs:356)."""
+        from . import gguf as gguf_reader
+        from .parallel import load_decoder_weights
+
+        held = gguf_reader.Gguf.open(source) if isinstance(source, str) else source
+        config = gguf_reader.read_config(held, name)
+        packed, norms = gguf_reader.decoder_tensors(held, config)
+        weights, device_norms = load_decoder_weights(rt, config, packed, norms, shard=shard)
+        return cls(rt, config, weights, device_norms, batch=batch, capacity=capacity, shard=shard, comm=comm)
+
     def generate(self, prompts, steps: int):
         """Feeds ``prompts`` [batch, length] one token at a time (every step attends to all the
         tokens before it), then decodes ``steps`` tokens greedily.  Returns [batch, steps] ids."""

@@ -64,6 +64,11 @@ class OracleDecoder:
         self.position += 1
         return oracle.argmax(self.logits)
 
+    def answer(self, tokens: np.ndarray, cursors: np.ndarray) -> np.ndarray:
+        """One step with every plane's token and cursor given (the stepper ``generate.Batch`` drives)."""
+        self.position[:] = np.asarray(cursors, dtype=np.uint32)
+        return self.step(np.ascontiguousarray(tokens, dtype=np.uint32))
+
     def generate(self, prompts: np.ndarray, steps: int):
         """Returns (tokens [batch, steps], margins [batch, steps]): the gap between the two largest
         logits at every decoded step, which says how decisive each greedy choice was."""

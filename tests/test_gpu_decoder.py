@@ -144,3 +144,93 @@ def test_greedy_tokens_match_the_oracle_for_64_steps(oracle, name, batch):
         b, at = differs[0]
         pytest.fail(f"sequence {b} leaves the oracle at step {at}: {eager[b, at]} for {want[b, at]}, "
                     f"the oracle's margin there is {margins[b, at]:.3e}")
+
+
+def test_a_decoder_read_from_a_gguf_file_decodes_what_the_poured_tensors_decode(oracle, tmp_path):
+    from neura_b200 import gguf
+    from oracle.decoder import OracleDecoder, synthetic_model
+
+    config = SMALL["q4_k"]
+    packed, norms = synthetic_model(config, seed=23)
+    norms["blk.1.attn_norm.weight"] = oracle.Stream(4).uniform(config.hidden, 0.5, 1.5)
+    path = tmp_path / "tiny.gguf"
+    path.write_bytes(gguf.write_decoder(config, packed, norms))
+    prompts = (oracle.Stream(31).uniform(8, 0.0, 1.0) * config.vocab).astype(np.uint32).reshape(1, 8)
+    want, margins = OracleDecoder(config, packed, norms, batch=1, capacity=48).generate(prompts, 32)
+    rt = nb.Runtime(0)
+    try:
+        decoder = qwen.Decoder.from_gguf(rt, str(path), batch=1, capacity=48)
+        assert decoder.config == config
+        got = decoder.generate(prompts, 32)
+    finally:
+        rt.close()
+    assert np.array_equal(got, want), f"smallest oracle margin {margins.min():.3e}"
+
+
+def test_continuous_batching_decodes_each_sequence_as_the_oracle_decodes_it_alone(oracle):
+    from neura_b200.generate import Batch
+    from oracle.decoder import OracleDecoder, synthetic_model
+
+    config = SMALL["q8_0"]
+    packed, norms = synthetic_model(config, seed=23)
+    draws = (oracle.Stream(37).uniform(24, 0.0, 1.0) * config.vocab).astype(np.uint32)
+    prompts = [list(draws[:9]), list(draws[9:10]), list(draws[10:16]), list(draws[16:24])]
+    steps = 12
+    alone = [OracleDecoder(config, packed, norms, batch=1, capacity=40).generate(np.array([p]), steps)[0][0].tolist()
+             for p in prompts]
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weights, dnorms = load_model(rt, config, packed, norms)
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=3, capacity=40)
+        decoder.record()
+        batch = Batch(decoder)
+        got = {i: [] for i in range(len(prompts))}
+        plane, waiting = {}, list(range(len(prompts)))
+        for _ in range(3):
+            index = waiting.pop(0)
+            plane[batch.admit(prompts[index])] = index
+            for slot, token in batch.step():  # every sequence joins a step after the one before it
+                got[plane[slot]].append(token)
+        for _ in range(200):
+            for slot, token in batch.step():
+                got[plane[slot]].append(token)
+            for slot in list(batch.occupied()):
+                if len(got[plane[slot]]) >= steps:
+                    batch.finish(slot)
+                    if waiting:
+                        index = waiting.pop(0)
+                        plane[batch.admit(prompts[index])] = index
+            if not list(batch.occupied()):
+                break
+    finally:
+        rt.close()
+    assert [got[i][:steps] for i in range(len(prompts))] == alone
+
+
+def test_the_whole_half_billion_decoder_decodes_the_golden_tokens(oracle):
+    """Qwen2.5-0.5B shapes, every projection Q8_0, tied head: 128 prompt tokens, 128 greedy tokens,
+    against the ids the CPU oracle decoded (tests/golden/make_decoder_golden.py)."""
+    import os
+
+    from oracle.decoder import synthetic_model
+
+    golden = np.load(os.path.join(os.path.dirname(__file__), "golden", "qwen05b_q8_0_greedy.npz"))
+    config = qwen.QWEN25_05B_Q8
+    packed, norms = synthetic_model(config, seed=int(golden["seeds"][0]))
+    prompts, want, margins = golden["prompt"], golden["tokens"], golden["margins"]
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weights, dnorms = load_model(rt, config, packed, norms)
+        del packed
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=1, capacity=256)
+        decoder.record()
+        got = decoder.generate(prompts, want.shape[1])
+    finally:
+        rt.close()
+    differs = np.argwhere(got != want)
+    if differs.size:
+        _, at = differs[0]
+        pytest.fail(f"the decoder leaves the golden ids at step {at}: {got[0, at]} for {want[0, at]}; "
+                    f"the oracle's margin there is {margins[0, at]:.3e}, the smallest before it {margins[0, :at + 1].min():.3e}")
