@@ -119,6 +119,13 @@ int32_t neura_cuda_sync(nc_context *ctx, void *stream);
  * `rows` activation rows against matrices of up to [n, k] never allocate. */
 int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k);
 
+/* The same for the decoder's other scratch: the partial results of an attention over a cache of
+ * `capacity` rows and the candidates of an argmax over `rows` rows, so that a decode step can be
+ * recorded without having run eagerly first.  (The reference sizes these at plan time,
+ * crates/neura-plan/src/layout.rs:22-55.) */
+int32_t neura_cuda_reserve_decoder(nc_context *ctx, uint32_t rows, uint32_t heads, uint32_t key_heads, uint32_t width,
+                                   uint32_t capacity);
+
 /* The load step after pour_one (store.rs:77-157): permutes a verbatim GGUF tensor
  * into the tiled layout the MMA kernels stream.  Out of place; `dst_dev` holds
  * neura_cuda_sealed_bytes().  Dequantised values are unchanged bit for bit. */

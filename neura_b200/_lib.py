@@ -19,7 +19,7 @@ SYMBOLS = [
     "neura_cuda_rms_norm_stage", "neura_cuda_rope_cache", "neura_cuda_attend", "neura_cuda_argmax", "neura_cuda_embed",
     "neura_cuda_advance", "neura_cuda_stage_window", "neura_cuda_argmax_segments", "neura_cuda_sealed_pair_bytes",
     "neura_cuda_weight_seal_pair", "neura_cuda_linear_bf16", "neura_cuda_comm_create",
-    "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce",
+    "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce", "neura_cuda_reserve_decoder",
 ]
 
 
@@ -73,6 +73,7 @@ def load() -> ctypes.CDLL:
         "neura_cuda_read": (i32, [p, p, p, p, u64]),
         "neura_cuda_sync": (i32, [p, p]),
         "neura_cuda_reserve": (i32, [p, u32, u32, u32]),
+        "neura_cuda_reserve_decoder": (i32, [p, u32, u32, u32, u32, u32]),
         "neura_cuda_weight_seal": (i32, [p, p, u32, u32, u32, p, p]),
         "neura_cuda_dequant": (i32, [p, p, ctypes.POINTER(NcWeight), p]),
         "neura_cuda_quantize": (i32, [p, p, u32, p, u64, p]),

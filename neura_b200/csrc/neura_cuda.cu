@@ -63,6 +63,7 @@ struct nc_context {
     uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
     uint64_t launches = 0;
     bool capturing = false;
+    cudaStream_t capture_stream = nullptr;
     uint64_t capture_mark = 0;
 };
 
@@ -242,6 +243,12 @@ int32_t neura_cuda_open(int32_t device, nc_context **out) {
 int32_t neura_cuda_close(nc_context *ctx) {
     if (!ctx) return 0;
     cudaSetDevice(ctx->device);
+    if (ctx->capturing) {  // a recording cut short by an error: end it, or the thread stays in capture mode
+        cudaGraph_t graph = nullptr;
+        cudaStreamEndCapture(ctx->capture_stream, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+    }
     for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
@@ -333,6 +340,19 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     if ((rc = ensure(ctx, ctx->stage_x, (uint64_t)rows * k * sizeof(float), false))) return rc;
     if ((rc = ensure(ctx, ctx->stage_out, (uint64_t)rows * n * sizeof(float), false))) return rc;
     return 0;
+}
+
+int32_t neura_cuda_reserve_decoder(nc_context *ctx, uint32_t rows, uint32_t heads, uint32_t key_heads, uint32_t width,
+                                   uint32_t capacity) {
+    if (!ctx || !rows || !heads || !key_heads || !width || !capacity)
+        return refuse(kBadArgument, "reserve needs a context and the decoder's shape");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc;
+    const uint64_t splits = ((uint64_t)capacity + 63) / 64;   // never fewer tiles than the attention launches
+    if ((rc = ensure(ctx, ctx->attend_partial, (uint64_t)rows * heads * splits * (width + 2) * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->attend_counters, (uint64_t)rows * key_heads * sizeof(unsigned int), true))) return rc;
+    if ((rc = ensure(ctx, ctx->argmax_scratch, (uint64_t)rows * 64 * 8 + (uint64_t)rows * 4 + 256, true))) return rc;
+    return ensure(ctx, ctx->status, 256, true);
 }
 
 static int32_t seal_any(nc_context *ctx, void *stream, uint32_t element, uint32_t n, uint32_t k, const void *gguf_dev,
@@ -1015,6 +1035,7 @@ int32_t neura_cuda_capture_begin(nc_context *ctx, void *stream) {
     if (!stream) return refuse(kBadArgument, "a program is recorded on a stream of its own, not the default stream");
     NC_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
+    ctx->capture_stream = (cudaStream_t)stream;
     ctx->capture_mark = ctx->launches;
     return 0;
 }

@@ -170,7 +170,8 @@ class Decoder:
         self.keys = [rt.tensor(cache) for _ in range(c.layers)]
         self.values = [rt.tensor(cache) for _ in range(c.layers)]
         widest_k = max(c.hidden, self.window(c.feed_forward)[0], self.window(c.query_width)[0])
-        rt.reserve(batch, max(self.vocab, self.feed_forward, c.hidden), widest_k)
+        rt.reserve(batch, max(self.vocab, 2 * self.feed_forward, c.hidden), widest_k)   # 2x: a sealed gate|up pair
+        rt.reserve_decoder(batch, self.heads, self.key_heads, c.head_width, capacity)
         self.program: Optional[int] = None
         self.scale = 1.0 / float(c.head_width) ** 0.5
 
@@ -229,7 +230,14 @@ class Decoder:
 
     def record(self) -> int:
         self.rt.capture_begin()
-        self.step()
+        try:
+            self.step()
+        except Exception:
+            try:   # leave no capture open behind a refused launch
+                self.rt.program_free(self.rt.capture_end())
+            except Exception:
+                pass
+            raise
         self.program = self.rt.capture_end()
         return self.program
 

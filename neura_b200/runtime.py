@@ -153,6 +153,9 @@ class Runtime:
     def reserve(self, rows: int, n: int, k: int) -> None:
         _check(self._lib.neura_cuda_reserve(self._ctx, rows, n, k))
 
+    def reserve_decoder(self, rows: int, heads: int, key_heads: int, width: int, capacity: int) -> None:
+        _check(self._lib.neura_cuda_reserve_decoder(self._ctx, rows, heads, key_heads, width, capacity))
+
     @property
     def launches(self) -> int:
         return int(self._lib.neura_cuda_launches(self._ctx))

@@ -1,4 +1,6 @@
 """The decoder step and its parts against the CPU oracle (needs a B200)."""
+import dataclasses
+
 import numpy as np
 import pytest
 
@@ -160,7 +162,7 @@ def test_a_decoder_read_from_a_gguf_file_decodes_what_the_poured_tensors_decode(
     rt = nb.Runtime(0)
     try:
         decoder = qwen.Decoder.from_gguf(rt, str(path), batch=1, capacity=48)
-        assert decoder.config == config
+        assert decoder.config == dataclasses.replace(config, floor=float(np.float32(config.floor)))  # stored as f32
         got = decoder.generate(prompts, 32)
     finally:
         rt.close()
@@ -234,3 +236,20 @@ def test_the_whole_half_billion_decoder_decodes_the_golden_tokens(oracle):
         _, at = differs[0]
         pytest.fail(f"the decoder leaves the golden ids at step {at}: {got[0, at]} for {want[0, at]}; "
                     f"the oracle's margin there is {margins[0, at]:.3e}, the smallest before it {margins[0, :at + 1].min():.3e}")
+
+
+def test_a_recording_cut_short_by_a_refusal_is_ended_when_the_context_closes(runtime, oracle):
+    packed = oracle.pack_rows(nb.Q8_0, oracle.Stream(2).normal(64 * 4096, 0.0, 0.02).reshape(64, 4096))
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weight = rt.load(nb.Q8_0, 64, 4096, packed)
+        x, out = rt.tensor(1, 4096), rt.tensor(1, 64)
+        rt.capture_begin()
+        with pytest.raises(nb.NeuraCudaError, match="may not grow the scratch"):
+            rt.linear(weight, x, out)
+    finally:
+        rt.close()
+    probe = runtime.tensor(16)          # the thread is out of capture mode: allocation works again
+    runtime.write(probe, np.arange(16, dtype=np.float32))
+    assert runtime.read(probe).tolist() == list(range(16))
