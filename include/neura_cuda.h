@@ -286,6 +286,42 @@ int32_t neura_cuda_capture_end(nc_context *ctx, void *stream, nc_program **out);
 int32_t neura_cuda_program_run(nc_context *ctx, void *stream, nc_program *program);
 int32_t neura_cuda_program_free(nc_context *ctx, nc_program *program);
 
+/* ---- a whole decode step as one persistent kernel ---------------------------------------------------
+ * The reference compiles a step into one device megakernel that walks task records
+ * (Runtime::compile, runtime.rs:528; crates/neura-kernel/src/substrate.rs).  neura_cuda_decoder_compile
+ * does the same for a Qwen-shaped decoder (examples/qwen/model.rs:77-103): it lays the step out as a
+ * table of phases (embedding gather; per layer: rms_norm + q|k|v product, RoPE + cache write + attention,
+ * output product + residual, rms_norm + gate|up product with SwiGLU, down product + residual; final
+ * rms_norm + head product; argmax; cursor += 1) that ONE cooperative kernel walks, one CTA per SM, with a
+ * grid barrier between phases.  neura_cuda_decoder_step is Batch::answer (batch.rs:1716-1725) for every
+ * sequence: it reads tokens_dev and position_dev, writes the chosen ids back to tokens_dev, the logits
+ * to logits_dev and moves the cursors.  Limits: 1 or 2 sequences, hidden and query width <= 8192. */
+typedef struct nc_decoder_layer {
+    nc_weight qkv;          /* q, k, v rows stacked, NC_LAYOUT_TILED */
+    nc_weight attn_output;  /* NC_LAYOUT_TILED */
+    nc_weight gate_up;      /* NC_LAYOUT_TILED_PAIR, n = feed_forward */
+    nc_weight down;         /* NC_LAYOUT_TILED */
+    const float *attn_norm_dev, *ffn_norm_dev; /* [hidden] */
+    float *keys_dev, *values_dev;              /* [batch][key_heads][capacity][head_width] */
+} nc_decoder_layer;
+
+typedef struct nc_decoder_desc {
+    uint32_t layers, hidden, heads, key_heads, head_width, feed_forward, vocab;
+    uint32_t batch, capacity;
+    float floor, rope_base, scale;
+    nc_weight embedding;     /* [vocab, hidden], either layout */
+    nc_weight head;          /* [vocab, hidden], NC_LAYOUT_TILED */
+    const float *output_norm_dev;
+    const nc_decoder_layer *layer; /* host array of `layers` entries */
+    uint32_t *tokens_dev, *position_dev; /* [batch] */
+    float *logits_dev;                   /* [batch][vocab] */
+} nc_decoder_desc;
+
+typedef struct nc_decoder nc_decoder;
+int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc, nc_decoder **out);
+int32_t neura_cuda_decoder_step(nc_context *ctx, void *stream, nc_decoder *decoder);
+int32_t neura_cuda_decoder_free(nc_context *ctx, nc_decoder *decoder);
+
 /* Streams for callers without a CUDA runtime of their own (Queue, crates/neura-gpu/src/context.rs:287). */
 int32_t neura_cuda_stream_create(nc_context *ctx, void **out_stream);
 int32_t neura_cuda_stream_destroy(nc_context *ctx, void *stream);

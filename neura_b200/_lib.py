@@ -20,6 +20,7 @@ SYMBOLS = [
     "neura_cuda_advance", "neura_cuda_stage_window", "neura_cuda_argmax_segments", "neura_cuda_sealed_pair_bytes",
     "neura_cuda_weight_seal_pair", "neura_cuda_linear_bf16", "neura_cuda_comm_create",
     "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce", "neura_cuda_reserve_decoder",
+    "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free",
 ]
 
 
@@ -40,6 +41,26 @@ class NcStep(ctypes.Structure):
         ("operand_dev", ctypes.c_void_p),
         ("row_stride", ctypes.c_int64),
         ("col_stride", ctypes.c_int64),
+    ]
+
+
+class NcDecoderLayer(ctypes.Structure):
+    _fields_ = [
+        ("qkv", NcWeight), ("attn_output", NcWeight), ("gate_up", NcWeight), ("down", NcWeight),
+        ("attn_norm_dev", ctypes.c_void_p), ("ffn_norm_dev", ctypes.c_void_p),
+        ("keys_dev", ctypes.c_void_p), ("values_dev", ctypes.c_void_p),
+    ]
+
+
+class NcDecoderDesc(ctypes.Structure):
+    _fields_ = [
+        ("layers", ctypes.c_uint32), ("hidden", ctypes.c_uint32), ("heads", ctypes.c_uint32),
+        ("key_heads", ctypes.c_uint32), ("head_width", ctypes.c_uint32), ("feed_forward", ctypes.c_uint32),
+        ("vocab", ctypes.c_uint32), ("batch", ctypes.c_uint32), ("capacity", ctypes.c_uint32),
+        ("floor", ctypes.c_float), ("rope_base", ctypes.c_float), ("scale", ctypes.c_float),
+        ("embedding", NcWeight), ("head", NcWeight), ("output_norm_dev", ctypes.c_void_p),
+        ("layer", ctypes.POINTER(NcDecoderLayer)),
+        ("tokens_dev", ctypes.c_void_p), ("position_dev", ctypes.c_void_p), ("logits_dev", ctypes.c_void_p),
     ]
 
 
@@ -74,6 +95,9 @@ def load() -> ctypes.CDLL:
         "neura_cuda_sync": (i32, [p, p]),
         "neura_cuda_reserve": (i32, [p, u32, u32, u32]),
         "neura_cuda_reserve_decoder": (i32, [p, u32, u32, u32, u32, u32]),
+        "neura_cuda_decoder_compile": (i32, [p, ctypes.POINTER(NcDecoderDesc), pp]),
+        "neura_cuda_decoder_step": (i32, [p, p, p]),
+        "neura_cuda_decoder_free": (i32, [p, p]),
         "neura_cuda_weight_seal": (i32, [p, p, u32, u32, u32, p, p]),
         "neura_cuda_dequant": (i32, [p, p, ctypes.POINTER(NcWeight), p]),
         "neura_cuda_quantize": (i32, [p, p, u32, p, u64, p]),

@@ -69,8 +69,9 @@ __device__ __forceinline__ float chained(const Chain &chain, uint64_t row, uint6
     float result = carried;
     for (uint32_t s = 0; s < chain.n; ++s) {
         const nc_step &step = chain.step[s];
+        // read through L2: in a persistent kernel the operand may have been rewritten by another SM
         float operand = step.operand_dev
-            ? step.operand_dev[(int64_t)row * step.row_stride + (int64_t)col * step.col_stride]
+            ? __ldcg(step.operand_dev + ((int64_t)row * step.row_stride + (int64_t)col * step.col_stride))
             : 0.0f;
         result = step.swapped ? op_apply(step.op, operand, result) : op_apply(step.op, result, operand);
     }

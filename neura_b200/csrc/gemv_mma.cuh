@@ -364,6 +364,7 @@ struct GemvWarp {
     uint32_t warp, units, steps;
     uint32_t tile, blk, first_blk, done;
     float acc[2][NT][4];
+    uint32_t base = 0;   // fills of this warp's ring before this product (a persistent kernel runs many on one ring)
 
     // Unit J of the stage at `buf`.
     template <int J>
@@ -387,7 +388,7 @@ struct GemvWarp {
     // One stage: wait for its bytes, multiply, finish tiles that end in it, refill it.
     // Returns false when the bounded wait ran out.
     __device__ __forceinline__ bool run(uint32_t step, const StageFrags<Q4K, NT> &f) {
-        const uint32_t stage = step % STAGES, parity = (step / STAGES) & 1u;
+        const uint32_t stage = (base + step) % STAGES, parity = ((base + step) / STAGES) & 1u;
         if (!mbar_wait(bars + stage * 8, parity)) return false;
         const uint32_t buf = ring + stage * kStage;
         unit<0>(buf, f);

@@ -1,0 +1,675 @@
+// One persistent kernel for a whole decode step.
+//
+// The reference runs a step as one device "megakernel" that walks a list of task records
+// (crates/neura-kernel/src/substrate.rs, crates/neura-runtime/src/runtime.rs:833-880).  This is the
+// same idea for the decoder path on B200: one CTA per SM, launched cooperatively so that all of them
+// are resident, walks a table of phases (embedding, products, attention, staging, argmax) and meets at
+// a grid-wide barrier between phases.  What it buys over one launch per phase:
+//   * no launch, fill and drain per phase: a phase boundary costs one barrier (about a microsecond);
+//   * the weight stream never stops: before a warp arrives at a barrier it has already issued the
+//     first copies of its next product, whose weights depend on nothing;
+//   * rms_norm and the activation staging fold into the products: every CTA digitises the activation
+//     row it multiplies into its own shared memory (the row is a few KB; the weights are the traffic).
+// The products are the streaming product of gemv_mma.cuh (same units, same split, same ring).
+//
+// Every wait is bounded (the ring's copies and the grid barrier, by %globaltimer); a CTA whose wait
+// runs out raises the status word, stops taking work and leaves, and so do the others at their next
+// barrier.
+#pragma once
+#include "common.cuh"
+#include "decoder_ops.cuh"
+#include "gemv_mma.cuh"
+#include "layout.cuh"
+#include "prep.cuh"
+
+namespace nc {
+
+constexpr int kMkWarps = 16;
+constexpr int kMkThreads = kMkWarps * 32;
+constexpr uint32_t kMkRing = kMkWarps * 2 * kQ4kStage;        // two stages a warp (a Q8_0 stage is shorter)
+constexpr uint32_t kMkBars = kMkWarps * 2 * 8;
+constexpr uint32_t kMkPatch = kMkWarps * 32 * 9 * sizeof(float);
+constexpr uint32_t kMkDigits = 62 * 1024;                     // the staged activations of a self-staging product
+constexpr uint32_t kMkSmem = kMkRing + kMkBars + kMkPatch + kMkDigits;
+constexpr uint32_t kMkTile = 64;                              // cached positions one attention item takes
+constexpr uint32_t kMkNone = 0xffffffffu;
+
+enum : uint32_t { MK_EMBED = 1, MK_GEMV = 2, MK_ATTEND = 3, MK_STAGE = 4, MK_ARGMAX = 5 };
+constexpr uint32_t MK_SELF = 1u;   // the product digitises its f32 input itself, into shared memory
+constexpr uint32_t MK_NORM = 2u;   // ... after rms_norm with the phase's weight
+
+struct MkPhase {
+    uint32_t kind, flags;
+    uint32_t prefetch;       // the product whose first copies are issued when this phase ends, or kMkNone
+    uint32_t k;              // columns of the input rows
+    GemvParams g;            // MK_GEMV (dig, cs, sums: the staged input in global memory when not MK_SELF)
+    const float *x;          // f32 input rows (MK_GEMV | MK_SELF, MK_STAGE, MK_ARGMAX)
+    uint64_t x_stride;
+    const float *norm;       // rms_norm weight [k] (MK_NORM)
+    float *keys, *values;    // MK_ATTEND: this layer's cache
+    WeightView table;        // MK_EMBED
+    float *out;              // MK_EMBED: rows of `out_stride`
+    uint64_t out_stride;
+    uint32_t lo, hi;         // MK_STAGE: the input is elements [lo, hi) of K, zero elsewhere
+};
+
+struct MkParams {
+    const MkPhase *phases;
+    uint32_t nphases;
+    unsigned int *barrier;       // zero at launch
+    unsigned int *status;
+    uint32_t *tokens, *position; // [rows]
+    uint32_t rows, granule;      // sequences; 256 (Q4_K) or 32 (Q8_0)
+    // attention
+    const float *qkv;            // [rows][qkv_stride]: q | k | v of this step
+    uint64_t qkv_stride;
+    float *attended;             // [rows][attended_stride]
+    uint64_t attended_stride;
+    float *attend_partial;       // [rows][heads][max_splits][width + 2]
+    unsigned int *attend_counters;  // [rows][key_heads], zero between launches
+    uint32_t heads, key_heads, width, capacity, max_splits;
+    float scale, rope_base, floor;
+    // activations staged in global memory (MK_STAGE phases write, products without MK_SELF read)
+    int8_t *dig;
+    float *cs;
+    uint32_t *sums;
+    // argmax
+    float *slice_value;          // [rows][gridDim.x]
+    uint32_t *slice_index;
+    unsigned int *argmax_counters;  // [rows], zero between launches
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Grid-wide barrier number `epoch` (1, 2, ...) of this launch.  The kernel is launched cooperatively,
+// so every CTA is resident and will arrive; the wait is bounded all the same.  Returns false once this
+// CTA has given up (now or earlier): the caller stops taking work.
+__device__ __forceinline__ bool mk_barrier(const MkParams &p, uint32_t epoch, volatile uint32_t *aborted) {
+    __syncthreads();
+    if (threadIdx.x == 0 && !*aborted) {
+        __threadfence();
+        atomicAdd(p.barrier, 1u);
+        const unsigned int target = epoch * gridDim.x;
+        if (ld_acquire_gpu(p.barrier) < target) {
+            const unsigned long long start = global_nanos();
+            for (;;) {
+                bool met = false;
+#pragma unroll 1
+                for (int tries = 0; tries < 32 && !met; ++tries) met = ld_acquire_gpu(p.barrier) >= target;
+                if (met) break;
+                if (global_nanos() - start > kWaitNanos) {
+                    *aborted = 1u;
+                    atomicOr(p.status, 2u);
+                    break;
+                }
+            }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    return *aborted == 0u;
+}
+
+// ---- activation fragments from shared memory (self-staged) or from global memory (through L2) -------
+struct MkFrags {
+    const uint8_t *dig;
+    const float *cs;
+    const uint8_t *sums;
+    uint32_t ncols;
+};
+
+template <bool SMEM, typename T>
+__device__ __forceinline__ T mk_ld(const T *p) {
+    if constexpr (SMEM) return *p;
+    else return __ldcg(p);
+}
+
+// load_frags of gemv_mma.cuh for one 8-column MMA tile, reading through `mk_ld`.
+template <bool Q4K, bool SMEM>
+__device__ __forceinline__ void mk_load_frags(StageFrags<Q4K, 1> &f, const MkFrags &s, uint32_t upt, uint32_t blk,
+                                              uint32_t have) {
+    const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int j = 0; j < StageFrags<Q4K, 1>::kUnits; ++j) {
+        const uint32_t col = 2 * t;
+        f.c[j][0][0] = col < s.ncols ? mk_ld<SMEM>(s.cs + blk * s.ncols + col) : 0.0f;
+        f.c[j][0][1] = col + 1 < s.ncols ? mk_ld<SMEM>(s.cs + blk * s.ncols + col + 1) : 0.0f;
+        const bool live = g < s.ncols;
+        if constexpr (Q4K) {
+            const uint32_t entry = (blk * s.ncols + g) * 4 + t;
+            const uint4 *from = reinterpret_cast<const uint4 *>(s.dig) + entry * 4u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f.wide[0][i] = live ? mk_ld<SMEM>(from + i) : make_uint4(0u, 0u, 0u, 0u);
+            f.sums[0] = live ? mk_ld<SMEM>(reinterpret_cast<const uint4 *>(s.sums) + entry) : make_uint4(0u, 0u, 0u, 0u);
+        } else {
+            f.narrow[j][0] = live ? mk_ld<SMEM>(reinterpret_cast<const uint2 *>(s.dig + (blk * s.ncols + g) * 32u + t * 8u))
+                                  : make_uint2(0u, 0u);
+        }
+        if ((uint32_t)(j + 1) < have && ++blk == upt) blk = 0;
+    }
+}
+
+// Where the three tables of a staged input of `k` columns sit inside one buffer.
+struct MkStaged {
+    int8_t *dig;
+    uint32_t *sums;
+    float *cs;
+};
+__device__ __forceinline__ MkStaged mk_staged_at(uint8_t *base, uint32_t k, uint32_t ncols, bool q4k) {
+    const uint32_t chunks = (k + 255) / 256;
+    MkStaged s;
+    s.dig = reinterpret_cast<int8_t *>(base);
+    s.sums = reinterpret_cast<uint32_t *>(base + (size_t)chunks * ncols * 256);
+    s.cs = reinterpret_cast<float *>(base + (size_t)chunks * ncols * (q4k ? 320 : 256));
+    return s;
+}
+
+// Every CTA digitises the whole input of the product it is about to run (rows of ph.k <= 8192 columns)
+// into its own shared memory, after rms_norm when the phase asks for it: what rms_norm_stage_kernel and
+// prep_kernel do for the one-launch-per-step path.  Warp w takes chunks w and w + 16 of every row.
+__device__ __forceinline__ void mk_self_stage(const MkParams &p, const MkPhase &ph, uint8_t *digits, float *reduce) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t chunks = (ph.k + 255) / 256;
+    const MkStaged at = mk_staged_at(digits, ph.k, ph.g.ncols, p.granule == 256);
+    PrepParams sp;
+    sp.x = ph.x;
+    sp.x_stride = ph.x_stride;
+    sp.dig = at.dig;
+    sp.cs = at.cs;
+    sp.sums = at.sums;
+    sp.rows = p.rows;
+    sp.k = ph.k;
+    sp.ncols = ph.g.ncols;
+    sp.granule = p.granule;
+    sp.vector = 1;
+    sp.lo = 0;
+    sp.hi = ph.k;
+    for (uint32_t row = 0; row < p.rows; ++row) {
+        float v[2][8];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t chunk = warp + i * kMkWarps, from = chunk * 256 + lane * 8;
+            load_chunk(sp, row, from, chunk < chunks && from < ph.k, v[i]);
+        }
+        float scale = 1.0f;
+        if (ph.flags & MK_NORM) {
+            float square = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) square = fmaf(v[i][j], v[i][j], square);
+            for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+            __syncthreads();   // the row before has been read out of `reduce`
+            if (lane == 0) reduce[warp] = square;
+            __syncthreads();
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kMkWarps; ++w) total += reduce[w];
+            scale = 1.0f / sqrtf(total / (float)ph.k + p.floor);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t chunk = warp + i * kMkWarps, from = chunk * 256 + lane * 8;
+            if (chunk >= chunks) continue;   // (the whole warp skips)
+            const bool live = from < ph.k;
+            if (live && (ph.flags & MK_NORM)) {
+                const float4 a = __ldg(reinterpret_cast<const float4 *>(ph.norm + from));
+                const float4 c = __ldg(reinterpret_cast<const float4 *>(ph.norm + from + 4));
+                const float gain[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * scale * gain[j];
+            }
+            stage_chunk(sp, row, chunk, v[i], live);
+        }
+    }
+    __syncthreads();
+}
+
+
+// ---- products ----------------------------------------------------------------------------------------
+// A warp's ring as it lives across the phases of one launch.
+struct MkRing {
+    uint32_t ring, bars;     // shared-memory addresses of this warp's two stages and their barriers
+    uint32_t fills;          // stages filled and consumed so far (their number fixes stage and parity)
+    uint32_t ahead_phase;    // the product whose first `ahead` stages are already on their way
+    uint32_t ahead;
+};
+
+// This warp's run of units in a product.
+struct MkRun {
+    const uint8_t *src;
+    uint64_t bytes;
+    uint32_t u0, units, steps;
+};
+template <bool Q4K>
+__device__ __forceinline__ MkRun mk_run_of(const uint8_t *w, uint32_t nwarps, uint32_t q, uint32_t r, uint32_t warp) {
+    constexpr uint32_t kUnit = Q4K ? kQ4kStage : 2 * kQ8Unit;
+    constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;
+    MkRun run;
+    run.u0 = warp * q + min(warp, r);
+    run.units = warp < nwarps ? q + (warp < r ? 1u : 0u) : 0u;
+    run.steps = (run.units + kGroup - 1) / kGroup;
+    run.src = w + (uint64_t)run.u0 * kUnit;
+    run.bytes = (uint64_t)run.units * kUnit;
+    return run;
+}
+
+// Issues fills [from, upto) of a run (lane 0 of the warp calls).
+template <bool Q4K>
+__device__ __forceinline__ void mk_issue(const MkRing &rg, const MkRun &run, uint32_t from, uint32_t upto) {
+    constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
+    // the ring may have been written by ordinary stores (the attention phase borrows it)
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (uint32_t i = from; i < upto; ++i) {
+        const uint32_t stage = (rg.fills + i) & 1u;
+        const uint64_t at = (uint64_t)i * kStage;
+        const uint32_t len = (uint32_t)min((uint64_t)kStage, run.bytes - at);
+        mbar_expect(rg.bars + stage * 8, len);
+        bulk_load(rg.ring + stage * kStage, run.src + at, len, rg.bars + stage * 8);
+    }
+}
+
+// Before a barrier: start the copies of the next product, whose weights depend on nothing.
+template <bool Q4K>
+__device__ __forceinline__ void mk_prefetch(const MkParams &p, uint32_t next, MkRing &rg) {
+    if (next == kMkNone || rg.ahead_phase == next) return;   // (a phase before this one may have started them)
+    const GemvParams &g = p.phases[next].g;
+    const uint32_t warp = blockIdx.x * kMkWarps + (threadIdx.x >> 5);
+    const MkRun run = mk_run_of<Q4K>(g.w, g.nwarps, g.q, g.r, warp);
+    rg.ahead_phase = next;
+    rg.ahead = min(run.steps, 2u);
+    if ((threadIdx.x & 31) == 0) mk_issue<Q4K>(rg, run, 0, rg.ahead);
+    __syncwarp();
+}
+
+template <bool Q4K, bool SMEM>
+__device__ __forceinline__ bool mk_stream(const GemvParams &g, const MkFrags &frags, MkRing &rg, const MkRun &run,
+                                          float *patch, uint32_t warp) {
+    constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;
+    GemvWarp<Q4K, 1, 2> w{g};
+    w.ring = rg.ring;
+    w.bars = rg.bars;
+    w.patch = patch;
+    w.src = run.src;
+    w.bytes = run.bytes;
+    w.warp = warp;
+    w.units = run.units;
+    w.steps = run.steps;
+    w.base = rg.fills;
+    w.tile = run.u0 / g.upt;
+    w.blk = run.u0 % g.upt;
+    w.first_blk = w.blk;
+    w.done = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) w.acc[h][0][0] = w.acc[h][0][1] = w.acc[h][0][2] = w.acc[h][0][3] = 0.0f;
+    StageFrags<Q4K, 1> even, odd;
+    mk_load_frags<Q4K, SMEM>(even, frags, g.upt, w.blk, min(w.units, kGroup));
+    uint32_t failed = kMkNone;
+    for (uint32_t step = 0; step < w.steps; step += 2) {
+        const bool second = step + 1 < w.steps;
+        if (second)
+            mk_load_frags<Q4K, SMEM>(odd, frags, g.upt, w.block_after(w.blk), min(w.units - (step + 1) * kGroup, kGroup));
+        if (!w.run(step, even)) { failed = step; break; }
+        if (second) {
+            if (step + 2 < w.steps)
+                mk_load_frags<Q4K, SMEM>(even, frags, g.upt, w.block_after(w.blk), min(w.units - (step + 2) * kGroup, kGroup));
+            if (!w.run(step + 1, odd)) { failed = step + 1; break; }
+        }
+    }
+    if (failed != kMkNone) {
+        // a copy never landed: give the copies still in flight a bounded time before the memory is reused
+        const uint32_t pending = min(2u, w.steps - failed);
+        for (uint32_t s = 0; s < pending; ++s)
+            mbar_wait(w.bars + ((w.base + failed + s) & 1u) * 8, ((w.base + failed + s) >> 1) & 1u);
+        return false;
+    }
+    rg.fills += run.steps;
+    return true;
+}
+
+template <bool Q4K>
+__device__ __forceinline__ void mk_gemv(const MkParams &p, const MkPhase &ph, uint32_t index, MkRing &rg, uint8_t *digits,
+                                        float *patch, float *reduce, volatile uint32_t *aborted) {
+    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5, warp = blockIdx.x * kMkWarps + wib;
+    const GemvParams &g = ph.g;
+    const MkRun run = mk_run_of<Q4K>(g.w, g.nwarps, g.q, g.r, warp);
+    const uint32_t ahead = rg.ahead_phase == index ? rg.ahead : 0u;
+    if (lane == 0) mk_issue<Q4K>(rg, run, ahead, min(run.steps, 2u));
+    rg.ahead_phase = kMkNone;
+    __syncwarp();
+    MkFrags frags;
+    frags.ncols = g.ncols;
+    bool ok = true;
+    if (ph.flags & MK_SELF) {
+        mk_self_stage(p, ph, digits, reduce);
+        const MkStaged at = mk_staged_at(digits, ph.k, g.ncols, Q4K);
+        frags.dig = reinterpret_cast<const uint8_t *>(at.dig);
+        frags.cs = at.cs;
+        frags.sums = reinterpret_cast<const uint8_t *>(at.sums);
+        if (run.units) ok = mk_stream<Q4K, true>(g, frags, rg, run, patch, warp);
+    } else {
+        frags.dig = g.dig;
+        frags.cs = g.cs;
+        frags.sums = g.sums;
+        if (run.units) ok = mk_stream<Q4K, false>(g, frags, rg, run, patch, warp);
+    }
+    if (!ok && lane == 0) {
+        atomicOr(p.status, 1u);
+        *aborted = 1u;
+    }
+}
+
+
+// ---- attention -----------------------------------------------------------------------------------------
+// Half-rotation RoPE of one channel pair (crates/neura-kernel/src/task/rope.rs:48-122), out of line: the
+// slow paths of powf, cosf and sinf want a stack frame the streaming loops should not carry.
+__device__ __noinline__ float2 mk_rope_pair(float low, float high, uint32_t position, uint32_t channel, uint32_t width,
+                                            float base) {
+    const float angle = (float)position * powf(base, -2.0f * (float)channel / (float)width);
+    const float cosine = cosf(angle), sine = sinf(angle);
+    return make_float2(low * cosine - high * sine, high * cosine + low * sine);
+}
+
+// rope_cache_kernel and attend_kernel of decoder_ops.cuh as one phase.  An item is (sequence, key head,
+// split of kMkTile cached positions); items are dealt round-robin to the CTAs.  Every item turns the
+// query heads of its key head itself; the item whose split holds the new position turns the new key,
+// puts it and the new value into its tile and into the cache.  Splits leave (largest logit, sum of
+// exponentials, weighted values) per query head; the last split of a (sequence, key head) to arrive
+// merges them in split order.  `shared` is the ring, idle during this phase.
+template <uint32_t WIDTH>
+__device__ __forceinline__ void mk_attend_item(const MkParams &p, const MkPhase &ph, float *shared, uint32_t *arrived,
+                                               uint32_t b, uint32_t kh, uint32_t split, uint32_t splits, uint32_t position,
+                                               uint32_t count) {
+    constexpr uint32_t TILE = kMkTile, KROW = WIDTH + 4, HALF = WIDTH / 2;
+    const uint32_t group = p.heads / p.key_heads;
+    float *ks = shared;                                   // [TILE][KROW]
+    float *vs = ks + TILE * KROW;                         // [TILE][WIDTH]
+    float *qs = vs + TILE * WIDTH;                        // [group][WIDTH]
+    float *logits = qs + kAttendMaxGroup * WIDTH;         // [group][kAttendMaxChunk]
+    float *stats = logits + kAttendMaxGroup * kAttendMaxChunk;  // [group][2]
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const uint32_t first = split * TILE, last = min(first + TILE, count), held = last - first;
+    const bool fresh = position < p.capacity && position >= first && position < last;   // the new row is ours
+    const uint32_t fresh_row = position - first;
+    const uint64_t slot0 = ((uint64_t)b * p.key_heads + kh) * p.capacity;
+    const float *k = ph.keys + (slot0 + first) * WIDTH;
+    const float *v = ph.values + (slot0 + first) * WIDTH;
+    for (uint32_t i = threadIdx.x; i < held * (WIDTH / 4); i += blockDim.x) {
+        const uint32_t row = i / (WIDTH / 4), quad = i % (WIDTH / 4);
+        if (fresh && row == fresh_row) continue;
+        copy16_async(ks + row * KROW + quad * 4, k + i * 4);
+        copy16_async(vs + i * 4, v + i * 4);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const float *row_qkv = p.qkv + (uint64_t)b * p.qkv_stride;
+    for (uint32_t i = threadIdx.x; i < group * HALF; i += blockDim.x) {
+        const uint32_t g = i / HALF, c = i % HALF;
+        const float *q = row_qkv + (uint64_t)(kh * group + g) * WIDTH;
+        const float2 turned = mk_rope_pair(__ldcg(q + c), __ldcg(q + c + HALF), position, c, WIDTH, p.rope_base);
+        qs[g * WIDTH + c] = turned.x;
+        qs[g * WIDTH + c + HALF] = turned.y;
+    }
+    if (fresh) {
+        const float *nk = row_qkv + (uint64_t)(p.heads + kh) * WIDTH;
+        const float *nv = row_qkv + (uint64_t)(p.heads + p.key_heads + kh) * WIDTH;
+        float *cache_k = ph.keys + (slot0 + position) * WIDTH, *cache_v = ph.values + (slot0 + position) * WIDTH;
+        // (the last threads of the CTA, so that they do not queue behind the query turns)
+        for (uint32_t i = blockDim.x - 1 - threadIdx.x; i < HALF; i += blockDim.x) {
+            const float2 turned = mk_rope_pair(__ldcg(nk + i), __ldcg(nk + i + HALF), position, i, WIDTH, p.rope_base);
+            ks[fresh_row * KROW + i] = turned.x;
+            ks[fresh_row * KROW + i + HALF] = turned.y;
+            cache_k[i] = turned.x;
+            cache_k[i + HALF] = turned.y;
+        }
+        for (uint32_t i = blockDim.x - 1 - threadIdx.x; i < WIDTH; i += blockDim.x) {
+            const float value = __ldcg(nv + i);
+            vs[fresh_row * WIDTH + i] = value;
+            cache_v[i] = value;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    for (uint32_t item = threadIdx.x; item < group * held; item += blockDim.x) {
+        const uint32_t g = item / held, pos = item % held;
+        const float4 *kr = reinterpret_cast<const float4 *>(ks + pos * KROW);
+        const float4 *qr = reinterpret_cast<const float4 *>(qs + g * WIDTH);
+        float t0 = 0.0f, t1 = 0.0f, t2 = 0.0f, t3 = 0.0f;
+#pragma unroll 8
+        for (uint32_t c = 0; c < WIDTH / 4; ++c) {
+            const float4 a = kr[c], q4 = qr[c];
+            t0 = fmaf(a.x, q4.x, t0);
+            t1 = fmaf(a.y, q4.y, t1);
+            t2 = fmaf(a.z, q4.z, t2);
+            t3 = fmaf(a.w, q4.w, t3);
+        }
+        logits[g * kAttendMaxChunk + pos] = ((t0 + t1) + (t2 + t3)) * p.scale;
+    }
+    __syncthreads();
+    for (uint32_t g = warp; g < group; g += warps) {
+        float largest = -INFINITY;
+        for (uint32_t i = lane; i < held; i += 32) largest = fmaxf(largest, logits[g * kAttendMaxChunk + i]);
+        for (int o = 16; o; o >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+        float sum = 0.0f;
+        for (uint32_t i = lane; i < held; i += 32) {
+            const float e = expf(logits[g * kAttendMaxChunk + i] - largest);
+            logits[g * kAttendMaxChunk + i] = e;
+            sum += e;
+        }
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) { stats[g * 2] = largest; stats[g * 2 + 1] = sum; }
+    }
+    __syncthreads();
+    float *mine = p.attend_partial + ((uint64_t)b * p.heads + kh * group) * p.max_splits * (WIDTH + 2);
+    // weighted values: one thread per (query head, channel)
+    for (uint32_t item = threadIdx.x; item < group * WIDTH; item += blockDim.x) {
+        const uint32_t g = item / WIDTH, d = item % WIDTH;
+        float acc = 0.0f;
+        for (uint32_t pos = 0; pos < held; ++pos) acc = fmaf(logits[g * kAttendMaxChunk + pos], vs[pos * WIDTH + d], acc);
+        __stcg(mine + ((uint64_t)g * p.max_splits + split) * (WIDTH + 2) + d, acc);
+    }
+    if (threadIdx.x < group * 2) {
+        const uint32_t g = threadIdx.x / 2, which = threadIdx.x % 2;
+        __stcg(mine + ((uint64_t)g * p.max_splits + split) * (WIDTH + 2) + WIDTH + which, stats[g * 2 + which]);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        *arrived = atomicAdd(p.attend_counters + b * p.key_heads + kh, 1u);
+        __threadfence();
+    }
+    __syncthreads();
+    if (*arrived == splits - 1) {
+        float *factor = logits;   // [group][splits]
+        float *sums = ks;         // [group][splits]
+        float *totals = stats;    // [group]
+        for (uint32_t i = threadIdx.x; i < group * splits; i += blockDim.x) {
+            const float *from = mine + ((uint64_t)(i / splits) * p.max_splits + i % splits) * (WIDTH + 2) + WIDTH;
+            factor[(i / splits) * kAttendMaxChunk + i % splits] = __ldcg(from);
+            sums[(i / splits) * kAttendMaxChunk + i % splits] = __ldcg(from + 1);
+        }
+        __syncthreads();
+        for (uint32_t g = warp; g < group; g += warps) {
+            float largest = -INFINITY;
+            for (uint32_t s = lane; s < splits; s += 32) largest = fmaxf(largest, factor[g * kAttendMaxChunk + s]);
+            for (int o = 16; o; o >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+            float total = 0.0f;
+            for (uint32_t s = lane; s < splits; s += 32) {
+                const float m = factor[g * kAttendMaxChunk + s];
+                const float f = m == -INFINITY ? 0.0f : expf(m - largest);
+                factor[g * kAttendMaxChunk + s] = f;
+                total = fmaf(sums[g * kAttendMaxChunk + s], f, total);
+            }
+            for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+            if (lane == 0) totals[g] = total;
+        }
+        __syncthreads();
+        for (uint32_t item = threadIdx.x; item < group * WIDTH; item += blockDim.x) {
+            const uint32_t g = item / WIDTH, d = item % WIDTH;
+            float acc = 0.0f;
+            for (uint32_t s = 0; s < splits; ++s)
+                acc = fmaf(__ldcg(mine + ((uint64_t)g * p.max_splits + s) * (WIDTH + 2) + d), factor[g * kAttendMaxChunk + s], acc);
+            p.attended[(uint64_t)b * p.attended_stride + (uint64_t)(kh * group + g) * WIDTH + d] = acc / totals[g];
+        }
+        if (threadIdx.x == 0) p.attend_counters[b * p.key_heads + kh] = 0u;
+    }
+    __syncthreads();   // the tile is free for the CTA's next item
+}
+
+template <uint32_t WIDTH>
+__device__ __forceinline__ void mk_attend(const MkParams &p, const MkPhase &ph, float *shared, uint32_t *arrived) {
+    uint32_t dealt = 0;   // items of the sequences before this one
+    for (uint32_t b = 0; b < p.rows; ++b) {
+        const uint32_t position = __ldcg(p.position + b);
+        const uint32_t count = min(position + 1, p.capacity);
+        const uint32_t splits = (count + kMkTile - 1) / kMkTile;
+        const uint32_t items = p.key_heads * splits;
+        const uint32_t skip = (blockIdx.x + gridDim.x - dealt % gridDim.x) % gridDim.x;
+        for (uint32_t i = skip; i < items; i += gridDim.x)
+            mk_attend_item<WIDTH>(p, ph, shared, arrived, b, i / splits, i % splits, splits, position, count);
+        dealt += items;
+    }
+}
+
+
+// ---- the small phases -------------------------------------------------------------------------------------
+// prep_kernel as a phase: the rows of ph.x digitised into the global staging tables, one warp per
+// (row, 256 columns).  The input is elements [lo, hi) of the K axis (a tensor-parallel rank's window).
+__device__ __forceinline__ void mk_stage(const MkParams &p, const MkPhase &ph) {
+    PrepParams sp;
+    sp.x = ph.x;
+    sp.x_stride = ph.x_stride;
+    sp.dig = p.dig;
+    sp.cs = p.cs;
+    sp.sums = p.sums;
+    sp.rows = p.rows;
+    sp.k = ph.k;
+    sp.ncols = ph.g.ncols;
+    sp.granule = p.granule;
+    sp.vector = 1;
+    sp.lo = ph.lo;
+    sp.hi = ph.hi;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t chunks = (ph.k + 255) / 256, total = p.rows * chunks;
+    for (uint32_t w = blockIdx.x * kMkWarps + (threadIdx.x >> 5); w < total; w += gridDim.x * kMkWarps) {
+        const uint32_t row = w / chunks, chunk = w % chunks, from = chunk * 256 + lane * 8;
+        const bool live = from < ph.k;
+        float v[8];
+        load_chunk(sp, row, from, live, v);
+        stage_chunk(sp, row, chunk, v, live);
+    }
+}
+
+// embed_kernel as a phase.
+__device__ __forceinline__ void mk_embed(const MkParams &p, const MkPhase &ph) {
+    const uint32_t total = p.rows * ph.table.k;
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const uint32_t r = idx / ph.table.k, at = idx % ph.table.k;
+        const uint32_t row = min(__ldcg(p.tokens + r), ph.table.n - 1);
+        ph.out[(uint64_t)r * ph.out_stride + at] = dequant_at(ph.table, row, at);
+    }
+}
+
+// argmax_kernel and advance_kernel as the last phase: every CTA takes a slice of every row, the last CTA
+// to arrive at a row picks among the slices (lowest index on ties), writes the token and moves the cursor.
+__device__ __forceinline__ void mk_argmax(const MkParams &p, const MkPhase &ph, float *best_value, uint32_t *best_index,
+                                          uint32_t *arrived) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t per = (ph.k + gridDim.x - 1) / gridDim.x;
+    const uint32_t first = min(blockIdx.x * per, ph.k), last = min(first + per, ph.k);
+    for (uint32_t row = 0; row < p.rows; ++row) {
+        const float *x = ph.x + (uint64_t)row * ph.x_stride;
+        float value = -INFINITY;
+        uint32_t index = 0xffffffffu;
+        for (uint32_t c = first + threadIdx.x; c < last; c += blockDim.x) argmax_take(value, index, __ldcg(x + c), c);
+        for (int o = 16; o; o >>= 1)
+            argmax_take(value, index, __shfl_xor_sync(0xffffffffu, value, o), __shfl_xor_sync(0xffffffffu, index, o));
+        __syncthreads();   // the row before has been read out of the tables
+        if (lane == 0) { best_value[warp] = value; best_index[warp] = index; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) argmax_take(value, index, best_value[w], best_index[w]);
+            __stcg(p.slice_value + row * gridDim.x + blockIdx.x, value);
+            __stcg(p.slice_index + row * gridDim.x + blockIdx.x, index);
+            __threadfence();
+            *arrived = atomicAdd(p.argmax_counters + row, 1u);
+            __threadfence();
+        }
+        __syncthreads();
+        if (*arrived == gridDim.x - 1 && warp == 0) {
+            value = -INFINITY;
+            index = 0xffffffffu;
+            for (uint32_t s = lane; s < gridDim.x; s += 32)
+                argmax_take(value, index, __ldcg(p.slice_value + row * gridDim.x + s), __ldcg(p.slice_index + row * gridDim.x + s));
+            for (int o = 16; o; o >>= 1)
+                argmax_take(value, index, __shfl_xor_sync(0xffffffffu, value, o), __shfl_xor_sync(0xffffffffu, index, o));
+            if (lane == 0) {
+                p.tokens[row] = index == 0xffffffffu ? 0u : index;
+                p.position[row] = __ldcg(p.position + row) + 1u;
+                p.argmax_counters[row] = 0u;
+            }
+        }
+    }
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------------------
+template <bool Q4K>
+__global__ void __launch_bounds__(kMkThreads, 1) decode_megakernel(const __grid_constant__ MkParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(16) MkPhase phase;
+    __shared__ float reduce[kMkWarps];
+    __shared__ uint32_t best_index[kMkWarps];
+    __shared__ uint32_t arrived;
+    __shared__ volatile uint32_t aborted;
+    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
+    MkRing rg;
+    rg.ring = smem_addr(smem) + wib * 2 * kStage;
+    rg.bars = smem_addr(smem) + kMkRing + wib * 16;
+    rg.fills = 0;
+    rg.ahead_phase = kMkNone;
+    rg.ahead = 0;
+    float *patch = reinterpret_cast<float *>(smem + kMkRing + kMkBars) + wib * 32 * 9;
+    uint8_t *digits = smem + kMkRing + kMkBars + kMkPatch;
+    if (threadIdx.x == 0) aborted = 0u;
+    if (lane == 0) {
+        mbar_init(rg.bars, 1);
+        mbar_init(rg.bars + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    for (uint32_t index = 0; index < p.nphases; ++index) {
+        {
+            const uint32_t *from = reinterpret_cast<const uint32_t *>(p.phases + index);
+            uint32_t *to = reinterpret_cast<uint32_t *>(&phase);
+            for (uint32_t i = threadIdx.x; i < sizeof(MkPhase) / 4; i += blockDim.x) to[i] = __ldg(from + i);
+        }
+        __syncthreads();
+        if (aborted) break;
+        switch (phase.kind) {
+        case MK_EMBED: mk_embed(p, phase); break;
+        case MK_GEMV: mk_gemv<Q4K>(p, phase, index, rg, digits, patch, reduce, &aborted); break;
+        case MK_ATTEND:
+            if (p.width == 128) mk_attend<128>(p, phase, reinterpret_cast<float *>(smem), &arrived);
+            else mk_attend<64>(p, phase, reinterpret_cast<float *>(smem), &arrived);
+            break;
+        case MK_STAGE: mk_stage(p, phase); break;
+        case MK_ARGMAX: mk_argmax(p, phase, reduce, best_index, &arrived); break;
+        default: break;
+        }
+        if (index + 1 == p.nphases) break;   // nothing follows the last phase
+        __syncthreads();                     // the CTA is done with the ring and with `phase`
+        mk_prefetch<Q4K>(p, phase.prefetch, rg);
+        if (!mk_barrier(p, index + 1, &aborted)) break;
+    }
+    // copies issued ahead of a product that never ran: let them land before the memory is handed back
+    if (rg.ahead_phase != kMkNone) {
+        for (uint32_t s = 0; s < rg.ahead; ++s) mbar_wait(rg.bars + ((rg.fills + s) & 1u) * 8, ((rg.fills + s) >> 1) & 1u);
+    }
+}
+
+}  // namespace nc

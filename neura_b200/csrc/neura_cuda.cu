@@ -3,8 +3,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "allreduce.cuh"
 #include "common.cuh"
@@ -12,6 +14,7 @@
 #include "gemm_tcgen05.cuh"
 #include "gemv_mma.cuh"
 #include "layout.cuh"
+#include "megakernel.cuh"
 #include "prep.cuh"
 #include "quantize.cuh"
 
@@ -1089,6 +1092,315 @@ int32_t neura_cuda_program_free(nc_context *ctx, nc_program *program) {
     if (program->exec) cudaGraphExecDestroy(program->exec);
     if (program->graph) cudaGraphDestroy(program->graph);
     delete program;
+    return 0;
+}
+
+
+// ---- a decode step as one persistent kernel (megakernel.cuh) -----------------------------------------------
+}  // extern "C"
+
+struct nc_decoder {
+    int device = 0;
+    MkParams params = {};
+    bool q4k = false;
+    unsigned int grid = 0;
+    std::vector<void *> owned;   // device blocks freed with the decoder
+};
+
+namespace {
+
+int32_t decoder_alloc(nc_decoder *d, uint64_t bytes, bool zero, void **out) {
+    void *ptr = nullptr;
+    NC_CUDA(cudaMalloc(&ptr, bytes ? bytes : 1));
+    d->owned.push_back(ptr);
+    if (zero) NC_CUDA(cudaMemset(ptr, 0, bytes ? bytes : 1));
+    *out = ptr;
+    return 0;
+}
+
+// The (q, r) split of a product over all the warps of the persistent grid.
+void plan_phase(GemvParams &g, uint32_t element, uint32_t plan_n, uint32_t k, uint64_t warps) {
+    const uint32_t ntiles = (plan_n + kTileRows - 1) / kTileRows;
+    g.upt = k / block_elements(element);
+    const uint64_t units = (uint64_t)ntiles * g.upt;
+    const uint64_t least = element == NC_ELEMENT_Q4K ? 2 : 8;
+    if (warps > units / least) warps = units / least;
+    if (warps < 1) warps = 1;
+    g.nwarps = (uint32_t)warps;
+    g.q = (uint32_t)(units / warps);
+    g.r = (uint32_t)(units % warps);
+    g.maxp = (g.upt + g.q - 1) / g.q + 1;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t neura_cuda_decoder_free(nc_context *ctx, nc_decoder *decoder) {
+    (void)ctx;
+    if (!decoder) return 0;
+    cudaSetDevice(decoder->device);
+    for (void *ptr : decoder->owned) cudaFree(ptr);
+    delete decoder;
+    return 0;
+}
+
+int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc, nc_decoder **out) {
+    if (!ctx || !desc || !out) return refuse(kBadArgument, "compile needs a context, a description and somewhere to put the decoder");
+    *out = nullptr;
+    const nc_decoder_desc &c = *desc;
+    if (!c.layers || !c.layer || !c.tokens_dev || !c.position_dev || !c.logits_dev || !c.output_norm_dev)
+        return refuse(kBadArgument, "a decoder needs its layers, token ids, cursors, logits and output norm");
+    if (c.batch < 1 || c.batch > 2)
+        return refuse(kBadArgument, "the persistent step carries 1 or 2 sequences, not %u", c.batch);
+    if (!c.heads || !c.key_heads || c.heads % c.key_heads || c.heads / c.key_heads > kAttendMaxGroup)
+        return refuse(kBadArgument, "%u query heads do not share %u key heads", c.heads, c.key_heads);
+    if (c.head_width != 64 && c.head_width != 128)
+        return refuse(kBadArgument, "the attention phase is built for heads of width 64 and 128, not %u", c.head_width);
+    if (!c.capacity || c.capacity > kMkTile * kAttendMaxChunk)
+        return refuse(kBadArgument, "a cache of %u slots is more than the %u the attention phase splits", c.capacity,
+                      kMkTile * kAttendMaxChunk);
+    const uint32_t element = c.head.element;
+    const uint32_t per = block_elements(element);
+    if (!per) return refuse(kBadArgument, "element %u is not a block format this path multiplies", element);
+    const uint32_t query_width = c.heads * c.head_width, key_width = c.key_heads * c.head_width;
+    const uint32_t ncols = c.batch * 3;
+    const bool q4k = element == NC_ELEMENT_Q4K;
+    // what a self-staging product keeps in shared memory: rows of at most 8192 columns, digits, sums and scales
+    auto staged_bytes = [&](uint32_t k) { return (uint64_t)((k + 255) / 256) * ncols * (q4k ? 324u : 288u); };
+    auto self_stages = [&](uint32_t k) { return k <= 8192 && k % 8 == 0 && staged_bytes(k) <= kMkDigits; };
+    if (!self_stages(c.hidden) || c.hidden % per)
+        return refuse(kBadArgument, "a hidden width of %u does not fit the persistent step's shared memory", c.hidden);
+    auto fits = [&](const nc_weight &w, uint32_t n, uint32_t k, uint32_t layout, const char *name) -> int32_t {
+        int32_t rc = check_weight(&w);
+        if (rc) return rc;
+        if (w.element != element || w.layout != layout || w.n != n || w.k != k)
+            return refuse(kBadArgument, "%s is [%u, %u] of element %u in layout %u where the decoder wants [%u, %u] of element %u in layout %u",
+                          name, w.n, w.k, w.element, w.layout, n, k, element, layout);
+        return 0;
+    };
+    int32_t rc;
+    if ((rc = fits(c.head, c.vocab, c.hidden, NC_LAYOUT_TILED, "the head"))) return rc;
+    if ((rc = check_weight(&c.embedding))) return rc;
+    if (c.embedding.n != c.vocab || c.embedding.k != c.hidden)
+        return refuse(kBadArgument, "the embedding is [%u, %u] where the decoder wants [%u, %u]", c.embedding.n, c.embedding.k, c.vocab, c.hidden);
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        const nc_decoder_layer &layer = c.layer[l];
+        if ((rc = fits(layer.qkv, query_width + 2 * key_width, c.hidden, NC_LAYOUT_TILED, "a q|k|v projection"))) return rc;
+        if ((rc = fits(layer.attn_output, c.hidden, query_width, NC_LAYOUT_TILED, "an attention output projection"))) return rc;
+        if ((rc = fits(layer.gate_up, c.feed_forward, c.hidden, NC_LAYOUT_TILED_PAIR, "a gate|up pair"))) return rc;
+        if ((rc = fits(layer.down, c.hidden, c.feed_forward, NC_LAYOUT_TILED, "a down projection"))) return rc;
+        if (!layer.attn_norm_dev || !layer.ffn_norm_dev || !layer.keys_dev || !layer.values_dev)
+            return refuse(kBadArgument, "layer %u lacks a norm weight or its cache", l);
+    }
+    NC_CUDA(cudaSetDevice(ctx->device));
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
+    nc_decoder *d = new (std::nothrow) nc_decoder();
+    if (!d) return refuse(kBadState, "out of host memory");
+    d->device = ctx->device;
+    d->q4k = q4k;
+    d->grid = (unsigned int)ctx->sms;
+    const uint64_t warps = (uint64_t)ctx->sms * kMkWarps;
+    auto fail = [&](int32_t code) { neura_cuda_decoder_free(ctx, d); return code; };
+
+    // activations and scratch
+    float *hidden, *qkv, *attended, *held, *partial, *attend_partial, *slice_value, *cs;
+    uint32_t *slice_index, *sums;
+    unsigned int *counters, *attend_counters, *argmax_counters, *barrier;
+    int8_t *dig;
+    const uint32_t qkv_width = query_width + 2 * key_width;
+    const uint32_t max_splits = (c.capacity + kMkTile - 1) / kMkTile;
+    const uint32_t widest = std::max(std::max(c.vocab, 2 * ((c.feed_forward + 15) / 16 * 16)), std::max(c.hidden, qkv_width));
+    const uint32_t ntiles_max = (widest + kTileRows - 1) / kTileRows + 1;
+    const uint32_t longest = std::max(std::max(c.hidden, query_width), c.feed_forward);
+    const uint64_t kpad = ((uint64_t)longest + 255) / 256 * 256;
+#define NC_TRY(call) do { int32_t rc_ = (call); if (rc_) return fail(rc_); } while (0)
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.hidden * 4, true, (void **)&hidden));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * qkv_width * 4, true, (void **)&qkv));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * query_width * 4, true, (void **)&attended));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.feed_forward * 4, true, (void **)&held));
+    NC_TRY(decoder_alloc(d, kpad * ncols, true, (void **)&dig));
+    NC_TRY(decoder_alloc(d, kpad / 32 * ncols * 4, true, (void **)&cs));
+    NC_TRY(decoder_alloc(d, kpad / 256 * ncols * 64, true, (void **)&sums));
+    NC_TRY(decoder_alloc(d, (uint64_t)ntiles_max * sizeof(unsigned int), true, (void **)&counters));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.heads * max_splits * (c.head_width + 2) * 4, true, (void **)&attend_partial));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.key_heads * sizeof(unsigned int), true, (void **)&attend_counters));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * d->grid * 4, true, (void **)&slice_value));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * d->grid * 4, true, (void **)&slice_index));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * sizeof(unsigned int), true, (void **)&argmax_counters));
+    NC_TRY(decoder_alloc(d, 256, true, (void **)&barrier));
+
+    // the phase table
+    std::vector<MkPhase> phases;
+    uint64_t partial_cells = 0;
+    auto blank = [](uint32_t kind) {
+        MkPhase ph;
+        memset(&ph, 0, sizeof ph);
+        ph.kind = kind;
+        ph.prefetch = kMkNone;
+        return ph;
+    };
+    auto product = [&](const nc_weight &w, const float *x, uint64_t x_stride, uint32_t flags, const float *norm,
+                       float *out_rows, uint64_t out_stride, const float *residual) {
+        MkPhase ph = blank(MK_GEMV);
+        ph.flags = flags;
+        ph.k = w.k;
+        ph.x = x;
+        ph.x_stride = x_stride;
+        ph.norm = norm;
+        GemvParams &g = ph.g;
+        const bool pair = w.layout == NC_LAYOUT_TILED_PAIR;
+        const uint32_t plan_n = pair ? (w.n + 15) / 16 * 32 : w.n;
+        g.w = (const uint8_t *)w.data_dev;
+        g.dig = (const uint8_t *)dig;
+        g.cs = cs;
+        g.sums = (const uint8_t *)sums;
+        g.out = out_rows;
+        g.out_stride = out_stride;
+        g.counters = counters;
+        g.status = (unsigned int *)ctx->status.ptr;
+        g.n = w.n;
+        g.rows = c.batch;
+        g.ncols = ncols;
+        g.pair = pair ? 1u : 0u;
+        if (residual) {
+            g.chain.n = 1;
+            g.chain.step[0].op = NC_OP_ADD;
+            g.chain.step[0].swapped = 0;
+            g.chain.step[0].operand_dev = residual;
+            g.chain.step[0].row_stride = (int64_t)out_stride;
+            g.chain.step[0].col_stride = 1;
+        }
+        plan_phase(g, element, plan_n, w.k, warps);
+        const uint64_t ntiles = (plan_n + kTileRows - 1) / kTileRows;
+        partial_cells = std::max(partial_cells, ntiles * g.maxp * c.batch * kTileRows);
+        phases.push_back(ph);
+    };
+    {
+        MkPhase ph = blank(MK_EMBED);
+        ph.table = WeightView{(const uint8_t *)c.embedding.data_dev, c.embedding.element, c.embedding.layout, c.embedding.n, c.embedding.k};
+        ph.out = hidden;
+        ph.out_stride = c.hidden;
+        phases.push_back(ph);
+    }
+    const bool output_self = self_stages(query_width) && query_width % per == 0;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        const nc_decoder_layer &layer = c.layer[l];
+        product(layer.qkv, hidden, c.hidden, MK_SELF | MK_NORM, layer.attn_norm_dev, qkv, qkv_width, nullptr);
+        {
+            MkPhase ph = blank(MK_ATTEND);
+            ph.keys = layer.keys_dev;
+            ph.values = layer.values_dev;
+            phases.push_back(ph);
+        }
+        if (!output_self) {
+            MkPhase ph = blank(MK_STAGE);
+            ph.x = attended;
+            ph.x_stride = query_width;
+            ph.k = query_width;
+            ph.lo = 0;
+            ph.hi = query_width;
+            ph.g.ncols = ncols;
+            phases.push_back(ph);
+        }
+        product(layer.attn_output, attended, query_width, output_self ? MK_SELF : 0u, nullptr, hidden, c.hidden, hidden);
+        product(layer.gate_up, hidden, c.hidden, MK_SELF | MK_NORM, layer.ffn_norm_dev, held, c.feed_forward, nullptr);
+        {
+            MkPhase ph = blank(MK_STAGE);
+            ph.x = held;
+            ph.x_stride = c.feed_forward;
+            ph.k = c.feed_forward;
+            ph.lo = 0;
+            ph.hi = c.feed_forward;
+            ph.g.ncols = ncols;
+            phases.push_back(ph);
+        }
+        product(layer.down, held, c.feed_forward, 0u, nullptr, hidden, c.hidden, hidden);
+    }
+    product(c.head, hidden, c.hidden, MK_SELF | MK_NORM, c.output_norm_dev, c.logits_dev, c.vocab, nullptr);
+    {
+        MkPhase ph = blank(MK_ARGMAX);
+        ph.x = c.logits_dev;
+        ph.x_stride = c.vocab;
+        ph.k = c.vocab;
+        phases.push_back(ph);
+    }
+    // when a phase ends, its warps start the copies of the next product, unless the attention phase
+    // (which borrows the ring) comes first
+    for (size_t i = 0; i < phases.size(); ++i) {
+        for (size_t j = i + 1; j < phases.size(); ++j) {
+            if (phases[j].kind == MK_ATTEND) break;
+            if (phases[j].kind == MK_GEMV) { phases[i].prefetch = (uint32_t)j; break; }
+        }
+    }
+    NC_TRY(decoder_alloc(d, partial_cells * sizeof(float), false, (void **)&partial));
+    for (MkPhase &ph : phases)
+        if (ph.kind == MK_GEMV) ph.g.partial = partial;
+    MkPhase *table = nullptr;
+    NC_TRY(decoder_alloc(d, phases.size() * sizeof(MkPhase), false, (void **)&table));
+    cudaError_t e = cudaMemcpy(table, phases.data(), phases.size() * sizeof(MkPhase), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(cuda_refuse(e, "cudaMemcpy of the phase table"));
+#undef NC_TRY
+
+    MkParams &p = d->params;
+    p.phases = table;
+    p.nphases = (uint32_t)phases.size();
+    p.barrier = barrier;
+    p.status = (unsigned int *)ctx->status.ptr;
+    p.tokens = c.tokens_dev;
+    p.position = c.position_dev;
+    p.rows = c.batch;
+    p.granule = q4k ? 256 : 32;
+    p.qkv = qkv;
+    p.qkv_stride = qkv_width;
+    p.attended = attended;
+    p.attended_stride = query_width;
+    p.attend_partial = attend_partial;
+    p.attend_counters = attend_counters;
+    p.heads = c.heads;
+    p.key_heads = c.key_heads;
+    p.width = c.head_width;
+    p.capacity = c.capacity;
+    p.max_splits = max_splits;
+    p.scale = c.scale;
+    p.rope_base = c.rope_base;
+    p.floor = c.floor;
+    p.dig = dig;
+    p.cs = cs;
+    p.sums = sums;
+    p.slice_value = slice_value;
+    p.slice_index = slice_index;
+    p.argmax_counters = argmax_counters;
+
+    // the kernel must be resident on every SM at once
+    const void *kernel = q4k ? (const void *)decode_megakernel<true> : (const void *)decode_megakernel<false>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMkSmem);
+    if (e != cudaSuccess) return fail(cuda_refuse(e, "cudaFuncSetAttribute"));
+    int resident = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kMkThreads, kMkSmem);
+    if (e != cudaSuccess) return fail(cuda_refuse(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor"));
+    if (resident < 1) return fail(refuse(kBadState, "the persistent step does not fit an SM"));
+    *out = d;
+    return 0;
+}
+
+int32_t neura_cuda_decoder_step(nc_context *ctx, void *stream_, nc_decoder *decoder) {
+    if (!ctx || !decoder) return refuse(kBadArgument, "a step needs a context and a compiled decoder");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    NC_CUDA(cudaMemsetAsync(decoder->params.barrier, 0, sizeof(unsigned int), stream));
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(decoder->grid);
+    config.blockDim = dim3(kMkThreads);
+    config.dynamicSmemBytes = kMkSmem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeCooperative;
+    attribute[0].val.cooperative = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    if (decoder->q4k) NC_CUDA(cudaLaunchKernelEx(&config, decode_megakernel<true>, decoder->params));
+    else NC_CUDA(cudaLaunchKernelEx(&config, decode_megakernel<false>, decoder->params));
+    ctx->launches++;
     return 0;
 }
 

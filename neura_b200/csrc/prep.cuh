@@ -128,14 +128,15 @@ __device__ __forceinline__ void stage_chunk(const PrepParams &p, uint32_t row, u
 __device__ __forceinline__ void load_chunk(const PrepParams &p, uint32_t row, uint32_t at, bool live, float (&v)[8]) {
     if (live && at >= p.lo && at < p.hi) {
         const float *from = p.x + (uint64_t)row * p.x_stride + (at - p.lo);
+        // (through L2: a persistent kernel stages activations another SM wrote moments ago)
         if (p.vector) {
-            const float4 a = *reinterpret_cast<const float4 *>(from);
-            const float4 b = *reinterpret_cast<const float4 *>(from + 4);
+            const float4 a = __ldcg(reinterpret_cast<const float4 *>(from));
+            const float4 b = __ldcg(reinterpret_cast<const float4 *>(from + 4));
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
             v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
         } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = from[i];
+            for (int i = 0; i < 8; ++i) v[i] = __ldcg(from + i);
         }
     } else {
 #pragma unroll

@@ -95,6 +95,7 @@ class LinearStack:
         widest_n = max(c.vocab, c.feed_forward)
         rt.reserve(rows, widest_n, max(c.hidden, c.feed_forward, c.query_width))
         self.program: Optional[int] = None
+        self.compiled = None   # the step as one persistent kernel (compile())
 
     def layer(self, index: int) -> None:
         rt, c, w = self.rt, self.config, self.weights
@@ -173,6 +174,7 @@ class Decoder:
         rt.reserve(batch, max(self.vocab, 2 * self.feed_forward, c.hidden), widest_k)   # 2x: a sealed gate|up pair
         rt.reserve_decoder(batch, self.heads, self.key_heads, c.head_width, capacity)
         self.program: Optional[int] = None
+        self.compiled = None   # the step as one persistent kernel (compile())
         self.scale = 1.0 / float(c.head_width) ** 0.5
 
     def window(self, k: int):
@@ -224,7 +226,45 @@ class Decoder:
                                self.batch * self.vocab, self.tokens)
         rt.advance(self.position, 1)
 
+    def compile(self) -> None:
+        """Runtime::compile for the whole step (crates/neura-runtime/src/runtime.rs:528): lays the step out
+        as the phase table of one persistent kernel (``neura_cuda_decoder_compile``); ``run_token`` then
+        launches that kernel instead of one kernel per operation.  Single GPU, 1 or 2 sequences, the MLP
+        sealed as a gate|up pair."""
+        import ctypes
+
+        from ._lib import NcDecoderDesc, NcDecoderLayer
+        from .runtime import _check
+
+        if self.shard is not None:
+            raise ValueError("the persistent step runs on one GPU")
+        c, w, n = self.config, self.weights, self.norms
+        layers = (NcDecoderLayer * c.layers)()
+        for index in range(c.layers):
+            at = lambda name: f"blk.{index}.{name}.weight"  # noqa: E731
+            if at("ffn_gate_up") not in w:
+                raise ValueError("the persistent step wants the MLP sealed as a gate|up pair")
+            layer = layers[index]
+            layer.qkv, layer.attn_output = w[at("attn_qkv")].record(), w[at("attn_output")].record()
+            layer.gate_up, layer.down = w[at("ffn_gate_up")].record(), w[at("ffn_down")].record()
+            layer.attn_norm_dev, layer.ffn_norm_dev = n[at("attn_norm")].ptr, n[at("ffn_norm")].ptr
+            layer.keys_dev, layer.values_dev = self.keys[index].ptr, self.values[index].ptr
+        desc = NcDecoderDesc(c.layers, c.hidden, c.heads, c.key_heads, c.head_width, c.feed_forward, c.vocab,
+                             self.batch, self.capacity, c.floor, c.rope_base, self.scale,
+                             w["token_embd.weight"].record(), w["output.weight"].record(), n["output_norm.weight"].ptr,
+                             layers, self.tokens.ptr, self.position.ptr, self.logits.ptr)
+        handle = ctypes.c_void_p()
+        _check(self.rt._lib.neura_cuda_decoder_compile(self.rt._ctx, ctypes.byref(desc), ctypes.byref(handle)))
+        self.compiled = handle
+
+    def release(self) -> None:
+        if self.compiled is not None:
+            self.rt._lib.neura_cuda_decoder_free(self.rt._ctx, self.compiled)
+            self.compiled = None
+
     def launches_per_token(self) -> int:
+        if self.compiled is not None:
+            return 1
         paired = "blk.0.ffn_gate_up.weight" in self.weights
         return self.config.layers * (10 if paired else 11) + 5
 
@@ -247,7 +287,11 @@ class Decoder:
         self.rt.write(self.position, np.zeros(self.batch, dtype=np.uint32))
 
     def run_token(self) -> None:
-        if self.program is None:
+        if self.compiled is not None:
+            from .runtime import _check
+
+            _check(self.rt._lib.neura_cuda_decoder_step(self.rt._ctx, self.rt.stream, self.compiled))
+        elif self.program is None:
             self.step()
         else:
             self.rt.run(self.program)

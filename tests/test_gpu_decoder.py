@@ -253,3 +253,34 @@ def test_a_recording_cut_short_by_a_refusal_is_ended_when_the_context_closes(run
     probe = runtime.tensor(16)          # the thread is out of capture mode: allocation works again
     runtime.write(probe, np.arange(16, dtype=np.float32))
     assert runtime.read(probe).tolist() == list(range(16))
+
+
+@pytest.mark.parametrize("name,batch,prompt,steps,capacity", [
+    ("q8_0", 1, 16, 64, 96), ("q4_k", 1, 16, 64, 96), ("q4_k", 2, 16, 64, 96),
+    ("q4_k", 1, 200, 24, 256),    # four splits of the cached positions to merge
+])
+def test_the_persistent_step_decodes_what_the_oracle_decodes(oracle, name, batch, prompt, steps, capacity):
+    from oracle.decoder import OracleDecoder, synthetic_model
+
+    config = SMALL[name]
+    packed, norms = synthetic_model(config, seed=23)
+    prompts = (oracle.Stream(41).uniform(batch * prompt, 0.0, 1.0) * config.vocab).astype(np.uint32).reshape(batch, prompt)
+    want, margins = OracleDecoder(config, packed, norms, batch=batch, capacity=capacity).generate(prompts, steps)
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weights, dnorms = load_model(rt, config, packed, norms)
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=capacity)
+        decoder.compile()
+        assert decoder.launches_per_token() == 1
+        got = decoder.generate(prompts, steps)
+        again = decoder.generate(prompts, steps)
+        decoder.release()
+    finally:
+        rt.close()
+    assert np.array_equal(got, again), "the persistent step decodes the same ids twice"
+    differs = np.argwhere(got != want)
+    if differs.size:
+        b, at = differs[0]
+        pytest.fail(f"sequence {b} leaves the oracle at step {at}: {got[b, at]} for {want[b, at]}, "
+                    f"the oracle's margin there is {margins[b, at]:.3e}")
