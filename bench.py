@@ -26,6 +26,9 @@ sys.path.insert(0, ROOT)
 
 METRIC = "decode tok/s (Q4_K Qwen-shaped)"
 UNIT = "tok/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent step, from the ncu captures
+# summarised under profiles/ (taken on a cut of few layers and scaled by the weights per step)
+MEGAKERNEL_TRAFFIC = {}
 
 
 def measured_peaks():
@@ -211,9 +214,15 @@ def run_ours(args):
     prompts = np.random.default_rng(29).integers(0, config.vocab, (rows, args.prompt), dtype=np.uint32)
     decoder.reset()
     rt.write(decoder.tokens, prompts[:, 0].copy())
-    decoder.step()          # eager once: sizes every scratch region before recording
-    rt.sync()
-    decoder.record()
+    persistent = world == 1 and rows <= 2 and args.step == "persistent"
+    if persistent:          # the whole step as one cooperative kernel
+        decoder.compile()
+        decoder.run_token()
+        rt.sync()
+    else:
+        decoder.step()      # eager once: sizes every scratch region before recording
+        rt.sync()
+        decoder.record()
     launches_per_token = decoder.launches_per_token()
     for at in range(1, args.prompt):
         rt.write(decoder.tokens, prompts[:, at].copy())
@@ -282,10 +291,23 @@ def run_ours(args):
     kernel_ms = r0.elapsed_time(r1) / (reps * config.layers)
     algorithmic = 2 * nb.payload_bytes(config.element, n * k) + 4 * rows * k + 4 * rows * n
     achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
+    kernel_name = f"gemv_stream_kernel<Q4_K> on the paired gate|up [2x{n}x{k}] at batch {rows}"
+    product_alone = {"kernel": kernel_name, "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
+                     "achieved": achieved, "frac": achieved / peak}
 
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel from the ncu capture
     # summarised in profiles/decode_step_qwen32b_q4k_kernels.md (the full-size shape, batch 1, one GPU)
     traffic = 163.4e6 if (config.name.startswith("qwen2.5-32b-q4_k") and rows == 1 and world == 1) else None
+    if persistent:
+        # the step is one kernel: its algorithmic bytes are those of all its products,
+        # payload_bytes(N*K) + 4*B*K + 4*B*N each (the KV cache it also reads is left out)
+        shapes = [(nn, kk) for _, nn, kk in config.linears()] * config.layers + [(config.vocab, config.hidden)]
+        algorithmic = sum(nb.payload_bytes(config.element, nn * kk) + 4 * rows * (nn + kk) for nn, kk in shapes)
+        kernel_ms = ms / args.steps
+        achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
+        kernel_name = (f"decode_megakernel<{'Q4_K' if config.element == nb.Q4K else 'Q8_0'}>: the whole step "
+                       f"({config.layers} layers + head) as one cooperative launch at batch {rows}")
+        traffic = MEGAKERNEL_TRAFFIC.get((config.name, rows))
     times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=torch.device("cuda", local))
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -308,8 +330,8 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                         "kernel": f"gemv_stream_kernel<Q4_K> on the paired gate|up [2x{n}x{k}] at batch {rows}",
-                         "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
+                         "kernel": kernel_name,
+                         "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms, "product_alone": product_alone,
                          "step_gbs_per_gpu": (shard.local_bytes_per_token() if shard else config.weight_bytes())
                                              / (ms / args.steps * 1e-3) / 1e9,
                          "launches_per_token": launches_per_token},
@@ -336,6 +358,9 @@ def main():
     parser.add_argument("--prompt", type=int, default=512)
     parser.add_argument("--comm", default="peer", choices=["peer", "nccl"])
     parser.add_argument("--no-cpu", action="store_true")
+    parser.add_argument("--step", default="graph", choices=["graph", "persistent"],
+                        help="a recorded graph of one kernel per operation (the faster of the two as measured), or one "
+                             "cooperative kernel per token (one GPU, batch <= 2)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -322,6 +322,14 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
 int32_t neura_cuda_decoder_step(nc_context *ctx, void *stream, nc_decoder *decoder);
 int32_t neura_cuda_decoder_free(nc_context *ctx, nc_decoder *decoder);
 
+/* Where the last completed step spent its time (the reference's Trace of a run,
+ * crates/neura-runtime/src/runtime.rs:95-121): for each phase of the table its kind (1 embedding,
+ * 2 product, 3 attention, 4 staging, 5 argmax) and the nanoseconds from the moment CTA 0 entered it to
+ * the moment it entered the next one (so a phase's barrier counts with it).  Writes the number of phases
+ * to phases_out; fills the arrays when `capacity` holds them.  Synchronise the stream first. */
+int32_t neura_cuda_decoder_trace(nc_context *ctx, nc_decoder *decoder, uint32_t capacity, uint32_t *kinds_out,
+                                 uint64_t *nanos_out, uint32_t *phases_out);
+
 /* Streams for callers without a CUDA runtime of their own (Queue, crates/neura-gpu/src/context.rs:287). */
 int32_t neura_cuda_stream_create(nc_context *ctx, void **out_stream);
 int32_t neura_cuda_stream_destroy(nc_context *ctx, void *stream);

@@ -20,7 +20,7 @@ SYMBOLS = [
     "neura_cuda_advance", "neura_cuda_stage_window", "neura_cuda_argmax_segments", "neura_cuda_sealed_pair_bytes",
     "neura_cuda_weight_seal_pair", "neura_cuda_linear_bf16", "neura_cuda_comm_create",
     "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce", "neura_cuda_reserve_decoder",
-    "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free",
+    "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free", "neura_cuda_decoder_trace",
 ]
 
 
@@ -98,6 +98,7 @@ def load() -> ctypes.CDLL:
         "neura_cuda_decoder_compile": (i32, [p, ctypes.POINTER(NcDecoderDesc), pp]),
         "neura_cuda_decoder_step": (i32, [p, p, p]),
         "neura_cuda_decoder_free": (i32, [p, p]),
+        "neura_cuda_decoder_trace": (i32, [p, p, u32, p, p, p]),
         "neura_cuda_weight_seal": (i32, [p, p, u32, u32, u32, p, p]),
         "neura_cuda_dequant": (i32, [p, p, ctypes.POINTER(NcWeight), p]),
         "neura_cuda_quantize": (i32, [p, p, u32, p, u64, p]),

@@ -20,6 +20,7 @@
 // status word, drains its own copies and leaves.
 #pragma once
 #include "common.cuh"
+#include "prep.cuh"
 
 namespace nc {
 
@@ -47,6 +48,10 @@ struct GemvParams {
     uint32_t pair;        // 1: a tile is 16 rows of one matrix over the same 16 rows of a second one, and
                           //    output c is silu(first row c) * (second row c): the SwiGLU of a gate and an up projection
     Chain chain;
+    const StageAfter *after;  // not null: finished tiles are counted and full chunks digitised for the next product
+    const float *sumsq;       // not null: [rows][sumsq_chunks] sums of squares of the input rows, whose rms_norm
+    uint32_t sumsq_chunks;    //           scalar 1 / sqrt(sum / k + floor) multiplies the outputs
+    float floor, inv_k;
 };
 
 // D = A * B with a zero accumulator (the zeros are immediates, not registers).
@@ -131,9 +136,12 @@ __device__ __forceinline__ uint32_t owner_of(uint32_t u, uint32_t q, uint32_t r)
 // Ends a warp's stretch [first_blk, end_blk) of the 32-row tile `tile`: either finishes the
 // tile or leaves a partial for the last contributor to add up.  acc[h] holds, for rows
 // 16h..16h+15 and per 8-column MMA tile, (row g, col 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).
+// `scale0` and `scale1` multiply the sums of rows 0 and 1 (an rms_norm's scalar; 1 otherwise).  Returns
+// whether this warp wrote the tile's final outputs.
 template <int NT>
-__device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][NT][4], float *patch, uint32_t warp,
-                                        uint32_t tile, uint32_t first_blk, uint32_t end_blk) {
+__device__ __forceinline__ bool flush_tile(const GemvParams &p, float (&acc)[2][NT][4], float *patch, uint32_t warp,
+                                        uint32_t tile, uint32_t first_blk, uint32_t end_blk, float scale0 = 1.0f,
+                                        float scale1 = 1.0f) {
     const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     constexpr int W = NT * 8 + 1;  // padded row of the per-warp patch
 #pragma unroll
@@ -149,18 +157,20 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
     __syncwarp();
     const uint32_t cells = p.rows * 32;
     const bool whole = first_blk == 0 && end_blk == p.upt;
+    bool final = whole;
     if (whole && p.pair) {
         for (uint32_t idx = lane; idx < p.rows * 16; idx += 32) {
             const uint32_t rr = idx & 15, b = idx >> 4, col = tile * 16 + rr, up = rr + 16;
-            const float gate = (patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2];
-            const float other = (patch[up * W + 3 * b] + patch[up * W + 3 * b + 1]) + patch[up * W + 3 * b + 2];
+            const float rs = b == 0 ? scale0 : scale1;
+            const float gate = ((patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2]) * rs;
+            const float other = ((patch[up * W + 3 * b] + patch[up * W + 3 * b + 1]) + patch[up * W + 3 * b + 2]) * rs;
             if (col < p.n)
                 p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, gate * sigmoid_f(gate) * other);
         }
     } else if (whole) {
         for (uint32_t idx = lane; idx < cells; idx += 32) {
             const uint32_t rr = idx & 31, b = idx >> 5, col = tile * 32 + rr;
-            const float v = (patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2];
+            const float v = ((patch[rr * W + 3 * b] + patch[rr * W + 3 * b + 1]) + patch[rr * W + 3 * b + 2]) * (b == 0 ? scale0 : scale1);
             if (col < p.n) p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, v);
         }
     } else {
@@ -182,6 +192,7 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
             __threadfence();
         }
         seen = __shfl_sync(0xffffffffu, seen, 0);
+        final = seen == count - 1;
         if (seen == count - 1 && p.pair) {
             const float *all = p.partial + (uint64_t)tile * p.maxp * cells;
             for (uint32_t idx = lane; idx < p.rows * 16; idx += 32) {
@@ -191,6 +202,8 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
                     gate += __ldcg(all + (uint64_t)s * cells + b * 32 + rr);
                     other += __ldcg(all + (uint64_t)s * cells + b * 32 + rr + 16);
                 }
+                gate *= b == 0 ? scale0 : scale1;
+                other *= b == 0 ? scale0 : scale1;
                 if (col < p.n)
                     p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, gate * sigmoid_f(gate) * other);
             }
@@ -201,12 +214,15 @@ __device__ __forceinline__ void flush_tile(const GemvParams &p, float (&acc)[2][
                 const uint32_t rr = idx & 31, b = idx >> 5, col = tile * 32 + rr;
                 float v = 0.0f;
                 for (uint32_t s = 0; s < count; ++s) v += __ldcg(all + (uint64_t)s * cells + idx);
+                v *= b == 0 ? scale0 : scale1;
                 if (col < p.n) p.out[(uint64_t)b * p.out_stride + col] = chained(p.chain, b, col, v);
             }
             if (lane == 0) p.counters[tile] = 0u;
         }
     }
     __syncwarp();
+    if (final && p.after) stage_after_piece(*p.after, tile * p.after->piece);
+    return final;
 }
 
 // ---- Q4_K: one 16-row half of a unit ---------------------------------------------------
@@ -365,6 +381,7 @@ struct GemvWarp {
     uint32_t tile, blk, first_blk, done;
     float acc[2][NT][4];
     uint32_t base = 0;   // fills of this warp's ring before this product (a persistent kernel runs many on one ring)
+    float scale0 = 1.0f, scale1 = 1.0f;   // the rms_norm scalars of rows 0 and 1 of the input (GemvParams::sumsq)
 
     // Unit J of the stage at `buf`.
     template <int J>
@@ -379,7 +396,7 @@ struct GemvWarp {
         }
         ++done;
         if (++blk == p.upt || done == units) {
-            flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk);
+            flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk, scale0, scale1);
             if (blk == p.upt) { blk = 0; ++tile; }
             first_blk = blk;
         }

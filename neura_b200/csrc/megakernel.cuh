@@ -8,8 +8,9 @@
 //   * no launch, fill and drain per phase: a phase boundary costs one barrier (about a microsecond);
 //   * the weight stream never stops: before a warp arrives at a barrier it has already issued the
 //     first copies of its next product, whose weights depend on nothing;
-//   * rms_norm and the activation staging fold into the products: every CTA digitises the activation
-//     row it multiplies into its own shared memory (the row is a few KB; the weights are the traffic).
+//   * rms_norm and the activation staging fold into the producers: the warp that completes a 256-column
+//     chunk of a product's output (or of the attention's) digitises it at once for the next product
+//     (prep.cuh, StageAfter), and the norm's scalar is applied by that product to its outputs.
 // The products are the streaming product of gemv_mma.cuh (same units, same split, same ring).
 //
 // Every wait is bounded (the ring's copies and the grid barrier, by %globaltimer); a CTA whose wait
@@ -29,28 +30,28 @@ constexpr int kMkThreads = kMkWarps * 32;
 constexpr uint32_t kMkRing = kMkWarps * 2 * kQ4kStage;        // two stages a warp (a Q8_0 stage is shorter)
 constexpr uint32_t kMkBars = kMkWarps * 2 * 8;
 constexpr uint32_t kMkPatch = kMkWarps * 32 * 9 * sizeof(float);
-constexpr uint32_t kMkDigits = 62 * 1024;                     // the staged activations of a self-staging product
-constexpr uint32_t kMkSmem = kMkRing + kMkBars + kMkPatch + kMkDigits;
+constexpr uint32_t kMkSmem = kMkRing + kMkBars + kMkPatch;
 constexpr uint32_t kMkTile = 64;                              // cached positions one attention item takes
 constexpr uint32_t kMkNone = 0xffffffffu;
 
 enum : uint32_t { MK_EMBED = 1, MK_GEMV = 2, MK_ATTEND = 3, MK_STAGE = 4, MK_ARGMAX = 5 };
-constexpr uint32_t MK_SELF = 1u;   // the product digitises its f32 input itself, into shared memory
-constexpr uint32_t MK_NORM = 2u;   // ... after rms_norm with the phase's weight
 
 struct MkPhase {
     uint32_t kind, flags;
     uint32_t prefetch;       // the product whose first copies are issued when this phase ends, or kMkNone
     uint32_t k;              // columns of the input rows
-    GemvParams g;            // MK_GEMV (dig, cs, sums: the staged input in global memory when not MK_SELF)
-    const float *x;          // f32 input rows (MK_GEMV | MK_SELF, MK_STAGE, MK_ARGMAX)
+    GemvParams g;            // MK_GEMV (dig, cs, sums: the staged input rows)
+    StageAfter after;        // MK_GEMV, MK_ATTEND, MK_STAGE: how the rows this phase writes are staged for the next product
+    uint32_t has_after, pad;
+    const float *x;          // f32 input rows (MK_STAGE, MK_ARGMAX)
     uint64_t x_stride;
-    const float *norm;       // rms_norm weight [k] (MK_NORM)
     float *keys, *values;    // MK_ATTEND: this layer's cache
     WeightView table;        // MK_EMBED
     float *out;              // MK_EMBED: rows of `out_stride`
     uint64_t out_stride;
     uint32_t lo, hi;         // MK_STAGE: the input is elements [lo, hi) of K, zero elsewhere
+    // when this phase ends, bytes [from, to) of every warp's run in product `ahead_phase[i]` are asked into L2
+    uint32_t ahead_phase[2], ahead_from[2], ahead_to[2];
 };
 
 struct MkParams {
@@ -69,14 +70,13 @@ struct MkParams {
     unsigned int *attend_counters;  // [rows][key_heads], zero between launches
     uint32_t heads, key_heads, width, capacity, max_splits;
     float scale, rope_base, floor;
-    // activations staged in global memory (MK_STAGE phases write, products without MK_SELF read)
-    int8_t *dig;
-    float *cs;
-    uint32_t *sums;
     // argmax
     float *slice_value;          // [rows][gridDim.x]
     uint32_t *slice_index;
     unsigned int *argmax_counters;  // [rows], zero between launches
+    unsigned long long *trace;   // [nphases + 1]: %globaltimer as CTA 0 enters each phase, and as it leaves the last
+    unsigned long long *detail;  // [nphases][4] or null: CTA 0's clock when its warp 0 is done with the phase ([1]),
+                                 // when all its warps are ([2]), and when the last CTA's are ([3])
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
@@ -91,15 +91,19 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
 __device__ __forceinline__ bool mk_barrier(const MkParams &p, uint32_t epoch, volatile uint32_t *aborted) {
     __syncthreads();
     if (threadIdx.x == 0 && !*aborted) {
+        // arrivals count on one line, the release is a flag on another: the CTAs that wait read the flag's
+        // line only and do not stand in the way of the arrivals still on their way
+        unsigned int *flag = p.barrier + 32;
         __threadfence();
-        atomicAdd(p.barrier, 1u);
-        const unsigned int target = epoch * gridDim.x;
-        if (ld_acquire_gpu(p.barrier) < target) {
+        const unsigned int before = atomicAdd(p.barrier, 1u);
+        if (before + 1u == epoch * gridDim.x) {
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+        } else if (ld_acquire_gpu(flag) < epoch) {
             const unsigned long long start = global_nanos();
             for (;;) {
                 bool met = false;
 #pragma unroll 1
-                for (int tries = 0; tries < 32 && !met; ++tries) met = ld_acquire_gpu(p.barrier) >= target;
+                for (int tries = 0; tries < 32 && !met; ++tries) met = ld_acquire_gpu(flag) >= epoch;
                 if (met) break;
                 if (global_nanos() - start > kWaitNanos) {
                     *aborted = 1u;
@@ -114,121 +118,33 @@ __device__ __forceinline__ bool mk_barrier(const MkParams &p, uint32_t epoch, vo
     return *aborted == 0u;
 }
 
-// ---- activation fragments from shared memory (self-staged) or from global memory (through L2) -------
-struct MkFrags {
-    const uint8_t *dig;
-    const float *cs;
-    const uint8_t *sums;
-    uint32_t ncols;
-};
-
-template <bool SMEM, typename T>
-__device__ __forceinline__ T mk_ld(const T *p) {
-    if constexpr (SMEM) return *p;
-    else return __ldcg(p);
-}
-
-// load_frags of gemv_mma.cuh for one 8-column MMA tile, reading through `mk_ld`.
-template <bool Q4K, bool SMEM>
-__device__ __forceinline__ void mk_load_frags(StageFrags<Q4K, 1> &f, const MkFrags &s, uint32_t upt, uint32_t blk,
-                                              uint32_t have) {
+// ---- activation fragments -----------------------------------------------------------------------------------
+// load_frags of gemv_mma.cuh for one 8-column MMA tile.  Ordinary loads, so that the SM's L1 serves the warps
+// that share a block of K: the fragments were written in an earlier phase, and the fence of the barrier
+// between (mk_barrier) makes this SM's L1 drop what it held before.  (Not ld.global.nc: that path is for
+// data no one writes during the kernel.)
+template <bool Q4K>
+__device__ __forceinline__ void mk_load_frags(StageFrags<Q4K, 1> &f, const GemvParams &s, uint32_t blk, uint32_t have) {
     const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int j = 0; j < StageFrags<Q4K, 1>::kUnits; ++j) {
         const uint32_t col = 2 * t;
-        f.c[j][0][0] = col < s.ncols ? mk_ld<SMEM>(s.cs + blk * s.ncols + col) : 0.0f;
-        f.c[j][0][1] = col + 1 < s.ncols ? mk_ld<SMEM>(s.cs + blk * s.ncols + col + 1) : 0.0f;
+        f.c[j][0][0] = col < s.ncols ? s.cs[blk * s.ncols + col] : 0.0f;
+        f.c[j][0][1] = col + 1 < s.ncols ? s.cs[blk * s.ncols + col + 1] : 0.0f;
         const bool live = g < s.ncols;
         if constexpr (Q4K) {
             const uint32_t entry = (blk * s.ncols + g) * 4 + t;
             const uint4 *from = reinterpret_cast<const uint4 *>(s.dig) + entry * 4u;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) f.wide[0][i] = live ? mk_ld<SMEM>(from + i) : make_uint4(0u, 0u, 0u, 0u);
-            f.sums[0] = live ? mk_ld<SMEM>(reinterpret_cast<const uint4 *>(s.sums) + entry) : make_uint4(0u, 0u, 0u, 0u);
+            for (int i = 0; i < 4; ++i) f.wide[0][i] = live ? from[i] : make_uint4(0u, 0u, 0u, 0u);
+            f.sums[0] = live ? reinterpret_cast<const uint4 *>(s.sums)[entry] : make_uint4(0u, 0u, 0u, 0u);
         } else {
-            f.narrow[j][0] = live ? mk_ld<SMEM>(reinterpret_cast<const uint2 *>(s.dig + (blk * s.ncols + g) * 32u + t * 8u))
+            f.narrow[j][0] = live ? *reinterpret_cast<const uint2 *>(s.dig + (blk * s.ncols + g) * 32u + t * 8u)
                                   : make_uint2(0u, 0u);
         }
-        if ((uint32_t)(j + 1) < have && ++blk == upt) blk = 0;
+        if ((uint32_t)(j + 1) < have && ++blk == s.upt) blk = 0;
     }
 }
-
-// Where the three tables of a staged input of `k` columns sit inside one buffer.
-struct MkStaged {
-    int8_t *dig;
-    uint32_t *sums;
-    float *cs;
-};
-__device__ __forceinline__ MkStaged mk_staged_at(uint8_t *base, uint32_t k, uint32_t ncols, bool q4k) {
-    const uint32_t chunks = (k + 255) / 256;
-    MkStaged s;
-    s.dig = reinterpret_cast<int8_t *>(base);
-    s.sums = reinterpret_cast<uint32_t *>(base + (size_t)chunks * ncols * 256);
-    s.cs = reinterpret_cast<float *>(base + (size_t)chunks * ncols * (q4k ? 320 : 256));
-    return s;
-}
-
-// Every CTA digitises the whole input of the product it is about to run (rows of ph.k <= 8192 columns)
-// into its own shared memory, after rms_norm when the phase asks for it: what rms_norm_stage_kernel and
-// prep_kernel do for the one-launch-per-step path.  Warp w takes chunks w and w + 16 of every row.
-__device__ __forceinline__ void mk_self_stage(const MkParams &p, const MkPhase &ph, uint8_t *digits, float *reduce) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t chunks = (ph.k + 255) / 256;
-    const MkStaged at = mk_staged_at(digits, ph.k, ph.g.ncols, p.granule == 256);
-    PrepParams sp;
-    sp.x = ph.x;
-    sp.x_stride = ph.x_stride;
-    sp.dig = at.dig;
-    sp.cs = at.cs;
-    sp.sums = at.sums;
-    sp.rows = p.rows;
-    sp.k = ph.k;
-    sp.ncols = ph.g.ncols;
-    sp.granule = p.granule;
-    sp.vector = 1;
-    sp.lo = 0;
-    sp.hi = ph.k;
-    for (uint32_t row = 0; row < p.rows; ++row) {
-        float v[2][8];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const uint32_t chunk = warp + i * kMkWarps, from = chunk * 256 + lane * 8;
-            load_chunk(sp, row, from, chunk < chunks && from < ph.k, v[i]);
-        }
-        float scale = 1.0f;
-        if (ph.flags & MK_NORM) {
-            float square = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) square = fmaf(v[i][j], v[i][j], square);
-            for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
-            __syncthreads();   // the row before has been read out of `reduce`
-            if (lane == 0) reduce[warp] = square;
-            __syncthreads();
-            float total = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kMkWarps; ++w) total += reduce[w];
-            scale = 1.0f / sqrtf(total / (float)ph.k + p.floor);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const uint32_t chunk = warp + i * kMkWarps, from = chunk * 256 + lane * 8;
-            if (chunk >= chunks) continue;   // (the whole warp skips)
-            const bool live = from < ph.k;
-            if (live && (ph.flags & MK_NORM)) {
-                const float4 a = __ldg(reinterpret_cast<const float4 *>(ph.norm + from));
-                const float4 c = __ldg(reinterpret_cast<const float4 *>(ph.norm + from + 4));
-                const float gain[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * scale * gain[j];
-            }
-            stage_chunk(sp, row, chunk, v[i], live);
-        }
-    }
-    __syncthreads();
-}
-
 
 // ---- products ----------------------------------------------------------------------------------------
 // A warp's ring as it lives across the phases of one launch.
@@ -238,6 +154,10 @@ struct MkRing {
     uint32_t ahead_phase;    // the product whose first `ahead` stages are already on their way
     uint32_t ahead;
 };
+
+// The grid's warps are numbered across the CTAs (warp w of CTA c is w * gridDim.x + c): a product gives its
+// first r warps one unit more than the rest, and this way every SM gets its share of them.
+__device__ __forceinline__ uint32_t mk_warp() { return (threadIdx.x >> 5) * gridDim.x + blockIdx.x; }
 
 // This warp's run of units in a product.
 struct MkRun {
@@ -278,17 +198,35 @@ template <bool Q4K>
 __device__ __forceinline__ void mk_prefetch(const MkParams &p, uint32_t next, MkRing &rg) {
     if (next == kMkNone || rg.ahead_phase == next) return;   // (a phase before this one may have started them)
     const GemvParams &g = p.phases[next].g;
-    const uint32_t warp = blockIdx.x * kMkWarps + (threadIdx.x >> 5);
-    const MkRun run = mk_run_of<Q4K>(g.w, g.nwarps, g.q, g.r, warp);
+    const MkRun run = mk_run_of<Q4K>(g.w, g.nwarps, g.q, g.r, mk_warp());
     rg.ahead_phase = next;
     rg.ahead = min(run.steps, 2u);
     if ((threadIdx.x & 31) == 0) mk_issue<Q4K>(rg, run, 0, rg.ahead);
     __syncwarp();
 }
 
-template <bool Q4K, bool SMEM>
-__device__ __forceinline__ bool mk_stream(const GemvParams &g, const MkFrags &frags, MkRing &rg, const MkRun &run,
-                                          float *patch, uint32_t warp) {
+// Before a barrier: ask the head of the coming products' weights into L2, so that HBM keeps streaming while
+// the grid meets at the barrier and stages its activations (shared memory holds two stages a warp, L2 holds
+// tens of MB).  Lane l asks for the l-th piece of 4 KB of its warp's range.
+template <bool Q4K>
+__device__ __forceinline__ void mk_prefetch_l2(const MkParams &p, const MkPhase &ph) {
+    const uint32_t lane = threadIdx.x & 31, warp = mk_warp();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (ph.ahead_phase[i] == kMkNone) continue;
+        const GemvParams &g = p.phases[ph.ahead_phase[i]].g;
+        const MkRun run = mk_run_of<Q4K>(g.w, g.nwarps, g.q, g.r, warp);
+        const uint64_t to = min((uint64_t)ph.ahead_to[i], run.bytes);
+        for (uint64_t at = (uint64_t)ph.ahead_from[i] + (uint64_t)lane * 4096; at < to; at += 32 * 4096) {
+            const uint32_t len = (uint32_t)min((uint64_t)4096, to - at);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(run.src + at), "r"(len) : "memory");
+        }
+    }
+}
+
+template <bool Q4K>
+__device__ __forceinline__ bool mk_stream(const GemvParams &g, MkRing &rg, const MkRun &run, float *patch, uint32_t warp,
+                                          float scale0, float scale1) {
     constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;
     GemvWarp<Q4K, 1, 2> w{g};
     w.ring = rg.ring;
@@ -300,6 +238,8 @@ __device__ __forceinline__ bool mk_stream(const GemvParams &g, const MkFrags &fr
     w.units = run.units;
     w.steps = run.steps;
     w.base = rg.fills;
+    w.scale0 = scale0;
+    w.scale1 = scale1;
     w.tile = run.u0 / g.upt;
     w.blk = run.u0 % g.upt;
     w.first_blk = w.blk;
@@ -307,16 +247,14 @@ __device__ __forceinline__ bool mk_stream(const GemvParams &g, const MkFrags &fr
 #pragma unroll
     for (int h = 0; h < 2; ++h) w.acc[h][0][0] = w.acc[h][0][1] = w.acc[h][0][2] = w.acc[h][0][3] = 0.0f;
     StageFrags<Q4K, 1> even, odd;
-    mk_load_frags<Q4K, SMEM>(even, frags, g.upt, w.blk, min(w.units, kGroup));
+    mk_load_frags<Q4K>(even, g, w.blk, min(w.units, kGroup));
     uint32_t failed = kMkNone;
     for (uint32_t step = 0; step < w.steps; step += 2) {
         const bool second = step + 1 < w.steps;
-        if (second)
-            mk_load_frags<Q4K, SMEM>(odd, frags, g.upt, w.block_after(w.blk), min(w.units - (step + 1) * kGroup, kGroup));
+        if (second) mk_load_frags<Q4K>(odd, g, w.block_after(w.blk), min(w.units - (step + 1) * kGroup, kGroup));
         if (!w.run(step, even)) { failed = step; break; }
         if (second) {
-            if (step + 2 < w.steps)
-                mk_load_frags<Q4K, SMEM>(even, frags, g.upt, w.block_after(w.blk), min(w.units - (step + 2) * kGroup, kGroup));
+            if (step + 2 < w.steps) mk_load_frags<Q4K>(even, g, w.block_after(w.blk), min(w.units - (step + 2) * kGroup, kGroup));
             if (!w.run(step + 1, odd)) { failed = step + 1; break; }
         }
     }
@@ -331,38 +269,34 @@ __device__ __forceinline__ bool mk_stream(const GemvParams &g, const MkFrags &fr
     return true;
 }
 
+// The rms_norm scalar of input row `row`: the chunks' sums of squares, added in chunk order.
+__device__ __forceinline__ float mk_row_scale(const GemvParams &g, uint32_t row) {
+    float total = 0.0f;
+    for (uint32_t c = 0; c < g.sumsq_chunks; ++c) total += __ldcg(g.sumsq + row * g.sumsq_chunks + c);
+    return 1.0f / sqrtf(total * g.inv_k + g.floor);
+}
+
 template <bool Q4K>
-__device__ __forceinline__ void mk_gemv(const MkParams &p, const MkPhase &ph, uint32_t index, MkRing &rg, uint8_t *digits,
-                                        float *patch, float *reduce, volatile uint32_t *aborted) {
-    const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5, warp = blockIdx.x * kMkWarps + wib;
+__device__ __noinline__ void mk_gemv(const MkParams &p, const MkPhase &ph, uint32_t index, MkRing &rg, float *patch,
+                                        volatile uint32_t *aborted) {
+    const uint32_t lane = threadIdx.x & 31, warp = mk_warp();
     const GemvParams &g = ph.g;
     const MkRun run = mk_run_of<Q4K>(g.w, g.nwarps, g.q, g.r, warp);
     const uint32_t ahead = rg.ahead_phase == index ? rg.ahead : 0u;
     if (lane == 0) mk_issue<Q4K>(rg, run, ahead, min(run.steps, 2u));
     rg.ahead_phase = kMkNone;
     __syncwarp();
-    MkFrags frags;
-    frags.ncols = g.ncols;
-    bool ok = true;
-    if (ph.flags & MK_SELF) {
-        mk_self_stage(p, ph, digits, reduce);
-        const MkStaged at = mk_staged_at(digits, ph.k, g.ncols, Q4K);
-        frags.dig = reinterpret_cast<const uint8_t *>(at.dig);
-        frags.cs = at.cs;
-        frags.sums = reinterpret_cast<const uint8_t *>(at.sums);
-        if (run.units) ok = mk_stream<Q4K, true>(g, frags, rg, run, patch, warp);
-    } else {
-        frags.dig = g.dig;
-        frags.cs = g.cs;
-        frags.sums = g.sums;
-        if (run.units) ok = mk_stream<Q4K, false>(g, frags, rg, run, patch, warp);
+    if (!run.units) return;
+    float scale0 = 1.0f, scale1 = 1.0f;
+    if (g.sumsq) {
+        scale0 = mk_row_scale(g, 0);
+        if (g.rows > 1) scale1 = mk_row_scale(g, 1);
     }
-    if (!ok && lane == 0) {
+    if (!mk_stream<Q4K>(g, rg, run, patch, warp, scale0, scale1) && lane == 0) {
         atomicOr(p.status, 1u);
         *aborted = 1u;
     }
 }
-
 
 // ---- attention -----------------------------------------------------------------------------------------
 // Half-rotation RoPE of one channel pair (crates/neura-kernel/src/task/rope.rs:48-122), out of line: the
@@ -515,6 +449,28 @@ __device__ __forceinline__ void mk_attend_item(const MkParams &p, const MkPhase 
             p.attended[(uint64_t)b * p.attended_stride + (uint64_t)(kh * group + g) * WIDTH + d] = acc / totals[g];
         }
         if (threadIdx.x == 0) p.attend_counters[b * p.key_heads + kh] = 0u;
+        if (ph.has_after) {
+            // the heads of this key head are columns [kh, kh + 1) * group * WIDTH of the row the output product
+            // multiplies: count this arrival on the 256-column chunks they touch; whoever completes a chunk stages it
+            __syncthreads();
+            const StageAfter &a = ph.after;
+            const uint32_t span = group * WIDTH, chunks = (a.prep.k + 255) / 256;
+            const uint32_t c0 = kh * span / 256, c1 = ((kh + 1) * span - 1) / 256;
+            for (uint32_t c = c0 + warp; c <= c1; c += warps) {
+                const uint32_t expected = (min(a.prep.k, (c + 1) * 256) - 1) / span - c * 256 / span + 1;
+                unsigned int seen = 0;
+                if (lane == 0) {
+                    __threadfence();
+                    seen = atomicAdd(a.counters + b * chunks + c, 1u);
+                    __threadfence();
+                }
+                seen = __shfl_sync(0xffffffffu, seen, 0);
+                if (seen == expected - 1) {
+                    stage_after_chunk(a, b, c);
+                    if (lane == 0) a.counters[b * chunks + c] = 0u;
+                }
+            }
+        }
     }
     __syncthreads();   // the tile is free for the CTA's next item
 }
@@ -536,31 +492,12 @@ __device__ __forceinline__ void mk_attend(const MkParams &p, const MkPhase &ph, 
 
 
 // ---- the small phases -------------------------------------------------------------------------------------
-// prep_kernel as a phase: the rows of ph.x digitised into the global staging tables, one warp per
-// (row, 256 columns).  The input is elements [lo, hi) of the K axis (a tensor-parallel rank's window).
+// A staging pass of its own (after the embedding gather, whose rows no product wrote): one warp per
+// (row, 256 columns) of ph.after.
 __device__ __forceinline__ void mk_stage(const MkParams &p, const MkPhase &ph) {
-    PrepParams sp;
-    sp.x = ph.x;
-    sp.x_stride = ph.x_stride;
-    sp.dig = p.dig;
-    sp.cs = p.cs;
-    sp.sums = p.sums;
-    sp.rows = p.rows;
-    sp.k = ph.k;
-    sp.ncols = ph.g.ncols;
-    sp.granule = p.granule;
-    sp.vector = 1;
-    sp.lo = ph.lo;
-    sp.hi = ph.hi;
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t chunks = (ph.k + 255) / 256, total = p.rows * chunks;
-    for (uint32_t w = blockIdx.x * kMkWarps + (threadIdx.x >> 5); w < total; w += gridDim.x * kMkWarps) {
-        const uint32_t row = w / chunks, chunk = w % chunks, from = chunk * 256 + lane * 8;
-        const bool live = from < ph.k;
-        float v[8];
-        load_chunk(sp, row, from, live, v);
-        stage_chunk(sp, row, chunk, v, live);
-    }
+    const uint32_t chunks = (ph.after.prep.k + 255) / 256, total = p.rows * chunks;
+    for (uint32_t w = blockIdx.x * kMkWarps + (threadIdx.x >> 5); w < total; w += gridDim.x * kMkWarps)
+        stage_after_chunk(ph.after, w / chunks, w % chunks);
 }
 
 // embed_kernel as a phase.
@@ -633,7 +570,6 @@ __global__ void __launch_bounds__(kMkThreads, 1) decode_megakernel(const __grid_
     rg.ahead_phase = kMkNone;
     rg.ahead = 0;
     float *patch = reinterpret_cast<float *>(smem + kMkRing + kMkBars) + wib * 32 * 9;
-    uint8_t *digits = smem + kMkRing + kMkBars + kMkPatch;
     if (threadIdx.x == 0) aborted = 0u;
     if (lane == 0) {
         mbar_init(rg.bars, 1);
@@ -650,9 +586,12 @@ __global__ void __launch_bounds__(kMkThreads, 1) decode_megakernel(const __grid_
         }
         __syncthreads();
         if (aborted) break;
+        if (threadIdx.x == 0) phase.g.after = phase.has_after ? &phase.after : nullptr;
+        __syncthreads();
+        if (blockIdx.x == 0 && threadIdx.x == 0) p.trace[index] = global_nanos();
         switch (phase.kind) {
         case MK_EMBED: mk_embed(p, phase); break;
-        case MK_GEMV: mk_gemv<Q4K>(p, phase, index, rg, digits, patch, reduce, &aborted); break;
+        case MK_GEMV: mk_gemv<Q4K>(p, phase, index, rg, patch, &aborted); break;
         case MK_ATTEND:
             if (p.width == 128) mk_attend<128>(p, phase, reinterpret_cast<float *>(smem), &arrived);
             else mk_attend<64>(p, phase, reinterpret_cast<float *>(smem), &arrived);
@@ -661,11 +600,18 @@ __global__ void __launch_bounds__(kMkThreads, 1) decode_megakernel(const __grid_
         case MK_ARGMAX: mk_argmax(p, phase, reduce, best_index, &arrived); break;
         default: break;
         }
+        if (p.detail && blockIdx.x == 0 && threadIdx.x == 0) p.detail[index * 4 + 1] = global_nanos();
         if (index + 1 == p.nphases) break;   // nothing follows the last phase
         __syncthreads();                     // the CTA is done with the ring and with `phase`
+        if (p.detail && threadIdx.x == 0) {
+            if (blockIdx.x == 0) p.detail[index * 4 + 2] = global_nanos();
+            if (blockIdx.x == gridDim.x - 1) p.detail[index * 4 + 3] = global_nanos();
+        }
         mk_prefetch<Q4K>(p, phase.prefetch, rg);
+        mk_prefetch_l2<Q4K>(p, phase);
         if (!mk_barrier(p, index + 1, &aborted)) break;
     }
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.trace[p.nphases] = global_nanos();
     // copies issued ahead of a product that never ran: let them land before the memory is handed back
     if (rg.ahead_phase != kMkNone) {
         for (uint32_t s = 0; s < rg.ahead; ++s) mbar_wait(rg.bars + ((rg.fills + s) & 1u) * 8, ((rg.fills + s) >> 1) & 1u);

@@ -2,6 +2,7 @@
 // Built for sm_100a only; there is no CPU path behind any entry point.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <algorithm>
 #include <new>
@@ -1105,6 +1106,7 @@ struct nc_decoder {
     bool q4k = false;
     unsigned int grid = 0;
     std::vector<void *> owned;   // device blocks freed with the decoder
+    std::vector<uint32_t> kinds; // the phase table's kinds, for the trace
 };
 
 namespace {
@@ -1166,11 +1168,8 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     const uint32_t query_width = c.heads * c.head_width, key_width = c.key_heads * c.head_width;
     const uint32_t ncols = c.batch * 3;
     const bool q4k = element == NC_ELEMENT_Q4K;
-    // what a self-staging product keeps in shared memory: rows of at most 8192 columns, digits, sums and scales
-    auto staged_bytes = [&](uint32_t k) { return (uint64_t)((k + 255) / 256) * ncols * (q4k ? 324u : 288u); };
-    auto self_stages = [&](uint32_t k) { return k <= 8192 && k % 8 == 0 && staged_bytes(k) <= kMkDigits; };
-    if (!self_stages(c.hidden) || c.hidden % per)
-        return refuse(kBadArgument, "a hidden width of %u does not fit the persistent step's shared memory", c.hidden);
+    if (c.hidden % per || c.hidden % 8)
+        return refuse(kBadArgument, "a hidden width of %u is not whole blocks of %u", c.hidden, per);
     auto fits = [&](const nc_weight &w, uint32_t n, uint32_t k, uint32_t layout, const char *name) -> int32_t {
         int32_t rc = check_weight(&w);
         if (rc) return rc;
@@ -1204,24 +1203,18 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     auto fail = [&](int32_t code) { neura_cuda_decoder_free(ctx, d); return code; };
 
     // activations and scratch
-    float *hidden, *qkv, *attended, *held, *partial, *attend_partial, *slice_value, *cs;
-    uint32_t *slice_index, *sums;
+    float *hidden, *qkv, *attended, *held, *partial, *attend_partial, *slice_value, *sumsq;
+    uint32_t *slice_index;
     unsigned int *counters, *attend_counters, *argmax_counters, *barrier;
-    int8_t *dig;
     const uint32_t qkv_width = query_width + 2 * key_width;
     const uint32_t max_splits = (c.capacity + kMkTile - 1) / kMkTile;
     const uint32_t widest = std::max(std::max(c.vocab, 2 * ((c.feed_forward + 15) / 16 * 16)), std::max(c.hidden, qkv_width));
     const uint32_t ntiles_max = (widest + kTileRows - 1) / kTileRows + 1;
-    const uint32_t longest = std::max(std::max(c.hidden, query_width), c.feed_forward);
-    const uint64_t kpad = ((uint64_t)longest + 255) / 256 * 256;
 #define NC_TRY(call) do { int32_t rc_ = (call); if (rc_) return fail(rc_); } while (0)
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.hidden * 4, true, (void **)&hidden));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * qkv_width * 4, true, (void **)&qkv));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * query_width * 4, true, (void **)&attended));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.feed_forward * 4, true, (void **)&held));
-    NC_TRY(decoder_alloc(d, kpad * ncols, true, (void **)&dig));
-    NC_TRY(decoder_alloc(d, kpad / 32 * ncols * 4, true, (void **)&cs));
-    NC_TRY(decoder_alloc(d, kpad / 256 * ncols * 64, true, (void **)&sums));
     NC_TRY(decoder_alloc(d, (uint64_t)ntiles_max * sizeof(unsigned int), true, (void **)&counters));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.heads * max_splits * (c.head_width + 2) * 4, true, (void **)&attend_partial));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * c.key_heads * sizeof(unsigned int), true, (void **)&attend_counters));
@@ -1229,6 +1222,33 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * d->grid * 4, true, (void **)&slice_index));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * sizeof(unsigned int), true, (void **)&argmax_counters));
     NC_TRY(decoder_alloc(d, 256, true, (void **)&barrier));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * ((c.hidden + 255) / 256) * 4, true, (void **)&sumsq));
+    unsigned long long *trace;
+
+    // the staged form of each kind of activation row: what the products read (prep.cuh)
+    struct Staged {
+        int8_t *dig;
+        float *cs;
+        uint32_t *sums;
+        unsigned int *counters;
+        float *rows;
+        uint32_t width;
+    };
+    auto staged = [&](float *rows, uint32_t width, Staged &out) -> int32_t {
+        const uint64_t kpad = ((uint64_t)width + 255) / 256 * 256;
+        int32_t rc_;
+        if ((rc_ = decoder_alloc(d, kpad * ncols, true, (void **)&out.dig))) return rc_;
+        if ((rc_ = decoder_alloc(d, kpad / 32 * ncols * 4, true, (void **)&out.cs))) return rc_;
+        if ((rc_ = decoder_alloc(d, kpad / 256 * ncols * 64, true, (void **)&out.sums))) return rc_;
+        if ((rc_ = decoder_alloc(d, (uint64_t)c.batch * (kpad / 256) * sizeof(unsigned int), true, (void **)&out.counters))) return rc_;
+        out.rows = rows;
+        out.width = width;
+        return 0;
+    };
+    Staged of_hidden, of_attended, of_held;
+    NC_TRY(staged(hidden, c.hidden, of_hidden));
+    NC_TRY(staged(attended, query_width, of_attended));
+    NC_TRY(staged(held, c.feed_forward, of_held));
 
     // the phase table
     std::vector<MkPhase> phases;
@@ -1238,23 +1258,41 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         memset(&ph, 0, sizeof ph);
         ph.kind = kind;
         ph.prefetch = kMkNone;
+        ph.ahead_phase[0] = ph.ahead_phase[1] = kMkNone;
         return ph;
     };
-    auto product = [&](const nc_weight &w, const float *x, uint64_t x_stride, uint32_t flags, const float *norm,
-                       float *out_rows, uint64_t out_stride, const float *residual) {
+    // how the rows a phase writes become the operand of the next product
+    auto stage_after = [&](MkPhase &ph, const Staged &to, uint32_t piece, const float *gain, bool squares) {
+        ph.has_after = 1;
+        StageAfter &a = ph.after;
+        a.prep.x = to.rows;
+        a.prep.x_stride = to.width;
+        a.prep.dig = to.dig;
+        a.prep.cs = to.cs;
+        a.prep.sums = to.sums;
+        a.prep.rows = c.batch;
+        a.prep.k = to.width;
+        a.prep.ncols = ncols;
+        a.prep.granule = q4k ? 256 : 32;
+        a.prep.vector = 1;
+        a.prep.lo = 0;
+        a.prep.hi = to.width;
+        a.gain = gain;
+        a.sumsq = squares ? sumsq : nullptr;
+        a.counters = to.counters;
+        a.piece = piece;
+    };
+    auto product = [&](const nc_weight &w, const Staged &from, bool normed, float *out_rows, uint64_t out_stride,
+                       const float *residual) -> MkPhase & {
         MkPhase ph = blank(MK_GEMV);
-        ph.flags = flags;
         ph.k = w.k;
-        ph.x = x;
-        ph.x_stride = x_stride;
-        ph.norm = norm;
         GemvParams &g = ph.g;
         const bool pair = w.layout == NC_LAYOUT_TILED_PAIR;
         const uint32_t plan_n = pair ? (w.n + 15) / 16 * 32 : w.n;
         g.w = (const uint8_t *)w.data_dev;
-        g.dig = (const uint8_t *)dig;
-        g.cs = cs;
-        g.sums = (const uint8_t *)sums;
+        g.dig = (const uint8_t *)from.dig;
+        g.cs = from.cs;
+        g.sums = (const uint8_t *)from.sums;
         g.out = out_rows;
         g.out_stride = out_stride;
         g.counters = counters;
@@ -1263,6 +1301,12 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         g.rows = c.batch;
         g.ncols = ncols;
         g.pair = pair ? 1u : 0u;
+        if (normed) {
+            g.sumsq = sumsq;
+            g.sumsq_chunks = (from.width + 255) / 256;
+            g.floor = c.floor;
+            g.inv_k = 1.0f / (float)from.width;
+        }
         if (residual) {
             g.chain.n = 1;
             g.chain.step[0].op = NC_OP_ADD;
@@ -1275,6 +1319,7 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         const uint64_t ntiles = (plan_n + kTileRows - 1) / kTileRows;
         partial_cells = std::max(partial_cells, ntiles * g.maxp * c.batch * kTileRows);
         phases.push_back(ph);
+        return phases.back();
     };
     {
         MkPhase ph = blank(MK_EMBED);
@@ -1282,42 +1327,26 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         ph.out = hidden;
         ph.out_stride = c.hidden;
         phases.push_back(ph);
+        MkPhase first = blank(MK_STAGE);
+        stage_after(first, of_hidden, 256, c.layer[0].attn_norm_dev, true);
+        phases.push_back(first);
     }
-    const bool output_self = self_stages(query_width) && query_width % per == 0;
     for (uint32_t l = 0; l < c.layers; ++l) {
         const nc_decoder_layer &layer = c.layer[l];
-        product(layer.qkv, hidden, c.hidden, MK_SELF | MK_NORM, layer.attn_norm_dev, qkv, qkv_width, nullptr);
+        const float *next_norm = l + 1 < c.layers ? c.layer[l + 1].attn_norm_dev : c.output_norm_dev;
+        product(layer.qkv, of_hidden, true, qkv, qkv_width, nullptr);
         {
             MkPhase ph = blank(MK_ATTEND);
             ph.keys = layer.keys_dev;
             ph.values = layer.values_dev;
+            stage_after(ph, of_attended, 256, nullptr, false);
             phases.push_back(ph);
         }
-        if (!output_self) {
-            MkPhase ph = blank(MK_STAGE);
-            ph.x = attended;
-            ph.x_stride = query_width;
-            ph.k = query_width;
-            ph.lo = 0;
-            ph.hi = query_width;
-            ph.g.ncols = ncols;
-            phases.push_back(ph);
-        }
-        product(layer.attn_output, attended, query_width, output_self ? MK_SELF : 0u, nullptr, hidden, c.hidden, hidden);
-        product(layer.gate_up, hidden, c.hidden, MK_SELF | MK_NORM, layer.ffn_norm_dev, held, c.feed_forward, nullptr);
-        {
-            MkPhase ph = blank(MK_STAGE);
-            ph.x = held;
-            ph.x_stride = c.feed_forward;
-            ph.k = c.feed_forward;
-            ph.lo = 0;
-            ph.hi = c.feed_forward;
-            ph.g.ncols = ncols;
-            phases.push_back(ph);
-        }
-        product(layer.down, held, c.feed_forward, 0u, nullptr, hidden, c.hidden, hidden);
+        stage_after(product(layer.attn_output, of_attended, false, hidden, c.hidden, hidden), of_hidden, 32, layer.ffn_norm_dev, true);
+        stage_after(product(layer.gate_up, of_hidden, true, held, c.feed_forward, nullptr), of_held, 16, nullptr, false);
+        stage_after(product(layer.down, of_held, false, hidden, c.hidden, hidden), of_hidden, 32, next_norm, true);
     }
-    product(c.head, hidden, c.hidden, MK_SELF | MK_NORM, c.output_norm_dev, c.logits_dev, c.vocab, nullptr);
+    product(c.head, of_hidden, true, c.logits_dev, c.vocab, nullptr);
     {
         MkPhase ph = blank(MK_ARGMAX);
         ph.x = c.logits_dev;
@@ -1333,10 +1362,36 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
             if (phases[j].kind == MK_GEMV) { phases[i].prefetch = (uint32_t)j; break; }
         }
     }
+    // ... and ask the head of the coming products' weights into L2: about 48 MB per phase boundary (what HBM
+    // moves while the grid is at a barrier and stages activations), never the same bytes twice
+    {
+        const char *knob = getenv("NEURA_MK_L2");
+        const uint64_t budget = knob ? (uint64_t)atoi(knob) * 1024 : 20 * 1024;   // bytes a warp asks for at one boundary
+        const uint64_t unit = q4k ? kQ4kStage : 2 * kQ8Unit;
+        std::vector<uint64_t> covered(phases.size(), 0);
+        for (size_t i = 0; i + 1 < phases.size(); ++i) {
+            uint64_t left = budget;
+            int slot = 0;
+            for (size_t j = i + 1; j < phases.size() && slot < 2 && left >= unit; ++j) {
+                if (phases[j].kind != MK_GEMV) continue;
+                const uint64_t run = (uint64_t)(phases[j].g.q + 1) * unit;   // the longest run of a warp
+                if (covered[j] >= run) continue;
+                const uint64_t upto = std::min(run, covered[j] + left);
+                phases[i].ahead_phase[slot] = (uint32_t)j;
+                phases[i].ahead_from[slot] = (uint32_t)covered[j];
+                phases[i].ahead_to[slot] = (uint32_t)upto;
+                left -= upto - covered[j];
+                covered[j] = upto;
+                ++slot;
+            }
+        }
+    }
     NC_TRY(decoder_alloc(d, partial_cells * sizeof(float), false, (void **)&partial));
     for (MkPhase &ph : phases)
         if (ph.kind == MK_GEMV) ph.g.partial = partial;
     MkPhase *table = nullptr;
+    NC_TRY(decoder_alloc(d, (phases.size() + 1) * sizeof(unsigned long long), true, (void **)&trace));
+    for (const MkPhase &ph : phases) d->kinds.push_back(ph.kind);
     NC_TRY(decoder_alloc(d, phases.size() * sizeof(MkPhase), false, (void **)&table));
     cudaError_t e = cudaMemcpy(table, phases.data(), phases.size() * sizeof(MkPhase), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) return fail(cuda_refuse(e, "cudaMemcpy of the phase table"));
@@ -1365,12 +1420,15 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     p.scale = c.scale;
     p.rope_base = c.rope_base;
     p.floor = c.floor;
-    p.dig = dig;
-    p.cs = cs;
-    p.sums = sums;
     p.slice_value = slice_value;
     p.slice_index = slice_index;
     p.argmax_counters = argmax_counters;
+    p.trace = trace;
+    p.detail = nullptr;
+    if (getenv("NEURA_MK_DETAIL")) {
+        unsigned long long *detail = nullptr;
+        if (decoder_alloc(d, phases.size() * 4 * sizeof(unsigned long long), true, (void **)&detail) == 0) p.detail = detail;
+    }
 
     // the kernel must be resident on every SM at once
     const void *kernel = q4k ? (const void *)decode_megakernel<true> : (const void *)decode_megakernel<false>;
@@ -1384,10 +1442,34 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     return 0;
 }
 
+int32_t neura_cuda_decoder_trace(nc_context *ctx, nc_decoder *decoder, uint32_t capacity, uint32_t *kinds_out,
+                                 uint64_t *nanos_out, uint32_t *phases_out) {
+    if (!ctx || !decoder || !phases_out) return refuse(kBadArgument, "a trace needs a context, a decoder and somewhere to put the count");
+    const uint32_t phases = (uint32_t)decoder->kinds.size();
+    *phases_out = phases;
+    if (!kinds_out || !nanos_out || capacity < phases) return 0;   // the caller asked for the count
+    std::vector<unsigned long long> stamps(phases + 1);
+    NC_CUDA(cudaMemcpy(stamps.data(), decoder->params.trace, stamps.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    for (uint32_t i = 0; i < phases; ++i) {
+        kinds_out[i] = decoder->kinds[i];
+        nanos_out[i] = stamps[i + 1] >= stamps[i] ? stamps[i + 1] - stamps[i] : 0;
+    }
+    if (decoder->params.detail) {   // NEURA_MK_DETAIL: the finer stamps, one line a phase, on stderr
+        std::vector<unsigned long long> detail((size_t)phases * 4);
+        NC_CUDA(cudaMemcpy(detail.data(), decoder->params.detail, detail.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        for (uint32_t i = 0; i < phases; ++i) {
+            auto since = [&](unsigned long long t) { return t >= stamps[i] ? (double)(t - stamps[i]) / 1e3 : -1.0; };
+            fprintf(stderr, "phase %u kind %u: staged %.2f streamed %.2f cta0 %.2f last-cta %.2f next %.2f us\n", i, decoder->kinds[i],
+                    since(detail[i * 4]), since(detail[i * 4 + 1]), since(detail[i * 4 + 2]), since(detail[i * 4 + 3]), since(stamps[i + 1]));
+        }
+    }
+    return 0;
+}
+
 int32_t neura_cuda_decoder_step(nc_context *ctx, void *stream_, nc_decoder *decoder) {
     if (!ctx || !decoder) return refuse(kBadArgument, "a step needs a context and a compiled decoder");
     cudaStream_t stream = (cudaStream_t)stream_;
-    NC_CUDA(cudaMemsetAsync(decoder->params.barrier, 0, sizeof(unsigned int), stream));
+    NC_CUDA(cudaMemsetAsync(decoder->params.barrier, 0, 256, stream));
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(decoder->grid);
     config.blockDim = dim3(kMkThreads);

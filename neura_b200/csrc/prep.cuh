@@ -144,6 +144,62 @@ __device__ __forceinline__ void load_chunk(const PrepParams &p, uint32_t row, ui
     }
 }
 
+// Staging by the producer.  In a persistent kernel the rows a product (or the attention merge) writes are the
+// activations of the next product.  Instead of a staging pass of its own, the warp that completes the last
+// tile of a 256-column chunk digitises that chunk at once (every chunk has a counter of finished tiles), so
+// the next product finds its operand ready after one barrier.  With `gain` the chunk is multiplied by the
+// coming rms_norm's weight first and the chunk's sum of squares is left in `sumsq`: the norm's scalar
+// 1 / sqrt(mean(x^2) + floor) is applied by the consumer to its outputs (a product is linear in a row scale).
+struct StageAfter {
+    PrepParams prep;         // x = the rows being produced, k = their width, dig/cs/sums = the consumer's operand
+    const float *gain;       // [k] or null
+    float *sumsq;            // [rows][chunks] or null
+    unsigned int *counters;  // [rows][chunks] finished pieces, zero between launches
+    uint32_t piece;          // columns one arrival covers (a tile's 32, a pair tile's 16)
+};
+
+// Digitises chunk `chunk` of row `row` from the produced values (the whole warp calls).
+__device__ __forceinline__ void stage_after_chunk(const StageAfter &a, uint32_t row, uint32_t chunk) {
+    const uint32_t lane = threadIdx.x & 31, from = chunk * 256 + lane * 8;
+    const bool live = from < a.prep.k;
+    float v[8];
+    load_chunk(a.prep, row, from, live, v);
+    if (a.sumsq) {
+        float square = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) square = fmaf(v[j], v[j], square);
+        for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+        if (lane == 0) __stcg(a.sumsq + row * ((a.prep.k + 255) / 256) + chunk, square);
+    }
+    if (a.gain && live) {
+        const float4 g0 = __ldg(reinterpret_cast<const float4 *>(a.gain + from));
+        const float4 g1 = __ldg(reinterpret_cast<const float4 *>(a.gain + from + 4));
+        v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w;
+        v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
+    }
+    stage_chunk(a.prep, row, chunk, v, live);
+}
+
+// Columns [first, first + a.piece) of every row are final (the whole warp calls, after a __syncwarp that
+// follows its stores).  Counts the arrival; the warp that completes a chunk digitises it for all rows.
+__device__ __forceinline__ void stage_after_piece(const StageAfter &a, uint32_t first) {
+    const uint32_t lane = threadIdx.x & 31;
+    if (first >= a.prep.k) return;
+    const uint32_t chunk = first / 256;
+    const uint32_t width = min(a.prep.k, (chunk + 1) * 256) - chunk * 256;
+    const uint32_t expected = (width + a.piece - 1) / a.piece;
+    unsigned int seen = 0;
+    if (lane == 0) {
+        __threadfence();
+        seen = atomicAdd(a.counters + chunk, 1u);
+        __threadfence();
+    }
+    seen = __shfl_sync(0xffffffffu, seen, 0);
+    if (seen != expected - 1) return;
+    for (uint32_t row = 0; row < a.prep.rows; ++row) stage_after_chunk(a, row, chunk);
+    if (lane == 0) a.counters[chunk] = 0u;
+}
+
 // One warp per (row, 256-element chunk): lane l owns elements [8l, 8l+8) of the chunk.
 __global__ void prep_kernel(const __grid_constant__ PrepParams p) {
     // Programmatic dependent launch: the product that follows may start fetching its

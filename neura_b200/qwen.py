@@ -257,6 +257,22 @@ class Decoder:
         _check(self.rt._lib.neura_cuda_decoder_compile(self.rt._ctx, ctypes.byref(desc), ctypes.byref(handle)))
         self.compiled = handle
 
+    def trace(self):
+        """(kinds, nanoseconds) per phase of the last completed persistent step."""
+        import ctypes
+
+        import numpy as np
+
+        from .runtime import _check
+
+        self.rt.sync()
+        count = ctypes.c_uint32()
+        _check(self.rt._lib.neura_cuda_decoder_trace(self.rt._ctx, self.compiled, 0, None, None, ctypes.byref(count)))
+        kinds, nanos = np.zeros(count.value, np.uint32), np.zeros(count.value, np.uint64)
+        _check(self.rt._lib.neura_cuda_decoder_trace(self.rt._ctx, self.compiled, count.value, kinds.ctypes.data,
+                                                     nanos.ctypes.data, ctypes.byref(count)))
+        return kinds, nanos
+
     def release(self) -> None:
         if self.compiled is not None:
             self.rt._lib.neura_cuda_decoder_free(self.rt._ctx, self.compiled)
