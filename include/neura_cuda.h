@@ -226,6 +226,20 @@ int32_t neura_cuda_argmax(nc_context *ctx, void *stream, const float *x_dev, uin
 int32_t neura_cuda_argmax_segments(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint32_t width,
                                    uint64_t stride, uint32_t segment, uint64_t segment_stride, uint32_t *out_dev);
 
+/* The angles of one decode step: table_dev[b][c] = (cosine, sine) of position_dev[b] in channel c < width / 2
+ * (the angle of rope.rs:48-122).  They are the same in every layer, so a step computes them once. */
+int32_t neura_cuda_rope_table(nc_context *ctx, void *stream, const uint32_t *position_dev, float base, uint32_t batch,
+                              uint32_t width, float *table_dev);
+
+/* neura_cuda_rope_cache and neura_cuda_attend as one launch: `qkv_dev` holds the un-turned q | k | v rows of this
+ * step (they are left as they are); the queries are turned by table_dev (neura_cuda_rope_table) as the kernel loads
+ * them, and the new key (turned) and value go to slot position_dev[b] of the cache before the row attends to
+ * positions 0..position_dev[b].  Bit for bit what the two launches give. */
+int32_t neura_cuda_rope_attend(nc_context *ctx, void *stream, const float *qkv_dev, uint64_t row_stride,
+                               const uint32_t *position_dev, const float *table_dev, float scale, uint32_t batch,
+                               uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
+                               float *values_dev, float *out_dev, uint64_t out_stride);
+
 /* graph.gather of a quantised embedding table (crates/neura-kernel/src/task/select.rs:29-49 with
  * fetch_q8_0 / fetch_q4_k, fetch.rs:236-267): out[r] = dequantised row tokens_dev[r], bit-exact;
  * the table may be in either layout (a tied head is sealed). */
@@ -253,6 +267,11 @@ int32_t neura_cuda_comm_destroy(nc_context *ctx, nc_comm *comm);
  * leaves its input untouched and the next neura_cuda_sync returns the refusal.  Every rank must
  * issue the same calls in the same order.  `count` is a multiple of 4, `inout_dev` 16-byte aligned. */
 int32_t neura_cuda_allreduce(nc_context *ctx, void *stream, nc_comm *comm, float *inout_dev, uint32_t count);
+
+/* neura_cuda_allreduce of `rows` rows of `k` numbers followed, in the same launch, by neura_cuda_rms_norm_stage
+ * of the summed rows (a row-parallel projection is followed by the next block's norm in every decoder layer). */
+int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream, nc_comm *comm, float *inout_dev, uint32_t rows,
+                                        uint32_t k, const float *weight_dev, float floor, uint32_t element);
 
 /* No counterpart in the reference.  neura_cuda_linear for callers that may not touch the
  * device allocator: a game loop stepping generation under a frame budget (where a

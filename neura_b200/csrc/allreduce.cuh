@@ -12,6 +12,7 @@
 #pragma once
 #include "common.cuh"
 #include "gemv_mma.cuh"
+#include "prep.cuh"
 
 namespace nc {
 
@@ -45,10 +46,8 @@ __device__ __forceinline__ void store_peer16(float *p, float4 v) {
     asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-// One CTA; count is a multiple of 4.
-__global__ void __launch_bounds__(1024) allreduce_kernel(const __grid_constant__ AllreduceParams p) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+// One CTA; count is a multiple of 4.  Returns false when the wait for the peers ran out.
+__device__ __forceinline__ bool allreduce_body(const AllreduceParams &p) {
     __shared__ unsigned int gave_up;
     unsigned int *counter = reinterpret_cast<unsigned int *>(p.mine);
     const unsigned int seq = *counter + 1u;
@@ -76,7 +75,7 @@ __global__ void __launch_bounds__(1024) allreduce_kernel(const __grid_constant__
     __syncthreads();
     if (gave_up) {
         if (threadIdx.x == 0) atomicOr(p.status, 4u);
-        return;   // the counter stays: the next call repeats this sequence number
+        return false;   // the counter stays: the next call repeats this sequence number
     }
     for (uint32_t i = threadIdx.x * 4; i < p.count; i += blockDim.x * 4) {
         float4 part[kMaxRanks];
@@ -95,6 +94,29 @@ __global__ void __launch_bounds__(1024) allreduce_kernel(const __grid_constant__
     }
     __syncthreads();
     if (threadIdx.x == 0) *counter = seq;
+    return true;
+}
+
+__global__ void __launch_bounds__(1024) allreduce_kernel(const __grid_constant__ AllreduceParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    allreduce_body(p);
+}
+
+// The all-reduce of a row-parallel projection's partial sums followed, in the same launch, by the rms_norm of the
+// summed rows and their staging for the next product (prep.cuh): the CTA that added the rows up has them at hand.
+__global__ void __launch_bounds__(1024) allreduce_norm_stage_kernel(const __grid_constant__ AllreduceParams p,
+                                                                     const __grid_constant__ NormStageParams then) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float partial[32];
+    __shared__ float scale_shared;
+    if (!allreduce_body(p)) return;
+    __syncthreads();
+    for (uint32_t row = 0; row < then.prep.rows; ++row) {
+        rms_norm_stage_row(then, row, partial, &scale_shared);
+        __syncthreads();
+    }
 }
 
 }  // namespace nc

@@ -21,6 +21,34 @@ struct RopeCacheParams {
     uint32_t batch, heads, key_heads, width, capacity;
 };
 
+// Half-rotation of one channel pair by (cosine, sine), every rounding pinned so that all callers agree bit for bit.
+__device__ __forceinline__ float2 rope_turn(float low, float high, float cosine, float sine) {
+    return make_float2(__fmaf_rn(low, cosine, -__fmul_rn(high, sine)), __fmaf_rn(high, cosine, __fmul_rn(low, sine)));
+}
+
+// (cosine, sine) of a position's angle in one channel, out of line: the slow paths of powf, cosf and sinf want a
+// stack frame that the callers' loops should not carry.
+__device__ __noinline__ float2 rope_angle(uint32_t position, uint32_t channel, uint32_t width, float base) {
+    const float angle = (float)position * powf(base, -2.0f * (float)channel / (float)width);
+    return make_float2(cosf(angle), sinf(angle));
+}
+
+__device__ __forceinline__ float2 rope_pair(float low, float high, uint32_t position, uint32_t channel, uint32_t width,
+                                            float base) {
+    const float2 turn = rope_angle(position, channel, width, base);
+    return rope_turn(low, high, turn.x, turn.y);
+}
+
+// The angles of one decode step: table[b][channel] = (cosine, sine) of position[b] in that channel.  They are the
+// same in every layer, so a step computes them once (rope_attend reads them).
+__global__ void rope_table_kernel(const uint32_t *position, float base, uint32_t batch, uint32_t width, float2 *table) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t half = width / 2;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < batch * half; i += gridDim.x * blockDim.x)
+        table[i] = rope_angle(position[i / half], i % half, width, base);
+}
+
 __global__ void rope_cache_kernel(const __grid_constant__ RopeCacheParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -35,11 +63,8 @@ __global__ void rope_cache_kernel(const __grid_constant__ RopeCacheParams p) {
         if (at < turned) {
             const uint32_t head = at / half, channel = at % half;
             float *v = row + (uint64_t)head * p.width;   // key heads follow the query heads in the row
-            const float angle = (float)position * powf(p.base, -2.0f * (float)channel / (float)p.width);
-            const float cosine = cosf(angle), sine = sinf(angle);
-            const float low = v[channel], high = v[channel + half];
-            const float new_low = low * cosine - high * sine;
-            const float new_high = high * cosine + low * sine;
+            const float2 turned = rope_pair(v[channel], v[channel + half], position, channel, p.width, p.base);
+            const float new_low = turned.x, new_high = turned.y;
             v[channel] = new_low;
             v[channel + half] = new_high;
             if (head >= p.heads && position < p.capacity) {
@@ -80,6 +105,11 @@ struct AttendParams {
     unsigned int *counters;   // [batch][key_heads], zero between launches
     float scale;
     uint32_t batch, heads, key_heads, width, capacity, splits;
+    // rope_cache_kernel folded in: when `fresh` is not null, q points at the un-turned q | k | v rows of this
+    // step; the queries are turned as they are loaded, and the split that holds the new position turns the new
+    // key and puts it and the new value into its tile and into the cache (`fresh` = the cache, writable)
+    float *fresh_keys, *fresh_values;
+    const float2 *rope_table;   // [batch][width / 2] (cosine, sine) of each sequence's position (rope_table_kernel)
 };
 
 __device__ __forceinline__ void copy16_async(void *dst_shared, const void *src_global) {
@@ -118,14 +148,50 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     const uint32_t first = min(split * chunk, count), last = min(first + chunk, count), held = last - first;
     const float *k = p.keys + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
     const float *v = p.values + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
+    const uint32_t position = p.position[b];
+    const bool turning = p.fresh_keys != nullptr;
+    const bool fresh = turning && position < p.capacity && position >= first && position < last;  // the new row is ours
+    const uint32_t fresh_row = position - first;
     for (uint32_t i = threadIdx.x; i < held * (WIDTH / 4); i += blockDim.x) {
         const uint32_t row = i / (WIDTH / 4), quad = i % (WIDTH / 4);
+        if (fresh && row == fresh_row) continue;
         copy16_async(ks + row * KROW + quad * 4, k + i * 4);
         copy16_async(vs + i * 4, v + i * 4);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    for (uint32_t i = threadIdx.x; i < group * WIDTH; i += blockDim.x)
-        qs[i] = p.q[(uint64_t)b * p.q_stride + (uint64_t)(kh * group) * WIDTH + i];
+    if (turning) {
+        constexpr uint32_t HALF = WIDTH / 2;
+        const float *row_qkv = p.q + (uint64_t)b * p.q_stride;
+        for (uint32_t i = threadIdx.x; i < group * HALF; i += blockDim.x) {
+            const uint32_t g = i / HALF, c = i % HALF;
+            const float *q = row_qkv + (uint64_t)(kh * group + g) * WIDTH;
+            const float2 turn = p.rope_table[b * HALF + c];
+            const float2 turned = rope_turn(q[c], q[c + HALF], turn.x, turn.y);
+            qs[g * WIDTH + c] = turned.x;
+            qs[g * WIDTH + c + HALF] = turned.y;
+        }
+        if (fresh) {
+            const float *nk = row_qkv + (uint64_t)(p.heads + kh) * WIDTH;
+            const float *nv = row_qkv + (uint64_t)(p.heads + p.key_heads + kh) * WIDTH;
+            const uint64_t slot = (((uint64_t)b * p.key_heads + kh) * p.capacity + position) * WIDTH;
+            for (uint32_t i = blockDim.x - 1 - threadIdx.x; i < HALF; i += blockDim.x) {   // (the threads the queries use least)
+                const float2 turn = p.rope_table[b * HALF + i];
+                const float2 turned = rope_turn(nk[i], nk[i + HALF], turn.x, turn.y);
+                ks[fresh_row * KROW + i] = turned.x;
+                ks[fresh_row * KROW + i + HALF] = turned.y;
+                p.fresh_keys[slot + i] = turned.x;
+                p.fresh_keys[slot + i + HALF] = turned.y;
+            }
+            for (uint32_t i = blockDim.x - 1 - threadIdx.x; i < WIDTH; i += blockDim.x) {
+                const float value = nv[i];
+                vs[fresh_row * WIDTH + i] = value;
+                p.fresh_values[slot + i] = value;
+            }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < group * WIDTH; i += blockDim.x)
+            qs[i] = p.q[(uint64_t)b * p.q_stride + (uint64_t)(kh * group) * WIDTH + i];
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     // logits of this split: one thread per (query head, position), the whole dot product in registers

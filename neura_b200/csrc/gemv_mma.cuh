@@ -434,7 +434,7 @@ struct GemvWarp {
 
 template <bool Q4K, int NT, int STAGES>
 __global__ void __launch_bounds__(kGemvWarps * 32, NT <= 1 ? 4 : 1) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
-    static_assert(STAGES == 2 && kQ8Group == 4, "a pair of steps is unrolled by hand, and so are the four units of a Q8_0 stage");
+    static_assert(STAGES >= 2 && kQ8Group == 4, "the four units of a Q8_0 stage are unrolled by hand");
     constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
     constexpr uint32_t kUnit = Q4K ? kQ4kStage : 2 * kQ8Unit;  // bytes of one 32-row unit
     constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;            // units per stage

@@ -50,8 +50,6 @@ struct MkPhase {
     float *out;              // MK_EMBED: rows of `out_stride`
     uint64_t out_stride;
     uint32_t lo, hi;         // MK_STAGE: the input is elements [lo, hi) of K, zero elsewhere
-    // when this phase ends, bytes [from, to) of every warp's run in product `ahead_phase[i]` are asked into L2
-    uint32_t ahead_phase[2], ahead_from[2], ahead_to[2];
 };
 
 struct MkParams {
@@ -70,13 +68,12 @@ struct MkParams {
     unsigned int *attend_counters;  // [rows][key_heads], zero between launches
     uint32_t heads, key_heads, width, capacity, max_splits;
     float scale, rope_base, floor;
+    float2 *rope_table;          // [rows][width / 2]: the step's angles, written by the embedding phase
     // argmax
     float *slice_value;          // [rows][gridDim.x]
     uint32_t *slice_index;
     unsigned int *argmax_counters;  // [rows], zero between launches
     unsigned long long *trace;   // [nphases + 1]: %globaltimer as CTA 0 enters each phase, and as it leaves the last
-    unsigned long long *detail;  // [nphases][4] or null: CTA 0's clock when its warp 0 is done with the phase ([1]),
-                                 // when all its warps are ([2]), and when the last CTA's are ([3])
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
@@ -205,25 +202,6 @@ __device__ __forceinline__ void mk_prefetch(const MkParams &p, uint32_t next, Mk
     __syncwarp();
 }
 
-// Before a barrier: ask the head of the coming products' weights into L2, so that HBM keeps streaming while
-// the grid meets at the barrier and stages its activations (shared memory holds two stages a warp, L2 holds
-// tens of MB).  Lane l asks for the l-th piece of 4 KB of its warp's range.
-template <bool Q4K>
-__device__ __forceinline__ void mk_prefetch_l2(const MkParams &p, const MkPhase &ph) {
-    const uint32_t lane = threadIdx.x & 31, warp = mk_warp();
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        if (ph.ahead_phase[i] == kMkNone) continue;
-        const GemvParams &g = p.phases[ph.ahead_phase[i]].g;
-        const MkRun run = mk_run_of<Q4K>(g.w, g.nwarps, g.q, g.r, warp);
-        const uint64_t to = min((uint64_t)ph.ahead_to[i], run.bytes);
-        for (uint64_t at = (uint64_t)ph.ahead_from[i] + (uint64_t)lane * 4096; at < to; at += 32 * 4096) {
-            const uint32_t len = (uint32_t)min((uint64_t)4096, to - at);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(run.src + at), "r"(len) : "memory");
-        }
-    }
-}
-
 template <bool Q4K>
 __device__ __forceinline__ bool mk_stream(const GemvParams &g, MkRing &rg, const MkRun &run, float *patch, uint32_t warp,
                                           float scale0, float scale1) {
@@ -299,15 +277,6 @@ __device__ __noinline__ void mk_gemv(const MkParams &p, const MkPhase &ph, uint3
 }
 
 // ---- attention -----------------------------------------------------------------------------------------
-// Half-rotation RoPE of one channel pair (crates/neura-kernel/src/task/rope.rs:48-122), out of line: the
-// slow paths of powf, cosf and sinf want a stack frame the streaming loops should not carry.
-__device__ __noinline__ float2 mk_rope_pair(float low, float high, uint32_t position, uint32_t channel, uint32_t width,
-                                            float base) {
-    const float angle = (float)position * powf(base, -2.0f * (float)channel / (float)width);
-    const float cosine = cosf(angle), sine = sinf(angle);
-    return make_float2(low * cosine - high * sine, high * cosine + low * sine);
-}
-
 // rope_cache_kernel and attend_kernel of decoder_ops.cuh as one phase.  An item is (sequence, key head,
 // split of kMkTile cached positions); items are dealt round-robin to the CTAs.  Every item turns the
 // query heads of its key head itself; the item whose split holds the new position turns the new key,
@@ -343,7 +312,8 @@ __device__ __forceinline__ void mk_attend_item(const MkParams &p, const MkPhase 
     for (uint32_t i = threadIdx.x; i < group * HALF; i += blockDim.x) {
         const uint32_t g = i / HALF, c = i % HALF;
         const float *q = row_qkv + (uint64_t)(kh * group + g) * WIDTH;
-        const float2 turned = mk_rope_pair(__ldcg(q + c), __ldcg(q + c + HALF), position, c, WIDTH, p.rope_base);
+        const float2 turn = __ldcg(p.rope_table + b * HALF + c);
+        const float2 turned = rope_turn(__ldcg(q + c), __ldcg(q + c + HALF), turn.x, turn.y);
         qs[g * WIDTH + c] = turned.x;
         qs[g * WIDTH + c + HALF] = turned.y;
     }
@@ -353,7 +323,8 @@ __device__ __forceinline__ void mk_attend_item(const MkParams &p, const MkPhase 
         float *cache_k = ph.keys + (slot0 + position) * WIDTH, *cache_v = ph.values + (slot0 + position) * WIDTH;
         // (the last threads of the CTA, so that they do not queue behind the query turns)
         for (uint32_t i = blockDim.x - 1 - threadIdx.x; i < HALF; i += blockDim.x) {
-            const float2 turned = mk_rope_pair(__ldcg(nk + i), __ldcg(nk + i + HALF), position, i, WIDTH, p.rope_base);
+            const float2 turn = __ldcg(p.rope_table + b * HALF + i);
+            const float2 turned = rope_turn(__ldcg(nk + i), __ldcg(nk + i + HALF), turn.x, turn.y);
             ks[fresh_row * KROW + i] = turned.x;
             ks[fresh_row * KROW + i + HALF] = turned.y;
             cache_k[i] = turned.x;
@@ -508,6 +479,12 @@ __device__ __forceinline__ void mk_embed(const MkParams &p, const MkPhase &ph) {
         const uint32_t row = min(__ldcg(p.tokens + r), ph.table.n - 1);
         ph.out[(uint64_t)r * ph.out_stride + at] = dequant_at(ph.table, row, at);
     }
+    // the step's RoPE angles, the same in every layer (the last CTA has the least to gather)
+    if (blockIdx.x == gridDim.x - 1) {
+        const uint32_t half = p.width / 2;
+        for (uint32_t i = threadIdx.x; i < p.rows * half; i += blockDim.x)
+            p.rope_table[i] = rope_angle(__ldcg(p.position + i / half), i % half, p.width, p.rope_base);
+    }
 }
 
 // argmax_kernel and advance_kernel as the last phase: every CTA takes a slice of every row, the last CTA
@@ -600,15 +577,9 @@ __global__ void __launch_bounds__(kMkThreads, 1) decode_megakernel(const __grid_
         case MK_ARGMAX: mk_argmax(p, phase, reduce, best_index, &arrived); break;
         default: break;
         }
-        if (p.detail && blockIdx.x == 0 && threadIdx.x == 0) p.detail[index * 4 + 1] = global_nanos();
         if (index + 1 == p.nphases) break;   // nothing follows the last phase
         __syncthreads();                     // the CTA is done with the ring and with `phase`
-        if (p.detail && threadIdx.x == 0) {
-            if (blockIdx.x == 0) p.detail[index * 4 + 2] = global_nanos();
-            if (blockIdx.x == gridDim.x - 1) p.detail[index * 4 + 3] = global_nanos();
-        }
         mk_prefetch<Q4K>(p, phase.prefetch, rg);
-        mk_prefetch_l2<Q4K>(p, phase);
         if (!mk_barrier(p, index + 1, &aborted)) break;
     }
     if (blockIdx.x == 0 && threadIdx.x == 0) p.trace[p.nphases] = global_nanos();

@@ -133,7 +133,10 @@ GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t
     return plan;
 }
 
-constexpr int kStages = 2;
+#ifndef NC_GEMV_STAGES
+#define NC_GEMV_STAGES 2
+#endif
+constexpr int kStages = NC_GEMV_STAGES;   // ring depth of the streaming product (stages a warp)
 
 // Launches with the programmatic-stream-serialization attribute, so that a kernel's
 // prologue (for the product: its first weight copies) overlaps the tail of the kernel
@@ -646,9 +649,14 @@ int32_t neura_cuda_linear_host(nc_context *ctx, void *stream_, const nc_weight *
     return check_status(ctx);
 }
 
-int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
-                                  uint32_t k, const float *weight_dev, float floor, uint32_t element,
-                                  float *normed_dev, uint64_t normed_stride) {
+}  // extern "C"
+
+namespace {
+
+// Checks the rows of an rms_norm + staging and fills its parameters (the scratch may grow).
+int32_t norm_stage_params(nc_context *ctx, const float *x_dev, uint32_t rows, uint64_t x_stride, uint32_t k,
+                          const float *weight_dev, float floor, uint32_t element, float *normed_dev,
+                          uint64_t normed_stride, NormStageParams &p) {
     if (!ctx || !x_dev) return refuse(kBadArgument, "a norm needs a context and a row to norm");
     const uint32_t per = block_elements(element);
     if (!per || !k || k % per)
@@ -664,7 +672,6 @@ int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x
     if ((rc = ensure(ctx, ctx->dig, kpad * ncols, false))) return rc;
     if ((rc = ensure(ctx, ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
     if ((rc = ensure(ctx, ctx->sums, kpad / 256 * ncols * 64, false))) return rc;
-    NormStageParams p;
     p.prep.x = x_dev;
     p.prep.x_stride = x_stride;
     p.prep.dig = (int8_t *)ctx->dig.ptr;
@@ -681,6 +688,20 @@ int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x
     p.normed = normed_dev;
     p.normed_stride = normed_stride;
     p.floor = floor;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                                  uint32_t k, const float *weight_dev, float floor, uint32_t element,
+                                  float *normed_dev, uint64_t normed_stride) {
+    NormStageParams p;
+    int32_t rc;
+    if ((rc = norm_stage_params(ctx, x_dev, rows, x_stride, k, weight_dev, floor, element, normed_dev, normed_stride, p)))
+        return rc;
     NC_CUDA(launch_dependent(rms_norm_stage_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream_, p));
     ctx->launches++;
     ctx->staged_rows = rows;
@@ -707,10 +728,16 @@ int32_t neura_cuda_rope_cache(nc_context *ctx, void *stream_, float *qkv_dev, ui
     return 0;
 }
 
-int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, uint64_t q_stride, const float *keys_dev,
-                          const float *values_dev, const uint32_t *position_dev, float scale, uint32_t batch,
-                          uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
-                          uint64_t out_stride) {
+}  // extern "C"
+
+namespace {
+
+// Attention of one new row per sequence; with `fresh_keys` the rows at q_dev are the un-turned q | k | v of this
+// step and the kernel turns them and writes the cache itself.
+int32_t attend_any(nc_context *ctx, void *stream_, const float *q_dev, uint64_t q_stride, const float *keys_dev,
+                   const float *values_dev, const uint32_t *position_dev, float scale, uint32_t batch, uint32_t heads,
+                   uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev, uint64_t out_stride,
+                   float *fresh_keys, float *fresh_values, const float2 *rope_table) {
     if (!ctx || !q_dev || !keys_dev || !values_dev || !position_dev || !out_dev)
         return refuse(kBadArgument, "attention needs a context, queries, a cache, positions and an output");
     if (!batch || !heads || !key_heads || heads % key_heads || !width || !capacity)
@@ -753,7 +780,7 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, ui
     }
     AttendParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride,
                    (float *)ctx->attend_partial.ptr, (unsigned int *)ctx->attend_counters.ptr, scale,
-                   batch, heads, key_heads, width, capacity, splits};
+                   batch, heads, key_heads, width, capacity, splits, fresh_keys, fresh_values, rope_table};
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(batch * key_heads * splits);
     config.blockDim = dim3(128);
@@ -771,6 +798,40 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream_, const float *q_dev, ui
     NC_CUDA(cudaLaunchKernelEx(&config, kernel, p));
     ctx->launches++;
     return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t neura_cuda_attend(nc_context *ctx, void *stream, const float *q_dev, uint64_t q_stride, const float *keys_dev,
+                          const float *values_dev, const uint32_t *position_dev, float scale, uint32_t batch,
+                          uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
+                          uint64_t out_stride) {
+    return attend_any(ctx, stream, q_dev, q_stride, keys_dev, values_dev, position_dev, scale, batch, heads, key_heads,
+                      width, capacity, out_dev, out_stride, nullptr, nullptr, nullptr);
+}
+
+int32_t neura_cuda_rope_table(nc_context *ctx, void *stream, const uint32_t *position_dev, float base, uint32_t batch,
+                              uint32_t width, float *table_dev) {
+    if (!ctx || !position_dev || !table_dev || !batch || !width || width % 2)
+        return refuse(kBadArgument, "the angles need a context, cursors, an even head width and a table");
+    if ((uintptr_t)table_dev % 8) return refuse(kBadArgument, "the table of (cosine, sine) pairs starts on an 8-byte boundary");
+    const uint32_t total = batch * (width / 2);
+    NC_CUDA(launch_dependent(rope_table_kernel, dim3((total + 63) / 64), dim3(64), 0, (cudaStream_t)stream, position_dev, base,
+                             batch, width, (float2 *)table_dev));
+    ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_rope_attend(nc_context *ctx, void *stream, const float *qkv_dev, uint64_t row_stride,
+                               const uint32_t *position_dev, const float *table_dev, float scale, uint32_t batch,
+                               uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
+                               float *values_dev, float *out_dev, uint64_t out_stride) {
+    if (!keys_dev || !values_dev || !table_dev)
+        return refuse(kBadArgument, "attention needs the cache it writes the new row to and the step's angles");
+    return attend_any(ctx, stream, qkv_dev, row_stride, keys_dev, values_dev, position_dev, scale, batch, heads, key_heads,
+                      width, capacity, out_dev, out_stride, keys_dev, values_dev, (const float2 *)table_dev);
 }
 
 int32_t neura_cuda_argmax_segments(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint32_t width,
@@ -889,6 +950,36 @@ int32_t neura_cuda_allreduce(nc_context *ctx, void *stream_, nc_comm *comm, floa
     const unsigned int threads = count / 4 >= 1024 ? 1024 : ((count / 4 + 31) / 32 * 32 < 32 ? 32 : (count / 4 + 31) / 32 * 32);
     NC_CUDA(launch_dependent(allreduce_kernel, dim3(1), dim3(threads), 0, (cudaStream_t)stream_, p));
     ctx->launches++;
+    return 0;
+}
+
+int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream_, nc_comm *comm, float *inout_dev, uint32_t rows,
+                                        uint32_t k, const float *weight_dev, float floor, uint32_t element) {
+    if (!ctx || !comm || !inout_dev || !rows || !k) return refuse(kBadArgument, "an all-reduce needs a context, a communicator and rows");
+    if (!comm->connected) return refuse(kBadState, "the communicator is not connected to its peers");
+    const uint64_t count = (uint64_t)rows * k;
+    if (count % 4 || count > comm->max_count || (uintptr_t)inout_dev % 16)
+        return refuse(kBadArgument, "an all-reduce takes a 16-byte aligned multiple of 4 numbers, at most %llu (got %llu)",
+                      (unsigned long long)comm->max_count, (unsigned long long)count);
+    NormStageParams then;
+    int32_t rc;
+    if ((rc = norm_stage_params(ctx, inout_dev, rows, k, k, weight_dev, floor, element, nullptr, 0, then))) return rc;
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
+    AllreduceParams p;
+    memset(&p, 0, sizeof p);
+    p.mine = comm->mine;
+    for (uint32_t r = 0; r < comm->world; ++r) p.peer[r] = comm->peer[r];
+    p.inout = inout_dev;
+    p.slot_bytes = comm->slot_bytes;
+    p.count = (uint32_t)count;
+    p.world = comm->world;
+    p.rank = comm->rank;
+    p.status = (unsigned int *)ctx->status.ptr;
+    NC_CUDA(launch_dependent(allreduce_norm_stage_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream_, p, then));
+    ctx->launches++;
+    ctx->staged_rows = rows;
+    ctx->staged_k = k;
+    ctx->staged_granule = then.prep.granule;
     return 0;
 }
 
@@ -1223,6 +1314,8 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * sizeof(unsigned int), true, (void **)&argmax_counters));
     NC_TRY(decoder_alloc(d, 256, true, (void **)&barrier));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * ((c.hidden + 255) / 256) * 4, true, (void **)&sumsq));
+    float2 *rope_table;
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * (c.head_width / 2) * sizeof(float2), true, (void **)&rope_table));
     unsigned long long *trace;
 
     // the staged form of each kind of activation row: what the products read (prep.cuh)
@@ -1258,7 +1351,6 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         memset(&ph, 0, sizeof ph);
         ph.kind = kind;
         ph.prefetch = kMkNone;
-        ph.ahead_phase[0] = ph.ahead_phase[1] = kMkNone;
         return ph;
     };
     // how the rows a phase writes become the operand of the next product
@@ -1362,30 +1454,6 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
             if (phases[j].kind == MK_GEMV) { phases[i].prefetch = (uint32_t)j; break; }
         }
     }
-    // ... and ask the head of the coming products' weights into L2: about 48 MB per phase boundary (what HBM
-    // moves while the grid is at a barrier and stages activations), never the same bytes twice
-    {
-        const char *knob = getenv("NEURA_MK_L2");
-        const uint64_t budget = knob ? (uint64_t)atoi(knob) * 1024 : 20 * 1024;   // bytes a warp asks for at one boundary
-        const uint64_t unit = q4k ? kQ4kStage : 2 * kQ8Unit;
-        std::vector<uint64_t> covered(phases.size(), 0);
-        for (size_t i = 0; i + 1 < phases.size(); ++i) {
-            uint64_t left = budget;
-            int slot = 0;
-            for (size_t j = i + 1; j < phases.size() && slot < 2 && left >= unit; ++j) {
-                if (phases[j].kind != MK_GEMV) continue;
-                const uint64_t run = (uint64_t)(phases[j].g.q + 1) * unit;   // the longest run of a warp
-                if (covered[j] >= run) continue;
-                const uint64_t upto = std::min(run, covered[j] + left);
-                phases[i].ahead_phase[slot] = (uint32_t)j;
-                phases[i].ahead_from[slot] = (uint32_t)covered[j];
-                phases[i].ahead_to[slot] = (uint32_t)upto;
-                left -= upto - covered[j];
-                covered[j] = upto;
-                ++slot;
-            }
-        }
-    }
     NC_TRY(decoder_alloc(d, partial_cells * sizeof(float), false, (void **)&partial));
     for (MkPhase &ph : phases)
         if (ph.kind == MK_GEMV) ph.g.partial = partial;
@@ -1420,15 +1488,11 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     p.scale = c.scale;
     p.rope_base = c.rope_base;
     p.floor = c.floor;
+    p.rope_table = rope_table;
     p.slice_value = slice_value;
     p.slice_index = slice_index;
     p.argmax_counters = argmax_counters;
     p.trace = trace;
-    p.detail = nullptr;
-    if (getenv("NEURA_MK_DETAIL")) {
-        unsigned long long *detail = nullptr;
-        if (decoder_alloc(d, phases.size() * 4 * sizeof(unsigned long long), true, (void **)&detail) == 0) p.detail = detail;
-    }
 
     // the kernel must be resident on every SM at once
     const void *kernel = q4k ? (const void *)decode_megakernel<true> : (const void *)decode_megakernel<false>;
@@ -1453,15 +1517,6 @@ int32_t neura_cuda_decoder_trace(nc_context *ctx, nc_decoder *decoder, uint32_t 
     for (uint32_t i = 0; i < phases; ++i) {
         kinds_out[i] = decoder->kinds[i];
         nanos_out[i] = stamps[i + 1] >= stamps[i] ? stamps[i + 1] - stamps[i] : 0;
-    }
-    if (decoder->params.detail) {   // NEURA_MK_DETAIL: the finer stamps, one line a phase, on stderr
-        std::vector<unsigned long long> detail((size_t)phases * 4);
-        NC_CUDA(cudaMemcpy(detail.data(), decoder->params.detail, detail.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-        for (uint32_t i = 0; i < phases; ++i) {
-            auto since = [&](unsigned long long t) { return t >= stamps[i] ? (double)(t - stamps[i]) / 1e3 : -1.0; };
-            fprintf(stderr, "phase %u kind %u: staged %.2f streamed %.2f cta0 %.2f last-cta %.2f next %.2f us\n", i, decoder->kinds[i],
-                    since(detail[i * 4]), since(detail[i * 4 + 1]), since(detail[i * 4 + 2]), since(detail[i * 4 + 3]), since(stamps[i + 1]));
-        }
     }
     return 0;
 }

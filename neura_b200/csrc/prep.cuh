@@ -233,12 +233,9 @@ struct NormStageParams {
 
 constexpr uint32_t kNormChunksPerWarp = 4;   // 8 warps x 4 chunks x 256 = rows of up to 8192 stay in registers
 
-__global__ void __launch_bounds__(256) rms_norm_stage_kernel(const __grid_constant__ NormStageParams p) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ float partial[8];
-    __shared__ float scale_shared;
-    const uint32_t row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+// One row by one CTA (of at most 32 warps); `partial` holds a float a warp, `scale_shared` one float.
+__device__ __forceinline__ void rms_norm_stage_row(const NormStageParams &p, uint32_t row, float *partial, float *scale_shared) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const uint32_t chunks = (p.prep.k + 255) / 256;
     const bool held = chunks <= warps * kNormChunksPerWarp;
     // every load of the row is issued before the first use, so the row costs one memory round trip
@@ -264,10 +261,10 @@ __global__ void __launch_bounds__(256) rms_norm_stage_kernel(const __grid_consta
     if (threadIdx.x == 0) {
         float total = 0.0f;
         for (uint32_t w = 0; w < warps; ++w) total += partial[w];
-        scale_shared = 1.0f / sqrtf(total / (float)p.prep.k + p.floor);
+        *scale_shared = 1.0f / sqrtf(total / (float)p.prep.k + p.floor);
     }
     __syncthreads();
-    const float scale = scale_shared;
+    const float scale = *scale_shared;
 #pragma unroll
     for (uint32_t i = 0; i < kNormChunksPerWarp; ++i) {
         for (uint32_t chunk = warp + i * warps; chunk < chunks; chunk += held ? chunks : warps * kNormChunksPerWarp) {
@@ -298,6 +295,14 @@ __global__ void __launch_bounds__(256) rms_norm_stage_kernel(const __grid_consta
             stage_chunk(p.prep, row, chunk, w, live);
         }
     }
+}
+
+__global__ void __launch_bounds__(256) rms_norm_stage_kernel(const __grid_constant__ NormStageParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float partial[32];
+    __shared__ float scale_shared;
+    rms_norm_stage_row(p, blockIdx.x, partial, &scale_shared);
 }
 
 }  // namespace nc

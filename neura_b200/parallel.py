@@ -141,6 +141,11 @@ class TorchComm:
         with self.torch.cuda.stream(self.stream):
             self.dist.all_reduce(tensor)
 
+    def all_reduce_norm_stage(self, ptr: int, rows: int, k: int, weight_ptr: int, floor: float, element: int) -> bool:
+        """The all-reduce fused with the rms_norm and staging that follow it; False when this transport has no
+        such launch (the caller then issues the three separately)."""
+        return False
+
     def all_gather(self, dst_ptr: int, src_ptr: int, count: int) -> None:
         """dst [world][count] <- every rank's src [count]."""
         dst, src = self.view(dst_ptr, count * self.world), self.view(src_ptr, count)
@@ -226,3 +231,12 @@ class PeerComm(TorchComm):
         from .runtime import _check
 
         _check(self.rt._lib.neura_cuda_allreduce(self.rt._ctx, self.rt.stream, self.comm, ctypes.c_void_p(ptr), count))
+
+    def all_reduce_norm_stage(self, ptr: int, rows: int, k: int, weight_ptr: int, floor: float, element: int) -> bool:
+        import ctypes
+
+        from .runtime import _check
+
+        _check(self.rt._lib.neura_cuda_allreduce_norm_stage(self.rt._ctx, self.rt.stream, self.comm, ctypes.c_void_p(ptr),
+                                                            rows, k, ctypes.c_void_p(weight_ptr), floor, element))
+        return True

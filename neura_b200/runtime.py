@@ -356,6 +356,24 @@ class Runtime:
                                            ctypes.c_void_p(position.ptr), scale, batch, heads, key_heads, width,
                                            capacity, ctypes.c_void_p(out.ptr), out.shape[-1]))
 
+    def rope_table(self, position: DeviceTensor, base: float, width: int, table: DeviceTensor,
+                   batch: Optional[int] = None) -> None:
+        """The step's RoPE angles: table [batch, width / 2, 2] = (cosine, sine) of every sequence's position."""
+        batch = batch if batch is not None else position.shape[0]
+        _check(self._lib.neura_cuda_rope_table(self._ctx, self.stream, ctypes.c_void_p(position.ptr), base, batch, width,
+                                               ctypes.c_void_p(table.ptr)))
+
+    def rope_attend(self, qkv: DeviceTensor, position: DeviceTensor, table: DeviceTensor, scale: float, heads: int,
+                    key_heads: int, width: int, capacity: int, keys: DeviceTensor, values: DeviceTensor,
+                    out: DeviceTensor, batch: Optional[int] = None) -> None:
+        """``rope_cache`` and ``attend`` as one launch: ``qkv`` holds the un-turned rows and stays as it is;
+        ``table`` holds the step's angles (``rope_table``)."""
+        batch = batch if batch is not None else qkv.rows
+        _check(self._lib.neura_cuda_rope_attend(self._ctx, self.stream, ctypes.c_void_p(qkv.ptr), qkv.shape[-1],
+                                                ctypes.c_void_p(position.ptr), ctypes.c_void_p(table.ptr), scale, batch, heads, key_heads,
+                                                width, capacity, ctypes.c_void_p(keys.ptr), ctypes.c_void_p(values.ptr),
+                                                ctypes.c_void_p(out.ptr), out.shape[-1]))
+
     def argmax(self, x: DeviceTensor, out: DeviceTensor, rows: Optional[int] = None) -> None:
         rows = rows if rows is not None else x.rows
         _check(self._lib.neura_cuda_argmax(self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1],

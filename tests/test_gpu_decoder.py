@@ -284,3 +284,36 @@ def test_the_persistent_step_decodes_what_the_oracle_decodes(oracle, name, batch
         b, at = differs[0]
         pytest.fail(f"sequence {b} leaves the oracle at step {at}: {got[b, at]} for {want[b, at]}, "
                     f"the oracle's margin there is {margins[b, at]:.3e}")
+
+
+@pytest.mark.parametrize("heads,key_heads,width,capacity,positions", [
+    (6, 2, 64, 96, (0, 70)), (10, 2, 128, 600, (599, 301)), (4, 4, 128, 1100, (1099, 5)), (8, 2, 128, 64, (70, 63)),
+])
+def test_rope_and_attention_in_one_launch_equal_the_two_launches(runtime, oracle, heads, key_heads, width, capacity, positions):
+    batch = len(positions)
+    row = (heads + 2 * key_heads) * width
+    qkv = oracle.Stream(51).normal(batch * row).reshape(batch, row)
+    cache = batch * key_heads * capacity * width
+    filled_k = oracle.Stream(52).normal(cache)
+    filled_v = oracle.Stream(53).normal(cache)
+    position = np.array(positions, dtype=np.uint32)     # (70 in a cache of 64: the cache is full, nothing is written)
+    qd, pd = runtime.tensor(batch, row), runtime.tensor_u32(batch)
+    runtime.write(pd, position)
+    outs, caches = [], []
+    for fused in (False, True):
+        keys, values, out = runtime.tensor(cache), runtime.tensor(cache), runtime.tensor(batch, heads * width)
+        runtime.write(keys, filled_k)
+        runtime.write(values, filled_v)
+        runtime.write(qd, qkv)
+        if fused:
+            angles = runtime.tensor(batch, width // 2, 2)
+            runtime.rope_table(pd, 1e6, width, angles)
+            runtime.rope_attend(qd, pd, angles, 0.125, heads, key_heads, width, capacity, keys, values, out)
+            assert np.array_equal(bits(runtime.read(qd)), bits(qkv)), "the fused launch leaves q | k | v as they were"
+        else:
+            runtime.rope_cache(qd, pd, 1e6, heads, key_heads, width, capacity, keys, values)
+            runtime.attend(qd, keys, values, pd, 0.125, heads, key_heads, width, capacity, out)
+        outs.append(runtime.read(out))
+        caches.append((runtime.read(keys), runtime.read(values)))
+    assert np.array_equal(bits(outs[0]), bits(outs[1]))
+    assert np.array_equal(bits(caches[0][0]), bits(caches[1][0])) and np.array_equal(bits(caches[0][1]), bits(caches[1][1]))
