@@ -28,7 +28,7 @@ METRIC = "decode tok/s (Q4_K Qwen-shaped)"
 UNIT = "tok/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent step, from the ncu captures
 # summarised under profiles/ (taken on a cut of few layers and scaled by the weights per step)
-MEGAKERNEL_TRAFFIC = {}
+MEGAKERNEL_TRAFFIC = {("qwen2.5-32b-q4_k", 1): 18.10e9}   # profiles/decode_megakernel_qwen32b_q4k_2l.md
 
 
 def measured_peaks():

@@ -154,10 +154,18 @@ __device__ __forceinline__ void dequant_row_quarter(uint32_t tile, uint32_t row,
     const uint32_t lo0 = w0 & 0x0f0f0f0fu, lo1 = w1 & 0x0f0f0f0fu;
     const uint32_t hi0 = (w0 >> 4) & 0x0f0f0f0fu, hi1 = (w1 >> 4) & 0x0f0f0f0fu;
     const uint32_t at = tile + row * 128;
-    sts16(at + ((t ^ (row & 7)) << 4), bf16_pair(quantum[0], low[0], lo0, 0, 1), bf16_pair(quantum[0], low[0], lo0, 2, 3),
-          bf16_pair(quantum[0], low[0], lo1, 0, 1), bf16_pair(quantum[0], low[0], lo1, 2, 3));
-    sts16(at + (((4 + t) ^ (row & 7)) << 4), bf16_pair(quantum[1], low[1], hi0, 0, 1), bf16_pair(quantum[1], low[1], hi0, 2, 3),
-          bf16_pair(quantum[1], low[1], hi1, 0, 1), bf16_pair(quantum[1], low[1], hi1, 2, 3));
+    // Eight lanes store together: two rows (g, g + 1) x four chunks t.  Both rows' low chunks swizzle into the same
+    // four 16-byte columns and would collide two by two, so odd rows store their high chunk first: every group of
+    // eight then covers all eight columns of the 128-byte line.
+    const bool odd = row & 1u;
+    const float qa = odd ? quantum[1] : quantum[0], la = odd ? low[1] : low[0];
+    const float qb = odd ? quantum[0] : quantum[1], lb = odd ? low[0] : low[1];
+    const uint32_t a0 = odd ? hi0 : lo0, a1 = odd ? hi1 : lo1, b0 = odd ? lo0 : hi0, b1 = odd ? lo1 : hi1;
+    const uint32_t ca = odd ? 4 + t : t, cb = odd ? t : 4 + t;
+    sts16(at + ((ca ^ (row & 7)) << 4), bf16_pair(qa, la, a0, 0, 1), bf16_pair(qa, la, a0, 2, 3), bf16_pair(qa, la, a1, 0, 1),
+          bf16_pair(qa, la, a1, 2, 3));
+    sts16(at + ((cb ^ (row & 7)) << 4), bf16_pair(qb, lb, b0, 0, 1), bf16_pair(qb, lb, b0, 2, 3), bf16_pair(qb, lb, b1, 0, 1),
+          bf16_pair(qb, lb, b1, 2, 3));
 }
 
 struct RawQuarter {   // what one producer thread fetches for one k-step: 16 rows' lane of one unit half
