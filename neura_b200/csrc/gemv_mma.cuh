@@ -40,7 +40,8 @@ struct GemvParams {
     unsigned int *counters;  // [tile], zero between launches
     unsigned int *status;    // raised when a bounded wait ran out
     uint64_t out_stride;
-    uint32_t n, rows, ncols;
+    uint32_t n, rows, ncols;  // output features; activation rows of this launch and their 3 * rows digit columns
+    uint32_t col_stride, col0;  // the staged tables hold col_stride columns a block; this launch reads [col0, col0 + ncols)
     uint32_t upt;         // units per tile (blocks along K)
     uint32_t nwarps;      // warps that take work
     uint32_t q, r;        // every warp takes q units, the first r one more
@@ -347,19 +348,19 @@ __device__ __forceinline__ void load_frags(StageFrags<Q4K, NT> &f, const GemvPar
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const uint32_t col = nt * 8 + 2 * t;
-            f.c[j][nt][0] = col < p.ncols ? __ldg(p.cs + blk * p.ncols + col) : 0.0f;
-            f.c[j][nt][1] = col + 1 < p.ncols ? __ldg(p.cs + blk * p.ncols + col + 1) : 0.0f;
+            f.c[j][nt][0] = col < p.ncols ? __ldg(p.cs + blk * p.col_stride + p.col0 + col) : 0.0f;
+            f.c[j][nt][1] = col + 1 < p.ncols ? __ldg(p.cs + blk * p.col_stride + p.col0 + col + 1) : 0.0f;
             const uint32_t mine = nt * 8 + g;
             const bool live = mine < p.ncols;
             if constexpr (Q4K) {
-                const uint32_t entry = (blk * p.ncols + mine) * 4 + t;
+                const uint32_t entry = (blk * p.col_stride + p.col0 + mine) * 4 + t;
                 const uint4 *from = reinterpret_cast<const uint4 *>(p.dig) + entry * 4u;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) f.wide[nt][i] = live ? __ldg(from + i) : make_uint4(0u, 0u, 0u, 0u);
                 f.sums[nt] = live ? __ldg(reinterpret_cast<const uint4 *>(p.sums) + entry) : make_uint4(0u, 0u, 0u, 0u);
             } else {
                 f.narrow[j][nt] = live
-                    ? __ldg(reinterpret_cast<const uint2 *>(p.dig + (blk * p.ncols + mine) * 32u + t * 8u))
+                    ? __ldg(reinterpret_cast<const uint2 *>(p.dig + (blk * p.col_stride + p.col0 + mine) * 32u + t * 8u))
                     : make_uint2(0u, 0u);
             }
         }

@@ -126,17 +126,17 @@ __device__ __forceinline__ void mk_load_frags(StageFrags<Q4K, 1> &f, const GemvP
 #pragma unroll
     for (int j = 0; j < StageFrags<Q4K, 1>::kUnits; ++j) {
         const uint32_t col = 2 * t;
-        f.c[j][0][0] = col < s.ncols ? s.cs[blk * s.ncols + col] : 0.0f;
-        f.c[j][0][1] = col + 1 < s.ncols ? s.cs[blk * s.ncols + col + 1] : 0.0f;
+        f.c[j][0][0] = col < s.ncols ? s.cs[blk * s.col_stride + s.col0 + col] : 0.0f;
+        f.c[j][0][1] = col + 1 < s.ncols ? s.cs[blk * s.col_stride + s.col0 + col + 1] : 0.0f;
         const bool live = g < s.ncols;
         if constexpr (Q4K) {
-            const uint32_t entry = (blk * s.ncols + g) * 4 + t;
+            const uint32_t entry = (blk * s.col_stride + s.col0 + g) * 4 + t;
             const uint4 *from = reinterpret_cast<const uint4 *>(s.dig) + entry * 4u;
 #pragma unroll
             for (int i = 0; i < 4; ++i) f.wide[0][i] = live ? from[i] : make_uint4(0u, 0u, 0u, 0u);
             f.sums[0] = live ? reinterpret_cast<const uint4 *>(s.sums)[entry] : make_uint4(0u, 0u, 0u, 0u);
         } else {
-            f.narrow[j][0] = live ? *reinterpret_cast<const uint2 *>(s.dig + (blk * s.ncols + g) * 32u + t * 8u)
+            f.narrow[j][0] = live ? *reinterpret_cast<const uint2 *>(s.dig + (blk * s.col_stride + s.col0 + g) * 32u + t * 8u)
                                   : make_uint2(0u, 0u);
         }
         if ((uint32_t)(j + 1) < have && ++blk == s.upt) blk = 0;

@@ -51,7 +51,8 @@ int32_t cuda_refuse(cudaError_t e, const char *what) {
 constexpr int32_t kBadArgument = -1;
 constexpr int32_t kBadState = -2;
 constexpr int32_t kDeviceRefusal = -3;
-constexpr uint32_t kMaxRowsPerPass = 16;  // activation rows one GEMV launch carries
+constexpr uint32_t kMaxRowsPerPass = 16;  // activation rows one staging holds
+constexpr uint32_t kRowsPerLaunch = 8;    // activation rows one product launch carries (three 8-column MMA tiles)
 
 struct Region {
     void *ptr = nullptr;
@@ -509,29 +510,38 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
     if ((uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
-    GemvParams p;
-    memset(&p, 0, sizeof p);
-    p.w = (const uint8_t *)w->data_dev;
-    p.dig = (const uint8_t *)ctx->dig.ptr;
-    p.cs = (const float *)ctx->cs.ptr;
-    p.sums = (const uint8_t *)ctx->sums.ptr;
-    p.out = out_dev;
-    p.out_stride = out_stride;
-    p.n = w->n;
-    p.rows = ctx->staged_rows;
-    p.ncols = ctx->staged_rows * 3;
-    p.pair = pair ? 1u : 0u;
-    p.chain.n = n_steps;
-    for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
     cudaStream_t stream = (cudaStream_t)stream_;
-    switch ((p.ncols + 7) / 8) {
-    case 1: return launch_gemv<1>(ctx, stream, w->element, p, plan_n, w->k);
-    case 2: return launch_gemv<2>(ctx, stream, w->element, p, plan_n, w->k);
-    case 3: return launch_gemv<3>(ctx, stream, w->element, p, plan_n, w->k);
-    case 4: return launch_gemv<4>(ctx, stream, w->element, p, plan_n, w->k);
-    case 5: return launch_gemv<5>(ctx, stream, w->element, p, plan_n, w->k);
-    default: return launch_gemv<6>(ctx, stream, w->element, p, plan_n, w->k);
+    // a launch carries at most kRowsPerLaunch rows: beyond that the accumulators of the wider MMA tiles spill
+    // and two launches over the same weights are faster than one
+    for (uint32_t first = 0; first < ctx->staged_rows; first += kRowsPerLaunch) {
+        GemvParams p;
+        memset(&p, 0, sizeof p);
+        p.w = (const uint8_t *)w->data_dev;
+        p.dig = (const uint8_t *)ctx->dig.ptr;
+        p.cs = (const float *)ctx->cs.ptr;
+        p.sums = (const uint8_t *)ctx->sums.ptr;
+        p.out = out_dev + (uint64_t)first * out_stride;
+        p.out_stride = out_stride;
+        p.n = w->n;
+        p.rows = std::min(kRowsPerLaunch, ctx->staged_rows - first);
+        p.ncols = p.rows * 3;
+        p.col_stride = ctx->staged_rows * 3;
+        p.col0 = first * 3;
+        p.pair = pair ? 1u : 0u;
+        p.chain.n = n_steps;
+        for (uint32_t s = 0; s < n_steps; ++s) {
+            p.chain.step[s] = chain[s];
+            if (chain[s].operand_dev)   // the operand is read at this launch's rows
+                p.chain.step[s].operand_dev = chain[s].operand_dev + (int64_t)first * chain[s].row_stride;
+        }
+        switch ((p.ncols + 7) / 8) {
+        case 1: rc = launch_gemv<1>(ctx, stream, w->element, p, plan_n, w->k); break;
+        case 2: rc = launch_gemv<2>(ctx, stream, w->element, p, plan_n, w->k); break;
+        default: rc = launch_gemv<3>(ctx, stream, w->element, p, plan_n, w->k); break;
+        }
+        if (rc) return rc;
     }
+    return 0;
 }
 
 int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_dev, uint32_t rows,
@@ -1109,6 +1119,8 @@ int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight
     p.n = w->n;
     p.rows = rows;
     p.ncols = ncols;
+    p.col_stride = ncols;
+    p.col0 = 0;
     p.upt = plan.upt;
     p.nwarps = plan.nwarps;
     p.q = plan.q;
@@ -1392,6 +1404,8 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         g.n = w.n;
         g.rows = c.batch;
         g.ncols = ncols;
+        g.col_stride = ncols;
+        g.col0 = 0;
         g.pair = pair ? 1u : 0u;
         if (normed) {
             g.sumsq = sumsq;
