@@ -260,15 +260,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
             tc_fence_after();
             const uint32_t which = (warp >> 2) & 1, lanes = (warp & 3) * 32, columns = (warp >> 3) * (kGemmBN / 2);
             const uint32_t row = m0 + which * 128 + lanes + lane;
+            float *turn = reinterpret_cast<float *>(gemm_raw + (base - smem_addr(gemm_raw))) + warp * 32 * 33;
             for (uint32_t c0 = columns; c0 < columns + kGemmBN / 2; c0 += 32) {
                 uint32_t r[32];
                 tmem_load_32(tmem + (lanes << 16) + which * kGemmBN + c0, r);
-                if (row < p.m) {
-                    float *to = p.out + (uint64_t)row * p.out_stride + n0 + c0;
+                // A lane holds 32 consecutive outputs of ONE row; stored as they are, one instruction touches 32
+                // rows (32 sectors), and those stores held the whole kernel back (without them it runs twice as
+                // fast).  So the warp turns its 32 x 32 block through shared memory (the ring is idle by now) and
+                // every store instruction writes 128 contiguous bytes of one row.
 #pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i)
-                        if (n0 + c0 + i < p.n) to[i] = chained(p.chain, row, n0 + c0 + i, __uint_as_float(r[i]));
+                for (uint32_t i = 0; i < 32; ++i)
+                    turn[lane * 33 + i] = (row < p.m && n0 + c0 + i < p.n) ? chained(p.chain, row, n0 + c0 + i, __uint_as_float(r[i])) : 0.0f;
+                __syncwarp();
+                const uint32_t col = n0 + c0 + lane;
+                if (col < p.n) {
+                    const uint32_t first_row = m0 + which * 128 + lanes;
+                    float *to = p.out + (uint64_t)first_row * p.out_stride + col;
+#pragma unroll 8
+                    for (uint32_t rr = 0; rr < 32; ++rr)
+                        if (first_row + rr < p.m) __stcs(to + (uint64_t)rr * p.out_stride, turn[rr * 33 + lane]);
                 }
+                __syncwarp();
             }
         } else {
             failed = 1;
