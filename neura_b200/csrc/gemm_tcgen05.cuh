@@ -168,22 +168,21 @@ __device__ __forceinline__ void dequant_row_quarter(uint32_t tile, uint32_t row,
           bf16_pair(qb, lb, b1, 2, 3));
 }
 
-struct RawQuarter {   // what one producer thread fetches for one k-step: 16 rows' lane of one unit half
-    uint4 q, h0, h1;
-};
-
-// Warp w of the 16 producers owns half (w & 1) of 32-row unit (w >> 1) of the 256-row W tile.
-__device__ __forceinline__ void fetch_quarter(RawQuarter &raw, const GemmParams &p, uint32_t n0, uint32_t it, uint32_t warp,
+// Warp w of the 16 producers owns half (w & 1) of 32-row unit (w >> 1) of the 256-row W tile.  What one of its
+// threads fetches: per k-step the 16 bytes of quants of its lane, per super-block (four k-steps) the headers of
+// its two rows.
+__device__ __forceinline__ const uint8_t *half_unit_of(const GemmParams &p, uint32_t n0, uint32_t sb, uint32_t warp) {
+    const uint32_t nsb = p.k / kSuperBlock, unit = min(n0 / 32 + (warp >> 1), p.units32 - 1);
+    return p.w + (((uint64_t)unit * nsb + sb) * 2 + (warp & 1)) * kQ4kUnit;
+}
+__device__ __forceinline__ uint4 fetch_quants(const GemmParams &p, uint32_t n0, uint32_t it, uint32_t warp, uint32_t lane) {
+    return ld_stream16(half_unit_of(p, n0, it >> 2, warp) + 256 + (it & 3) * 512 + lane * 16);
+}
+__device__ __forceinline__ void fetch_headers(uint4 (&h)[2], const GemmParams &p, uint32_t n0, uint32_t sb, uint32_t warp,
                                               uint32_t lane) {
-    const uint32_t nsb = p.k / kSuperBlock, sb = it >> 2, G = it & 3, g = lane >> 2, half = warp & 1;
-    const uint32_t unit = n0 / 32 + (warp >> 1);
-    raw.q = raw.h0 = raw.h1 = make_uint4(0u, 0u, 0u, 0u);
-    if (unit < p.units32) {
-        const uint8_t *from = p.w + (((uint64_t)unit * nsb + sb) * 2 + half) * kQ4kUnit;
-        raw.q = ld_stream16(from + 256 + G * 512 + lane * 16);
-        raw.h0 = ld_stream16(from + g * 16);
-        raw.h1 = ld_stream16(from + (g + 8) * 16);
-    }
+    const uint8_t *from = half_unit_of(p, n0, sb, warp);
+    h[0] = ld_stream16(from + (lane >> 2) * 16);
+    h[1] = ld_stream16(from + ((lane >> 2) + 8) * 16);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t bar) {
@@ -227,32 +226,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
         // ---------------- producers ----------------
         const uint32_t g = lane >> 2, t = lane & 3, half = warp & 1;
         bool alive = true;
-        // the raw blocks travel three steps ahead of their use (a miss to HBM takes longer than one step)
-        RawQuarter raw[4];
+        // the quants travel three steps ahead of their use, the headers one super-block ahead, and the super-block
+        // after the next is asked into L2 (a miss to HBM takes longer than a step); rows past the weight's end
+        // re-read its last unit, and the epilogue does not store them
+        const uint32_t nsb = p.k / kSuperBlock;
+        uint4 quants[4], headers[2], coming[2];
 #pragma unroll
         for (uint32_t j = 0; j < 3; ++j)
-            if (j < ksteps) fetch_quarter(raw[j], p, n0, j, warp, lane);
+            if (j < ksteps) quants[j] = fetch_quants(p, n0, j, warp, lane);
+        fetch_headers(headers, p, n0, 0, warp, lane);
         for (uint32_t it0 = 0; it0 < ksteps && alive; it0 += 4) {
+            const uint32_t sb = it0 >> 2;
+            if (sb + 1 < nsb) fetch_headers(coming, p, n0, sb + 1, warp, lane);
+            if (lane == 0 && sb + 2 < nsb)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(half_unit_of(p, n0, sb + 2, warp)), "r"(kQ4kUnit) : "memory");
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
                 const uint32_t it = it0 + j;
                 if (it >= ksteps || !alive) break;
                 const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
-                if (it + 3 < ksteps) fetch_quarter(raw[(j + 3) & 3], p, n0, it + 3, warp, lane);
+                if (it + 3 < ksteps) quants[(j + 3) & 3] = fetch_quants(p, n0, it + 3, warp, lane);
                 if (!mbar_wait(empty + 8 * s, parity ^ 1u)) { alive = false; break; }
                 const uint32_t a_tile = base + s * kGemmStageBytes, b_tile = a_tile + kGemmABytes;
                 if (tid == 0) {   // x (columns) is a multiple of 64 bf16 = 128 bytes: the 16-byte rule of the copy holds
                     mbar_expect(full + 8 * s, kGemmABytes);
                     tma_load_2d(a_tile, &p.x_map, it * kGemmBK, m0, full + 8 * s);
                 }
-                const uint32_t G = it & 3;
                 const uint32_t row = (warp >> 1) * 32 + half * 16 + g;
-                dequant_row_quarter(b_tile, row, t, G, raw[j].q.x, raw[j].q.y, raw[j].h0);
-                dequant_row_quarter(b_tile, row + 8, t, G, raw[j].q.z, raw[j].q.w, raw[j].h1);
+                dequant_row_quarter(b_tile, row, t, j, quants[j].x, quants[j].y, headers[0]);
+                dequant_row_quarter(b_tile, row + 8, t, j, quants[j].z, quants[j].w, headers[1]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tile through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full + 8 * s);   // one arrival per warp: 512 arrivals on one barrier word would queue up
             }
+            headers[0] = coming[0];
+            headers[1] = coming[1];
         }
         if (!alive) failed = 1;
         // ---------------- epilogue: warp w reads lanes 32 (w % 4).. of accumulator (w / 4) % 2, column half w / 8 ----------------
