@@ -347,6 +347,65 @@ def run_ours(args):
         os._exit(0)
 
 
+def run_prefill(args):
+    """A secondary line: the tensor-core prefill product (Q4_K, bf16 operands, f32 accumulate) on one GPU,
+    ``--workload prefill-MxNxK`` (the reference's prefill shape is 2048x18944x3584).  Device timing only."""
+    import torch
+
+    import neura_b200 as nb
+
+    m, n, k = (int(v) for v in args.workload.split("-", 1)[1].split("x"))
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    device = torch.device("cuda", 0)
+    tstream = torch.cuda.ExternalStream(rt.stream.value, device=device)
+    with torch.cuda.stream(tstream):
+        numbers = torch.randn(n * k, device=device) * 0.02
+        blocks = torch.empty(nb.payload_bytes(nb.Q4K, n * k) + 16, dtype=torch.uint8, device=device)
+        rt.quantize_device(nb.Q4K, numbers.data_ptr(), n * k, blocks.data_ptr())
+        weight = rt.seal_device(nb.Q4K, n, k, blocks.data_ptr())
+        x = torch.randn(m, k, device=device)
+        out = torch.empty(m, n, device=device)
+    rt.sync()
+    xd = nb.DeviceTensor(x.data_ptr(), x.numel() * 4, (m, k))
+    od = nb.DeviceTensor(out.data_ptr(), out.numel() * 4, (m, n))
+    warmup = max(3, args.warmup)
+    for _ in range(warmup):
+        rt.linear_bf16(weight, xd, od)
+    rt.sync()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = rt.launches
+    with ClockSampler(0) as clocks:
+        time.sleep(0.15)
+        start.record(tstream)
+        for _ in range(args.steps):
+            rt.linear_bf16(weight, xd, od)
+        stop.record(tstream)
+        rt.sync()
+        time.sleep(0.15)
+    ms = start.elapsed_time(stop) / args.steps
+    flops = 2.0 * m * n * k
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = {}
+    if os.path.exists(path):
+        with open(path) as fh:
+            peaks = json.load(fh)
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    print(json.dumps({
+        "metric": "prefill TFLOP/s (Q4_K weights dequantised to bf16 tiles, tcgen05)", "value": flops / ms / 1e9,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x bf16 -> f32", "data": "synthetic",
+        "config": {"workload": f"[{m} x {k}] f32 activations x Q4_K [{n} x {k}]; a step converts the activations to bf16 "
+                               "and runs the product", "l2": "weights, activations and output exceed L2 together"},
+        "clocks": clocks.summary(), "gpu_launches": int(rt.launches - launches0),
+        "roofline": {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": peak, "unit": "TFLOP/s",
+                     "frac": flops / ms / 1e9 / peak, "traffic": None,
+                     "peak_kind": "measured burst" if peaks else "fallback",
+                     "kernel": "gemm_q4k_tcgen05_kernel (+ to_bf16_kernel)"},
+    }))
+    rt.close()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -362,7 +421,9 @@ def main():
                         help="a recorded graph of one kernel per operation (the faster of the two as measured), or one "
                              "cooperative kernel per token (one GPU, batch <= 2)")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.workload.startswith("prefill-"):
+        run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
