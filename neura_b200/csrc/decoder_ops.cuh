@@ -26,16 +26,20 @@ __device__ __forceinline__ float2 rope_turn(float low, float high, float cosine,
     return make_float2(__fmaf_rn(low, cosine, -__fmul_rn(high, sine)), __fmaf_rn(high, cosine, __fmul_rn(low, sine)));
 }
 
-// (cosine, sine) of a position's angle in one channel, out of line: the slow paths of powf, cosf and sinf want a
-// stack frame that the callers' loops should not carry.
-__device__ __noinline__ float2 rope_angle(uint32_t position, uint32_t channel, uint32_t width, float base) {
+// (cosine, sine) of a position's angle in one channel.
+__device__ __forceinline__ float2 rope_angle_inline(uint32_t position, uint32_t channel, uint32_t width, float base) {
     const float angle = (float)position * powf(base, -2.0f * (float)channel / (float)width);
     return make_float2(cosf(angle), sinf(angle));
+}
+// The same out of line, for callers whose loops should not carry the stack frame that the slow paths of powf,
+// cosf and sinf want.
+__device__ __noinline__ float2 rope_angle(uint32_t position, uint32_t channel, uint32_t width, float base) {
+    return rope_angle_inline(position, channel, width, base);
 }
 
 __device__ __forceinline__ float2 rope_pair(float low, float high, uint32_t position, uint32_t channel, uint32_t width,
                                             float base) {
-    const float2 turn = rope_angle(position, channel, width, base);
+    const float2 turn = rope_angle_inline(position, channel, width, base);
     return rope_turn(low, high, turn.x, turn.y);
 }
 
@@ -93,6 +97,10 @@ __global__ void rope_cache_kernel(const __grid_constant__ RopeCacheParams p) {
 constexpr uint32_t kAttendMaxGroup = 8;    // query heads per key head
 constexpr uint32_t kAttendMaxChunk = 128;  // row length of the per-head logit and merge tables (>= tile, >= splits)
 constexpr uint32_t kAttendMaxCluster = 8;  // splits that merge through distributed shared memory
+#ifndef NC_ATTEND_THREADS
+#define NC_ATTEND_THREADS 128
+#endif
+constexpr uint32_t kAttendThreads = NC_ATTEND_THREADS;
 
 struct AttendParams {
     const float *q;           // [batch][q_stride], head h at h*width
@@ -125,8 +133,8 @@ __device__ __forceinline__ void copy16_async(void *dst_shared, const void *src_g
 // (sequence, key head) form a thread-block cluster and merge their partials through distributed
 // shared memory behind a cluster barrier; otherwise they merge through global memory, the last
 // CTA to arrive doing the work.
-template <uint32_t WIDTH, uint32_t TILE, bool CLUSTER>
-__global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ AttendParams p) {
+template <uint32_t WIDTH, uint32_t TILE, bool CLUSTER, bool TURNING>
+__global__ void __launch_bounds__(kAttendThreads) attend_kernel(const __grid_constant__ AttendParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(16) float shared[];
@@ -149,7 +157,7 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
     const float *k = p.keys + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
     const float *v = p.values + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
     const uint32_t position = p.position[b];
-    const bool turning = p.fresh_keys != nullptr;
+    constexpr bool turning = TURNING;   // (the plain instantiation carries none of the folded-in RoPE)
     const bool fresh = turning && position < p.capacity && position >= first && position < last;  // the new row is ours
     const uint32_t fresh_row = position - first;
     for (uint32_t i = threadIdx.x; i < held * (WIDTH / 4); i += blockDim.x) {
@@ -159,7 +167,7 @@ __global__ void __launch_bounds__(128) attend_kernel(const __grid_constant__ Att
         copy16_async(vs + i * 4, v + i * 4);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    if (turning) {
+    if constexpr (TURNING) {
         constexpr uint32_t HALF = WIDTH / 2;
         const float *row_qkv = p.q + (uint64_t)b * p.q_stride;
         for (uint32_t i = threadIdx.x; i < group * HALF; i += blockDim.x) {

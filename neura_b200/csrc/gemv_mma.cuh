@@ -139,10 +139,11 @@ __device__ __forceinline__ uint32_t owner_of(uint32_t u, uint32_t q, uint32_t r)
 // 16h..16h+15 and per 8-column MMA tile, (row g, col 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).
 // `scale0` and `scale1` multiply the sums of rows 0 and 1 (an rms_norm's scalar; 1 otherwise).  Returns
 // whether this warp wrote the tile's final outputs.
-template <int NT>
+// With HOOKS false (the one-launch-per-product kernel) the scales and `p.after` are not looked at.
+template <int NT, bool HOOKS>
 __device__ __forceinline__ bool flush_tile(const GemvParams &p, float (&acc)[2][NT][4], float *patch, uint32_t warp,
-                                        uint32_t tile, uint32_t first_blk, uint32_t end_blk, float scale0 = 1.0f,
-                                        float scale1 = 1.0f) {
+                                        uint32_t tile, uint32_t first_blk, uint32_t end_blk, float scale0_, float scale1_) {
+    const float scale0 = HOOKS ? scale0_ : 1.0f, scale1 = HOOKS ? scale1_ : 1.0f;
     const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     constexpr int W = NT * 8 + 1;  // padded row of the per-warp patch
 #pragma unroll
@@ -222,7 +223,9 @@ __device__ __forceinline__ bool flush_tile(const GemvParams &p, float (&acc)[2][
         }
     }
     __syncwarp();
-    if (final && p.after) stage_after_piece(*p.after, tile * p.after->piece);
+    if constexpr (HOOKS) {
+        if (final && p.after) stage_after_piece(*p.after, tile * p.after->piece);
+    }
     return final;
 }
 
@@ -369,7 +372,7 @@ __device__ __forceinline__ void load_frags(StageFrags<Q4K, NT> &f, const GemvPar
     }
 }
 
-template <bool Q4K, int NT, int STAGES>
+template <bool Q4K, int NT, int STAGES, bool HOOKS = false>
 struct GemvWarp {
     static constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
     static constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;
@@ -397,7 +400,7 @@ struct GemvWarp {
         }
         ++done;
         if (++blk == p.upt || done == units) {
-            flush_tile<NT>(p, acc, patch, warp, tile, first_blk, blk, scale0, scale1);
+            flush_tile<NT, HOOKS>(p, acc, patch, warp, tile, first_blk, blk, scale0, scale1);
             if (blk == p.upt) { blk = 0; ++tile; }
             first_blk = blk;
         }

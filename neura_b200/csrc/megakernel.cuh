@@ -206,7 +206,7 @@ template <bool Q4K>
 __device__ __forceinline__ bool mk_stream(const GemvParams &g, MkRing &rg, const MkRun &run, float *patch, uint32_t warp,
                                           float scale0, float scale1) {
     constexpr uint32_t kGroup = Q4K ? 1 : kQ8Group;
-    GemvWarp<Q4K, 1, 2> w{g};
+    GemvWarp<Q4K, 1, 2, true> w{g};
     w.ring = rg.ring;
     w.bars = rg.bars;
     w.patch = patch;

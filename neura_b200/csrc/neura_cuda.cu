@@ -767,18 +767,27 @@ int32_t attend_any(nc_context *ctx, void *stream_, const float *q_dev, uint64_t 
     const size_t smem = ((size_t)tile * (2 * width + 4) + (size_t)kAttendMaxGroup * width +
                          (size_t)kAttendMaxGroup * kAttendMaxChunk + (size_t)kAttendMaxGroup * 2) * sizeof(float);
     void (*kernel)(AttendParams);
-    const int which = (width == 128 ? 4 : 0) + (tile == 128 ? 2 : 0) + (cluster ? 1 : 0);
+    const bool turning = fresh_keys != nullptr;
+    const int which = (turning ? 8 : 0) + (width == 128 ? 4 : 0) + (tile == 128 ? 2 : 0) + (cluster ? 1 : 0);
     switch (which) {
-    case 0: kernel = attend_kernel<64, 64, false>; break;
-    case 1: kernel = attend_kernel<64, 64, true>; break;
-    case 2: kernel = attend_kernel<64, 128, false>; break;
-    case 3: kernel = attend_kernel<64, 128, true>; break;
-    case 4: kernel = attend_kernel<128, 64, false>; break;
-    case 5: kernel = attend_kernel<128, 64, true>; break;
-    case 6: kernel = attend_kernel<128, 128, false>; break;
-    default: kernel = attend_kernel<128, 128, true>; break;
+    case 0: kernel = attend_kernel<64, 64, false, false>; break;
+    case 1: kernel = attend_kernel<64, 64, true, false>; break;
+    case 2: kernel = attend_kernel<64, 128, false, false>; break;
+    case 3: kernel = attend_kernel<64, 128, true, false>; break;
+    case 4: kernel = attend_kernel<128, 64, false, false>; break;
+    case 5: kernel = attend_kernel<128, 64, true, false>; break;
+    case 6: kernel = attend_kernel<128, 128, false, false>; break;
+    case 7: kernel = attend_kernel<128, 128, true, false>; break;
+    case 8: kernel = attend_kernel<64, 64, false, true>; break;
+    case 9: kernel = attend_kernel<64, 64, true, true>; break;
+    case 10: kernel = attend_kernel<64, 128, false, true>; break;
+    case 11: kernel = attend_kernel<64, 128, true, true>; break;
+    case 12: kernel = attend_kernel<128, 64, false, true>; break;
+    case 13: kernel = attend_kernel<128, 64, true, true>; break;
+    case 14: kernel = attend_kernel<128, 128, false, true>; break;
+    default: kernel = attend_kernel<128, 128, true, true>; break;
     }
-    static bool raised[64][8] = {{false}};
+    static bool raised[64][16] = {{false}};
     if (!raised[ctx->device & 63][which]) {
         NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         raised[ctx->device & 63][which] = true;
@@ -793,7 +802,7 @@ int32_t attend_any(nc_context *ctx, void *stream_, const float *q_dev, uint64_t 
                    batch, heads, key_heads, width, capacity, splits, fresh_keys, fresh_values, rope_table};
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(batch * key_heads * splits);
-    config.blockDim = dim3(128);
+    config.blockDim = dim3(kAttendThreads);
     config.dynamicSmemBytes = smem;
     config.stream = (cudaStream_t)stream_;
     cudaLaunchAttribute attribute[2];
