@@ -98,7 +98,7 @@ constexpr uint32_t kAttendMaxGroup = 8;    // query heads per key head
 constexpr uint32_t kAttendMaxChunk = 128;  // row length of the per-head logit and merge tables (>= tile, >= splits)
 constexpr uint32_t kAttendMaxCluster = 8;  // splits that merge through distributed shared memory
 #ifndef NC_ATTEND_THREADS
-#define NC_ATTEND_THREADS 128
+#define NC_ATTEND_THREADS 256
 #endif
 constexpr uint32_t kAttendThreads = NC_ATTEND_THREADS;
 
