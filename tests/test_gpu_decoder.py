@@ -275,10 +275,13 @@ def test_the_persistent_step_decodes_what_the_oracle_decodes(oracle, name, batch
         assert decoder.launches_per_token() == 1
         got = decoder.generate(prompts, steps)
         again = decoder.generate(prompts, steps)
+        kinds, nanos = decoder.trace()
         decoder.release()
     finally:
         rt.close()
     assert np.array_equal(got, again), "the persistent step decodes the same ids twice"
+    # embedding, staging, five phases a layer, head, argmax; every phase took some time
+    assert kinds.tolist() == [1, 4] + [2, 3, 2, 2, 2] * config.layers + [2, 5] and (nanos > 0).all()
     differs = np.argwhere(got != want)
     if differs.size:
         b, at = differs[0]
