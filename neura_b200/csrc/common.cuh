@@ -78,6 +78,15 @@ __device__ __forceinline__ float chained(const Chain &chain, uint64_t row, uint6
     return result;
 }
 
+// An arrival on a counter of finished pieces: one atomic that releases the arriving thread's earlier writes (and,
+// through the barrier before it, its warp's or CTA's) and acquires those of the arrivals before it.  Two fences
+// around a relaxed atomic say the same and cost two more trips to L2.
+__device__ __forceinline__ unsigned int arrive_on(unsigned int *counter) {
+    unsigned int before;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(before) : "l"(counter) : "memory");
+    return before;
+}
+
 __device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
     return __half2float(__ushort_as_half((unsigned short)bits16));
 }

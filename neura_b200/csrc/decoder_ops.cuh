@@ -288,9 +288,7 @@ __global__ void __launch_bounds__(kAttendThreads) attend_kernel(const __grid_con
     // the last split of this (sequence, key head) to arrive merges them all, in split order
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();
-        arrived = atomicAdd(p.counters + b * p.key_heads + kh, 1u);
-        __threadfence();
+        arrived = arrive_on(p.counters + b * p.key_heads + kh);
     }
     __syncthreads();
     if (arrived != p.splits - 1) return;
@@ -395,9 +393,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const __grid_constant__ Arg
         for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) argmax_take(value, index, best_value[w], best_index[w]);
         __stcg(p.slice_value + row * p.slices + slice, value);
         __stcg(p.slice_index + row * p.slices + slice, index);
-        __threadfence();
-        arrived = atomicAdd(p.counters + row, 1u);
-        __threadfence();
+        arrived = arrive_on(p.counters + row);
     }
     __syncthreads();
     if (arrived != p.slices - 1 || warp != 0) return;

@@ -189,9 +189,7 @@ __device__ __forceinline__ bool flush_tile(const GemvParams &p, float (&acc)[2][
         __syncwarp();
         unsigned int seen = 0;
         if (lane == 0) {
-            __threadfence();
-            seen = atomicAdd(p.counters + tile, 1u);
-            __threadfence();
+            seen = arrive_on(p.counters + tile);
         }
         seen = __shfl_sync(0xffffffffu, seen, 0);
         final = seen == count - 1;

@@ -382,9 +382,7 @@ __device__ __forceinline__ void mk_attend_item(const MkParams &p, const MkPhase 
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();
-        *arrived = atomicAdd(p.attend_counters + b * p.key_heads + kh, 1u);
-        __threadfence();
+        *arrived = arrive_on(p.attend_counters + b * p.key_heads + kh);
     }
     __syncthreads();
     if (*arrived == splits - 1) {
@@ -431,9 +429,7 @@ __device__ __forceinline__ void mk_attend_item(const MkParams &p, const MkPhase 
                 const uint32_t expected = (min(a.prep.k, (c + 1) * 256) - 1) / span - c * 256 / span + 1;
                 unsigned int seen = 0;
                 if (lane == 0) {
-                    __threadfence();
-                    seen = atomicAdd(a.counters + b * chunks + c, 1u);
-                    __threadfence();
+                    seen = arrive_on(a.counters + b * chunks + c);
                 }
                 seen = __shfl_sync(0xffffffffu, seen, 0);
                 if (seen == expected - 1) {
@@ -508,9 +504,7 @@ __device__ __forceinline__ void mk_argmax(const MkParams &p, const MkPhase &ph, 
             for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) argmax_take(value, index, best_value[w], best_index[w]);
             __stcg(p.slice_value + row * gridDim.x + blockIdx.x, value);
             __stcg(p.slice_index + row * gridDim.x + blockIdx.x, index);
-            __threadfence();
-            *arrived = atomicAdd(p.argmax_counters + row, 1u);
-            __threadfence();
+            *arrived = arrive_on(p.argmax_counters + row);
         }
         __syncthreads();
         if (*arrived == gridDim.x - 1 && warp == 0) {

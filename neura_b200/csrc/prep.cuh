@@ -190,9 +190,7 @@ __device__ __forceinline__ void stage_after_piece(const StageAfter &a, uint32_t 
     const uint32_t expected = (width + a.piece - 1) / a.piece;
     unsigned int seen = 0;
     if (lane == 0) {
-        __threadfence();
-        seen = atomicAdd(a.counters + chunk, 1u);
-        __threadfence();
+        seen = arrive_on(a.counters + chunk);
     }
     seen = __shfl_sync(0xffffffffu, seen, 0);
     if (seen != expected - 1) return;
