@@ -290,6 +290,24 @@ int32_t neura_cuda_linear_static(nc_context *ctx, void *stream, const nc_weight 
                                  uint32_t rows, uint64_t x_stride, float *out_dev, uint64_t out_stride,
                                  const nc_step *chain, uint32_t n_steps);
 
+/* Staging slots.  A context keeps three staged forms of activation rows; neura_cuda_stage, neura_cuda_stage_window
+ * and neura_cuda_rms_norm_stage write, and the staged products read, the selected one (slot 0 until told otherwise). */
+#define NC_NO_SLOT 0xffffffffu
+int32_t neura_cuda_staging_select(nc_context *ctx, uint32_t slot);
+
+/* neura_cuda_linear_staged over the selected slot (1 or 2 rows) with the staging of the NEXT product folded into
+ * its epilogue (the planner's fusion of a product with the pointwise tasks that follow it,
+ * crates/neura-plan/src/lower.rs:415-423, taken one step further): when then_slot is a slot, the warp that
+ * completes a 256-column chunk of the output rows digitises it into that slot at once, multiplied by
+ * then_gain_dev (a coming rms_norm's weight, or NULL), and with then_squares leaves the chunk's sum of squares
+ * with the context.  `normed` says that the rows being read were staged that way: the product multiplies its
+ * outputs by their norm's scalar 1 / sqrt(mean(x^2) + floor) (a product is linear in a row scale), so
+ *   rms_norm_stage(x, g) ; linear_staged(W)   ==   [x staged with gain g and squares] ; linear_staged_then(W, normed)
+ * up to the rounding of the staging.  then_slot = NC_NO_SLOT stages nothing. */
+int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev, uint64_t out_stride,
+                                      const nc_step *chain, uint32_t n_steps, uint32_t normed, float floor,
+                                      uint32_t then_slot, const float *then_gain_dev, uint32_t then_squares);
+
 /* The same product called the way Runtime::{write, run, read} are (runtime.rs:1020,833,1064):
  * activations come from and results return to host memory; blocks until done. */
 int32_t neura_cuda_linear_host(nc_context *ctx, void *stream, const nc_weight *w, const float *x_host,

@@ -20,7 +20,8 @@ SYMBOLS = [
     "neura_cuda_advance", "neura_cuda_stage_window", "neura_cuda_argmax_segments", "neura_cuda_sealed_pair_bytes",
     "neura_cuda_weight_seal_pair", "neura_cuda_linear_bf16", "neura_cuda_comm_create",
     "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce", "neura_cuda_reserve_decoder",
-    "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free", "neura_cuda_decoder_trace", "neura_cuda_rope_attend", "neura_cuda_rope_table", "neura_cuda_allreduce_norm_stage",
+    "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free", "neura_cuda_decoder_trace", "neura_cuda_rope_attend", "neura_cuda_rope_table", "neura_cuda_allreduce_norm_stage", "neura_cuda_staging_select",
+    "neura_cuda_linear_staged_then",
 ]
 
 
@@ -119,6 +120,9 @@ def load() -> ctypes.CDLL:
         "neura_cuda_rope_attend": (i32, [p, p, p, u64, p, p, ctypes.c_float, u32, u32, u32, u32, u32, p, p, p, u64]),
         "neura_cuda_rope_table": (i32, [p, p, p, ctypes.c_float, u32, u32, p]),
         "neura_cuda_allreduce_norm_stage": (i32, [p, p, p, p, u32, u32, p, ctypes.c_float, u32]),
+        "neura_cuda_staging_select": (i32, [p, u32]),
+        "neura_cuda_linear_staged_then": (i32, [p, p, ctypes.POINTER(NcWeight), p, u64, ctypes.POINTER(NcStep), u32, u32,
+                                             ctypes.c_float, u32, p, u32]),
         "neura_cuda_argmax": (i32, [p, p, p, u32, u32, u64, p]),
         "neura_cuda_embed": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, p, u64]),
         "neura_cuda_advance": (i32, [p, p, p, u32, u32]),

@@ -49,7 +49,8 @@ struct GemvParams {
     uint32_t pair;        // 1: a tile is 16 rows of one matrix over the same 16 rows of a second one, and
                           //    output c is silu(first row c) * (second row c): the SwiGLU of a gate and an up projection
     Chain chain;
-    const StageAfter *after;  // not null: finished tiles are counted and full chunks digitised for the next product
+    StageAfter then;          // has_then: finished tiles are counted and full chunks digitised for the next product
+    uint32_t has_then;
     const float *sumsq;       // not null: [rows][sumsq_chunks] sums of squares of the input rows, whose rms_norm
     uint32_t sumsq_chunks;    //           scalar 1 / sqrt(sum / k + floor) multiplies the outputs
     float floor, inv_k;
@@ -222,7 +223,7 @@ __device__ __forceinline__ bool flush_tile(const GemvParams &p, float (&acc)[2][
     }
     __syncwarp();
     if constexpr (HOOKS) {
-        if (final && p.after) stage_after_piece(*p.after, tile * p.after->piece);
+        if (final && p.has_then) stage_after_piece(p.then, tile * p.then.piece);
     }
     return final;
 }
@@ -434,7 +435,9 @@ struct GemvWarp {
     }
 };
 
-template <bool Q4K, int NT, int STAGES>
+// HOOKS: the product also applies the rms_norm scalar of its input rows (GemvParams::sumsq, at most two rows) and
+// stages its own output for the next product (GemvParams::then).
+template <bool Q4K, int NT, int STAGES, bool HOOKS = false>
 __global__ void __launch_bounds__(kGemvWarps * 32, NT <= 1 ? 4 : 1) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
     static_assert(STAGES >= 2 && kQ8Group == 4, "the four units of a Q8_0 stage are unrolled by hand");
     constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
@@ -444,7 +447,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT <= 1 ? 4 : 1) gemv_stream_
     const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const uint32_t warp = blockIdx.x * kGemvWarps + wib;
     if (warp >= p.nwarps) return;
-    GemvWarp<Q4K, NT, STAGES> w{p};
+    GemvWarp<Q4K, NT, STAGES, HOOKS> w{p};
     w.ring = smem_addr(smem) + wib * STAGES * kStage;
     w.bars = smem_addr(smem) + kGemvWarps * STAGES * kStage + wib * STAGES * 8;
     w.patch = reinterpret_cast<float *>(smem + kGemvWarps * STAGES * (kStage + 8)) + wib * 32 * (NT * 8 + 1);
@@ -482,6 +485,17 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT <= 1 ? 4 : 1) gemv_stream_
     w.blk = u0 % p.upt;
     w.first_blk = w.blk;
     w.done = 0;
+    if constexpr (HOOKS) {
+        if (p.sumsq) {   // the chunks' sums of squares, added in chunk order
+            float total0 = 0.0f, total1 = 0.0f;
+            for (uint32_t c = 0; c < p.sumsq_chunks; ++c) {
+                total0 += __ldcg(p.sumsq + c);
+                if (p.rows > 1) total1 += __ldcg(p.sumsq + p.sumsq_chunks + c);
+            }
+            w.scale0 = 1.0f / sqrtf(total0 * p.inv_k + p.floor);
+            w.scale1 = 1.0f / sqrtf(total1 * p.inv_k + p.floor);
+        }
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll

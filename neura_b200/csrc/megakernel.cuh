@@ -557,8 +557,6 @@ __global__ void __launch_bounds__(kMkThreads, 1) decode_megakernel(const __grid_
         }
         __syncthreads();
         if (aborted) break;
-        if (threadIdx.x == 0) phase.g.after = phase.has_after ? &phase.after : nullptr;
-        __syncthreads();
         if (blockIdx.x == 0 && threadIdx.x == 0) p.trace[index] = global_nanos();
         switch (phase.kind) {
         case MK_EMBED: mk_embed(p, phase); break;

@@ -61,11 +61,21 @@ struct Region {
 
 }  // namespace
 
+// One staged form of some activation rows (prep.cuh): what the products read.  A context holds kStagingSlots
+// of them, so that a product can read one while its epilogue stages its own output into another.
+struct Staging {
+    Region dig, cs, sums, chunks;   // chunks: finished pieces of every 256-column chunk (StageAfter::counters)
+    uint32_t rows = 0, k = 0, granule = 0;   // what was last staged here
+};
+constexpr uint32_t kStagingSlots = 3;
+
 struct nc_context {
     int device = 0;
     int sms = 0;
-    Region dig, cs, sums, partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch, x_bf16;
-    uint32_t staged_rows = 0, staged_k = 0, staged_granule = 0;  // what neura_cuda_stage last wrote
+    Staging slots[kStagingSlots];
+    uint32_t cur = 0;            // the slot neura_cuda_stage writes and the products read (neura_cuda_staging_select)
+    Region squares;              // [rows][chunks] sums of squares left by an epilogue that staged with a norm's gain
+    Region partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch, x_bf16;
     uint64_t launches = 0;
     bool capturing = false;
     cudaStream_t capture_stream = nullptr;
@@ -158,9 +168,9 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
-template <bool Q4K, int NT>
+template <bool Q4K, int NT, bool HOOKS = false>
 int32_t launch_gemv_as(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
-    auto kernel = gemv_stream_kernel<Q4K, NT, kStages>;
+    auto kernel = gemv_stream_kernel<Q4K, NT, kStages, HOOKS>;
     constexpr size_t stage = Q4K ? kQ4kStage : kQ8Stage;
     constexpr size_t smem = kGemvWarps * kStages * (stage + 8) + kGemvWarps * 32 * (NT * 8 + 1) * sizeof(float);
     static int resident[16] = {0};  // per device, filled on first use
@@ -194,6 +204,12 @@ template <int NT>
 int32_t launch_gemv(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
     return element == NC_ELEMENT_Q4K ? launch_gemv_as<true, NT>(ctx, stream, element, p, n, k)
                                      : launch_gemv_as<false, NT>(ctx, stream, element, p, n, k);
+}
+
+// The product of at most two rows that also applies its input's rms_norm scalar and stages its own output.
+int32_t launch_gemv_hooked(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
+    return element == NC_ELEMENT_Q4K ? launch_gemv_as<true, 1, true>(ctx, stream, element, p, n, k)
+                                     : launch_gemv_as<false, 1, true>(ctx, stream, element, p, n, k);
 }
 
 int32_t check_weight(const nc_weight *w) {
@@ -257,7 +273,10 @@ int32_t neura_cuda_close(nc_context *ctx) {
         if (graph) cudaGraphDestroy(graph);
         cudaGetLastError();
     }
-    for (Region *region : {&ctx->dig, &ctx->cs, &ctx->sums, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16})
+    for (Staging &slot : ctx->slots)
+        for (Region *region : {&slot.dig, &slot.cs, &slot.sums, &slot.chunks})
+            if (region->ptr) cudaFree(region->ptr);
+    for (Region *region : {&ctx->squares, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
     return 0;
@@ -329,9 +348,13 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     const uint32_t pass = rows < kMaxRowsPerPass ? rows : kMaxRowsPerPass;
     const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
     int32_t rc;
-    if ((rc = ensure(ctx, ctx->dig, kpad * 3 * pass, false))) return rc;
-    if ((rc = ensure(ctx, ctx->cs, kpad / 32 * 3 * pass * sizeof(float), false))) return rc;
-    if ((rc = ensure(ctx, ctx->sums, kpad / 256 * 3 * pass * 64, false))) return rc;
+    for (Staging &slot : ctx->slots) {   // every staging slot, so that no product grows one while a program is recorded
+        if ((rc = ensure(ctx, slot.dig, kpad * 3 * pass, false))) return rc;
+        if ((rc = ensure(ctx, slot.cs, kpad / 32 * 3 * pass * sizeof(float), false))) return rc;
+        if ((rc = ensure(ctx, slot.sums, kpad / 256 * 3 * pass * 64, false))) return rc;
+        if ((rc = ensure(ctx, slot.chunks, std::max<uint64_t>(kpad, ((uint64_t)n + 255) / 256 * 256) / 256 * sizeof(unsigned int), true))) return rc;
+    }
+    if ((rc = ensure(ctx, ctx->squares, (uint64_t)kMaxRowsPerPass * 1024 * sizeof(float), true))) return rc;
     // partial sums: the widest split is one unit per warp and two warps per tile ... bounded by the
     // plan for the narrowest block (32), computed with the resident grid of the largest kernel
     const uint32_t ntiles = (n + kTileRows - 1) / kTileRows;
@@ -458,15 +481,15 @@ int32_t neura_cuda_stage_window(nc_context *ctx, void *stream_, const float *x_d
     const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
     const uint32_t ncols = rows * 3;
     int32_t rc;
-    if ((rc = ensure(ctx, ctx->dig, kpad * ncols, false))) return rc;
-    if ((rc = ensure(ctx, ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
-    if ((rc = ensure(ctx, ctx->sums, kpad / 256 * ncols * 64, false))) return rc;
+    if ((rc = ensure(ctx, ctx->slots[ctx->cur].dig, kpad * ncols, false))) return rc;
+    if ((rc = ensure(ctx, ctx->slots[ctx->cur].cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->slots[ctx->cur].sums, kpad / 256 * ncols * 64, false))) return rc;
     PrepParams prep;
     prep.x = x_dev;
     prep.x_stride = x_stride;
-    prep.dig = (int8_t *)ctx->dig.ptr;
-    prep.cs = (float *)ctx->cs.ptr;
-    prep.sums = (uint32_t *)ctx->sums.ptr;
+    prep.dig = (int8_t *)ctx->slots[ctx->cur].dig.ptr;
+    prep.cs = (float *)ctx->slots[ctx->cur].cs.ptr;
+    prep.sums = (uint32_t *)ctx->slots[ctx->cur].sums.ptr;
     prep.rows = rows;
     prep.k = k;
     prep.ncols = ncols;
@@ -478,9 +501,9 @@ int32_t neura_cuda_stage_window(nc_context *ctx, void *stream_, const float *x_d
     NC_CUDA(launch_dependent(prep_kernel, dim3((unsigned int)((prep_warps + 3) / 4)), dim3(128), 0,
                              (cudaStream_t)stream_, prep));
     ctx->launches++;
-    ctx->staged_rows = rows;
-    ctx->staged_k = k;
-    ctx->staged_granule = prep.granule;
+    ctx->slots[ctx->cur].rows = rows;
+    ctx->slots[ctx->cur].k = k;
+    ctx->slots[ctx->cur].granule = prep.granule;
     return 0;
 }
 
@@ -502,9 +525,9 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     // a pair is planned as the matrix of both tensors' rows, 16 of each per 32-row tile
     const uint32_t plan_n = pair ? (w->n + 15) / 16 * 32 : w->n;
     const uint32_t granule = w->element == NC_ELEMENT_Q4K ? 256 : 32;
-    if (!ctx->staged_rows || ctx->staged_k != w->k || ctx->staged_granule != granule)
+    if (!ctx->slots[ctx->cur].rows || ctx->slots[ctx->cur].k != w->k || ctx->slots[ctx->cur].granule != granule)
         return refuse(kBadArgument, "the staged activations (%u rows of %u for blocks of %u) do not fit a [%u, %u] weight of element %u",
-                      ctx->staged_rows, ctx->staged_k, ctx->staged_granule, w->n, w->k, w->element);
+                      ctx->slots[ctx->cur].rows, ctx->slots[ctx->cur].k, ctx->slots[ctx->cur].granule, w->n, w->k, w->element);
     if (out_stride < w->n)
         return refuse(kBadArgument, "rows of %u outputs overlap at stride %llu", w->n, (unsigned long long)out_stride);
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
@@ -513,19 +536,19 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     cudaStream_t stream = (cudaStream_t)stream_;
     // a launch carries at most kRowsPerLaunch rows: beyond that the accumulators of the wider MMA tiles spill
     // and two launches over the same weights are faster than one
-    for (uint32_t first = 0; first < ctx->staged_rows; first += kRowsPerLaunch) {
+    for (uint32_t first = 0; first < ctx->slots[ctx->cur].rows; first += kRowsPerLaunch) {
         GemvParams p;
         memset(&p, 0, sizeof p);
         p.w = (const uint8_t *)w->data_dev;
-        p.dig = (const uint8_t *)ctx->dig.ptr;
-        p.cs = (const float *)ctx->cs.ptr;
-        p.sums = (const uint8_t *)ctx->sums.ptr;
+        p.dig = (const uint8_t *)ctx->slots[ctx->cur].dig.ptr;
+        p.cs = (const float *)ctx->slots[ctx->cur].cs.ptr;
+        p.sums = (const uint8_t *)ctx->slots[ctx->cur].sums.ptr;
         p.out = out_dev + (uint64_t)first * out_stride;
         p.out_stride = out_stride;
         p.n = w->n;
-        p.rows = std::min(kRowsPerLaunch, ctx->staged_rows - first);
+        p.rows = std::min(kRowsPerLaunch, ctx->slots[ctx->cur].rows - first);
         p.ncols = p.rows * 3;
-        p.col_stride = ctx->staged_rows * 3;
+        p.col_stride = ctx->slots[ctx->cur].rows * 3;
         p.col0 = first * 3;
         p.pair = pair ? 1u : 0u;
         p.chain.n = n_steps;
@@ -540,6 +563,97 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
         default: rc = launch_gemv<3>(ctx, stream, w->element, p, plan_n, w->k); break;
         }
         if (rc) return rc;
+    }
+    return 0;
+}
+
+int32_t neura_cuda_staging_select(nc_context *ctx, uint32_t slot) {
+    if (!ctx || slot >= kStagingSlots) return refuse(kBadArgument, "a context holds staging slots 0 to %u", kStagingSlots - 1);
+    ctx->cur = slot;
+    return 0;
+}
+
+int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream_, const nc_weight *w, float *out_dev, uint64_t out_stride,
+                                      const nc_step *chain, uint32_t n_steps, uint32_t normed, float floor,
+                                      uint32_t then_slot, const float *then_gain_dev, uint32_t then_squares) {
+    if (!ctx || !out_dev) return refuse(kBadArgument, "a product needs a context and an output");
+    int32_t rc;
+    if ((rc = check_weight(w))) return rc;
+    if (w->layout != NC_LAYOUT_TILED && w->layout != NC_LAYOUT_TILED_PAIR)
+        return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order");
+    Staging &from = ctx->slots[ctx->cur];
+    const bool pair = w->layout == NC_LAYOUT_TILED_PAIR;
+    const uint32_t plan_n = pair ? (w->n + 15) / 16 * 32 : w->n;
+    const uint32_t granule = w->element == NC_ELEMENT_Q4K ? 256 : 32;
+    if (!from.rows || from.k != w->k || from.granule != granule)
+        return refuse(kBadArgument, "the staged activations (%u rows of %u for blocks of %u) do not fit a [%u, %u] weight of element %u",
+                      from.rows, from.k, from.granule, w->n, w->k, w->element);
+    if (from.rows > 2) return refuse(kBadArgument, "a product that stages its own output carries 1 or 2 rows, not %u", from.rows);
+    const bool then = then_slot != NC_NO_SLOT;
+    if (then && (then_slot >= kStagingSlots || then_slot == ctx->cur))
+        return refuse(kBadArgument, "the output is staged into another slot than the one the product reads (0 to %u)", kStagingSlots - 1);
+    if (out_stride < w->n || out_stride % 4 || (uintptr_t)out_dev % 16)
+        return refuse(kBadArgument, "output rows of %u start 16-byte aligned and do not overlap (stride %llu)", w->n, (unsigned long long)out_stride);
+    if (then && w->n % 8) return refuse(kBadArgument, "%u outputs do not stage in whole runs of eight", w->n);
+    if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
+        return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
+    // the slot the output is staged into
+    Staging &to = ctx->slots[then ? then_slot : ctx->cur];
+    const uint64_t kpad = ((uint64_t)w->n + 255) / 256 * 256;
+    const uint32_t ncols = from.rows * 3;
+    if (then) {
+        if (kpad / 256 > 1024) return refuse(kBadArgument, "rows of %u outputs are more than this path stages (262144)", w->n);
+        if ((rc = ensure(ctx, to.dig, kpad * ncols, false))) return rc;
+        if ((rc = ensure(ctx, to.cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
+        if ((rc = ensure(ctx, to.sums, kpad / 256 * ncols * 64, false))) return rc;
+        if ((rc = ensure(ctx, to.chunks, kpad / 256 * sizeof(unsigned int), true))) return rc;
+    }
+    if ((rc = ensure(ctx, ctx->squares, (uint64_t)kMaxRowsPerPass * 1024 * sizeof(float), true))) return rc;
+    GemvParams p;
+    memset(&p, 0, sizeof p);
+    p.w = (const uint8_t *)w->data_dev;
+    p.dig = (const uint8_t *)from.dig.ptr;
+    p.cs = (const float *)from.cs.ptr;
+    p.sums = (const uint8_t *)from.sums.ptr;
+    p.out = out_dev;
+    p.out_stride = out_stride;
+    p.n = w->n;
+    p.rows = from.rows;
+    p.ncols = ncols;
+    p.col_stride = ncols;
+    p.col0 = 0;
+    p.pair = pair ? 1u : 0u;
+    p.chain.n = n_steps;
+    for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
+    if (normed) {   // the input rows were staged with a norm's gain: their scalar is still to be applied
+        p.sumsq = (const float *)ctx->squares.ptr;
+        p.sumsq_chunks = (from.k + 255) / 256;
+        p.floor = floor;
+        p.inv_k = 1.0f / (float)from.k;
+    }
+    p.has_then = then ? 1u : 0u;
+    StageAfter &a = p.then;
+    a.prep.x = out_dev;
+    a.prep.x_stride = out_stride;
+    a.prep.dig = (int8_t *)to.dig.ptr;
+    a.prep.cs = (float *)to.cs.ptr;
+    a.prep.sums = (uint32_t *)to.sums.ptr;
+    a.prep.rows = from.rows;
+    a.prep.k = w->n;
+    a.prep.ncols = ncols;
+    a.prep.granule = granule;
+    a.prep.vector = 1;
+    a.prep.lo = 0;
+    a.prep.hi = w->n;
+    a.gain = then_gain_dev;
+    a.sumsq = then_squares ? (float *)ctx->squares.ptr : nullptr;
+    a.counters = (unsigned int *)to.chunks.ptr;
+    a.piece = pair ? 16 : 32;
+    if ((rc = launch_gemv_hooked(ctx, (cudaStream_t)stream_, w->element, p, plan_n, w->k))) return rc;
+    if (then) {
+        to.rows = from.rows;
+        to.k = w->n;
+        to.granule = granule;
     }
     return 0;
 }
@@ -679,14 +793,14 @@ int32_t norm_stage_params(nc_context *ctx, const float *x_dev, uint32_t rows, ui
     const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
     const uint32_t ncols = rows * 3;
     int32_t rc;
-    if ((rc = ensure(ctx, ctx->dig, kpad * ncols, false))) return rc;
-    if ((rc = ensure(ctx, ctx->cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
-    if ((rc = ensure(ctx, ctx->sums, kpad / 256 * ncols * 64, false))) return rc;
+    if ((rc = ensure(ctx, ctx->slots[ctx->cur].dig, kpad * ncols, false))) return rc;
+    if ((rc = ensure(ctx, ctx->slots[ctx->cur].cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
+    if ((rc = ensure(ctx, ctx->slots[ctx->cur].sums, kpad / 256 * ncols * 64, false))) return rc;
     p.prep.x = x_dev;
     p.prep.x_stride = x_stride;
-    p.prep.dig = (int8_t *)ctx->dig.ptr;
-    p.prep.cs = (float *)ctx->cs.ptr;
-    p.prep.sums = (uint32_t *)ctx->sums.ptr;
+    p.prep.dig = (int8_t *)ctx->slots[ctx->cur].dig.ptr;
+    p.prep.cs = (float *)ctx->slots[ctx->cur].cs.ptr;
+    p.prep.sums = (uint32_t *)ctx->slots[ctx->cur].sums.ptr;
     p.prep.rows = rows;
     p.prep.k = k;
     p.prep.ncols = ncols;
@@ -714,9 +828,9 @@ int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x
         return rc;
     NC_CUDA(launch_dependent(rms_norm_stage_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream_, p));
     ctx->launches++;
-    ctx->staged_rows = rows;
-    ctx->staged_k = k;
-    ctx->staged_granule = p.prep.granule;
+    ctx->slots[ctx->cur].rows = rows;
+    ctx->slots[ctx->cur].k = k;
+    ctx->slots[ctx->cur].granule = p.prep.granule;
     return 0;
 }
 
@@ -996,9 +1110,9 @@ int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream_, nc_comm 
     p.status = (unsigned int *)ctx->status.ptr;
     NC_CUDA(launch_dependent(allreduce_norm_stage_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream_, p, then));
     ctx->launches++;
-    ctx->staged_rows = rows;
-    ctx->staged_k = k;
-    ctx->staged_granule = then.prep.granule;
+    ctx->slots[ctx->cur].rows = rows;
+    ctx->slots[ctx->cur].k = k;
+    ctx->slots[ctx->cur].granule = then.prep.granule;
     return 0;
 }
 
@@ -1394,6 +1508,10 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         a.sumsq = squares ? sumsq : nullptr;
         a.counters = to.counters;
         a.piece = piece;
+        if (ph.kind == MK_GEMV) {
+            ph.g.then = a;
+            ph.g.has_then = 1;
+        }
     };
     auto product = [&](const nc_weight &w, const Staged &from, bool normed, float *out_rows, uint64_t out_stride,
                        const float *residual) -> MkPhase & {

@@ -46,6 +46,9 @@ def payload_bytes(element: int, elements: int) -> int:
     return int(_lib.load().neura_cuda_payload_bytes(element, elements))
 
 
+NO_SLOT = 0xFFFFFFFF   # NC_NO_SLOT
+
+
 @dataclass
 class DeviceTensor:
     """A run of f32 (or raw bytes) in device memory owned by a Runtime."""
@@ -320,6 +323,23 @@ class Runtime:
         _check(self._lib.neura_cuda_linear_staged(
             self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(out_ptr if out_ptr is not None else out.ptr),
             out_stride if out_stride is not None else out.shape[-1], arr, count))
+
+    def staging_select(self, slot: int) -> None:
+        """Which of the context's three staged forms ``stage`` writes and the staged products read."""
+        _check(self._lib.neura_cuda_staging_select(self._ctx, slot))
+
+    def linear_staged_then(self, weight: Weight, out: DeviceTensor, chain: Optional[Sequence[Step]] = None,
+                           normed: bool = False, floor: float = 0.0, then_slot: Optional[int] = None,
+                           gain: Optional[DeviceTensor] = None, squares: bool = False) -> None:
+        """``linear_staged`` (1 or 2 rows) that applies the rms_norm scalar of its input when the input was staged
+        with a norm's gain (``normed``), and whose epilogue stages its output rows into ``then_slot`` for the next
+        product, multiplied by ``gain`` and leaving their sums of squares (``squares``)."""
+        arr, count = self._steps(chain, weight.n)
+        rec = weight.record()
+        _check(self._lib.neura_cuda_linear_staged_then(
+            self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(out.ptr), out.shape[-1], arr, count,
+            1 if normed else 0, floor, NO_SLOT if then_slot is None else then_slot,
+            ctypes.c_void_p(gain.ptr) if gain is not None else None, 1 if squares else 0))
 
     # -- the steps either side of the products ---------------------------------------
     def tensor_u32(self, count: int) -> DeviceTensor:

@@ -122,10 +122,11 @@ SMALL = {
 }
 
 
-@pytest.mark.parametrize("name,batch", [("q8_0", 1), ("q4_k", 1), ("q4_k", 3)])
+@pytest.mark.parametrize("name,batch", [("q8_0", 1), ("q4_k", 1), ("q4_k", 3), ("q4_k-folded", 2), ("q8_0-folded", 1)])
 def test_greedy_tokens_match_the_oracle_for_64_steps(oracle, name, batch):
     from oracle.decoder import OracleDecoder, synthetic_model
 
+    name, _, folded = name.partition("-")   # "-folded": norms and stagings in the products' epilogues
     config = SMALL[name]
     packed, norms = synthetic_model(config, seed=23)
     prompts = (oracle.Stream(29).uniform(batch * 16, 0.0, 1.0) * config.vocab).astype(np.uint32).reshape(batch, 16)
@@ -135,6 +136,8 @@ def test_greedy_tokens_match_the_oracle_for_64_steps(oracle, name, batch):
     try:
         weights, dnorms = load_model(rt, config, packed, norms)
         decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=96)
+        decoder.fold = bool(folded)
+        assert decoder.folded() == bool(folded)
         eager = decoder.generate(prompts, 64)
         decoder.record()
         replayed = decoder.generate(prompts, 64)
