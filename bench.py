@@ -106,6 +106,16 @@ def workload_config(name: str):
     raise SystemExit(f"unknown workload {name}")
 
 
+def workload_description(config, prompt: int, rows: int, parallelism: str) -> dict:
+    """The `config` object of a line: both arms describe the workload the same way."""
+    return {"workload": f"{config.name} decode: {config.layers} layers, hidden {config.hidden}, "
+                        f"{config.heads}/{config.key_heads} heads x {config.head_width}, ff {config.feed_forward}, "
+                        f"vocab {config.vocab}; {prompt}-token random prompt, greedy",
+            "batch": rows, "parallelism": parallelism,
+            "l2": f"inputs larger than L2 ({config.weight_bytes() / 1e9:.2f} GB of weights per step)",
+            "weight_bytes_per_token": config.weight_bytes()}
+
+
 def cpu_baseline(config, seconds: float = 12.0):
     """The oracle's product (the reference tests' f32 loop over unpacked blocks) on the host
     cores, on a bounded sample of the token: rows of the up projection of one layer."""
@@ -162,8 +172,8 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": config.name, "batch": 1},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_description(config, args.prompt, 1, "host cores"),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -318,12 +328,8 @@ def run_ours(args):
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{config.name} decode: {config.layers} layers, hidden {config.hidden}, "
-                                   f"{config.heads}/{config.key_heads} heads x {config.head_width}, ff {config.feed_forward}, "
-                                   f"vocab {config.vocab}; {args.prompt}-token random prompt, greedy",
-                       "batch": rows, "parallelism": f"tp{world} ({args.comm} all-reduce)" if world > 1 else "single GPU",
-                       "l2": f"inputs larger than L2 ({config.weight_bytes() / 1e9:.2f} GB of weights per step)",
-                       "weight_bytes_per_token": config.weight_bytes()},
+            "config": workload_description(config, args.prompt, rows,
+                                           f"tp{world} ({args.comm} all-reduce)" if world > 1 else "single GPU"),
             "clocks": clock_summary,
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
