@@ -295,7 +295,7 @@ __device__ __forceinline__ void rms_norm_stage_row(const NormStageParams &p, uin
     }
 }
 
-__global__ void __launch_bounds__(256) rms_norm_stage_kernel(const __grid_constant__ NormStageParams p) {
+__global__ void __launch_bounds__(1024) rms_norm_stage_kernel(const __grid_constant__ NormStageParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float partial[32];
