@@ -234,27 +234,48 @@ __global__ void __launch_bounds__(kAttendThreads) attend_kernel(const __grid_con
         if (lane == 0) { stats[g * 2] = largest; stats[g * 2 + 1] = sum; }
     }
     __syncthreads();
-    // weighted values: one thread per channel, every value row read once for all the group's heads
-    for (uint32_t d = threadIdx.x; d < WIDTH; d += blockDim.x) {
+    // weighted values: a thread per channel, every value row read once for all the group's heads.  With at least
+    // 2 * WIDTH threads two threads share a channel, one taking the even positions and one the odd; the odd half
+    // hands its sums over through the query rows (no longer needed) and the even half adds them.
+    {
+        const uint32_t parts = blockDim.x >= 2 * WIDTH ? 2u : 1u;
+        const uint32_t part = threadIdx.x / WIDTH, d = threadIdx.x % WIDTH;
         float acc[kAttendMaxGroup];
 #pragma unroll
         for (uint32_t g = 0; g < kAttendMaxGroup; ++g) acc[g] = 0.0f;
-        for (uint32_t pos = 0; pos < held; ++pos) {
-            const float value = vs[pos * WIDTH + d];
+        if (part < parts) {
+            for (uint32_t pos = part; pos < held; pos += parts) {
+                const float value = vs[pos * WIDTH + d];
 #pragma unroll
-            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
-                if (g < group) acc[g] = fmaf(logits[g * kAttendMaxChunk + pos], value, acc[g]);
+                for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                    if (g < group) acc[g] = fmaf(logits[g * kAttendMaxChunk + pos], value, acc[g]);
+            }
         }
-        if constexpr (CLUSTER) {
-            // (every thread of the CTA is past the logits phase, which was the last reader of the key tile)
+        if (parts == 2) {
+            if (part == 1) {
 #pragma unroll
-            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
-                if (g < group) ks[g * WIDTH + d] = acc[g];
-        } else {
+                for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                    if (g < group) qs[g * WIDTH + d] = acc[g];
+            }
+            __syncthreads();
+            if (part == 0) {
 #pragma unroll
-            for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
-                if (g < group)
-                    __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (WIDTH + 2) + d, acc[g]);
+                for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                    if (g < group) acc[g] += qs[g * WIDTH + d];
+            }
+        }
+        if (part == 0) {
+            if constexpr (CLUSTER) {
+                // (every thread of the CTA is past the logits phase, which was the last reader of the key tile)
+#pragma unroll
+                for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                    if (g < group) ks[g * WIDTH + d] = acc[g];
+            } else {
+#pragma unroll
+                for (uint32_t g = 0; g < kAttendMaxGroup; ++g)
+                    if (g < group)
+                        __stcg(p.partial + (((uint64_t)b * p.heads + kh * group + g) * p.splits + split) * (WIDTH + 2) + d, acc[g]);
+            }
         }
     }
     if constexpr (CLUSTER) {
