@@ -5,6 +5,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+# NEURA_CUDA_LIB names another build of the same library (a build with other compile-time knobs, for A/B timing)
 LIB_PATH = os.environ.get("NEURA_CUDA_LIB") or os.path.join(HERE, "lib", "libneura_cuda.so")
 
 # every symbol include/neura_cuda.h declares

@@ -10,7 +10,7 @@ ELEMENTS = [nb.Q8_0, nb.Q4K]
 # the reference's own bar: |device - naive f32 loop| <= 1e-3 absolute on uniform(-1, 1) data
 # (crates/neura-runtime/tests/runtime.rs:85, tests/support/mod.rs:50-67)
 ABS_TOL = 1e-3
-# BASELINE north star: within 1e-3 relative
+# the bar of this path: within 1e-3 relative (fp32 accumulation-order differences only)
 REL_TOL = 1e-3
 
 
