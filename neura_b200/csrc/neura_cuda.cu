@@ -134,7 +134,8 @@ GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t
     const uint64_t units = (uint64_t)plan.ntiles * plan.upt;  // below 2^32: n and k are 32-bit, units = n*k/8192 at most
     // 32-row units a warp should at least stream (Q4_K: one; a sweep over 1, 2, 3, 4, 6 on the 32B decode step gave
     // 6.04, 6.12, 6.42, 6.25, 6.69 ms: the small projections want every warp)
-    const uint64_t least = element == NC_ELEMENT_Q4K ? 1 : 8;
+    // (Q8_0: one stage of four units; 2, 4, 8, 16 gave 823, 890, 826, 668 tok/s on the 0.5B decoder)
+    const uint64_t least = element == NC_ELEMENT_Q4K ? 1 : 4;
     uint64_t warps = (uint64_t)ctx->sms * resident_blocks_per_sm * kGemvWarps;
     if (warps > units / least) warps = units / least;
     if (warps < 1) warps = 1;
@@ -1360,7 +1361,7 @@ void plan_phase(GemvParams &g, uint32_t element, uint32_t plan_n, uint32_t k, ui
     const uint32_t ntiles = (plan_n + kTileRows - 1) / kTileRows;
     g.upt = k / block_elements(element);
     const uint64_t units = (uint64_t)ntiles * g.upt;
-    const uint64_t least = element == NC_ELEMENT_Q4K ? 1 : 8;
+    const uint64_t least = element == NC_ELEMENT_Q4K ? 1 : 4;
     if (warps > units / least) warps = units / least;
     if (warps < 1) warps = 1;
     g.nwarps = (uint32_t)warps;
