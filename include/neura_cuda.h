@@ -115,6 +115,18 @@ int32_t neura_cuda_write(nc_context *ctx, void *stream, void *dst_dev, const voi
 int32_t neura_cuda_read(nc_context *ctx, void *stream, void *dst_host, const void *src_dev, uint64_t bytes);
 int32_t neura_cuda_sync(nc_context *ctx, void *stream);
 
+/* Free and total bytes of the context's GPU (what a host sizes its heap request from, MemoryRequest,
+ * runtime.rs:150-167). */
+int32_t neura_cuda_memory(nc_context *ctx, uint64_t *free_out, uint64_t *total_out);
+
+/* How long a kernel of this context waits for another party before it gives up: a peer's flag in an
+ * all-reduce, the other CTAs at the grid barrier of the persistent step (the reference's hang deadline,
+ * FRAME_TIMEOUT, crates/neura-gpu/src/native.rs:20-35).  Default two seconds.  A kernel that gives up
+ * raises the context's status word and returns; the next neura_cuda_sync reports it as a refusal and
+ * clears it, and the context stays usable.  (Waits for a kernel's own asynchronous copies keep a fixed
+ * two-second limit.) */
+int32_t neura_cuda_set_wait_limit(nc_context *ctx, uint64_t nanoseconds);
+
 /* Grows the context's scratch ahead of time so that later linear calls of up to
  * `rows` activation rows against matrices of up to [n, k] never allocate. */
 int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k);
@@ -259,12 +271,18 @@ int32_t neura_cuda_advance(nc_context *ctx, void *stream, uint32_t *position_dev
 typedef struct nc_comm nc_comm;
 int32_t neura_cuda_comm_create(nc_context *ctx, uint64_t max_count, nc_comm **out, void *handle_out);
 int32_t neura_cuda_comm_connect(nc_context *ctx, nc_comm *comm, uint32_t rank, uint32_t world, const void *handles);
+/* The same for a group whose communicators all live in this process (one host thread per GPU, or a test
+ * with several seats on one GPU): `all` holds the `world` communicators in rank order, all[rank] == comm;
+ * peers on other GPUs are reached through peer access, which this call enables. */
+int32_t neura_cuda_comm_connect_local(nc_context *ctx, nc_comm *comm, uint32_t rank, uint32_t world, nc_comm *const *all);
 int32_t neura_cuda_comm_destroy(nc_context *ctx, nc_comm *comm);
 
 /* inout_dev[i] <- sum over the ranks of their inout_dev[i], added in rank order (every rank gets
- * the same bits).  One kernel: the ranks' partial sums cross NVLink as plain peer loads, the only
- * waiting is on the peers' sequence flags, bounded by a two-second timer; a rank that gives up
- * leaves its input untouched and the next neura_cuda_sync returns the refusal.  Every rank must
+ * the same bits).  One kernel: every rank pushes its partial sums into its seat of every peer's buffer
+ * (plain peer stores over NVLink; nothing is read remotely), the only waiting is on the peers' sequence
+ * flags, bounded by the context's wait limit; a rank that gives up leaves its input untouched, the
+ * next neura_cuda_sync returns the refusal, and the call can be issued again (it repeats its sequence
+ * number and completes once the missing peer has pushed).  Every rank must
  * issue the same calls in the same order.  `count` is a multiple of 4, `inout_dev` 16-byte aligned. */
 int32_t neura_cuda_allreduce(nc_context *ctx, void *stream, nc_comm *comm, float *inout_dev, uint32_t count);
 
@@ -282,8 +300,11 @@ int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream, nc_comm *
  * cudaMalloc, cudaFree or other allocating call.
  *  - limits: 1 to 4 rows, w->k <= 32768, w->n <= 262144; anything larger is refused with a
  *    sentence in neura_cuda_last_error();
- *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress):
- *    make that first call outside any stream capture;
+ *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress) and has
+ *    the CUDA runtime load the kernels the entry point can launch (loading a kernel on first use may
+ *    allocate): make that first call at set-up time, outside any stream capture; later calls only launch;
+ *  - a kernel that gives up on a bounded wait raises a status word kept in the array; neura_cuda_sync
+ *    reports it like any other refusal;
  *  - all calls on a device share the array: two calls whose kernels can overlap on the GPU
  *    (different streams without an ordering between them) race; order them. */
 int32_t neura_cuda_linear_static(nc_context *ctx, void *stream, const nc_weight *w, const float *x_dev,

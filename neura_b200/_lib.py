@@ -22,7 +22,7 @@ SYMBOLS = [
     "neura_cuda_weight_seal_pair", "neura_cuda_linear_bf16", "neura_cuda_comm_create",
     "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce", "neura_cuda_reserve_decoder",
     "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free", "neura_cuda_decoder_trace", "neura_cuda_rope_attend", "neura_cuda_rope_table", "neura_cuda_allreduce_norm_stage", "neura_cuda_staging_select",
-    "neura_cuda_linear_staged_then",
+    "neura_cuda_linear_staged_then", "neura_cuda_set_wait_limit", "neura_cuda_memory", "neura_cuda_comm_connect_local",
 ]
 
 
@@ -135,6 +135,9 @@ def load() -> ctypes.CDLL:
         "neura_cuda_comm_connect": (i32, [p, p, u32, u32, p]),
         "neura_cuda_comm_destroy": (i32, [p, p]),
         "neura_cuda_allreduce": (i32, [p, p, p, p, u32]),
+        "neura_cuda_set_wait_limit": (i32, [p, u64]),
+        "neura_cuda_memory": (i32, [p, ctypes.POINTER(u64), ctypes.POINTER(u64)]),
+        "neura_cuda_comm_connect_local": (i32, [p, p, u32, u32, pp]),
         "neura_cuda_stage_window": (i32, [p, p, p, u32, u64, u32, u32, u32, u32]),
         "neura_cuda_linear_static": (i32, [p, p, ctypes.POINTER(NcWeight), p, u32, u64, p, u64, ctypes.POINTER(NcStep), u32]),
     }

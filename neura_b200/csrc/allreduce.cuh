@@ -8,7 +8,9 @@
 // until all senders' flags in its own memory show that number (local acquire loads, bounded by a
 // timer) and adds the seats in rank order, so every rank computes bit-identical sums.  Two slots
 // suffice: a rank can only reach call s+2 after every peer has published s+1, i.e. has finished
-// reading call s.  A wait that runs out raises the status word and leaves the input untouched.
+// reading call s.  A wait that runs out (the context's wait limit) raises the status word and leaves
+// the input untouched; the call counter stays, so the next call repeats the sequence number and
+// completes once the missing peer has published it.
 #pragma once
 #include "common.cuh"
 #include "gemv_mma.cuh"
@@ -26,6 +28,7 @@ struct AllreduceParams {
     uint64_t slot_bytes;                 // bytes of one sender's seat; a slot is world seats
     uint32_t count, world, rank;
     unsigned int *status;
+    unsigned long long wait_nanos;       // how long a rank waits for its peers' flags before it gives up
 };
 
 __device__ __forceinline__ unsigned int load_acquire_sys(const unsigned int *p) {
@@ -69,7 +72,7 @@ __device__ __forceinline__ bool allreduce_body(const AllreduceParams &p) {
         const unsigned long long start = global_nanos();
         // (flags only grow; a peer may already be one call ahead)
         while ((int)(load_acquire_sys(flag) - seq) < 0) {
-            if (global_nanos() - start > kWaitNanos) { gave_up = 1u; break; }
+            if (global_nanos() - start > p.wait_nanos) { gave_up = 1u; break; }
         }
     }
     __syncthreads();

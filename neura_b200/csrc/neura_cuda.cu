@@ -21,6 +21,10 @@
 
 using namespace nc;
 
+#ifndef NC_GEMV_STAGES
+#define NC_GEMV_STAGES 2
+#endif
+
 namespace {
 
 thread_local std::string g_error;
@@ -77,6 +81,7 @@ struct nc_context {
     Region squares;              // [rows][chunks] sums of squares left by an epilogue that staged with a norm's gain
     Region partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch, x_bf16;
     uint64_t launches = 0;
+    unsigned long long wait_nanos = 2000000000ull;   // how long a kernel waits for another party (neura_cuda_set_wait_limit)
     bool capturing = false;
     cudaStream_t capture_stream = nullptr;
     uint64_t capture_mark = 0;
@@ -89,6 +94,7 @@ struct nc_comm {
     uint64_t slot_bytes = 0, max_count = 0;
     uint32_t world = 0, rank = 0;
     bool connected = false;
+    bool local = false;   // the peers are communicators of this process (plain pointers, nothing to unmap)
 };
 
 struct nc_program {
@@ -147,9 +153,6 @@ GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t
     return plan;
 }
 
-#ifndef NC_GEMV_STAGES
-#define NC_GEMV_STAGES 2
-#endif
 constexpr int kStages = NC_GEMV_STAGES;   // ring depth of the streaming product (stages a warp)
 
 // Launches with the programmatic-stream-serialization attribute, so that a kernel's
@@ -231,13 +234,95 @@ int32_t check_weight(const nc_weight *w) {
 
 // The device status word (the reference's refusal word, crates/neura-kernel/src/substrate.rs:93-100):
 // read after a synchronisation, non-zero when a kernel gave up on a bounded wait.
+// ---------------------------------------------------------------------------------------
+// Scratch of the product for callers that must not allocate (neura_cuda_linear_static).
+//
+// Everything neura_cuda_linear keeps in scratch that it may have to cudaMalloc (digit
+// planes, digit scales, split-tile partial sums, tile counters, the status word) lives
+// here in one fixed array inside the library image.  Every GPU whose context loads the
+// library carries these 16 MiB until the process exits.
+// ---------------------------------------------------------------------------------------
+constexpr uint64_t kStaticScratchBytes = 16ull << 20;
+constexpr uint32_t kStaticMaxRows = 4;
+constexpr uint32_t kStaticMaxK = 32768;
+constexpr uint32_t kStaticMaxN = 262144;
+constexpr uint64_t kStaticCountersBytes = (uint64_t)(kStaticMaxN / kTileRows) * sizeof(unsigned int);
+constexpr int kStaticDevices = 64;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// `g_static_scratch` names a host-side shadow in host code, not device memory: the device
+// address has to be asked for, once per device, with that device current.
+struct StaticScratch {
+    unsigned char *base = nullptr;   // the array's address on this device, null until the first call
+    int resident[4] = {0, 0, 0, 0};  // CTAs of each kernel variant an SM holds
+};
+StaticScratch g_static[kStaticDevices];
+
+// The four kernels the allocation-free product may launch: Q8_0 / Q4_K, one or two 8-column MMA tiles.
+void (*static_variant(int variant))(GemvParams) {
+    switch (variant) {
+    case 0: return gemv_stream_kernel<false, 1, NC_GEMV_STAGES>;
+    case 1: return gemv_stream_kernel<false, 2, NC_GEMV_STAGES>;
+    case 2: return gemv_stream_kernel<true, 1, NC_GEMV_STAGES>;
+    default: return gemv_stream_kernel<true, 2, NC_GEMV_STAGES>;
+    }
+}
+size_t static_variant_smem(int variant) {
+    const size_t stage = variant >= 2 ? kQ4kStage : kQ8Stage;
+    const int nt = (variant & 1) + 1;
+    return kGemvWarps * NC_GEMV_STAGES * (stage + 8) + kGemvWarps * 32 * (nt * 8 + 1) * sizeof(float);
+}
+
+// The first call on a device: looks the array's device address up and makes the runtime load every kernel the
+// entry point may launch (loading a kernel's code on first use may allocate), so that later calls only launch.
+int32_t static_setup(int device) {
+    StaticScratch &fixed = g_static[device];
+    if (fixed.base) return 0;
+    NC_CUDA(cudaSetDevice(device));
+    unsigned char *address = nullptr;
+    NC_CUDA(cudaGetSymbolAddress((void **)&address, g_static_scratch));
+    if (!address) return refuse(kBadState, "the static scratch has no address on device %d", device);
+    for (int variant = 0; variant < 4; ++variant) {
+        NC_CUDA(cudaFuncSetAttribute(static_variant(variant), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)static_variant_smem(variant)));
+        NC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fixed.resident[variant], static_variant(variant),
+                                                              kGemvWarps * 32, static_variant_smem(variant)));
+        if (fixed.resident[variant] < 1) return refuse(kBadState, "the product kernel does not fit an SM");
+    }
+    cudaFuncAttributes attributes;
+    NC_CUDA(cudaFuncGetAttributes(&attributes, prep_kernel));
+    fixed.base = address;
+    return 0;
+}
+
+unsigned int *static_status_of(int device) {
+    return device >= 0 && device < kStaticDevices ? (unsigned int *)g_static[device].base : nullptr;
+}
+
+// After a reported failure: the status word and the tile counters start from zero again.
+int32_t static_scratch_clear(int device) {
+    NC_CUDA(cudaMemset(g_static[device].base, 0, 256 + kStaticCountersBytes));
+    return 0;
+}
+
+const char *status_sentence(unsigned int word) {
+    if (word & 4u) return "an all-reduce gave up waiting for a peer's partial sums";
+    if (word & 2u) return "a kernel gave up waiting at a barrier";
+    return "a kernel gave up waiting for its own copies";
+}
+
 int32_t check_status(nc_context *ctx) {
-    if (!ctx->status.ptr) return 0;
-    unsigned int word = 0;
-    NC_CUDA(cudaMemcpy(&word, ctx->status.ptr, sizeof word, cudaMemcpyDeviceToHost));
-    if (word == 0) return 0;
-    NC_CUDA(cudaMemset(ctx->status.ptr, 0, sizeof word));
-    return refuse(kDeviceRefusal, "a kernel gave up waiting for its own copies (status %u); its output is not valid", word);
+    unsigned int word = 0, fixed = 0;
+    if (ctx->status.ptr) NC_CUDA(cudaMemcpy(&word, ctx->status.ptr, sizeof word, cudaMemcpyDeviceToHost));
+    unsigned int *fixed_dev = static_status_of(ctx->device);
+    if (fixed_dev) NC_CUDA(cudaMemcpy(&fixed, fixed_dev, sizeof fixed, cudaMemcpyDeviceToHost));
+    if (word == 0 && fixed == 0) return 0;
+    if (word) NC_CUDA(cudaMemset(ctx->status.ptr, 0, sizeof word));
+    if (fixed) {   // a product that gave up may have left tile counters behind: the array starts over
+        int32_t rc = static_scratch_clear(ctx->device);
+        if (rc) return rc;
+    }
+    return refuse(kDeviceRefusal, "%s (status %u); its output is not valid", status_sentence(word | fixed), word | fixed);
 }
 
 }  // namespace
@@ -343,6 +428,22 @@ int32_t neura_cuda_sync(nc_context *ctx, void *stream) {
     if (!ctx) return refuse(kBadArgument, "sync needs a context");
     NC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return check_status(ctx);
+}
+
+int32_t neura_cuda_set_wait_limit(nc_context *ctx, uint64_t nanoseconds) {
+    if (!ctx || !nanoseconds) return refuse(kBadArgument, "a wait limit needs a context and a time above zero");
+    ctx->wait_nanos = nanoseconds;
+    return 0;
+}
+
+int32_t neura_cuda_memory(nc_context *ctx, uint64_t *free_out, uint64_t *total_out) {
+    if (!ctx) return refuse(kBadArgument, "a memory query needs a context");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    size_t free_bytes = 0, total_bytes = 0;
+    NC_CUDA(cudaMemGetInfo(&free_bytes, &total_bytes));
+    if (free_out) *free_out = free_bytes;
+    if (total_out) *total_out = total_bytes;
+    return 0;
 }
 
 int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k) {
@@ -1072,6 +1173,34 @@ int32_t neura_cuda_comm_connect(nc_context *ctx, nc_comm *comm, uint32_t rank, u
     return 0;
 }
 
+int32_t neura_cuda_comm_connect_local(nc_context *ctx, nc_comm *comm, uint32_t rank, uint32_t world, nc_comm *const *all) {
+    if (!ctx || !comm || !all) return refuse(kBadArgument, "connect needs a context, a communicator and the group's communicators");
+    if (world < 2 || world > kMaxRanks || rank >= world)
+        return refuse(kBadArgument, "rank %u of %u is not a place in a group of 2 to %u", rank, world, kMaxRanks);
+    if (comm->connected) return refuse(kBadState, "this communicator is already connected");
+    if (all[rank] != comm) return refuse(kBadArgument, "place %u of the group holds another communicator", rank);
+    NC_CUDA(cudaSetDevice(ctx->device));
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!all[r] || !all[r]->mine) return refuse(kBadArgument, "place %u of the group is empty", r);
+        if (all[r]->slot_bytes != comm->slot_bytes)
+            return refuse(kBadArgument, "the communicators of a group are created for the same count");
+        if (all[r]->device != comm->device) {   // another GPU of this process: its memory has to be reachable from here
+            int reachable = 0;
+            NC_CUDA(cudaDeviceCanAccessPeer(&reachable, comm->device, all[r]->device));
+            if (!reachable) return refuse(kBadState, "device %d cannot reach the memory of device %d", comm->device, all[r]->device);
+            cudaError_t e = cudaDeviceEnablePeerAccess(all[r]->device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return cuda_refuse(e, "cudaDeviceEnablePeerAccess");
+            cudaGetLastError();
+        }
+        comm->peer[r] = all[r]->mine;
+    }
+    comm->world = world;
+    comm->rank = rank;
+    comm->connected = true;
+    comm->local = true;
+    return 0;
+}
+
 int32_t neura_cuda_allreduce(nc_context *ctx, void *stream_, nc_comm *comm, float *inout_dev, uint32_t count) {
     if (!ctx || !comm || !inout_dev || !count) return refuse(kBadArgument, "an all-reduce needs a context, a communicator and numbers");
     if (!comm->connected) return refuse(kBadState, "the communicator is not connected to its peers");
@@ -1090,6 +1219,7 @@ int32_t neura_cuda_allreduce(nc_context *ctx, void *stream_, nc_comm *comm, floa
     p.world = comm->world;
     p.rank = comm->rank;
     p.status = (unsigned int *)ctx->status.ptr;
+    p.wait_nanos = ctx->wait_nanos;
     const unsigned int threads = count / 4 >= 1024 ? 1024 : ((count / 4 + 31) / 32 * 32 < 32 ? 32 : (count / 4 + 31) / 32 * 32);
     NC_CUDA(launch_dependent(allreduce_kernel, dim3(1), dim3(threads), 0, (cudaStream_t)stream_, p));
     ctx->launches++;
@@ -1118,6 +1248,7 @@ int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream_, nc_comm 
     p.world = comm->world;
     p.rank = comm->rank;
     p.status = (unsigned int *)ctx->status.ptr;
+    p.wait_nanos = ctx->wait_nanos;
     NC_CUDA(launch_dependent(allreduce_norm_stage_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream_, p, then));
     ctx->launches++;
     ctx->slots[ctx->cur].rows = rows;
@@ -1129,30 +1260,12 @@ int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream_, nc_comm 
 int32_t neura_cuda_comm_destroy(nc_context *ctx, nc_comm *comm) {
     if (!comm) return 0;
     if (ctx) cudaSetDevice(ctx->device);
-    for (uint32_t r = 0; r < comm->world; ++r)
+    for (uint32_t r = 0; r < comm->world && !comm->local; ++r)
         if (r != comm->rank && comm->peer[r]) cudaIpcCloseMemHandle(comm->peer[r]);
     if (comm->mine) cudaFree(comm->mine);
     delete comm;
     return 0;
 }
-
-// ---------------------------------------------------------------------------------------
-// The product for callers that must not allocate.
-//
-// Everything neura_cuda_linear keeps in scratch that it may have to cudaMalloc (digit
-// planes, digit scales, split-tile partial sums, tile counters, the status word) lives
-// here in one fixed array inside the library image.  Every GPU whose context loads the
-// library carries these 16 MiB until the process exits.
-// ---------------------------------------------------------------------------------------
-constexpr uint64_t kStaticScratchBytes = 16ull << 20;
-constexpr uint32_t kStaticMaxRows = 4;
-constexpr uint32_t kStaticMaxK = 32768;
-constexpr uint32_t kStaticMaxN = 262144;
-static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-
-// `g_static_scratch` names a host-side shadow in host code, not device memory: the device
-// address has to be asked for, once per device, with that device current.
-static unsigned char *g_static_scratch_dev[64] = {nullptr};
 
 int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_dev,
                                  uint32_t rows, uint64_t x_stride, float *out_dev, uint64_t out_stride,
@@ -1173,53 +1286,42 @@ int32_t neura_cuda_linear_static(nc_context *ctx, void *stream_, const nc_weight
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
     if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
-    if (ctx->device < 0 || ctx->device >= 64) return refuse(kBadState, "device %d is outside the table of scratch addresses", ctx->device);
+    if (ctx->device < 0 || ctx->device >= kStaticDevices) return refuse(kBadState, "device %d is outside the table of scratch addresses", ctx->device);
     cudaStream_t stream = (cudaStream_t)stream_;
 
     // one-time set-up per device (the first call on a device; make it before any stream capture)
-    if (!g_static_scratch_dev[ctx->device]) {
-        NC_CUDA(cudaSetDevice(ctx->device));
-        unsigned char *address = nullptr;
-        NC_CUDA(cudaGetSymbolAddress((void **)&address, g_static_scratch));
-        if (!address) return refuse(kBadState, "the static scratch has no address on device %d", ctx->device);
-        g_static_scratch_dev[ctx->device] = address;
-    }
-    unsigned char *base = g_static_scratch_dev[ctx->device];
+    if ((rc = static_setup(ctx->device))) return rc;
+    StaticScratch &fixed = g_static[ctx->device];
+    unsigned char *base = fixed.base;
 
     // carve: [status 256][counters][digit scales][digit planes][partial sums ...]
     const uint32_t ncols = rows * 3;
     const uint64_t kpad = ((uint64_t)w->k + 255) / 256 * 256;
-    const uint64_t counters_bytes = (uint64_t)(kStaticMaxN / kTileRows) * sizeof(unsigned int);
     const uint64_t cs_bytes = (uint64_t)(kStaticMaxK / 32) * kStaticMaxRows * 3 * sizeof(float);
     const uint64_t dig_bytes = (uint64_t)kStaticMaxK * kStaticMaxRows * 3;
     const uint64_t sums_bytes = (uint64_t)(kStaticMaxK / 256) * kStaticMaxRows * 3 * 64;
     unsigned int *status = (unsigned int *)base;
     unsigned int *counters = (unsigned int *)(base + 256);
-    float *cs = (float *)(base + 256 + counters_bytes);
-    uint8_t *dig = base + 256 + counters_bytes + cs_bytes;
-    uint32_t *sums = (uint32_t *)(base + 256 + counters_bytes + cs_bytes + dig_bytes);
-    float *partial = (float *)(base + 256 + counters_bytes + cs_bytes + dig_bytes + sums_bytes);
-    const uint64_t partial_room = kStaticScratchBytes - (256 + counters_bytes + cs_bytes + dig_bytes + sums_bytes);
+    float *cs = (float *)(base + 256 + kStaticCountersBytes);
+    uint8_t *dig = base + 256 + kStaticCountersBytes + cs_bytes;
+    uint32_t *sums = (uint32_t *)(base + 256 + kStaticCountersBytes + cs_bytes + dig_bytes);
+    float *partial = (float *)(base + 256 + kStaticCountersBytes + cs_bytes + dig_bytes + sums_bytes);
+    const uint64_t partial_room = kStaticScratchBytes - (256 + kStaticCountersBytes + cs_bytes + dig_bytes + sums_bytes);
 
     const bool q4k = w->element == NC_ELEMENT_Q4K;
     const int nt = (int)((ncols + 7) / 8);  // 1 or 2 for up to four rows
-    void (*kernel)(GemvParams) = q4k ? (nt == 1 ? gemv_stream_kernel<true, 1, kStages> : gemv_stream_kernel<true, 2, kStages>)
-                                     : (nt == 1 ? gemv_stream_kernel<false, 1, kStages> : gemv_stream_kernel<false, 2, kStages>);
-    const size_t stage = q4k ? kQ4kStage : kQ8Stage;
-    const size_t smem = kGemvWarps * kStages * (stage + 8) + kGemvWarps * 32 * (nt * 8 + 1) * sizeof(float);
-    NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int resident = 0;
-    NC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kGemvWarps * 32, smem));
-    if (resident < 1) return refuse(kBadState, "the product kernel does not fit an SM");
-    const GemvPlan plan = plan_gemv(ctx, w->element, w->n, w->k, resident);
+    const int variant = (q4k ? 2 : 0) + (nt - 1);
+    void (*kernel)(GemvParams) = static_variant(variant);
+    const size_t smem = static_variant_smem(variant);
+    const GemvPlan plan = plan_gemv(ctx, w->element, w->n, w->k, fixed.resident[variant]);
     const uint64_t partial_need = (uint64_t)plan.ntiles * plan.maxp * rows * kTileRows * sizeof(float);
     if (partial_need > partial_room)
         return refuse(kBadArgument, "this product splits into %llu bytes of partial sums and the static scratch holds %llu",
                       (unsigned long long)partial_need, (unsigned long long)partial_room);
 
-    // the array keeps whatever the last call left: the counters and the status word start at zero
-    NC_CUDA(cudaMemsetAsync(base, 0, 256 + counters_bytes, stream));
-
+    // The array keeps what the last call left.  Nothing has to be cleared here: the array loads as zeros, the warp
+    // that finishes a split tile puts the tile's counter back to zero, and the status word stays raised until
+    // neura_cuda_sync has reported it (which then clears the counters a product that gave up may have left).
     PrepParams prep;
     prep.x = x_dev;
     prep.x_stride = x_stride;

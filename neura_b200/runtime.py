@@ -153,6 +153,16 @@ class Runtime:
     def sync(self) -> None:
         _check(self._lib.neura_cuda_sync(self._ctx, self.stream))
 
+    def set_wait_limit(self, nanoseconds: int) -> None:
+        """How long a kernel waits for another party (a peer's flag, the grid barrier) before it gives up."""
+        _check(self._lib.neura_cuda_set_wait_limit(self._ctx, nanoseconds))
+
+    def memory(self) -> tuple:
+        """(free, total) bytes of the GPU."""
+        free, total = ctypes.c_uint64(), ctypes.c_uint64()
+        _check(self._lib.neura_cuda_memory(self._ctx, ctypes.byref(free), ctypes.byref(total)))
+        return free.value, total.value
+
     def reserve(self, rows: int, n: int, k: int) -> None:
         _check(self._lib.neura_cuda_reserve(self._ctx, rows, n, k))
 

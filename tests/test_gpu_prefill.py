@@ -1,4 +1,6 @@
 """The tensor-core prefill product against the CPU oracle (needs a B200)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -11,7 +13,7 @@ pytestmark = pytest.mark.gpu
 REL_TOL = 1e-3
 
 
-def check(runtime, oracle, m, n, k, chain=False, seed=61):
+def check(runtime, oracle, m, n, k, chain=False, seed=61, residual=False):
     w = oracle.Stream(seed).normal(n * k, 0.0, 0.02).reshape(n, k)
     packed = oracle.pack_rows(nb.Q4K, w)
     x = oracle.Stream(seed + 2).normal(m * k).reshape(m, k)
@@ -24,9 +26,14 @@ def check(runtime, oracle, m, n, k, chain=False, seed=61):
         bd = runtime.tensor(n)
         runtime.write(bd, bias)
         steps, ochain = [nb.Step(nb.ADD, bd), nb.Step(nb.SILU)], [(oracle.ADD, bias), (oracle.SILU, None)]
+    if residual:   # an operand read at the output coordinate through a row stride
+        carried = oracle.Stream(seed + 6).normal(m * n).reshape(m, n)
+        rd = runtime.tensor(m, n)
+        runtime.write(rd, carried)
+        steps, ochain = steps + [nb.Step(nb.ADD, rd)], ochain + [(oracle.ADD, carried)]
     runtime.linear_bf16(weight, xd, od, steps)
     got = runtime.read(od)
-    want = oracle.linear(nb.Q4K, packed, n, k, x, chain=ochain, threads=8, bf16=True)
+    want = oracle.linear(nb.Q4K, packed, n, k, x, chain=ochain, threads=os.cpu_count() or 8, bf16=True)
     scale = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
     worst = float(np.abs(got - want).max())
     assert worst <= REL_TOL * scale, f"[{m}x{k}] x [{n}x{k}]: |diff| {worst:.3e} against rms {scale:.3e}"
@@ -40,13 +47,29 @@ def test_prefill_product_matches_the_bf16_oracle(runtime, oracle, m, n, k):
     check(runtime, oracle, m, n, k)
 
 
+@pytest.mark.parametrize("m,n,k", [(257, 300, 512), (512, 512, 512), (600, 300, 512), (700, 300, 512),
+                                   (1024, 512, 256), (600, 512, 3584)])
+def test_prefill_product_over_several_row_tiles(runtime, oracle, m, n, k):
+    # more than 256 rows: the second and later row tiles of the grid, with a ragged last one
+    check(runtime, oracle, m, n, k)
+
+
 def test_prefill_product_applies_the_fused_chain(runtime, oracle):
     check(runtime, oracle, 96, 320, 512, chain=True)
+
+
+def test_prefill_product_applies_a_row_strided_chain_over_several_row_tiles(runtime, oracle):
+    check(runtime, oracle, 520, 300, 512, chain=True, residual=True)
 
 
 def test_prefill_product_at_the_benchmark_depth_on_a_slice_of_its_width(runtime, oracle):
     # config 4 is [2048 x 3584] x [18944 x 3584]; the oracle takes a slice of that in seconds
     check(runtime, oracle, 64, 512, 3584)
+
+
+def test_prefill_product_at_the_benchmark_rows_on_a_slice_of_its_width(runtime, oracle):
+    # all 2048 rows of config 4 (eight row tiles) against one 256-row tile of its weight
+    check(runtime, oracle, 2048, 256, 3584)
 
 
 def test_prefill_refuses_what_it_does_not_multiply(runtime, oracle):

@@ -42,6 +42,24 @@ def test_the_static_scratch_product_matches_the_allocating_one_twice_in_a_row(ru
         assert np.abs(b - reference).max() <= TOLERANCE * scale
 
 
+def test_the_static_scratch_product_allocates_nothing_after_its_first_call(runtime, oracle):
+    n, k, rows = 300, 1024, 2
+    w = oracle.Stream(43).normal(n * k, 0.0, 0.02).reshape(n, k)
+    weights = [runtime.load(element, n, k, oracle.pack_rows(element, w)) for element in (nb.Q4K, nb.Q8_0)]
+    x, out = runtime.tensor(rows, k), runtime.tensor(rows, n)
+    runtime.write(x, oracle.Stream(47).normal(rows * k).reshape(rows, k))
+    runtime.linear_static(weights[0], x, out)   # the set-up call of this device (if no test before made it)
+    runtime.sync()
+    free_before, _ = runtime.memory()
+    for _ in range(3):
+        for weight in weights:                  # both block formats, one and two rows: all four kernel variants
+            runtime.linear_static(weight, x, out)
+            runtime.linear_static(weight, x, out, rows=1)
+    runtime.sync()
+    free_after, _ = runtime.memory()
+    assert free_after == free_before, f"device memory moved by {free_before - free_after} bytes across allocation-free calls"
+
+
 def test_the_static_scratch_product_refuses_what_it_cannot_hold(runtime, oracle):
     n, k = 64, 512
     w = oracle.Stream(5).normal(n * k, 0.0, 0.02).reshape(n, k)

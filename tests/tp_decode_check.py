@@ -63,9 +63,15 @@ def main() -> int:
             print(f"FAIL: sequence {b} leaves the oracle at step {at}: {eager[b, at]} for {want[b, at]} "
                   f"(oracle margin {margins[b, at]:.3e})")
             status = 1
-        if status == 0:
-            print(f"tp{world}: 64 greedy tokens x {batch} sequences match the oracle, eager and recorded "
-                  f"({type(comm).__name__})")
+        verdict = (f"tp{world}: 64 greedy tokens x {batch} sequences match the oracle, eager and recorded "
+                   f"({type(comm).__name__})") if status == 0 else f"tp{world}: FAILED ({type(comm).__name__})"
+        print(verdict)
+        # a record of the run for boxes whose test collection has fewer GPUs than this check wants
+        log = os.environ.get("TP_CHECK_LOG")
+        if log:
+            os.makedirs(os.path.dirname(log) or ".", exist_ok=True)
+            with open(log, "a") as fh:
+                fh.write(verdict + "\n")
     flag = torch.tensor([status], device=device)
     dist.broadcast(flag, 0)
     rt.sync()
