@@ -301,7 +301,7 @@ def run_ours(args):
     kernel_ms = r0.elapsed_time(r1) / (reps * config.layers)
     algorithmic = 2 * nb.payload_bytes(config.element, n * k) + 4 * rows * k + 4 * rows * n
     achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
-    kernel_name = f"gemv_stream_kernel<Q4_K> on the paired gate|up [2x{n}x{k}] at batch {rows}"
+    kernel_name = f"qlinear_stream_kernel<Q4_K> on the paired gate|up [2x{n}x{k}] at batch {rows}"
     product_alone = {"kernel": kernel_name, "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
                      "achieved": achieved, "frac": achieved / peak}
 

@@ -25,7 +25,7 @@
 namespace nc {
 
 #ifndef NC_GEMV_WARPS
-#define NC_GEMV_WARPS 8   // 2, 4, 8, 16 warps a CTA gave 5.99, 5.95, 5.87, 6.08 ms on the 32B decode step
+#define NC_GEMV_WARPS 8   // warps a CTA; two such CTAs share an SM
 #endif
 constexpr int kGemvWarps = NC_GEMV_WARPS;            // warps per CTA (they never synchronise with each other)
 constexpr uint32_t kQ4kStage = 2 * kQ4kUnit;       // one 32-row unit: 4608 B
@@ -441,7 +441,7 @@ struct GemvWarp {
 // HOOKS: the product also applies the rms_norm scalar of its input rows (GemvParams::sumsq, at most two rows) and
 // stages its own output for the next product (GemvParams::then).
 template <bool Q4K, int NT, int STAGES, bool HOOKS = false>
-__global__ void __launch_bounds__(kGemvWarps * 32, NT <= 1 ? 16 / kGemvWarps : 1) gemv_stream_kernel(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(kGemvWarps * 32, NT <= 1 ? 16 / kGemvWarps : 1) qlinear_stream_kernel(const __grid_constant__ GemvParams p) {
     static_assert(STAGES >= 2 && kQ8Group == 4, "the four units of a Q8_0 stage are unrolled by hand");
     constexpr uint32_t kStage = Q4K ? kQ4kStage : kQ8Stage;
     constexpr uint32_t kUnit = Q4K ? kQ4kStage : 2 * kQ8Unit;  // bytes of one 32-row unit

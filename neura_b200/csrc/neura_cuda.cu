@@ -138,9 +138,8 @@ GemvPlan plan_gemv(const nc_context *ctx, uint32_t element, uint32_t n, uint32_t
     plan.ntiles = (n + kTileRows - 1) / kTileRows;
     plan.upt = k / block_elements(element);
     const uint64_t units = (uint64_t)plan.ntiles * plan.upt;  // below 2^32: n and k are 32-bit, units = n*k/8192 at most
-    // 32-row units a warp should at least stream (Q4_K: one; a sweep over 1, 2, 3, 4, 6 on the 32B decode step gave
-    // 6.04, 6.12, 6.42, 6.25, 6.69 ms: the small projections want every warp)
-    // (Q8_0: one stage of four units; 2, 4, 8, 16 gave 823, 890, 826, 668 tok/s on the 0.5B decoder)
+    // 32-row units a warp should at least stream: one Q4_K unit (the small projections want every warp), one
+    // stage of four Q8_0 units
     const uint64_t least = element == NC_ELEMENT_Q4K ? 1 : 4;
     uint64_t warps = (uint64_t)ctx->sms * resident_blocks_per_sm * kGemvWarps;
     if (warps > units / least) warps = units / least;
@@ -176,7 +175,7 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
 
 template <bool Q4K, int NT, bool HOOKS = false>
 int32_t launch_gemv_as(nc_context *ctx, cudaStream_t stream, uint32_t element, GemvParams &p, uint32_t n, uint32_t k) {
-    auto kernel = gemv_stream_kernel<Q4K, NT, kStages, HOOKS>;
+    auto kernel = qlinear_stream_kernel<Q4K, NT, kStages, HOOKS>;
     constexpr size_t stage = Q4K ? kQ4kStage : kQ8Stage;
     constexpr size_t smem = kGemvWarps * kStages * (stage + 8) + kGemvWarps * 32 * (NT * 8 + 1) * sizeof(float);
     static int resident[16] = {0};  // per device, filled on first use
@@ -261,10 +260,10 @@ StaticScratch g_static[kStaticDevices];
 // The four kernels the allocation-free product may launch: Q8_0 / Q4_K, one or two 8-column MMA tiles.
 void (*static_variant(int variant))(GemvParams) {
     switch (variant) {
-    case 0: return gemv_stream_kernel<false, 1, NC_GEMV_STAGES>;
-    case 1: return gemv_stream_kernel<false, 2, NC_GEMV_STAGES>;
-    case 2: return gemv_stream_kernel<true, 1, NC_GEMV_STAGES>;
-    default: return gemv_stream_kernel<true, 2, NC_GEMV_STAGES>;
+    case 0: return qlinear_stream_kernel<false, 1, NC_GEMV_STAGES>;
+    case 1: return qlinear_stream_kernel<false, 2, NC_GEMV_STAGES>;
+    case 2: return qlinear_stream_kernel<true, 1, NC_GEMV_STAGES>;
+    default: return qlinear_stream_kernel<true, 2, NC_GEMV_STAGES>;
     }
 }
 size_t static_variant_smem(int variant) {

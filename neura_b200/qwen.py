@@ -73,63 +73,6 @@ def scaled(config: Config, layers: int, vocab: Optional[int] = None) -> Config:
                   config.rope_base, config.tied_head)
 
 
-class LinearStack:
-    """The projections of a decoder, called in order on one token's activations.
-
-    This is the part of a decode step the quantized-linear path owns: per layer
-    q/k/v (one staging of the normed hidden state), the output projection with
-    the residual add fused, gate and up (one staging; ``silu(gate) * up`` fused
-    into the up product) and down with its residual add, then the head.  What
-    sits between them in a full model (norms, RoPE, attention) is not part of it.
-    """
-
-    def __init__(self, rt: Runtime, config: Config, weights: Dict[str, Weight], rows: int = 1):
-        self.rt, self.config, self.weights, self.rows = rt, config, weights, rows
-        c = config
-        self.hidden = rt.tensor(rows, c.hidden)
-        self.qkv = rt.tensor(rows, c.query_width + 2 * c.key_width)
-        self.attended = rt.tensor(rows, c.query_width)
-        self.gate = rt.tensor(rows, c.feed_forward)
-        self.held = rt.tensor(rows, c.feed_forward)
-        self.logits = rt.tensor(rows, c.vocab)
-        widest_n = max(c.vocab, c.feed_forward)
-        rt.reserve(rows, widest_n, max(c.hidden, c.feed_forward, c.query_width))
-        self.program: Optional[int] = None
-        self.compiled = None   # the step as one persistent kernel (compile())
-        self.fold = False      # True: fold norms and stagings into the products' epilogues (seven launches a layer
-                               # instead of ten; measured slower on the 32B shapes, 7.1 ms against 6.45 ms a token)
-
-    def layer(self, index: int) -> None:
-        rt, c, w = self.rt, self.config, self.weights
-        at = lambda name: w[f"blk.{index}.{name}.weight"]  # noqa: E731
-        rt.stage(self.hidden, c.element)
-        rt.linear_staged(at("attn_qkv"), self.qkv)
-        # stands where attention would: the query third of qkv feeds the output projection
-        rt.stage(self.qkv, c.element, k=c.query_width)
-        rt.linear_staged(at("attn_output"), self.hidden, [Step(ADD, self.hidden)])
-        rt.stage(self.hidden, c.element)
-        rt.linear_staged(at("ffn_gate"), self.gate, [Step(SILU)])
-        rt.linear_staged(at("ffn_up"), self.held, [Step(MUL, self.gate)])
-        rt.stage(self.held, c.element)
-        rt.linear_staged(at("ffn_down"), self.hidden, [Step(ADD, self.hidden)])
-
-    def token(self) -> None:
-        for index in range(self.config.layers):
-            self.layer(index)
-        self.rt.stage(self.hidden, self.config.element)
-        self.rt.linear_staged(self.weights["output.weight"], self.logits)
-
-    def record(self) -> int:
-        """Runtime::compile: one token's launches as a replayable program."""
-        self.rt.capture_begin()
-        self.token()
-        self.program = self.rt.capture_end()
-        return self.program
-
-    def launches_per_token(self) -> int:
-        return self.config.layers * 9 + 2
-
-
 class Decoder:
     """A Qwen2.5-shaped decoder stepping one token per sequence (greedy), on the device.
 
@@ -177,8 +120,7 @@ class Decoder:
         rt.reserve_decoder(batch, self.heads, self.key_heads, c.head_width, capacity)
         self.program: Optional[int] = None
         self.compiled = None   # the step as one persistent kernel (compile())
-        self.fold = False      # True: fold norms and stagings into the products' epilogues (seven launches a layer
-                               # instead of ten; measured slower on the 32B shapes, 7.1 ms against 6.45 ms a token)
+        self.fold = False      # True: fold norms and stagings into the products' epilogues (fewer, longer launches)
         self.scale = 1.0 / float(c.head_width) ** 0.5
 
     def window(self, k: int):
@@ -251,9 +193,8 @@ class Decoder:
             at = lambda name: f"blk.{layer}.{name}.weight"  # noqa: E731
             after = n[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < c.layers else n["output_norm.weight"]
             rt.linear_staged(w[at("attn_qkv")], self.qkv)
-            # (two launches on purpose: as one launch, rope_attend, the step measured 0.3 ms slower on the 32B
-            # shapes; the attention's clusters then start only when the product before them has drained, where
-            # the small RoPE launch gives them time to become resident)
+            # (two launches on purpose: the small RoPE launch gives the attention's clusters time to become resident
+            # while the product before them drains)
             rt.rope_cache(self.qkv, self.position, c.rope_base, self.heads, self.key_heads, c.head_width,
                           self.capacity, self.keys[layer], self.values[layer])
             rt.attend(self.qkv, self.keys[layer], self.values[layer], self.position, self.scale, self.heads,
