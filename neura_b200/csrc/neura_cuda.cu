@@ -18,6 +18,7 @@
 #include "megakernel.cuh"
 #include "prep.cuh"
 #include "quantize.cuh"
+#include "skinny_tcgen05.cuh"
 
 using namespace nc;
 
@@ -55,8 +56,15 @@ int32_t cuda_refuse(cudaError_t e, const char *what) {
 constexpr int32_t kBadArgument = -1;
 constexpr int32_t kBadState = -2;
 constexpr int32_t kDeviceRefusal = -3;
-constexpr uint32_t kMaxRowsPerPass = 16;  // activation rows one staging holds
-constexpr uint32_t kRowsPerLaunch = 8;    // activation rows one product launch carries (three 8-column MMA tiles)
+constexpr uint32_t kMaxRowsPerPass = 16;  // activation rows one staging of digit planes holds
+constexpr uint32_t kRowsPerLaunch = 8;    // activation rows one launch of the streaming product carries (three 8-column MMA tiles)
+// From this many rows on a Q4_K product takes the tensor-core skinny kernel (skinny_tcgen05.cuh), which streams the
+// weight once for up to kSkMaxRows rows: the reference's choice between folded and staged-run tiles by row count
+// (Product::planned, crates/neura-plan/src/product.rs:103-195: folded up to 4 rows of a K-quant, staged runs above).
+#ifndef NC_SKINNY_FROM
+#define NC_SKINNY_FROM 9
+#endif
+constexpr uint32_t kSkinnyFrom = NC_SKINNY_FROM;
 
 struct Region {
     void *ptr = nullptr;
@@ -70,6 +78,8 @@ struct Region {
 struct Staging {
     Region dig, cs, sums, chunks;   // chunks: finished pieces of every 256-column chunk (StageAfter::counters)
     uint32_t rows = 0, k = 0, granule = 0;   // what was last staged here
+    uint32_t halves = 0;            // 1: the rows were staged as half floats for the skinny product (the context's
+                                    //    one set of skinny buffers), not as digit planes
 };
 constexpr uint32_t kStagingSlots = 3;
 
@@ -80,6 +90,8 @@ struct nc_context {
     uint32_t cur = 0;            // the slot neura_cuda_stage writes and the products read (neura_cuda_staging_select)
     Region squares;              // [rows][chunks] sums of squares left by an epilogue that staged with a norm's gain
     Region partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch, x_bf16;
+    Region sk_xh, sk_sx, sk_xs, sk_rs, sk_partial, sk_counters;   // the skinny product's staged activations and split-K scratch
+    uint32_t sk_bpad = 0, sk_sx_cols = 0;
     uint64_t launches = 0;
     unsigned long long wait_nanos = 2000000000ull;   // how long a kernel waits for another party (neura_cuda_set_wait_limit)
     bool capturing = false;
@@ -324,6 +336,186 @@ int32_t check_status(nc_context *ctx) {
     return refuse(kDeviceRefusal, "%s (status %u); its output is not valid", status_sentence(word | fixed), word | fixed);
 }
 
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library links the runtime only.
+typedef CUresult (*tensor_map_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                         const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                         CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int32_t tensor_map_encoder(tensor_map_encode_fn *out) {
+    static tensor_map_encode_fn encode = nullptr;
+    if (!encode) {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        NC_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found));
+        if (!entry || found != cudaDriverEntryPointSuccess) return refuse(kBadState, "the driver does not offer cuTensorMapEncodeTiled");
+        encode = (tensor_map_encode_fn)entry;
+    }
+    *out = encode;
+    return 0;
+}
+
+// A 16-bit [rows][cols] tensor read in boxes of 64 columns x `box_rows` rows, 128-byte swizzled.
+int32_t tensor_map_16bit(CUtensorMap *map, CUtensorMapDataType type, void *base, uint64_t cols, uint64_t rows, uint32_t box_rows) {
+    tensor_map_encode_fn encode;
+    int32_t rc;
+    if ((rc = tensor_map_encoder(&encode))) return rc;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, box_rows}, steps[2] = {1, 1};
+    const CUresult made = encode(map, type, 2, base, dims, strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (made != CUDA_SUCCESS) return refuse(kBadState, "cuTensorMapEncodeTiled refused the activations (%d)", (int)made);
+    return 0;
+}
+
+// ---- the skinny product (skinny_tcgen05.cuh) ---------------------------------------------------------------
+// How many rows one pass of a product carries: up to 16 as digit planes (8 a launch), or, for a Q4_K weight from
+// kSkinnyFrom rows on, up to kSkMaxRows through the skinny kernel, the rows dealt evenly over the passes.
+uint32_t rows_per_pass(uint32_t element, uint32_t rows) {
+    if (element == NC_ELEMENT_Q4K && rows >= kSkinnyFrom) {
+        const uint32_t passes = (rows + kSkMaxRows - 1) / kSkMaxRows;
+        return (rows + passes - 1) / passes;
+    }
+    return rows < kMaxRowsPerPass ? rows : kMaxRowsPerPass;
+}
+
+struct SkinnyPlan {
+    uint32_t tiles32, ntile128, splits, grid;
+};
+
+// Items are (128-row tile, K slice); a CTA per SM walks them.  The K axis is split when that fills the SMs better:
+// the cost of a split is the rounds of items times the super-blocks of an item, a little more for the partial sums.
+SkinnyPlan skinny_plan(const nc_context *ctx, uint32_t n, uint32_t k, bool pair, uint32_t bpad) {
+    SkinnyPlan plan;
+    plan.tiles32 = pair ? (n + 15) / 16 : (n + kTileRows - 1) / kTileRows;
+    plan.ntile128 = (plan.tiles32 + 3) / 4;
+    const uint32_t nsb = k / kSuperBlock, sms = (uint32_t)ctx->sms;
+    double best = 0.0;
+    plan.splits = 1;
+    for (uint32_t s = 1; s <= nsb && s <= 16; ++s) {
+        if (s > 1 && (uint64_t)plan.ntile128 * s * bpad * kSkTileRows * sizeof(float) > (16ull << 20)) break;
+        const uint64_t rounds = ((uint64_t)plan.ntile128 * s + sms - 1) / sms;
+        const double cost = (double)rounds * (double)((nsb + s - 1) / s + (s > 1 ? 1 : 0)) * (1.0 + 0.02 * (s - 1));
+        if (s == 1 || cost < best) {
+            best = cost;
+            plan.splits = s;
+        }
+    }
+    const uint64_t items = (uint64_t)plan.ntile128 * plan.splits;
+    plan.grid = (uint32_t)(items < sms ? items : sms);
+    return plan;
+}
+
+int32_t skinny_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k) {
+    const uint32_t bpad = (std::min(rows, kSkMaxRows) + 7) / 8 * 8;
+    const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256, nsb = kpad / 256, sx_cols = skinny_sx_cols((uint32_t)nsb);
+    int32_t rc;
+    if ((rc = ensure(ctx, ctx->sk_xh, 2ull * kSkMaxRows * kpad * 2, false))) return rc;
+    if ((rc = ensure(ctx, ctx->sk_sx, 2ull * kSkMaxRows * sx_cols * 2, true))) return rc;
+    if ((rc = ensure(ctx, ctx->sk_xs, nsb * kSkMaxRows * sizeof(float), true))) return rc;
+    if ((rc = ensure(ctx, ctx->sk_rs, kSkMaxRows * sizeof(float), true))) return rc;
+    if (n) {
+        uint64_t partial = 0, tiles = 0;
+        for (int pair = 0; pair < 2; ++pair) {
+            const SkinnyPlan plan = skinny_plan(ctx, n, (uint32_t)kpad, pair != 0, bpad);
+            partial = std::max<uint64_t>(partial, plan.splits > 1 ? (uint64_t)plan.ntile128 * plan.splits * bpad * kSkTileRows * sizeof(float) : 0);
+            tiles = std::max<uint64_t>(tiles, plan.ntile128);
+        }
+        if (partial && (rc = ensure(ctx, ctx->sk_partial, partial, false))) return rc;
+        if ((rc = ensure(ctx, ctx->sk_counters, tiles * 4 * sizeof(unsigned int), true))) return rc;
+    }
+    return ensure(ctx, ctx->status, 256, true);
+}
+
+// Stages 9 to 32 rows for the skinny product, optionally rms-normed first.
+int32_t skinny_stage(nc_context *ctx, cudaStream_t stream, const float *x_dev, uint32_t rows, uint64_t x_stride, uint32_t k,
+                     uint32_t lo, uint32_t hi, bool norm, const float *gain, float floor, float *normed, uint64_t normed_stride) {
+    int32_t rc;
+    if ((rc = skinny_reserve(ctx, rows, 0, k))) return rc;
+    SkinnyPrepParams p;
+    memset(&p, 0, sizeof p);
+    p.x = x_dev;
+    p.x_stride = x_stride;
+    p.xh = (__half *)ctx->sk_xh.ptr;
+    p.sx = (__half *)ctx->sk_sx.ptr;
+    p.xs = (float *)ctx->sk_xs.ptr;
+    p.rs = (float *)ctx->sk_rs.ptr;
+    p.rows = rows;
+    p.bpad = (rows + 7) / 8 * 8;
+    p.k = k;
+    p.sx_cols = skinny_sx_cols(k / kSuperBlock);
+    p.lo = lo;
+    p.hi = hi;
+    p.vector = ((uintptr_t)x_dev % 16 == 0 && x_stride % 4 == 0 && lo % 8 == 0) ? 1u : 0u;
+    p.gain = gain;
+    p.norm = norm ? 1u : 0u;
+    p.floor = floor;
+    p.normed = normed;
+    p.normed_stride = normed_stride;
+    NC_CUDA(launch_dependent(skinny_prep_kernel, dim3(rows), dim3(256), 0, stream, p));
+    ctx->launches++;
+    ctx->sk_bpad = p.bpad;
+    ctx->sk_sx_cols = p.sx_cols;
+    Staging &slot = ctx->slots[ctx->cur];
+    slot.rows = rows;
+    slot.k = k;
+    slot.granule = 256;
+    slot.halves = 1;
+    return 0;
+}
+
+int32_t skinny_product(nc_context *ctx, cudaStream_t stream, const nc_weight *w, float *out_dev, uint64_t out_stride,
+                       const nc_step *chain, uint32_t n_steps) {
+    const Staging &slot = ctx->slots[ctx->cur];
+    const bool pair = w->layout == NC_LAYOUT_TILED_PAIR;
+    const uint32_t bpad = ctx->sk_bpad;
+    const SkinnyPlan plan = skinny_plan(ctx, w->n, w->k, pair, bpad);
+    int32_t rc;
+    if (plan.splits > 1 &&
+        (rc = ensure(ctx, ctx->sk_partial, (uint64_t)plan.ntile128 * plan.splits * bpad * kSkTileRows * sizeof(float), false)))
+        return rc;
+    if ((rc = ensure(ctx, ctx->sk_counters, (uint64_t)plan.ntile128 * 4 * sizeof(unsigned int), true))) return rc;
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
+    SkinnyParams p;
+    memset(&p, 0, sizeof p);
+    if ((rc = tensor_map_16bit(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, ctx->sk_xh.ptr, w->k, 2 * bpad, 2 * bpad))) return rc;
+    if ((rc = tensor_map_16bit(&p.sx_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, ctx->sk_sx.ptr, ctx->sk_sx_cols, 2 * bpad, 2 * bpad))) return rc;
+    p.w = (const uint8_t *)w->data_dev;
+    p.xs = (const float *)ctx->sk_xs.ptr;
+    p.rs = (const float *)ctx->sk_rs.ptr;
+    p.out = out_dev;
+    p.out_stride = out_stride;
+    p.partial = (float *)ctx->sk_partial.ptr;
+    p.counters = (unsigned int *)ctx->sk_counters.ptr;
+    p.status = (unsigned int *)ctx->status.ptr;
+    p.n = w->n;
+    p.rows = slot.rows;
+    p.bpad = bpad;
+    p.nsb = w->k / kSuperBlock;
+    p.tiles32 = plan.tiles32;
+    p.ntile128 = plan.ntile128;
+    p.splits = plan.splits;
+    p.pair = pair ? 1u : 0u;
+    p.chain.n = n_steps;
+    for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
+    void (*kernel)(SkinnyParams);
+    switch (bpad / 8) {
+    case 1: kernel = skinny_q4k_tcgen05_kernel<1>; break;
+    case 2: kernel = skinny_q4k_tcgen05_kernel<2>; break;
+    case 3: kernel = skinny_q4k_tcgen05_kernel<3>; break;
+    default: kernel = skinny_q4k_tcgen05_kernel<4>; break;
+    }
+    const uint32_t smem = skinny_smem_bytes(bpad);
+    static bool raised[64][5] = {{false}};
+    if (!raised[ctx->device & 63][bpad / 8]) {
+        NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        raised[ctx->device & 63][bpad / 8] = true;
+    }
+    NC_CUDA(launch_dependent(kernel, dim3(plan.grid), dim3(kSkThreads), smem, stream, p));
+    ctx->launches++;
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -363,7 +555,8 @@ int32_t neura_cuda_close(nc_context *ctx) {
     for (Staging &slot : ctx->slots)
         for (Region *region : {&slot.dig, &slot.cs, &slot.sums, &slot.chunks})
             if (region->ptr) cudaFree(region->ptr);
-    for (Region *region : {&ctx->squares, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16})
+    for (Region *region : {&ctx->squares, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16,
+                           &ctx->sk_xh, &ctx->sk_sx, &ctx->sk_xs, &ctx->sk_rs, &ctx->sk_partial, &ctx->sk_counters})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
     return 0;
@@ -473,6 +666,7 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
     if ((rc = ensure(ctx, ctx->stage_x, (uint64_t)rows * k * sizeof(float), false))) return rc;
     if ((rc = ensure(ctx, ctx->stage_out, (uint64_t)rows * n * sizeof(float), false))) return rc;
+    if (rows >= kSkinnyFrom && k % kSuperBlock == 0 && (rc = skinny_reserve(ctx, rows_per_pass(NC_ELEMENT_Q4K, rows), n, k))) return rc;
     return 0;
 }
 
@@ -574,13 +768,16 @@ int32_t neura_cuda_stage_window(nc_context *ctx, void *stream_, const float *x_d
     const uint32_t per = block_elements(element);
     if (!per || !k || k % per)
         return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
-    if (rows == 0 || rows > kMaxRowsPerPass)
-        return refuse(kBadArgument, "one staging holds 1 to %u rows, not %u", kMaxRowsPerPass, rows);
+    const uint32_t most = element == NC_ELEMENT_Q4K ? kSkMaxRows : kMaxRowsPerPass;
+    if (rows == 0 || rows > most)
+        return refuse(kBadArgument, "one staging holds 1 to %u rows of element %u, not %u", most, element, rows);
     if (lo >= hi || hi > k || lo % 32 || hi % 32)
         return refuse(kBadArgument, "a window [%u, %u) of %u activations starts and ends on multiples of 32 inside them", lo, hi, k);
     if (x_stride < hi - lo)
         return refuse(kBadArgument, "rows of %u activations overlap at stride %llu", hi - lo, (unsigned long long)x_stride);
     if ((uintptr_t)x_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    if (element == NC_ELEMENT_Q4K && (rows >= kSkinnyFrom || rows > kMaxRowsPerPass))
+        return skinny_stage(ctx, (cudaStream_t)stream_, x_dev, rows, x_stride, k, lo, hi, false, nullptr, 0.0f, nullptr, 0);
     const uint64_t kpad = ((uint64_t)k + 255) / 256 * 256;
     const uint32_t ncols = rows * 3;
     int32_t rc;
@@ -607,6 +804,7 @@ int32_t neura_cuda_stage_window(nc_context *ctx, void *stream_, const float *x_d
     ctx->slots[ctx->cur].rows = rows;
     ctx->slots[ctx->cur].k = k;
     ctx->slots[ctx->cur].granule = prep.granule;
+    ctx->slots[ctx->cur].halves = 0;
     return 0;
 }
 
@@ -637,6 +835,7 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
     if ((uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
     cudaStream_t stream = (cudaStream_t)stream_;
+    if (ctx->slots[ctx->cur].halves) return skinny_product(ctx, stream, w, out_dev, out_stride, chain, n_steps);
     // a launch carries at most kRowsPerLaunch rows: beyond that the accumulators of the wider MMA tiles spill
     // and two launches over the same weights are faster than one
     for (uint32_t first = 0; first < ctx->slots[ctx->cur].rows; first += kRowsPerLaunch) {
@@ -691,7 +890,7 @@ int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream_, const nc_w
     if (!from.rows || from.k != w->k || from.granule != granule)
         return refuse(kBadArgument, "the staged activations (%u rows of %u for blocks of %u) do not fit a [%u, %u] weight of element %u",
                       from.rows, from.k, from.granule, w->n, w->k, w->element);
-    if (from.rows > 2) return refuse(kBadArgument, "a product that stages its own output carries 1 or 2 rows, not %u", from.rows);
+    if (from.rows > 2 || from.halves) return refuse(kBadArgument, "a product that stages its own output carries 1 or 2 rows, not %u", from.rows);
     const bool then = then_slot != NC_NO_SLOT;
     if (then && (then_slot >= kStagingSlots || then_slot == ctx->cur))
         return refuse(kBadArgument, "the output is staged into another slot than the one the product reads (0 to %u)", kStagingSlots - 1);
@@ -757,6 +956,7 @@ int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream_, const nc_w
         to.rows = from.rows;
         to.k = w->n;
         to.granule = granule;
+        to.halves = 0;
     }
     return 0;
 }
@@ -770,8 +970,9 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, co
     if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
-    for (uint32_t first = 0; first < rows; first += kMaxRowsPerPass) {
-        const uint32_t pass = rows - first < kMaxRowsPerPass ? rows - first : kMaxRowsPerPass;
+    const uint32_t per = rows_per_pass(w->element, rows);
+    for (uint32_t first = 0; first < rows; first += per) {
+        const uint32_t pass = rows - first < per ? rows - first : per;
         if ((rc = neura_cuda_stage(ctx, stream_, x_dev + (uint64_t)first * x_stride, pass, x_stride, w->k, w->element)))
             return rc;
         nc_step steps[NC_MAX_STEPS];
@@ -817,29 +1018,9 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
         NC_CUDA(cudaFuncSetAttribute(gemm_q4k_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
         raised[ctx->device & 63] = true;
     }
-    // the tensor map of the bf16 activations, encoded by the driver (looked up, so the library links the runtime only)
-    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static encode_fn encode = nullptr;
-    if (!encode) {
-        void *entry = nullptr;
-        cudaDriverEntryPointQueryResult found;
-        NC_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found));
-        if (!entry || found != cudaDriverEntryPointSuccess) return refuse(kBadState, "the driver does not offer cuTensorMapEncodeTiled");
-        encode = (encode_fn)entry;
-    }
     GemmParams p;
     memset(&p, 0, sizeof p);
-    {
-        const cuuint64_t dims[2] = {w->k, rows};
-        const cuuint64_t strides[1] = {(cuuint64_t)w->k * 2};
-        const cuuint32_t box[2] = {kGemmBK, kGemmBM}, steps[2] = {1, 1};
-        const CUresult made = encode(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ctx->x_bf16.ptr, dims, strides, box, steps,
-                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (made != CUDA_SUCCESS) return refuse(kBadState, "cuTensorMapEncodeTiled refused the activations (%d)", (int)made);
-    }
+    if ((rc = tensor_map_16bit(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ctx->x_bf16.ptr, w->k, rows, kGemmBM))) return rc;
     p.w = (const uint8_t *)w->data_dev;
     p.x = (const __nv_bfloat16 *)ctx->x_bf16.ptr;
     p.out = out_dev;
@@ -925,6 +1106,14 @@ extern "C" {
 int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
                                   uint32_t k, const float *weight_dev, float floor, uint32_t element,
                                   float *normed_dev, uint64_t normed_stride) {
+    if (ctx && x_dev && element == NC_ELEMENT_Q4K && rows >= kSkinnyFrom) {   // many rows: staged for the skinny product
+        if (rows > kSkMaxRows) return refuse(kBadArgument, "one staging holds 1 to %u rows, not %u", kSkMaxRows, rows);
+        if (!k || k % kSuperBlock) return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
+        if (x_stride < k || (normed_dev && normed_stride < k))
+            return refuse(kBadArgument, "rows of %u numbers overlap at the strides given", k);
+        if ((uintptr_t)x_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+        return skinny_stage(ctx, (cudaStream_t)stream_, x_dev, rows, x_stride, k, 0, k, true, weight_dev, floor, normed_dev, normed_stride);
+    }
     NormStageParams p;
     int32_t rc;
     if ((rc = norm_stage_params(ctx, x_dev, rows, x_stride, k, weight_dev, floor, element, normed_dev, normed_stride, p)))
@@ -938,6 +1127,7 @@ int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x
     ctx->slots[ctx->cur].rows = rows;
     ctx->slots[ctx->cur].k = k;
     ctx->slots[ctx->cur].granule = p.prep.granule;
+    ctx->slots[ctx->cur].halves = 0;
     return 0;
 }
 
@@ -1253,6 +1443,7 @@ int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream_, nc_comm 
     ctx->slots[ctx->cur].rows = rows;
     ctx->slots[ctx->cur].k = k;
     ctx->slots[ctx->cur].granule = then.prep.granule;
+    ctx->slots[ctx->cur].halves = 0;
     return 0;
 }
 
