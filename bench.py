@@ -9,6 +9,9 @@ streams them from HBM) after a 512-token random prompt.  Prints ONE JSON line.
 With N > 1 (launched under torchrun) the model is split tensor-parallel over the N GPUs: q/k/v, gate, up
 and the head by rows, attention output and down by K with one all-reduce each (the library's own
 one-shot kernel over NVLink peer memory, or NCCL with --comm nccl).
+On one GPU the line also carries `secondary`: the other configurations of the baseline (the Q8_0 product of the
+0.5B MLP, the 7B MLP product at batch 1/4/16/64, the 0.5B decoder, the prefill product, decode at batch 16),
+each timed in the same process with CUDA events.
 """
 from __future__ import annotations
 
@@ -26,18 +29,72 @@ sys.path.insert(0, ROOT)
 
 METRIC = "decode tok/s (Q4_K Qwen-shaped)"
 UNIT = "tok/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent step, from the ncu captures
-# summarised under profiles/ (taken on a cut of few layers and scaled by the weights per step)
-MEGAKERNEL_TRAFFIC = {("qwen2.5-32b-q4_k", 1): 18.10e9}   # profiles/decode_megakernel_qwen32b_q4k_2l.md
+Q8_0, Q4K = 8, 9
+BLOCK = {Q8_0: (32, 34), Q4K: (256, 144)}   # elements and bytes of a block (crates/neura-abi/src/element.rs:33-40,145-178)
+
+# The decoders the baseline's configurations name.  Both arms read the shapes from here; the reference arm
+# imports nothing else of this repository but the oracle.
+WORKLOADS = {
+    "qwen2.5-32b-q4_k": dict(layers=64, hidden=5120, heads=40, key_heads=8, head_width=128, feed_forward=27648,
+                             vocab=152064, element=Q4K, tied_head=False),
+    "qwen2.5-0.5b-q8_0": dict(layers=24, hidden=896, heads=14, key_heads=2, head_width=64, feed_forward=4864,
+                              vocab=151936, element=Q8_0, tied_head=True),
+}
+
+
+def workload_shape(name: str) -> dict:
+    """The shape table of a workload; `NAME-<n>l` is the same decoder cut to n layers."""
+    if name in WORKLOADS:
+        return dict(WORKLOADS[name], name=name)
+    base, _, cut = name.rpartition("-")
+    if base in WORKLOADS and cut.endswith("l") and cut[:-1].isdigit():
+        return dict(WORKLOADS[base], layers=int(cut[:-1]), name=name)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def payload(element: int, elements: int) -> int:
+    per, size = BLOCK[element]
+    return (elements + per - 1) // per * size
+
+
+def layer_products(shape: dict):
+    """(name, n, k) of the seven projections of a layer, in call order (examples/qwen/attention.rs:106-150, mlp.rs:31-34)."""
+    q, kv = shape["heads"] * shape["head_width"], shape["key_heads"] * shape["head_width"]
+    h, ff = shape["hidden"], shape["feed_forward"]
+    return [("attn_q", q, h), ("attn_k", kv, h), ("attn_v", kv, h), ("attn_output", h, q), ("ffn_gate", ff, h),
+            ("ffn_up", ff, h), ("ffn_down", h, ff)]
+
+
+def weight_elements(shape: dict) -> int:
+    return shape["layers"] * sum(n * k for _, n, k in layer_products(shape)) + shape["vocab"] * shape["hidden"]
+
+
+def workload_description(shape: dict, prompt: int, rows: int, parallelism: str) -> dict:
+    """The `config` object of a line: both arms describe the workload the same way."""
+    weights = payload(shape["element"], weight_elements(shape))
+    return {"workload": f"{shape['name']} decode: {shape['layers']} layers, hidden {shape['hidden']}, "
+                        f"{shape['heads']}/{shape['key_heads']} heads x {shape['head_width']}, ff {shape['feed_forward']}, "
+                        f"vocab {shape['vocab']}; {prompt}-token random prompt, greedy",
+            "batch": rows, "parallelism": parallelism,
+            "l2": f"inputs larger than L2 ({weights / 1e9:.2f} GB of weights per step)",
+            "weight_bytes_per_token": weights}
 
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as fh:
-            data = json.load(fh)
-        return float(data["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            return json.load(fh), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def recorded_traffic(key: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised beside this file."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as fh:
+        return json.load(fh).get(key)
 
 
 class ClockSampler:
@@ -94,89 +151,248 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def workload_config(name: str):
-    from neura_b200 import qwen
+# ---- the CPU arm: the oracle's product over one whole layer at its real shapes ----------------------------------
+class CpuLayer:
+    """The seven projections of one layer (and the head) of a workload as packed GGUF blocks in host memory, every
+    matrix at its real shape and with bytes of its own (274 MB a layer for the 32B shapes: nothing stays in the host
+    caches between products), multiplied by the oracle's f32 loop over unpacked blocks on all the host cores.
+    The blocks come from one random slab per K, repeated down the rows: the time of a product does not depend on
+    the values."""
 
-    if name == "qwen2.5-32b-q4_k":
-        return qwen.QWEN25_32B_Q4K
-    if name == "qwen2.5-0.5b-q8_0":
-        return qwen.QWEN25_05B_Q8
-    if name.startswith("qwen2.5-32b-q4_k-"):
-        return qwen.scaled(qwen.QWEN25_32B_Q4K, int(name.rsplit("-", 1)[1].rstrip("l")))
-    raise SystemExit(f"unknown workload {name}")
+    def __init__(self, shape: dict):
+        import numpy as np
+        import oracle
 
+        self.oracle, self.shape, self.element = oracle, shape, shape["element"]
+        self.cores = os.cpu_count() or 1
+        slabs = {}
 
-def workload_description(config, prompt: int, rows: int, parallelism: str) -> dict:
-    """The `config` object of a line: both arms describe the workload the same way."""
-    return {"workload": f"{config.name} decode: {config.layers} layers, hidden {config.hidden}, "
-                        f"{config.heads}/{config.key_heads} heads x {config.head_width}, ff {config.feed_forward}, "
-                        f"vocab {config.vocab}; {prompt}-token random prompt, greedy",
-            "batch": rows, "parallelism": parallelism,
-            "l2": f"inputs larger than L2 ({config.weight_bytes() / 1e9:.2f} GB of weights per step)",
-            "weight_bytes_per_token": config.weight_bytes()}
+        def matrix(n: int, k: int):
+            row_bytes = payload(self.element, k)
+            if k not in slabs:
+                slabs[k] = oracle.pack_rows(self.element, oracle.Stream(23 + k).normal(256 * k, 0.0, 0.02).reshape(256, k))
+            return np.tile(slabs[k][: 256 * row_bytes], (n + 255) // 256)[: n * row_bytes].copy()
 
+        self.layer = [(n, k, matrix(n, k)) for _, n, k in layer_products(shape)]
+        self.head = (shape["vocab"], shape["hidden"], matrix(shape["vocab"], shape["hidden"]))
+        self.x = {k: oracle.Stream(29).normal(k).reshape(1, k) for k in {k for _, k, _ in self.layer} | {shape["hidden"]}}
 
-def cpu_baseline(config, seconds: float = 12.0):
-    """The oracle's product (the reference tests' f32 loop over unpacked blocks) on the host
-    cores, on a bounded sample of the token: rows of the up projection of one layer."""
-    import numpy as np
-    import oracle
-
-    cores = os.cpu_count() or 1
-    k = config.hidden
-    n = min(config.feed_forward, 4096)
-    w = oracle.Stream(23).normal(n * k, 0.0, 0.02).reshape(n, k)
-    packed = oracle.pack_rows(config.element, w)
-    x = oracle.Stream(29).normal(k).reshape(1, k)
-    oracle.linear(config.element, packed, n, k, x, threads=cores)  # warm-up
-    runs, spent = 0, 0.0
-    while spent < seconds and runs < 4096:
+    def run_layer(self) -> float:
         t0 = time.perf_counter()
-        oracle.linear(config.element, packed, n, k, x, threads=cores)
-        spent += time.perf_counter() - t0
-        runs += 1
-    per_weight = spent / runs / (n * k)
-    tok_s = 1.0 / (per_weight * config.weight_elements())
-    return {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{runs} runs of a [{n}x{k}] {('Q4_K' if config.element == 9 else 'Q8_0')} product at batch 1 "
-                      f"({spent:.1f} s), scaled by weights per token ({config.weight_elements()})"}
+        for n, k, packed in self.layer:
+            self.oracle.linear(self.element, packed, n, k, self.x[k], threads=self.cores)
+        return time.perf_counter() - t0
+
+    def run_head(self) -> float:
+        n, k, packed = self.head
+        t0 = time.perf_counter()
+        self.oracle.linear(self.element, packed, n, k, self.x[k], threads=self.cores)
+        return time.perf_counter() - t0
+
+    def token_ms(self, layer_seconds: float, head_seconds: float) -> float:
+        return (self.shape["layers"] * layer_seconds + head_seconds) * 1e3
+
+    def describe(self, passes: int) -> dict:
+        return {"factor": self.shape["layers"],
+                "timed": f"{passes} passes over the seven products of ONE layer at their real shapes and the head once, "
+                         f"batch 1, {self.cores} threads",
+                "token": "layers x (a layer's time) + the head's time; attention, norms and the cache are left out "
+                         "(under 1 % of the weights' bytes)"}
+
+
+def cpu_baseline(shape: dict, seconds: float = 10.0) -> dict:
+    """The in-line CPU figure of our own line: the same code as the reference arm, on a bounded number of passes."""
+    cpu = CpuLayer(shape)
+    cpu.run_layer()
+    head = cpu.run_head()
+    spent, passes = 0.0, 0
+    while spent < seconds and passes < 256:
+        spent += cpu.run_layer()
+        passes += 1
+    ms = cpu.token_ms(spent / passes, head)
+    return {"value": 1e3 / ms, "unit": UNIT, "cores": cpu.cores, "kind": "port", "extrapolated": cpu.describe(passes),
+            "sample": f"{passes} layer passes ({spent:.1f} s) of the oracle's product, scaled by the layer count"}
 
 
 def run_reference(args):
-    """The reference has no CPU (or CUDA) implementation of the product; its only executable
-    statement of it is the f32 loop of its tests, which the oracle restates.  This arm times
-    that on the host cores."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference has no CPU (or CUDA) implementation of the product; its only executable statement of it is the
+    f32 loop of its tests, which the oracle restates.  This arm times that on the host cores: a step is one pass over
+    one whole layer's seven products at their real shapes; a token is `layers` such passes and the head."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    config = workload_config(args.workload)
-    import numpy as np  # noqa: F401
-    import oracle
-
-    cores = os.cpu_count() or 1
-    k, n = config.hidden, min(config.feed_forward, 2048)
-    w = oracle.Stream(23).normal(n * k, 0.0, 0.02).reshape(n, k)
-    packed = oracle.pack_rows(config.element, w)
-    x = oracle.Stream(29).normal(k).reshape(1, k)
-    for _ in range(max(1, args.warmup)):
-        oracle.linear(config.element, packed, n, k, x, threads=cores)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        oracle.linear(config.element, packed, n, k, x, threads=cores)
-    elapsed = time.perf_counter() - t0
-    scale = config.weight_elements() / (n * k)
-    ms_per_step = elapsed / args.steps * scale * 1e3
-    value = 1e3 / ms_per_step
-    sample = (f"each step = a [{n}x{k}] product at batch 1 on {cores} threads, scaled by weights per token "
-              f"(x{scale:.0f})")
+    shape = workload_shape(args.workload)
+    cpu = CpuLayer(shape)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu.run_layer()
+    head = cpu.run_head()
+    steps = max(1, min(args.steps, 64))   # a bounded sample: a pass over a 32B layer takes a tenth of a second
+    spent = sum(cpu.run_layer() for _ in range(steps))
+    ms_per_token = cpu.token_ms(spent / steps, head)
+    value = 1e3 / ms_per_token
+    extrapolated = cpu.describe(steps)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_token, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_description(config, args.prompt, 1, "host cores"),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": workload_description(shape, args.prompt, 1, "host cores"),
+        "extrapolated": extrapolated,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu.cores, "kind": "port", "extrapolated": extrapolated,
+                         "sample": f"{steps} layer passes ({spent:.1f} s) of the oracle's product, scaled by the layer count"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+# ---- our arm -------------------------------------------------------------------------------------------------------
+def qwen_config(shape: dict):
+    from neura_b200 import qwen
+
+    return qwen.Config(shape["name"], shape["layers"], shape["hidden"], shape["heads"], shape["key_heads"], shape["head_width"],
+                       shape["feed_forward"], shape["vocab"], shape["element"], tied_head=shape["tied_head"])
+
+
+def time_products(rt, torch, tstream, weights, rows: int, k: int, n: int, reps: int = 6):
+    """Microseconds per product of `rows` activation rows (staging included) against the sealed weights in turn."""
+    import numpy as np
+
+    x, out = rt.tensor(rows, k), rt.tensor(rows, n)
+    rt.write(x, np.random.default_rng(5).standard_normal((rows, k)).astype(np.float32))
+    rt.reserve(rows, n, k)
+    for w in weights:
+        rt.linear(w, x, out)
+    rt.sync()
+    rt.capture_begin()
+    for w in weights:
+        rt.linear(w, x, out)
+    program = rt.capture_end()
+    for _ in range(3):
+        rt.run(program)
+    rt.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(tstream)
+    for _ in range(reps):
+        rt.run(program)
+    e1.record(tstream)
+    rt.sync()
+    rt.program_free(program)
+    rt.free(x.ptr)
+    rt.free(out.ptr)
+    return e0.elapsed_time(e1) * 1e3 / (reps * len(weights))
+
+
+def sealed_copies(rt, torch, tstream, device, element: int, n: int, k: int, copies: int):
+    import neura_b200 as nb
+
+    made = []
+    with torch.cuda.stream(tstream):
+        numbers = torch.randn(n * k, device=device) * 0.02
+        blocks = torch.empty(nb.payload_bytes(element, n * k) + 16, dtype=torch.uint8, device=device)
+        rt.quantize_device(element, numbers.data_ptr(), n * k, blocks.data_ptr())
+        for _ in range(copies):
+            made.append(rt.seal_device(element, n, k, blocks.data_ptr()))
+    rt.sync()
+    return made
+
+
+def secondary_lines(rt, torch, tstream, device, peaks, main_weights, main_norms, main_config, args):
+    """The baseline's other configurations, each timed here with CUDA events on the launching stream."""
+    import numpy as np
+
+    import neura_b200 as nb
+    from neura_b200 import qwen
+    from neura_b200.synthetic import synthetic_norms, synthetic_weights
+
+    hbm = float(peaks["hbm_gbs"])
+    out = {}
+    # config 1: the Q8_0 product of the 0.5B MLP's up projection, batch 1: cold (64 copies, 296 MB between reuses)
+    # and resident in L2 (one copy)
+    n, k = 4864, 896
+    copies = sealed_copies(rt, torch, tstream, device, nb.Q8_0, n, k, 64)
+    algorithmic = nb.payload_bytes(nb.Q8_0, n * k) + 4 * (k + n)
+    cold = time_products(rt, torch, tstream, copies, 1, k, n)
+    warm = time_products(rt, torch, tstream, copies[:1] * 64, 1, k, n)
+    out["q8_0_gemv_4864x896_b1"] = {"algorithmic_bytes": algorithmic, "cold_us": cold, "cold_gbs": algorithmic / cold / 1e3,
+                                    "cold_frac_of_hbm": algorithmic / cold / 1e3 / hbm, "l2_resident_us": warm,
+                                    "l2_resident_gbs": algorithmic / warm / 1e3, "includes": "activation staging"}
+    for w in copies:
+        rt.free(w.ptr)
+    # config 2: the 7B MLP product, Q4_K [18944 x 3584], batch 1 / 4 / 16 / 64, 32 copies (1.2 GB between reuses)
+    n, k = 18944, 3584
+    copies = sealed_copies(rt, torch, tstream, device, nb.Q4K, n, k, 32)
+    sweep = {}
+    for rows in (1, 4, 16, 64):
+        algorithmic = nb.payload_bytes(nb.Q4K, n * k) + 4 * rows * (k + n)
+        us = time_products(rt, torch, tstream, copies, rows, k, n)
+        sweep[f"b{rows}"] = {"algorithmic_bytes": algorithmic, "us": us, "gbs": algorithmic / us / 1e3,
+                             "frac_of_hbm": algorithmic / us / 1e3 / hbm}
+    out["q4_k_product_18944x3584"] = dict(sweep, includes="activation staging",
+                                          kernels="qlinear_stream_kernel up to 8 rows, skinny_q4k_tcgen05_kernel above")
+    # config 4: the prefill product on the same weights, 2048 rows, bf16 operands
+    m = 2048
+    x, y = rt.tensor(m, k), rt.tensor(m, n)
+    rt.write(x, np.random.default_rng(7).standard_normal((m, k)).astype(np.float32))
+    for _ in range(3):
+        rt.linear_bf16(copies[0], x, y)
+    rt.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(tstream)
+    for index in range(16):
+        rt.linear_bf16(copies[index % len(copies)], x, y)
+    e1.record(tstream)
+    rt.sync()
+    ms = e0.elapsed_time(e1) / 16
+    tflops = 2.0 * m * n * k / ms / 1e9
+    out["q4_k_prefill_2048x18944x3584"] = {"ms": ms, "tflops": tflops,
+                                           "roofline": {"bound": "tensor", "achieved": tflops, "peak": float(peaks["bf16_tflops"]),
+                                                        "unit": "TFLOP/s", "frac": tflops / float(peaks["bf16_tflops"]),
+                                                        "kernel": "gemm_q4k_tcgen05_kernel (+ to_bf16_kernel)"}}
+    rt.free(x.ptr)
+    rt.free(y.ptr)
+    for w in copies:
+        rt.free(w.ptr)
+    # config 5 at batch 16: the same 32B weights, sixteen sequences
+    if main_config.name.startswith("qwen2.5-32b-q4_k"):
+        rows, steps = 16, 20
+        decoder = qwen.Decoder(rt, main_config, main_weights, main_norms, batch=rows, capacity=args.prompt + steps + 16)
+        prompts = np.random.default_rng(31).integers(0, main_config.vocab, (rows, args.prompt), dtype=np.uint32)
+        decoder.reset()
+        decoder.prefill(prompts)
+        decoder.step()
+        rt.sync()
+        decoder.record()
+        for _ in range(3):
+            decoder.run_token()
+        rt.sync()
+        e0.record(tstream)
+        for _ in range(steps):
+            decoder.run_token()
+        e1.record(tstream)
+        rt.sync()
+        ms = e0.elapsed_time(e1) / steps
+        out["decode_batch16"] = {"ms_per_step": ms, "tok_s": rows / ms * 1e3, "launches_per_step": decoder.launches_per_token()}
+    # config 3: the 0.5B decoder, all projections Q8_0, 128-token prompt, 128 tokens
+    shape = workload_shape("qwen2.5-0.5b-q8_0")
+    config = qwen_config(shape)
+    weights = synthetic_weights(rt, config, seed=41)
+    decoder = qwen.Decoder(rt, config, weights, synthetic_norms(rt, config), batch=1, capacity=128 + 128 + 16)
+    prompts = np.random.default_rng(37).integers(0, config.vocab, (1, 128), dtype=np.uint32)
+    decoder.reset()
+    decoder.prefill(prompts)
+    decoder.step()
+    rt.sync()
+    decoder.record()
+    for _ in range(3):
+        decoder.run_token()
+    rt.sync()
+    e0.record(tstream)
+    for _ in range(124):
+        decoder.run_token()
+    e1.record(tstream)
+    rt.sync()
+    ms = e0.elapsed_time(e1) / 124
+    out["decode_qwen2.5-0.5b-q8_0"] = {"ms_per_step": ms, "tok_s": 1e3 / ms,
+                                       "step_gbs": payload(Q8_0, weight_elements(shape)) / ms / 1e6,
+                                       "launches_per_step": decoder.launches_per_token()}
+    return out
 
 
 def run_ours(args):
@@ -200,31 +416,44 @@ def run_ours(args):
     from neura_b200 import qwen
     from neura_b200.synthetic import synthetic_norms, synthetic_weights
 
-    config = workload_config(args.workload)
+    shape = workload_shape(args.workload)
+    config = qwen_config(shape)
     rows = args.batch
     warmup = max(3, args.warmup)
     capacity = args.prompt + 2 * (warmup + args.steps) + 8
+    device = torch.device("cuda", local)
     rt = nb.Runtime(local)
     rt.use_stream(rt.new_stream())
-    tstream = torch.cuda.ExternalStream(rt.stream.value, device=torch.device("cuda", local))
+    tstream = torch.cuda.ExternalStream(rt.stream.value, device=device)
     shard = comm = None
+    if world == 1 and args.rank_of:   # a diagnostic: one rank's share of an N-way split, timed alone without exchanges
+        from neura_b200 import parallel
+
+        shard = parallel.Shard(config, args.rank_of, 0)
+        comm = parallel.NullComm(args.rank_of, 0)
     if world > 1:  # tensor parallel: one model split over the ranks
         from neura_b200 import parallel
 
         shard = parallel.Shard(config, world, rank)
         if args.comm == "peer":   # the library's one-shot all-reduce over NVLink peer memory
-            comm = parallel.PeerComm(rt, world, rank, rows * config.hidden, device=torch.device("cuda", local), stream=tstream)
+            comm = parallel.PeerComm(rt, world, rank, rows * config.hidden, device=device, stream=tstream)
         else:
-            comm = parallel.TorchComm(world, rank, device=torch.device("cuda", local), stream=tstream)
+            comm = parallel.TorchComm(world, rank, device=device, stream=tstream)
     weights = synthetic_weights(rt, config, seed=23 + rank, shard=shard)
     norms = synthetic_norms(rt, config)
     decoder = qwen.Decoder(rt, config, weights, norms, batch=rows, capacity=capacity, shard=shard, comm=comm)
+    decoder.fold = args.fold == "on"
 
-    # the prompt: random token ids, fed one position at a time through the decode step
+    # the prompt: random token ids; in chunks where the decoder fills in chunks, else one position at a time
     prompts = np.random.default_rng(29).integers(0, config.vocab, (rows, args.prompt), dtype=np.uint32)
     decoder.reset()
-    rt.write(decoder.tokens, prompts[:, 0].copy())
-    persistent = world == 1 and rows <= 2 and args.step == "persistent"
+    persistent = world == 1 and rows <= 2 and args.step == "persistent" and shard is None
+    if decoder.chunks:
+        decoder.prefill(prompts)
+        fed = args.prompt - 1
+    else:
+        rt.write(decoder.tokens, prompts[:, 0].copy())
+        fed = 0
     if persistent:          # the whole step as one cooperative kernel
         decoder.compile()
         decoder.run_token()
@@ -234,7 +463,7 @@ def run_ours(args):
         rt.sync()
         decoder.record()
     launches_per_token = decoder.launches_per_token()
-    for at in range(1, args.prompt):
+    for at in range(fed + 1, args.prompt):
         rt.write(decoder.tokens, prompts[:, at].copy())
         decoder.run_token()
     rt.sync()
@@ -281,9 +510,11 @@ def run_ours(args):
     barrier()
     e2e_ms = t_start.elapsed_time(t_stop)
 
-    # ---- roofline of the dominant kernel (the Q4_K product), timed on its own ----------
-    peak, peak_kind = measured_peaks()
+    # ---- roofline of the dominant kernel (the streaming product on the paired gate|up), timed on its own ----------
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks["hbm_gbs"])
     name, n, k = "ffn_gate_up", decoder.feed_forward, config.hidden   # gate and up as one paired product
+    rt.staging_select(0)
     rt.stage(decoder.hidden, config.element)
     reps = 4
     r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -301,13 +532,12 @@ def run_ours(args):
     kernel_ms = r0.elapsed_time(r1) / (reps * config.layers)
     algorithmic = 2 * nb.payload_bytes(config.element, n * k) + 4 * rows * k + 4 * rows * n
     achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
-    kernel_name = f"qlinear_stream_kernel<Q4_K> on the paired gate|up [2x{n}x{k}] at batch {rows}"
+    tag = "Q4_K" if config.element == nb.Q4K else "Q8_0"
+    kernel_key = f"qlinear_stream_kernel<{tag}> gate|up [2x{n}x{k}] b{rows}"
+    kernel_name = f"qlinear_stream_kernel<{tag}> on the paired gate|up [2x{n}x{k}] at batch {rows}"
     product_alone = {"kernel": kernel_name, "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms,
                      "achieved": achieved, "frac": achieved / peak}
-
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel from the ncu capture
-    # summarised in profiles/decode_step_qwen32b_q4k_kernels.md (the full-size shape, batch 1, one GPU)
-    traffic = 163.4e6 if (config.name.startswith("qwen2.5-32b-q4_k") and rows == 1 and world == 1) else None
+    traffic = recorded_traffic(kernel_key) if world == 1 and shard is None else None
     if persistent:
         # the step is one kernel: its algorithmic bytes are those of all its products,
         # payload_bytes(N*K) + 4*B*K + 4*B*N each (the KV cache it also reads is left out)
@@ -315,10 +545,12 @@ def run_ours(args):
         algorithmic = sum(nb.payload_bytes(config.element, nn * kk) + 4 * rows * (nn + kk) for nn, kk in shapes)
         kernel_ms = ms / args.steps
         achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
-        kernel_name = (f"decode_megakernel<{'Q4_K' if config.element == nb.Q4K else 'Q8_0'}>: the whole step "
-                       f"({config.layers} layers + head) as one cooperative launch at batch {rows}")
-        traffic = MEGAKERNEL_TRAFFIC.get((config.name, rows))
-    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=torch.device("cuda", local))
+        kernel_name = f"decode_megakernel<{tag}>: the whole step ({config.layers} layers + head) as one cooperative launch at batch {rows}"
+        traffic = recorded_traffic(f"decode_megakernel<{tag}> {config.name} b{rows}")
+    secondary = None
+    if world == 1 and shard is None and not persistent and not args.no_secondary and rows == 1:
+        secondary = secondary_lines(rt, torch, tstream, device, peaks, weights, norms, config, args)
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(times[0]), float(times[1])
@@ -328,22 +560,27 @@ def run_ours(args):
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_description(config, args.prompt, rows,
+            "config": workload_description(shape, args.prompt, rows,
                                            f"tp{world} ({args.comm} all-reduce)" if world > 1 else "single GPU"),
             "clocks": clock_summary,
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                         "frac": achieved / peak, "traffic": traffic,
+                         "traffic_source": "an ncu capture of this kernel, recorded in profiles/traffic.json (not measured live)"
+                                           if traffic else None,
+                         "peak_kind": peak_kind,
                          "kernel": kernel_name,
                          "algorithmic_bytes": algorithmic, "kernel_ms": kernel_ms, "product_alone": product_alone,
                          "step_gbs_per_gpu": (shard.local_bytes_per_token() if shard else config.weight_bytes())
                                              / (ms / args.steps * 1e-3) / 1e9,
                          "launches_per_token": launches_per_token},
         }
+        if secondary is not None:
+            line["secondary"] = secondary
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(config)
+            line["cpu_baseline"] = cpu_baseline(shape)
         print(json.dumps(line))
     if dist is not None:
         # (no destroy_process_group: with NCCL kernels held in a recorded program it was seen to wait forever)
@@ -354,8 +591,8 @@ def run_ours(args):
 
 
 def run_prefill(args):
-    """A secondary line: the tensor-core prefill product (Q4_K, bf16 operands, f32 accumulate) on one GPU,
-    ``--workload prefill-MxNxK`` (the reference's prefill shape is 2048x18944x3584).  Device timing only."""
+    """A line of its own for the tensor-core prefill product (Q4_K, bf16 operands, f32 accumulate) on one GPU,
+    ``--workload prefill-MxNxK`` (the baseline's prefill shape is 2048x18944x3584).  Device timing only."""
     import torch
 
     import neura_b200 as nb
@@ -391,12 +628,8 @@ def run_prefill(args):
         time.sleep(0.15)
     ms = start.elapsed_time(stop) / args.steps
     flops = 2.0 * m * n * k
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    peaks = {}
-    if os.path.exists(path):
-        with open(path) as fh:
-            peaks = json.load(fh)
-    peak = float(peaks.get("bf16_tflops", 1590.0))
+    peaks, kind = measured_peaks()
+    peak = float(peaks["bf16_tflops"])
     print(json.dumps({
         "metric": "prefill TFLOP/s (Q4_K weights dequantised to bf16 tiles, tcgen05)", "value": flops / ms / 1e9,
         "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
@@ -406,7 +639,7 @@ def run_prefill(args):
         "clocks": clocks.summary(), "gpu_launches": int(rt.launches - launches0),
         "roofline": {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": peak, "unit": "TFLOP/s",
                      "frac": flops / ms / 1e9 / peak, "traffic": None,
-                     "peak_kind": "measured burst" if peaks else "fallback",
+                     "peak_kind": "measured burst" if kind == "measured" else "fallback",
                      "kernel": "gemm_q4k_tcgen05_kernel (+ to_bf16_kernel)"},
     }))
     rt.close()
@@ -423,6 +656,12 @@ def main():
     parser.add_argument("--prompt", type=int, default=512)
     parser.add_argument("--comm", default="peer", choices=["peer", "nccl"])
     parser.add_argument("--no-cpu", action="store_true")
+    parser.add_argument("--no-secondary", action="store_true", help="skip the other configurations of the baseline")
+    parser.add_argument("--fold", default="off", choices=["on", "off"],
+                        help="fold norms, stagings and (tensor parallel) exchanges into the products' epilogues: fewer, "
+                             "longer launches (measured slower at every split, so off)")
+    parser.add_argument("--rank-of", type=int, default=0,
+                        help="diagnostic, one GPU: time rank 0's share of a split over this many ranks, no exchanges")
     parser.add_argument("--step", default="graph", choices=["graph", "persistent"],
                         help="a recorded graph of one kernel per operation (the faster of the two as measured), or one "
                              "cooperative kernel per token (one GPU, batch <= 2)")

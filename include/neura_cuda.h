@@ -227,6 +227,20 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream, const float *q_dev, uin
                           uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
                           uint64_t out_stride);
 
+/* The same two steps for a chunk of a prompt (Batch::prefill and its fill programs,
+ * crates/neura-generate/src/batch.rs:1595-1599, :298-325; examples/qwen/main.rs:21 fills in chunks of 32 and 8): the
+ * `rows` rows are consecutive tokens of ONE sequence, row i at position_dev[i]; keys_dev / values_dev point at that
+ * sequence's cache [key_heads][capacity][width].  neura_cuda_rope_cache_rows writes all the rows' keys and values;
+ * neura_cuda_attend_rows then lets row i attend to slots 0..position_dev[i], the rows before it in the chunk included. */
+int32_t neura_cuda_rope_cache_rows(nc_context *ctx, void *stream, float *qkv_dev, uint64_t row_stride,
+                                   const uint32_t *position_dev, float base, uint32_t rows, uint32_t heads,
+                                   uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
+                                   float *values_dev);
+int32_t neura_cuda_attend_rows(nc_context *ctx, void *stream, const float *q_dev, uint64_t q_stride, const float *keys_dev,
+                               const float *values_dev, const uint32_t *position_dev, float scale, uint32_t rows,
+                               uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
+                               uint64_t out_stride);
+
 /* Sampling::Greedy -> graph.argmax (crates/neura-generate/src/sampling.rs:79-81,
  * crates/neura-kernel/src/task/choice.rs:46-52): the lowest index wins a tie. */
 int32_t neura_cuda_argmax(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint32_t width,
@@ -328,6 +342,28 @@ int32_t neura_cuda_staging_select(nc_context *ctx, uint32_t slot);
 int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev, uint64_t out_stride,
                                       const nc_step *chain, uint32_t n_steps, uint32_t normed, float floor,
                                       uint32_t then_slot, const float *then_gain_dev, uint32_t then_squares);
+
+/* neura_cuda_linear_staged_then for a rank of a tensor-parallel group (no counterpart in the reference, which runs on
+ * one device).  Two additions:
+ *  - `then` says where the output rows sit on the K axis of the product that will read them: elements [lo, hi) of
+ *    an axis of `k` (a row-parallel weight keeps the whole blocks that cover its share of K, neura_cuda_stage_window);
+ *    k = 0 means the rows as they are;
+ *  - `reduce`, when not NULL, says that the rows this rank computes are partial sums over its share of K: the warp
+ *    that completes a 256-column chunk pushes it to every peer (plain peer stores over NVLink), waits (bounded by the
+ *    context's wait limit) for the peers' chunks and adds them up in rank order, so that `out_dev` ends up holding the
+ *    sums on every rank, bit for bit the same, and it is the sums that get staged.  One launch where a row-parallel
+ *    projection had three (product, all-reduce, staging).  Rows of a multiple of 256 numbers; every rank issues the
+ *    same calls in the same order; a chunk whose wait runs out raises the status word (neura_cuda_sync reports it)
+ *    and leaves the call incomplete, after which the group makes a new communicator. */
+typedef struct nc_then {
+    uint32_t slot;            /* the staging slot the output rows go to; NC_NO_SLOT stages nothing */
+    uint32_t k, lo, hi;       /* the rows are elements [lo, hi) of a K axis of k; k = 0: the rows as they are */
+    const float *gain_dev;    /* a coming rms_norm's weight [hi - lo], or NULL */
+    uint32_t squares;         /* 1: leave the chunks' sums of squares with the context */
+} nc_then;
+int32_t neura_cuda_linear_staged_fused(nc_context *ctx, void *stream, const nc_weight *w, float *out_dev, uint64_t out_stride,
+                                       const nc_step *chain, uint32_t n_steps, uint32_t normed, float floor, nc_comm *reduce,
+                                       const nc_then *then);
 
 /* The same product called the way Runtime::{write, run, read} are (runtime.rs:1020,833,1064):
  * activations come from and results return to host memory; blocks until done. */

@@ -23,6 +23,7 @@ SYMBOLS = [
     "neura_cuda_comm_connect", "neura_cuda_comm_destroy", "neura_cuda_allreduce", "neura_cuda_reserve_decoder",
     "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free", "neura_cuda_decoder_trace", "neura_cuda_rope_attend", "neura_cuda_rope_table", "neura_cuda_allreduce_norm_stage", "neura_cuda_staging_select",
     "neura_cuda_linear_staged_then", "neura_cuda_set_wait_limit", "neura_cuda_memory", "neura_cuda_comm_connect_local",
+    "neura_cuda_linear_staged_fused", "neura_cuda_rope_cache_rows", "neura_cuda_attend_rows",
 ]
 
 
@@ -43,6 +44,13 @@ class NcStep(ctypes.Structure):
         ("operand_dev", ctypes.c_void_p),
         ("row_stride", ctypes.c_int64),
         ("col_stride", ctypes.c_int64),
+    ]
+
+
+class NcThen(ctypes.Structure):
+    _fields_ = [
+        ("slot", ctypes.c_uint32), ("k", ctypes.c_uint32), ("lo", ctypes.c_uint32), ("hi", ctypes.c_uint32),
+        ("gain_dev", ctypes.c_void_p), ("squares", ctypes.c_uint32),
     ]
 
 
@@ -118,6 +126,8 @@ def load() -> ctypes.CDLL:
         "neura_cuda_rms_norm_stage": (i32, [p, p, p, u32, u64, u32, p, ctypes.c_float, u32, p, u64]),
         "neura_cuda_rope_cache": (i32, [p, p, p, u64, p, ctypes.c_float, u32, u32, u32, u32, u32, p, p]),
         "neura_cuda_attend": (i32, [p, p, p, u64, p, p, p, ctypes.c_float, u32, u32, u32, u32, u32, p, u64]),
+        "neura_cuda_rope_cache_rows": (i32, [p, p, p, u64, p, ctypes.c_float, u32, u32, u32, u32, u32, p, p]),
+        "neura_cuda_attend_rows": (i32, [p, p, p, u64, p, p, p, ctypes.c_float, u32, u32, u32, u32, u32, p, u64]),
         "neura_cuda_rope_attend": (i32, [p, p, p, u64, p, p, ctypes.c_float, u32, u32, u32, u32, u32, p, p, p, u64]),
         "neura_cuda_rope_table": (i32, [p, p, p, ctypes.c_float, u32, u32, p]),
         "neura_cuda_allreduce_norm_stage": (i32, [p, p, p, p, u32, u32, p, ctypes.c_float, u32]),
@@ -136,6 +146,8 @@ def load() -> ctypes.CDLL:
         "neura_cuda_comm_destroy": (i32, [p, p]),
         "neura_cuda_allreduce": (i32, [p, p, p, p, u32]),
         "neura_cuda_set_wait_limit": (i32, [p, u64]),
+        "neura_cuda_linear_staged_fused": (i32, [p, p, ctypes.POINTER(NcWeight), p, u64, ctypes.POINTER(NcStep), u32, u32,
+                                              ctypes.c_float, p, ctypes.POINTER(NcThen)]),
         "neura_cuda_memory": (i32, [p, ctypes.POINTER(u64), ctypes.POINTER(u64)]),
         "neura_cuda_comm_connect_local": (i32, [p, p, u32, u32, pp]),
         "neura_cuda_stage_window": (i32, [p, p, p, u32, u64, u32, u32, u32, u32]),

@@ -13,41 +13,22 @@
 // completes once the missing peer has published it.
 #pragma once
 #include "common.cuh"
+#include "exchange.cuh"
 #include "gemv_mma.cuh"
 #include "prep.cuh"
 
 namespace nc {
-
-constexpr uint32_t kMaxRanks = 8;
-constexpr uint32_t kCommHeaderBytes = 256;   // [0] call counter, [64 + 4 r] flag of sender r
 
 struct AllreduceParams {
     unsigned char *mine;                 // this rank's communication buffer
     unsigned char *peer[kMaxRanks];      // every rank's buffer as mapped here (peer[rank] == mine)
     float *inout;                        // [count]
     uint64_t slot_bytes;                 // bytes of one sender's seat; a slot is world seats
+    uint32_t header_bytes;               // where the seats start in a buffer
     uint32_t count, world, rank;
     unsigned int *status;
     unsigned long long wait_nanos;       // how long a rank waits for its peers' flags before it gives up
 };
-
-__device__ __forceinline__ unsigned int load_acquire_sys(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void store_release_sys(unsigned int *p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float4 load_peer16(const float *p) {
-    float4 v;
-    asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-    return v;
-}
-
-__device__ __forceinline__ void store_peer16(float *p, float4 v) {
-    asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
-}
 
 // One CTA; count is a multiple of 4.  Returns false when the wait for the peers ran out.
 __device__ __forceinline__ bool allreduce_body(const AllreduceParams &p) {
@@ -62,13 +43,13 @@ __device__ __forceinline__ bool allreduce_body(const AllreduceParams &p) {
 #pragma unroll
         for (uint32_t r = 0; r < kMaxRanks; ++r)
             if (r < p.world)
-                store_peer16(reinterpret_cast<float *>(p.peer[r] + kCommHeaderBytes + slot + p.rank * p.slot_bytes) + i, v);
+                store_peer16(reinterpret_cast<float *>(p.peer[r] + p.header_bytes + slot + p.rank * p.slot_bytes) + i, v);
     }
     __syncthreads();   // orders every thread's stores before the fences below
     if (threadIdx.x < p.world) {
         __threadfence_system();
-        store_release_sys(reinterpret_cast<unsigned int *>(p.peer[threadIdx.x] + 64) + p.rank, seq);
-        const unsigned int *flag = reinterpret_cast<const unsigned int *>(p.mine + 64) + threadIdx.x;
+        store_release_sys(reinterpret_cast<unsigned int *>(p.peer[threadIdx.x] + kCommFlagsAt) + p.rank, seq);
+        const unsigned int *flag = reinterpret_cast<const unsigned int *>(p.mine + kCommFlagsAt) + threadIdx.x;
         const unsigned long long start = global_nanos();
         // (flags only grow; a peer may already be one call ahead)
         while ((int)(load_acquire_sys(flag) - seq) < 0) {
@@ -85,7 +66,7 @@ __device__ __forceinline__ bool allreduce_body(const AllreduceParams &p) {
 #pragma unroll
         for (uint32_t r = 0; r < kMaxRanks; ++r)
             if (r < p.world)
-                part[r] = load_peer16(reinterpret_cast<const float *>(p.mine + kCommHeaderBytes + slot + r * p.slot_bytes) + i);
+                part[r] = load_peer16(reinterpret_cast<const float *>(p.mine + p.header_bytes + slot + r * p.slot_bytes) + i);
         float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (uint32_t r = 0; r < kMaxRanks; ++r) {

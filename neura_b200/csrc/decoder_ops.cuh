@@ -19,6 +19,7 @@ struct RopeCacheParams {
     float *keys, *values;     // [batch][key_heads][capacity][width]
     float base;
     uint32_t batch, heads, key_heads, width, capacity;
+    uint32_t shared;          // 1: every row belongs to ONE sequence, whose cache starts at keys / values (a prompt chunk)
 };
 
 // Half-rotation of one channel pair by (cosine, sine), every rounding pinned so that all callers agree bit for bit.
@@ -73,14 +74,14 @@ __global__ void rope_cache_kernel(const __grid_constant__ RopeCacheParams p) {
             v[channel + half] = new_high;
             if (head >= p.heads && position < p.capacity) {
                 const uint32_t kh = head - p.heads;
-                float *slot = p.keys + (((uint64_t)b * p.key_heads + kh) * p.capacity + position) * p.width;
+                float *slot = p.keys + (((uint64_t)(p.shared ? 0 : b) * p.key_heads + kh) * p.capacity + position) * p.width;
                 slot[channel] = new_low;
                 slot[channel + half] = new_high;
             }
         } else if (position < p.capacity) {
             const uint32_t c = at - turned, kh = c / p.width, d = c % p.width;
             const float value = row[(uint64_t)(p.heads + p.key_heads) * p.width + c];
-            p.values[(((uint64_t)b * p.key_heads + kh) * p.capacity + position) * p.width + d] = value;
+            p.values[(((uint64_t)(p.shared ? 0 : b) * p.key_heads + kh) * p.capacity + position) * p.width + d] = value;
         }
     }
 }
@@ -118,6 +119,7 @@ struct AttendParams {
     // key and puts it and the new value into its tile and into the cache (`fresh` = the cache, writable)
     float *fresh_keys, *fresh_values;
     const float2 *rope_table;   // [batch][width / 2] (cosine, sine) of each sequence's position (rope_table_kernel)
+    uint32_t shared;            // 1: every row belongs to ONE sequence, whose cache starts at keys / values (a prompt chunk)
 };
 
 __device__ __forceinline__ void copy16_async(void *dst_shared, const void *src_global) {
@@ -154,8 +156,9 @@ __global__ void __launch_bounds__(kAttendThreads) attend_kernel(const __grid_con
     const uint32_t chunk = min((count + p.splits - 1) / p.splits, TILE);
     // (the host sizes `splits` so that capacity / splits <= TILE)
     const uint32_t first = min(split * chunk, count), last = min(first + chunk, count), held = last - first;
-    const float *k = p.keys + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
-    const float *v = p.values + (((uint64_t)b * p.key_heads + kh) * p.capacity + first) * WIDTH;
+    const uint32_t sequence = p.shared ? 0u : b;
+    const float *k = p.keys + (((uint64_t)sequence * p.key_heads + kh) * p.capacity + first) * WIDTH;
+    const float *v = p.values + (((uint64_t)sequence * p.key_heads + kh) * p.capacity + first) * WIDTH;
     const uint32_t position = p.position[b];
     constexpr bool turning = TURNING;   // (the plain instantiation carries none of the folded-in RoPE)
     const bool fresh = turning && position < p.capacity && position >= first && position < last;  // the new row is ours
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(kAttendThreads) attend_kernel(const __grid_con
         if (fresh) {
             const float *nk = row_qkv + (uint64_t)(p.heads + kh) * WIDTH;
             const float *nv = row_qkv + (uint64_t)(p.heads + p.key_heads + kh) * WIDTH;
-            const uint64_t slot = (((uint64_t)b * p.key_heads + kh) * p.capacity + position) * WIDTH;
+            const uint64_t slot = (((uint64_t)sequence * p.key_heads + kh) * p.capacity + position) * WIDTH;
             for (uint32_t i = blockDim.x - 1 - threadIdx.x; i < HALF; i += blockDim.x) {   // (the threads the queries use least)
                 const float2 turn = p.rope_table[b * HALF + i];
                 const float2 turned = rope_turn(nk[i], nk[i + HALF], turn.x, turn.y);

@@ -72,6 +72,12 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, ui
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One lane of a converged warp.
+__device__ __forceinline__ bool elect_one_lane() {
+    uint32_t chosen;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(chosen));
+    return chosen != 0;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -199,7 +205,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
     const uint32_t full = bars, empty = bars + 8 * kGemmStages, accum = bars + 16 * kGemmStages;
     const uint32_t slot = accum + 8;
     __shared__ uint32_t failed;
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     const uint32_t m0 = blockIdx.y * kGemmBM, n0 = blockIdx.x * kGemmBN;
     const uint32_t ksteps = p.k / kGemmBK;
     constexpr uint32_t kMmaWarp = kGemmProducers / 32;
@@ -293,8 +299,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
         } else {
             failed = 1;
         }
-    } else if (lane == 0) {
+    } else {
         // ---------------- MMA issue ----------------
+        // The whole warp walks the loop and one elected lane issues: the loop state is then the same in every lane
+        // and the compiler keeps the descriptors in uniform registers.  (Inside an `if (lane == 0)` branch every
+        // MMA paid about 65 ns for moving them there, as much as the MMA itself takes.)
         const uint32_t idesc = instruction_descriptor(128, kGemmBN);
         bool alive = true;
         for (uint32_t it = 0; it < ksteps; ++it) {
@@ -304,15 +313,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
             const uint32_t a_tile = base + s * kGemmStageBytes;
             const uint64_t desc_a0 = smem_descriptor(a_tile), desc_a1 = smem_descriptor(a_tile + kGemmABytes / 2);
             const uint64_t desc_b = smem_descriptor(a_tile + kGemmABytes);
+            if (elect_one_lane()) {
 #pragma unroll
-            for (uint32_t kk = 0; kk < kGemmBK / 16; ++kk) {   // 16 bf16 = 32 bytes further along K inside the swizzle atom
-                tc_mma_bf16(tmem, desc_a0 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
-                tc_mma_bf16(tmem + kGemmBN, desc_a1 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
+                for (uint32_t kk = 0; kk < kGemmBK / 16; ++kk) {   // 16 bf16 = 32 bytes further along K inside the swizzle atom
+                    tc_mma_bf16(tmem, desc_a0 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
+                    tc_mma_bf16(tmem + kGemmBN, desc_a1 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
+                }
+                tc_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
             }
-            tc_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
+            __syncwarp();
         }
-        if (alive) tc_commit(accum);
-        else failed = 1;
+        if (alive) {
+            if (elect_one_lane()) tc_commit(accum);
+            __syncwarp();
+        } else {
+            failed = 1;
+        }
     }
     tc_fence_before();
     __syncthreads();

@@ -104,6 +104,8 @@ struct nc_comm {
     unsigned char *mine = nullptr;
     unsigned char *peer[kMaxRanks] = {nullptr};
     uint64_t slot_bytes = 0, max_count = 0;
+    uint32_t header_bytes = 0, chunks_most = 0;
+    ExchangeView *view_dev = nullptr;   // what a product that exchanges in its own epilogue reads (filled on connect)
     uint32_t world = 0, rank = 0;
     bool connected = false;
     bool local = false;   // the peers are communicators of this process (plain pointers, nothing to unmap)
@@ -875,9 +877,9 @@ int32_t neura_cuda_staging_select(nc_context *ctx, uint32_t slot) {
     return 0;
 }
 
-int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream_, const nc_weight *w, float *out_dev, uint64_t out_stride,
-                                      const nc_step *chain, uint32_t n_steps, uint32_t normed, float floor,
-                                      uint32_t then_slot, const float *then_gain_dev, uint32_t then_squares) {
+int32_t neura_cuda_linear_staged_fused(nc_context *ctx, void *stream_, const nc_weight *w, float *out_dev, uint64_t out_stride,
+                                       const nc_step *chain, uint32_t n_steps, uint32_t normed, float floor, nc_comm *reduce,
+                                       const nc_then *then_) {
     if (!ctx || !out_dev) return refuse(kBadArgument, "a product needs a context and an output");
     int32_t rc;
     if ((rc = check_weight(w))) return rc;
@@ -891,26 +893,40 @@ int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream_, const nc_w
         return refuse(kBadArgument, "the staged activations (%u rows of %u for blocks of %u) do not fit a [%u, %u] weight of element %u",
                       from.rows, from.k, from.granule, w->n, w->k, w->element);
     if (from.rows > 2 || from.halves) return refuse(kBadArgument, "a product that stages its own output carries 1 or 2 rows, not %u", from.rows);
-    const bool then = then_slot != NC_NO_SLOT;
-    if (then && (then_slot >= kStagingSlots || then_slot == ctx->cur))
+    nc_then none = {NC_NO_SLOT, 0, 0, 0, nullptr, 0};
+    const nc_then &want = then_ ? *then_ : none;
+    const bool then = want.slot != NC_NO_SLOT;
+    if (then && (want.slot >= kStagingSlots || want.slot == ctx->cur))
         return refuse(kBadArgument, "the output is staged into another slot than the one the product reads (0 to %u)", kStagingSlots - 1);
     if (out_stride < w->n || out_stride % 4 || (uintptr_t)out_dev % 16)
         return refuse(kBadArgument, "output rows of %u start 16-byte aligned and do not overlap (stride %llu)", w->n, (unsigned long long)out_stride);
     if (then && w->n % 8) return refuse(kBadArgument, "%u outputs do not stage in whole runs of eight", w->n);
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
+    // where the output rows sit on the K axis of the product that will read them
+    const uint32_t then_k = want.k ? want.k : w->n, lo = want.k ? want.lo : 0, hi = want.k ? want.hi : w->n;
+    if (then && (hi - lo != w->n || hi > then_k || lo % 32 || then_k % granule))
+        return refuse(kBadArgument, "rows of %u outputs are not the window [%u, %u) of %u activations in blocks of %u", w->n, lo, hi, then_k, granule);
+    if (reduce) {
+        if (!then) return refuse(kBadArgument, "a product that adds the ranks' sums up also stages them: name a slot");
+        if (!reduce->connected) return refuse(kBadState, "the communicator is not connected to its peers");
+        if (lo || w->n % 256 || (uint64_t)from.rows * w->n > reduce->max_count)
+            return refuse(kBadArgument, "an exchange in the epilogue takes whole rows of a multiple of 256 numbers, at most %llu in all (got %u x %u)",
+                          (unsigned long long)reduce->max_count, from.rows, w->n);
+    }
     // the slot the output is staged into
-    Staging &to = ctx->slots[then ? then_slot : ctx->cur];
-    const uint64_t kpad = ((uint64_t)w->n + 255) / 256 * 256;
+    Staging &to = ctx->slots[then ? want.slot : ctx->cur];
+    const uint64_t kpad = ((uint64_t)then_k + 255) / 256 * 256;
     const uint32_t ncols = from.rows * 3;
     if (then) {
-        if (kpad / 256 > 1024) return refuse(kBadArgument, "rows of %u outputs are more than this path stages (262144)", w->n);
+        if (kpad / 256 > 1024) return refuse(kBadArgument, "rows of %u activations are more than this path stages (262144)", then_k);
         if ((rc = ensure(ctx, to.dig, kpad * ncols, false))) return rc;
         if ((rc = ensure(ctx, to.cs, kpad / 32 * ncols * sizeof(float), false))) return rc;
         if ((rc = ensure(ctx, to.sums, kpad / 256 * ncols * 64, false))) return rc;
         if ((rc = ensure(ctx, to.chunks, kpad / 256 * sizeof(unsigned int), true))) return rc;
     }
     if ((rc = ensure(ctx, ctx->squares, (uint64_t)kMaxRowsPerPass * 1024 * sizeof(float), true))) return rc;
+    if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
     GemvParams p;
     memset(&p, 0, sizeof p);
     p.w = (const uint8_t *)w->data_dev;
@@ -941,24 +957,34 @@ int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream_, const nc_w
     a.prep.cs = (float *)to.cs.ptr;
     a.prep.sums = (uint32_t *)to.sums.ptr;
     a.prep.rows = from.rows;
-    a.prep.k = w->n;
+    a.prep.k = then_k;
     a.prep.ncols = ncols;
     a.prep.granule = granule;
     a.prep.vector = 1;
-    a.prep.lo = 0;
-    a.prep.hi = w->n;
-    a.gain = then_gain_dev;
-    a.sumsq = then_squares ? (float *)ctx->squares.ptr : nullptr;
+    a.prep.lo = lo;
+    a.prep.hi = hi;
+    a.gain = want.gain_dev;
+    a.sumsq = want.squares ? (float *)ctx->squares.ptr : nullptr;
     a.counters = (unsigned int *)to.chunks.ptr;
     a.piece = pair ? 16 : 32;
+    a.exchange = reduce ? reduce->view_dev : nullptr;
+    a.wait_nanos = ctx->wait_nanos;
+    a.status = (unsigned int *)ctx->status.ptr;
     if ((rc = launch_gemv_hooked(ctx, (cudaStream_t)stream_, w->element, p, plan_n, w->k))) return rc;
     if (then) {
         to.rows = from.rows;
-        to.k = w->n;
+        to.k = then_k;
         to.granule = granule;
         to.halves = 0;
     }
     return 0;
+}
+
+int32_t neura_cuda_linear_staged_then(nc_context *ctx, void *stream_, const nc_weight *w, float *out_dev, uint64_t out_stride,
+                                      const nc_step *chain, uint32_t n_steps, uint32_t normed, float floor,
+                                      uint32_t then_slot, const float *then_gain_dev, uint32_t then_squares) {
+    const nc_then then = {then_slot, 0, 0, 0, then_gain_dev, then_squares};
+    return neura_cuda_linear_staged_fused(ctx, stream_, w, out_dev, out_stride, chain, n_steps, normed, floor, nullptr, &then);
 }
 
 int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, const float *x_dev, uint32_t rows,
@@ -1131,10 +1157,10 @@ int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream_, const float *x
     return 0;
 }
 
-int32_t neura_cuda_rope_cache(nc_context *ctx, void *stream_, float *qkv_dev, uint64_t row_stride,
+static int32_t rope_cache_any(nc_context *ctx, void *stream_, float *qkv_dev, uint64_t row_stride,
                               const uint32_t *position_dev, float base, uint32_t batch, uint32_t heads,
                               uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
-                              float *values_dev) {
+                              float *values_dev, uint32_t shared) {
     if (!ctx || !qkv_dev || !position_dev || !keys_dev || !values_dev)
         return refuse(kBadArgument, "rope needs a context, the q|k|v rows, their positions and a cache");
     if (!batch || !heads || !key_heads || !width || width % 2 || !capacity)
@@ -1142,11 +1168,27 @@ int32_t neura_cuda_rope_cache(nc_context *ctx, void *stream_, float *qkv_dev, ui
     if (row_stride < (uint64_t)(heads + 2 * key_heads) * width)
         return refuse(kBadArgument, "a q|k|v row of %u numbers overlaps at stride %llu", (heads + 2 * key_heads) * width,
                       (unsigned long long)row_stride);
-    RopeCacheParams p{qkv_dev, row_stride, position_dev, keys_dev, values_dev, base, batch, heads, key_heads, width, capacity};
+    RopeCacheParams p{qkv_dev, row_stride, position_dev, keys_dev, values_dev, base, batch, heads, key_heads, width, capacity, shared};
     const uint32_t work = batch * ((heads + key_heads) * (width / 2) + key_heads * width);
     NC_CUDA(launch_dependent(rope_cache_kernel, dim3((work + 255) / 256), dim3(256), 0, (cudaStream_t)stream_, p));
     ctx->launches++;
     return 0;
+}
+
+int32_t neura_cuda_rope_cache(nc_context *ctx, void *stream_, float *qkv_dev, uint64_t row_stride,
+                              const uint32_t *position_dev, float base, uint32_t batch, uint32_t heads,
+                              uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
+                              float *values_dev) {
+    return rope_cache_any(ctx, stream_, qkv_dev, row_stride, position_dev, base, batch, heads, key_heads, width, capacity, keys_dev,
+                          values_dev, 0);
+}
+
+int32_t neura_cuda_rope_cache_rows(nc_context *ctx, void *stream_, float *qkv_dev, uint64_t row_stride,
+                                   const uint32_t *position_dev, float base, uint32_t rows, uint32_t heads,
+                                   uint32_t key_heads, uint32_t width, uint32_t capacity, float *keys_dev,
+                                   float *values_dev) {
+    return rope_cache_any(ctx, stream_, qkv_dev, row_stride, position_dev, base, rows, heads, key_heads, width, capacity, keys_dev,
+                          values_dev, 1);
 }
 
 }  // extern "C"
@@ -1158,7 +1200,7 @@ namespace {
 int32_t attend_any(nc_context *ctx, void *stream_, const float *q_dev, uint64_t q_stride, const float *keys_dev,
                    const float *values_dev, const uint32_t *position_dev, float scale, uint32_t batch, uint32_t heads,
                    uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev, uint64_t out_stride,
-                   float *fresh_keys, float *fresh_values, const float2 *rope_table) {
+                   float *fresh_keys, float *fresh_values, const float2 *rope_table, uint32_t shared = 0) {
     if (!ctx || !q_dev || !keys_dev || !values_dev || !position_dev || !out_dev)
         return refuse(kBadArgument, "attention needs a context, queries, a cache, positions and an output");
     if (!batch || !heads || !key_heads || heads % key_heads || !width || !capacity)
@@ -1213,7 +1255,7 @@ int32_t attend_any(nc_context *ctx, void *stream_, const float *q_dev, uint64_t 
     }
     AttendParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride,
                    (float *)ctx->attend_partial.ptr, (unsigned int *)ctx->attend_counters.ptr, scale,
-                   batch, heads, key_heads, width, capacity, splits, fresh_keys, fresh_values, rope_table};
+                   batch, heads, key_heads, width, capacity, splits, fresh_keys, fresh_values, rope_table, shared};
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(batch * key_heads * splits);
     config.blockDim = dim3(kAttendThreads);
@@ -1243,6 +1285,14 @@ int32_t neura_cuda_attend(nc_context *ctx, void *stream, const float *q_dev, uin
                           uint64_t out_stride) {
     return attend_any(ctx, stream, q_dev, q_stride, keys_dev, values_dev, position_dev, scale, batch, heads, key_heads,
                       width, capacity, out_dev, out_stride, nullptr, nullptr, nullptr);
+}
+
+int32_t neura_cuda_attend_rows(nc_context *ctx, void *stream, const float *q_dev, uint64_t q_stride, const float *keys_dev,
+                               const float *values_dev, const uint32_t *position_dev, float scale, uint32_t rows,
+                               uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
+                               uint64_t out_stride) {
+    return attend_any(ctx, stream, q_dev, q_stride, keys_dev, values_dev, position_dev, scale, rows, heads, key_heads,
+                      width, capacity, out_dev, out_stride, nullptr, nullptr, nullptr, 1);
 }
 
 int32_t neura_cuda_rope_table(nc_context *ctx, void *stream, const uint32_t *position_dev, float base, uint32_t batch,
@@ -1325,19 +1375,37 @@ int32_t neura_cuda_comm_create(nc_context *ctx, uint64_t max_count, nc_comm **ou
     comm->device = ctx->device;
     comm->max_count = (max_count + 3) / 4 * 4;
     comm->slot_bytes = (comm->max_count * sizeof(float) + 255) / 256 * 256;
-    const uint64_t bytes = kCommHeaderBytes + 2 * kMaxRanks * comm->slot_bytes;   // two slots of one seat per sender
+    comm->chunks_most = (uint32_t)((comm->max_count + 255) / 256);
+    comm->header_bytes = (kCommChunkFlagsAt + 32 * comm->chunks_most + 255) / 256 * 256;
+    const uint64_t bytes = comm->header_bytes + 2 * kMaxRanks * comm->slot_bytes;   // two slots of one seat per sender
     cudaError_t e = cudaMalloc((void **)&comm->mine, bytes);
     if (e == cudaSuccess) e = cudaMemset(comm->mine, 0, bytes);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&comm->view_dev, sizeof(ExchangeView));
     cudaIpcMemHandle_t handle;
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(&handle, comm->mine);
     if (e != cudaSuccess) {
         if (comm->mine) cudaFree(comm->mine);
+        if (comm->view_dev) cudaFree(comm->view_dev);
         delete comm;
         return cuda_refuse(e, "neura_cuda_comm_create");
     }
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
     memcpy(handle_out, &handle, sizeof handle);
     *out = comm;
+    return 0;
+}
+
+static int32_t comm_publish_view(nc_comm *comm) {
+    ExchangeView view;
+    memset(&view, 0, sizeof view);
+    view.mine = comm->mine;
+    for (uint32_t r = 0; r < comm->world; ++r) view.peer[r] = comm->peer[r];
+    view.slot_bytes = comm->slot_bytes;
+    view.header_bytes = comm->header_bytes;
+    view.world = comm->world;
+    view.rank = comm->rank;
+    view.chunks_most = comm->chunks_most;
+    NC_CUDA(cudaMemcpy(comm->view_dev, &view, sizeof view, cudaMemcpyHostToDevice));
     return 0;
 }
 
@@ -1359,7 +1427,7 @@ int32_t neura_cuda_comm_connect(nc_context *ctx, nc_comm *comm, uint32_t rank, u
     comm->world = world;
     comm->rank = rank;
     comm->connected = true;
-    return 0;
+    return comm_publish_view(comm);
 }
 
 int32_t neura_cuda_comm_connect_local(nc_context *ctx, nc_comm *comm, uint32_t rank, uint32_t world, nc_comm *const *all) {
@@ -1387,7 +1455,7 @@ int32_t neura_cuda_comm_connect_local(nc_context *ctx, nc_comm *comm, uint32_t r
     comm->rank = rank;
     comm->connected = true;
     comm->local = true;
-    return 0;
+    return comm_publish_view(comm);
 }
 
 int32_t neura_cuda_allreduce(nc_context *ctx, void *stream_, nc_comm *comm, float *inout_dev, uint32_t count) {
@@ -1404,6 +1472,7 @@ int32_t neura_cuda_allreduce(nc_context *ctx, void *stream_, nc_comm *comm, floa
     for (uint32_t r = 0; r < comm->world; ++r) p.peer[r] = comm->peer[r];
     p.inout = inout_dev;
     p.slot_bytes = comm->slot_bytes;
+    p.header_bytes = comm->header_bytes;
     p.count = count;
     p.world = comm->world;
     p.rank = comm->rank;
@@ -1433,6 +1502,7 @@ int32_t neura_cuda_allreduce_norm_stage(nc_context *ctx, void *stream_, nc_comm 
     for (uint32_t r = 0; r < comm->world; ++r) p.peer[r] = comm->peer[r];
     p.inout = inout_dev;
     p.slot_bytes = comm->slot_bytes;
+    p.header_bytes = comm->header_bytes;
     p.count = (uint32_t)count;
     p.world = comm->world;
     p.rank = comm->rank;
@@ -1453,6 +1523,7 @@ int32_t neura_cuda_comm_destroy(nc_context *ctx, nc_comm *comm) {
     for (uint32_t r = 0; r < comm->world && !comm->local; ++r)
         if (r != comm->rank && comm->peer[r]) cudaIpcCloseMemHandle(comm->peer[r]);
     if (comm->mine) cudaFree(comm->mine);
+    if (comm->view_dev) cudaFree(comm->view_dev);
     delete comm;
     return 0;
 }

@@ -20,6 +20,7 @@
 //                       4 + t, words 2 and 3 the same for S1; the other bytes are zero.
 #pragma once
 #include "common.cuh"
+#include "exchange.cuh"
 
 namespace nc {
 
@@ -150,12 +151,21 @@ __device__ __forceinline__ void load_chunk(const PrepParams &p, uint32_t row, ui
 // the next product finds its operand ready after one barrier.  With `gain` the chunk is multiplied by the
 // coming rms_norm's weight first and the chunk's sum of squares is left in `sumsq`: the norm's scalar
 // 1 / sqrt(mean(x^2) + floor) is applied by the consumer to its outputs (a product is linear in a row scale).
+//
+// On a rank of a tensor-parallel group two more things ride here.  The produced rows may be a window [lo, hi) of the
+// consumer's K axis (a row-parallel weight keeps the whole blocks that cover its share of K): chunks, counters and
+// the staged form are in the consumer's coordinates, the rows themselves start at lo.  And the produced rows may be
+// partial sums over a share of K (`exchange`): the warp that completes a chunk first adds the ranks' chunks up
+// (exchange_chunk), writes the sums back to the rows, and stages those.
 struct StageAfter {
-    PrepParams prep;         // x = the rows being produced, k = their width, dig/cs/sums = the consumer's operand
-    const float *gain;       // [k] or null
+    PrepParams prep;         // x = the rows being produced, k = the consumer's K, [lo, hi) = where the rows sit in it
+    const float *gain;       // [hi - lo] or null
     float *sumsq;            // [rows][chunks] or null
     unsigned int *counters;  // [rows][chunks] finished pieces, zero between launches
     uint32_t piece;          // columns one arrival covers (a tile's 32, a pair tile's 16)
+    const ExchangeView *exchange;   // not null: the rows are this rank's partial sums of a [rows x (hi - lo)] all-reduce
+    unsigned long long wait_nanos;  // how long a chunk waits for the peers, and the word raised when that runs out
+    unsigned int *status;
 };
 
 // Digitises chunk `chunk` of row `row` from the produced values (the whole warp calls).
@@ -164,6 +174,13 @@ __device__ __forceinline__ void stage_after_chunk(const StageAfter &a, uint32_t 
     const bool live = from < a.prep.k;
     float v[8];
     load_chunk(a.prep, row, from, live, v);
+    if (a.exchange) {   // the row holds this rank's partial sums: add the ranks' up, keep the sums (lo = 0, whole chunks)
+        const uint32_t chunks = a.prep.k / 256;
+        if (!exchange_chunk(*a.exchange, row * a.prep.k + from - lane * 8, row * chunks + chunk, a.prep.rows * chunks, v, a.wait_nanos, a.status)) return;
+        float *to = const_cast<float *>(a.prep.x) + (uint64_t)row * a.prep.x_stride + from;
+        __stcg(reinterpret_cast<float4 *>(to), make_float4(v[0], v[1], v[2], v[3]));
+        __stcg(reinterpret_cast<float4 *>(to + 4), make_float4(v[4], v[5], v[6], v[7]));
+    }
     if (a.sumsq) {
         float square = 0.0f;
 #pragma unroll
@@ -171,9 +188,9 @@ __device__ __forceinline__ void stage_after_chunk(const StageAfter &a, uint32_t 
         for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
         if (lane == 0) __stcg(a.sumsq + row * ((a.prep.k + 255) / 256) + chunk, square);
     }
-    if (a.gain && live) {
-        const float4 g0 = __ldg(reinterpret_cast<const float4 *>(a.gain + from));
-        const float4 g1 = __ldg(reinterpret_cast<const float4 *>(a.gain + from + 4));
+    if (a.gain && live && from >= a.prep.lo && from < a.prep.hi) {
+        const float4 g0 = __ldg(reinterpret_cast<const float4 *>(a.gain + (from - a.prep.lo)));
+        const float4 g1 = __ldg(reinterpret_cast<const float4 *>(a.gain + (from - a.prep.lo) + 4));
         v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w;
         v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
     }
@@ -184,9 +201,10 @@ __device__ __forceinline__ void stage_after_chunk(const StageAfter &a, uint32_t 
 // follows its stores).  Counts the arrival; the warp that completes a chunk digitises it for all rows.
 __device__ __forceinline__ void stage_after_piece(const StageAfter &a, uint32_t first) {
     const uint32_t lane = threadIdx.x & 31;
-    if (first >= a.prep.k) return;
+    first += a.prep.lo;                      // where the piece sits on the consumer's K axis
+    if (first >= a.prep.hi) return;
     const uint32_t chunk = first / 256;
-    const uint32_t width = min(a.prep.k, (chunk + 1) * 256) - chunk * 256;
+    const uint32_t width = min(a.prep.hi, (chunk + 1) * 256) - max(a.prep.lo, chunk * 256);
     const uint32_t expected = (width + a.piece - 1) / a.piece;
     unsigned int seen = 0;
     if (lane == 0) {

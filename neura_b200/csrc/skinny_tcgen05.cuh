@@ -329,15 +329,10 @@ __device__ __forceinline__ uint4 skinny_min_chunk(float dmin, uint32_t mins) {
     return make_uint4(v[0], v[1], v[2], v[3]);
 }
 
-// One lane of a converged warp.  The roles that issue MMAs and copies run as whole warps with the issue itself
-// under this predicate: their loop state is then the same in every lane, which lets the compiler keep descriptors
-// and addresses in uniform registers (inside an `if (lane == 0)` branch every MMA paid for moving them there: 65 ns
-// an MMA, whatever its shape).
-__device__ __forceinline__ bool elect_one() {
-    uint32_t chosen;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(chosen));
-    return chosen != 0;
-}
+// The roles that issue MMAs and copies run as whole warps with the issue itself under elect_one_lane(): their loop
+// state is then the same in every lane, which lets the compiler keep descriptors and addresses in uniform registers
+// (inside an `if (lane == 0)` branch every MMA paid for moving them there: 65 ns an MMA, whatever its shape).
+__device__ __forceinline__ bool elect_one() { return elect_one_lane(); }
 
 // A position in a ring of `n` stages and the phase of its barriers.
 struct SkRing {

@@ -4,9 +4,9 @@ Mirrors the plane bookkeeping of crates/neura-generate/src/batch.rs: ``admit`` (
 ``restart`` (1056-1105), ``resume`` (1015-1054), ``suspend`` (1107-1123), ``step`` (1125-1135),
 ``finish`` (1137-1148) and the emission rule of ``complete_answer`` (1676-1714): a plane that feeds
 its last prompt token keeps the chosen token as its feed and emits nothing; a generating plane emits
-its feed and keeps the new choice.  Greedy choice only (the reference's default ``Sampling``);
-every prompt token goes through the decode step (the reference's chunked fills are a faster way to
-the same cache, not a different result).
+its feed and keeps the new choice.  Greedy choice only (the reference's default ``Sampling``).
+A stepper that offers ``fill`` takes the prompts in chunks first (``Batch::prefill``, batch.rs:1595-1599,
+:298-325): all but a prompt's last token, which goes through the decode step like every generated one.
 
 The device work is one call per step: ``stepper.answer(tokens, cursors) -> chosen`` over all planes
 (``qwen.Decoder.answer``).  A plane that is empty or suspended rides along with token 0 at its own
@@ -143,6 +143,12 @@ class Batch:
                 tokens[slot] = held.feed
             if held.running and held.cursor >= self.context:
                 raise BatchError(f"plane {slot} has filled its context of {self.context}; finish, suspend or restart it")
+        self._prefill()
+        for slot, held in enumerate(self.slots):   # (a fill moved the cursors of the planes it fed)
+            if held is not None:
+                cursors[slot] = min(held.cursor, self.stepper.capacity - 1)
+                if held.phase == PROMPTING:
+                    tokens[slot] = held.prompt[0]
         chosen = self.stepper.answer(tokens, cursors)
         emitted: List[Emitted] = []
         for slot, held in enumerate(self.slots):
@@ -158,6 +164,23 @@ class Batch:
                 held.feed = token
             held.cursor += 1
         return emitted
+
+    def _prefill(self) -> None:
+        """Batch::prefill: every feeding plane hands all but the last token of its prompt to the stepper's ``fill`` in
+        the chunk sizes it names (largest first); what is left over, fewer tokens than the smallest chunk, goes
+        through the decode steps."""
+        chunks = tuple(getattr(self.stepper, "chunks", ()) or ())
+        if not chunks or not hasattr(self.stepper, "fill"):
+            return
+        for slot, held in enumerate(self.slots):
+            if held is None or held.phase != PROMPTING:
+                continue
+            while True:
+                size = next((c for c in chunks if c <= len(held.prompt) - 1), None)
+                if size is None:
+                    break
+                self.stepper.fill(slot, [held.prompt.popleft() for _ in range(size)], held.cursor)
+                held.cursor += size
 
     def advance(self, waves: int) -> List[Emitted]:
         """``waves`` steps in a row (batch.rs:1174-1190 walks them as one frame)."""

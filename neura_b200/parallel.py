@@ -153,6 +153,24 @@ class TorchComm:
             self.dist.all_gather_into_tensor(dst, src)
 
 
+class NullComm(TorchComm):
+    """No exchange at all: one rank's share of a tensor-parallel step on one GPU, for timing the rank's own chain
+    of launches without its peers (the sums it leaves are partial, so the tokens mean nothing)."""
+
+    def __init__(self, world: int, rank: int):
+        self.world, self.rank = world, rank
+
+    def all_reduce(self, ptr: int, count: int) -> None:
+        pass
+
+    def all_gather(self, dst_ptr: int, src_ptr: int, count: int) -> None:
+        pass
+
+    def reduce_handle(self):
+        """No communicator: a product that would exchange in its epilogue keeps its own partial sums."""
+        return None
+
+
 def load_decoder_weights(rt, config: Config, packed: Dict[str, np.ndarray], norms: Dict[str, np.ndarray],
                          shard: Shard = None, pair_mlp: bool = True):
     """Runtime::load for a whole decoder: pours the GGUF tensors of ``packed`` (named as a Qwen GGUF
@@ -231,6 +249,11 @@ class PeerComm(TorchComm):
         from .runtime import _check
 
         _check(self.rt._lib.neura_cuda_allreduce(self.rt._ctx, self.rt.stream, self.comm, ctypes.c_void_p(ptr), count))
+
+    def reduce_handle(self):
+        """The communicator as ``Runtime.linear_staged_fused`` takes it: the product then adds the ranks' partial
+        sums up in its own epilogue."""
+        return self.comm
 
     def all_reduce_norm_stage(self, ptr: int, rows: int, k: int, weight_ptr: int, floor: float, element: int) -> bool:
         import ctypes

@@ -116,8 +116,11 @@ class Decoder:
         self.keys = [rt.tensor(cache) for _ in range(c.layers)]
         self.values = [rt.tensor(cache) for _ in range(c.layers)]
         widest_k = max(c.hidden, self.window(c.feed_forward)[0], self.window(c.query_width)[0])
-        rt.reserve(batch, max(self.vocab, 2 * self.feed_forward, c.hidden), widest_k)   # 2x: a sealed gate|up pair
-        rt.reserve_decoder(batch, self.heads, self.key_heads, c.head_width, capacity)
+        # scratch for the decode step and for the largest prompt chunk, all of it now: a recorded step holds the
+        # scratch's addresses, so nothing may grow it later
+        most = max([batch, *self.chunks])
+        rt.reserve(most, max(self.vocab, 2 * self.feed_forward, c.hidden), widest_k)   # 2x: a sealed gate|up pair
+        rt.reserve_decoder(most, self.heads, self.key_heads, c.head_width, capacity)
         self.program: Optional[int] = None
         self.compiled = None   # the step as one persistent kernel (compile())
         self.fold = False      # True: fold norms and stagings into the products' epilogues (fewer, longer launches)
@@ -149,20 +152,31 @@ class Decoder:
 
     def folded(self) -> bool:
         """Whether the step may fold the norms and stagings into the products' epilogues (``linear_staged_then``):
-        one GPU, 1 or 2 sequences, the MLP sealed as a pair."""
-        return self.shard is None and self.batch <= 2 and "blk.0.ffn_gate_up.weight" in self.weights and self.fold
+        1 or 2 sequences, the MLP sealed as a pair, and, for a tensor-parallel rank, a communicator whose exchange a
+        product can do in its own epilogue."""
+        if self.batch > 2 or "blk.0.ffn_gate_up.weight" not in self.weights or not self.fold:
+            return False
+        return self.shard is None or hasattr(self.comm, "reduce_handle")
 
     def _step_folded(self) -> None:
         """The step with seven launches a layer instead of ten: the output and down products stage the hidden row
         for the next norm (gain and sums of squares in their epilogues, the scalar applied by the consumer), the
-        gate|up product stages its own output for the down product.  Slots: 0 hidden, 1 attended, 2 held."""
+        gate|up product stages its own output for the down product.  On a tensor-parallel rank the output and down
+        products also add the ranks' partial sums up in their epilogues (no launch of its own for the exchange), and
+        the attended and held rows are staged at their window of the row-parallel weights' K axes.
+        Slots: 0 hidden, 1 attended, 2 held."""
         rt, c, w, n = self.rt, self.config, self.weights, self.norms
+        reduce = self.comm.reduce_handle() if self.shard is not None else None
+        carries = self.shard is None or self.shard.rank == 0   # rank 0 carries the residual into the sum
+        attended_k, attended_lo, attended_hi = self.window(c.query_width)
+        held_window = self.window(c.feed_forward)
         rt.staging_select(0)
         rt.embed(w["token_embd.weight"], self.tokens, self.hidden)
         rt.rms_norm_stage(self.hidden, n["blk.0.attn_norm.weight"], c.floor, c.element)
         for layer in range(c.layers):
             at = lambda name: f"blk.{layer}.{name}.weight"  # noqa: E731
             after = n[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < c.layers else n["output_norm.weight"]
+            residual = [Step(ADD, self.hidden)] if carries else None
             rt.staging_select(0)
             rt.linear_staged_then(w[at("attn_qkv")], self.qkv, normed=layer > 0, floor=c.floor)
             rt.rope_cache(self.qkv, self.position, c.rope_base, self.heads, self.key_heads, c.head_width,
@@ -170,17 +184,23 @@ class Decoder:
             rt.attend(self.qkv, self.keys[layer], self.values[layer], self.position, self.scale, self.heads,
                       self.key_heads, c.head_width, self.capacity, self.attended)
             rt.staging_select(1)
-            rt.stage(self.attended, c.element)
-            rt.linear_staged_then(w[at("attn_output")], self.hidden, [Step(ADD, self.hidden)], then_slot=0,
-                                  gain=n[at("ffn_norm")], squares=True)
+            rt.stage_window(self.attended, c.element, attended_k, attended_lo, attended_hi)
+            rt.linear_staged_fused(w[at("attn_output")], self.hidden, residual, reduce=reduce, then_slot=0,
+                                   gain=n[at("ffn_norm")], squares=True)
             rt.staging_select(0)
-            rt.linear_staged_then(w[at("ffn_gate_up")], self.held, normed=True, floor=c.floor, then_slot=2)
+            rt.linear_staged_fused(w[at("ffn_gate_up")], self.held, normed=True, floor=c.floor, then_slot=2,
+                                   window=held_window if self.shard is not None else None)
             rt.staging_select(2)
-            rt.linear_staged_then(w[at("ffn_down")], self.hidden, [Step(ADD, self.hidden)], then_slot=0, gain=after,
-                                  squares=True)
+            rt.linear_staged_fused(w[at("ffn_down")], self.hidden, residual, reduce=reduce, then_slot=0, gain=after,
+                                   squares=True)
         rt.staging_select(0)
         rt.linear_staged_then(w["output.weight"], self.logits, normed=True, floor=c.floor)
-        rt.argmax(self.logits, self.tokens)
+        if self.shard is None:
+            rt.argmax(self.logits, self.tokens)
+        else:
+            self.comm.all_gather(self.gathered.ptr, self.logits.ptr, self.batch * self.vocab)
+            rt.argmax_segments(self.gathered.ptr, self.batch, c.vocab, self.vocab, self.vocab,
+                               self.batch * self.vocab, self.tokens)
         rt.advance(self.position, 1)
 
     def step(self) -> None:
@@ -214,6 +234,89 @@ class Decoder:
             rt.argmax_segments(self.gathered.ptr, self.batch, c.vocab, self.vocab, self.vocab,
                                self.batch * self.vocab, self.tokens)
         rt.advance(self.position, 1)
+
+    @property
+    def chunks(self) -> tuple:
+        """The prompt chunk sizes ``fill`` takes, largest first (the reference fills in chunks of 32 and 8,
+        examples/qwen/main.rs:21); empty where a prompt goes through the decode step token by token."""
+        if self.shard is not None:
+            return ()
+        return (32, 8) if self.config.element == Q4K else (16, 8)
+
+    def fill(self, sequence: int, tokens, start: int) -> None:
+        """Batch::prefill for one chunk (crates/neura-generate/src/batch.rs:1595-1599, :298-325): feeds ``tokens``, consecutive
+        prompt tokens of plane ``sequence`` at cursors start, start + 1, ..., through every layer at once.  The
+        projections see all the rows of the chunk in one product (a Q4_K chunk of more than eight rows streams each
+        weight once for all of them), the rows' keys and values go to the plane's cache, and row i attends to the
+        cache up to its own cursor.  Nothing is chosen: a prompt's last token goes through ``answer``."""
+        import numpy as np
+
+        rt, c, w, n = self.rt, self.config, self.weights, self.norms
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32).reshape(-1)
+        rows = int(tokens.size)
+        if self.shard is not None:
+            raise ValueError("a tensor-parallel rank feeds its prompt through the decode step")
+        if not 1 <= rows <= self.chunks[0]:
+            raise ValueError(f"a chunk holds 1 to {self.chunks[0]} tokens, not {rows}")
+        if not 0 <= sequence < self.batch or start + rows > self.capacity:
+            raise ValueError(f"plane {sequence} has no room for cursors {start}..{start + rows - 1}")
+        held = self._fill_buffers(rows)
+        rt.write(held["tokens"], tokens)
+        rt.write(held["position"], np.arange(start, start + rows, dtype=np.uint32))
+        hidden, qkv, attended, mlp = held["hidden"], held["qkv"], held["attended"], held["held"]
+        per_plane = self.key_heads * self.capacity * c.head_width * 4
+        rt.staging_select(0)
+        rt.embed(w["token_embd.weight"], held["tokens"], hidden)
+        for layer in range(c.layers):
+            at = lambda name: f"blk.{layer}.{name}.weight"  # noqa: E731
+            keys_ptr = self.keys[layer].ptr + sequence * per_plane
+            values_ptr = self.values[layer].ptr + sequence * per_plane
+            rt.rms_norm_stage(hidden, n[at("attn_norm")], c.floor, c.element)
+            rt.linear_staged(w[at("attn_qkv")], qkv)
+            rt.rope_cache_rows(qkv, held["position"], c.rope_base, rows, self.heads, self.key_heads, c.head_width,
+                               self.capacity, keys_ptr, values_ptr)
+            rt.attend_rows(qkv, keys_ptr, values_ptr, held["position"], self.scale, rows, self.heads, self.key_heads,
+                           c.head_width, self.capacity, attended)
+            rt.stage(attended, c.element)
+            rt.linear_staged(w[at("attn_output")], hidden, [Step(ADD, hidden)])
+            rt.rms_norm_stage(hidden, n[at("ffn_norm")], c.floor, c.element)
+            if at("ffn_gate_up") in w:
+                rt.linear_staged(w[at("ffn_gate_up")], mlp)
+            else:
+                rt.linear_staged(w[at("ffn_gate")], held["gate"], [Step(SILU)])
+                rt.linear_staged(w[at("ffn_up")], mlp, [Step(MUL, held["gate"])])
+            rt.stage(mlp, c.element)
+            rt.linear_staged(w[at("ffn_down")], hidden, [Step(ADD, hidden)])
+
+    def _fill_buffers(self, rows: int) -> dict:
+        """The activation rows of a chunk of ``rows`` tokens (kept per row count: shapes carry the row strides)."""
+        if not hasattr(self, "_fills"):
+            self._fills = {}
+        if rows not in self._fills:
+            rt, c = self.rt, self.config
+            self._fills[rows] = {
+                "tokens": rt.tensor_u32(rows), "position": rt.tensor_u32(rows), "hidden": rt.tensor(rows, c.hidden),
+                "qkv": rt.tensor(rows, self.query_width + 2 * self.key_width), "attended": rt.tensor(rows, self.query_width),
+                "held": rt.tensor(rows, self.feed_forward), "gate": rt.tensor(rows, self.feed_forward),
+            }
+        return self._fills[rows]
+
+    def prefill(self, prompts) -> None:
+        """Feeds all but the last token of every plane's prompt in chunks (``fill``), then leaves tokens and cursors
+        so that the next ``run_token`` feeds the last prompt token of every plane."""
+        import numpy as np
+
+        prompts = np.ascontiguousarray(prompts, dtype=np.uint32).reshape(self.batch, -1)
+        length = prompts.shape[1]
+        for sequence in range(self.batch):
+            at = 0
+            while at < length - 1:
+                left = length - 1 - at
+                take = next((size for size in self.chunks if size <= left), left)
+                self.fill(sequence, prompts[sequence, at: at + take], at)
+                at += take
+        self.rt.write(self.tokens, prompts[:, -1].copy())
+        self.rt.write(self.position, np.full(self.batch, length - 1, dtype=np.uint32))
 
     def compile(self) -> None:
         """Runtime::compile for the whole step (crates/neura-runtime/src/runtime.rs:528): lays the step out
@@ -271,7 +374,7 @@ class Decoder:
         if self.compiled is not None:
             return 1
         if self.folded():
-            return self.config.layers * 7 + 5
+            return self.config.layers * 7 + (5 if self.shard is None else 6)
         paired = "blk.0.ffn_gate_up.weight" in self.weights
         return self.config.layers * (10 if paired else 11) + 5
 
@@ -308,8 +411,11 @@ class Decoder:
         them (crates/neura-generate/src/batch.rs:1716-1725); returns the chosen ids [batch]."""
         import numpy as np
 
+        cursors = np.ascontiguousarray(cursors, dtype=np.uint32)
+        if cursors.size and int(cursors.max()) >= self.capacity:
+            raise ValueError(f"cursor {int(cursors.max())} lies past a cache of {self.capacity} rows")
         self.rt.write(self.tokens, np.ascontiguousarray(tokens, dtype=np.uint32))
-        self.rt.write(self.position, np.ascontiguousarray(cursors, dtype=np.uint32))
+        self.rt.write(self.position, cursors)
         self.run_token()
         return self.rt.read(self.tokens, dtype=np.uint32)
 
@@ -328,17 +434,24 @@ class Decoder:
         weights, device_norms = load_decoder_weights(rt, config, packed, norms, shard=shard)
         return cls(rt, config, weights, device_norms, batch=batch, capacity=capacity, shard=shard, comm=comm)
 
-    def generate(self, prompts, steps: int):
-        """Feeds ``prompts`` [batch, length] one token at a time (every step attends to all the
-        tokens before it), then decodes ``steps`` tokens greedily.  Returns [batch, steps] ids."""
+    def generate(self, prompts, steps: int, chunked: bool = False):
+        """Feeds ``prompts`` [batch, length] (one token at a time, every step attending to all the tokens before
+        it; or, ``chunked``, in chunks through ``prefill``), then decodes ``steps`` tokens greedily.
+        Returns [batch, steps] ids."""
         import numpy as np
 
         prompts = np.ascontiguousarray(prompts, dtype=np.uint32).reshape(self.batch, -1)
+        if prompts.shape[1] + steps > self.capacity:
+            raise ValueError(f"{prompts.shape[1]} prompt tokens and {steps} steps do not fit a cache of {self.capacity} rows")
         self.reset()
         out = np.zeros((self.batch, steps), dtype=np.uint32)
-        for at in range(prompts.shape[1]):
-            self.rt.write(self.tokens, prompts[:, at].copy())
+        if chunked and self.chunks:
+            self.prefill(prompts)
             self.run_token()
+        else:
+            for at in range(prompts.shape[1]):
+                self.rt.write(self.tokens, prompts[:, at].copy())
+                self.run_token()
         out[:, 0] = self.rt.read(self.tokens, dtype=np.uint32)
         for at in range(1, steps):
             self.run_token()

@@ -351,6 +351,24 @@ class Runtime:
             1 if normed else 0, floor, NO_SLOT if then_slot is None else then_slot,
             ctypes.c_void_p(gain.ptr) if gain is not None else None, 1 if squares else 0))
 
+    def linear_staged_fused(self, weight: Weight, out: DeviceTensor, chain: Optional[Sequence[Step]] = None,
+                            normed: bool = False, floor: float = 0.0, reduce=None, then_slot: Optional[int] = None,
+                            window: Optional[tuple] = None, gain: Optional[DeviceTensor] = None,
+                            squares: bool = False) -> None:
+        """``linear_staged_then`` for a tensor-parallel rank: ``window`` = (k, lo, hi) places the output rows on the K
+        axis of the row-parallel product that reads them, ``reduce`` (a communicator handle) makes the rows the sum
+        over the ranks, exchanged chunk by chunk in the product's epilogue before they are staged."""
+        from ._lib import NcThen
+
+        arr, count = self._steps(chain, weight.n)
+        rec = weight.record()
+        k, lo, hi = window if window is not None else (0, 0, 0)
+        then = NcThen(NO_SLOT if then_slot is None else then_slot, k, lo, hi, gain.ptr if gain is not None else None,
+                      1 if squares else 0)
+        _check(self._lib.neura_cuda_linear_staged_fused(
+            self._ctx, self.stream, ctypes.byref(rec), ctypes.c_void_p(out.ptr), out.shape[-1], arr, count,
+            1 if normed else 0, floor, reduce, ctypes.byref(then)))
+
     # -- the steps either side of the products ---------------------------------------
     def tensor_u32(self, count: int) -> DeviceTensor:
         return DeviceTensor(self.alloc(count * 4), count * 4, (count,))
@@ -385,6 +403,21 @@ class Runtime:
                                            ctypes.c_void_p(keys.ptr), ctypes.c_void_p(values.ptr),
                                            ctypes.c_void_p(position.ptr), scale, batch, heads, key_heads, width,
                                            capacity, ctypes.c_void_p(out.ptr), out.shape[-1]))
+
+    def rope_cache_rows(self, qkv: DeviceTensor, position: DeviceTensor, base: float, rows: int, heads: int,
+                        key_heads: int, width: int, capacity: int, keys_ptr: int, values_ptr: int) -> None:
+        """``rope_cache`` for a chunk of one sequence's prompt: ``keys_ptr`` / ``values_ptr`` are that sequence's cache."""
+        _check(self._lib.neura_cuda_rope_cache_rows(self._ctx, self.stream, ctypes.c_void_p(qkv.ptr), qkv.shape[-1],
+                                                    ctypes.c_void_p(position.ptr), base, rows, heads, key_heads, width,
+                                                    capacity, ctypes.c_void_p(keys_ptr), ctypes.c_void_p(values_ptr)))
+
+    def attend_rows(self, q: DeviceTensor, keys_ptr: int, values_ptr: int, position: DeviceTensor, scale: float,
+                    rows: int, heads: int, key_heads: int, width: int, capacity: int, out: DeviceTensor) -> None:
+        """``attend`` for a chunk of one sequence's prompt: row i attends to slots 0..position[i] of that sequence."""
+        _check(self._lib.neura_cuda_attend_rows(self._ctx, self.stream, ctypes.c_void_p(q.ptr), q.shape[-1],
+                                                ctypes.c_void_p(keys_ptr), ctypes.c_void_p(values_ptr),
+                                                ctypes.c_void_p(position.ptr), scale, rows, heads, key_heads, width,
+                                                capacity, ctypes.c_void_p(out.ptr), out.shape[-1]))
 
     def rope_table(self, position: DeviceTensor, base: float, width: int, table: DeviceTensor,
                    batch: Optional[int] = None) -> None:

@@ -69,6 +69,25 @@ class OracleDecoder:
         self.position[:] = np.asarray(cursors, dtype=np.uint32)
         return self.step(np.ascontiguousarray(tokens, dtype=np.uint32))
 
+    chunks = (4, 2)   # the chunk sizes ``fill`` offers a ``generate.Batch`` (small, for the bookkeeping tests)
+
+    def fill(self, sequence: int, tokens, start: int) -> None:
+        """A prompt chunk of one plane: the same cache rows the decode step writes token by token (the other
+        planes ride along at their own cursors and are put back afterwards)."""
+        keep = self.position.copy()
+        for offset, token in enumerate(tokens):
+            feed = np.zeros(self.batch, dtype=np.uint32)
+            feed[sequence] = token
+            cursors = keep.copy()
+            cursors[sequence] = start + offset
+            saved = (self.keys[:, :, :, :].copy(), self.values[:, :, :, :].copy())
+            self.answer(feed, cursors)
+            for b in range(self.batch):   # only the fed plane keeps what the step wrote
+                if b != sequence:
+                    self.keys[:, b] = saved[0][:, b]
+                    self.values[:, b] = saved[1][:, b]
+        self.position[:] = keep
+
     def generate(self, prompts: np.ndarray, steps: int):
         """Returns (tokens [batch, steps], margins [batch, steps]): the gap between the two largest
         logits at every decoded step, which says how decisive each greedy choice was."""

@@ -151,6 +151,37 @@ def test_greedy_tokens_match_the_oracle_for_64_steps(oracle, name, batch):
                     f"the oracle's margin there is {margins[b, at]:.3e}")
 
 
+@pytest.mark.parametrize("name,batch,length", [("q4_k", 1, 45), ("q4_k", 2, 70), ("q8_0", 1, 45), ("q8_0", 3, 21)])
+def test_a_prompt_fed_in_chunks_decodes_what_the_oracle_decodes(oracle, name, batch, length):
+    # Batch::prefill (crates/neura-generate/src/batch.rs:1595-1599): chunks of 32 and 8 (16 and 8 for Q8_0), the rest alone
+    from oracle.decoder import OracleDecoder, synthetic_model
+
+    config = SMALL[name]
+    packed, norms = synthetic_model(config, seed=23)
+    prompts = (oracle.Stream(43).uniform(batch * length, 0.0, 1.0) * config.vocab).astype(np.uint32).reshape(batch, length)
+    want, margins = OracleDecoder(config, packed, norms, batch=batch, capacity=length + 40).generate(prompts, 32)
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weights, dnorms = load_model(rt, config, packed, norms)
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=length + 40)
+        decoder.record()
+        launches = rt.launches
+        one_by_one = decoder.generate(prompts, 32)
+        stepped, launches = rt.launches - launches, rt.launches
+        chunked = decoder.generate(prompts, 32, chunked=True)
+        fed = rt.launches - launches
+    finally:
+        rt.close()
+    assert fed < stepped, "the chunks take fewer launches than the tokens one by one"
+    assert np.array_equal(chunked, one_by_one), "a prompt fed in chunks leaves the cache the decode steps leave"
+    differs = np.argwhere(chunked != want)
+    if differs.size:
+        b, at = differs[0]
+        pytest.fail(f"sequence {b} leaves the oracle at step {at}: {chunked[b, at]} for {want[b, at]}, "
+                    f"the oracle's margin there is {margins[b, at]:.3e}")
+
+
 def test_a_decoder_read_from_a_gguf_file_decodes_what_the_poured_tensors_decode(oracle, tmp_path):
     from neura_b200 import gguf
     from oracle.decoder import OracleDecoder, synthetic_model

@@ -48,6 +48,7 @@ def main() -> int:
         comm = parallel.TorchComm(world, rank, device=device, stream=stream)
     weights, dnorms = parallel.load_decoder_weights(rt, config, packed, norms, shard)
     decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=96, shard=shard, comm=comm)
+    decoder.fold = os.environ.get("TP_FOLD", "0") == "1"   # exchanges in the products' epilogues (the peer transport only)
     eager = decoder.generate(prompts, 64)
     decoder.record()
     replayed = decoder.generate(prompts, 64)
