@@ -32,6 +32,7 @@ extern "C" {
 #define NC_ELEMENT_BFLOAT16 2u
 #define NC_ELEMENT_Q8_0 8u
 #define NC_ELEMENT_Q4K 9u
+#define NC_ELEMENT_Q6K 11u /* heads and embeddings of common GGUF mixes: multiplied where the GGUF left it (NC_LAYOUT_GGUF) */
 
 /* How the blocks of a weight tensor are laid out in device memory. */
 #define NC_LAYOUT_GGUF 0u   /* verbatim GGUF: row after row, blocks in order (what store.rs:131-135 copies) */
@@ -72,7 +73,7 @@ typedef struct nc_context nc_context;
  * features (GGUF ne[1]), `k` input features (GGUF ne[0], contiguous inside a row). */
 typedef struct nc_weight {
     const void *data_dev;
-    uint32_t element; /* NC_ELEMENT_Q8_0 | NC_ELEMENT_Q4K */
+    uint32_t element; /* NC_ELEMENT_Q8_0 | NC_ELEMENT_Q4K | NC_ELEMENT_Q6K */
     uint32_t layout;  /* NC_LAYOUT_* */
     uint32_t n;
     uint32_t k;
@@ -166,7 +167,12 @@ int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, con
 /* run_matmul + chained (crates/neura-kernel/src/task/matmul.rs:376-517, pointwise.rs:90-104):
  *   out[r*out_stride + c] = chain(sum_k W[c][k] * x[r*x_stride + k]),  r < rows, c < w->n
  * f32 activations, f32 accumulation, f32 output (promote(Single, Q*) = Single, element.rs:306-323).
- * Needs a NC_LAYOUT_TILED weight. */
+ * A Q8_0 or Q4K weight is sealed (NC_LAYOUT_TILED, or a sealed pair); a Q6K weight stays in GGUF order.
+ * The kernel follows the row count the way the reference's planner picks its tiles (Product::planned,
+ * crates/neura-plan/src/product.rs:103-195): up to eight rows the streaming product (the reference's folded tiles),
+ * from nine rows on a Q4K weight takes the skinny tensor-core product that streams the weight once for up to 32 rows
+ * (its staged-run tiles), more rows go in passes.  The bf16 tensor path is neura_cuda_linear_bf16: the reference, too,
+ * takes its cooperative-matrix tiles only when asked to measure them (product.rs:109-113, 191-195). */
 int32_t neura_cuda_linear(nc_context *ctx, void *stream, const nc_weight *w, const float *x_dev, uint32_t rows,
                           uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
                           uint32_t n_steps);

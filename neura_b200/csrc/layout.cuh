@@ -17,6 +17,7 @@
 // and g+8, eight K values) with conflict-free 16-byte loads.
 #pragma once
 #include "common.cuh"
+#include "qlinear_rows.cuh"
 
 namespace nc {
 
@@ -48,6 +49,8 @@ __device__ __forceinline__ uint32_t weight_byte(const WeightView &w, uint32_t ro
 // One element of unpack: q8_0_values / q4_k_values (crates/neura-precision/src/ggml.rs:211-216,
 // :336-350).  Each product is rounded to f32 on its own (no fma), which is what makes it bit-exact.
 __device__ __forceinline__ float dequant_at(const WeightView &w, uint32_t row, uint32_t at) {
+    if (w.element == NC_ELEMENT_Q6K)   // kept in GGUF order only
+        return q6k_value(w.data + ((uint64_t)row * (w.k / kSuperBlock) + at / kSuperBlock) * kQ6kBytes, at % kSuperBlock);
     if (w.element == NC_ELEMENT_Q8_0) {
         const uint32_t blk = at / kQ8Block, lane = at % kQ8Block;
         const float quantum = half_bits_to_float(weight_byte(w, row, blk, 0) | (weight_byte(w, row, blk, 1) << 8));

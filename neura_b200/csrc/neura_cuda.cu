@@ -136,10 +136,10 @@ int32_t ensure(nc_context *ctx, Region &region, uint64_t bytes, bool zero) {
 }
 
 uint32_t block_elements(uint32_t element) {
-    return element == NC_ELEMENT_Q8_0 ? kQ8Block : element == NC_ELEMENT_Q4K ? kSuperBlock : 0;
+    return element == NC_ELEMENT_Q8_0 ? kQ8Block : element == NC_ELEMENT_Q4K || element == NC_ELEMENT_Q6K ? kSuperBlock : 0;
 }
 uint32_t block_bytes(uint32_t element) {
-    return element == NC_ELEMENT_Q8_0 ? kQ8Bytes : element == NC_ELEMENT_Q4K ? kQ4kBytes : 0;
+    return element == NC_ELEMENT_Q8_0 ? kQ8Bytes : element == NC_ELEMENT_Q4K ? kQ4kBytes : element == NC_ELEMENT_Q6K ? kQ6kBytes : 0;
 }
 
 struct GemvPlan {
@@ -235,13 +235,46 @@ int32_t check_weight(const nc_weight *w) {
     if (!w || !w->data_dev) return refuse(kBadArgument, "a product needs a weight on the device");
     const uint32_t per = block_elements(w->element);
     if (!per)
-        return refuse(kBadArgument, "element %u is not a block format this path multiplies (Q8_0 = 8, Q4K = 9)",
+        return refuse(kBadArgument, "element %u is not a block format this path multiplies (Q8_0 = 8, Q4K = 9, Q6K = 11)",
                       w->element);
     if (w->n == 0 || w->k == 0 || w->k % per)
         return refuse(kBadArgument, "a [%u, %u] weight does not fill whole blocks of %u along its rows", w->n,
                       w->k, per);
+    if (w->element == NC_ELEMENT_Q6K) {
+        if (w->layout != NC_LAYOUT_GGUF) return refuse(kBadArgument, "a Q6K weight is multiplied in GGUF order; it has no sealed layout");
+        return 0;
+    }
     if ((uintptr_t)w->data_dev % 16)
         return refuse(kBadArgument, "a weight starts on a 16-byte boundary");
+    return 0;
+}
+
+// The product of a Q6K weight (qlinear_rows.cuh): passes of up to eight rows.
+int32_t rows_product(nc_context *ctx, cudaStream_t stream, const nc_weight *w, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                     float *out_dev, uint64_t out_stride, const nc_step *chain, uint32_t n_steps) {
+    for (uint32_t first = 0; first < rows; first += kRowsKernelMost) {
+        RowsParams p;
+        memset(&p, 0, sizeof p);
+        p.w = (const uint8_t *)w->data_dev;
+        p.x = x_dev + (uint64_t)first * x_stride;
+        p.out = out_dev + (uint64_t)first * out_stride;
+        p.x_stride = x_stride;
+        p.out_stride = out_stride;
+        p.n = w->n;
+        p.k = w->k;
+        p.rows = std::min(kRowsKernelMost, rows - first);
+        p.chain.n = n_steps;
+        for (uint32_t s = 0; s < n_steps; ++s) {
+            p.chain.step[s] = chain[s];
+            if (chain[s].operand_dev) p.chain.step[s].operand_dev = chain[s].operand_dev + (int64_t)first * chain[s].row_stride;
+        }
+        const uint64_t want = ((uint64_t)w->n + 7) / 8;   // eight warps a CTA, a warp a weight row
+        const unsigned int blocks = (unsigned int)std::min<uint64_t>(want, (uint64_t)ctx->sms * 8);
+        void (*kernel)(RowsParams) = p.rows <= 1 ? qlinear_rows_q6k_kernel<1> : p.rows <= 2 ? qlinear_rows_q6k_kernel<2>
+                                     : p.rows <= 4 ? qlinear_rows_q6k_kernel<4> : qlinear_rows_q6k_kernel<8>;
+        NC_CUDA(launch_dependent(kernel, dim3(blocks), dim3(256), 0, stream, p));
+        ctx->launches++;
+    }
     return 0;
 }
 
@@ -689,8 +722,8 @@ static int32_t seal_any(nc_context *ctx, void *stream, uint32_t element, uint32_
                         const void *second_dev, void *dst_dev) {
     if (!ctx || !gguf_dev || !dst_dev) return refuse(kBadArgument, "seal needs a context, a source and a destination");
     const uint32_t per = block_elements(element);
-    if (!per || !n || !k || k % per)
-        return refuse(kBadArgument, "a [%u, %u] tensor of element %u is not whole blocks this path seals", n, k, element);
+    if (!per || !n || !k || k % per || element == NC_ELEMENT_Q6K)
+        return refuse(kBadArgument, "a [%u, %u] tensor of element %u is not whole blocks this path seals (a Q6K weight stays in GGUF order)", n, k, element);
     const uintptr_t align = element == NC_ELEMENT_Q4K ? 8 : 2;
     if ((uintptr_t)gguf_dev % align || (uintptr_t)second_dev % align || (uintptr_t)dst_dev % 16)
         return refuse(kBadArgument, "seal reads an 8-byte aligned tensor and writes a 16-byte aligned one");
@@ -750,6 +783,8 @@ int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, con
     if (!per || !elements || elements % per)
         return refuse(kBadArgument, "%llu numbers do not fill whole blocks of element %u",
                       (unsigned long long)elements, element);
+    if (element != NC_ELEMENT_Q8_0 && element != NC_ELEMENT_Q4K)
+        return refuse(kBadArgument, "the device packs Q8_0 and Q4K blocks, not element %u", element);
     if ((uintptr_t)dst_dev % 2 || (uintptr_t)src_dev % 4)
         return refuse(kBadArgument, "quantize reads 4-byte aligned numbers and writes 2-byte aligned blocks");
     const uint64_t blocks = elements / per;
@@ -767,9 +802,9 @@ int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, con
 int32_t neura_cuda_stage_window(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
                                 uint32_t k, uint32_t element, uint32_t lo, uint32_t hi) {
     if (!ctx || !x_dev) return refuse(kBadArgument, "staging needs a context and activations");
-    const uint32_t per = block_elements(element);
+    const uint32_t per = element == NC_ELEMENT_Q6K ? 0 : block_elements(element);   // (a Q6K product takes f32 rows as they are)
     if (!per || !k || k % per)
-        return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
+        return refuse(kBadArgument, "%u activations do not line up with blocks of element %u (Q8_0 or Q4K)", k, element);
     const uint32_t most = element == NC_ELEMENT_Q4K ? kSkMaxRows : kMaxRowsPerPass;
     if (rows == 0 || rows > most)
         return refuse(kBadArgument, "one staging holds 1 to %u rows of element %u, not %u", most, element, rows);
@@ -823,7 +858,8 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     int32_t rc;
     if ((rc = check_weight(w))) return rc;
     if (w->layout != NC_LAYOUT_TILED && w->layout != NC_LAYOUT_TILED_PAIR)
-        return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order");
+        return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order "
+                                    "(a Q6K weight takes neura_cuda_linear, which needs no staging)");
     const bool pair = w->layout == NC_LAYOUT_TILED_PAIR;
     // a pair is planned as the matrix of both tensors' rows, 16 of each per 32-row tile
     const uint32_t plan_n = pair ? (w->n + 15) / 16 * 32 : w->n;
@@ -996,6 +1032,13 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, co
     if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
+    if (w->element == NC_ELEMENT_Q6K) {
+        if (x_stride < w->k || out_stride < w->n)
+            return refuse(kBadArgument, "rows of %u activations and %u outputs overlap at strides %llu and %llu", w->k, w->n,
+                          (unsigned long long)x_stride, (unsigned long long)out_stride);
+        if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+        return rows_product(ctx, (cudaStream_t)stream_, w, x_dev, rows, x_stride, out_dev, out_stride, chain, n_steps);
+    }
     const uint32_t per = rows_per_pass(w->element, rows);
     for (uint32_t first = 0; first < rows; first += per) {
         const uint32_t pass = rows - first < per ? rows - first : per;
@@ -1092,7 +1135,7 @@ int32_t norm_stage_params(nc_context *ctx, const float *x_dev, uint32_t rows, ui
                           const float *weight_dev, float floor, uint32_t element, float *normed_dev,
                           uint64_t normed_stride, NormStageParams &p) {
     if (!ctx || !x_dev) return refuse(kBadArgument, "a norm needs a context and a row to norm");
-    const uint32_t per = block_elements(element);
+    const uint32_t per = element == NC_ELEMENT_Q6K ? 0 : block_elements(element);
     if (!per || !k || k % per)
         return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
     if (rows == 0 || rows > kMaxRowsPerPass)

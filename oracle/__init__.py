@@ -17,6 +17,7 @@ import numpy as np
 SINGLE = 0
 Q8_0 = 8
 Q4K = 9
+Q6K = 11
 
 # neura-pointwise op codes in declaration order (crates/neura-pointwise/src/op.rs:141-170)
 ADD, MUL, SUB, DIV, MAXIMUM, MINIMUM, RELU, SQRT, RECIP, EXP = range(10)

@@ -11,7 +11,7 @@
  * crates/neura-abi/tests/layout.rs:148-158, the Q4_K walk by three independent
  * restatements inside the reference, and by the published GGML layout).  The
  * *quantiser* (which nibble/int8 code a float becomes) is "parity unpinned":
- * the reference holds no known-answer test for Q8_0 or Q4_K bytes and cannot be
+ * the reference holds no known-answer test for Q8_0, Q4_K or Q6_K bytes and cannot be
  * compiled here (no Rust toolchain), so the quantiser follows the reference's
  * source by reading only.
  *
@@ -28,6 +28,7 @@
 #define NRO_SINGLE 0u
 #define NRO_Q8_0 8u /* crates/neura-abi/src/element.rs:3-17 (enum discriminants) */
 #define NRO_Q4K 9u
+#define NRO_Q6K 11u
 
 #define QUANT_BLOCK 32      /* element.rs:35 */
 #define SUPER_BLOCK 256     /* element.rs:36 */
@@ -35,6 +36,8 @@
 #define SUPER_SCALE_BYTES 12 /* element.rs:40 */
 #define Q8_0_BYTES 34       /* element.rs:155-158: 2 + 32 */
 #define Q4K_BYTES 144       /* element.rs:159-162: 4 + 12 + 128 */
+#define SUPER_SMALL_BLOCK 16 /* element.rs:38 */
+#define Q6K_BYTES 210       /* element.rs:167-170: 2 + 128 + 64 + 16 */
 
 /* ------------------------------------------------------------------ */
 /* IEEE binary16 <-> binary32, round-to-nearest-even, subnormals kept. */
@@ -128,6 +131,7 @@ int nro_block(uint32_t element, uint32_t *elements, uint32_t *bytes) {
     switch (element) {
     case NRO_Q8_0: *elements = QUANT_BLOCK; *bytes = Q8_0_BYTES; return 0;
     case NRO_Q4K: *elements = SUPER_BLOCK; *bytes = Q4K_BYTES; return 0;
+    case NRO_Q6K: *elements = SUPER_BLOCK; *bytes = Q6K_BYTES; return 0;
     default: return -1;
     }
 }
@@ -274,6 +278,63 @@ static void q4_k_decode(const uint8_t *field, float *out) {
     }
 }
 
+/* peak (ggml.rs:98-108): the largest magnitude of a run (the first to reach it wins) */
+static float peak_size(const float *values, int count) {
+    float size = 0.0f;
+    for (int i = 0; i < count; ++i)
+        if (size < fabsf(values[i])) size = fabsf(values[i]);
+    return size;
+}
+
+/* `(value / quantum).round().clamp(low, high) as u32` (ggml.rs:120-125) for a range that reaches below zero: Rust's
+ * float-to-unsigned cast saturates, so every negative quotient becomes 0.  (q6_k calls it with low = -32: a negative
+ * weight packs as code 0 + 32, which decodes as zero.  This file follows the reference, not the GGML quantiser.) */
+static uint32_t quantized_saturating(float value, float quantum, float low, float high) {
+    if (quantum == 0.0f) return 0;
+    float r = clampf(roundf(value / quantum), low, high);
+    return r <= 0.0f ? 0u : (uint32_t)r;
+}
+
+/* q6_k (ggml.rs:352-393): sixteen runs of 16 with an int8 scale each, six-bit codes biased by 32 */
+static void q6_k_encode(const float *values, uint8_t *field) {
+    const int sub = SUPER_SMALL_BLOCK, count = SUPER_BLOCK / SUPER_SMALL_BLOCK;
+    float factors[16];
+    for (int at = 0; at < count; ++at) factors[at] = peak_size(values + at * sub, sub) / 32.0f;
+    float scale = 0.0f;
+    for (int at = 0; at < count; ++at) scale = greatest(scale, fabsf(factors[at]));
+    scale = scale / 127.0f;
+    memset(field, 0, Q6K_BYTES);
+    put_half(field, 208, scale);
+    for (int at = 0; at < count; ++at) {
+        int8_t code = 0;
+        if (scale != 0.0f) code = (int8_t)clampf(roundf(factors[at] / scale), -127.0f, 127.0f);
+        field[192 + at] = (uint8_t)code;
+        float factor = scale * (float)code;
+        for (int within = 0; within < sub; ++within) {
+            int element = at * sub + within;
+            int half = element / 128, group = (element % 128) / 32, seat = element % 32;
+            uint32_t quant = quantized_saturating(values[element], factor, -32.0f, 31.0f) + 32u;
+            field[half * 64 + (group % 2) * 32 + seat] |= (uint8_t)((quant & 0x0fu) << (group >= 2 ? 4 : 0));
+            field[128 + half * 32 + seat] |= (uint8_t)(((quant >> 4) & 3u) << (2 * group));
+        }
+    }
+}
+
+/* q6_k_values (ggml.rs:395-407) */
+static void q6_k_decode(const uint8_t *field, float *out) {
+    float scale = half_at(field, 208);
+    int at = 0;
+    for (int seat = 0; seat < 2; ++seat)
+        for (int group = 0; group < 4; ++group)
+            for (int within = 0; within < SUPER_SUB_BLOCK; ++within) {
+                int index = group * 2 + within / 16;
+                int8_t sub = (int8_t)field[192 + seat * 8 + index];
+                uint8_t packed = field[seat * 64 + (group % 2) * 32 + within];
+                uint32_t quant = (group >= 2 ? packed >> 4 : packed & 0x0fu) | (((field[128 + seat * 32 + within] >> (2 * group)) & 3u) << 4);
+                out[at++] = scale * (float)sub * ((float)quant - 32.0f);
+            }
+}
+
 /* pack(): ggml.rs:8-20.  `out` must hold nro_packed_bytes(element, count). */
 int nro_pack(uint32_t element, const float *values, uint64_t count, uint8_t *out) {
     uint32_t per, bytes;
@@ -285,6 +346,7 @@ int nro_pack(uint32_t element, const float *values, uint64_t count, uint8_t *out
         uint64_t have = count - b * per < per ? count - b * per : per;
         memcpy(held, values + b * per, have * sizeof(float));
         if (element == NRO_Q8_0) q8_0_encode(held, out + b * bytes);
+        else if (element == NRO_Q6K) q6_k_encode(held, out + b * bytes);
         else q4_k_encode(held, out + b * bytes);
     }
     uint64_t end = blocks * bytes;
@@ -301,6 +363,7 @@ int nro_unpack(uint32_t element, uint64_t count, const uint8_t *bytes_in, float 
     for (uint64_t b = 0; b < blocks; ++b) {
         float held[SUPER_BLOCK];
         if (element == NRO_Q8_0) q8_0_decode(bytes_in + b * bytes, held);
+        else if (element == NRO_Q6K) q6_k_decode(bytes_in + b * bytes, held);
         else q4_k_decode(bytes_in + b * bytes, held);
         uint64_t have = count - b * per < per ? count - b * per : per;
         memcpy(out + b * per, held, have * sizeof(float));
@@ -348,6 +411,19 @@ float nro_fetch(uint32_t element, const uint8_t *heap, uint64_t at) {
         float a = half_at(heap + base, 0) * (float)ggml_k4_scale(heap, base + 4u, sub);
         float b = half_at(heap + base, 2) * (float)ggml_k4_min(heap, base + 4u, sub);
         return a * (float)quant - b;
+    }
+    if (element == NRO_Q6K) { /* fetch.rs:284-301 */
+        uint64_t base = at / SUPER_BLOCK * Q6K_BYTES;
+        uint32_t within = (uint32_t)(at % SUPER_BLOCK);
+        uint32_t half = within / 128u, seat = within % 128u;
+        uint32_t group = seat / SUPER_SUB_BLOCK, lane = seat % SUPER_SUB_BLOCK;
+        uint32_t packed = ggml_byte(heap, base + half * 64u + (group % 2u) * 32u + lane);
+        uint32_t low = group >= 2u ? packed >> 4 : packed & 0xfu;
+        uint32_t high = (ggml_byte(heap, base + 128u + half * 32u + lane) >> (2u * group)) & 3u;
+        uint32_t quant = low | (high << 4);
+        uint32_t scale = ggml_byte(heap, base + 192u + half * 8u + group * 2u + lane / 16u);
+        float signed_scale = (float)((int32_t)scale - (scale >= 128u ? 256 : 0));
+        return half_at(heap + base, 208) * signed_scale * ((float)quant - 32.0f);
     }
     return NAN;
 }

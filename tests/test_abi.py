@@ -37,6 +37,7 @@ def test_geometry_entry_points_need_no_device(lib):
     assert lib.neura_cuda_payload_bytes(9, 256) == 144
     assert lib.neura_cuda_payload_bytes(9, 18944 * 3584) == 38191104
     assert lib.neura_cuda_payload_bytes(0, 10) == 40
+    assert lib.neura_cuda_payload_bytes(11, 256) == 210        # Q6_K: heads and embeddings of common GGUF mixes
     assert lib.neura_cuda_payload_bytes(12, 256) == 0          # Q3_K is not on this path
     # sealing pads rows to tiles of 32 and keeps the block bytes
     assert lib.neura_cuda_sealed_bytes(9, 18944, 3584) == 38191104

@@ -217,3 +217,67 @@ def test_a_sealed_gate_up_pair_is_the_swiglu_of_the_two_products(runtime, oracle
     runtime.write(xd, x)
     runtime.linear(pair, xd, od)
     assert_close(runtime.read(od), expected, f"pair element {element} [{n},{k}] rows {rows}")
+
+
+def q6k_blocks(seed, n, k):
+    """Random Q6_K blocks with every code in use (the reference's own packer never writes a negative code) and a
+    finite d, as a real GGUF holds them."""
+    rng = np.random.default_rng(seed)
+    blocks = rng.integers(0, 256, (n * (k // 256), 210), dtype=np.uint8)
+    blocks[:, 208:210] = rng.uniform(-2e-3, 2e-3, blocks.shape[0]).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    return blocks.reshape(-1)
+
+
+@pytest.mark.parametrize("n,k", [(16, 256), (40, 512), (33, 1280), (1000, 5120)])
+def test_q6k_dequant_is_bit_exact(runtime, oracle, n, k):
+    for packed in (q6k_blocks(3, n, k), oracle.pack_rows(nb.Q6K, weights(oracle, nb.Q8_0, n, k, seed=9)[0])):
+        expected = oracle.unpack(nb.Q6K, n * k, packed).reshape(n, k)
+        held = runtime.load(nb.Q6K, n, k, packed)
+        assert held.layout == nb.LAYOUT_GGUF
+        assert np.array_equal(bits(runtime.dequant(held)), bits(expected))
+        runtime.free(held.ptr)
+
+
+@pytest.mark.parametrize("n,k", [(1, 256), (31, 768), (1000, 3584), (4099, 5120)])
+@pytest.mark.parametrize("rows", [1, 2, 3, 8, 19])
+def test_q6k_products_over_ragged_shapes(runtime, oracle, n, k, rows):
+    packed = q6k_blocks(11, n, k)
+    x = oracle.Stream(7).normal(rows * k).reshape(rows, k)
+    expected = oracle.linear(nb.Q6K, packed, n, k, x, threads=8)
+    w = runtime.load(nb.Q6K, n, k, packed)
+    assert_close(runtime.linear_host(w, x), expected, f"Q6_K [{n},{k}] rows {rows}")
+    runtime.free(w.ptr)
+
+
+def test_q6k_narrow_and_wide_products_of_the_reference_tests(runtime, oracle):
+    # crates/neura-runtime/tests/runtime.rs:12-144 run every GGML format, Q6_K among them: uniform(-1, 1) weights through
+    # the host packer, absolute 1e-3
+    for rows, depth, columns in ((1, 2048, 1024), (4, 2048, 1024), (8, 512, 4096)):
+        w, _ = weights(oracle, nb.Q8_0, columns, depth, seed=23)
+        packed = oracle.pack_rows(nb.Q6K, w)
+        x = oracle.random(rows * depth, 29).reshape(rows, depth)
+        expected = oracle.linear(nb.Q6K, packed, columns, depth, x, threads=8)
+        held = runtime.load(nb.Q6K, columns, depth, packed)
+        assert np.abs(runtime.linear_host(held, x) - expected).max() <= ABS_TOL
+        runtime.free(held.ptr)
+
+
+def test_q6k_product_applies_the_fused_chain_and_gathers_rows(runtime, oracle):
+    n, k, rows = 96, 512, 3
+    packed = q6k_blocks(13, n, k)
+    x = oracle.Stream(11).normal(rows * k).reshape(rows, k)
+    bias = oracle.Stream(17).normal(n)
+    expected = oracle.linear(nb.Q6K, packed, n, k, x, chain=[(oracle.ADD, bias), (oracle.SILU, None)])
+    w = runtime.load(nb.Q6K, n, k, packed)
+    xd, od, bd = runtime.tensor(rows, k), runtime.tensor(rows, n), runtime.tensor(n)
+    runtime.write(xd, x)
+    runtime.write(bd, bias)
+    runtime.linear(w, xd, od, [nb.Step(nb.ADD, bd), nb.Step(nb.SILU)])
+    assert_close(runtime.read(od), expected, "Q6_K chain")
+    # the embedding gather of a Q6_K table (select.rs:29-49 over fetch_q6_k)
+    tokens = runtime.tensor_u32(4)
+    runtime.write(tokens, np.array([5, 0, 95, 5], dtype=np.uint32))
+    rows_out = runtime.tensor(4, k)
+    runtime.embed(w, tokens, rows_out)
+    table = oracle.unpack(nb.Q6K, n * k, packed).reshape(n, k)
+    assert np.array_equal(bits(runtime.read(rows_out)), bits(table[[5, 0, 95, 5]]))

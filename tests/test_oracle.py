@@ -228,3 +228,55 @@ def test_golden_vectors_still_hold(oracle):
         assert np.allclose(oracle.linear(element, packed, n, k, x, chain=chain), golden[f"{name}_chain"], rtol=0, atol=1e-6)
     assert np.array_equal(oracle.pack_rows(oracle.Q8_0, golden["edge_weight"]), golden["edge_q8_0"])
     assert np.array_equal(oracle.pack_rows(oracle.Q4K, golden["edge_weight"]), golden["edge_q4k"])
+
+
+def q6k_numpy(blocks):
+    """An independent restatement of the published GGML Q6_K layout for [count, 210] bytes: ql 128, qh 64, int8 scales
+    16, d; numbers 128 half + 32 group + lane."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 210)
+    ql, qh = blocks[:, :128].astype(np.int32), blocks[:, 128:192].astype(np.int32)
+    scales = blocks[:, 192:208].view(np.int8).astype(np.float32)
+    d = blocks[:, 208:210].copy().view(np.float16).astype(np.float32)[:, 0]
+    out = np.zeros((blocks.shape[0], 256), dtype=np.float32)
+    for half in range(2):
+        for group in range(4):
+            low = ql[:, half * 64 + (group % 2) * 32: half * 64 + (group % 2) * 32 + 32]
+            low = (low >> 4) if group >= 2 else (low & 15)
+            high = (qh[:, half * 32: half * 32 + 32] >> (2 * group)) & 3
+            code = (low | (high << 4)).astype(np.float32) - np.float32(32.0)
+            scale = np.repeat(scales[:, half * 8 + group * 2: half * 8 + group * 2 + 2], 16, axis=1)
+            out[:, half * 128 + group * 32: half * 128 + group * 32 + 32] = (d[:, None] * scale) * code
+    return out
+
+
+def test_the_q6k_walk_agrees_across_restatements(oracle):
+    # crates/neura-abi/tests/layout.rs:150 pins 256 -> 210 bytes; the walk is stated in ggml.rs:395-407 and fetch.rs:284-301
+    assert oracle.payload_bytes(oracle.Q6K, 256) == 210 and oracle.payload_bytes(oracle.Q6K, 257) == 420
+    rng = np.random.default_rng(7)
+    blocks = rng.integers(0, 256, (64, 210), dtype=np.uint8)
+    blocks[:, 208:210] = rng.uniform(-0.01, 0.01, 64).astype(np.float16).view(np.uint8).reshape(64, 2)   # finite d
+    packed = blocks.reshape(-1)
+    unpacked = oracle.unpack(oracle.Q6K, 64 * 256, packed)
+    assert np.array_equal(bits(unpacked), bits(q6k_numpy(blocks).reshape(-1)))
+    lib = oracle.lib()
+    fetched = np.array([lib.nro_fetch(oracle.Q6K, packed.ctypes.data, at) for at in range(0, 64 * 256, 5)], dtype=np.float32)
+    assert np.array_equal(bits(fetched), bits(unpacked[::5]))
+
+
+def test_the_q6k_packer_follows_the_reference_to_the_letter(oracle):
+    # ggml.rs:352-393.  The sub-block scale comes from the largest magnitude; `quantized(..., -32, 31) as u32` saturates
+    # at zero, so what the reference's packer keeps of a negative number is code 32, i.e. zero.
+    w = oracle.Stream(5).normal(4 * 512, 0.0, 0.02).reshape(4, 512)
+    packed = oracle.pack_rows(oracle.Q6K, w)
+    assert packed.size == 4 * 2 * 210
+    back = oracle.unpack(oracle.Q6K, w.size, packed).reshape(w.shape)
+    assert np.all(back[w < 0] == 0.0)
+    step = np.abs(w).reshape(4, 32, 16).max(axis=2, keepdims=True) / 32.0
+    err = np.abs(back - w).reshape(4, 32, 16)
+    keep = (w > 0).reshape(4, 32, 16)
+    # half a step inside the range; a whole step at the run's own peak, whose quotient 32 is clamped to 31; and the
+    # run's factor is itself rounded to an int8 multiple of the block's scale
+    assert np.all(err[keep] <= (np.broadcast_to(step, err.shape)[keep] * 1.1 + 2e-4))
+    # a block of zeros: every code is the bias 32 (high bits 10 in all four groups), scales and d are zero; 210 bytes
+    # padded to whole words
+    assert oracle.pack(oracle.Q6K, np.zeros(256, np.float32)).tolist() == [0] * 128 + [170] * 64 + [0] * 20
