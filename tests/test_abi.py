@@ -75,3 +75,47 @@ def test_model_shapes_count_the_bytes_the_baseline_names():
     assert qwen.QWEN25_32B_Q4K.weight_bytes() == 17991106560
     assert qwen.QWEN25_05B_Q8.weight_elements() == 493961216
     assert qwen.QWEN25_05B_Q8.weight_bytes() == 524833792
+
+
+def header_signatures():
+    """name -> number of parameters, for every entry point the header declares."""
+    with open(os.path.join(ROOT, "include", "neura_cuda.h")) as fh:
+        text = re.sub(r"/\*.*?\*/", "", fh.read(), flags=re.S)
+    found = {}
+    for name, args in re.findall(r"\b(neura_cuda_\w+)\s*\(([^;{]*?)\)\s*;", text):
+        args = args.strip()
+        found[name] = 0 if args == "void" else args.count(",") + 1
+    return found
+
+
+def test_the_rust_binding_declares_every_entry_point_with_the_headers_arity():
+    # crates/neura-cuda/src/sys.rs is what a Rust host links against; no Rust toolchain is here to compile it, so its
+    # declarations are checked against the header: the same names, the same number of parameters, nothing extra
+    with open(os.path.join(ROOT, "crates", "neura-cuda", "src", "sys.rs")) as fh:
+        text = fh.read()
+    declared = {}
+    for name, args in re.findall(r"pub fn (neura_cuda_\w+)\(([^)]*)\)", text):
+        args = args.strip()
+        declared[name] = 0 if not args else args.count(",") + 1
+    header = header_signatures()
+    assert len(header) >= 50
+    assert declared == header
+    # the structs that cross the boundary by value or by pointer keep the header's fields, in order
+    with open(os.path.join(ROOT, "include", "neura_cuda.h")) as fh:
+        c_text = re.sub(r"/\*.*?\*/", "", fh.read(), flags=re.S)
+    for c_name, rust_name in (("nc_weight", "NcWeight"), ("nc_step", "NcStep"), ("nc_then", "NcThen"),
+                              ("nc_decoder_layer", "NcDecoderLayer"), ("nc_decoder_desc", "NcDecoderDesc")):
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (c_name, c_name), c_text, flags=re.S).group(1)
+        c_fields = []
+        for statement in body.split(";"):
+            statement = statement.strip()
+            if statement:
+                c_fields += [re.sub(r"[\s\*]", "", part).split(" ")[-1] for part in
+                             re.sub(r"^(const\s+)?\w+\s+", "", statement).split(",")]
+        rust_body = re.search(r"pub struct %s \{(.*?)\n\}" % rust_name, text, flags=re.S).group(1)
+        rust_fields = re.findall(r"pub (\w+):", rust_body)
+        assert rust_fields == c_fields, f"{rust_name} and {c_name} disagree"
+    # and the safe wrapper uses nothing the binding does not declare
+    with open(os.path.join(ROOT, "crates", "neura-cuda", "src", "lib.rs")) as fh:
+        used = set(re.findall(r"sys::(neura_cuda_\w+)", fh.read()))
+    assert used and used <= set(declared)
