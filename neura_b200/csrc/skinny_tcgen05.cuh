@@ -23,8 +23,8 @@
 //     like the activations.  They accumulate into a third accumulator that is read once per item.
 //
 // Roles of a CTA (one per SM, persistent over (128-row tile, K slice) items):
-//   warps 0-15  producers, a thread per (weight row, eight quant bytes of a 64-k step): wait for a super-block of raw
-//               units in the raw ring, turn nibbles into sc * q (two weights per instruction: the nibble is or-ed into
+//   warps 0-15  producers, a thread per (two weight rows, eight quant bytes of each 64-k step), eight warps for each of
+//               the two stages of a super-block: wait for a super-block of raw units in the raw ring, turn nibbles into sc * q (two weights per instruction: the nibble is or-ed into
 //               the mantissa of 1024, one HFMA2 multiplies by sc and takes the 1024 sc away; the four half-float
 //               constants of a scale come from a 64-entry table in shared memory) and store them 128-byte swizzled,
 //               K-major, into the A tiles of a ring stage;
@@ -294,22 +294,26 @@ __device__ __forceinline__ uint2 lds8(uint32_t addr) {
     return v;
 }
 
-// One weight row's 64 k of a step: its eight quant bytes (w0, w1) hold elements 8t.. of sub-block 2G in their low
-// nibbles and of sub-block 2G+1 in their high nibbles; `lo` = (sc, sc | -1024 sc, -1024 sc) of sub-block 2G and `hi` =
-// (sc / 16 twice | -64 sc twice) of sub-block 2G+1 as pairs of half floats (the scale table's entries).  `at_lo` and
-// `at_hi` are the shared-memory addresses of the row's two 16-byte chunks.
+// One weight row's 64 k of a step.  Its eight quant bytes (w0, w1) hold elements 8t.. of sub-block 2G in their low
+// nibbles and of sub-block 2G+1 in their high nibbles.  The row stores two 16-byte chunks; which nibble kind goes first
+// depends on the row's parity (`first_mask` 0x000f000f: the low nibbles, 0x00f000f0: the high ones; `first` and `second`
+// the half-float constants of their sub-blocks' scales from the scale table; `at_first`, `at_second` the chunks'
+// addresses): an even and an odd row of the eight lanes that store together then cover all eight 16-byte columns of a
+// 128-byte line, where both rows' low chunks would land on the same four.
+//   low nibbles:            (1024 + q) * sc - 1024 sc          (entry halves (sc, sc), (-1024 sc, -1024 sc))
+//   high nibbles, in place: (1024 + 16 q) * (sc / 16) - 64 sc  (entry halves (sc / 16) x 2, (-64 sc) x 2)
 // A mask and an or turn the nibbles of bytes 0 and 2 of a word into two half floats at once (bytes 1 and 3 after a
 // shift), so the eight elements of a chunk are stored in the order 0 2 1 3 4 6 5 7; the activation staging stores its
 // chunks in the same order (kSkChunkOrder), and a dot product does not mind.
-__device__ __forceinline__ void skinny_row_step(uint32_t at_lo, uint32_t at_hi, uint32_t w0, uint32_t w1, uint2 lo, uint2 hi) {
-    // low nibbles: (1024 + q) * sc - 1024 sc;  high nibbles in place: (1024 + 16 q) * (sc / 16) - 64 sc
+__device__ __forceinline__ void skinny_row_step(uint32_t at_first, uint32_t at_second, uint32_t w0, uint32_t w1, uint2 first, uint2 second,
+                                                uint32_t first_mask, uint32_t second_mask) {
     const uint32_t s0 = w0 >> 8, s1 = w1 >> 8;
-    const uint32_t l0 = hfma2_bits((w0 & 0x000f000fu) | 0x64006400u, lo.x, lo.y), l1 = hfma2_bits((s0 & 0x000f000fu) | 0x64006400u, lo.x, lo.y);
-    const uint32_t l2 = hfma2_bits((w1 & 0x000f000fu) | 0x64006400u, lo.x, lo.y), l3 = hfma2_bits((s1 & 0x000f000fu) | 0x64006400u, lo.x, lo.y);
-    const uint32_t h0 = hfma2_bits((w0 & 0x00f000f0u) | 0x64006400u, hi.x, hi.y), h1 = hfma2_bits((s0 & 0x00f000f0u) | 0x64006400u, hi.x, hi.y);
-    const uint32_t h2 = hfma2_bits((w1 & 0x00f000f0u) | 0x64006400u, hi.x, hi.y), h3 = hfma2_bits((s1 & 0x00f000f0u) | 0x64006400u, hi.x, hi.y);
-    sts16(at_lo, l0, l1, l2, l3);
-    sts16(at_hi, h0, h1, h2, h3);
+    const uint32_t a0 = hfma2_bits((w0 & first_mask) | 0x64006400u, first.x, first.y), a1 = hfma2_bits((s0 & first_mask) | 0x64006400u, first.x, first.y);
+    const uint32_t a2 = hfma2_bits((w1 & first_mask) | 0x64006400u, first.x, first.y), a3 = hfma2_bits((s1 & first_mask) | 0x64006400u, first.x, first.y);
+    const uint32_t b0 = hfma2_bits((w0 & second_mask) | 0x64006400u, second.x, second.y), b1 = hfma2_bits((s0 & second_mask) | 0x64006400u, second.x, second.y);
+    const uint32_t b2 = hfma2_bits((w1 & second_mask) | 0x64006400u, second.x, second.y), b3 = hfma2_bits((s1 & second_mask) | 0x64006400u, second.x, second.y);
+    sts16(at_first, a0, a1, a2, a3);
+    sts16(at_second, b0, b1, b2, b3);
 }
 
 // The byte of sub-block `sub` out of the two words q4k_scales returns.
@@ -377,7 +381,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     if (tid == 0) {
         failed = 0;
         for (uint32_t s = 0; s < kSkStages; ++s) {
-            mbar_init(a_full + 8 * s, kSkProducerWarps);   // every producer warp
+            mbar_init(a_full + 8 * s, kSkProducerWarps / 2);   // the eight producer warps that write the stage
             mbar_init(a_empty + 8 * s, 1);                 // one tcgen05.commit
         }
         for (uint32_t s = 0; s < kXStages; ++s) {
@@ -406,12 +410,20 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
 
     if (warp < kSkProducerWarps) {
         // ---------------- producers: raw units -> sc * q tiles ----------------
-        // warp w serves half-unit w / 2 (16 weight rows); its lanes (g, t) take row g (w even) or g + 8 (w odd)
-        const uint32_t g = lane >> 2, t = lane & 3, upper = warp & 1u;
-        const uint32_t row = (warp >> 1) * 16 + g + 8 * upper;
+        // Warp w serves half-unit w / 2 (rows g and g + 8 of its 16, lane (g, t)) and, of every super-block, the 128-k
+        // stage w % 2: the two stages of a super-block are written side by side by two sets of eight warps.  Ring
+        // positions are counted over the whole launch: the stages of super-block i of an item sit at base + 2 i and
+        // base + 2 i + 1, the stages of the second sum follow them.
+        const uint32_t g = lane >> 2, t = lane & 3, mine = warp & 1u, hu = warp >> 1;
+        const uint32_t row = hu * 16 + g, turn = row & 7, odd = row & 1u;   // (row + 8 has the same parity and turn)
         const uint32_t table = smem_addr(scale_table);
-        const uint32_t chunk_lo = row * 128 + ((t ^ (row & 7)) << 4), chunk_hi = row * 128 + (((4 + t) ^ (row & 7)) << 4);
-        SkRing at_raw, at_a;
+        // per thread, once: which nibble kind it stores first (see skinny_row_step)
+        const uint32_t first_mask = odd ? 0x00f000f0u : 0x000f000fu, second_mask = odd ? 0x000f000fu : 0x00f000f0u;
+        const uint32_t first_sub = odd, second_sub = odd ^ 1u;              // sub-block 2G + ... of the first / second chunk
+        const uint32_t first_half = odd * 8, second_half = (odd ^ 1u) * 8;  // the table entry's half: low or high nibble form
+        const uint32_t at_first = row * 128 + (((odd ? 4 + t : t) ^ turn) << 4), at_second = row * 128 + (((odd ? t : 4 + t) ^ turn) << 4);
+        uint32_t base = 0;   // ring position of the running item's first stage
+        SkRing at_raw;
         bool alive = true;
         uint32_t events = 0;
         for (uint32_t item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
@@ -420,63 +432,71 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
             for (uint32_t sb = sb0; sb < sb1 && alive; ++sb) {
                 if (!mbar_wait(raw_full + 8 * at_raw.s, at_raw.phase)) { alive = false; break; }
                 if (tid == 0) { SK_TRACE(0, events); }
-                const uint32_t half_unit = raw + at_raw.s * kSkRawStage + (warp >> 1) * kQ4kUnit;
-                const uint4 header = lds16(half_unit + (g + 8 * upper) * 16);
-                uint2 q[4];
-#pragma unroll
-                for (int G = 0; G < 4; ++G) q[G] = lds8(half_unit + 256 + G * 512 + lane * 16 + upper * 8);
+                const uint32_t half_unit = raw + at_raw.s * kSkRawStage + hu * kQ4kUnit;
+                const uint4 h0 = lds16(half_unit + g * 16), h1 = lds16(half_unit + (g + 8) * 16);
+                const uint4 q0 = lds16(half_unit + 256 + (2 * mine) * 512 + lane * 16), q1 = lds16(half_unit + 256 + (2 * mine + 1) * 512 + lane * 16);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(raw_empty + 8 * at_raw.s);
                 at_raw.next(kSkRawStages);
-                uint32_t sc[2], mn[2];
-                q4k_scales(header.y, header.z, header.w, sc, mn);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint2 lo0 = lds8(table + k4_byte(sc, 4 * h) * 16), hi0 = lds8(table + k4_byte(sc, 4 * h + 1) * 16 + 8);
-                    const uint2 lo1 = lds8(table + k4_byte(sc, 4 * h + 2) * 16), hi1 = lds8(table + k4_byte(sc, 4 * h + 3) * 16 + 8);
-                    if (!SK_WAIT_A(a_empty + 8 * at_a.s, at_a.phase ^ 1u)) { alive = false; break; }
-                    if (tid == 0) { SK_TRACE(1, events * 2 + h); }
-                    const uint32_t stage = ring + at_a.s * kSkStageBytes;
-                    skinny_row_step(stage + chunk_lo, stage + chunk_hi, q[2 * h].x, q[2 * h].y, lo0, hi0);
-                    if (tid == 0) { SK_TRACE(5, events * 2 + h); }
-                    skinny_row_step(stage + kSkATile + chunk_lo, stage + kSkATile + chunk_hi, q[2 * h + 1].x, q[2 * h + 1].y, lo1, hi1);
-                    if (tid == 0) { SK_TRACE(8, events * 2 + h); }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tiles through the async proxy
-                    if (tid == 0) { SK_TRACE(9, events * 2 + h); }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(a_full + 8 * at_a.s);
-                    if (tid == 0) { SK_TRACE(2, events * 2 + h); }
-                    at_a.next(kSkStages);
-                }
+                uint32_t sc0[2], mn0[2], sc1[2], mn1[2];
+                q4k_scales(h0.y, h0.z, h0.w, sc0, mn0);
+                q4k_scales(h1.y, h1.z, h1.w, sc1, mn1);
+                const uint32_t G = 2 * mine;   // this warp's two 64-k tiles of the super-block: nibble groups G and G + 1
+                const uint2 f00 = lds8(table + k4_byte(sc0, 2 * G + first_sub) * 16 + first_half), s00 = lds8(table + k4_byte(sc0, 2 * G + second_sub) * 16 + second_half);
+                const uint2 f01 = lds8(table + k4_byte(sc0, 2 * G + 2 + first_sub) * 16 + first_half), s01 = lds8(table + k4_byte(sc0, 2 * G + 2 + second_sub) * 16 + second_half);
+                const uint2 f10 = lds8(table + k4_byte(sc1, 2 * G + first_sub) * 16 + first_half), s10 = lds8(table + k4_byte(sc1, 2 * G + second_sub) * 16 + second_half);
+                const uint2 f11 = lds8(table + k4_byte(sc1, 2 * G + 2 + first_sub) * 16 + first_half), s11 = lds8(table + k4_byte(sc1, 2 * G + 2 + second_sub) * 16 + second_half);
+                const uint32_t position = base + 2 * (sb - sb0) + mine, slot_a = position % kSkStages;
+                if (!SK_WAIT_A(a_empty + 8 * slot_a, ((position / kSkStages) & 1u) ^ 1u)) { alive = false; break; }
+                if (tid == 0) { SK_TRACE(1, events); }
+                const uint32_t stage = ring + slot_a * kSkStageBytes;
+                skinny_row_step(stage + at_first, stage + at_second, q0.x, q0.y, f00, s00, first_mask, second_mask);
+                skinny_row_step(stage + at_first + 1024, stage + at_second + 1024, q0.z, q0.w, f10, s10, first_mask, second_mask);
+                if (tid == 0) { SK_TRACE(5, events); }
+                skinny_row_step(stage + kSkATile + at_first, stage + kSkATile + at_second, q1.x, q1.y, f01, s01, first_mask, second_mask);
+                skinny_row_step(stage + kSkATile + at_first + 1024, stage + kSkATile + at_second + 1024, q1.z, q1.w, f11, s11, first_mask, second_mask);
+                if (tid == 0) { SK_TRACE(8, events); }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tiles through the async proxy
+                if (tid == 0) { SK_TRACE(9, events); }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(a_full + 8 * slot_a);
+                if (tid == 0) { SK_TRACE(2, events); }
                 ++events;
             }
             if (!alive) break;
-            // ---- the second sum: dmin * m of eight super-blocks a stage, this thread's row, super-block 4 j + t of the stage ----
+            base += 2 * (sb1 - sb0);
+            // ---- the second sum: dmin * m of eight super-blocks a stage; this thread's two rows, super-block 4 j + t of the stage ----
             const uint32_t held = min(tile * 4 + (row >> 5), p.tiles32 - 1);
             const uint8_t *headers = p.w + ((uint64_t)held * p.nsb * 2 + ((row >> 4) & 1u)) * kQ4kUnit + (row & 15) * 16;
-            for (uint32_t first = sb0; first < sb1 && alive; first += 8) {
-                uint4 h[2];
+            for (uint32_t first = sb0; first < sb1 && alive; first += 8, ++base) {
+                if ((base & 1u) != mine) continue;   // the stages of the second sum go to the two sets of warps in turn
+                uint4 h[2][2];
 #pragma unroll
                 for (uint32_t j = 0; j < 2; ++j) {
                     const uint32_t sb = first + 4 * j + t;
-                    h[j] = sb < sb1 ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit) : make_uint4(0u, 0u, 0u, 0u);
+                    const bool there = sb < sb1;
+                    h[j][0] = there ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit) : make_uint4(0u, 0u, 0u, 0u);
+                    h[j][1] = there ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit + 128) : make_uint4(0u, 0u, 0u, 0u);   // row + 8
                 }
-                if (!mbar_wait(a_empty + 8 * at_a.s, at_a.phase ^ 1u)) { alive = false; break; }
-                const uint32_t stage = ring + at_a.s * kSkStageBytes;
+                const uint32_t slot_a = base % kSkStages;
+                if (!SK_WAIT_A(a_empty + 8 * slot_a, ((base / kSkStages) & 1u) ^ 1u)) { alive = false; break; }
+                const uint32_t stage = ring + slot_a * kSkStageBytes;
 #pragma unroll
                 for (uint32_t j = 0; j < 2; ++j) {
-                    uint32_t sc[2], mn[2];
-                    q4k_scales(h[j].y, h[j].z, h[j].w, sc, mn);
-                    const float dmin = half_bits_to_float(h[j].x >> 16);   // (a super-block past the slice reads as zeros)
-                    const uint4 c0 = skinny_min_chunk(dmin, mn[0]), c1 = skinny_min_chunk(dmin, mn[1]);
-                    const uint32_t at = stage + j * kSkATile + row * 128, turn = row & 7;
-                    sts16(at + (((2 * t) ^ turn) << 4), c0.x, c0.y, c0.z, c0.w);
-                    sts16(at + (((2 * t + 1) ^ turn) << 4), c1.x, c1.y, c1.z, c1.w);
+#pragma unroll
+                    for (uint32_t r = 0; r < 2; ++r) {
+                        uint32_t sc[2], mn[2];
+                        q4k_scales(h[j][r].y, h[j][r].z, h[j][r].w, sc, mn);
+                        const float dmin = half_bits_to_float(h[j][r].x >> 16);   // (a super-block past the slice reads as zeros)
+                        const uint4 c0 = skinny_min_chunk(dmin, mn[0]), c1 = skinny_min_chunk(dmin, mn[1]);
+                        const uint32_t at = stage + j * kSkATile + (row + 8 * r) * 128;
+                        sts16(at + (((2 * t) ^ turn) << 4), c0.x, c0.y, c0.z, c0.w);
+                        sts16(at + (((2 * t + 1) ^ turn) << 4), c1.x, c1.y, c1.z, c1.w);
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(a_full + 8 * at_a.s);
-                at_a.next(kSkStages);
+                if (lane == 0) mbar_arrive(a_full + 8 * slot_a);
             }
         }
         if (!alive) failed = 1;
