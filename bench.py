@@ -447,7 +447,7 @@ def run_ours(args):
     # the prompt: random token ids; in chunks where the decoder fills in chunks, else one position at a time
     prompts = np.random.default_rng(29).integers(0, config.vocab, (rows, args.prompt), dtype=np.uint32)
     decoder.reset()
-    persistent = world == 1 and rows <= 2 and args.step == "persistent" and shard is None
+    persistent = rows <= 2 and args.step == "persistent" and ((world == 1 and shard is None) or (world > 1 and args.comm == "peer"))
     if decoder.chunks:
         decoder.prefill(prompts)
         fed = args.prompt - 1
@@ -543,10 +543,12 @@ def run_ours(args):
         # payload_bytes(N*K) + 4*B*K + 4*B*N each (the KV cache it also reads is left out)
         shapes = [(nn, kk) for _, nn, kk in config.linears()] * config.layers + [(config.vocab, config.hidden)]
         algorithmic = sum(nb.payload_bytes(config.element, nn * kk) + 4 * rows * (nn + kk) for nn, kk in shapes)
+        if shard is not None:   # a rank streams its shares only
+            algorithmic = shard.local_bytes_per_token()
         kernel_ms = ms / args.steps
         achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
         kernel_name = f"decode_megakernel<{tag}>: the whole step ({config.layers} layers + head) as one cooperative launch at batch {rows}"
-        traffic = recorded_traffic(f"decode_megakernel<{tag}> {config.name} b{rows}")
+        traffic = recorded_traffic(f"decode_megakernel<{tag}> {config.name} b{rows}") if shard is None else None
     secondary = None
     if world == 1 and shard is None and not persistent and not args.no_secondary and rows == 1:
         secondary = secondary_lines(rt, torch, tstream, device, peaks, weights, norms, config, args)

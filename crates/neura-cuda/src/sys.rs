@@ -162,6 +162,7 @@ extern "C" {
     pub fn neura_cuda_program_run(ctx: *mut NcContext, stream: *mut c_void, program: *mut NcProgram) -> i32;
     pub fn neura_cuda_program_free(ctx: *mut NcContext, program: *mut NcProgram) -> i32;
     pub fn neura_cuda_decoder_compile(ctx: *mut NcContext, desc: *const NcDecoderDesc, out: *mut *mut NcDecoder) -> i32;
+    pub fn neura_cuda_decoder_compile_rank(ctx: *mut NcContext, desc: *const NcDecoderDesc, comm: *mut NcComm, world: u32, rank: u32, out: *mut *mut NcDecoder) -> i32;
     pub fn neura_cuda_decoder_step(ctx: *mut NcContext, stream: *mut c_void, decoder: *mut NcDecoder) -> i32;
     pub fn neura_cuda_decoder_free(ctx: *mut NcContext, decoder: *mut NcDecoder) -> i32;
     pub fn neura_cuda_decoder_trace(ctx: *mut NcContext, decoder: *mut NcDecoder, capacity: u32, kinds_out: *mut u32, nanos_out: *mut u64, phases_out: *mut u32) -> i32;

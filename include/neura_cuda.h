@@ -419,6 +419,17 @@ typedef struct nc_decoder_desc {
 
 typedef struct nc_decoder nc_decoder;
 int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc, nc_decoder **out);
+/* The same for rank `rank` of a tensor-parallel group of `world` devices (no counterpart in the reference, which
+ * runs on one device).  `desc` describes the rank's shares: heads, key_heads, feed_forward and vocab are the
+ * rank's (the head holds rows [rank, rank + 1) * vocab of the group's vocabulary, the embedding all vocab * world
+ * rows); attn_output and down keep the whole blocks that cover the rank's share of their K axes.  The output and
+ * down products add the ranks' partial sums up inside the step (the exchange of neura_cuda_linear_staged_fused,
+ * plain peer stores, bounded waits), rank 0 carries the residual, and a last phase picks among the ranks' argmax
+ * winners, so every rank leaves the same token ids in tokens_dev.  `comm` is connected, holds batch * hidden numbers
+ * and serves no other call while a step runs.  A wait that runs out raises the status word (neura_cuda_sync
+ * reports it) and ends the step at its next barrier. */
+int32_t neura_cuda_decoder_compile_rank(nc_context *ctx, const nc_decoder_desc *desc, nc_comm *comm, uint32_t world,
+                                        uint32_t rank, nc_decoder **out);
 int32_t neura_cuda_decoder_step(nc_context *ctx, void *stream, nc_decoder *decoder);
 int32_t neura_cuda_decoder_free(nc_context *ctx, nc_decoder *decoder);
 

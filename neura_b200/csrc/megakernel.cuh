@@ -34,10 +34,11 @@ constexpr uint32_t kMkSmem = kMkRing + kMkBars + kMkPatch;
 constexpr uint32_t kMkTile = 64;                              // cached positions one attention item takes
 constexpr uint32_t kMkNone = 0xffffffffu;
 
-enum : uint32_t { MK_EMBED = 1, MK_GEMV = 2, MK_ATTEND = 3, MK_STAGE = 4, MK_ARGMAX = 5 };
+enum : uint32_t { MK_EMBED = 1, MK_GEMV = 2, MK_ATTEND = 3, MK_STAGE = 4, MK_ARGMAX = 5, MK_CHOOSE = 6 };
 
 struct MkPhase {
-    uint32_t kind, flags;
+    uint32_t kind;
+    uint32_t flags;          // MK_ARGMAX: 1 = leave the rows' winners for an MK_CHOOSE phase instead of writing the tokens
     uint32_t prefetch;       // the product whose first copies are issued when this phase ends, or kMkNone
     uint32_t k;              // columns of the input rows
     GemvParams g;            // MK_GEMV (dig, cs, sums: the staged input rows)
@@ -73,6 +74,8 @@ struct MkParams {
     float *slice_value;          // [rows][gridDim.x]
     uint32_t *slice_index;
     unsigned int *argmax_counters;  // [rows], zero between launches
+    float *best_value;           // [rows]: this rank's winners, for the phase that picks among the ranks'
+    uint32_t *best_index;
     unsigned long long *trace;   // [nphases + 1]: %globaltimer as CTA 0 enters each phase, and as it leaves the last
 };
 
@@ -110,6 +113,9 @@ __device__ __forceinline__ bool mk_barrier(const MkParams &p, uint32_t epoch, vo
             }
         }
         __threadfence();
+        // a phase that gave up (a copy that never landed, a peer that never answered) has raised the status word:
+        // what follows would compute on rows that are not there
+        if (__ldcg(p.status)) *aborted = 1u;
     }
     __syncthreads();
     return *aborted == 0u;
@@ -422,11 +428,14 @@ __device__ __forceinline__ void mk_attend_item(const MkParams &p, const MkPhase 
             // the heads of this key head are columns [kh, kh + 1) * group * WIDTH of the row the output product
             // multiplies: count this arrival on the 256-column chunks they touch; whoever completes a chunk stages it
             __syncthreads();
+            // (on a rank of a tensor-parallel group the row sits at [lo, hi) of the axis of K, see StageAfter)
             const StageAfter &a = ph.after;
-            const uint32_t span = group * WIDTH, chunks = (a.prep.k + 255) / 256;
-            const uint32_t c0 = kh * span / 256, c1 = ((kh + 1) * span - 1) / 256;
+            const uint32_t span = group * WIDTH, chunks = (a.prep.k + 255) / 256, lo = a.prep.lo;
+            const uint32_t c0 = (lo + kh * span) / 256, c1 = (lo + (kh + 1) * span - 1) / 256;
             for (uint32_t c = c0 + warp; c <= c1; c += warps) {
-                const uint32_t expected = (min(a.prep.k, (c + 1) * 256) - 1) / span - c * 256 / span + 1;
+                // the key heads whose columns reach into chunk c
+                const uint32_t from = max(c * 256, lo) - lo, upto = min(a.prep.hi, (c + 1) * 256) - lo;
+                const uint32_t expected = (upto - 1) / span - from / span + 1;
                 unsigned int seen = 0;
                 if (lane == 0) {
                     seen = arrive_on(a.counters + b * chunks + c);
@@ -515,10 +524,50 @@ __device__ __forceinline__ void mk_argmax(const MkParams &p, const MkPhase &ph, 
             for (int o = 16; o; o >>= 1)
                 argmax_take(value, index, __shfl_xor_sync(0xffffffffu, value, o), __shfl_xor_sync(0xffffffffu, index, o));
             if (lane == 0) {
-                p.tokens[row] = index == 0xffffffffu ? 0u : index;
-                p.position[row] = __ldcg(p.position + row) + 1u;
+                if (ph.flags & 1u) {
+                    __stcg(p.best_value + row, value);
+                    __stcg(p.best_index + row, index);
+                } else {
+                    p.tokens[row] = index == 0xffffffffu ? 0u : index;
+                    p.position[row] = __ldcg(p.position + row) + 1u;
+                }
                 p.argmax_counters[row] = 0u;
             }
+        }
+    }
+}
+
+// The last phase on a rank of a tensor-parallel group, whose head holds rows [rank, rank + 1) * ph.k of the
+// vocabulary: warp 0 of CTA 0 gathers the ranks' winners of every row (an exchange of a vector that is zero except
+// for this rank's (value, index) pair, so the sum over the ranks is the list of pairs), picks among them (lowest
+// index on ties, as one device would), writes the token and moves the cursor.  Every rank computes the same.
+__device__ __forceinline__ void mk_choose(const MkParams &p, const MkPhase &ph) {
+    if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+    const uint32_t lane = threadIdx.x;
+    const ExchangeView &e = *ph.after.exchange;
+    for (uint32_t row = 0; row < p.rows; ++row) {
+        const float value = __ldcg(p.best_value + row);
+        const uint32_t index = __ldcg(p.best_index + row);
+        // pair r sits at numbers [2 r, 2 r + 2) of the vector: lane r / 4, numbers 2 (r % 4) of its eight
+        float mine8[8];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const bool here = lane * 4 + i == e.rank;
+            mine8[2 * i] = here ? value : 0.0f;
+            mine8[2 * i + 1] = here ? (float)(index == 0xffffffffu ? 0u : index + e.rank * ph.k) : 0.0f;   // (exact below 2^24)
+        }
+        if (!exchange_chunk(e, 0, 0, 1, mine8, ph.after.wait_nanos, ph.after.status)) return;
+        float best = -INFINITY;
+        uint32_t chosen = 0xffffffffu;
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxRanks; ++r) {
+            const float v = __shfl_sync(0xffffffffu, mine8[2 * (r % 4)], r / 4);
+            const float at = __shfl_sync(0xffffffffu, mine8[2 * (r % 4) + 1], r / 4);
+            if (r < e.world) argmax_take(best, chosen, v, (uint32_t)at);
+        }
+        if (lane == 0) {
+            p.tokens[row] = chosen == 0xffffffffu ? 0u : chosen;
+            p.position[row] = __ldcg(p.position + row) + 1u;
         }
     }
 }
@@ -567,6 +616,7 @@ __global__ void __launch_bounds__(kMkThreads, 1) decode_megakernel(const __grid_
             break;
         case MK_STAGE: mk_stage(p, phase); break;
         case MK_ARGMAX: mk_argmax(p, phase, reduce, best_index, &arrived); break;
+        case MK_CHOOSE: mk_choose(p, phase); break;
         default: break;
         }
         if (index + 1 == p.nphases) break;   // nothing follows the last phase

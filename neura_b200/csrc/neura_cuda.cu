@@ -1790,9 +1790,18 @@ int32_t neura_cuda_decoder_free(nc_context *ctx, nc_decoder *decoder) {
 }
 
 int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc, nc_decoder **out) {
+    return neura_cuda_decoder_compile_rank(ctx, desc, nullptr, 1, 0, out);
+}
+
+int32_t neura_cuda_decoder_compile_rank(nc_context *ctx, const nc_decoder_desc *desc, nc_comm *comm, uint32_t world, uint32_t rank,
+                                        nc_decoder **out) {
     if (!ctx || !desc || !out) return refuse(kBadArgument, "compile needs a context, a description and somewhere to put the decoder");
     *out = nullptr;
     const nc_decoder_desc &c = *desc;
+    if (world < 1 || world > kMaxRanks || rank >= world) return refuse(kBadArgument, "rank %u of %u ranks", rank, world);
+    if ((world > 1) != (comm != nullptr)) return refuse(kBadArgument, "a rank of a group compiles with the group's communicator, a single device without one");
+    if (comm && (!comm->connected || comm->world != world || comm->rank != rank))
+        return refuse(kBadState, "the communicator is not connected as rank %u of %u", rank, world);
     if (!c.layers || !c.layer || !c.tokens_dev || !c.position_dev || !c.logits_dev || !c.output_norm_dev)
         return refuse(kBadArgument, "a decoder needs its layers, token ids, cursors, logits and output norm");
     if (c.batch < 1 || c.batch > 2)
@@ -1821,16 +1830,27 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         return 0;
     };
     int32_t rc;
+    // a rank's share of a row-parallel projection's K axis: the whole blocks that cover elements
+    // [rank, rank + 1) * width of the group's axis, the share itself at [lo, hi) inside them
+    struct Window { uint32_t k, lo, hi; };
+    auto window_of = [&](uint32_t width) {
+        const uint32_t k0 = rank * width, k1 = k0 + width, b0 = k0 / per, b1 = (k1 + per - 1) / per;
+        return Window{(b1 - b0) * per, k0 - b0 * per, k1 - b0 * per};
+    };
+    const Window attended_at = window_of(query_width), held_at = window_of(c.feed_forward);
+    if (world > 1 && (query_width % 32 || c.feed_forward % 32 || c.hidden % 256 || (uint64_t)c.batch * c.hidden > comm->max_count))
+        return refuse(kBadArgument, "a rank's shares of %u and %u columns start on multiples of 32, and the exchange takes rows of a multiple of 256 numbers, %llu in all",
+                      query_width, c.feed_forward, (unsigned long long)comm->max_count);
     if ((rc = fits(c.head, c.vocab, c.hidden, NC_LAYOUT_TILED, "the head"))) return rc;
     if ((rc = check_weight(&c.embedding))) return rc;
-    if (c.embedding.n != c.vocab || c.embedding.k != c.hidden)
-        return refuse(kBadArgument, "the embedding is [%u, %u] where the decoder wants [%u, %u]", c.embedding.n, c.embedding.k, c.vocab, c.hidden);
+    if (c.embedding.n != c.vocab * world || c.embedding.k != c.hidden)
+        return refuse(kBadArgument, "the embedding is [%u, %u] where the decoder wants [%u, %u]", c.embedding.n, c.embedding.k, c.vocab * world, c.hidden);
     for (uint32_t l = 0; l < c.layers; ++l) {
         const nc_decoder_layer &layer = c.layer[l];
         if ((rc = fits(layer.qkv, query_width + 2 * key_width, c.hidden, NC_LAYOUT_TILED, "a q|k|v projection"))) return rc;
-        if ((rc = fits(layer.attn_output, c.hidden, query_width, NC_LAYOUT_TILED, "an attention output projection"))) return rc;
+        if ((rc = fits(layer.attn_output, c.hidden, attended_at.k, NC_LAYOUT_TILED, "an attention output projection"))) return rc;
         if ((rc = fits(layer.gate_up, c.feed_forward, c.hidden, NC_LAYOUT_TILED_PAIR, "a gate|up pair"))) return rc;
-        if ((rc = fits(layer.down, c.hidden, c.feed_forward, NC_LAYOUT_TILED, "a down projection"))) return rc;
+        if ((rc = fits(layer.down, c.hidden, held_at.k, NC_LAYOUT_TILED, "a down projection"))) return rc;
         if (!layer.attn_norm_dev || !layer.ffn_norm_dev || !layer.keys_dev || !layer.values_dev)
             return refuse(kBadArgument, "layer %u lacks a norm weight or its cache", l);
     }
@@ -1863,6 +1883,10 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * d->grid * 4, true, (void **)&slice_value));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * d->grid * 4, true, (void **)&slice_index));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * sizeof(unsigned int), true, (void **)&argmax_counters));
+    float *best_value;
+    uint32_t *best_index;
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * 4, true, (void **)&best_value));
+    NC_TRY(decoder_alloc(d, (uint64_t)c.batch * 4, true, (void **)&best_index));
     NC_TRY(decoder_alloc(d, 256, true, (void **)&barrier));
     NC_TRY(decoder_alloc(d, (uint64_t)c.batch * ((c.hidden + 255) / 256) * 4, true, (void **)&sumsq));
     float2 *rope_table;
@@ -1876,9 +1900,14 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         uint32_t *sums;
         unsigned int *counters;
         float *rows;
-        uint32_t width;
+        uint32_t width;          // the K axis of the product that reads the staged rows
+        uint32_t stride, lo, hi; // the rows themselves: their stride, and where they sit on that axis
     };
-    auto staged = [&](float *rows, uint32_t width, Staged &out) -> int32_t {
+    auto staged = [&](float *rows, uint32_t stride, const Window &at, Staged &out) -> int32_t {
+        const uint32_t width = at.k;
+        out.stride = stride;
+        out.lo = at.lo;
+        out.hi = at.hi;
         const uint64_t kpad = ((uint64_t)width + 255) / 256 * 256;
         int32_t rc_;
         if ((rc_ = decoder_alloc(d, kpad * ncols, true, (void **)&out.dig))) return rc_;
@@ -1890,9 +1919,9 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         return 0;
     };
     Staged of_hidden, of_attended, of_held;
-    NC_TRY(staged(hidden, c.hidden, of_hidden));
-    NC_TRY(staged(attended, query_width, of_attended));
-    NC_TRY(staged(held, c.feed_forward, of_held));
+    NC_TRY(staged(hidden, c.hidden, Window{c.hidden, 0, c.hidden}, of_hidden));
+    NC_TRY(staged(attended, query_width, attended_at, of_attended));
+    NC_TRY(staged(held, c.feed_forward, held_at, of_held));
 
     // the phase table
     std::vector<MkPhase> phases;
@@ -1909,7 +1938,7 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         ph.has_after = 1;
         StageAfter &a = ph.after;
         a.prep.x = to.rows;
-        a.prep.x_stride = to.width;
+        a.prep.x_stride = to.stride;
         a.prep.dig = to.dig;
         a.prep.cs = to.cs;
         a.prep.sums = to.sums;
@@ -1918,12 +1947,16 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         a.prep.ncols = ncols;
         a.prep.granule = q4k ? 256 : 32;
         a.prep.vector = 1;
-        a.prep.lo = 0;
-        a.prep.hi = to.width;
+        a.prep.lo = to.lo;
+        a.prep.hi = to.hi;
         a.gain = gain;
         a.sumsq = squares ? sumsq : nullptr;
         a.counters = to.counters;
         a.piece = piece;
+        // the hidden rows a rank's row-parallel products write are partial sums: whoever completes a chunk adds the ranks' up
+        a.exchange = comm && ph.kind == MK_GEMV && to.rows == hidden ? comm->view_dev : nullptr;
+        a.wait_nanos = ctx->wait_nanos;
+        a.status = (unsigned int *)ctx->status.ptr;
         if (ph.kind == MK_GEMV) {
             ph.g.then = a;
             ph.g.has_then = 1;
@@ -1991,9 +2024,10 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
             stage_after(ph, of_attended, 256, nullptr, false);
             phases.push_back(ph);
         }
-        stage_after(product(layer.attn_output, of_attended, false, hidden, c.hidden, hidden), of_hidden, 32, layer.ffn_norm_dev, true);
+        const float *residual = rank == 0 ? hidden : nullptr;   // rank 0 carries the residual into the ranks' sum
+        stage_after(product(layer.attn_output, of_attended, false, hidden, c.hidden, residual), of_hidden, 32, layer.ffn_norm_dev, true);
         stage_after(product(layer.gate_up, of_hidden, true, held, c.feed_forward, nullptr), of_held, 16, nullptr, false);
-        stage_after(product(layer.down, of_held, false, hidden, c.hidden, hidden), of_hidden, 32, next_norm, true);
+        stage_after(product(layer.down, of_held, false, hidden, c.hidden, residual), of_hidden, 32, next_norm, true);
     }
     product(c.head, of_hidden, true, c.logits_dev, c.vocab, nullptr);
     {
@@ -2002,6 +2036,15 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
         ph.x_stride = c.vocab;
         ph.k = c.vocab;
         phases.push_back(ph);
+        if (comm) {   // the ranks hold shares of the vocabulary: one more phase picks among their winners
+            MkPhase choose = blank(MK_CHOOSE);
+            choose.k = c.vocab;
+            choose.after.exchange = comm->view_dev;
+            choose.after.wait_nanos = ctx->wait_nanos;
+            choose.after.status = (unsigned int *)ctx->status.ptr;
+            phases.back().flags = 1;   // the argmax phase leaves its winners for the next phase
+            phases.push_back(choose);
+        }
     }
     // when a phase ends, its warps start the copies of the next product, unless the attention phase
     // (which borrows the ring) comes first
@@ -2049,6 +2092,8 @@ int32_t neura_cuda_decoder_compile(nc_context *ctx, const nc_decoder_desc *desc,
     p.slice_value = slice_value;
     p.slice_index = slice_index;
     p.argmax_counters = argmax_counters;
+    p.best_value = best_value;
+    p.best_index = best_index;
     p.trace = trace;
 
     // the kernel must be resident on every SM at once

@@ -321,15 +321,16 @@ class Decoder:
     def compile(self) -> None:
         """Runtime::compile for the whole step (crates/neura-runtime/src/runtime.rs:528): lays the step out
         as the phase table of one persistent kernel (``neura_cuda_decoder_compile``); ``run_token`` then
-        launches that kernel instead of one kernel per operation.  Single GPU, 1 or 2 sequences, the MLP
-        sealed as a gate|up pair."""
+        launches that kernel instead of one kernel per operation.  1 or 2 sequences, the MLP sealed as a gate|up
+        pair; a tensor-parallel rank needs a communicator whose exchange a kernel can do itself (``PeerComm``): the
+        ranks' sums and the choice among their argmax winners then happen inside the step."""
         import ctypes
 
         from ._lib import NcDecoderDesc, NcDecoderLayer
         from .runtime import _check
 
-        if self.shard is not None:
-            raise ValueError("the persistent step runs on one GPU")
+        if self.shard is not None and not hasattr(self.comm, "reduce_handle"):
+            raise ValueError("the persistent step of a tensor-parallel rank exchanges over peer memory: give it a PeerComm")
         c, w, n = self.config, self.weights, self.norms
         layers = (NcDecoderLayer * c.layers)()
         for index in range(c.layers):
@@ -341,12 +342,16 @@ class Decoder:
             layer.gate_up, layer.down = w[at("ffn_gate_up")].record(), w[at("ffn_down")].record()
             layer.attn_norm_dev, layer.ffn_norm_dev = n[at("attn_norm")].ptr, n[at("ffn_norm")].ptr
             layer.keys_dev, layer.values_dev = self.keys[index].ptr, self.values[index].ptr
-        desc = NcDecoderDesc(c.layers, c.hidden, c.heads, c.key_heads, c.head_width, c.feed_forward, c.vocab,
+        desc = NcDecoderDesc(c.layers, c.hidden, self.heads, self.key_heads, c.head_width, self.feed_forward, self.vocab,
                              self.batch, self.capacity, c.floor, c.rope_base, self.scale,
                              w["token_embd.weight"].record(), w["output.weight"].record(), n["output_norm.weight"].ptr,
                              layers, self.tokens.ptr, self.position.ptr, self.logits.ptr)
         handle = ctypes.c_void_p()
-        _check(self.rt._lib.neura_cuda_decoder_compile(self.rt._ctx, ctypes.byref(desc), ctypes.byref(handle)))
+        if self.shard is None:
+            _check(self.rt._lib.neura_cuda_decoder_compile(self.rt._ctx, ctypes.byref(desc), ctypes.byref(handle)))
+        else:
+            _check(self.rt._lib.neura_cuda_decoder_compile_rank(self.rt._ctx, ctypes.byref(desc), self.comm.reduce_handle(),
+                                                                self.shard.world, self.shard.rank, ctypes.byref(handle)))
         self.compiled = handle
 
     def trace(self):

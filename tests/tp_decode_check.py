@@ -50,13 +50,17 @@ def main() -> int:
     decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=96, shard=shard, comm=comm)
     decoder.fold = os.environ.get("TP_FOLD", "0") == "1"   # exchanges in the products' epilogues (the peer transport only)
     eager = decoder.generate(prompts, 64)
-    decoder.record()
+    if os.environ.get("TP_STEP", "graph") == "persistent":   # the whole step as one cooperative kernel a rank
+        decoder.compile()
+    else:
+        decoder.record()
     replayed = decoder.generate(prompts, 64)
     status = 0
     if rank == 0:
         want, margins = OracleDecoder(config, packed, norms, batch=batch, capacity=96).generate(prompts, 64)
         if not np.array_equal(eager, replayed):
-            print("FAIL: the recorded step decodes other tokens than the eager step")
+            at = np.argwhere(eager != replayed)[0]
+            print(f"FAIL: the recorded step decodes other tokens than the eager step, first at {tuple(at)}")
             status = 1
         differs = np.argwhere(eager != want)
         if differs.size:
@@ -64,8 +68,10 @@ def main() -> int:
             print(f"FAIL: sequence {b} leaves the oracle at step {at}: {eager[b, at]} for {want[b, at]} "
                   f"(oracle margin {margins[b, at]:.3e})")
             status = 1
+        how = type(comm).__name__ + (", exchanges folded into the products" if decoder.fold else "") + \
+            (", the step as one persistent kernel" if decoder.compiled is not None else "")
         verdict = (f"tp{world}: 64 greedy tokens x {batch} sequences match the oracle, eager and recorded "
-                   f"({type(comm).__name__})") if status == 0 else f"tp{world}: FAILED ({type(comm).__name__})"
+                   f"({how})") if status == 0 else f"tp{world}: FAILED ({how})"
         print(verdict)
         # a record of the run for boxes whose test collection has fewer GPUs than this check wants
         log = os.environ.get("TP_CHECK_LOG")
