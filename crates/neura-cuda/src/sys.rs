@@ -8,10 +8,13 @@ use core::ffi::{c_char, c_void};
 
 /// Element codes: the discriminants of `neura_abi::Element` (`crates/neura-abi/src/element.rs:3-17`).
 pub const NC_ELEMENT_SINGLE: u32 = 0;
+pub const NC_ELEMENT_HALF: u32 = 1;
 pub const NC_ELEMENT_BFLOAT16: u32 = 2;
 pub const NC_ELEMENT_Q8_0: u32 = 8;
 pub const NC_ELEMENT_Q4K: u32 = 9;
+pub const NC_ELEMENT_Q5K: u32 = 10;
 pub const NC_ELEMENT_Q6K: u32 = 11;
+pub const NC_ELEMENT_Q3K: u32 = 12;
 
 pub const NC_LAYOUT_GGUF: u32 = 0;
 pub const NC_LAYOUT_TILED: u32 = 1;

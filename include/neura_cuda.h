@@ -33,6 +33,11 @@ extern "C" {
 #define NC_ELEMENT_Q8_0 8u
 #define NC_ELEMENT_Q4K 9u
 #define NC_ELEMENT_Q6K 11u /* heads and embeddings of common GGUF mixes: multiplied where the GGUF left it (NC_LAYOUT_GGUF) */
+/* The other weight formats a GGUF of this model family may hold (element.rs:3-17), all multiplied in GGUF order by
+ * the plain row-at-a-time product: */
+#define NC_ELEMENT_HALF 1u   /* IEEE half numbers, two to a word (as a weight; NC_ELEMENT_BFLOAT16 likewise) */
+#define NC_ELEMENT_Q5K 10u   /* 256 numbers in 176 bytes */
+#define NC_ELEMENT_Q3K 12u   /* 256 numbers in 110 bytes */
 
 /* How the blocks of a weight tensor are laid out in device memory. */
 #define NC_LAYOUT_GGUF 0u   /* verbatim GGUF: row after row, blocks in order (what store.rs:131-135 copies) */
@@ -73,7 +78,7 @@ typedef struct nc_context nc_context;
  * features (GGUF ne[1]), `k` input features (GGUF ne[0], contiguous inside a row). */
 typedef struct nc_weight {
     const void *data_dev;
-    uint32_t element; /* NC_ELEMENT_Q8_0 | NC_ELEMENT_Q4K | NC_ELEMENT_Q6K */
+    uint32_t element; /* NC_ELEMENT_Q8_0 | NC_ELEMENT_Q4K, or one of the formats kept in GGUF order: Q6K, Q5K, Q3K, HALF, BFLOAT16 */
     uint32_t layout;  /* NC_LAYOUT_* */
     uint32_t n;
     uint32_t k;
@@ -167,7 +172,8 @@ int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, con
 /* run_matmul + chained (crates/neura-kernel/src/task/matmul.rs:376-517, pointwise.rs:90-104):
  *   out[r*out_stride + c] = chain(sum_k W[c][k] * x[r*x_stride + k]),  r < rows, c < w->n
  * f32 activations, f32 accumulation, f32 output (promote(Single, Q*) = Single, element.rs:306-323).
- * A Q8_0 or Q4K weight is sealed (NC_LAYOUT_TILED, or a sealed pair); a Q6K weight stays in GGUF order.
+ * A Q8_0 or Q4K weight is sealed (NC_LAYOUT_TILED, or a sealed pair); a Q6K, Q5K, Q3K, half or bfloat16 weight stays in
+ * GGUF order.
  * The kernel follows the row count the way the reference's planner picks its tiles (Product::planned,
  * crates/neura-plan/src/product.rs:103-195): up to eight rows the streaming product (the reference's folded tiles),
  * from nine rows on a Q4K weight takes the skinny tensor-core product that streams the weight once for up to 32 rows

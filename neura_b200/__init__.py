@@ -6,6 +6,6 @@ calls for the path.  Nothing here computes on the CPU.
 """
 from .runtime import (  # noqa: F401
     ADD, MUL, SUB, DIV, MAXIMUM, MINIMUM, RELU, SQRT, RECIP, EXP, LOG, TANH, SIGMOID, NEG, ABS, IDENTITY,
-    SIN, COS, POW, FLOOR, GELU, SILU, SINGLE, BFLOAT16, Q8_0, Q4K, Q6K, LAYOUT_GGUF, LAYOUT_TILED, LAYOUT_TILED_PAIR,
+    SIN, COS, POW, FLOOR, GELU, SILU, SINGLE, HALF, BFLOAT16, Q8_0, Q4K, Q5K, Q6K, Q3K, LAYOUT_GGUF, LAYOUT_TILED, LAYOUT_TILED_PAIR,
     DeviceTensor, NeuraCudaError, Runtime, Step, Weight, payload_bytes,
 )

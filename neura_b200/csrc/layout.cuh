@@ -49,8 +49,12 @@ __device__ __forceinline__ uint32_t weight_byte(const WeightView &w, uint32_t ro
 // One element of unpack: q8_0_values / q4_k_values (crates/neura-precision/src/ggml.rs:211-216,
 // :336-350).  Each product is rounded to f32 on its own (no fma), which is what makes it bit-exact.
 __device__ __forceinline__ float dequant_at(const WeightView &w, uint32_t row, uint32_t at) {
-    if (w.element == NC_ELEMENT_Q6K)   // kept in GGUF order only
-        return q6k_value(w.data + ((uint64_t)row * (w.k / kSuperBlock) + at / kSuperBlock) * kQ6kBytes, at % kSuperBlock);
+    // the formats kept in GGUF order only
+    if (w.element == NC_ELEMENT_Q6K) return gguf_value<NC_ELEMENT_Q6K>(w.data + (uint64_t)row * (w.k / kSuperBlock) * kQ6kBytes, at);
+    if (w.element == NC_ELEMENT_Q5K) return gguf_value<NC_ELEMENT_Q5K>(w.data + (uint64_t)row * (w.k / kSuperBlock) * kQ5kBytes, at);
+    if (w.element == NC_ELEMENT_Q3K) return gguf_value<NC_ELEMENT_Q3K>(w.data + (uint64_t)row * (w.k / kSuperBlock) * kQ3kBytes, at);
+    if (w.element == NC_ELEMENT_HALF) return gguf_value<NC_ELEMENT_HALF>(w.data + (uint64_t)row * w.k * 2, at);
+    if (w.element == NC_ELEMENT_BFLOAT16) return gguf_value<NC_ELEMENT_BFLOAT16>(w.data + (uint64_t)row * w.k * 2, at);
     if (w.element == NC_ELEMENT_Q8_0) {
         const uint32_t blk = at / kQ8Block, lane = at % kQ8Block;
         const float quantum = half_bits_to_float(weight_byte(w, row, blk, 0) | (weight_byte(w, row, blk, 1) << 8));

@@ -135,11 +135,29 @@ int32_t ensure(nc_context *ctx, Region &region, uint64_t bytes, bool zero) {
     return 0;
 }
 
+// The formats that are multiplied where the GGUF left them (qlinear_rows.cuh); the streaming kernels take Q8_0 and Q4K.
+bool gguf_only(uint32_t element) {
+    return element == NC_ELEMENT_Q6K || element == NC_ELEMENT_Q5K || element == NC_ELEMENT_Q3K || element == NC_ELEMENT_HALF ||
+           element == NC_ELEMENT_BFLOAT16;
+}
 uint32_t block_elements(uint32_t element) {
-    return element == NC_ELEMENT_Q8_0 ? kQ8Block : element == NC_ELEMENT_Q4K || element == NC_ELEMENT_Q6K ? kSuperBlock : 0;
+    switch (element) {
+    case NC_ELEMENT_Q8_0: return kQ8Block;
+    case NC_ELEMENT_Q4K: case NC_ELEMENT_Q5K: case NC_ELEMENT_Q6K: case NC_ELEMENT_Q3K: return kSuperBlock;
+    case NC_ELEMENT_HALF: case NC_ELEMENT_BFLOAT16: return 1;
+    default: return 0;
+    }
 }
 uint32_t block_bytes(uint32_t element) {
-    return element == NC_ELEMENT_Q8_0 ? kQ8Bytes : element == NC_ELEMENT_Q4K ? kQ4kBytes : element == NC_ELEMENT_Q6K ? kQ6kBytes : 0;
+    switch (element) {
+    case NC_ELEMENT_Q8_0: return kQ8Bytes;
+    case NC_ELEMENT_Q4K: return kQ4kBytes;
+    case NC_ELEMENT_Q5K: return kQ5kBytes;
+    case NC_ELEMENT_Q6K: return kQ6kBytes;
+    case NC_ELEMENT_Q3K: return kQ3kBytes;
+    case NC_ELEMENT_HALF: case NC_ELEMENT_BFLOAT16: return 2;
+    default: return 0;
+    }
 }
 
 struct GemvPlan {
@@ -235,13 +253,13 @@ int32_t check_weight(const nc_weight *w) {
     if (!w || !w->data_dev) return refuse(kBadArgument, "a product needs a weight on the device");
     const uint32_t per = block_elements(w->element);
     if (!per)
-        return refuse(kBadArgument, "element %u is not a block format this path multiplies (Q8_0 = 8, Q4K = 9, Q6K = 11)",
+        return refuse(kBadArgument, "element %u is not a format this path multiplies (Q8_0 = 8, Q4K = 9; in GGUF order Q5K = 10, Q6K = 11, Q3K = 12, half = 1, bfloat16 = 2)",
                       w->element);
     if (w->n == 0 || w->k == 0 || w->k % per)
         return refuse(kBadArgument, "a [%u, %u] weight does not fill whole blocks of %u along its rows", w->n,
                       w->k, per);
-    if (w->element == NC_ELEMENT_Q6K) {
-        if (w->layout != NC_LAYOUT_GGUF) return refuse(kBadArgument, "a Q6K weight is multiplied in GGUF order; it has no sealed layout");
+    if (gguf_only(w->element)) {
+        if (w->layout != NC_LAYOUT_GGUF) return refuse(kBadArgument, "a weight of element %u is multiplied in GGUF order; it has no sealed layout", w->element);
         return 0;
     }
     if ((uintptr_t)w->data_dev % 16)
@@ -249,7 +267,13 @@ int32_t check_weight(const nc_weight *w) {
     return 0;
 }
 
-// The product of a Q6K weight (qlinear_rows.cuh): passes of up to eight rows.
+template <uint32_t ELEMENT>
+void (*rows_kernel_of(uint32_t rows))(RowsParams, uint64_t) {
+    return rows <= 1 ? qlinear_rows_kernel<ELEMENT, 1> : rows <= 2 ? qlinear_rows_kernel<ELEMENT, 2>
+           : rows <= 4 ? qlinear_rows_kernel<ELEMENT, 4> : qlinear_rows_kernel<ELEMENT, 8>;
+}
+
+// The product of a weight kept in GGUF order (qlinear_rows.cuh): passes of up to eight rows.
 int32_t rows_product(nc_context *ctx, cudaStream_t stream, const nc_weight *w, const float *x_dev, uint32_t rows, uint64_t x_stride,
                      float *out_dev, uint64_t out_stride, const nc_step *chain, uint32_t n_steps) {
     for (uint32_t first = 0; first < rows; first += kRowsKernelMost) {
@@ -270,9 +294,18 @@ int32_t rows_product(nc_context *ctx, cudaStream_t stream, const nc_weight *w, c
         }
         const uint64_t want = ((uint64_t)w->n + 7) / 8;   // eight warps a CTA, a warp a weight row
         const unsigned int blocks = (unsigned int)std::min<uint64_t>(want, (uint64_t)ctx->sms * 8);
-        void (*kernel)(RowsParams) = p.rows <= 1 ? qlinear_rows_q6k_kernel<1> : p.rows <= 2 ? qlinear_rows_q6k_kernel<2>
-                                     : p.rows <= 4 ? qlinear_rows_q6k_kernel<4> : qlinear_rows_q6k_kernel<8>;
-        NC_CUDA(launch_dependent(kernel, dim3(blocks), dim3(256), 0, stream, p));
+        if (w->element == NC_ELEMENT_Q6K) {
+            void (*kernel)(RowsParams) = p.rows <= 1 ? qlinear_rows_q6k_kernel<1> : p.rows <= 2 ? qlinear_rows_q6k_kernel<2>
+                                         : p.rows <= 4 ? qlinear_rows_q6k_kernel<4> : qlinear_rows_q6k_kernel<8>;
+            NC_CUDA(launch_dependent(kernel, dim3(blocks), dim3(256), 0, stream, p));
+        } else {
+            void (*kernel)(RowsParams, uint64_t) = w->element == NC_ELEMENT_Q5K ? rows_kernel_of<NC_ELEMENT_Q5K>(p.rows)
+                                                   : w->element == NC_ELEMENT_Q3K ? rows_kernel_of<NC_ELEMENT_Q3K>(p.rows)
+                                                   : w->element == NC_ELEMENT_HALF ? rows_kernel_of<NC_ELEMENT_HALF>(p.rows)
+                                                                                   : rows_kernel_of<NC_ELEMENT_BFLOAT16>(p.rows);
+            const uint64_t row_bytes = (uint64_t)w->k / block_elements(w->element) * block_bytes(w->element);
+            NC_CUDA(launch_dependent(kernel, dim3(blocks), dim3(256), 0, stream, p, row_bytes));
+        }
         ctx->launches++;
     }
     return 0;
@@ -599,7 +632,6 @@ int32_t neura_cuda_close(nc_context *ctx) {
 
 uint64_t neura_cuda_payload_bytes(uint32_t element, uint64_t elements) {
     if (element == NC_ELEMENT_SINGLE) return elements * 4;
-    if (element == NC_ELEMENT_BFLOAT16) return elements * 2;
     const uint32_t per = block_elements(element);
     if (!per) return 0;
     return (elements + per - 1) / per * block_bytes(element);
@@ -607,7 +639,7 @@ uint64_t neura_cuda_payload_bytes(uint32_t element, uint64_t elements) {
 
 uint64_t neura_cuda_sealed_bytes(uint32_t element, uint32_t n, uint32_t k) {
     const uint32_t per = block_elements(element);
-    if (!per || k % per) return 0;
+    if (!per || k % per || gguf_only(element)) return 0;
     const uint64_t padded = ((uint64_t)n + kTileRows - 1) / kTileRows * kTileRows;
     return padded * (k / per) * block_bytes(element);
 }
@@ -722,8 +754,8 @@ static int32_t seal_any(nc_context *ctx, void *stream, uint32_t element, uint32_
                         const void *second_dev, void *dst_dev) {
     if (!ctx || !gguf_dev || !dst_dev) return refuse(kBadArgument, "seal needs a context, a source and a destination");
     const uint32_t per = block_elements(element);
-    if (!per || !n || !k || k % per || element == NC_ELEMENT_Q6K)
-        return refuse(kBadArgument, "a [%u, %u] tensor of element %u is not whole blocks this path seals (a Q6K weight stays in GGUF order)", n, k, element);
+    if (!per || !n || !k || k % per || gguf_only(element))
+        return refuse(kBadArgument, "a [%u, %u] tensor of element %u is not whole blocks this path seals (Q8_0 and Q4K are sealed; the other formats stay in GGUF order)", n, k, element);
     const uintptr_t align = element == NC_ELEMENT_Q4K ? 8 : 2;
     if ((uintptr_t)gguf_dev % align || (uintptr_t)second_dev % align || (uintptr_t)dst_dev % 16)
         return refuse(kBadArgument, "seal reads an 8-byte aligned tensor and writes a 16-byte aligned one");
@@ -802,7 +834,7 @@ int32_t neura_cuda_quantize(nc_context *ctx, void *stream, uint32_t element, con
 int32_t neura_cuda_stage_window(nc_context *ctx, void *stream_, const float *x_dev, uint32_t rows, uint64_t x_stride,
                                 uint32_t k, uint32_t element, uint32_t lo, uint32_t hi) {
     if (!ctx || !x_dev) return refuse(kBadArgument, "staging needs a context and activations");
-    const uint32_t per = element == NC_ELEMENT_Q6K ? 0 : block_elements(element);   // (a Q6K product takes f32 rows as they are)
+    const uint32_t per = gguf_only(element) ? 0 : block_elements(element);   // (a product in GGUF order takes f32 rows as they are)
     if (!per || !k || k % per)
         return refuse(kBadArgument, "%u activations do not line up with blocks of element %u (Q8_0 or Q4K)", k, element);
     const uint32_t most = element == NC_ELEMENT_Q4K ? kSkMaxRows : kMaxRowsPerPass;
@@ -859,7 +891,7 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream_, const nc_weight
     if ((rc = check_weight(w))) return rc;
     if (w->layout != NC_LAYOUT_TILED && w->layout != NC_LAYOUT_TILED_PAIR)
         return refuse(kBadArgument, "the product streams a sealed weight (neura_cuda_weight_seal); this one is in GGUF order "
-                                    "(a Q6K weight takes neura_cuda_linear, which needs no staging)");
+                                    "(a weight kept in GGUF order takes neura_cuda_linear, which needs no staging)");
     const bool pair = w->layout == NC_LAYOUT_TILED_PAIR;
     // a pair is planned as the matrix of both tensors' rows, 16 of each per 32-row tile
     const uint32_t plan_n = pair ? (w->n + 15) / 16 * 32 : w->n;
@@ -1032,7 +1064,7 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream_, const nc_weight *w, co
     if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
     if (n_steps > NC_MAX_STEPS || (n_steps && !chain))
         return refuse(kBadArgument, "an epilogue holds at most %u steps", NC_MAX_STEPS);
-    if (w->element == NC_ELEMENT_Q6K) {
+    if (gguf_only(w->element)) {
         if (x_stride < w->k || out_stride < w->n)
             return refuse(kBadArgument, "rows of %u activations and %u outputs overlap at strides %llu and %llu", w->k, w->n,
                           (unsigned long long)x_stride, (unsigned long long)out_stride);
@@ -1135,7 +1167,7 @@ int32_t norm_stage_params(nc_context *ctx, const float *x_dev, uint32_t rows, ui
                           const float *weight_dev, float floor, uint32_t element, float *normed_dev,
                           uint64_t normed_stride, NormStageParams &p) {
     if (!ctx || !x_dev) return refuse(kBadArgument, "a norm needs a context and a row to norm");
-    const uint32_t per = element == NC_ELEMENT_Q6K ? 0 : block_elements(element);
+    const uint32_t per = gguf_only(element) ? 0 : block_elements(element);
     if (!per || !k || k % per)
         return refuse(kBadArgument, "%u activations do not line up with blocks of element %u", k, element);
     if (rows == 0 || rows > kMaxRowsPerPass)

@@ -20,14 +20,15 @@ import numpy as np
 from . import _lib
 from ._lib import NcStep, NcWeight
 
-SINGLE, BFLOAT16, Q8_0, Q4K, Q6K = 0, 2, 8, 9, 11
+SINGLE, HALF, BFLOAT16, Q8_0, Q4K, Q5K, Q6K, Q3K = 0, 1, 2, 8, 9, 10, 11, 12
+GGUF_ONLY = (HALF, BFLOAT16, Q5K, Q6K, Q3K)   # multiplied where the GGUF left them; Q8_0 and Q4K are sealed
 LAYOUT_GGUF, LAYOUT_TILED, LAYOUT_TILED_PAIR = 0, 1, 2
 
 # neura-pointwise op codes (crates/neura-pointwise/src/op.rs:141-170)
 ADD, MUL, SUB, DIV, MAXIMUM, MINIMUM, RELU, SQRT, RECIP, EXP = range(10)
 LOG, TANH, SIGMOID, NEG, ABS, IDENTITY, SIN, COS, POW, FLOOR, GELU, SILU = range(10, 22)
 
-_BLOCK = {Q8_0: (32, 34), Q4K: (256, 144), Q6K: (256, 210)}
+_BLOCK = {Q8_0: (32, 34), Q4K: (256, 144), Q6K: (256, 210), Q5K: (256, 176), Q3K: (256, 110), HALF: (1, 2), BFLOAT16: (1, 2)}
 
 
 class NeuraCudaError(RuntimeError):
@@ -196,7 +197,7 @@ class Runtime:
         if data.size < need:
             raise NeuraCudaError(-1, f"a [{n}, {k}] tensor packs {need} bytes and the source holds {data.size}")
         raw = self.upload(data[:need])
-        if not seal or element == Q6K:   # a Q6K weight is multiplied where the GGUF left it
+        if not seal or element in GGUF_ONLY:   # these weights are multiplied where the GGUF left them
             return Weight(raw.ptr, element, LAYOUT_GGUF, n, k, need)
         sealed = self.seal_device(element, n, k, raw.ptr)
         self.sync()

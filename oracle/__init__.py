@@ -15,9 +15,13 @@ from typing import Sequence
 import numpy as np
 
 SINGLE = 0
+HALF = 1
+BFLOAT16 = 2
 Q8_0 = 8
 Q4K = 9
+Q5K = 10
 Q6K = 11
+Q3K = 12
 
 # neura-pointwise op codes in declaration order (crates/neura-pointwise/src/op.rs:141-170)
 ADD, MUL, SUB, DIV, MAXIMUM, MINIMUM, RELU, SQRT, RECIP, EXP = range(10)
@@ -140,7 +144,7 @@ def pack_rows(element: int, weight: np.ndarray) -> np.ndarray:
     """Pack an [N, K] matrix the way a GGUF stores it: K contiguous, row after row."""
     weight = np.ascontiguousarray(weight, dtype=np.float32)
     n, k = weight.shape
-    per = 32 if element == Q8_0 else 256
+    per = 32 if element == Q8_0 else 1 if element in (HALF, BFLOAT16) else 256
     if k % per:
         raise ValueError(f"rows of {k} numbers do not fill whole blocks of {per}")
     return pack(element, weight.reshape(-1))[: payload_bytes(element, n * k)]

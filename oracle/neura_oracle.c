@@ -26,9 +26,13 @@
 #include <string.h>
 
 #define NRO_SINGLE 0u
+#define NRO_HALF 1u
+#define NRO_BFLOAT16 2u
 #define NRO_Q8_0 8u /* crates/neura-abi/src/element.rs:3-17 (enum discriminants) */
 #define NRO_Q4K 9u
+#define NRO_Q5K 10u
 #define NRO_Q6K 11u
+#define NRO_Q3K 12u
 
 #define QUANT_BLOCK 32      /* element.rs:35 */
 #define SUPER_BLOCK 256     /* element.rs:36 */
@@ -38,6 +42,8 @@
 #define Q4K_BYTES 144       /* element.rs:159-162: 4 + 12 + 128 */
 #define SUPER_SMALL_BLOCK 16 /* element.rs:38 */
 #define Q6K_BYTES 210       /* element.rs:167-170: 2 + 128 + 64 + 16 */
+#define Q5K_BYTES 176       /* element.rs:163-166: 4 + 12 + 32 + 128 */
+#define Q3K_BYTES 110       /* element.rs:171-174: 32 + 64 + 12 + 2 */
 
 /* ------------------------------------------------------------------ */
 /* IEEE binary16 <-> binary32, round-to-nearest-even, subnormals kept. */
@@ -132,6 +138,9 @@ int nro_block(uint32_t element, uint32_t *elements, uint32_t *bytes) {
     case NRO_Q8_0: *elements = QUANT_BLOCK; *bytes = Q8_0_BYTES; return 0;
     case NRO_Q4K: *elements = SUPER_BLOCK; *bytes = Q4K_BYTES; return 0;
     case NRO_Q6K: *elements = SUPER_BLOCK; *bytes = Q6K_BYTES; return 0;
+    case NRO_Q5K: *elements = SUPER_BLOCK; *bytes = Q5K_BYTES; return 0;
+    case NRO_Q3K: *elements = SUPER_BLOCK; *bytes = Q3K_BYTES; return 0;
+    case NRO_HALF: case NRO_BFLOAT16: *elements = 1; *bytes = 2; return 0;   /* element.rs:134: two to a word */
     default: return -1;
     }
 }
@@ -214,9 +223,12 @@ static uint32_t quantized(float value, float quantum, float low, float high) { /
     return (uint32_t)clampf(roundf(value / quantum), low, high);
 }
 
-/* ggml.rs:149-199 with steps = 15, sub = 32 (q4_k, :314-316) */
-static void q4_k_encode(const float *values, uint8_t *field) {
+/* affine_block (ggml.rs:149-199) with sub = 32: steps = 15 and the codes at byte 16 for q4_k (:314-316); steps = 31,
+ * the low nibbles at byte 48 and the fifth bits at byte 16 for q5_k (:310-312) */
+static void affine_encode(const float *values, uint8_t *field, int fifth) {
     const int count = SUPER_BLOCK / SUPER_SUB_BLOCK;
+    const float steps = fifth ? 31.0f : 15.0f;
+    const int quants = fifth ? 48 : 16;
     float lows[8], quantums[8];
     for (int at = 0; at < count; ++at) {
         float low = 0.0f, high = 0.0f; /* span(): fold from (0, 0) */
@@ -226,7 +238,7 @@ static void q4_k_encode(const float *values, uint8_t *field) {
             high = greatest(high, v);
         }
         lows[at] = least(0.0f, low);
-        quantums[at] = (high - lows[at]) / 15.0f;
+        quantums[at] = (high - lows[at]) / steps;
     }
     float scale = 0.0f, min = 0.0f;
     for (int at = 0; at < count; ++at) scale = greatest(scale, quantums[at]);
@@ -241,7 +253,7 @@ static void q4_k_encode(const float *values, uint8_t *field) {
     uint8_t scales[SUPER_SCALE_BYTES];
     memset(scales, 0, sizeof scales);
     for (int at = 0; at < count; ++at) put_scale_min_k4(scales, at, codes[at], mins[at]);
-    memset(field, 0, Q4K_BYTES);
+    memset(field, 0, fifth ? Q5K_BYTES : Q4K_BYTES);
     put_half(field, 0, scale);
     put_half(field, 2, min);
     memcpy(field + 4, scales, SUPER_SCALE_BYTES);
@@ -250,13 +262,17 @@ static void q4_k_encode(const float *values, uint8_t *field) {
         float quantum = scale * (float)codes[at];
         float low = min * (float)mins[at];
         for (int within = 0; within < SUPER_SUB_BLOCK; ++within) {
-            uint32_t code = quantized(values[at * SUPER_SUB_BLOCK + within] + low, quantum, 0.0f, 15.0f);
+            uint32_t code = quantized(values[at * SUPER_SUB_BLOCK + within] + low, quantum, 0.0f, steps);
             int group = at / 2;
             int seat = at % 2;
-            field[16 + group * SUPER_SUB_BLOCK + within] |= (uint8_t)((code & 0x0f) << (seat ? 4 : 0));
+            field[quants + group * SUPER_SUB_BLOCK + within] |= (uint8_t)((code & 0x0f) << (seat ? 4 : 0));
+            if (fifth && (code & 0x10u)) field[16 + within] |= (uint8_t)(1u << (2 * group + seat));
         }
     }
 }
+
+static void q4_k_encode(const float *values, uint8_t *field) { affine_encode(values, field, 0); }
+static void q5_k_encode(const float *values, uint8_t *field) { affine_encode(values, field, 1); }
 
 /* ggml.rs:336-350 */
 static void q4_k_decode(const uint8_t *field, float *out) {
@@ -275,6 +291,90 @@ static void q4_k_decode(const uint8_t *field, float *out) {
                 out[n++] = quantum * (float)quant - low;
             }
         }
+    }
+}
+
+/* q5_k_values (ggml.rs:318-334): q4_k's walk with a fifth bit per code, bit 2 group + seat of byte 16 + within */
+static void q5_k_decode(const uint8_t *field, float *out) {
+    float scale = half_at(field, 0);
+    float min = half_at(field, 2);
+    int n = 0;
+    for (int group = 0; group < 4; ++group) {
+        for (int seat = 0; seat < 2; ++seat) {
+            uint32_t code, offset;
+            scale_min_k4(field + 4, group * 2 + seat, &code, &offset);
+            float quantum = scale * (float)code;
+            float low = min * (float)offset;
+            for (int within = 0; within < SUPER_SUB_BLOCK; ++within) {
+                uint8_t byte = field[48 + group * 32 + within];
+                uint32_t high = (uint32_t)(field[16 + within] >> (2 * group + seat)) & 1u;
+                uint32_t quant = (seat ? (uint32_t)(byte >> 4) : (uint32_t)(byte & 0x0f)) | (high << 4);
+                out[n++] = quantum * (float)quant - low;
+            }
+        }
+    }
+}
+
+/* q3_k_scale / put_q3_k_scale (ggml.rs:222-241): sixteen six-bit codes; the low nibbles of codes 0-7 and 8-15 share
+ * bytes 0-7, the top two bits of codes at, at + 4, at + 8, at + 12 share byte 8 + at % 4 */
+static uint32_t q3_k_scale(const uint8_t *scales, int at) {
+    uint8_t low = scales[at % 8];
+    uint32_t nibble = at < 8 ? (uint32_t)(low & 0x0f) : (uint32_t)(low >> 4);
+    return nibble | ((((uint32_t)scales[8 + at % 4] >> (2 * (at / 4))) & 3u) << 4);
+}
+static void put_q3_k_scale(uint8_t *scales, int at, uint32_t code) {
+    if (at < 8) scales[at] |= (uint8_t)(code & 0x0f);
+    else scales[at - 8] |= (uint8_t)((code & 0x0f) << 4);
+    scales[8 + at % 4] |= (uint8_t)(((code >> 4) & 3u) << (2 * (at / 4)));
+}
+
+/* Where number `at` of a q3_k block keeps its two low bits (byte, shift) and its third bit (byte, bit)
+ * (ggml.rs:267-281, :292-300): runs of 16, eight runs a half; run `within` of a half sits in bit pair within / 2 of
+ * byte half * 32 + (within % 2) * 16 + lane */
+static void q3_k_seat(int at, int *byte, int *shift, int *mask_byte, int *mask_bit) {
+    int sub = at / 16, lane = at % 16, half = sub / 8, within = sub % 8, j = within / 2, second = within % 2;
+    *byte = 32 + half * 32 + second * 16 + lane;
+    *shift = 2 * j;
+    *mask_byte = second * 16 + lane;
+    *mask_bit = half * 4 + j;
+}
+
+/* q3_k (ggml.rs:243-290): one d for the block, a six-bit scale (biased by 32) for every run of 16, codes -4..3 */
+static void q3_k_encode(const float *values, uint8_t *field) {
+    float peaks[16], widest = 0.0f;
+    for (int at = 0; at < 16; ++at) {
+        peaks[at] = 0.0f;
+        for (int i = 0; i < 16; ++i) peaks[at] = greatest(peaks[at], fabsf(values[at * 16 + i]));
+        widest = greatest(widest, peaks[at]);
+    }
+    if (!(widest > FLT_MIN)) widest = FLT_MIN;   /* .max(f32::MIN_POSITIVE) */
+    float d = widest / 4.0f / 31.0f;
+    uint32_t codes[16];
+    memset(field, 0, Q3K_BYTES);
+    for (int at = 0; at < 16; ++at) {
+        codes[at] = (uint32_t)clampf(roundf(peaks[at] / 4.0f / d), 0.0f, 31.0f) + 32u;
+        put_q3_k_scale(field + 96, at, codes[at]);
+    }
+    for (int at = 0; at < SUPER_BLOCK; ++at) {
+        float quantum = d * (float)(codes[at / 16] - 32u);
+        int quant = quantum == 0.0f ? 0 : (int)clampf(roundf(values[at] / quantum), -4.0f, 3.0f);
+        int byte, shift, mask_byte, mask_bit;
+        q3_k_seat(at, &byte, &shift, &mask_byte, &mask_bit);
+        field[byte] |= (uint8_t)(((uint32_t)quant & 3u) << shift);
+        if (quant >= 0) field[mask_byte] |= (uint8_t)(1u << mask_bit);
+    }
+    put_half(field, 108, d);
+}
+
+/* q3_k_values (ggml.rs:292-308) */
+static void q3_k_decode(const uint8_t *field, float *out) {
+    float d = half_at(field, 108);
+    for (int at = 0; at < SUPER_BLOCK; ++at) {
+        int byte, shift, mask_byte, mask_bit;
+        q3_k_seat(at, &byte, &shift, &mask_byte, &mask_bit);
+        int low = (field[byte] >> shift) & 3;
+        int quant = low - ((field[mask_byte] >> mask_bit) & 1 ? 0 : 4);
+        out[at] = d * ((float)(uint8_t)q3_k_scale(field + 96, at / 16) - 32.0f) * (float)quant;
     }
 }
 
@@ -340,13 +440,23 @@ int nro_pack(uint32_t element, const float *values, uint64_t count, uint8_t *out
     uint32_t per, bytes;
     if (nro_block(element, &per, &bytes)) return -1;
     uint64_t blocks = (count + per - 1) / per;
-    for (uint64_t b = 0; b < blocks; ++b) {
+    if (element == NRO_HALF || element == NRO_BFLOAT16) { /* crates/neura-precision/src/lib.rs:8-9: two to a word, the first low */
+        for (uint64_t i = 0; i < count; ++i) {
+            uint16_t h = element == NRO_HALF ? nro_f32_to_f16(values[i]) : nro_bf16_rne(values[i]);
+            out[2 * i] = (uint8_t)(h & 0xff);
+            out[2 * i + 1] = (uint8_t)(h >> 8);
+        }
+        blocks = count;
+    }
+    else for (uint64_t b = 0; b < blocks; ++b) {
         float held[SUPER_BLOCK];
         memset(held, 0, sizeof held);
         uint64_t have = count - b * per < per ? count - b * per : per;
         memcpy(held, values + b * per, have * sizeof(float));
         if (element == NRO_Q8_0) q8_0_encode(held, out + b * bytes);
         else if (element == NRO_Q6K) q6_k_encode(held, out + b * bytes);
+        else if (element == NRO_Q5K) q5_k_encode(held, out + b * bytes);
+        else if (element == NRO_Q3K) q3_k_encode(held, out + b * bytes);
         else q4_k_encode(held, out + b * bytes);
     }
     uint64_t end = blocks * bytes;
@@ -360,10 +470,19 @@ int nro_unpack(uint32_t element, uint64_t count, const uint8_t *bytes_in, float 
     uint32_t per, bytes;
     if (nro_block(element, &per, &bytes)) return -1;
     uint64_t blocks = (count + per - 1) / per;
+    if (element == NRO_HALF || element == NRO_BFLOAT16) { /* crates/neura-precision/src/lib.rs:34-42 */
+        for (uint64_t i = 0; i < count; ++i) {
+            uint16_t h = (uint16_t)(bytes_in[2 * i] | (bytes_in[2 * i + 1] << 8));
+            out[i] = element == NRO_HALF ? nro_f16_to_f32(h) : nro_bf16_to_f32(h);
+        }
+        return 0;
+    }
     for (uint64_t b = 0; b < blocks; ++b) {
         float held[SUPER_BLOCK];
         if (element == NRO_Q8_0) q8_0_decode(bytes_in + b * bytes, held);
         else if (element == NRO_Q6K) q6_k_decode(bytes_in + b * bytes, held);
+        else if (element == NRO_Q5K) q5_k_decode(bytes_in + b * bytes, held);
+        else if (element == NRO_Q3K) q3_k_decode(bytes_in + b * bytes, held);
         else q4_k_decode(bytes_in + b * bytes, held);
         uint64_t have = count - b * per < per ? count - b * per : per;
         memcpy(out + b * per, held, have * sizeof(float));
@@ -411,6 +530,36 @@ float nro_fetch(uint32_t element, const uint8_t *heap, uint64_t at) {
         float a = half_at(heap + base, 0) * (float)ggml_k4_scale(heap, base + 4u, sub);
         float b = half_at(heap + base, 2) * (float)ggml_k4_min(heap, base + 4u, sub);
         return a * (float)quant - b;
+    }
+    if (element == NRO_HALF || element == NRO_BFLOAT16) { /* fetch.rs:95-107 */
+        uint16_t h = (uint16_t)(heap[2 * at] | (heap[2 * at + 1] << 8));
+        return element == NRO_HALF ? nro_f16_to_f32(h) : nro_bf16_to_f32(h);
+    }
+    if (element == NRO_Q5K) { /* fetch.rs:269-282 */
+        uint64_t base = at / SUPER_BLOCK * Q5K_BYTES;
+        uint32_t within = (uint32_t)(at % SUPER_BLOCK);
+        uint32_t group = within / 64u, seat = (within % 64u) / SUPER_SUB_BLOCK, lane = within % SUPER_SUB_BLOCK;
+        uint32_t sub = group * 2u + seat;
+        uint32_t packed = ggml_byte(heap, base + 48u + group * 32u + lane);
+        uint32_t nibble = seat == 1u ? packed >> 4 : packed & 0xfu;
+        uint32_t fifth = (ggml_byte(heap, base + 16u + lane) >> (2u * group + seat)) & 1u;
+        float a = half_at(heap + base, 0) * (float)ggml_k4_scale(heap, base + 4u, sub);
+        float b = half_at(heap + base, 2) * (float)ggml_k4_min(heap, base + 4u, sub);
+        return a * (float)(nibble | (fifth << 4)) - b;
+    }
+    if (element == NRO_Q3K) { /* fetch.rs:226-233 (ggml_q3_scale), :242-254 */
+        uint64_t base = at / SUPER_BLOCK * Q3K_BYTES;
+        uint32_t within = (uint32_t)(at % SUPER_BLOCK);
+        uint32_t half = within / 128u, local = within % 128u, j = local / 32u, seat = local % 32u;
+        uint32_t index = half * 8u + j * 2u + seat / 16u;
+        uint32_t low_byte = ggml_byte(heap, base + 96u + index % 8u);
+        uint32_t nibble = index >= 8u ? low_byte >> 4 : low_byte & 0x0fu;
+        uint32_t code = nibble | (((ggml_byte(heap, base + 96u + 8u + index % 4u) >> (2u * (index / 4u))) & 3u) << 4);
+        float scale = (float)code - 32.0f;
+        uint32_t low = (ggml_byte(heap, base + 32u + half * 32u + seat) >> (2u * j)) & 3u;
+        uint32_t high = (ggml_byte(heap, base + seat) >> (half * 4u + j)) & 1u;
+        float quant = (float)low - (high == 0u ? 4.0f : 0.0f);
+        return half_at(heap + base, 108) * scale * quant;
     }
     if (element == NRO_Q6K) { /* fetch.rs:284-301 */
         uint64_t base = at / SUPER_BLOCK * Q6K_BYTES;

@@ -38,7 +38,11 @@ def test_geometry_entry_points_need_no_device(lib):
     assert lib.neura_cuda_payload_bytes(9, 18944 * 3584) == 38191104
     assert lib.neura_cuda_payload_bytes(0, 10) == 40
     assert lib.neura_cuda_payload_bytes(11, 256) == 210        # Q6_K: heads and embeddings of common GGUF mixes
-    assert lib.neura_cuda_payload_bytes(12, 256) == 0          # Q3_K is not on this path
+    # the other formats a GGUF may hold (crates/neura-abi/tests/layout.rs pins the same sizes)
+    assert lib.neura_cuda_payload_bytes(10, 256) == 176 and lib.neura_cuda_payload_bytes(12, 512) == 220
+    assert lib.neura_cuda_payload_bytes(1, 7) == 14 and lib.neura_cuda_payload_bytes(2, 7) == 14
+    assert lib.neura_cuda_sealed_bytes(10, 32, 256) == 0       # sealed layouts exist for Q8_0 and Q4_K only
+    assert lib.neura_cuda_payload_bytes(3, 256) == 0           # the int8 element (element.rs:7) is not on this path
     # sealing pads rows to tiles of 32 and keeps the block bytes
     assert lib.neura_cuda_sealed_bytes(9, 18944, 3584) == 38191104
     assert lib.neura_cuda_sealed_bytes(9, 33, 256) == 64 * 144

@@ -281,3 +281,80 @@ def test_q6k_product_applies_the_fused_chain_and_gathers_rows(runtime, oracle):
     runtime.embed(w, tokens, rows_out)
     table = oracle.unpack(nb.Q6K, n * k, packed).reshape(n, k)
     assert np.array_equal(bits(runtime.read(rows_out)), bits(table[[5, 0, 95, 5]]))
+
+
+# ---- the other formats kept in GGUF order: Q5_K, Q3_K, half and bfloat16 numbers --------------------------------
+def gguf_blocks(element, seed, n, k):
+    """Random payload bytes of [n, k] numbers of ``element`` with finite scales, every code in use."""
+    rng = np.random.default_rng(seed)
+    if element in (nb.HALF, nb.BFLOAT16):
+        numbers = rng.normal(0.0, 0.05, n * k).astype(np.float32)
+        if element == nb.HALF:
+            return numbers.astype(np.float16).view(np.uint8).reshape(-1).copy()
+        return (numbers.view(np.uint32) >> 16).astype(np.uint16).view(np.uint8).reshape(-1).copy()
+    size, halves = {nb.Q5K: (176, (0, 2)), nb.Q3K: (110, (108,)), nb.Q6K: (210, (208,))}[element]
+    blocks = rng.integers(0, 256, (n * (k // 256), size), dtype=np.uint8)
+    for at in halves:
+        blocks[:, at: at + 2] = rng.uniform(-2e-3, 2e-3, blocks.shape[0]).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    return blocks.reshape(-1)
+
+
+GGUF_ORDER = [nb.Q5K, nb.Q3K, nb.HALF, nb.BFLOAT16]
+
+
+@pytest.mark.parametrize("element", GGUF_ORDER)
+@pytest.mark.parametrize("n,k", [(16, 256), (33, 1280), (1000, 5120)])
+def test_dequant_of_the_formats_kept_in_gguf_order_is_bit_exact(runtime, oracle, element, n, k):
+    sources = [gguf_blocks(element, 3, n, k), oracle.pack_rows(element, weights(oracle, nb.Q8_0, n, k, seed=9)[0])]
+    for packed in sources:
+        expected = oracle.unpack(element, n * k, packed).reshape(n, k)
+        held = runtime.load(element, n, k, packed)
+        assert held.layout == nb.LAYOUT_GGUF
+        assert np.array_equal(bits(runtime.dequant(held)), bits(expected))
+        runtime.free(held.ptr)
+
+
+@pytest.mark.parametrize("element", GGUF_ORDER)
+@pytest.mark.parametrize("n,k", [(1, 256), (31, 768), (1000, 3584)])
+@pytest.mark.parametrize("rows", [1, 3, 8, 19])
+def test_products_of_the_formats_kept_in_gguf_order(runtime, oracle, element, n, k, rows):
+    packed = gguf_blocks(element, 11, n, k)
+    x = oracle.Stream(7).normal(rows * k).reshape(rows, k)
+    expected = oracle.linear(element, packed, n, k, x, threads=8)
+    w = runtime.load(element, n, k, packed)
+    assert_close(runtime.linear_host(w, x), expected, f"element {element} [{n},{k}] rows {rows}")
+    runtime.free(w.ptr)
+
+
+@pytest.mark.parametrize("element", GGUF_ORDER)
+def test_the_reference_products_chain_and_gather_in_gguf_order(runtime, oracle, element):
+    # crates/neura-runtime/tests/runtime.rs:12-144 run every GGML format: uniform(-1, 1) weights through the host packer,
+    # absolute 1e-3
+    for rows, depth, columns in ((1, 2048, 1024), (4, 2048, 1024)):
+        w, _ = weights(oracle, nb.Q8_0, columns, depth, seed=23)
+        packed = oracle.pack_rows(element, w)
+        x = oracle.random(rows * depth, 29).reshape(rows, depth)
+        expected = oracle.linear(element, packed, columns, depth, x, threads=8)
+        held = runtime.load(element, columns, depth, packed)
+        assert np.abs(runtime.linear_host(held, x) - expected).max() <= ABS_TOL
+        runtime.free(held.ptr)
+    n, k, rows = 96, 512, 3
+    packed = gguf_blocks(element, 13, n, k)
+    x = oracle.Stream(11).normal(rows * k).reshape(rows, k)
+    bias = oracle.Stream(17).normal(n)
+    expected = oracle.linear(element, packed, n, k, x, chain=[(oracle.ADD, bias), (oracle.SILU, None)])
+    w = runtime.load(element, n, k, packed)
+    xd, od, bd = runtime.tensor(rows, k), runtime.tensor(rows, n), runtime.tensor(n)
+    runtime.write(xd, x)
+    runtime.write(bd, bias)
+    runtime.linear(w, xd, od, [nb.Step(nb.ADD, bd), nb.Step(nb.SILU)])
+    assert_close(runtime.read(od), expected, f"element {element} chain")
+    tokens = runtime.tensor_u32(4)
+    runtime.write(tokens, np.array([5, 0, 95, 5], dtype=np.uint32))
+    rows_out = runtime.tensor(4, k)
+    runtime.embed(w, tokens, rows_out)   # the embedding gather (select.rs:29-49 over the format's fetch)
+    table = oracle.unpack(element, n * k, packed).reshape(n, k)
+    assert np.array_equal(bits(runtime.read(rows_out)), bits(table[[5, 0, 95, 5]]))
+    # nothing seals these formats, and no staged product takes them
+    with pytest.raises(nb.NeuraCudaError):
+        runtime.seal_device(element, n, k, w.ptr)

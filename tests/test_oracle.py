@@ -280,3 +280,105 @@ def test_the_q6k_packer_follows_the_reference_to_the_letter(oracle):
     # a block of zeros: every code is the bias 32 (high bits 10 in all four groups), scales and d are zero; 210 bytes
     # padded to whole words
     assert oracle.pack(oracle.Q6K, np.zeros(256, np.float32)).tolist() == [0] * 128 + [170] * 64 + [0] * 20
+
+
+def q5k_numpy(blocks):
+    """An independent restatement of the published GGML Q5_K layout for [count, 176] bytes: d, dmin, twelve bytes of
+    six-bit scales and mins, qh 32, qs 128; numbers 64 group + 32 seat + lane."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 176)
+    d = blocks[:, 0:2].copy().view(np.float16).astype(np.float32)[:, 0]
+    dmin = blocks[:, 2:4].copy().view(np.float16).astype(np.float32)[:, 0]
+    sc = blocks[:, 4:16].astype(np.int32)
+    qh, qs = blocks[:, 16:48].astype(np.int32), blocks[:, 48:176].astype(np.int32)
+    out = np.zeros((blocks.shape[0], 256), dtype=np.float32)
+    for sub in range(8):
+        if sub < 4:
+            scale, low = sc[:, sub] & 63, sc[:, sub + 4] & 63
+        else:
+            scale = (sc[:, sub + 4] & 15) | ((sc[:, sub - 4] >> 6) << 4)
+            low = (sc[:, sub + 4] >> 4) | ((sc[:, sub] >> 6) << 4)
+        group, seat = sub // 2, sub % 2
+        nibble = qs[:, group * 32: group * 32 + 32]
+        nibble = (nibble >> 4) if seat else (nibble & 15)
+        code = (nibble | (((qh >> sub) & 1) << 4)).astype(np.float32)
+        out[:, sub * 32: sub * 32 + 32] = (d * scale.astype(np.float32))[:, None] * code - (dmin * low.astype(np.float32))[:, None]
+    return out
+
+
+def q3k_numpy(blocks):
+    """An independent restatement of the published GGML Q3_K layout for [count, 110] bytes: hmask 32, qs 64, twelve bytes
+    of six-bit scales, d; numbers 128 half + 32 j + lane, run 8 half + 2 j + lane // 16."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 110)
+    hmask, qs, sc = blocks[:, :32].astype(np.int32), blocks[:, 32:96].astype(np.int32), blocks[:, 96:108].astype(np.int32)
+    d = blocks[:, 108:110].copy().view(np.float16).astype(np.float32)[:, 0]
+    out = np.zeros((blocks.shape[0], 256), dtype=np.float32)
+    for run in range(16):
+        low = sc[:, run % 8]
+        code = ((low >> 4) if run >= 8 else (low & 15)) | (((sc[:, 8 + run % 4] >> (2 * (run // 4))) & 3) << 4)
+        half, j, upper = run // 8, (run % 8) // 2, run % 2
+        lanes = slice(upper * 16, upper * 16 + 16)
+        two = (qs[:, half * 32: half * 32 + 32][:, lanes] >> (2 * j)) & 3
+        third = (hmask[:, lanes] >> (half * 4 + j)) & 1
+        quant = (two - np.where(third == 1, 0, 4)).astype(np.float32)
+        at = half * 128 + j * 32 + upper * 16
+        out[:, at: at + 16] = (d * (code.astype(np.float32) - np.float32(32.0)))[:, None] * quant
+    return out
+
+
+def random_blocks(seed, count, size, halves):
+    """Random bytes with finite half floats at the byte offsets ``halves`` (a real GGUF holds finite scales)."""
+    rng = np.random.default_rng(seed)
+    blocks = rng.integers(0, 256, (count, size), dtype=np.uint8)
+    for at in halves:
+        blocks[:, at: at + 2] = rng.uniform(-0.01, 0.01, count).astype(np.float16).view(np.uint8).reshape(count, 2)
+    return blocks
+
+
+@pytest.mark.parametrize("name,size,halves,restated", [("Q5K", 176, (0, 2), q5k_numpy), ("Q3K", 110, (108,), q3k_numpy)])
+def test_the_q5k_and_q3k_walks_agree_across_restatements(oracle, name, size, halves, restated):
+    # crates/neura-abi/tests/layout.rs pins the block sizes; each walk is stated in ggml.rs (q5_k_values :318-334,
+    # q3_k_values :292-308) and again in fetch.rs (:269-282, :242-254)
+    element = getattr(oracle, name)
+    assert oracle.payload_bytes(element, 256) == size and oracle.payload_bytes(element, 257) == 2 * size
+    blocks = random_blocks(17, 64, size, halves)
+    packed = blocks.reshape(-1)
+    unpacked = oracle.unpack(element, 64 * 256, packed)
+    assert np.array_equal(bits(unpacked), bits(restated(blocks).reshape(-1)))
+    lib = oracle.lib()
+    fetched = np.array([lib.nro_fetch(element, packed.ctypes.data, at) for at in range(0, 64 * 256, 7)], dtype=np.float32)
+    assert np.array_equal(bits(fetched), bits(unpacked[::7]))
+
+
+def test_the_q5k_and_q3k_packers_follow_the_reference(oracle):
+    w = oracle.Stream(5).normal(4 * 512, 0.0, 0.02).reshape(4, 512)
+    # q5_k (ggml.rs:310-312): affine_block with 31 steps; half a step of the sub-block's own span, plus what the six-bit
+    # scale and min and the half-float d and dmin lose
+    back = oracle.unpack(oracle.Q5K, w.size, oracle.pack_rows(oracle.Q5K, w)).reshape(w.shape)
+    runs = w.reshape(4, 16, 32)
+    span = np.maximum(runs.max(axis=2), 0) - np.minimum(runs.min(axis=2), 0)
+    assert np.all(np.abs(back - w).reshape(4, 16, 32) <= (span / 31.0)[:, :, None] * 1.6 + 1e-4)
+    # q3_k (ggml.rs:243-290): codes -4..3 times a quarter of the run's peak (rounded to 1/31 of the block's widest):
+    # half a step inside the range, a whole step at the positive peak whose quotient 4 is clamped to 3 (three steps, each
+    # off by up to half of d = widest / 124)
+    packed = oracle.pack_rows(oracle.Q3K, w)
+    assert packed.size == 4 * 2 * 110
+    back = oracle.unpack(oracle.Q3K, w.size, packed).reshape(w.shape)
+    peak = np.abs(w).reshape(4, 32, 16).max(axis=2, keepdims=True)
+    widest = np.abs(w).reshape(4, 2, 256).max(axis=2).repeat(16, axis=1)[:, :, None]
+    assert np.all(np.abs(back - w).reshape(4, 32, 16) <= peak / 4.0 + 2.0 * widest / 124.0 + 1e-5)
+    # a block of zeros: d is the smallest normal over 124 (a half-float zero), every scale code the bias 32, every code
+    # zero with its third bit set
+    zero = oracle.pack(oracle.Q3K, np.zeros(256, np.float32)).tolist()
+    assert zero[:32] == [255] * 32 and zero[32:96] == [0] * 64 and zero[96:104] == [0] * 8 and zero[104:108] == [170] * 4
+    assert zero[108:110] == [0, 0] and len(zero) == 112   # 110 bytes padded to whole words
+
+
+def test_sixteen_bit_weights_round_as_the_reference_packs_them(oracle):
+    # crates/neura-precision/src/lib.rs:8-9, :34-42: half::f16::from_f32 and the bfloat16 of :325-329, both to nearest even
+    w = np.array([1.0, -2.5, 1.0009765625, 1.00048828125, 65504.0, 1e-8, 3.140625, 1.00390625, 1.001953125], dtype=np.float32)
+    halves = oracle.unpack(oracle.HALF, w.size, oracle.pack(oracle.HALF, w))
+    assert np.array_equal(bits(halves), bits(w.astype(np.float16).astype(np.float32)))
+    brains = oracle.unpack(oracle.BFLOAT16, w.size, oracle.pack(oracle.BFLOAT16, w))
+    rounded = ((w.view(np.uint32).astype(np.uint64) + 0x7fff + ((w.view(np.uint32) >> 16) & 1)) >> 16 << 16).astype(np.uint32)
+    assert np.array_equal(bits(brains), rounded)
+    assert oracle.payload_bytes(oracle.HALF, 7) == 14 and oracle.pack(oracle.HALF, w[:7]).size == 16
