@@ -369,6 +369,30 @@ def secondary_lines(rt, torch, tstream, device, peaks, main_weights, main_norms,
         rt.sync()
         ms = e0.elapsed_time(e1) / steps
         out["decode_batch16"] = {"ms_per_step": ms, "tok_s": rows / ms * 1e3, "launches_per_step": decoder.launches_per_token()}
+    # the 32B head as common GGUF mixes keep it: Q6_K [152064 x 5120] in GGUF order, batch 1 (639 MB, larger than L2)
+    n, k = 152064, 5120
+    rng = np.random.default_rng(43)
+    blocks = rng.integers(0, 256, (n * (k // 256), 210), dtype=np.uint8)
+    blocks[:, 208:210] = rng.uniform(-2e-3, 2e-3, blocks.shape[0]).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    head = rt.load(nb.Q6K, n, k, blocks.reshape(-1))
+    del blocks
+    x, y = rt.tensor(1, k), rt.tensor(1, n)
+    rt.write(x, rng.standard_normal((1, k)).astype(np.float32))
+    for _ in range(3):
+        rt.linear(head, x, y)
+    rt.sync()
+    e0.record(tstream)
+    for _ in range(8):
+        rt.linear(head, x, y)
+    e1.record(tstream)
+    rt.sync()
+    us = e0.elapsed_time(e1) / 8 * 1e3
+    algorithmic = nb.payload_bytes(nb.Q6K, n * k) + 4 * (k + n)
+    out["q6_k_head_152064x5120_b1"] = {"algorithmic_bytes": algorithmic, "us": us, "gbs": algorithmic / us / 1e3,
+                                       "frac_of_hbm": algorithmic / us / 1e3 / hbm, "kernel": "qlinear_rows_q6k_kernel (GGUF order)"}
+    rt.free(head.ptr)
+    rt.free(x.ptr)
+    rt.free(y.ptr)
     # config 3: the 0.5B decoder, all projections Q8_0, 128-token prompt, 128 tokens
     shape = workload_shape("qwen2.5-0.5b-q8_0")
     config = qwen_config(shape)

@@ -11,7 +11,9 @@
 // nibble, sc and m six-bit integers per 32-element sub-block and d, dmin half floats per 256-element super-block.
 // So   sum_k w_k x_k = sum_sb d_sb * sum_{k in sb} (sc q)_k x_k  -  sum_sb sum_sub (dmin_sb m_sub) * (sum of x over the sub-block).
 //   * First sum, A operand: sc * q as a half float (an integer below 1024: exact), 128 weight rows x 128 k per
-//     stage.  B operand: the activations as half floats.  Each 256-element stretch of a row is scaled by a power of
+//     stage, written by the producers straight into tensor memory (tcgen05.st: lane = weight row, a column = two
+//     consecutive half floats of K) and read from there by the MMA, so the operand never crosses shared memory.
+//     B operand: the activations as half floats.  Each 256-element stretch of a row is scaled by a power of
 //     two so that its peak lies in [2^13, 2^14) and split x = hi + lo * 2^-11, hi = fp16(x), lo = fp16((x - hi) * 2^11):
 //     22 bits of the peak.  hi rows and lo rows are stacked along the MMA's N dimension (N = 2 x rows, padded to 16),
 //     so one MMA serves both.  tcgen05.mma kind::f16 accumulates in f32 in tensor memory; products of integers below
@@ -23,20 +25,21 @@
 //     like the activations.  They accumulate into a third accumulator that is read once per item.
 //
 // Roles of a CTA (one per SM, persistent over (128-row tile, K slice) items):
-//   warps 0-15  producers, a thread per (two weight rows, eight quant bytes of each 64-k step), eight warps for each of
-//               the two stages of a super-block: wait for a super-block of raw units in the raw ring, turn nibbles into sc * q (two weights per instruction: the nibble is or-ed into
-//               the mantissa of 1024, one HFMA2 multiplies by sc and takes the 1024 sc away; the four half-float
-//               constants of a scale come from a 64-entry table in shared memory) and store them 128-byte swizzled,
-//               K-major, into the A tiles of a ring stage;
+//   warps 0-15  producers, a thread per (weight row, 128-k stage of every other super-block): wait for a super-block of
+//               raw units in the raw ring, turn the row's 64 quant bytes into 128 values sc * q (two weights per
+//               instruction: the nibble is or-ed into the mantissa of 1024, one HFMA2 multiplies by sc and takes the
+//               1024 sc away; the half-float constants of a scale come from a 64-entry table in shared memory) and
+//               store them into the 64 columns of a tensor-memory stage;
 //   warps 16-19 epilogue: read the accumulator of a finished super-block (tcgen05.ld), scale, add up; at the end of
 //               an item take the second sum away, apply the fused chain and store, or leave a partial for the last
 //               slice to arrive;
 //   warp 20     one thread issues the MMAs;  warp 21: one thread asks the tensor memory accelerator for the activation
 //               tiles (a ring of their own: a load's latency is several stages long);  warp 22: one thread issues the
-//               bulk copies of the raw weight units and asks the units of later super-blocks into L2.
-// A stage is 128 k (two 64-k tiles) because the cost of a stage is mostly fixed: the waits, the proxy fence, the
-// arrival and, for the one thread that issues MMAs, its own instruction stream.  (With 64-k stages and the second sum
-// as a fifth step of every super-block that thread took 0.5 us a step and the kernel ran at 0.2 of the HBM rate.)
+//               bulk copies of the raw weight units into a ring of four super-blocks (asking later ones into L2 as well made
+//               the kernel slower).
+// Tensor memory: four A stages of 64 columns, then two accumulators of the first sum and one of the second (N columns
+// each).  A stage is 128 k because the cost of a stage is mostly fixed: the waits, the fences, the arrival and, for the
+// one thread that issues MMAs, its own instruction stream.
 // Every wait is bounded; a wait that runs out raises the status word, and the CTA still frees its tensor memory.
 #pragma once
 #include <cuda.h>
@@ -50,12 +53,12 @@ namespace nc {
 
 constexpr uint32_t kSkTileRows = 128;                   // weight rows of one item: the M of the MMA
 constexpr uint32_t kSkMaxRows = 32;                     // activation rows one launch carries
-constexpr uint32_t kSkATile = kSkTileRows * 128;        // 16 KiB: 128 rows x 64 half floats
-constexpr uint32_t kSkStageBytes = 2 * kSkATile;        // a stage: 128 k as two 64-k tiles
+constexpr uint32_t kSkStageCols = 64;                   // a stage of the A operand in tensor memory: 128 k as half floats, two to a column
 constexpr uint32_t kSkStages = 4;
+constexpr uint32_t kSkAccAt = kSkStages * kSkStageCols; // the accumulators follow the A stages
+constexpr uint32_t kSkTmemCols = 512;                   // 256 columns of A stages + three accumulators of at most 64
 constexpr uint32_t kSkRawStage = 4 * kQ4kStage;         // 18 KiB: the four 32-row units of one super-block
-constexpr uint32_t kSkRawStages = 2;                    // (the producers take a stage into registers at once)
-constexpr uint32_t kSkRawAhead = 4;                     // super-blocks asked into L2 ahead of the ring
+constexpr uint32_t kSkRawStages = 4;
 constexpr uint32_t kSkXRing = 60 * 1024;                // activation tiles: a ring of their own
 constexpr uint32_t kSkXStagesMost = 8;
 constexpr uint32_t kSkProducerWarps = 16, kSkEpilogueWarp0 = 16, kSkMmaWarp = 20, kSkTmaWarp = 21, kSkRawWarp = 22;
@@ -66,12 +69,7 @@ __host__ __device__ constexpr uint32_t skinny_x_stages(uint32_t bpad) {
     return kSkXRing / (2u * bpad * 256u) < kSkXStagesMost ? kSkXRing / (2u * bpad * 256u) : kSkXStagesMost;
 }
 __host__ __device__ inline uint32_t skinny_smem_bytes(uint32_t bpad) {
-    return 1024u + kSkStages * kSkStageBytes + skinny_x_stages(bpad) * 2u * bpad * 256u + kSkRawStages * kSkRawStage +
-           kSkBarriers * 8u + 64u;
-}
-__host__ __device__ inline uint32_t skinny_tmem_columns(uint32_t bpad) {
-    const uint32_t want = 6u * bpad;   // three accumulators of N = 2 bpad columns
-    return want <= 32u ? 32u : want <= 64u ? 64u : want <= 128u ? 128u : 256u;
+    return 1024u + skinny_x_stages(bpad) * 2u * bpad * 256u + kSkRawStages * kSkRawStage + kSkBarriers * 8u + 64u;
 }
 // Columns of the table of sub-block sums: 16 a super-block, padded so that every 128-column stage lies inside.
 __host__ __device__ inline uint32_t skinny_sx_cols(uint32_t nsb) { return (nsb * 16u + 127u) / 128u * 128u; }
@@ -294,26 +292,41 @@ __device__ __forceinline__ uint2 lds8(uint32_t addr) {
     return v;
 }
 
-// One weight row's 64 k of a step.  Its eight quant bytes (w0, w1) hold elements 8t.. of sub-block 2G in their low
-// nibbles and of sub-block 2G+1 in their high nibbles.  The row stores two 16-byte chunks; which nibble kind goes first
-// depends on the row's parity (`first_mask` 0x000f000f: the low nibbles, 0x00f000f0: the high ones; `first` and `second`
-// the half-float constants of their sub-blocks' scales from the scale table; `at_first`, `at_second` the chunks'
-// addresses): an even and an odd row of the eight lanes that store together then cover all eight 16-byte columns of a
-// 128-byte line, where both rows' low chunks would land on the same four.
-//   low nibbles:            (1024 + q) * sc - 1024 sc          (entry halves (sc, sc), (-1024 sc, -1024 sc))
-//   high nibbles, in place: (1024 + 16 q) * (sc / 16) - 64 sc  (entry halves (sc / 16) x 2, (-64 sc) x 2)
+// Thirty-two nibbles of one kind (`mask` 0x000f000f: the low ones, 0x00f000f0: the high ones, in place) out of a weight
+// row's 32 quant bytes, times their sub-block's scale, as sixteen pairs of half floats.  `mul` and `bias` are the scale's
+// constants from the scale table:
+//   low nibbles:            (1024 + q) * sc - 1024 sc          (halves (sc, sc), (-1024 sc, -1024 sc))
+//   high nibbles, in place: (1024 + 16 q) * (sc / 16) - 64 sc  (halves (sc / 16) x 2, (-64 sc) x 2)
 // A mask and an or turn the nibbles of bytes 0 and 2 of a word into two half floats at once (bytes 1 and 3 after a
-// shift), so the eight elements of a chunk are stored in the order 0 2 1 3 4 6 5 7; the activation staging stores its
-// chunks in the same order (kSkChunkOrder), and a dot product does not mind.
-__device__ __forceinline__ void skinny_row_step(uint32_t at_first, uint32_t at_second, uint32_t w0, uint32_t w1, uint2 first, uint2 second,
-                                                uint32_t first_mask, uint32_t second_mask) {
-    const uint32_t s0 = w0 >> 8, s1 = w1 >> 8;
-    const uint32_t a0 = hfma2_bits((w0 & first_mask) | 0x64006400u, first.x, first.y), a1 = hfma2_bits((s0 & first_mask) | 0x64006400u, first.x, first.y);
-    const uint32_t a2 = hfma2_bits((w1 & first_mask) | 0x64006400u, first.x, first.y), a3 = hfma2_bits((s1 & first_mask) | 0x64006400u, first.x, first.y);
-    const uint32_t b0 = hfma2_bits((w0 & second_mask) | 0x64006400u, second.x, second.y), b1 = hfma2_bits((s0 & second_mask) | 0x64006400u, second.x, second.y);
-    const uint32_t b2 = hfma2_bits((w1 & second_mask) | 0x64006400u, second.x, second.y), b3 = hfma2_bits((s1 & second_mask) | 0x64006400u, second.x, second.y);
-    sts16(at_first, a0, a1, a2, a3);
-    sts16(at_second, b0, b1, b2, b3);
+// shift), so every eight elements come out in the order 0 2 1 3 4 6 5 7; the activation staging stores its numbers in
+// the same order (kSkChunkOrder), and a dot product does not mind.
+__device__ __forceinline__ void skinny_scaled(const uint2 (&q)[4], uint32_t mask, uint32_t mul, uint32_t bias, uint32_t (&out)[16]) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const uint32_t w0 = q[t].x, w1 = q[t].y, s0 = w0 >> 8, s1 = w1 >> 8;
+        out[4 * t + 0] = hfma2_bits((w0 & mask) | 0x64006400u, mul, bias);
+        out[4 * t + 1] = hfma2_bits((s0 & mask) | 0x64006400u, mul, bias);
+        out[4 * t + 2] = hfma2_bits((w1 & mask) | 0x64006400u, mul, bias);
+        out[4 * t + 3] = hfma2_bits((s1 & mask) | 0x64006400u, mul, bias);
+    }
+}
+
+// Sixteen 32-bit columns of this thread's tensor-memory lane (the warp's 32 lanes start at the address's lane).
+__device__ __forceinline__ void tmem_store_16(uint32_t address, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(address),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+                 "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D (+)= A B with the A operand in tensor memory (lane = row of A, a column = two consecutive half floats of K) and B
+// through a shared-memory descriptor.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 // The byte of sub-block `sub` out of the two words q4k_scales returns.
@@ -361,7 +374,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     constexpr uint32_t BPAD = NB * 8, N = 2 * BPAD;
     constexpr uint32_t kXTile = N * 128, kXStage = 2 * kXTile, kXStages = skinny_x_stages(BPAD);
     const uint32_t base = (smem_addr(skinny_raw) + 1023u) & ~1023u;
-    const uint32_t ring = base, xring = ring + kSkStages * kSkStageBytes, raw = xring + kXStages * kXStage;
+    const uint32_t xring = base, raw = xring + kXStages * kXStage;
     const uint32_t bars = raw + kSkRawStages * kSkRawStage;
     const uint32_t a_full = bars, a_empty = a_full + 8 * kSkStages, x_full = a_empty + 8 * kSkStages;
     const uint32_t x_empty = x_full + 8 * kSkXStagesMost, raw_full = x_empty + 8 * kSkXStagesMost;
@@ -381,7 +394,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     if (tid == 0) {
         failed = 0;
         for (uint32_t s = 0; s < kSkStages; ++s) {
-            mbar_init(a_full + 8 * s, kSkProducerWarps / 2);   // the eight producer warps that write the stage
+            mbar_init(a_full + 8 * s, 4);                  // the four producer warps that write the stage
             mbar_init(a_empty + 8 * s, 1);                 // one tcgen05.commit
         }
         for (uint32_t s = 0; s < kXStages; ++s) {
@@ -390,7 +403,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
         }
         for (uint32_t s = 0; s < kSkRawStages; ++s) {
             mbar_init(raw_full + 8 * s, 1);
-            mbar_init(raw_empty + 8 * s, kSkProducerWarps);
+            mbar_init(raw_empty + 8 * s, kSkProducerWarps / 2);   // the eight warps that take the super-block
         }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(d_full + 8 * b, 1);
@@ -401,7 +414,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == kSkMmaWarp) tmem_alloc(slot, skinny_tmem_columns(BPAD));
+    if (warp == kSkMmaWarp) tmem_alloc(slot, kSkTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -409,54 +422,66 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp < kSkProducerWarps) {
-        // ---------------- producers: raw units -> sc * q tiles ----------------
-        // Warp w serves half-unit w / 2 (rows g and g + 8 of its 16, lane (g, t)) and, of every super-block, the 128-k
-        // stage w % 2: the two stages of a super-block are written side by side by two sets of eight warps.  Ring
-        // positions are counted over the whole launch: the stages of super-block i of an item sit at base + 2 i and
-        // base + 2 i + 1, the stages of the second sum follow them.
-        const uint32_t g = lane >> 2, t = lane & 3, mine = warp & 1u, hu = warp >> 1;
-        const uint32_t row = hu * 16 + g, turn = row & 7, odd = row & 1u;   // (row + 8 has the same parity and turn)
+        // ---------------- producers: raw units -> sc * q in tensor memory ----------------
+        // A warp reaches the 32 tensor-memory lanes of its rank in its group of four, so warp w writes weight rows
+        // 32 (w % 4) + lane: lane l is row l of 32-row unit w % 4.  It takes stage (w / 4) % 2 (128 k: nibble groups
+        // 2 h and 2 h + 1, each 32 quant bytes of the row whose low nibbles are one sub-block and whose high nibbles the
+        // next) of every other super-block, the even ones of the CTA's run for warps 0-7, the odd ones for warps 8-15:
+        // a thread then pays for its row's header, its waits and its arrivals once per 128 k, and the two sets of warps
+        // work on neighbouring super-blocks at the same time.  Ring positions are counted over the whole launch: the
+        // stages of super-block i of an item sit at base + 2 i and base + 2 i + 1, the stages of the second sum follow.
+        const uint32_t quarter = warp & 3u, mine = (warp >> 2) & 1u, parity = warp >> 3;
+        const uint32_t hu = lane >> 4, r16 = lane & 15, g = r16 & 7, upper = r16 >> 3;
         const uint32_t table = smem_addr(scale_table);
-        // per thread, once: which nibble kind it stores first (see skinny_row_step)
-        const uint32_t first_mask = odd ? 0x00f000f0u : 0x000f000fu, second_mask = odd ? 0x000f000fu : 0x00f000f0u;
-        const uint32_t first_sub = odd, second_sub = odd ^ 1u;              // sub-block 2G + ... of the first / second chunk
-        const uint32_t first_half = odd * 8, second_half = (odd ^ 1u) * 8;  // the table entry's half: low or high nibble form
-        const uint32_t at_first = row * 128 + (((odd ? 4 + t : t) ^ turn) << 4), at_second = row * 128 + (((odd ? t : 4 + t) ^ turn) << 4);
+        const uint32_t my_unit = quarter * kQ4kStage + hu * kQ4kUnit;                        // this row's half-unit inside a raw stage
+        const uint32_t my_quants = my_unit + 256 + 2 * mine * 512 + g * 64 + upper * 8;      // + 512 j + 16 t: quant bytes 8 t ... of group 2 h + j
+        const uint32_t my_columns = tmem + ((quarter * 32u) << 16);                          // + the stage's first column
         uint32_t base = 0;   // ring position of the running item's first stage
+        uint32_t seq = 0;    // super-blocks of this CTA so far
         SkRing at_raw;
         bool alive = true;
         uint32_t events = 0;
         for (uint32_t item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
             uint32_t tile, sb0, sb1;
             skinny_slice(p, item, tile, sb0, sb1);
-            for (uint32_t sb = sb0; sb < sb1 && alive; ++sb) {
-                if (!mbar_wait(raw_full + 8 * at_raw.s, at_raw.phase)) { alive = false; break; }
-                if (tid == 0) { SK_TRACE(0, events); }
-                const uint32_t half_unit = raw + at_raw.s * kSkRawStage + hu * kQ4kUnit;
-                const uint4 h0 = lds16(half_unit + g * 16), h1 = lds16(half_unit + (g + 8) * 16);
-                const uint4 q0 = lds16(half_unit + 256 + (2 * mine) * 512 + lane * 16), q1 = lds16(half_unit + 256 + (2 * mine + 1) * 512 + lane * 16);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(raw_empty + 8 * at_raw.s);
+            for (uint32_t sb = sb0; sb < sb1 && alive; ++sb, ++seq) {
+                const uint32_t raw_slot = at_raw.s, raw_phase = at_raw.phase;
                 at_raw.next(kSkRawStages);
-                uint32_t sc0[2], mn0[2], sc1[2], mn1[2];
-                q4k_scales(h0.y, h0.z, h0.w, sc0, mn0);
-                q4k_scales(h1.y, h1.z, h1.w, sc1, mn1);
-                const uint32_t G = 2 * mine;   // this warp's two 64-k tiles of the super-block: nibble groups G and G + 1
-                const uint2 f00 = lds8(table + k4_byte(sc0, 2 * G + first_sub) * 16 + first_half), s00 = lds8(table + k4_byte(sc0, 2 * G + second_sub) * 16 + second_half);
-                const uint2 f01 = lds8(table + k4_byte(sc0, 2 * G + 2 + first_sub) * 16 + first_half), s01 = lds8(table + k4_byte(sc0, 2 * G + 2 + second_sub) * 16 + second_half);
-                const uint2 f10 = lds8(table + k4_byte(sc1, 2 * G + first_sub) * 16 + first_half), s10 = lds8(table + k4_byte(sc1, 2 * G + second_sub) * 16 + second_half);
-                const uint2 f11 = lds8(table + k4_byte(sc1, 2 * G + 2 + first_sub) * 16 + first_half), s11 = lds8(table + k4_byte(sc1, 2 * G + 2 + second_sub) * 16 + second_half);
+                if ((seq & 1u) != parity) continue;
+                if (!mbar_wait(raw_full + 8 * raw_slot, raw_phase)) { alive = false; break; }
+                if (tid == 0) { SK_TRACE(0, events); }
+                const uint32_t stage = raw + raw_slot * kSkRawStage;
+                const uint4 header = lds16(stage + my_unit + r16 * 16);
+                uint2 q[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) q[j][t] = lds8(stage + my_quants + 512 * j + 16 * t);
+                // the six-bit scales of sub-blocks 4 h ... 4 h + 3, a byte each (q4k_scales' first or second word)
+                const uint32_t scales = mine ? ((header.w & 0x0f0f0f0fu) | (((header.y >> 6) & 0x03030303u) << 4)) : (header.y & 0x3f3f3f3fu);
+                const uint2 low0 = lds8(table + (scales & 0xffu) * 16), high0 = lds8(table + ((scales >> 8) & 0xffu) * 16 + 8);
+                const uint2 low1 = lds8(table + ((scales >> 16) & 0xffu) * 16), high1 = lds8(table + (scales >> 24) * 16 + 8);
                 const uint32_t position = base + 2 * (sb - sb0) + mine, slot_a = position % kSkStages;
                 if (!SK_WAIT_A(a_empty + 8 * slot_a, ((position / kSkStages) & 1u) ^ 1u)) { alive = false; break; }
                 if (tid == 0) { SK_TRACE(1, events); }
-                const uint32_t stage = ring + slot_a * kSkStageBytes;
-                skinny_row_step(stage + at_first, stage + at_second, q0.x, q0.y, f00, s00, first_mask, second_mask);
-                skinny_row_step(stage + at_first + 1024, stage + at_second + 1024, q0.z, q0.w, f10, s10, first_mask, second_mask);
-                if (tid == 0) { SK_TRACE(5, events); }
-                skinny_row_step(stage + kSkATile + at_first, stage + kSkATile + at_second, q1.x, q1.y, f01, s01, first_mask, second_mask);
-                skinny_row_step(stage + kSkATile + at_first + 1024, stage + kSkATile + at_second + 1024, q1.z, q1.w, f11, s11, first_mask, second_mask);
+                tc_fence_after();
+                const uint32_t columns = my_columns + slot_a * kSkStageCols;
+                uint32_t out[16];
+                skinny_scaled(q[0], 0x000f000fu, low0.x, low0.y, out);
+                tmem_store_16(columns, out);
+                skinny_scaled(q[0], 0x00f000f0u, high0.x, high0.y, out);
+                tmem_store_16(columns + 16, out);
+                skinny_scaled(q[1], 0x000f000fu, low1.x, low1.y, out);
+                tmem_store_16(columns + 32, out);
+                skinny_scaled(q[1], 0x00f000f0u, high1.x, high1.y, out);
+                // every lane's loads of the raw stage have delivered (their values are in `out` and in the stores): the
+                // stage may be refilled.  (An arrival right behind the loads let the refill overtake loads still in flight.)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(raw_empty + 8 * raw_slot);
+                tmem_store_16(columns + 48, out);
                 if (tid == 0) { SK_TRACE(8, events); }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tiles through the async proxy
+                tmem_store_wait();
+                tc_fence_before();
                 if (tid == 0) { SK_TRACE(9, events); }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(a_full + 8 * slot_a);
@@ -465,36 +490,46 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
             }
             if (!alive) break;
             base += 2 * (sb1 - sb0);
-            // ---- the second sum: dmin * m of eight super-blocks a stage; this thread's two rows, super-block 4 j + t of the stage ----
-            const uint32_t held = min(tile * 4 + (row >> 5), p.tiles32 - 1);
-            const uint8_t *headers = p.w + ((uint64_t)held * p.nsb * 2 + ((row >> 4) & 1u)) * kQ4kUnit + (row & 15) * 16;
+            // ---- the second sum: dmin * m of eight super-blocks a stage, 16 half floats = 8 columns a super-block.  The
+            //      warps of the even super-blocks take these stages, stage h of the ring position's parity. ----
+            const uint32_t held = min(tile * 4 + quarter, p.tiles32 - 1);
+            const uint8_t *headers = p.w + ((uint64_t)held * p.nsb * 2 + hu) * kQ4kUnit + r16 * 16;
             for (uint32_t first = sb0; first < sb1 && alive; first += 8, ++base) {
-                if ((base & 1u) != mine) continue;   // the stages of the second sum go to the two sets of warps in turn
-                uint4 h[2][2];
-#pragma unroll
-                for (uint32_t j = 0; j < 2; ++j) {
-                    const uint32_t sb = first + 4 * j + t;
-                    const bool there = sb < sb1;
-                    h[j][0] = there ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit) : make_uint4(0u, 0u, 0u, 0u);
-                    h[j][1] = there ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit + 128) : make_uint4(0u, 0u, 0u, 0u);   // row + 8
-                }
+                if (parity != 0u || (base & 1u) != mine) continue;
                 const uint32_t slot_a = base % kSkStages;
-                if (!SK_WAIT_A(a_empty + 8 * slot_a, ((base / kSkStages) & 1u) ^ 1u)) { alive = false; break; }
-                const uint32_t stage = ring + slot_a * kSkStageBytes;
+                bool waited = false;
 #pragma unroll
-                for (uint32_t j = 0; j < 2; ++j) {
+                for (uint32_t round = 0; round < 2; ++round) {
+                    uint4 h[4];
 #pragma unroll
-                    for (uint32_t r = 0; r < 2; ++r) {
-                        uint32_t sc[2], mn[2];
-                        q4k_scales(h[j][r].y, h[j][r].z, h[j][r].w, sc, mn);
-                        const float dmin = half_bits_to_float(h[j][r].x >> 16);   // (a super-block past the slice reads as zeros)
-                        const uint4 c0 = skinny_min_chunk(dmin, mn[0]), c1 = skinny_min_chunk(dmin, mn[1]);
-                        const uint32_t at = stage + j * kSkATile + (row + 8 * r) * 128;
-                        sts16(at + (((2 * t) ^ turn) << 4), c0.x, c0.y, c0.z, c0.w);
-                        sts16(at + (((2 * t + 1) ^ turn) << 4), c1.x, c1.y, c1.z, c1.w);
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint32_t sb = first + 4 * round + j;
+                        h[j] = sb < sb1 ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    if (!waited) {
+                        if (!SK_WAIT_A(a_empty + 8 * slot_a, ((base / kSkStages) & 1u) ^ 1u)) { alive = false; break; }
+                        tc_fence_after();
+                        waited = true;
+                    }
+#pragma unroll
+                    for (uint32_t pair = 0; pair < 2; ++pair) {
+                        uint32_t out[16];
+#pragma unroll
+                        for (uint32_t j = 0; j < 2; ++j) {
+                            const uint4 &held_header = h[2 * pair + j];
+                            uint32_t sc[2], mn[2];
+                            q4k_scales(held_header.y, held_header.z, held_header.w, sc, mn);
+                            const float dmin = half_bits_to_float(held_header.x >> 16);   // (a super-block past the slice reads as zeros)
+                            const uint4 c0 = skinny_min_chunk(dmin, mn[0]), c1 = skinny_min_chunk(dmin, mn[1]);
+                            out[8 * j + 0] = c0.x; out[8 * j + 1] = c0.y; out[8 * j + 2] = c0.z; out[8 * j + 3] = c0.w;
+                            out[8 * j + 4] = c1.x; out[8 * j + 5] = c1.y; out[8 * j + 6] = c1.z; out[8 * j + 7] = c1.w;
+                        }
+                        tmem_store_16(my_columns + slot_a * kSkStageCols + 32 * round + 16 * pair, out);
                     }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (!alive) break;
+                tmem_store_wait();
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(a_full + 8 * slot_a);
             }
@@ -524,7 +559,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
                 if (!mbar_wait(d_full + 8 * b, (seq >> 1) & 1u)) { alive = false; break; }
                 if (quarter == 0 && lane == 0) { SK_TRACE(6, seq); }
                 tc_fence_after();
-                const uint32_t d1 = tmem + lanes + b * N;
+                const uint32_t d1 = tmem + lanes + kSkAccAt + b * N;
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     uint32_t hi[8], lo[8];
@@ -548,7 +583,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
             if (!mbar_wait(m_full, items_done & 1u)) { alive = false; break; }
             tc_fence_after();
             {
-                const uint32_t d2 = tmem + lanes + 2 * N;
+                const uint32_t d2 = tmem + lanes + kSkAccAt + 2 * N;
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     uint32_t hi[8], lo[8];
@@ -608,7 +643,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     } else if (warp == kSkMmaWarp) {
         // ---------------- MMA issue (the whole warp walks the loop; one lane issues) ----------------
         const uint32_t idesc = skinny_instruction(kSkTileRows, N);
-        const uint64_t a_desc0 = smem_descriptor(ring), x_desc0 = smem_descriptor(xring);
+        const uint64_t x_desc0 = smem_descriptor(xring);
         SkRing at_a, at_x;
         uint32_t seq = 0, items_done = 0, events = 0;
         bool alive = true;
@@ -618,14 +653,15 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
             if (!mbar_wait(x_full + 8 * at_x.s, at_x.phase)) return false;
             if (lane == 0) { SK_TRACE(3, events); }
             tc_fence_after();
-            const uint64_t desc_a = a_desc0 + (uint64_t)((at_a.s * kSkStageBytes) >> 4), desc_b = x_desc0 + (uint64_t)((at_x.s * kXStage) >> 4);
+            const uint32_t a_columns = tmem + at_a.s * kSkStageCols;
+            const uint64_t desc_b = x_desc0 + (uint64_t)((at_x.s * kXStage) >> 4);
             if (elect_one()) {
 #pragma unroll
                 for (uint32_t j = 0; j < 2; ++j)
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk)   // 16 half floats = 32 bytes further along K inside the swizzle atom
-                        tc_mma_bf16(accumulator, desc_a + j * (kSkATile >> 4) + kk * 2, desc_b + j * (kXTile >> 4) + kk * 2, idesc,
-                                    (fresh && j == 0 && kk == 0) ? 0u : 1u);
+                    for (uint32_t kk = 0; kk < 4; ++kk)   // 16 half floats: 8 columns of A, 32 bytes further along K inside B's swizzle atom
+                        tc_mma_f16_ts(accumulator, a_columns + j * 32 + kk * 8, desc_b + j * (kXTile >> 4) + kk * 2, idesc,
+                                      (fresh && j == 0 && kk == 0) ? 0u : 1u);
                 tc_commit(a_empty + 8 * at_a.s);   // frees the stages when these MMAs have read them
                 tc_commit(x_empty + 8 * at_x.s);
             }
@@ -643,7 +679,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
                 const uint32_t b = seq & 1u;
                 if (!mbar_wait(d_empty + 8 * b, ((seq >> 1) & 1u) ^ 1u)) { alive = false; break; }
                 tc_fence_after();
-                if (!stage_mmas(tmem + b * N, true) || !stage_mmas(tmem + b * N, false)) { alive = false; break; }
+                if (!stage_mmas(tmem + kSkAccAt + b * N, true) || !stage_mmas(tmem + kSkAccAt + b * N, false)) { alive = false; break; }
                 if (elect_one()) tc_commit(d_full + 8 * b);
                 __syncwarp();
             }
@@ -651,7 +687,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
             if (!mbar_wait(m_empty, (items_done & 1u) ^ 1u)) { alive = false; break; }
             tc_fence_after();
             for (uint32_t first = sb0; first < sb1; first += 8)
-                if (!stage_mmas(tmem + 2 * N, first == sb0)) { alive = false; break; }
+                if (!stage_mmas(tmem + kSkAccAt + 2 * N, first == sb0)) { alive = false; break; }
             if (alive && elect_one()) tc_commit(m_full);
             __syncwarp();
         }
@@ -693,12 +729,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
             const uint8_t *unit[4];
 #pragma unroll
             for (uint32_t u = 0; u < 4; ++u) unit[u] = p.w + (uint64_t)min(tile * 4 + u, p.tiles32 - 1) * p.nsb * kQ4kStage;
-            if (lane < 4)   // lane u asks the first units of tile u into L2
-                for (uint32_t sb = sb0; sb < sb1 && sb < sb0 + kSkRawAhead; ++sb)
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(unit[lane] + (uint64_t)sb * kQ4kStage), "r"(kQ4kStage) : "memory");
             for (uint32_t sb = sb0; sb < sb1; ++sb) {
-                if (lane < 4 && sb + kSkRawAhead < sb1)
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(unit[lane] + (uint64_t)(sb + kSkRawAhead) * kQ4kStage), "r"(kQ4kStage) : "memory");
                 if (!mbar_wait(raw_empty + 8 * at_raw.s, at_raw.phase ^ 1u)) { alive = false; break; }
                 if (elect_one()) {
                     mbar_expect(raw_full + 8 * at_raw.s, kSkRawStage);
@@ -715,7 +746,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     tc_fence_before();
     __syncthreads();
     if (failed && tid == 0) atomicOr(p.status, 8u);
-    if (warp == kSkMmaWarp) tmem_free(tmem, skinny_tmem_columns(BPAD));
+    if (warp == kSkMmaWarp) tmem_free(tmem, kSkTmemCols);
 }
 
 }  // namespace nc
