@@ -462,10 +462,6 @@ SkinnyPlan skinny_plan(const nc_context *ctx, uint32_t n, uint32_t k, bool pair,
     plan.splits = 1;
     for (uint32_t s = 1; s <= nsb && s <= 16; ++s) {
         if (s > 1 && (uint64_t)plan.ntile128 * s * bpad * kSkTileRows * sizeof(float) > (16ull << 20)) break;
-        // a split K axis only while every item has a CTA of its own: a CTA that walked several slices in a row left
-        // wrong sums now and then on [7168 x 5120] at 24 and 32 rows (five slices, two items a CTA), and the cause
-        // was not found
-        if (s > 1 && (uint64_t)plan.ntile128 * s > sms) break;
         const uint64_t rounds = ((uint64_t)plan.ntile128 * s + sms - 1) / sms;
         const double cost = (double)rounds * (double)((nsb + s - 1) / s + (s > 1 ? 1 : 0)) * (1.0 + 0.02 * (s - 1));
         if (s == 1 || cost < best) {

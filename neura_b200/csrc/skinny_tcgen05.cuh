@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     if (tid == 0) {
         failed = 0;
         for (uint32_t s = 0; s < kSkStages; ++s) {
-            mbar_init(a_full + 8 * s, 4);                  // the four producer warps that write the stage
+            mbar_init(a_full + 8 * s, 4);                  // the four producer warps of the slot
             mbar_init(a_empty + 8 * s, 1);                 // one tcgen05.commit
         }
         for (uint32_t s = 0; s < kXStages; ++s) {
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
         }
         for (uint32_t s = 0; s < kSkRawStages; ++s) {
             mbar_init(raw_full + 8 * s, 1);
-            mbar_init(raw_empty + 8 * s, kSkProducerWarps / 2);   // the eight warps that take the super-block
+            mbar_init(raw_empty + 8 * s, kSkProducerWarps / 2);   // the eight warps that write the two stages of the super-block
         }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(d_full + 8 * b, 1);
@@ -424,62 +424,103 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
     if (warp < kSkProducerWarps) {
         // ---------------- producers: raw units -> sc * q in tensor memory ----------------
         // A warp reaches the 32 tensor-memory lanes of its rank in its group of four, so warp w writes weight rows
-        // 32 (w % 4) + lane: lane l is row l of 32-row unit w % 4.  It takes stage (w / 4) % 2 (128 k: nibble groups
-        // 2 h and 2 h + 1, each 32 quant bytes of the row whose low nibbles are one sub-block and whose high nibbles the
-        // next) of every other super-block, the even ones of the CTA's run for warps 0-7, the odd ones for warps 8-15:
-        // a thread then pays for its row's header, its waits and its arrivals once per 128 k, and the two sets of warps
-        // work on neighbouring super-blocks at the same time.  Ring positions are counted over the whole launch: the
-        // stages of super-block i of an item sit at base + 2 i and base + 2 i + 1, the stages of the second sum follow.
-        const uint32_t quarter = warp & 3u, mine = (warp >> 2) & 1u, parity = warp >> 3;
+        // 32 (w % 4) + lane: lane l is row l of 32-row unit w % 4.  The stages of the launch are numbered in the order
+        // the MMAs take them (for every item two per super-block, then the stages of its second sum), stage P lives
+        // in ring slot P % 4, and the four warps w / 4 == s write exactly the stages of slot s, whatever they hold.
+        // (A slot's writers must be the same warps every time: the wait for a slot to be free tells phases apart by
+        // one parity bit, which only holds for a warp that wrote the slot's previous stage itself.  With the stages
+        // dealt by super-block instead, a warp running ahead over an item's end took a slot two stages early, now and
+        // then, and two items of a CTA came out wrong.)  A stage of the first sum is 128 k of a super-block: nibble
+        // groups 2 h and 2 h + 1, each 32 quant bytes of the row whose low nibbles are one sub-block and whose high
+        // nibbles the next; a thread pays for its row's header, its waits and its arrivals once per 128 k.
+        const uint32_t quarter = warp & 3u, slot_a = warp >> 2;
         const uint32_t hu = lane >> 4, r16 = lane & 15, g = r16 & 7, upper = r16 >> 3;
         const uint32_t table = smem_addr(scale_table);
-        const uint32_t my_unit = quarter * kQ4kStage + hu * kQ4kUnit;                        // this row's half-unit inside a raw stage
-        const uint32_t my_quants = my_unit + 256 + 2 * mine * 512 + g * 64 + upper * 8;      // + 512 j + 16 t: quant bytes 8 t ... of group 2 h + j
-        const uint32_t my_columns = tmem + ((quarter * 32u) << 16);                          // + the stage's first column
-        uint32_t base = 0;   // ring position of the running item's first stage
-        uint32_t seq = 0;    // super-blocks of this CTA so far
-        SkRing at_raw;
+        const uint32_t my_unit = quarter * kQ4kStage + hu * kQ4kUnit;        // this row's half-unit inside a raw stage
+        const uint32_t my_quants = my_unit + 256 + g * 64 + upper * 8;       // + 1024 h + 512 j + 16 t: quant bytes 8 t ... of group 2 h + j
+        const uint32_t columns = tmem + ((quarter * 32u) << 16) + slot_a * kSkStageCols;
+        uint32_t base = 0;       // number of the running item's first stage
+        uint32_t seq_base = 0;   // super-blocks of this CTA before the running item (the raw ring follows them)
         bool alive = true;
         uint32_t events = 0;
         for (uint32_t item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
             uint32_t tile, sb0, sb1;
             skinny_slice(p, item, tile, sb0, sb1);
-            for (uint32_t sb = sb0; sb < sb1 && alive; ++sb, ++seq) {
-                const uint32_t raw_slot = at_raw.s, raw_phase = at_raw.phase;
-                at_raw.next(kSkRawStages);
-                if ((seq & 1u) != parity) continue;
-                if (!mbar_wait(raw_full + 8 * raw_slot, raw_phase)) { alive = false; break; }
-                if (tid == 0) { SK_TRACE(0, events); }
-                const uint32_t stage = raw + raw_slot * kSkRawStage;
-                const uint4 header = lds16(stage + my_unit + r16 * 16);
-                uint2 q[2][4];
+            const uint32_t count = sb1 - sb0, main_end = base + 2 * count, end = main_end + (count + 7) / 8;
+            const uint32_t held = min(tile * 4 + quarter, p.tiles32 - 1);
+            const uint8_t *headers = p.w + ((uint64_t)held * p.nsb * 2 + hu) * kQ4kUnit + r16 * 16;
+            for (uint32_t at = base + ((slot_a - base) & 3u); at < end && alive; at += 4) {
+                const uint32_t a_phase = (at >> 2) & 1u;
+                if (at < main_end) {
+                    // ---- a stage of the first sum ----
+                    const uint32_t step = (at - base) >> 1, h = (at - base) & 1u, seq = seq_base + step;
+                    const uint32_t raw_slot = seq % kSkRawStages, raw_phase = (seq / kSkRawStages) & 1u;
+                    if (!mbar_wait(raw_full + 8 * raw_slot, raw_phase)) { alive = false; break; }
+                    if (tid == 0) { SK_TRACE(0, events); }
+                    const uint32_t stage = raw + raw_slot * kSkRawStage;
+                    const uint4 header = lds16(stage + my_unit + r16 * 16);
+                    uint2 q[2][4];
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                    for (int j = 0; j < 2; ++j)
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) q[j][t] = lds8(stage + my_quants + 512 * j + 16 * t);
-                // the six-bit scales of sub-blocks 4 h ... 4 h + 3, a byte each (q4k_scales' first or second word)
-                const uint32_t scales = mine ? ((header.w & 0x0f0f0f0fu) | (((header.y >> 6) & 0x03030303u) << 4)) : (header.y & 0x3f3f3f3fu);
-                const uint2 low0 = lds8(table + (scales & 0xffu) * 16), high0 = lds8(table + ((scales >> 8) & 0xffu) * 16 + 8);
-                const uint2 low1 = lds8(table + ((scales >> 16) & 0xffu) * 16), high1 = lds8(table + (scales >> 24) * 16 + 8);
-                const uint32_t position = base + 2 * (sb - sb0) + mine, slot_a = position % kSkStages;
-                if (!SK_WAIT_A(a_empty + 8 * slot_a, ((position / kSkStages) & 1u) ^ 1u)) { alive = false; break; }
-                if (tid == 0) { SK_TRACE(1, events); }
-                tc_fence_after();
-                const uint32_t columns = my_columns + slot_a * kSkStageCols;
-                uint32_t out[16];
-                skinny_scaled(q[0], 0x000f000fu, low0.x, low0.y, out);
-                tmem_store_16(columns, out);
-                skinny_scaled(q[0], 0x00f000f0u, high0.x, high0.y, out);
-                tmem_store_16(columns + 16, out);
-                skinny_scaled(q[1], 0x000f000fu, low1.x, low1.y, out);
-                tmem_store_16(columns + 32, out);
-                skinny_scaled(q[1], 0x00f000f0u, high1.x, high1.y, out);
-                // every lane's loads of the raw stage have delivered (their values are in `out` and in the stores): the
-                // stage may be refilled.  (An arrival right behind the loads let the refill overtake loads still in flight.)
-                __syncwarp();
-                if (lane == 0) mbar_arrive(raw_empty + 8 * raw_slot);
-                tmem_store_16(columns + 48, out);
-                if (tid == 0) { SK_TRACE(8, events); }
+                        for (int t = 0; t < 4; ++t) q[j][t] = lds8(stage + my_quants + 1024 * h + 512 * j + 16 * t);
+                    // the six-bit scales of sub-blocks 4 h ... 4 h + 3, a byte each (q4k_scales' first or second word)
+                    const uint32_t scales = h ? ((header.w & 0x0f0f0f0fu) | (((header.y >> 6) & 0x03030303u) << 4)) : (header.y & 0x3f3f3f3fu);
+                    const uint2 low0 = lds8(table + (scales & 0xffu) * 16), high0 = lds8(table + ((scales >> 8) & 0xffu) * 16 + 8);
+                    const uint2 low1 = lds8(table + ((scales >> 16) & 0xffu) * 16), high1 = lds8(table + (scales >> 24) * 16 + 8);
+                    if (!SK_WAIT_A(a_empty + 8 * slot_a, a_phase ^ 1u)) { alive = false; break; }
+                    if (tid == 0) { SK_TRACE(1, events); }
+                    tc_fence_after();
+                    uint32_t out[16];
+                    skinny_scaled(q[0], 0x000f000fu, low0.x, low0.y, out);
+                    tmem_store_16(columns, out);
+                    skinny_scaled(q[0], 0x00f000f0u, high0.x, high0.y, out);
+                    tmem_store_16(columns + 16, out);
+                    skinny_scaled(q[1], 0x000f000fu, low1.x, low1.y, out);
+                    tmem_store_16(columns + 32, out);
+                    skinny_scaled(q[1], 0x00f000f0u, high1.x, high1.y, out);
+                    // every lane's loads of the raw stage have delivered (their values are in `out` and in the stores):
+                    // the stage may be refilled.  (An arrival right behind the loads let the refill overtake loads
+                    // still in flight.)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(raw_empty + 8 * raw_slot);
+                    tmem_store_16(columns + 48, out);
+                    if (tid == 0) { SK_TRACE(8, events); }
+                } else {
+                    // ---- a stage of the second sum: dmin * m of eight super-blocks, 16 half floats = 8 columns each ----
+                    const uint32_t first = sb0 + 8 * (at - main_end);
+                    bool waited = false;
+#pragma unroll
+                    for (uint32_t round = 0; round < 2; ++round) {
+                        uint4 hd[4];
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const uint32_t sb = first + 4 * round + j;
+                            hd[j] = sb < sb1 ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit) : make_uint4(0u, 0u, 0u, 0u);
+                        }
+                        if (!waited) {
+                            if (!SK_WAIT_A(a_empty + 8 * slot_a, a_phase ^ 1u)) { alive = false; break; }
+                            tc_fence_after();
+                            waited = true;
+                        }
+#pragma unroll
+                        for (uint32_t pair = 0; pair < 2; ++pair) {
+                            uint32_t out[16];
+#pragma unroll
+                            for (uint32_t j = 0; j < 2; ++j) {
+                                const uint4 &one = hd[2 * pair + j];
+                                uint32_t sc[2], mn[2];
+                                q4k_scales(one.y, one.z, one.w, sc, mn);
+                                const float dmin = half_bits_to_float(one.x >> 16);   // (a super-block past the slice reads as zeros)
+                                const uint4 c0 = skinny_min_chunk(dmin, mn[0]), c1 = skinny_min_chunk(dmin, mn[1]);
+                                out[8 * j + 0] = c0.x; out[8 * j + 1] = c0.y; out[8 * j + 2] = c0.z; out[8 * j + 3] = c0.w;
+                                out[8 * j + 4] = c1.x; out[8 * j + 5] = c1.y; out[8 * j + 6] = c1.z; out[8 * j + 7] = c1.w;
+                            }
+                            tmem_store_16(columns + 32 * round + 16 * pair, out);
+                        }
+                    }
+                    if (!alive) break;
+                }
                 tmem_store_wait();
                 tc_fence_before();
                 if (tid == 0) { SK_TRACE(9, events); }
@@ -488,51 +529,8 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
                 if (tid == 0) { SK_TRACE(2, events); }
                 ++events;
             }
-            if (!alive) break;
-            base += 2 * (sb1 - sb0);
-            // ---- the second sum: dmin * m of eight super-blocks a stage, 16 half floats = 8 columns a super-block.  The
-            //      warps of the even super-blocks take these stages, stage h of the ring position's parity. ----
-            const uint32_t held = min(tile * 4 + quarter, p.tiles32 - 1);
-            const uint8_t *headers = p.w + ((uint64_t)held * p.nsb * 2 + hu) * kQ4kUnit + r16 * 16;
-            for (uint32_t first = sb0; first < sb1 && alive; first += 8, ++base) {
-                if (parity != 0u || (base & 1u) != mine) continue;
-                const uint32_t slot_a = base % kSkStages;
-                bool waited = false;
-#pragma unroll
-                for (uint32_t round = 0; round < 2; ++round) {
-                    uint4 h[4];
-#pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j) {
-                        const uint32_t sb = first + 4 * round + j;
-                        h[j] = sb < sb1 ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit) : make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    if (!waited) {
-                        if (!SK_WAIT_A(a_empty + 8 * slot_a, ((base / kSkStages) & 1u) ^ 1u)) { alive = false; break; }
-                        tc_fence_after();
-                        waited = true;
-                    }
-#pragma unroll
-                    for (uint32_t pair = 0; pair < 2; ++pair) {
-                        uint32_t out[16];
-#pragma unroll
-                        for (uint32_t j = 0; j < 2; ++j) {
-                            const uint4 &held_header = h[2 * pair + j];
-                            uint32_t sc[2], mn[2];
-                            q4k_scales(held_header.y, held_header.z, held_header.w, sc, mn);
-                            const float dmin = half_bits_to_float(held_header.x >> 16);   // (a super-block past the slice reads as zeros)
-                            const uint4 c0 = skinny_min_chunk(dmin, mn[0]), c1 = skinny_min_chunk(dmin, mn[1]);
-                            out[8 * j + 0] = c0.x; out[8 * j + 1] = c0.y; out[8 * j + 2] = c0.z; out[8 * j + 3] = c0.w;
-                            out[8 * j + 4] = c1.x; out[8 * j + 5] = c1.y; out[8 * j + 6] = c1.z; out[8 * j + 7] = c1.w;
-                        }
-                        tmem_store_16(my_columns + slot_a * kSkStageCols + 32 * round + 16 * pair, out);
-                    }
-                }
-                if (!alive) break;
-                tmem_store_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(a_full + 8 * slot_a);
-            }
+            base = end;
+            seq_base += count;
         }
         if (!alive) failed = 1;
     } else if (warp < kSkMmaWarp) {

@@ -358,3 +358,20 @@ def test_the_reference_products_chain_and_gather_in_gguf_order(runtime, oracle, 
     # nothing seals these formats, and no staged product takes them
     with pytest.raises(nb.NeuraCudaError):
         runtime.seal_device(element, n, k, w.ptr)
+
+
+@pytest.mark.parametrize("rows", [24, 32])
+def test_a_product_whose_k_axis_is_split_gives_the_same_sums_every_time(runtime, oracle, rows):
+    # [7168 x 5120] (the 32B q|k|v projection) has fewer 128-row tiles than the GPU has SMs, so the product splits the K
+    # axis and adds the slices' partial sums up; run it often enough for a race between slices to show
+    n, k = 7168, 5120
+    w, packed = weights(oracle, nb.Q4K, n, k, seed=31)
+    x = oracle.Stream(37).normal(rows * k).reshape(rows, k)
+    expected = oracle.linear(nb.Q4K, packed, n, k, x, threads=16)
+    held = runtime.load(nb.Q4K, n, k, packed)
+    xd, od = runtime.tensor(rows, k), runtime.tensor(rows, n)
+    runtime.write(xd, x)
+    for turn in range(12):
+        runtime.linear(held, xd, od)
+        assert_close(runtime.read(od), expected, f"Q4_K [{n},{k}] rows {rows}, turn {turn}")
+    runtime.free(held.ptr)
