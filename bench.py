@@ -671,6 +671,45 @@ def run_prefill(args):
     rt.close()
 
 
+def run_product(args):
+    """A line of its own for ONE product shape on one GPU, ``--workload product-q4_k-NxK-bB`` (or ``q8_0``): B rows of
+    f32 activations against a sealed [N x K] weight, staging included; a step walks as many copies of the weight as
+    make 1.2 GB, so every launch streams its weight from HBM.  Device timing only."""
+    import torch
+
+    import neura_b200 as nb
+
+    _, kind, shape, batch = args.workload.split("-")
+    element = {"q4_k": nb.Q4K, "q8_0": nb.Q8_0}[kind]
+    n, k = (int(v) for v in shape.split("x"))
+    rows = int(batch.lstrip("b"))
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    device = torch.device("cuda", 0)
+    tstream = torch.cuda.ExternalStream(rt.stream.value, device=device)
+    copies = sealed_copies(rt, torch, tstream, device, element, n, k, max(2, min(64, int(1.2e9 // nb.payload_bytes(element, n * k)))))
+    warmup = max(3, args.warmup)
+    launches0 = rt.launches
+    with ClockSampler(0) as clocks:
+        us = time_products(rt, torch, tstream, copies, rows, k, n, reps=max(1, args.steps))
+    peaks, peak_kind = measured_peaks()
+    algorithmic = nb.payload_bytes(element, n * k) + 4 * rows * (k + n)
+    achieved = algorithmic / us / 1e3
+    kernel = "skinny_q4k_tcgen05_kernel (+ skinny_prep_kernel)" if element == nb.Q4K and rows > 8 else "qlinear_stream_kernel (+ prep_kernel)"
+    print(json.dumps({
+        "metric": "product GB/s of algorithmic bytes", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": us * len(copies) / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 activations, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{rows} rows x {kind} [{n} x {k}], {len(copies)} copies of the weight in turn",
+                   "l2": "the copies exceed L2 together", "us_per_product": us},
+        "clocks": clocks.summary(), "gpu_launches": int(rt.launches - launches0),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
+                     "frac": achieved / float(peaks["hbm_gbs"]), "traffic": None, "peak_kind": peak_kind, "kernel": kernel,
+                     "algorithmic_bytes": algorithmic},
+    }))
+    rt.close()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -694,6 +733,8 @@ def main():
     args = parser.parse_args()
     if args.workload.startswith("prefill-"):
         run_prefill(args)
+    elif args.workload.startswith("product-"):
+        run_product(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
