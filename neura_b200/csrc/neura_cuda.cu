@@ -520,7 +520,8 @@ int32_t skinny_stage(nc_context *ctx, cudaStream_t stream, const float *x_dev, u
     p.floor = floor;
     p.normed = normed;
     p.normed_stride = normed_stride;
-    NC_CUDA(launch_dependent(skinny_prep_kernel, dim3(rows), dim3(256), 0, stream, p));
+    const unsigned int prep_threads = std::min(1024u, std::max(256u, (k / kSuperBlock + 7) / 8 * 8 * 32));   // a warp a stretch, up to 32
+    NC_CUDA(launch_dependent(skinny_prep_kernel, dim3(rows), dim3(prep_threads), 0, stream, p));
     ctx->launches++;
     ctx->sk_bpad = p.bpad;
     ctx->sk_sx_cols = p.sx_cols;

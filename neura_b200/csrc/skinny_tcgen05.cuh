@@ -135,11 +135,12 @@ __device__ __forceinline__ void split_half(float value, __half &hi, __half &lo) 
     lo = __float2half_rn((value - __half2float(hi)) * 2048.0f);
 }
 
-// One CTA per activation row; a warp per 256-element stretch in turn.
-__global__ void __launch_bounds__(256) skinny_prep_kernel(const __grid_constant__ SkinnyPrepParams p) {
+// One CTA per activation row; a warp per 256-element stretch (in turn, where the row has more stretches than the CTA
+// has warps: the launch takes up to 32 warps, so rows of up to 8192 numbers go through in one round).
+__global__ void __launch_bounds__(1024) skinny_prep_kernel(const __grid_constant__ SkinnyPrepParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ float partial[8];
+    __shared__ float partial[32];
     __shared__ float shared_scalar;
     __shared__ float sums[kSkPrepSums];
     const uint32_t row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
