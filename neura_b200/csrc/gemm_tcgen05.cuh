@@ -336,205 +336,4 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
     if (warp == kMmaWarp) tmem_free(tmem, kGemmTmemCols);
 }
 
-// ---- the same product by pairs of CTAs (tcgen05 cta_group::2) -----------------------------------------------------
-// The product above is bound by its producers: a dequantised W tile feeds only the 256 X rows of its own CTA, and
-// dequantising takes about twice as long as the MMAs it feeds.  Here two CTAs on neighbouring SMs (a cluster of two
-// along the grid's y axis) share one 256-row W tile and compute 512 X rows: CTA r of the pair dequantises W rows
-// 128 r ... 128 r + 127 of the tile into its own shared memory and asks for its own 256 x 64 X tile; one thread of
-// CTA 0 issues tcgen05.mma.cta_group::2 with M = 256 (128 X rows of each CTA) and N = 256 (128 W rows out of each
-// CTA's shared memory), twice per 16 k (each CTA keeps two 128 x 256 accumulators, as above).  Per MMA a CTA now
-// dequantises half as much.  Its sixteen producer warps take the k-steps in turn, eight warps a step.
-// Barriers: `full` lives in CTA 0 and counts the producer warps of both CTAs (CTA 1's arrive through the cluster's
-// shared-memory window) plus CTA 0's expect-tx, and both CTAs' X copies complete on it (the copy's cta_group::2 form,
-// without multicast); `empty` and `accum` exist in both CTAs, and CTA 0's MMA thread commits to each of them in turn
-// (two plain commits, no multicast).  The pair meets at a cluster barrier before the first remote arrival and before
-// either CTA leaves.
-constexpr uint32_t kPairBBytes = kGemmBBytes / 2;                  // 16 KiB: this CTA's 128 W rows of a k-step
-constexpr uint32_t kPairStageBytes = kGemmABytes + kPairBBytes;    // 48 KiB
-constexpr uint32_t kPairStages = 4;
-constexpr uint32_t kPairSmem = kPairStages * kPairStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
-
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// The address of this CTA's shared-memory location `addr` as CTA `rank` of the cluster holds it.
-__device__ __forceinline__ uint32_t cluster_address(uint32_t addr, uint32_t rank) {
-    uint32_t out;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
-    return out;
-}
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(columns) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_free_pair(uint32_t address, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
-}
-// An arrival on `cluster_bar` (any CTA of the pair) when the MMAs this thread issued so far are complete.
-__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0)
-        : "memory");
-}
-// The pair's X copy: lands in this CTA's shared memory, completes on CTA 0's barrier.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t leader_bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
-        "l"(map), "r"(x), "r"(y), "r"(leader_bar)
-        : "memory");
-}
-
-// Launched with a cluster of (1, 2, 1): gridDim.y is even (rows past M read as zeros and are not stored).
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
-    extern __shared__ uint8_t gemm_raw[];
-    const uint32_t base = (smem_addr(gemm_raw) + 1023u) & ~1023u;
-    const uint32_t bars = base + kPairStages * kPairStageBytes;
-    const uint32_t full = bars, empty = bars + 8 * kPairStages, accum = bars + 16 * kPairStages;
-    const uint32_t slot = accum + 8;
-    __shared__ uint32_t failed;
-    const uint32_t tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
-    const uint32_t rank = cluster_rank();
-    const uint32_t m0 = blockIdx.y * kGemmBM, n0 = blockIdx.x * kGemmBN;
-    const uint32_t ksteps = p.k / kGemmBK;
-    constexpr uint32_t kMmaWarp = kGemmProducers / 32;
-    const uint32_t full_leader = cluster_address(full, 0);   // + 8 s: CTA 0's barrier as either CTA reaches it
-
-    if (tid == 0) {
-        failed = 0;
-        for (uint32_t s = 0; s < kPairStages; ++s) {
-            mbar_init(full + 8 * s, 2 * (kGemmProducers / 64) + 1);   // eight producer warps of each CTA, and CTA 0's expect-tx
-            mbar_init(empty + 8 * s, 1);                              // one tcgen05.commit
-        }
-        mbar_init(accum, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == kMmaWarp) tmem_alloc_pair(slot, kGemmTmemCols);   // (the same warp of both CTAs)
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync();   // both CTAs' barriers exist before anyone arrives across
-    tc_fence_after();
-    const uint32_t tmem = lds4(slot);
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    if (warp < kMmaWarp) {
-        // ---------------- producers: warps 0-7 take the even k-steps, warps 8-15 the odd ones ----------------
-        // warp v = warp % 8 of a set owns half (v & 1) of 32-row unit 4 rank + (v >> 1) of the W tile
-        const uint32_t g = lane >> 2, t = lane & 3, set = warp >> 3, v = warp & 7u, half = v & 1u;
-        const uint32_t as_warp = (4 * rank + (v >> 1)) * 2 + half;   // the warp number the fetch helpers count units by
-        bool alive = true;
-        const uint32_t nsb = p.k / kSuperBlock;
-        // the quants travel one of the warp's steps ahead of their use, the headers one super-block ahead, and the
-        // super-block after the next is asked into L2
-        uint4 quants[2], headers[2], coming[2];
-        uint32_t held_sb = 0;
-        if (set < ksteps) quants[0] = fetch_quants(p, n0, set, as_warp, lane);
-        fetch_headers(headers, p, n0, 0, as_warp, lane);
-        if (nsb > 1) fetch_headers(coming, p, n0, 1, as_warp, lane);
-        for (uint32_t it = set, turn = 0; it < ksteps && alive; it += 2, ++turn) {
-            const uint32_t sb = it >> 2, j = it & 3;
-            if (sb != held_sb) {   // (a warp takes two steps of every super-block, so the super-blocks come one by one)
-                headers[0] = coming[0];
-                headers[1] = coming[1];
-                held_sb = sb;
-                if (sb + 1 < nsb) fetch_headers(coming, p, n0, sb + 1, as_warp, lane);
-                if (lane == 0 && sb + 2 < nsb)
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(half_unit_of(p, n0, sb + 2, as_warp)), "r"(kQ4kUnit) : "memory");
-            }
-            if (it + 2 < ksteps) quants[(turn + 1) & 1] = fetch_quants(p, n0, it + 2, as_warp, lane);
-            const uint32_t s = it % kPairStages, parity = (it / kPairStages) & 1u;
-            if (!mbar_wait(empty + 8 * s, parity ^ 1u)) { alive = false; break; }
-            const uint32_t a_tile = base + s * kPairStageBytes, b_tile = a_tile + kGemmABytes;
-            if (v == 0 && lane == 0) {   // this CTA's X tile; x (columns) is a multiple of 64 bf16 = 128 bytes
-                if (rank == 0) mbar_expect(full + 8 * s, 2 * kGemmABytes);   // both CTAs' tiles complete on CTA 0's barrier
-                tma_load_2d_pair(a_tile, &p.x_map, it * kGemmBK, m0, full_leader + 8 * s);
-            }
-            const uint32_t row = (v >> 1) * 32 + half * 16 + g;   // among this CTA's 128 W rows
-            const uint4 q = quants[turn & 1];
-            dequant_row_quarter(b_tile, row, t, j, q.x, q.y, headers[0]);
-            dequant_row_quarter(b_tile, row + 8, t, j, q.z, q.w, headers[1]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads the tile through the async proxy
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(full_leader + 8 * s);
-        }
-        if (!alive) failed = 1;
-        // ---------------- epilogue: as in the single-CTA kernel, on this CTA's own accumulators ----------------
-        if (alive && mbar_wait(accum, 0)) {
-            tc_fence_after();
-            const uint32_t which = (warp >> 2) & 1, lanes = (warp & 3) * 32, columns = (warp >> 3) * (kGemmBN / 2);
-            const uint32_t row = m0 + which * 128 + lanes + lane;
-            float *turn = reinterpret_cast<float *>(gemm_raw + (base - smem_addr(gemm_raw))) + warp * 32 * 33;
-            for (uint32_t c0 = columns; c0 < columns + kGemmBN / 2; c0 += 32) {
-                uint32_t r[32];
-                tmem_load_32(tmem + (lanes << 16) + which * kGemmBN + c0, r);
-#pragma unroll
-                for (uint32_t i = 0; i < 32; ++i)
-                    turn[lane * 33 + i] = (row < p.m && n0 + c0 + i < p.n) ? chained(p.chain, row, n0 + c0 + i, __uint_as_float(r[i])) : 0.0f;
-                __syncwarp();
-                const uint32_t col = n0 + c0 + lane;
-                if (col < p.n) {
-                    const uint32_t first_row = m0 + which * 128 + lanes;
-                    float *to = p.out + (uint64_t)first_row * p.out_stride + col;
-#pragma unroll 8
-                    for (uint32_t rr = 0; rr < 32; ++rr)
-                        if (first_row + rr < p.m) __stcs(to + (uint64_t)rr * p.out_stride, turn[rr * 33 + lane]);
-                }
-                __syncwarp();
-            }
-        } else {
-            failed = 1;
-        }
-    } else if (rank == 0) {
-        // ---------------- MMA issue, CTA 0 for the pair ----------------
-        const uint32_t idesc = instruction_descriptor(256, kGemmBN);
-        const uint32_t empty_peer = cluster_address(empty, 1), accum_peer = cluster_address(accum, 1);
-        bool alive = true;
-        for (uint32_t it = 0; it < ksteps; ++it) {
-            const uint32_t s = it % kPairStages, parity = (it / kPairStages) & 1u;
-            if (!mbar_wait(full + 8 * s, parity)) { alive = false; break; }
-            tc_fence_after();
-            const uint32_t a_tile = base + s * kPairStageBytes;
-            const uint64_t desc_a0 = smem_descriptor(a_tile), desc_a1 = smem_descriptor(a_tile + kGemmABytes / 2);
-            const uint64_t desc_b = smem_descriptor(a_tile + kGemmABytes);
-            if (elect_one_lane()) {
-#pragma unroll
-                for (uint32_t kk = 0; kk < kGemmBK / 16; ++kk) {
-                    tc_mma_bf16_pair(tmem, desc_a0 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
-                    tc_mma_bf16_pair(tmem + kGemmBN, desc_a1 + kk * 2, desc_b + kk * 2, idesc, (it | kk) != 0 ? 1u : 0u);
-                }
-                tc_commit_pair(empty + 8 * s);        // frees the stage in both CTAs when these MMAs have read it
-                tc_commit_pair(empty_peer + 8 * s);
-            }
-            __syncwarp();
-        }
-        if (alive) {
-            if (elect_one_lane()) {
-                tc_commit_pair(accum);
-                tc_commit_pair(accum_peer);
-            }
-            __syncwarp();
-        } else {
-            failed = 1;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (failed && tid == 0) atomicOr(p.status, 2u);
-    cluster_sync();   // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
-    if (warp == kMmaWarp) tmem_free_pair(tmem, kGemmTmemCols);
-}
-
 }  // namespace nc

@@ -1118,7 +1118,6 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     static bool raised[64] = {false};
     if (!raised[ctx->device & 63]) {
         NC_CUDA(cudaFuncSetAttribute(gemm_q4k_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
-        NC_CUDA(cudaFuncSetAttribute(gemm_q4k_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmem));
         raised[ctx->device & 63] = true;
     }
     GemmParams p;
@@ -1135,28 +1134,8 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     p.status = (unsigned int *)ctx->status.ptr;
     p.chain.n = n_steps;
     for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
-    const unsigned int n_tiles = (w->n + kGemmBN - 1) / kGemmBN, m_tiles = (rows + kGemmBM - 1) / kGemmBM;
-    if (m_tiles >= 2) {
-        // pairs of CTAs along the rows share a dequantised W tile (a cluster of two; an odd last tile gets a partner
-        // that reads zeros and stores nothing)
-        cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(n_tiles, (m_tiles + 1) / 2 * 2);
-        config.blockDim = dim3(kGemmThreads);
-        config.dynamicSmemBytes = kPairSmem;
-        config.stream = stream;
-        cudaLaunchAttribute attribute[2];
-        attribute[0].id = cudaLaunchAttributeClusterDimension;
-        attribute[0].val.clusterDim.x = 1;
-        attribute[0].val.clusterDim.y = 2;
-        attribute[0].val.clusterDim.z = 1;
-        attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attribute[1].val.programmaticStreamSerializationAllowed = 1;
-        config.attrs = attribute;
-        config.numAttrs = 2;
-        NC_CUDA(cudaLaunchKernelEx(&config, gemm_q4k_tcgen05_pair_kernel, p));
-    } else {
-        NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3(n_tiles, m_tiles), dim3(kGemmThreads), kGemmSmem, stream, p));
-    }
+    NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((w->n + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM),
+                             dim3(kGemmThreads), kGemmSmem, stream, p));
     ctx->launches++;
     return 0;
 }
