@@ -463,7 +463,9 @@ SkinnyPlan skinny_plan(const nc_context *ctx, uint32_t n, uint32_t k, bool pair,
     for (uint32_t s = 1; s <= nsb && s <= 16; ++s) {
         if (s > 1 && (uint64_t)plan.ntile128 * s * bpad * kSkTileRows * sizeof(float) > (16ull << 20)) break;
         const uint64_t rounds = ((uint64_t)plan.ntile128 * s + sms - 1) / sms;
-        const double cost = (double)rounds * (double)((nsb + s - 1) / s + (s > 1 ? 1 : 0)) * (1.0 + 0.02 * (s - 1));
+        // (an item costs about four super-blocks' time on top of its own: the second sum's stages, the accumulator's
+        // last read, the partial sums)
+        const double cost = (double)rounds * (double)((nsb + s - 1) / s + (s > 1 ? 1 : 0) + 4) * (1.0 + 0.02 * (s - 1));
         if (s == 1 || cost < best) {
             best = cost;
             plan.splits = s;
@@ -1290,7 +1292,11 @@ int32_t attend_any(nc_context *ctx, void *stream_, const float *q_dev, uint64_t 
     if (capacity > 64 * 128)
         return refuse(kBadArgument, "a cache of %u slots is more than the %u the attention kernel splits", capacity, 64 * 128);
     // up to 8 splits merge inside a thread-block cluster; longer caches merge through global memory
-    const uint32_t tile = capacity <= kAttendMaxCluster * 64 ? 64 : 128;
+    // (tiles of 128 positions take 133 KB of shared memory, one CTA an SM: with many sequences that leaves the grid
+    // several waves long, so once the 128-position tiles outnumber the SMs the kernel takes tiles of 64, three CTAs an
+    // SM, and merges through global memory)
+    const bool crowded = (uint64_t)batch * key_heads * ((capacity + 127) / 128) > (uint64_t)ctx->sms;
+    const uint32_t tile = capacity <= kAttendMaxCluster * 64 || crowded ? 64 : 128;
     // a full cluster wherever the cache is long enough to give every CTA 64 positions: eight CTAs of 80 positions
     // beat five of 128 (1.2 % of the 32B decode step at 640 cache rows)
     uint32_t splits = (capacity + tile - 1) / tile;
