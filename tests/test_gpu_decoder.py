@@ -98,6 +98,25 @@ def test_attention_over_the_cache(runtime, oracle, heads, key_heads, width, capa
     assert np.abs(runtime.read(out) - expected.reshape(batch, -1)).max() <= 1e-5
 
 
+def test_attention_of_many_sequences_takes_the_small_tiles(runtime, oracle):
+    # 20 sequences x 8 key heads x two 128-position tiles are more tiles than the GPU has SMs: the launcher then takes
+    # tiles of 64 positions (three CTAs an SM) and merges the splits through global memory
+    batch, heads, key_heads, width, capacity = 20, 16, 8, 128, 200
+    q = oracle.Stream(19).normal(batch * heads * width).reshape(batch, heads, width)
+    keys = oracle.Stream(20).normal(batch * key_heads * capacity * width).reshape(batch, key_heads, capacity, width)
+    values = oracle.Stream(21).normal(keys.size).reshape(keys.shape)
+    position = (np.arange(batch, dtype=np.uint32) * 37 + 3) % capacity
+    expected = oracle.attend(q, keys, values, position + 1, 0.125)
+    qd, out = runtime.tensor(batch, heads * width), runtime.tensor(batch, heads * width)
+    kd, vd, pd = runtime.tensor(keys.size), runtime.tensor(values.size), runtime.tensor_u32(batch)
+    runtime.write(qd, q.reshape(batch, -1))
+    runtime.write(kd, keys.reshape(-1))
+    runtime.write(vd, values.reshape(-1))
+    runtime.write(pd, position)
+    runtime.attend(qd, kd, vd, pd, 0.125, heads, key_heads, width, capacity, out)
+    assert np.abs(runtime.read(out) - expected.reshape(batch, -1)).max() <= 1e-5
+
+
 def test_argmax_takes_the_lowest_index_on_ties(runtime, oracle):
     x = oracle.Stream(12).normal(3 * 5000).reshape(3, 5000)
     x[0, 4000] = x[0, 17] = 9.0
