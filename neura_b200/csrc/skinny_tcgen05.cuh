@@ -97,11 +97,6 @@ struct SkinnyParams {
 #endif
 };
 
-#ifdef NC_SKINNY_FREE   // a development build: producers and the MMA thread do not wait for each other (wrong sums, true speeds)
-#define SK_WAIT_A(bar, phase) true
-#else
-#define SK_WAIT_A(bar, phase) mbar_wait(bar, phase)
-#endif
 #ifdef NC_SKINNY_TRACE
 #define SK_TRACE(role, index) do { if (blockIdx.x == 0 && (index) < 256) p.trace[(role) * 256 + (index)] = global_nanos(); } while (0)
 #else
@@ -469,7 +464,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
                     const uint32_t scales = h ? ((header.w & 0x0f0f0f0fu) | (((header.y >> 6) & 0x03030303u) << 4)) : (header.y & 0x3f3f3f3fu);
                     const uint2 low0 = lds8(table + (scales & 0xffu) * 16), high0 = lds8(table + ((scales >> 8) & 0xffu) * 16 + 8);
                     const uint2 low1 = lds8(table + ((scales >> 16) & 0xffu) * 16), high1 = lds8(table + (scales >> 24) * 16 + 8);
-                    if (!SK_WAIT_A(a_empty + 8 * slot_a, a_phase ^ 1u)) { alive = false; break; }
+                    if (!mbar_wait(a_empty + 8 * slot_a, a_phase ^ 1u)) { alive = false; break; }
                     if (tid == 0) { SK_TRACE(1, events); }
                     tc_fence_after();
                     uint32_t out[16];
@@ -500,7 +495,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
                             hd[j] = sb < sb1 ? ld_stream16(headers + (uint64_t)sb * 2 * kQ4kUnit) : make_uint4(0u, 0u, 0u, 0u);
                         }
                         if (!waited) {
-                            if (!SK_WAIT_A(a_empty + 8 * slot_a, a_phase ^ 1u)) { alive = false; break; }
+                            if (!mbar_wait(a_empty + 8 * slot_a, a_phase ^ 1u)) { alive = false; break; }
                             tc_fence_after();
                             waited = true;
                         }
@@ -648,7 +643,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) skinny_q4k_tcgen05_kernel(const
         bool alive = true;
         // one stage: 128 k as two tiles of four 16-k MMAs; `fresh`: the first MMA starts the accumulator anew
         auto stage_mmas = [&](uint32_t accumulator, bool fresh) -> bool {
-            if (!SK_WAIT_A(a_full + 8 * at_a.s, at_a.phase)) return false;
+            if (!mbar_wait(a_full + 8 * at_a.s, at_a.phase)) return false;
             if (!mbar_wait(x_full + 8 * at_x.s, at_x.phase)) return false;
             if (lane == 0) { SK_TRACE(3, events); }
             tc_fence_after();
