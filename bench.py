@@ -453,12 +453,12 @@ def run_ours(args):
     if world == 1 and args.rank_of:   # a diagnostic: one rank's share of an N-way split, timed alone without exchanges
         from neura_b200 import parallel
 
-        shard = parallel.Shard(config, args.rank_of, 0)
+        shard = parallel.Shard(config, args.rank_of, 0, attention=args.attention)
         comm = parallel.NullComm(args.rank_of, 0)
     if world > 1:  # tensor parallel: one model split over the ranks
         from neura_b200 import parallel
 
-        shard = parallel.Shard(config, world, rank)
+        shard = parallel.Shard(config, world, rank, attention=args.attention)
         if args.comm == "peer":   # the library's one-shot all-reduce over NVLink peer memory
             comm = parallel.PeerComm(rt, world, rank, rows * config.hidden, device=device, stream=tstream)
         else:
@@ -471,7 +471,7 @@ def run_ours(args):
     # the prompt: random token ids; in chunks where the decoder fills in chunks, else one position at a time
     prompts = np.random.default_rng(29).integers(0, config.vocab, (rows, args.prompt), dtype=np.uint32)
     decoder.reset()
-    persistent = rows <= 2 and args.step == "persistent" and ((world == 1 and shard is None) or (world > 1 and args.comm == "peer"))
+    persistent = rows <= 2 and args.step == "persistent" and ((world == 1 and shard is None) or (world > 1 and args.comm == "peer" and args.attention == "split"))
     if decoder.chunks:
         decoder.prefill(prompts)
         fed = args.prompt - 1
@@ -587,7 +587,7 @@ def run_ours(args):
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_description(shape, args.prompt, rows,
-                                           f"tp{world} ({args.comm} all-reduce)" if world > 1 else "single GPU"),
+                                           f"tp{world} ({args.comm} all-reduce; " + ("MLP and head split, attention whole on every rank" if args.attention == "whole" else "attention, MLP and head split") + ")" if world > 1 else "single GPU"),
             "clocks": clock_summary,
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -725,6 +725,10 @@ def main():
     parser.add_argument("--fold", default="off", choices=["on", "off"],
                         help="fold norms, stagings and (tensor parallel) exchanges into the products' epilogues: fewer, "
                              "longer launches (measured slower at every split, so off)")
+    parser.add_argument("--attention", default="whole", choices=["whole", "split"],
+                        help="tensor parallel: every rank keeps the whole attention block and only the MLP and the head are "
+                             "split (one exchange a layer; the faster split as measured), or the attention block is split by heads "
+                             "as well (two exchanges a layer)")
     parser.add_argument("--rank-of", type=int, default=0,
                         help="diagnostic, one GPU: time rank 0's share of a split over this many ranks, no exchanges")
     parser.add_argument("--step", default="graph", choices=["graph", "persistent"],

@@ -34,29 +34,40 @@ class Window:
 
 @dataclass(frozen=True)
 class Shard:
+    """``attention``: "split" shards the attention block by heads (q/k/v rows, attention output by K, one exchange);
+    "whole" keeps it on every rank (each rank computes all heads; only the MLP and the head are split, one exchange a
+    layer).  At batch 1 the whole attention block streams 35 MB a layer, which takes a rank less time than its share
+    of it plus the exchange, so "whole" is the faster split at every group size measured."""
     config: Config
     world: int
     rank: int
+    attention: str = "split"
 
     def __post_init__(self):
         c, w = self.config, self.world
-        if c.heads % w or c.key_heads % w or c.feed_forward % w or c.vocab % w:
+        if self.attention not in ("split", "whole"):
+            raise ValueError(f"the attention block is split or whole, not {self.attention!r}")
+        if c.feed_forward % w or c.vocab % w or (not self.whole and (c.heads % w or c.key_heads % w)):
             raise ValueError(f"{c.name} does not split evenly over {w} ranks "
                              f"({c.heads}/{c.key_heads} heads, ff {c.feed_forward}, vocab {c.vocab})")
-        for width in (c.feed_forward // w, c.vocab // w, c.key_width // w):
+        for width in (c.feed_forward // w, c.vocab // w) + (() if self.whole else (c.key_width // w,)):
             if width % 32:
                 raise ValueError(f"a share of {width} rows does not fill tiles of 32")
-        if (c.query_width // w) % 32 or (c.feed_forward // w) % 32:
+        if (not self.whole and (c.query_width // w) % 32) or (c.feed_forward // w) % 32:
             raise ValueError("a share of a K axis starts on a multiple of 32")
+
+    @property
+    def whole(self) -> bool:
+        return self.attention == "whole"
 
     # -- shapes of the local model ---------------------------------------------------
     @property
     def heads(self) -> int:
-        return self.config.heads // self.world
+        return self.config.heads if self.whole else self.config.heads // self.world
 
     @property
     def key_heads(self) -> int:
-        return self.config.key_heads // self.world
+        return self.config.key_heads if self.whole else self.config.key_heads // self.world
 
     @property
     def query_width(self) -> int:
@@ -74,30 +85,36 @@ class Shard:
     def vocab(self) -> int:
         return self.config.vocab // self.world
 
-    def rows(self, n: int) -> Tuple[int, int]:
-        """The run of rows [n0, n1) of a column-parallel projection of ``n`` rows."""
+    def rows(self, n: int, whole: bool = False) -> Tuple[int, int]:
+        """The run of rows [n0, n1) of a column-parallel projection of ``n`` rows (all of them for a projection the
+        ranks keep whole)."""
+        if whole:
+            return 0, n
         share = n // self.world
         return self.rank * share, (self.rank + 1) * share
 
-    def window(self, k: int) -> Window:
-        """The share of a row-parallel projection's K axis of ``k`` columns."""
+    def window(self, k: int, whole: bool = False) -> Window:
+        """The share of a row-parallel projection's K axis of ``k`` columns (the whole axis for a projection the ranks
+        keep whole)."""
         per = _BLOCK[self.config.element][0]
+        if whole:
+            return Window(k, 0, k, 0)
         share = k // self.world
         k0, k1 = self.rank * share, (self.rank + 1) * share
         b0, b1 = k0 // per, (k1 + per - 1) // per
         return Window((b1 - b0) * per, k0 - b0 * per, k1 - b0 * per, b0)
 
     # -- slicing GGUF tensors ------------------------------------------------------------
-    def slice_rows(self, packed: np.ndarray, n: int, k: int, share_of: int = None) -> np.ndarray:
+    def slice_rows(self, packed: np.ndarray, n: int, k: int, whole: bool = False) -> np.ndarray:
         """Rows [n0, n1) of a GGUF [n, k] tensor (a contiguous run of its bytes)."""
-        n0, n1 = self.rows(n)
+        n0, n1 = self.rows(n, whole)
         row = payload_bytes(self.config.element, k)
         return np.ascontiguousarray(packed, dtype=np.uint8)[n0 * row: n1 * row]
 
-    def slice_columns(self, packed: np.ndarray, n: int, k: int) -> np.ndarray:
+    def slice_columns(self, packed: np.ndarray, n: int, k: int, whole: bool = False) -> np.ndarray:
         """The whole blocks that cover this rank's share of K, for every row of a GGUF [n, k] tensor."""
         per, size = _BLOCK[self.config.element]
-        window = self.window(k)
+        window = self.window(k, whole)
         blocks = np.ascontiguousarray(packed, dtype=np.uint8)[: n * (k // per) * size].reshape(n, k // per, size)
         return np.ascontiguousarray(blocks[:, window.first_block: window.first_block + window.k // per]).reshape(-1)
 
@@ -106,7 +123,7 @@ class Shard:
         c = self.config
         e = c.element
         per_layer = (payload_bytes(e, (self.query_width + 2 * self.key_width) * c.hidden)
-                     + payload_bytes(e, c.hidden * self.window(c.query_width).k)
+                     + payload_bytes(e, c.hidden * self.window(c.query_width, self.whole).k)
                      + 2 * payload_bytes(e, self.feed_forward * c.hidden)
                      + payload_bytes(e, c.hidden * self.window(c.feed_forward).k))
         return c.layers * per_layer + payload_bytes(e, self.vocab * c.hidden)
@@ -181,24 +198,27 @@ def load_decoder_weights(rt, config: Config, packed: Dict[str, np.ndarray], norm
     e = c.element
     weights, device_norms = {}, {}
 
-    def rows_of(name: str, n: int, k: int):
+    whole_attention = shard is not None and shard.whole
+
+    def rows_of(name: str, n: int, k: int, whole: bool = False):
         data = packed[name]
-        if shard is None:
+        if shard is None or whole:
             return n, data
         return n // shard.world, shard.slice_rows(data, n, k)
 
-    def columns_of(name: str, n: int, k: int):
+    def columns_of(name: str, n: int, k: int, whole: bool = False):
         data = packed[name]
-        if shard is None:
+        if shard is None or whole:
             return k, data
         return shard.window(k).k, shard.slice_columns(data, n, k)
 
     for layer in range(c.layers):
         name = lambda part: f"blk.{layer}.{part}.weight"  # noqa: E731
-        parts = [rows_of(name("attn_q"), c.query_width, c.hidden), rows_of(name("attn_k"), c.key_width, c.hidden),
-                 rows_of(name("attn_v"), c.key_width, c.hidden)]
+        parts = [rows_of(name("attn_q"), c.query_width, c.hidden, whole_attention),
+                 rows_of(name("attn_k"), c.key_width, c.hidden, whole_attention),
+                 rows_of(name("attn_v"), c.key_width, c.hidden, whole_attention)]
         weights[name("attn_qkv")] = rt.load_stacked(e, c.hidden, parts)
-        k, data = columns_of(name("attn_output"), c.hidden, c.query_width)
+        k, data = columns_of(name("attn_output"), c.hidden, c.query_width, whole_attention)
         weights[name("attn_output")] = rt.load(e, c.hidden, k, data)
         n, gate = rows_of(name("ffn_gate"), c.feed_forward, c.hidden)
         n, up = rows_of(name("ffn_up"), c.feed_forward, c.hidden)

@@ -100,7 +100,9 @@ class Decoder:
         self.batch, self.capacity, self.shard, self.comm = batch, capacity, shard, comm
         c = config
         world = shard.world if shard else 1
-        self.heads, self.key_heads = c.heads // world, c.key_heads // world
+        # (a group may keep the attention block whole on every rank and split the MLP and the head only)
+        self.whole_attention = bool(shard is not None and shard.whole)
+        self.heads, self.key_heads = (shard.heads, shard.key_heads) if shard else (c.heads, c.key_heads)
         self.query_width, self.key_width = self.heads * c.head_width, self.key_heads * c.head_width
         self.feed_forward, self.vocab = c.feed_forward // world, c.vocab // world
         self.tokens = rt.tensor_u32(batch)
@@ -115,7 +117,7 @@ class Decoder:
         cache = batch * self.key_heads * capacity * c.head_width
         self.keys = [rt.tensor(cache) for _ in range(c.layers)]
         self.values = [rt.tensor(cache) for _ in range(c.layers)]
-        widest_k = max(c.hidden, self.window(c.feed_forward)[0], self.window(c.query_width)[0])
+        widest_k = max(c.hidden, self.window(c.feed_forward)[0], self.window(c.query_width, self.whole_attention)[0])
         # scratch for the decode step and for the largest prompt chunk, all of it now: a recorded step holds the
         # scratch's addresses, so nothing may grow it later
         most = max([batch, *self.chunks])
@@ -126,19 +128,22 @@ class Decoder:
         self.fold = False      # True: fold norms and stagings into the products' epilogues (fewer, longer launches)
         self.scale = 1.0 / float(c.head_width) ** 0.5
 
-    def window(self, k: int):
-        """(local K, lo, hi) of a row-parallel projection over a K axis of ``k``."""
-        if self.shard is None:
+    def window(self, k: int, whole: bool = False):
+        """(local K, lo, hi) of a row-parallel projection over a K axis of ``k`` (all of it for a projection the ranks
+        keep whole)."""
+        if self.shard is None or whole:
             return k, 0, k
         w = self.shard.window(k)
         return w.k, w.lo, w.hi
 
-    def _row_parallel(self, x: DeviceTensor, weight: Weight, k: int, next_norm: DeviceTensor) -> None:
+    def _row_parallel(self, x: DeviceTensor, weight: Weight, k: int, next_norm: DeviceTensor, whole: bool = False) -> None:
         """hidden += W x over this rank's share of K, summed over the ranks; then the rms_norm that follows
-        every such projection (with ``next_norm``) and the staging of its result for the next product."""
+        every such projection (with ``next_norm``) and the staging of its result for the next product.  ``whole``: every
+        rank holds all of K and of x (the attention output where the group keeps the attention block whole), so there
+        is nothing to exchange."""
         rt, c = self.rt, self.config
-        local, lo, hi = self.window(k)
-        if self.shard is None:
+        local, lo, hi = self.window(k, whole)
+        if self.shard is None or whole:
             rt.stage(x, c.element)
             rt.linear_staged(weight, self.hidden, [Step(ADD, self.hidden)])
             rt.rms_norm_stage(self.hidden, next_norm, c.floor, c.element)
@@ -154,7 +159,7 @@ class Decoder:
         """Whether the step may fold the norms and stagings into the products' epilogues (``linear_staged_then``):
         1 or 2 sequences, the MLP sealed as a pair, and, for a tensor-parallel rank, a communicator whose exchange a
         product can do in its own epilogue."""
-        if self.batch > 2 or "blk.0.ffn_gate_up.weight" not in self.weights or not self.fold:
+        if self.batch > 2 or "blk.0.ffn_gate_up.weight" not in self.weights or not self.fold or self.whole_attention:
             return False
         return self.shard is None or hasattr(self.comm, "reduce_handle")
 
@@ -219,7 +224,7 @@ class Decoder:
                           self.capacity, self.keys[layer], self.values[layer])
             rt.attend(self.qkv, self.keys[layer], self.values[layer], self.position, self.scale, self.heads,
                       self.key_heads, c.head_width, self.capacity, self.attended)
-            self._row_parallel(self.attended, w[at("attn_output")], c.query_width, n[at("ffn_norm")])
+            self._row_parallel(self.attended, w[at("attn_output")], c.query_width, n[at("ffn_norm")], self.whole_attention)
             if at("ffn_gate_up") in w:   # gate and up sealed as a pair: one product, SwiGLU in its epilogue
                 rt.linear_staged(w[at("ffn_gate_up")], self.held)
             else:
@@ -331,6 +336,8 @@ class Decoder:
 
         if self.shard is not None and not hasattr(self.comm, "reduce_handle"):
             raise ValueError("the persistent step of a tensor-parallel rank exchanges over peer memory: give it a PeerComm")
+        if self.whole_attention:
+            raise ValueError("the persistent step of a rank splits the attention block: make the Shard with attention=\"split\"")
         c, w, n = self.config, self.weights, self.norms
         layers = (NcDecoderLayer * c.layers)()
         for index in range(c.layers):

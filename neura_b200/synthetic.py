@@ -24,7 +24,7 @@ def synthetic_weights(rt: Runtime, config: Config, seed: int = 23, deviation: fl
     if shard is not None:
         qw, kw = shard.query_width, shard.key_width
         shapes = [("attn_q", qw, config.hidden), ("attn_k", kw, config.hidden), ("attn_v", kw, config.hidden),
-                  ("attn_output", config.hidden, shard.window(config.query_width).k),
+                  ("attn_output", config.hidden, shard.window(config.query_width, shard.whole).k),
                   ("ffn_gate", shard.feed_forward, config.hidden), ("ffn_up", shard.feed_forward, config.hidden),
                   ("ffn_down", config.hidden, shard.window(config.feed_forward).k)]
         vocab = shard.vocab

@@ -15,15 +15,16 @@ def gpus() -> int:
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl", "peer-folded", "peer-persistent"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "peer-folded", "peer-persistent", "peer-whole", "nccl-whole"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_a_split_model_decodes_the_oracles_tokens(world, comm):
     if gpus() < world:
         pytest.skip(f"{world} GPUs are not here")
     # peer-folded: the exchanges ride in the epilogues of the row-parallel products; peer-persistent: the whole step
-    # is one cooperative kernel a rank, exchanges and the choice among the ranks' winners inside it
+    # is one cooperative kernel a rank, exchanges and the choice among the ranks' winners inside it; -whole: every rank
+    # keeps the whole attention block, only the MLP and the head are split
     env = dict(os.environ, TP_CHECK_LIMIT="150", NCCL_NVLS_ENABLE="0", TP_COMM=comm.split("-")[0],
-               TP_FOLD="1" if comm.endswith("folded") else "0", TP_STEP="persistent" if comm.endswith("persistent") else "graph",
+               TP_FOLD="1" if comm.endswith("folded") else "0", TP_STEP="persistent" if comm.endswith("persistent") else "graph", TP_ATTENTION="whole" if comm.endswith("whole") else "split",
                TP_CHECK_LOG=os.path.join(ROOT, "gpurun_out", "tp_decode_check.log"))
     run = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",

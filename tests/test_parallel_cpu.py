@@ -33,6 +33,26 @@ def test_shares_partition_rows_and_cover_k_in_whole_blocks():
         parallel.Shard(qwen.QWEN25_05B_Q8, 4, 0)   # 14 query heads over 2 key heads do not split in 4
 
 
+def test_a_group_may_keep_the_attention_block_whole():
+    from neura_b200 import parallel, qwen
+
+    c = qwen.QWEN25_32B_Q4K
+    for world in (2, 4, 8):
+        s = parallel.Shard(c, world, 1, attention="whole")
+        assert (s.heads, s.key_heads, s.query_width) == (c.heads, c.key_heads, c.query_width)   # every head on every rank
+        assert s.rows(c.query_width, whole=True) == (0, c.query_width)
+        w = s.window(c.query_width, whole=True)
+        assert (w.k, w.lo, w.hi, w.first_block) == (c.query_width, 0, c.query_width, 0)
+        assert s.feed_forward == c.feed_forward // world and s.vocab == c.vocab // world      # the MLP and the head are split
+        split = parallel.Shard(c, world, 1)
+        assert s.local_bytes_per_token() > split.local_bytes_per_token()
+    # the heads need not divide by the ranks when the attention stays whole: 14 query heads over 2 key heads on 4 ranks
+    small = qwen.Config("whole-tp", 2, 896, 14, 2, 64, 4864, 151936, qwen.Q8_0)
+    assert parallel.Shard(small, 4, 3, attention="whole").heads == 14
+    with pytest.raises(ValueError):
+        parallel.Shard(c, 2, 0, attention="some")
+
+
 def _rank_main(rank: int, world: int, port: int, out_dir: str) -> None:
     sys.path.insert(0, ROOT)
     import torch

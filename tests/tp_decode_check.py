@@ -40,7 +40,7 @@ def main() -> int:
     rt = nb.Runtime(local)
     rt.use_stream(rt.new_stream())
     device = torch.device("cuda", local)
-    shard = parallel.Shard(config, world, rank)
+    shard = parallel.Shard(config, world, rank, attention=os.environ.get("TP_ATTENTION", "split"))
     stream = torch.cuda.ExternalStream(rt.stream.value, device=device)
     if os.environ.get("TP_COMM", "peer") == "peer":   # the library's own all-reduce over NVLink peer memory
         comm = parallel.PeerComm(rt, world, rank, batch * config.hidden, device=device, stream=stream)
@@ -68,7 +68,8 @@ def main() -> int:
             print(f"FAIL: sequence {b} leaves the oracle at step {at}: {eager[b, at]} for {want[b, at]} "
                   f"(oracle margin {margins[b, at]:.3e})")
             status = 1
-        how = type(comm).__name__ + (", exchanges folded into the products" if decoder.fold else "") + \
+        how = type(comm).__name__ + (", attention whole on every rank" if shard.whole else "") + \
+            (", exchanges folded into the products" if decoder.fold else "") + \
             (", the step as one persistent kernel" if decoder.compiled is not None else "")
         verdict = (f"tp{world}: 64 greedy tokens x {batch} sequences match the oracle, eager and recorded "
                    f"({how})") if status == 0 else f"tp{world}: FAILED ({how})"
