@@ -121,7 +121,8 @@ struct SkinnyPrepParams {
     uint64_t normed_stride;
 };
 
-// Position p of a 16-byte chunk of the A and B tiles holds element kSkChunkOrder[p] of its eight (skinny_row_step).
+// Position p of every eight numbers along K, in the A operand and in the B tiles alike, holds element kSkChunkOrder[p]
+// of the eight (skinny_scaled says why).
 __device__ constexpr int kSkChunkOrder[8] = {0, 2, 1, 3, 4, 6, 5, 7};
 constexpr uint32_t kSkPrepSums = 2048;   // sub-block sums of a row kept in shared memory: rows of up to 65536 numbers
 
