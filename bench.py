@@ -465,16 +465,40 @@ def run_ours(args):
             comm = parallel.TorchComm(world, rank, device=device, stream=tstream)
     weights = synthetic_weights(rt, config, seed=23 + rank, shard=shard)
     norms = synthetic_norms(rt, config)
-    decoder = qwen.Decoder(rt, config, weights, norms, batch=rows, capacity=capacity, shard=shard, comm=comm)
+    wide = 512 if shard is None and config.element == nb.Q4K else 0   # (rows of a tensor-core prompt chunk)
+    decoder = qwen.Decoder(rt, config, weights, norms, batch=rows, capacity=capacity, shard=shard, comm=comm, wide=wide)
     decoder.fold = args.fold == "on"
 
     # the prompt: random token ids; in chunks where the decoder fills in chunks, else one position at a time
     prompts = np.random.default_rng(29).integers(0, config.vocab, (rows, args.prompt), dtype=np.uint32)
     decoder.reset()
     persistent = rows <= 2 and args.step == "persistent" and ((world == 1 and shard is None) or (world > 1 and args.comm == "peer" and args.attention == "split"))
+    prompt_fill = None
     if decoder.chunks:
-        decoder.prefill(prompts)
         fed = args.prompt - 1
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def timed_fill(through_tensor_cores: bool) -> float:
+            decoder.prefill(prompts, wide=through_tensor_cores)   # (first use sizes scratch, makes buffers and loads kernels: not timed)
+            rt.sync()
+            decoder.reset()
+            p0.record(tstream)
+            decoder.prefill(prompts, wide=through_tensor_cores)
+            p1.record(tstream)
+            rt.sync()
+            return p0.elapsed_time(p1)
+
+        tensor_fill = None
+        if decoder.wide and decoder.wide_tokens(args.prompt):
+            tensor_ms = timed_fill(True)
+            decoder.reset()
+            tensor_fill = {"tokens": rows * fed, "ms": tensor_ms, "tok_s": rows * fed / tensor_ms * 1e3,
+                           "rows_a_chunk": decoder.wide, "tokens_through_bf16": rows * decoder.wide_tokens(args.prompt),
+                           "how": "Decoder.prefill(wide=True): the prompt's head through the tcgen05 product with bf16 operands"}
+        fill_ms = timed_fill(False)   # the cache the timed decode reads is the one the f32 chunks leave
+        prompt_fill = {"tokens": rows * fed, "ms": fill_ms, "tok_s": rows * fed / fill_ms * 1e3,
+                       "chunks": list(decoder.chunks), "how": "Decoder.prefill(wide=False): one chunk after another, each chunk size a recorded program that is replayed",
+                       "tensor_cores": tensor_fill}
     else:
         rt.write(decoder.tokens, prompts[:, 0].copy())
         fed = 0
@@ -605,6 +629,8 @@ def run_ours(args):
         }
         if secondary is not None:
             line["secondary"] = secondary
+        if prompt_fill is not None:
+            line["prompt_fill"] = prompt_fill
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(shape)
         print(json.dumps(line))

@@ -330,6 +330,15 @@ impl CudaRuntime {
         });
     }
 
+    /// `decoder::rms` alone (`crates/neura-decoder/src/op.rs:3-5`): f32 rows out, any number of rows (a wide prompt chunk
+    /// on its way to `linear_bf16`).
+    #[allow(clippy::too_many_arguments)]
+    pub fn rms_norm(&self, x: &DeviceBuffer, rows: u32, x_stride: u64, k: u32, weight: Option<&DeviceBuffer>, floor: f32, out: &DeviceBuffer,
+                    out_stride: u64) {
+        let gain = weight.map_or(ptr::null(), |w| w.as_f32().cast_const());
+        check(unsafe { sys::neura_cuda_rms_norm(self.ctx, self.stream, x.as_f32(), rows, x_stride, k, gain, floor, out.as_f32(), out_stride) });
+    }
+
     /// `decoder::partial` over the full width + `Cache::write` (`crates/neura-decoder/src/rope.rs:3-12`, `cache.rs:267-310`).
     #[allow(clippy::too_many_arguments)]
     pub fn rope_cache(&self, qkv: &DeviceBuffer, row_stride: u64, position: &DeviceBuffer, base: f32, batch: u32, heads: u32, key_heads: u32,

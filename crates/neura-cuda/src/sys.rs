@@ -139,6 +139,7 @@ extern "C" {
     pub fn neura_cuda_stage_window(ctx: *mut NcContext, stream: *mut c_void, x_dev: *const f32, rows: u32, x_stride: u64, k: u32, element: u32, lo: u32, hi: u32) -> i32;
     pub fn neura_cuda_linear_staged(ctx: *mut NcContext, stream: *mut c_void, w: *const NcWeight, out_dev: *mut f32, out_stride: u64, chain: *const NcStep, n_steps: u32) -> i32;
     pub fn neura_cuda_rms_norm_stage(ctx: *mut NcContext, stream: *mut c_void, x_dev: *const f32, rows: u32, x_stride: u64, k: u32, weight_dev: *const f32, floor: f32, element: u32, normed_dev: *mut f32, normed_stride: u64) -> i32;
+    pub fn neura_cuda_rms_norm(ctx: *mut NcContext, stream: *mut c_void, x_dev: *const f32, rows: u32, x_stride: u64, k: u32, weight_dev: *const f32, floor: f32, out_dev: *mut f32, out_stride: u64) -> i32;
     pub fn neura_cuda_rope_cache(ctx: *mut NcContext, stream: *mut c_void, qkv_dev: *mut f32, row_stride: u64, position_dev: *const u32, base: f32, batch: u32, heads: u32, key_heads: u32, width: u32, capacity: u32, keys_dev: *mut f32, values_dev: *mut f32) -> i32;
     pub fn neura_cuda_attend(ctx: *mut NcContext, stream: *mut c_void, q_dev: *const f32, q_stride: u64, keys_dev: *const f32, values_dev: *const f32, position_dev: *const u32, scale: f32, batch: u32, heads: u32, key_heads: u32, width: u32, capacity: u32, out_dev: *mut f32, out_stride: u64) -> i32;
     pub fn neura_cuda_rope_cache_rows(ctx: *mut NcContext, stream: *mut c_void, qkv_dev: *mut f32, row_stride: u64, position_dev: *const u32, base: f32, rows: u32, heads: u32, key_heads: u32, width: u32, capacity: u32, keys_dev: *mut f32, values_dev: *mut f32) -> i32;

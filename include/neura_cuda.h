@@ -188,7 +188,10 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream, const nc_weight *w, con
  * crates/neura-precision/src/lib.rs:325-329), the Q4K weight is dequantised exactly and rounded to
  * bf16 tile by tile in shared memory, products accumulate in f32 (tcgen05 MMAs into tensor memory):
  *   out[r*out_stride + c] = chain(sum_k bf16(W[c][k]) * bf16(x[r*x_stride + k]))
- * Needs a sealed (NC_LAYOUT_TILED) Q4K weight; any number of rows. */
+ * Needs a sealed Q4K weight; any number of rows.  A sealed gate|up pair (NC_LAYOUT_TILED_PAIR) gives
+ *   out[r*out_stride + c] = chain(silu(gate_c . x_r) * (up_c . x_r))
+ * as neura_cuda_linear does: the product runs over both halves into scratch of the context and a second kernel
+ * joins them. */
 int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream, const nc_weight *w, const float *x_dev, uint32_t rows,
                                uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
                                uint32_t n_steps);
@@ -221,6 +224,12 @@ int32_t neura_cuda_linear_staged(nc_context *ctx, void *stream, const nc_weight 
 int32_t neura_cuda_rms_norm_stage(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint64_t x_stride,
                                   uint32_t k, const float *weight_dev, float floor, uint32_t element,
                                   float *normed_dev, uint64_t normed_stride);
+
+/* rms_norm alone, for any number of rows (the rows of a wide prompt chunk on their way to neura_cuda_linear_bf16):
+ *   out[r*out_stride + c] = x[r*x_stride + c] / sqrt(mean_c(x[r]^2) + floor) * weight[c]
+ * `weight_dev` may be NULL; `out_dev` may be `x_dev`. */
+int32_t neura_cuda_rms_norm(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint64_t x_stride,
+                            uint32_t k, const float *weight_dev, float floor, float *out_dev, uint64_t out_stride);
 
 /* rope over the full head width (crates/neura-decoder/src/rope.rs:3-12 -> crates/neura-kernel/src/task/rope.rs:48-122,
  * half rotation, angle = position * base^(-2c/width)) applied in place to the query and key parts of

@@ -24,7 +24,7 @@ SYMBOLS = [
     "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free", "neura_cuda_decoder_trace", "neura_cuda_rope_attend", "neura_cuda_rope_table", "neura_cuda_allreduce_norm_stage", "neura_cuda_staging_select",
     "neura_cuda_linear_staged_then", "neura_cuda_set_wait_limit", "neura_cuda_memory", "neura_cuda_comm_connect_local",
     "neura_cuda_linear_staged_fused", "neura_cuda_rope_cache_rows", "neura_cuda_attend_rows",
-    "neura_cuda_decoder_compile_rank",
+    "neura_cuda_decoder_compile_rank", "neura_cuda_rms_norm",
 ]
 
 
@@ -126,6 +126,7 @@ def load() -> ctypes.CDLL:
         "neura_cuda_stream_create": (i32, [p, pp]),
         "neura_cuda_stream_destroy": (i32, [p, p]),
         "neura_cuda_rms_norm_stage": (i32, [p, p, p, u32, u64, u32, p, ctypes.c_float, u32, p, u64]),
+        "neura_cuda_rms_norm": (i32, [p, p, p, u32, u64, u32, p, ctypes.c_float, p, u64]),
         "neura_cuda_rope_cache": (i32, [p, p, p, u64, p, ctypes.c_float, u32, u32, u32, u32, u32, p, p]),
         "neura_cuda_attend": (i32, [p, p, p, u64, p, p, p, ctypes.c_float, u32, u32, u32, u32, u32, p, u64]),
         "neura_cuda_rope_cache_rows": (i32, [p, p, p, u64, p, ctypes.c_float, u32, u32, u32, u32, u32, p, p]),

@@ -453,4 +453,46 @@ __global__ void advance_kernel(uint32_t *position, uint32_t rows, uint32_t by) {
     if (i < rows) position[i] += by;
 }
 
+// rms_norm alone (crates/neura-decoder/src/op.rs:3-5 -> crates/neura-kernel/src/task/norm.rs:55-131, op = NORM_RMS)
+// for any number of rows: one CTA a row, y = x / sqrt(mean(x^2) + floor) * weight as f32.  The rows of a wide prompt
+// chunk take it on their way to the tensor-core product, which rounds them to bf16 itself.
+__global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float *x, uint64_t x_stride, uint32_t k, const float *weight,
+                                                           float floor, float *out, uint64_t out_stride) {
+    __shared__ float partial[8];
+    __shared__ float scale_shared;
+    const float *row = x + (uint64_t)blockIdx.x * x_stride;
+    float square = 0.0f;
+    for (uint32_t c = threadIdx.x; c < k; c += blockDim.x) square = fmaf(row[c], row[c], square);
+    for (int o = 16; o; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = square;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (uint32_t w = 0; w < blockDim.x >> 5; ++w) total += partial[w];
+        scale_shared = 1.0f / sqrtf(total / (float)k + floor);
+    }
+    __syncthreads();
+    const float scale = scale_shared;
+    float *to = out + (uint64_t)blockIdx.x * out_stride;
+    for (uint32_t c = threadIdx.x; c < k; c += blockDim.x) {
+        float y = row[c] * scale;
+        if (weight) y = y * weight[c];
+        to[c] = y;
+    }
+}
+
+// The second half of a product with a sealed gate|up pair when the product itself ran as a plain one over the
+// pair's 32-row tiles (16 gate rows, then the 16 up rows of the same columns): out[r][c] = chain(silu(gate) * up).
+__global__ void swiglu_pair_kernel(const float *both, uint64_t both_stride, uint32_t rows, uint32_t n, float *out,
+                                   uint64_t out_stride, const __grid_constant__ Chain chain) {
+    const uint64_t total = (uint64_t)rows * n;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = i / n;
+        const uint32_t c = (uint32_t)(i % n);
+        const float *at = both + r * both_stride + (uint64_t)(c / 16) * 32 + c % 16;
+        const float gate = at[0], other = at[16];
+        out[r * out_stride + c] = chained(chain, r, c, gate * sigmoid_f(gate) * other);
+    }
+}
+
 }  // namespace nc

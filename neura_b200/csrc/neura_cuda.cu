@@ -89,7 +89,7 @@ struct nc_context {
     Staging slots[kStagingSlots];
     uint32_t cur = 0;            // the slot neura_cuda_stage writes and the products read (neura_cuda_staging_select)
     Region squares;              // [rows][chunks] sums of squares left by an epilogue that staged with a norm's gain
-    Region partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch, x_bf16;
+    Region partial, counters, status, stage_x, stage_out, attend_partial, attend_counters, argmax_scratch, x_bf16, pair_out;
     Region sk_xh, sk_sx, sk_xs, sk_rs, sk_partial, sk_counters;   // the skinny product's staged activations and split-K scratch
     uint32_t sk_bpad = 0, sk_sx_cols = 0;
     uint64_t launches = 0;
@@ -626,7 +626,7 @@ int32_t neura_cuda_close(nc_context *ctx) {
     for (Staging &slot : ctx->slots)
         for (Region *region : {&slot.dig, &slot.cs, &slot.sums, &slot.chunks})
             if (region->ptr) cudaFree(region->ptr);
-    for (Region *region : {&ctx->squares, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16,
+    for (Region *region : {&ctx->squares, &ctx->partial, &ctx->counters, &ctx->status, &ctx->stage_x, &ctx->stage_out, &ctx->attend_partial, &ctx->attend_counters, &ctx->argmax_scratch, &ctx->x_bf16, &ctx->pair_out,
                            &ctx->sk_xh, &ctx->sk_sx, &ctx->sk_xs, &ctx->sk_rs, &ctx->sk_partial, &ctx->sk_counters})
         if (region->ptr) cudaFree(region->ptr);
     delete ctx;
@@ -1098,10 +1098,14 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     if (!ctx || !x_dev || !out_dev) return refuse(kBadArgument, "a product needs a context, activations and an output");
     int32_t rc;
     if ((rc = check_weight(w))) return rc;
-    if (w->element != NC_ELEMENT_Q4K || w->layout != NC_LAYOUT_TILED)
+    if (w->element != NC_ELEMENT_Q4K || (w->layout != NC_LAYOUT_TILED && w->layout != NC_LAYOUT_TILED_PAIR))
         return refuse(kBadArgument, "the tensor-core product takes a sealed Q4K weight (element %u, layout %u given)",
                       w->element, w->layout);
     if (rows == 0) return refuse(kBadArgument, "a product of no rows computes nothing");
+    // a sealed gate|up pair is a sealed weight of twice the rows whose 32-row tiles hold 16 gate rows and the 16 up
+    // rows of the same columns: the product runs over all of them into scratch, a second kernel joins the halves
+    const bool pair = w->layout == NC_LAYOUT_TILED_PAIR;
+    const uint32_t n_all = pair ? (w->n + 15) / 16 * 32 : w->n;
     if (x_stride < w->k || out_stride < w->n)
         return refuse(kBadArgument, "rows of %u activations and %u outputs overlap at strides %llu and %llu", w->k, w->n,
                       (unsigned long long)x_stride, (unsigned long long)out_stride);
@@ -1110,6 +1114,7 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
     if ((rc = ensure(ctx, ctx->x_bf16, (uint64_t)rows * w->k * 2, false))) return rc;
     if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
+    if (pair && (rc = ensure(ctx, ctx->pair_out, (uint64_t)rows * n_all * sizeof(float), false))) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
     const uint64_t total = (uint64_t)rows * w->k;
     const uint64_t want = (total + 255) / 256;
@@ -1127,18 +1132,40 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     if ((rc = tensor_map_16bit(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ctx->x_bf16.ptr, w->k, rows, kGemmBM))) return rc;
     p.w = (const uint8_t *)w->data_dev;
     p.x = (const __nv_bfloat16 *)ctx->x_bf16.ptr;
-    p.out = out_dev;
-    p.out_stride = out_stride;
+    p.out = pair ? (float *)ctx->pair_out.ptr : out_dev;
+    p.out_stride = pair ? n_all : out_stride;
     p.m = rows;
-    p.n = w->n;
+    p.n = n_all;
     p.k = w->k;
-    p.units32 = (w->n + 31) / 32;
+    p.units32 = (n_all + 31) / 32;
     p.status = (unsigned int *)ctx->status.ptr;
-    p.chain.n = n_steps;
-    for (uint32_t s = 0; s < n_steps; ++s) p.chain.step[s] = chain[s];
-    NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((w->n + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM),
+    Chain steps;
+    memset(&steps, 0, sizeof steps);
+    steps.n = n_steps;
+    for (uint32_t s = 0; s < n_steps; ++s) steps.step[s] = chain[s];
+    if (!pair) p.chain = steps;
+    NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((n_all + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM),
                              dim3(kGemmThreads), kGemmSmem, stream, p));
     ctx->launches++;
+    if (pair) {
+        const uint64_t cells = ((uint64_t)rows * w->n + 255) / 256;
+        const unsigned int grid = (unsigned int)(cells < (uint64_t)ctx->sms * 16 ? cells : (uint64_t)ctx->sms * 16);
+        swiglu_pair_kernel<<<grid, 256, 0, stream>>>((const float *)ctx->pair_out.ptr, n_all, rows, w->n, out_dev, out_stride, steps);
+        ctx->launches++;
+        NC_CUDA(cudaGetLastError());
+    }
+    return 0;
+}
+
+int32_t neura_cuda_rms_norm(nc_context *ctx, void *stream, const float *x_dev, uint32_t rows, uint64_t x_stride, uint32_t k,
+                            const float *weight_dev, float floor, float *out_dev, uint64_t out_stride) {
+    if (!ctx || !x_dev || !out_dev) return refuse(kBadArgument, "a norm needs a context, rows to norm and somewhere to put them");
+    if (!rows || !k) return refuse(kBadArgument, "a norm of %u rows of %u numbers computes nothing", rows, k);
+    if (x_stride < k || out_stride < k) return refuse(kBadArgument, "rows of %u numbers overlap at the strides given", k);
+    if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
+    rms_norm_rows_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(x_dev, x_stride, k, weight_dev, floor, out_dev, out_stride);
+    ctx->launches++;
+    NC_CUDA(cudaGetLastError());
     return 0;
 }
 

@@ -88,10 +88,12 @@ class Decoder:
     """
 
     def __init__(self, rt: Runtime, config: Config, weights: Dict[str, Weight], norms: Dict[str, DeviceTensor],
-                 batch: int = 1, capacity: int = 640, shard=None, comm=None):
+                 batch: int = 1, capacity: int = 640, shard=None, comm=None, wide: int = 0):
         """``shard`` (parallel.Shard) and ``comm`` (parallel.TorchComm) make this one rank of a
         tensor-parallel group: ``weights`` then hold the rank's shares (q/k/v, gate, up and head
-        rows; the K blocks of attention output and down that cover its window)."""
+        rows; the K blocks of attention output and down that cover its window).
+        ``wide`` > 0 asks for the tensor-core prompt path: the head of a long prompt is fed in chunks of up to ``wide``
+        rows through the bf16 product (``fill_wide``); the caller asks because that product rounds both operands."""
         if batch > 16:
             raise ValueError("one decode step carries at most 16 sequences")
         if (shard is None) != (comm is None):
@@ -121,9 +123,14 @@ class Decoder:
         # scratch for the decode step and for the largest prompt chunk, all of it now: a recorded step holds the
         # scratch's addresses, so nothing may grow it later
         most = max([batch, *self.chunks])
+        if wide and (shard is not None or c.element != Q4K):
+            raise ValueError("the tensor-core prompt path takes sealed Q4_K weights on one GPU")
+        self.wide = min(int(wide), capacity) if wide else 0
         rt.reserve(most, max(self.vocab, 2 * self.feed_forward, c.hidden), widest_k)   # 2x: a sealed gate|up pair
-        rt.reserve_decoder(most, self.heads, self.key_heads, c.head_width, capacity)
+        rt.reserve_decoder(max(most, self.wide), self.heads, self.key_heads, c.head_width, capacity)
+        self._wide_rows = None   # the activation rows of a wide chunk, made at its first use
         self.program: Optional[int] = None
+        self._fill_programs: dict = {}   # (plane, rows of a chunk) -> "seen" once, then the chunk's recorded program
         self.compiled = None   # the step as one persistent kernel (compile())
         self.fold = False      # True: fold norms and stagings into the products' epilogues (fewer, longer launches)
         self.scale = 1.0 / float(c.head_width) ** 0.5
@@ -268,6 +275,33 @@ class Decoder:
         held = self._fill_buffers(rows)
         rt.write(held["tokens"], tokens)
         rt.write(held["position"], np.arange(start, start + rows, dtype=np.uint32))
+        # the launches of a chunk depend on (plane, row count) only: tokens and cursors are read from device buffers.
+        # The first chunk of a kind runs as it is issued (it may still size scratch), the second is recorded into a
+        # program, later ones replay it: 700 launches a chunk cost more on the host than on the device otherwise.
+        key = (sequence, rows)
+        state = self._fill_programs.get(key)
+        if isinstance(state, int):
+            rt.run(state)
+            return
+        if state == "seen":
+            rt.capture_begin()
+            try:
+                self._fill_launches(sequence, rows, held)
+            except Exception:
+                try:
+                    rt.program_free(rt.capture_end())
+                except Exception:
+                    pass
+                raise
+            self._fill_programs[key] = rt.capture_end()
+            rt.run(self._fill_programs[key])
+            return
+        self._fill_programs[key] = "seen"
+        self._fill_launches(sequence, rows, held)
+
+    def _fill_launches(self, sequence: int, rows: int, held: dict) -> None:
+        """The launches of one prompt chunk of ``rows`` tokens of plane ``sequence`` (tokens and cursors in ``held``)."""
+        rt, c, w, n = self.rt, self.config, self.weights, self.norms
         hidden, qkv, attended, mlp = held["hidden"], held["qkv"], held["attended"], held["held"]
         per_plane = self.key_heads * self.capacity * c.head_width * 4
         rt.staging_select(0)
@@ -293,6 +327,66 @@ class Decoder:
             rt.stage(mlp, c.element)
             rt.linear_staged(w[at("ffn_down")], hidden, [Step(ADD, hidden)])
 
+    WIDE_FROM = 64   # fewer prompt tokens than this go through the ordinary chunks
+
+    def wide_tokens(self, length: int) -> int:
+        """How many leading tokens of a prompt of ``length`` ``prefill`` feeds through ``fill_wide``."""
+        fed = length - 1
+        return 0 if not self.wide or fed < self.WIDE_FROM else fed - (fed % self.wide if fed % self.wide < self.WIDE_FROM else 0)
+
+    def fill_wide(self, sequence: int, tokens, start: int) -> None:
+        """A prompt chunk of up to ``wide`` rows on the tensor cores: as ``fill``, but every projection is the prefill
+        product (template_run_matmul_cooperative, crates/neura-kernel/src/task/matmul.rs:1344-1565: weights dequantised
+        to bf16 tile by tile, activations rounded to bf16, f32 accumulation), so a 512-token prompt streams each weight
+        once or twice instead of sixteen times.  Norms, RoPE, the cache and attention stay f32."""
+        import numpy as np
+
+        rt, c, w, n = self.rt, self.config, self.weights, self.norms
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32).reshape(-1)
+        rows = int(tokens.size)
+        if not self.wide:
+            raise ValueError("this decoder was built without the tensor-core prompt path (wide=0)")
+        if not 1 <= rows <= self.wide:
+            raise ValueError(f"a wide chunk holds 1 to {self.wide} tokens, not {rows}")
+        if not 0 <= sequence < self.batch or start + rows > self.capacity:
+            raise ValueError(f"plane {sequence} has no room for cursors {start}..{start + rows - 1}")
+        if self._wide_rows is None:
+            most = self.wide
+            self._wide_rows = {
+                "tokens": rt.tensor_u32(most), "position": rt.tensor_u32(most), "hidden": rt.tensor(most, c.hidden),
+                "normed": rt.tensor(most, c.hidden), "qkv": rt.tensor(most, self.query_width + 2 * self.key_width),
+                "attended": rt.tensor(most, self.query_width), "held": rt.tensor(most, self.feed_forward),
+                "gate": rt.tensor(most, self.feed_forward),
+            }
+        held = self._wide_rows
+        padded = np.zeros(self.wide, dtype=np.uint32)
+        padded[:rows] = tokens
+        rt.write(held["tokens"], padded)
+        padded[:rows] = np.arange(start, start + rows, dtype=np.uint32)
+        padded[rows:] = 0
+        rt.write(held["position"], padded)
+        hidden, normed, qkv, attended, mlp = held["hidden"], held["normed"], held["qkv"], held["attended"], held["held"]
+        per_plane = self.key_heads * self.capacity * c.head_width * 4
+        rt.embed(w["token_embd.weight"], held["tokens"], hidden, rows=rows)
+        for layer in range(c.layers):
+            at = lambda name: f"blk.{layer}.{name}.weight"  # noqa: E731
+            keys_ptr = self.keys[layer].ptr + sequence * per_plane
+            values_ptr = self.values[layer].ptr + sequence * per_plane
+            rt.rms_norm(hidden, n[at("attn_norm")], c.floor, normed, rows=rows)
+            rt.linear_bf16(w[at("attn_qkv")], normed, qkv, rows=rows)
+            rt.rope_cache_rows(qkv, held["position"], c.rope_base, rows, self.heads, self.key_heads, c.head_width,
+                               self.capacity, keys_ptr, values_ptr)
+            rt.attend_rows(qkv, keys_ptr, values_ptr, held["position"], self.scale, rows, self.heads, self.key_heads,
+                           c.head_width, self.capacity, attended)
+            rt.linear_bf16(w[at("attn_output")], attended, hidden, [Step(ADD, hidden)], rows=rows)
+            rt.rms_norm(hidden, n[at("ffn_norm")], c.floor, normed, rows=rows)
+            if at("ffn_gate_up") in w:
+                rt.linear_bf16(w[at("ffn_gate_up")], normed, mlp, rows=rows)
+            else:
+                rt.linear_bf16(w[at("ffn_gate")], normed, held["gate"], [Step(SILU)], rows=rows)
+                rt.linear_bf16(w[at("ffn_up")], normed, mlp, [Step(MUL, held["gate"])], rows=rows)
+            rt.linear_bf16(w[at("ffn_down")], mlp, hidden, [Step(ADD, hidden)], rows=rows)
+
     def _fill_buffers(self, rows: int) -> dict:
         """The activation rows of a chunk of ``rows`` tokens (kept per row count: shapes carry the row strides)."""
         if not hasattr(self, "_fills"):
@@ -306,15 +400,20 @@ class Decoder:
             }
         return self._fills[rows]
 
-    def prefill(self, prompts) -> None:
-        """Feeds all but the last token of every plane's prompt in chunks (``fill``), then leaves tokens and cursors
-        so that the next ``run_token`` feeds the last prompt token of every plane."""
+    def prefill(self, prompts, wide: bool = True) -> None:
+        """Feeds all but the last token of every plane's prompt in chunks (``fill``; where the decoder was built with
+        ``wide`` rows and ``wide`` is left on, the head of a long prompt through ``fill_wide``), then leaves tokens and
+        cursors so that the next ``run_token`` feeds the last prompt token of every plane."""
         import numpy as np
 
         prompts = np.ascontiguousarray(prompts, dtype=np.uint32).reshape(self.batch, -1)
         length = prompts.shape[1]
         for sequence in range(self.batch):
-            at = 0
+            at, wide_end = 0, self.wide_tokens(length) if wide else 0
+            while at < wide_end:   # the head of a long prompt on the tensor cores, where the decoder was built for it
+                take = min(self.wide, wide_end - at)
+                self.fill_wide(sequence, prompts[sequence, at: at + take], at)
+                at += take
             while at < length - 1:
                 left = length - 1 - at
                 take = next((size for size in self.chunks if size <= left), left)

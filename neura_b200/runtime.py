@@ -386,6 +386,15 @@ class Runtime:
             ctypes.c_void_p(normed.ptr) if normed is not None else None,
             normed.shape[-1] if normed is not None else 0))
 
+    def rms_norm(self, x: DeviceTensor, weight: Optional[DeviceTensor], floor: float, out: DeviceTensor,
+                 rows: Optional[int] = None, k: Optional[int] = None) -> None:
+        """decoder::rms (crates/neura-decoder/src/op.rs:3-5) alone: f32 rows out, any number of rows."""
+        rows = rows if rows is not None else x.rows
+        k = k if k is not None else x.shape[-1]
+        _check(self._lib.neura_cuda_rms_norm(self._ctx, self.stream, ctypes.c_void_p(x.ptr), rows, x.shape[-1], k,
+                                             ctypes.c_void_p(weight.ptr) if weight is not None else None, floor,
+                                             ctypes.c_void_p(out.ptr), out.shape[-1]))
+
     def rope_cache(self, qkv: DeviceTensor, position: DeviceTensor, base: float, heads: int, key_heads: int,
                    width: int, capacity: int, keys: DeviceTensor, values: DeviceTensor,
                    batch: Optional[int] = None) -> None:

@@ -14,6 +14,13 @@ import numpy as np
 import oracle
 
 
+def bf16_round(values: np.ndarray) -> np.ndarray:
+    """f32 -> bf16 -> f32, round to nearest even (crates/neura-precision/src/lib.rs:325-329); finite inputs."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32)
+    rounded = (bits + (((bits >> np.uint32(16)) & np.uint32(1)) + np.uint32(0x7FFF))) & np.uint32(0xFFFF0000)
+    return rounded.view(np.float32)
+
+
 class OracleDecoder:
     def __init__(self, config, packed: dict, norms: dict, batch: int = 1, capacity: int = 640, threads: int = 8):
         """``packed``: name -> GGUF bytes of "token_embd.weight", "output.weight" and per layer
@@ -33,8 +40,14 @@ class OracleDecoder:
         self.values = np.zeros_like(self.keys)
         self.position = np.zeros(batch, dtype=np.uint32)
         self.logits = None
+        self.bf16 = False     # True while a step stands for a row of a tensor-core prompt chunk
+        self.w_bf16 = {}
 
     def _mm(self, name: str, x: np.ndarray) -> np.ndarray:
+        if self.bf16:   # the tensor path: both operands rounded to bf16, f32 accumulation
+            if name not in self.w_bf16:
+                self.w_bf16[name] = bf16_round(self.w[name])
+            return oracle.matmul_f32(self.w_bf16[name], bf16_round(x), threads=self.threads)
         return oracle.matmul_f32(self.w[name], x, threads=self.threads)
 
     def step(self, tokens: np.ndarray) -> np.ndarray:
@@ -88,16 +101,19 @@ class OracleDecoder:
                     self.values[:, b] = saved[1][:, b]
         self.position[:] = keep
 
-    def generate(self, prompts: np.ndarray, steps: int):
+    def generate(self, prompts: np.ndarray, steps: int, bf16_tokens: int = 0):
         """Returns (tokens [batch, steps], margins [batch, steps]): the gap between the two largest
-        logits at every decoded step, which says how decisive each greedy choice was."""
+        logits at every decoded step, which says how decisive each greedy choice was.  The first ``bf16_tokens``
+        prompt tokens go through products with bf16 operands (a prompt fed through the tensor path)."""
         prompts = np.ascontiguousarray(prompts, dtype=np.uint32).reshape(self.batch, -1)
         self.position[:] = 0
         out = np.zeros((self.batch, steps), dtype=np.uint32)
         margins = np.zeros((self.batch, steps), dtype=np.float32)
         chosen = None
         for at in range(prompts.shape[1]):
+            self.bf16 = at < bf16_tokens
             chosen = self.step(prompts[:, at].copy())
+        self.bf16 = False
         for at in range(steps):
             if at:
                 chosen = self.step(chosen)

@@ -170,9 +170,10 @@ def test_greedy_tokens_match_the_oracle_for_64_steps(oracle, name, batch):
                     f"the oracle's margin there is {margins[b, at]:.3e}")
 
 
-@pytest.mark.parametrize("name,batch,length", [("q4_k", 1, 45), ("q4_k", 2, 70), ("q8_0", 1, 45), ("q8_0", 3, 21)])
+@pytest.mark.parametrize("name,batch,length", [("q4_k", 1, 45), ("q4_k", 2, 70), ("q4_k", 1, 110), ("q8_0", 1, 45), ("q8_0", 3, 21)])
 def test_a_prompt_fed_in_chunks_decodes_what_the_oracle_decodes(oracle, name, batch, length):
-    # Batch::prefill (crates/neura-generate/src/batch.rs:1595-1599): chunks of 32 and 8 (16 and 8 for Q8_0), the rest alone
+    # Batch::prefill (crates/neura-generate/src/batch.rs:1595-1599): chunks of 32 and 8 (16 and 8 for Q8_0), the rest alone.
+    # (70 tokens: the second chunk of 32 is recorded and replayed; 110 tokens: the third replays the recorded program)
     from oracle.decoder import OracleDecoder, synthetic_model
 
     config = SMALL[name]
@@ -198,6 +199,52 @@ def test_a_prompt_fed_in_chunks_decodes_what_the_oracle_decodes(oracle, name, ba
     if differs.size:
         b, at = differs[0]
         pytest.fail(f"sequence {b} leaves the oracle at step {at}: {chunked[b, at]} for {want[b, at]}, "
+                    f"the oracle's margin there is {margins[b, at]:.3e}")
+
+
+@pytest.mark.parametrize("rows,k,stride", [(1, 896, 896), (70, 1024, 1024), (300, 5120, 5200)])
+def test_rms_norm_of_many_rows_matches_the_oracle(oracle, rows, k, stride):
+    x = oracle.Stream(83).normal(rows * stride).reshape(rows, stride).astype(np.float32)
+    gain = oracle.Stream(85).uniform(k, 0.5, 1.5).astype(np.float32)
+    want = oracle.rms_norm(np.ascontiguousarray(x[:, :k]), gain, 1e-6)
+    with nb.Runtime(0) as rt:
+        xd, gd, od = rt.tensor(rows, stride), rt.tensor(k), rt.tensor(rows, stride)
+        rt.write(xd, x)
+        rt.write(gd, gain)
+        rt.write(od, np.zeros((rows, stride), dtype=np.float32))
+        rt.rms_norm(xd, gd, 1e-6, od, k=k)
+        got = rt.read(od).reshape(rows, stride)
+    assert np.abs(got[:, :k] - want).max() <= 1e-5 * np.abs(want).max()
+    assert not got[:, k:].any(), "the columns past k stay as they were"
+
+
+@pytest.mark.parametrize("batch,length,wide", [(1, 200, 128), (2, 150, 128), (1, 330, 512)])
+def test_a_prompt_fed_through_the_tensor_cores_decodes_what_the_oracle_decodes(oracle, batch, length, wide):
+    # the head of the prompt in chunks of up to `wide` rows through the bf16 product (200: 128 + 71 rows; 150: 128 rows,
+    # then 21 tokens through the f32 chunks; 330: one chunk of 329 rows); the oracle rounds the same products' operands
+    from oracle.decoder import OracleDecoder, synthetic_model
+
+    config = SMALL["q4_k"]
+    packed, norms = synthetic_model(config, seed=23)
+    prompts = (oracle.Stream(47).uniform(batch * length, 0.0, 1.0) * config.vocab).astype(np.uint32).reshape(batch, length)
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weights, dnorms = load_model(rt, config, packed, norms)
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=length + 40, wide=wide)
+        through = decoder.wide_tokens(length)
+        decoder.record()
+        got = decoder.generate(prompts, 32, chunked=True)
+        again = decoder.generate(prompts, 32, chunked=True)
+    finally:
+        rt.close()
+    assert through == {200: 199, 150: 128, 330: 329}[length]
+    want, margins = OracleDecoder(config, packed, norms, batch=batch, capacity=length + 40).generate(prompts, 32, bf16_tokens=through)
+    assert np.array_equal(got, again), "the same prompt fills the cache the same way twice"
+    differs = np.argwhere(got != want)
+    if differs.size:
+        b, at = differs[0]
+        pytest.fail(f"sequence {b} leaves the oracle at step {at}: {got[b, at]} for {want[b, at]}, "
                     f"the oracle's margin there is {margins[b, at]:.3e}")
 
 

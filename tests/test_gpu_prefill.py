@@ -72,6 +72,35 @@ def test_prefill_product_at_the_benchmark_rows_on_a_slice_of_its_width(runtime, 
     check(runtime, oracle, 2048, 256, 3584)
 
 
+@pytest.mark.parametrize("m,n,k,residual", [(96, 320, 512, False), (300, 300, 768, True), (1, 16, 256, False)])
+def test_prefill_product_of_a_sealed_gate_up_pair(runtime, oracle, m, n, k, residual):
+    # the pair's tiles hold 16 gate rows and the 16 up rows of the same columns: out = chain(silu(gate . x) * (up . x))
+    gate = oracle.Stream(71).normal(n * k, 0.0, 0.02).reshape(n, k)
+    up = oracle.Stream(73).normal(n * k, 0.0, 0.02).reshape(n, k)
+    packed_gate, packed_up = oracle.pack_rows(nb.Q4K, gate), oracle.pack_rows(nb.Q4K, up)
+    x = oracle.Stream(75).normal(m * k).reshape(m, k)
+    weight = runtime.load_pair(nb.Q4K, n, k, packed_gate, packed_up)
+    xd, od = runtime.tensor(m, k), runtime.tensor(m, n)
+    runtime.write(xd, x)
+    threads = os.cpu_count() or 8
+    g = oracle.linear(nb.Q4K, packed_gate, n, k, x, threads=threads, bf16=True)
+    u = oracle.linear(nb.Q4K, packed_up, n, k, x, threads=threads, bf16=True)
+    want = g * (np.float32(1.0) / (np.float32(1.0) + np.exp(-g, dtype=np.float32))) * u
+    steps = None
+    if residual:
+        carried = oracle.Stream(77).normal(m * n).reshape(m, n).astype(np.float32)
+        runtime.write(od, carried)
+        steps = [nb.Step(nb.ADD, od)]   # in place, as a decoder layer adds its residual
+        want = want + carried
+    runtime.linear_bf16(weight, xd, od, steps)
+    got = runtime.read(od).reshape(m, n)
+    scale = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    worst = float(np.abs(got - want).max())
+    assert worst <= REL_TOL * scale, f"pair [{m}x{k}] x 2[{n}x{k}]: |diff| {worst:.3e} against rms {scale:.3e}"
+    for ptr in (xd.ptr, od.ptr, weight.ptr):
+        runtime.free(ptr)
+
+
 def test_prefill_refuses_what_it_does_not_multiply(runtime, oracle):
     w = oracle.Stream(3).normal(32 * 256, 0.0, 0.02).reshape(32, 256)
     q8 = runtime.load(nb.Q8_0, 32, 256, oracle.pack_rows(nb.Q8_0, w))

@@ -382,3 +382,13 @@ def test_sixteen_bit_weights_round_as_the_reference_packs_them(oracle):
     rounded = ((w.view(np.uint32).astype(np.uint64) + 0x7fff + ((w.view(np.uint32) >> 16) & 1)) >> 16 << 16).astype(np.uint32)
     assert np.array_equal(bits(brains), rounded)
     assert oracle.payload_bytes(oracle.HALF, 7) == 14 and oracle.pack(oracle.HALF, w[:7]).size == 16
+
+
+def test_the_decoder_oracle_rounds_to_bf16_as_the_c_oracle_does(oracle):
+    from oracle.decoder import bf16_round
+
+    x = oracle.Stream(5).normal(4096).astype(np.float32)
+    x[:6] = [1.00390625, 1.01171875, -1.00390625, 0.0, 3.0e38, 1e-40]   # two ties, a negative tie, zero, near the top, a subnormal
+    want = np.array([oracle.lib().nro_bf16_rne(float(v)) for v in x], dtype=np.uint16)
+    got = (bf16_round(x).view(np.uint32) >> 16).astype(np.uint16)
+    assert np.array_equal(got, want)
