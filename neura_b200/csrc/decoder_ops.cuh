@@ -453,6 +453,179 @@ __global__ void advance_kernel(uint32_t *position, uint32_t rows, uint32_t by) {
     if (i < rows) position[i] += by;
 }
 
+// Attention for many rows of ONE sequence (a wide prompt chunk): a CTA takes 16 consecutive rows and one key head, so
+// a tile of keys and values is read from the cache once for 16 x group queries instead of once for `group`.  The
+// tiles are walked in order with the running largest logit and sum of each query (the same softmax, summed tile by
+// tile); row r sees the positions up to its own cursor.  All f32, as the decode attention.
+constexpr uint32_t kBlockRows = 16;      // query rows a CTA
+constexpr uint32_t kBlockTile = 32;      // positions a tile: one a lane
+constexpr uint32_t kBlockThreads = 256;
+constexpr uint32_t kAttendBlockFrom = 64;   // fewer rows than this keep the kernel of the decode step (a CTA a row)
+constexpr uint32_t kBlockQueriesPerWarp = kBlockRows * kAttendMaxGroup / (kBlockThreads / 32);   // 16
+
+struct AttendBlockParams {
+    const float *q;               // [rows][q_stride], head h at h*width
+    uint64_t q_stride;
+    const float *keys, *values;   // [key_heads][capacity][width] of the sequence
+    const uint32_t *position;     // [rows]
+    float *out;                   // [rows][out_stride]
+    uint64_t out_stride;
+    float scale;
+    uint32_t rows, heads, key_heads, capacity;
+};
+
+inline size_t attend_block_smem(uint32_t width, uint32_t group) {
+    const size_t queries = (size_t)kBlockRows * group;
+    return (queries * width + (size_t)kBlockTile * (width + 4) + (size_t)kBlockTile * width + queries * kBlockTile + queries * 3) * sizeof(float);
+}
+
+template <uint32_t WIDTH>
+__global__ void __launch_bounds__(kBlockThreads) attend_block_kernel(const __grid_constant__ AttendBlockParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    extern __shared__ __align__(16) float shared[];
+    constexpr uint32_t KROW = WIDTH + 4;      // padded key row: float4 reads of 8 rows hit 32 banks
+    constexpr uint32_t PER = WIDTH / 32;      // output channels a lane
+    const uint32_t group = p.heads / p.key_heads, queries = kBlockRows * group;
+    float *qs = shared;                                   // [queries][WIDTH], query r*group + g
+    float *ks = qs + queries * WIDTH;                     // [32][KROW]
+    float *vs = ks + kBlockTile * KROW;                   // [32][WIDTH]
+    float *weights = vs + kBlockTile * WIDTH;             // [queries][32]: exp(logit - largest so far) of this tile
+    float *largest = weights + queries * kBlockTile;      // [queries]
+    float *sums = largest + queries;                      // [queries]
+    float *shrink = sums + queries;                       // [queries]: exp(largest before - largest after) of this tile
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t blocks = (p.rows + kBlockRows - 1) / kBlockRows;
+    // (the longest row blocks first: a block's work grows with its cursors)
+    const uint32_t block = blocks - 1 - blockIdx.x / p.key_heads, kh = blockIdx.x % p.key_heads;
+    const uint32_t row0 = block * kBlockRows;
+    uint32_t most = 0;
+    for (uint32_t r = 0; r < kBlockRows; ++r) most = max(most, min(p.position[min(row0 + r, p.rows - 1)] + 1, p.capacity));
+    for (uint32_t i = threadIdx.x; i < queries * (WIDTH / 4); i += blockDim.x) {
+        const uint32_t query = i / (WIDTH / 4), quad = i % (WIDTH / 4);
+        const uint32_t row = min(row0 + query / group, p.rows - 1), g = query % group;   // (a row past the end repeats the last)
+        reinterpret_cast<float4 *>(qs)[i] = *reinterpret_cast<const float4 *>(p.q + (uint64_t)row * p.q_stride + (uint64_t)(kh * group + g) * WIDTH + quad * 4);
+    }
+    for (uint32_t i = threadIdx.x; i < queries; i += blockDim.x) { largest[i] = -INFINITY; sums[i] = 0.0f; }
+    float acc[kBlockQueriesPerWarp][PER];
+#pragma unroll
+    for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j)
+#pragma unroll
+        for (uint32_t c = 0; c < PER; ++c) acc[j][c] = 0.0f;
+    const float *k = p.keys + (uint64_t)kh * p.capacity * WIDTH, *v = p.values + (uint64_t)kh * p.capacity * WIDTH;
+    for (uint32_t t0 = 0; t0 < most; t0 += kBlockTile) {
+        __syncthreads();   // the tile before is done with (and, the first time, the queries are in place)
+        const uint32_t held = min(kBlockTile, most - t0);
+        for (uint32_t i = threadIdx.x; i < kBlockTile * (WIDTH / 4); i += blockDim.x) {
+            const uint32_t pos = i / (WIDTH / 4), quad = i % (WIDTH / 4);
+            if (pos < held) {
+                copy16_async(ks + pos * KROW + quad * 4, k + (uint64_t)(t0 + pos) * WIDTH + quad * 4);
+                copy16_async(vs + pos * WIDTH + quad * 4, v + (uint64_t)(t0 + pos) * WIDTH + quad * 4);
+            } else {   // past the last cursor of the block: nothing a weight of zero could turn into a NaN
+                *reinterpret_cast<float4 *>(ks + pos * KROW + quad * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                *reinterpret_cast<float4 *>(vs + pos * WIDTH + quad * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        // logits: a warp takes the queries warp, warp + 8, ...; a lane one position of the tile; four queries share
+        // each read of the key row
+        const float4 *kr = reinterpret_cast<const float4 *>(ks + lane * KROW);
+        for (uint32_t q0 = warp; q0 < queries; q0 += 32) {
+            float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float4 *qr[4];
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) qr[j] = reinterpret_cast<const float4 *>(qs + min(q0 + 8 * j, queries - 1) * WIDTH);
+#pragma unroll 4
+            for (uint32_t c = 0; c < WIDTH / 4; ++c) {
+                const float4 a = kr[c];
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    const float4 b = qr[j][c];
+                    dot[j] = fmaf(a.x, b.x, dot[j]);
+                    dot[j] = fmaf(a.y, b.y, dot[j]);
+                    dot[j] = fmaf(a.z, b.z, dot[j]);
+                    dot[j] = fmaf(a.w, b.w, dot[j]);
+                }
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t query = q0 + 8 * j;
+                if (query >= queries) break;   // (the same for every lane of the warp)
+                const uint32_t row = min(row0 + query / group, p.rows - 1);
+                const uint32_t count = min(p.position[row] + 1, p.capacity);
+                const float logit = t0 + lane < count ? dot[j] * p.scale : -INFINITY;
+                float top = logit;
+                for (int o = 16; o; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+                const float before = largest[query], after = fmaxf(before, top);
+                // (tile 0 holds position 0, which every row sees: `after` is finite from the first tile on)
+                const float weight = expf(logit - after);
+                float sum = weight;
+                for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                weights[query * kBlockTile + lane] = weight;
+                __syncwarp();
+                if (lane == 0) {
+                    const float factor = expf(before - after);
+                    shrink[query] = factor;
+                    sums[query] = fmaf(sums[query], factor, sum);
+                    largest[query] = after;
+                }
+            }
+        }
+        __syncthreads();
+        // weighted values: a lane holds PER channels of every query of its warp
+#pragma unroll
+        for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
+            const uint32_t query = warp + 8 * j;
+            if (query < queries) {
+                const float factor = shrink[query];
+#pragma unroll
+                for (uint32_t c = 0; c < PER; ++c) acc[j][c] *= factor;
+            }
+        }
+        for (uint32_t pos = 0; pos < kBlockTile; pos += 4) {
+            float value[4][PER];
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+                if constexpr (PER == 4) {
+                    const float4 a = *reinterpret_cast<const float4 *>(vs + (pos + i) * WIDTH + lane * 4);
+                    value[i][0] = a.x; value[i][1] = a.y; value[i][2] = a.z; value[i][3] = a.w;
+                } else {
+                    const float2 a = *reinterpret_cast<const float2 *>(vs + (pos + i) * WIDTH + lane * 2);
+                    value[i][0] = a.x; value[i][1] = a.y;
+                }
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
+                const uint32_t query = warp + 8 * j;
+                if (query < queries) {
+                    const float4 w4 = *reinterpret_cast<const float4 *>(weights + query * kBlockTile + pos);
+#pragma unroll
+                    for (uint32_t c = 0; c < PER; ++c) {
+                        acc[j][c] = fmaf(w4.x, value[0][c], acc[j][c]);
+                        acc[j][c] = fmaf(w4.y, value[1][c], acc[j][c]);
+                        acc[j][c] = fmaf(w4.z, value[2][c], acc[j][c]);
+                        acc[j][c] = fmaf(w4.w, value[3][c], acc[j][c]);
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();   // (a query's sum was last written by lane 0 of the warp that reads it here)
+#pragma unroll
+    for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
+        const uint32_t query = warp + 8 * j;
+        if (query >= queries) continue;
+        const uint32_t row = row0 + query / group, g = query % group;
+        if (row >= p.rows) continue;
+        const float total = sums[query];
+        float *to = p.out + (uint64_t)row * p.out_stride + (uint64_t)(kh * group + g) * WIDTH + lane * PER;
+#pragma unroll
+        for (uint32_t c = 0; c < PER; ++c) to[c] = acc[j][c] / total;
+    }
+}
+
 // rms_norm alone (crates/neura-decoder/src/op.rs:3-5 -> crates/neura-kernel/src/task/norm.rs:55-131, op = NORM_RMS)
 // for any number of rows: one CTA a row, y = x / sqrt(mean(x^2) + floor) * weight as f32.  The rows of a wide prompt
 // chunk take it on their way to the tensor-core product, which rounds them to bf16 itself.

@@ -1400,6 +1400,25 @@ int32_t neura_cuda_attend_rows(nc_context *ctx, void *stream, const float *q_dev
                                const float *values_dev, const uint32_t *position_dev, float scale, uint32_t rows,
                                uint32_t heads, uint32_t key_heads, uint32_t width, uint32_t capacity, float *out_dev,
                                uint64_t out_stride) {
+    // many rows (a wide prompt chunk): blocks of 16 rows share every tile of the cache they read
+    const bool lined_up = (uintptr_t)q_dev % 16 == 0 && q_stride % 4 == 0 && (uintptr_t)keys_dev % 16 == 0 && (uintptr_t)values_dev % 16 == 0;
+    if (ctx && q_dev && keys_dev && values_dev && position_dev && out_dev && rows >= kAttendBlockFrom && lined_up && key_heads &&
+        heads % key_heads == 0 && heads / key_heads <= kAttendMaxGroup && (width == 64 || width == 128) && capacity &&
+        q_stride >= (uint64_t)heads * width && out_stride >= (uint64_t)heads * width) {
+        const uint32_t group = heads / key_heads;
+        const size_t smem = attend_block_smem(width, group);
+        void (*kernel)(AttendBlockParams) = width == 128 ? attend_block_kernel<128> : attend_block_kernel<64>;
+        static size_t raised[64][2] = {{0}};
+        if (raised[ctx->device & 63][width == 128] < smem) {
+            NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            raised[ctx->device & 63][width == 128] = smem;
+        }
+        AttendBlockParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride, scale, rows, heads, key_heads, capacity};
+        NC_CUDA(launch_dependent(kernel, dim3((rows + kBlockRows - 1) / kBlockRows * key_heads), dim3(kBlockThreads), smem,
+                                 (cudaStream_t)stream, p));
+        ctx->launches++;
+        return 0;
+    }
     return attend_any(ctx, stream, q_dev, q_stride, keys_dev, values_dev, position_dev, scale, rows, heads, key_heads,
                       width, capacity, out_dev, out_stride, nullptr, nullptr, nullptr, 1);
 }

@@ -117,6 +117,29 @@ def test_attention_of_many_sequences_takes_the_small_tiles(runtime, oracle):
     assert np.abs(runtime.read(out) - expected.reshape(batch, -1)).max() <= 1e-5
 
 
+@pytest.mark.parametrize("rows,heads,key_heads,width,capacity,start", [
+    (64, 8, 2, 128, 96, 0), (100, 40, 8, 128, 200, 37), (511, 10, 2, 128, 640, 0), (77, 14, 2, 64, 130, 50), (130, 16, 2, 64, 140, 3)])
+def test_attention_of_a_wide_prompt_chunk_matches_the_oracle(runtime, oracle, rows, heads, key_heads, width, capacity, start):
+    # 64 rows and more of one sequence: blocks of 16 rows walk the cache tile by tile with a running softmax; row r sees the
+    # positions up to its own cursor start + r (the last block is ragged, the last tile of a block partly masked)
+    q = oracle.Stream(51).normal(rows * heads * width).reshape(rows, heads, width)
+    keys = oracle.Stream(52).normal(key_heads * capacity * width).reshape(1, key_heads, capacity, width)
+    values = oracle.Stream(53).normal(keys.size).reshape(keys.shape)
+    position = np.minimum(start + np.arange(rows, dtype=np.uint32), capacity - 1).astype(np.uint32)
+    expected = np.concatenate([oracle.attend(q[r: r + 1], keys, values, position[r: r + 1] + 1, 0.09) for r in range(rows)])
+    stride = heads * width + 2 * key_heads * width   # the queries sit at the head of q|k|v rows
+    rowsd = np.zeros((rows, stride), dtype=np.float32)
+    rowsd[:, : heads * width] = q.reshape(rows, -1)
+    qd, out = runtime.tensor(rows, stride), runtime.tensor(rows, heads * width)
+    kd, vd, pd = runtime.tensor(keys.size), runtime.tensor(values.size), runtime.tensor_u32(rows)
+    runtime.write(qd, rowsd)
+    runtime.write(kd, keys.reshape(-1))
+    runtime.write(vd, values.reshape(-1))
+    runtime.write(pd, position)
+    runtime.attend_rows(qd, kd.ptr, vd.ptr, pd, 0.09, rows, heads, key_heads, width, capacity, out)
+    assert np.abs(runtime.read(out) - expected.reshape(rows, -1)).max() <= 1e-5
+
+
 def test_argmax_takes_the_lowest_index_on_ties(runtime, oracle):
     x = oracle.Stream(12).normal(3 * 5000).reshape(3, 5000)
     x[0, 4000] = x[0, 17] = 9.0
