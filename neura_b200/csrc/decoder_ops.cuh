@@ -654,17 +654,24 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float *x, uint
     }
 }
 
-// The second half of a product with a sealed gate|up pair when the product itself ran as a plain one over the
-// pair's 32-row tiles (16 gate rows, then the 16 up rows of the same columns): out[r][c] = chain(silu(gate) * up).
-__global__ void swiglu_pair_kernel(const float *both, uint64_t both_stride, uint32_t rows, uint32_t n, float *out,
-                                   uint64_t out_stride, const __grid_constant__ Chain chain) {
+// What follows a tensor-core product that left its sums in scratch: `splits` runs of K (each [rows][both_stride], one
+// after another at `split_stride`) are added in order, and
+//   pair = 0: out[r][c] = chain(sum[r][c]);
+//   pair = 1: the product ran over a sealed gate|up pair's 32-row tiles (16 gate rows, then the 16 up rows of the same
+//             columns): out[r][c] = chain(silu(gate) * up).
+__global__ void gemm_finish_kernel(const float *both, uint64_t both_stride, uint64_t split_stride, uint32_t splits, uint32_t rows,
+                                   uint32_t n, uint32_t pair, float *out, uint64_t out_stride, const __grid_constant__ Chain chain) {
     const uint64_t total = (uint64_t)rows * n;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t r = i / n;
         const uint32_t c = (uint32_t)(i % n);
-        const float *at = both + r * both_stride + (uint64_t)(c / 16) * 32 + c % 16;
-        const float gate = at[0], other = at[16];
-        out[r * out_stride + c] = chained(chain, r, c, gate * sigmoid_f(gate) * other);
+        const float *at = both + r * both_stride + (pair ? (uint64_t)(c / 16) * 32 + c % 16 : (uint64_t)c);
+        float first = 0.0f, second = 0.0f;
+        for (uint32_t z = 0; z < splits; ++z) {
+            first += at[z * split_stride];
+            if (pair) second += at[z * split_stride + 16];
+        }
+        out[r * out_stride + c] = chained(chain, r, c, pair ? first * sigmoid_f(first) * second : first);
     }
 }
 

@@ -44,6 +44,9 @@ struct GemmParams {
     uint32_t units32;            // 32-row units along N the sealed weight holds
     unsigned int *status;
     Chain chain;
+    // gridDim.z CTAs share a tile, each taking a run of whole super-blocks of K; CTA z then writes its sums to
+    // out + z * split_stride (scratch: the launcher sums the runs in order afterwards and applies the chain there)
+    uint64_t split_stride;
 };
 
 // f32 -> bf16 with round-to-nearest-even (crates/neura-precision/src/lib.rs:325-329).
@@ -207,7 +210,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
     __shared__ uint32_t failed;
     const uint32_t tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     const uint32_t m0 = blockIdx.y * kGemmBM, n0 = blockIdx.x * kGemmBN;
-    const uint32_t ksteps = p.k / kGemmBK;
+    const uint32_t every_sb = p.k / kSuperBlock;
+    const uint32_t sb_first = (uint32_t)((uint64_t)every_sb * blockIdx.z / gridDim.z);
+    const uint32_t sb_last = (uint32_t)((uint64_t)every_sb * (blockIdx.z + 1) / gridDim.z);
+    const uint32_t step_first = sb_first * (kSuperBlock / kGemmBK), ksteps = sb_last * (kSuperBlock / kGemmBK);   // this CTA's k-steps: [step_first, ksteps)
+    float *const out = p.out + blockIdx.z * p.split_stride;
     constexpr uint32_t kMmaWarp = kGemmProducers / 32;
 
     if (tid == 0) {
@@ -235,13 +242,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
         // the quants travel three steps ahead of their use, the headers one super-block ahead, and the super-block
         // after the next is asked into L2 (a miss to HBM takes longer than a step); rows past the weight's end
         // re-read its last unit, and the epilogue does not store them
-        const uint32_t nsb = p.k / kSuperBlock;
+        const uint32_t nsb = sb_last;
         uint4 quants[4], headers[2], coming[2];
 #pragma unroll
         for (uint32_t j = 0; j < 3; ++j)
-            if (j < ksteps) quants[j] = fetch_quants(p, n0, j, warp, lane);
-        fetch_headers(headers, p, n0, 0, warp, lane);
-        for (uint32_t it0 = 0; it0 < ksteps && alive; it0 += 4) {
+            if (step_first + j < ksteps) quants[j] = fetch_quants(p, n0, step_first + j, warp, lane);
+        fetch_headers(headers, p, n0, sb_first, warp, lane);
+        for (uint32_t it0 = step_first; it0 < ksteps && alive; it0 += 4) {
             const uint32_t sb = it0 >> 2;
             if (sb + 1 < nsb) fetch_headers(coming, p, n0, sb + 1, warp, lane);
             if (lane == 0 && sb + 2 < nsb)
@@ -250,7 +257,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
             for (uint32_t j = 0; j < 4; ++j) {
                 const uint32_t it = it0 + j;
                 if (it >= ksteps || !alive) break;
-                const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
+                const uint32_t s = (it - step_first) % kGemmStages, parity = ((it - step_first) / kGemmStages) & 1u;
                 if (it + 3 < ksteps) quants[(j + 3) & 3] = fetch_quants(p, n0, it + 3, warp, lane);
                 if (!mbar_wait(empty + 8 * s, parity ^ 1u)) { alive = false; break; }
                 const uint32_t a_tile = base + s * kGemmStageBytes, b_tile = a_tile + kGemmABytes;
@@ -289,7 +296,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
                 const uint32_t col = n0 + c0 + lane;
                 if (col < p.n) {
                     const uint32_t first_row = m0 + which * 128 + lanes;
-                    float *to = p.out + (uint64_t)first_row * p.out_stride + col;
+                    float *to = out + (uint64_t)first_row * p.out_stride + col;
 #pragma unroll 8
                     for (uint32_t rr = 0; rr < 32; ++rr)
                         if (first_row + rr < p.m) __stcs(to + (uint64_t)rr * p.out_stride, turn[rr * 33 + lane]);
@@ -306,7 +313,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
         // MMA paid about 65 ns for moving them there, as much as the MMA itself takes.)
         const uint32_t idesc = instruction_descriptor(128, kGemmBN);
         bool alive = true;
-        for (uint32_t it = 0; it < ksteps; ++it) {
+        for (uint32_t it = 0; it < ksteps - step_first; ++it) {
             const uint32_t s = it % kGemmStages, parity = (it / kGemmStages) & 1u;
             if (!mbar_wait(full + 8 * s, parity)) { alive = false; break; }
             tc_fence_after();

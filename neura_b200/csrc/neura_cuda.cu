@@ -1114,7 +1114,12 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     if ((uintptr_t)x_dev % 4 || (uintptr_t)out_dev % 4) return refuse(kBadArgument, "f32 rows start on a 4-byte boundary");
     if ((rc = ensure(ctx, ctx->x_bf16, (uint64_t)rows * w->k * 2, false))) return rc;
     if ((rc = ensure(ctx, ctx->status, 256, true))) return rc;
-    if (pair && (rc = ensure(ctx, ctx->pair_out, (uint64_t)rows * n_all * sizeof(float), false))) return rc;
+    // few tiles (a chunk of a few hundred rows against a narrow weight) leave most SMs idle: runs of K then go to
+    // different CTAs, which leave their sums in scratch for gemm_finish_kernel to add in order
+    const uint32_t tiles = ((n_all + kGemmBN - 1) / kGemmBN) * ((rows + kGemmBM - 1) / kGemmBM);
+    const uint32_t splits = tiles * 2 <= (uint32_t)ctx->sms ? std::min({8u, (uint32_t)ctx->sms / tiles, w->k / kSuperBlock}) : 1u;
+    const bool scratch = pair || splits > 1;
+    if (scratch && (rc = ensure(ctx, ctx->pair_out, (uint64_t)splits * rows * n_all * sizeof(float), false))) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
     const uint64_t total = (uint64_t)rows * w->k;
     const uint64_t want = (total + 255) / 256;
@@ -1132,8 +1137,9 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     if ((rc = tensor_map_16bit(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ctx->x_bf16.ptr, w->k, rows, kGemmBM))) return rc;
     p.w = (const uint8_t *)w->data_dev;
     p.x = (const __nv_bfloat16 *)ctx->x_bf16.ptr;
-    p.out = pair ? (float *)ctx->pair_out.ptr : out_dev;
-    p.out_stride = pair ? n_all : out_stride;
+    p.out = scratch ? (float *)ctx->pair_out.ptr : out_dev;
+    p.out_stride = scratch ? n_all : out_stride;
+    p.split_stride = (uint64_t)rows * n_all;
     p.m = rows;
     p.n = n_all;
     p.k = w->k;
@@ -1143,14 +1149,15 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     memset(&steps, 0, sizeof steps);
     steps.n = n_steps;
     for (uint32_t s = 0; s < n_steps; ++s) steps.step[s] = chain[s];
-    if (!pair) p.chain = steps;
-    NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((n_all + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM),
+    if (!scratch) p.chain = steps;
+    NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((n_all + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM, splits),
                              dim3(kGemmThreads), kGemmSmem, stream, p));
     ctx->launches++;
-    if (pair) {
+    if (scratch) {
         const uint64_t cells = ((uint64_t)rows * w->n + 255) / 256;
         const unsigned int grid = (unsigned int)(cells < (uint64_t)ctx->sms * 16 ? cells : (uint64_t)ctx->sms * 16);
-        swiglu_pair_kernel<<<grid, 256, 0, stream>>>((const float *)ctx->pair_out.ptr, n_all, rows, w->n, out_dev, out_stride, steps);
+        gemm_finish_kernel<<<grid, 256, 0, stream>>>((const float *)ctx->pair_out.ptr, n_all, p.split_stride, splits, rows, w->n,
+                                                     pair ? 1u : 0u, out_dev, out_stride, steps);
         ctx->launches++;
         NC_CUDA(cudaGetLastError());
     }
