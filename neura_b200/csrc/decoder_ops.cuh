@@ -459,9 +459,10 @@ __global__ void advance_kernel(uint32_t *position, uint32_t rows, uint32_t by) {
 // tile); row r sees the positions up to its own cursor.  All f32, as the decode attention.
 constexpr uint32_t kBlockRows = 16;      // query rows a CTA
 constexpr uint32_t kBlockTile = 32;      // positions a tile: one a lane
-constexpr uint32_t kBlockThreads = 256;
+constexpr uint32_t kBlockThreads = 512;   // 16 warps: an SM holds one CTA, so the warps that hide each other's loads are its own
 constexpr uint32_t kAttendBlockFrom = 64;   // fewer rows than this keep the kernel of the decode step (a CTA a row)
-constexpr uint32_t kBlockQueriesPerWarp = kBlockRows * kAttendMaxGroup / (kBlockThreads / 32);   // 16
+constexpr uint32_t kBlockWarps = kBlockThreads / 32;
+constexpr uint32_t kBlockQueriesPerWarp = kBlockRows * kAttendMaxGroup / kBlockWarps;   // 8: query warp + 16 j for j < group
 
 struct AttendBlockParams {
     const float *q;               // [rows][q_stride], head h at h*width
@@ -480,7 +481,7 @@ inline size_t attend_block_smem(uint32_t width, uint32_t group) {
 }
 
 template <uint32_t WIDTH>
-__global__ void __launch_bounds__(kBlockThreads) attend_block_kernel(const __grid_constant__ AttendBlockParams p) {
+__global__ void __launch_bounds__(kBlockThreads, 1) attend_block_kernel(const __grid_constant__ AttendBlockParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(16) float shared[];
@@ -529,33 +530,34 @@ __global__ void __launch_bounds__(kBlockThreads) attend_block_kernel(const __gri
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        // logits: a warp takes the queries warp, warp + 8, ...; a lane one position of the tile; four queries share
-        // each read of the key row
-        const float4 *kr = reinterpret_cast<const float4 *>(ks + lane * KROW);
-        for (uint32_t q0 = warp; q0 < queries; q0 += 32) {
-            float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const float4 *qr[4];
+        // logits: a warp takes the queries warp, warp + 16, ... (one a query head of the group); a lane one position of
+        // the tile; all the warp's queries share each read of the key row
+        {
+            const float4 *kr = reinterpret_cast<const float4 *>(ks + lane * KROW);
+            float dot[kBlockQueriesPerWarp][2];
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) qr[j] = reinterpret_cast<const float4 *>(qs + min(q0 + 8 * j, queries - 1) * WIDTH);
+            for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) dot[j][0] = dot[j][1] = 0.0f;
 #pragma unroll 4
             for (uint32_t c = 0; c < WIDTH / 4; ++c) {
                 const float4 a = kr[c];
 #pragma unroll
-                for (uint32_t j = 0; j < 4; ++j) {
-                    const float4 b = qr[j][c];
-                    dot[j] = fmaf(a.x, b.x, dot[j]);
-                    dot[j] = fmaf(a.y, b.y, dot[j]);
-                    dot[j] = fmaf(a.z, b.z, dot[j]);
-                    dot[j] = fmaf(a.w, b.w, dot[j]);
+                for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
+                    if (j < group) {   // (the same for every thread of the CTA)
+                        const float4 b = reinterpret_cast<const float4 *>(qs + (warp + kBlockWarps * j) * WIDTH)[c];
+                        dot[j][0] = fmaf(a.x, b.x, dot[j][0]);
+                        dot[j][1] = fmaf(a.y, b.y, dot[j][1]);
+                        dot[j][0] = fmaf(a.z, b.z, dot[j][0]);
+                        dot[j][1] = fmaf(a.w, b.w, dot[j][1]);
+                    }
                 }
             }
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-                const uint32_t query = q0 + 8 * j;
-                if (query >= queries) break;   // (the same for every lane of the warp)
+            for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
+                if (j >= group) break;
+                const uint32_t query = warp + kBlockWarps * j;
                 const uint32_t row = min(row0 + query / group, p.rows - 1);
                 const uint32_t count = min(p.position[row] + 1, p.capacity);
-                const float logit = t0 + lane < count ? dot[j] * p.scale : -INFINITY;
+                const float logit = t0 + lane < count ? (dot[j][0] + dot[j][1]) * p.scale : -INFINITY;
                 float top = logit;
                 for (int o = 16; o; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
                 const float before = largest[query], after = fmaxf(before, top);
@@ -564,7 +566,6 @@ __global__ void __launch_bounds__(kBlockThreads) attend_block_kernel(const __gri
                 float sum = weight;
                 for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
                 weights[query * kBlockTile + lane] = weight;
-                __syncwarp();
                 if (lane == 0) {
                     const float factor = expf(before - after);
                     shrink[query] = factor;
@@ -577,8 +578,8 @@ __global__ void __launch_bounds__(kBlockThreads) attend_block_kernel(const __gri
         // weighted values: a lane holds PER channels of every query of its warp
 #pragma unroll
         for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
-            const uint32_t query = warp + 8 * j;
-            if (query < queries) {
+            const uint32_t query = warp + kBlockWarps * j;
+            if (j < group) {
                 const float factor = shrink[query];
 #pragma unroll
                 for (uint32_t c = 0; c < PER; ++c) acc[j][c] *= factor;
@@ -598,8 +599,8 @@ __global__ void __launch_bounds__(kBlockThreads) attend_block_kernel(const __gri
             }
 #pragma unroll
             for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
-                const uint32_t query = warp + 8 * j;
-                if (query < queries) {
+                const uint32_t query = warp + kBlockWarps * j;
+                if (j < group) {
                     const float4 w4 = *reinterpret_cast<const float4 *>(weights + query * kBlockTile + pos);
 #pragma unroll
                     for (uint32_t c = 0; c < PER; ++c) {
@@ -615,8 +616,8 @@ __global__ void __launch_bounds__(kBlockThreads) attend_block_kernel(const __gri
     __syncwarp();   // (a query's sum was last written by lane 0 of the warp that reads it here)
 #pragma unroll
     for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
-        const uint32_t query = warp + 8 * j;
-        if (query >= queries) continue;
+        const uint32_t query = warp + kBlockWarps * j;
+        if (j >= group) continue;
         const uint32_t row = row0 + query / group, g = query % group;
         if (row >= p.rows) continue;
         const float total = sums[query];
