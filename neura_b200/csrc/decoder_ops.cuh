@@ -462,7 +462,7 @@ constexpr uint32_t kBlockTile = 32;      // positions a tile: one a lane
 constexpr uint32_t kBlockThreads = 512;   // 16 warps: an SM holds one CTA, so the warps that hide each other's loads are its own
 constexpr uint32_t kAttendBlockFrom = 64;   // fewer rows than this keep the kernel of the decode step (a CTA a row)
 constexpr uint32_t kBlockWarps = kBlockThreads / 32;
-constexpr uint32_t kBlockQueriesPerWarp = kBlockRows * kAttendMaxGroup / kBlockWarps;   // 8: query warp + 16 j for j < group
+static_assert(kBlockRows == kBlockWarps, "warp w holds the queries w + 16 j, one a query head of the group");
 
 struct AttendBlockParams {
     const float *q;               // [rows][q_stride], head h at h*width
@@ -480,14 +480,16 @@ inline size_t attend_block_smem(uint32_t width, uint32_t group) {
     return (queries * width + (size_t)kBlockTile * (width + 4) + (size_t)kBlockTile * width + queries * kBlockTile + queries * 3) * sizeof(float);
 }
 
-template <uint32_t WIDTH>
+// GROUP (query heads a key head) is a template parameter: with a run-time bound the unrolled loops over a warp's queries were
+// predicated, and a group of 5 issued the instructions of 8.
+template <uint32_t WIDTH, uint32_t GROUP>
 __global__ void __launch_bounds__(kBlockThreads, 1) attend_block_kernel(const __grid_constant__ AttendBlockParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(16) float shared[];
     constexpr uint32_t KROW = WIDTH + 4;      // padded key row: float4 reads of 8 rows hit 32 banks
     constexpr uint32_t PER = WIDTH / 32;      // output channels a lane
-    const uint32_t group = p.heads / p.key_heads, queries = kBlockRows * group;
+    constexpr uint32_t group = GROUP, queries = kBlockRows * GROUP;
     float *qs = shared;                                   // [queries][WIDTH], query r*group + g
     float *ks = qs + queries * WIDTH;                     // [32][KROW]
     float *vs = ks + kBlockTile * KROW;                   // [32][WIDTH]
@@ -508,9 +510,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1) attend_block_kernel(const __
         reinterpret_cast<float4 *>(qs)[i] = *reinterpret_cast<const float4 *>(p.q + (uint64_t)row * p.q_stride + (uint64_t)(kh * group + g) * WIDTH + quad * 4);
     }
     for (uint32_t i = threadIdx.x; i < queries; i += blockDim.x) { largest[i] = -INFINITY; sums[i] = 0.0f; }
-    float acc[kBlockQueriesPerWarp][PER];
+    float acc[GROUP][PER];
 #pragma unroll
-    for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j)
+    for (uint32_t j = 0; j < GROUP; ++j)
 #pragma unroll
         for (uint32_t c = 0; c < PER; ++c) acc[j][c] = 0.0f;
     const float *k = p.keys + (uint64_t)kh * p.capacity * WIDTH, *v = p.values + (uint64_t)kh * p.capacity * WIDTH;
@@ -534,26 +536,23 @@ __global__ void __launch_bounds__(kBlockThreads, 1) attend_block_kernel(const __
         // the tile; all the warp's queries share each read of the key row
         {
             const float4 *kr = reinterpret_cast<const float4 *>(ks + lane * KROW);
-            float dot[kBlockQueriesPerWarp][2];
+            float dot[GROUP][2];
 #pragma unroll
-            for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) dot[j][0] = dot[j][1] = 0.0f;
+            for (uint32_t j = 0; j < GROUP; ++j) dot[j][0] = dot[j][1] = 0.0f;
 #pragma unroll 4
             for (uint32_t c = 0; c < WIDTH / 4; ++c) {
                 const float4 a = kr[c];
 #pragma unroll
-                for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
-                    if (j < group) {   // (the same for every thread of the CTA)
-                        const float4 b = reinterpret_cast<const float4 *>(qs + (warp + kBlockWarps * j) * WIDTH)[c];
-                        dot[j][0] = fmaf(a.x, b.x, dot[j][0]);
-                        dot[j][1] = fmaf(a.y, b.y, dot[j][1]);
-                        dot[j][0] = fmaf(a.z, b.z, dot[j][0]);
-                        dot[j][1] = fmaf(a.w, b.w, dot[j][1]);
-                    }
+                for (uint32_t j = 0; j < GROUP; ++j) {
+                    const float4 b = reinterpret_cast<const float4 *>(qs + (warp + kBlockWarps * j) * WIDTH)[c];
+                    dot[j][0] = fmaf(a.x, b.x, dot[j][0]);
+                    dot[j][1] = fmaf(a.y, b.y, dot[j][1]);
+                    dot[j][0] = fmaf(a.z, b.z, dot[j][0]);
+                    dot[j][1] = fmaf(a.w, b.w, dot[j][1]);
                 }
             }
 #pragma unroll
-            for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
-                if (j >= group) break;
+            for (uint32_t j = 0; j < GROUP; ++j) {
                 const uint32_t query = warp + kBlockWarps * j;
                 const uint32_t row = min(row0 + query / group, p.rows - 1);
                 const uint32_t count = min(p.position[row] + 1, p.capacity);
@@ -577,13 +576,10 @@ __global__ void __launch_bounds__(kBlockThreads, 1) attend_block_kernel(const __
         __syncthreads();
         // weighted values: a lane holds PER channels of every query of its warp
 #pragma unroll
-        for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
-            const uint32_t query = warp + kBlockWarps * j;
-            if (j < group) {
-                const float factor = shrink[query];
+        for (uint32_t j = 0; j < GROUP; ++j) {
+            const float factor = shrink[warp + kBlockWarps * j];
 #pragma unroll
-                for (uint32_t c = 0; c < PER; ++c) acc[j][c] *= factor;
-            }
+            for (uint32_t c = 0; c < PER; ++c) acc[j][c] *= factor;
         }
         for (uint32_t pos = 0; pos < kBlockTile; pos += 4) {
             float value[4][PER];
@@ -598,26 +594,22 @@ __global__ void __launch_bounds__(kBlockThreads, 1) attend_block_kernel(const __
                 }
             }
 #pragma unroll
-            for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
-                const uint32_t query = warp + kBlockWarps * j;
-                if (j < group) {
-                    const float4 w4 = *reinterpret_cast<const float4 *>(weights + query * kBlockTile + pos);
+            for (uint32_t j = 0; j < GROUP; ++j) {
+                const float4 w4 = *reinterpret_cast<const float4 *>(weights + (warp + kBlockWarps * j) * kBlockTile + pos);
 #pragma unroll
-                    for (uint32_t c = 0; c < PER; ++c) {
-                        acc[j][c] = fmaf(w4.x, value[0][c], acc[j][c]);
-                        acc[j][c] = fmaf(w4.y, value[1][c], acc[j][c]);
-                        acc[j][c] = fmaf(w4.z, value[2][c], acc[j][c]);
-                        acc[j][c] = fmaf(w4.w, value[3][c], acc[j][c]);
-                    }
+                for (uint32_t c = 0; c < PER; ++c) {
+                    acc[j][c] = fmaf(w4.x, value[0][c], acc[j][c]);
+                    acc[j][c] = fmaf(w4.y, value[1][c], acc[j][c]);
+                    acc[j][c] = fmaf(w4.z, value[2][c], acc[j][c]);
+                    acc[j][c] = fmaf(w4.w, value[3][c], acc[j][c]);
                 }
             }
         }
     }
     __syncwarp();   // (a query's sum was last written by lane 0 of the warp that reads it here)
 #pragma unroll
-    for (uint32_t j = 0; j < kBlockQueriesPerWarp; ++j) {
+    for (uint32_t j = 0; j < GROUP; ++j) {
         const uint32_t query = warp + kBlockWarps * j;
-        if (j >= group) continue;
         const uint32_t row = row0 + query / group, g = query % group;
         if (row >= p.rows) continue;
         const float total = sums[query];

@@ -1414,11 +1414,16 @@ int32_t neura_cuda_attend_rows(nc_context *ctx, void *stream, const float *q_dev
         q_stride >= (uint64_t)heads * width && out_stride >= (uint64_t)heads * width) {
         const uint32_t group = heads / key_heads;
         const size_t smem = attend_block_smem(width, group);
-        void (*kernel)(AttendBlockParams) = width == 128 ? attend_block_kernel<128> : attend_block_kernel<64>;
-        static size_t raised[64][2] = {{0}};
-        if (raised[ctx->device & 63][width == 128] < smem) {
+        void (*kernel)(AttendBlockParams) = nullptr;
+        switch ((width == 128 ? 8 : 0) + group - 1) {
+#define NC_BLOCK_CASE(G) case G - 1: kernel = attend_block_kernel<64, G>; break; case 8 + G - 1: kernel = attend_block_kernel<128, G>; break;
+            NC_BLOCK_CASE(1) NC_BLOCK_CASE(2) NC_BLOCK_CASE(3) NC_BLOCK_CASE(4) NC_BLOCK_CASE(5) NC_BLOCK_CASE(6) NC_BLOCK_CASE(7) NC_BLOCK_CASE(8)
+#undef NC_BLOCK_CASE
+        }
+        static bool raised[64][16] = {{false}};
+        if (!raised[ctx->device & 63][(width == 128 ? 8 : 0) + group - 1]) {
             NC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            raised[ctx->device & 63][width == 128] = smem;
+            raised[ctx->device & 63][(width == 128 ? 8 : 0) + group - 1] = true;
         }
         AttendBlockParams p{q_dev, q_stride, keys_dev, values_dev, position_dev, out_dev, out_stride, scale, rows, heads, key_heads, capacity};
         NC_CUDA(launch_dependent(kernel, dim3((rows + kBlockRows - 1) / kBlockRows * key_heads), dim3(kBlockThreads), smem,
