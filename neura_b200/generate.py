@@ -175,6 +175,14 @@ class Batch:
         for slot, held in enumerate(self.slots):
             if held is None or held.phase != PROMPTING:
                 continue
+            # (a stepper built for it takes the head of a long prompt in wide chunks through the tensor-core product)
+            wide = int(getattr(self.stepper, "wide", 0) or 0)
+            through = self.stepper.wide_tokens(len(held.prompt)) if wide and hasattr(self.stepper, "fill_wide") else 0
+            while through > 0:
+                size = min(wide, through)
+                self.stepper.fill_wide(slot, [held.prompt.popleft() for _ in range(size)], held.cursor)
+                held.cursor += size
+                through -= size
             while True:
                 size = next((c for c in chunks if c <= len(held.prompt) - 1), None)
                 if size is None:

@@ -83,6 +83,23 @@ class OracleDecoder:
         return self.step(np.ascontiguousarray(tokens, dtype=np.uint32))
 
     chunks = (4, 2)   # the chunk sizes ``fill`` offers a ``generate.Batch`` (small, for the bookkeeping tests)
+    wide = 0          # rows of a tensor-path chunk (``fill_wide``); 0: the stepper offers none
+    WIDE_FROM = 64    # fewer prompt tokens than this go through the ordinary chunks
+
+    def wide_tokens(self, length: int) -> int:
+        """How many leading tokens of a prompt of ``length`` go through ``fill_wide`` (the rule of ``qwen.Decoder``)."""
+        fed = length - 1
+        if not self.wide or fed < self.WIDE_FROM:
+            return 0
+        return fed - (fed % self.wide if fed % self.wide < self.WIDE_FROM else 0)
+
+    def fill_wide(self, sequence: int, tokens, start: int) -> None:
+        """A prompt chunk through the tensor path: ``fill`` with both operands of every product rounded to bf16."""
+        self.bf16 = True
+        try:
+            self.fill(sequence, tokens, start)
+        finally:
+            self.bf16 = False
 
     def fill(self, sequence: int, tokens, start: int) -> None:
         """A prompt chunk of one plane: the same cache rows the decode step writes token by token (the other

@@ -129,3 +129,26 @@ def test_ragged_admissions_decode_what_a_batch_of_one_decodes():
         if not list(batch.occupied()):
             break
     assert [got[i][:6] for i in range(3)] == alone
+
+
+def test_a_stepper_with_a_wide_path_takes_the_head_of_a_long_prompt_through_it():
+    # Batch::prefill with a stepper that offers the tensor path: 13 prompt tokens, wide chunks of 8 from 5 tokens up:
+    # 12 are fed, 8 in one wide chunk (bf16 operands), the other 4 as a chunk of 4; the last goes through the step
+    packed, norms = synthetic_model(CONFIG, seed=11)
+    prompt = [3, 9, 27, 81, 5, 7, 49, 11, 2, 4, 8, 16, 32]
+    alone = OracleDecoder(CONFIG, packed, norms, batch=1, capacity=24, threads=2)
+    want, _ = alone.generate(np.array([prompt]), 6, bf16_tokens=8)
+    stepper = OracleDecoder(CONFIG, packed, norms, batch=2, capacity=24, threads=2)
+    stepper.wide, stepper.WIDE_FROM = 8, 5
+    assert stepper.wide_tokens(len(prompt)) == 8
+    calls = []
+    fill_wide, fill = stepper.fill_wide, stepper.fill
+    stepper.fill_wide = lambda slot, tokens, start: (calls.append(("wide", len(tokens), start)), fill_wide(slot, tokens, start))[1]
+    stepper.fill = lambda slot, tokens, start: (calls.append(("fill", len(tokens), start, stepper.bf16)), fill(slot, tokens, start))[1]
+    batch = Batch(stepper)
+    slot = batch.admit(prompt)
+    got = []
+    for _ in range(8):
+        got += [token for s, token in batch.step() if s == slot]
+    assert calls == [("wide", 8, 0), ("fill", 8, 0, True), ("fill", 4, 8, False)]
+    assert got[:6] == [int(t) for t in want[0]]

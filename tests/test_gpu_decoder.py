@@ -254,15 +254,15 @@ def test_a_prompt_fed_through_the_tensor_cores_decodes_what_the_oracle_decodes(o
     rt.use_stream(rt.new_stream())
     try:
         weights, dnorms = load_model(rt, config, packed, norms)
-        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=length + 40, wide=wide)
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=batch, capacity=length + 72, wide=wide)
         through = decoder.wide_tokens(length)
         decoder.record()
-        got = decoder.generate(prompts, 32, chunked=True)
-        again = decoder.generate(prompts, 32, chunked=True)
+        got = decoder.generate(prompts, 64, chunked=True)
+        again = decoder.generate(prompts, 64, chunked=True)
     finally:
         rt.close()
     assert through == {200: 199, 150: 128, 330: 329}[length]
-    want, margins = OracleDecoder(config, packed, norms, batch=batch, capacity=length + 40).generate(prompts, 32, bf16_tokens=through)
+    want, margins = OracleDecoder(config, packed, norms, batch=batch, capacity=length + 72).generate(prompts, 64, bf16_tokens=through)
     assert np.array_equal(got, again), "the same prompt fills the cache the same way twice"
     differs = np.argwhere(got != want)
     if differs.size:
@@ -331,6 +331,40 @@ def test_continuous_batching_decodes_each_sequence_as_the_oracle_decodes_it_alon
     finally:
         rt.close()
     assert [got[i][:steps] for i in range(len(prompts))] == alone
+
+
+def test_continuous_batching_feeds_a_long_prompt_through_the_tensor_cores(oracle):
+    # Batch::prefill over a decoder built with wide rows: the long prompt's head goes through fill_wide (100 of its 120
+    # tokens in one chunk; the 19 left in chunks of 8 and alone), the short prompt through the f32 chunks only
+    from neura_b200.generate import Batch
+    from oracle.decoder import OracleDecoder, synthetic_model
+
+    config = SMALL["q4_k"]
+    packed, norms = synthetic_model(config, seed=23)
+    draws = (oracle.Stream(39).uniform(160, 0.0, 1.0) * config.vocab).astype(np.uint32)
+    prompts = [list(draws[:120]), list(draws[120:160])]
+    steps = 16
+    rt = nb.Runtime(0)
+    rt.use_stream(rt.new_stream())
+    try:
+        weights, dnorms = load_model(rt, config, packed, norms)
+        decoder = qwen.Decoder(rt, config, weights, dnorms, batch=2, capacity=160, wide=100)
+        through = [decoder.wide_tokens(len(p)) for p in prompts]
+        decoder.record()
+        batch = Batch(decoder)
+        plane = {batch.admit(p): i for i, p in enumerate(prompts)}
+        got = {0: [], 1: []}
+        for _ in range(60):
+            for slot, token in batch.step():
+                got[plane[slot]].append(token)
+            if min(len(tokens) for tokens in got.values()) >= steps:
+                break
+    finally:
+        rt.close()
+    assert through == [100, 0]
+    alone = [OracleDecoder(config, packed, norms, batch=1, capacity=160).generate(np.array([p]), steps, bf16_tokens=t)[0][0].tolist()
+             for p, t in zip(prompts, through)]
+    assert [got[i][:steps] for i in range(2)] == alone
 
 
 def test_the_whole_half_billion_decoder_decodes_the_golden_tokens(oracle):
