@@ -477,9 +477,17 @@ class Decoder:
         return kinds, nanos
 
     def release(self) -> None:
+        """Gives back what the decoder recorded or compiled (the step's program, the prompt chunks' programs, the
+        persistent step); the decoder steps eagerly afterwards."""
         if self.compiled is not None:
             self.rt._lib.neura_cuda_decoder_free(self.rt._ctx, self.compiled)
             self.compiled = None
+        self.rt.sync()   # (a program may still be running)
+        for program in [self.program, *self._fill_programs.values()]:
+            if isinstance(program, int):
+                self.rt.program_free(program)
+        self.program = None
+        self._fill_programs = {}
 
     def launches_per_token(self) -> int:
         if self.compiled is not None:

@@ -214,6 +214,8 @@ def test_a_prompt_fed_in_chunks_decodes_what_the_oracle_decodes(oracle, name, ba
         stepped, launches = rt.launches - launches, rt.launches
         chunked = decoder.generate(prompts, 32, chunked=True)
         fed = rt.launches - launches
+        decoder.release()   # the step's and the chunks' programs go back; the decoder steps eagerly from here on
+        assert decoder.program is None and np.array_equal(decoder.generate(prompts, 4, chunked=True), chunked[:, :4])
     finally:
         rt.close()
     assert fed < stepped, "the chunks take fewer launches than the tokens one by one"
