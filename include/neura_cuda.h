@@ -190,8 +190,8 @@ int32_t neura_cuda_linear(nc_context *ctx, void *stream, const nc_weight *w, con
  *   out[r*out_stride + c] = chain(sum_k bf16(W[c][k]) * bf16(x[r*x_stride + k]))
  * Needs a sealed Q4K weight; any number of rows.  A sealed gate|up pair (NC_LAYOUT_TILED_PAIR) gives
  *   out[r*out_stride + c] = chain(silu(gate_c . x_r) * (up_c . x_r))
- * as neura_cuda_linear does: the product runs over both halves into scratch of the context and a second kernel
- * joins them. */
+ * as neura_cuda_linear does (the epilogue joins the halves; a product of few tiles splits K over CTAs and leaves
+ * the joining, like the chain, to a second kernel over scratch of the context). */
 int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream, const nc_weight *w, const float *x_dev, uint32_t rows,
                                uint64_t x_stride, float *out_dev, uint64_t out_stride, const nc_step *chain,
                                uint32_t n_steps);

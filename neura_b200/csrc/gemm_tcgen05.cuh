@@ -47,6 +47,9 @@ struct GemmParams {
     // gridDim.z CTAs share a tile, each taking a run of whole super-blocks of K; CTA z then writes its sums to
     // out + z * split_stride (scratch: the launcher sums the runs in order afterwards and applies the chain there)
     uint64_t split_stride;
+    // pair = 1: the weight is a sealed gate|up pair (every 32-row unit holds 16 gate rows, then the 16 up rows of the
+    // same columns) and the epilogue writes out[r][16 u + i] = chain(silu(gate) * up) for unit u: n_out columns in all
+    uint32_t pair, n_out;
 };
 
 // f32 -> bf16 with round-to-nearest-even (crates/neura-precision/src/lib.rs:325-329).
@@ -289,6 +292,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
                 // rows (32 sectors), and those stores held the whole kernel back (without them it runs twice as
                 // fast).  So the warp turns its 32 x 32 block through shared memory (the ring is idle by now) and
                 // every store instruction writes 128 contiguous bytes of one row.
+                if (p.pair) {
+                    // a lane holds one unit of one row: its gate sums in r[0..15], its up sums in r[16..31]
+                    const uint32_t first_col = (n0 + c0) / 2;
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const float gate = __uint_as_float(r[i]), other = __uint_as_float(r[16 + i]);
+                        turn[lane * 33 + i] = (row < p.m && first_col + i < p.n_out) ? chained(p.chain, row, first_col + i, gate * sigmoid_f(gate) * other) : 0.0f;
+                    }
+                    __syncwarp();
+                    const uint32_t col = first_col + (lane & 15);
+                    if (col < p.n_out) {   // the two halves of the warp take the even and the odd rows: 64 contiguous bytes each
+                        const uint32_t first_row = m0 + which * 128 + lanes;
+                        float *to = out + (uint64_t)first_row * p.out_stride + col;
+#pragma unroll 8
+                        for (uint32_t rr = lane >> 4; rr < 32; rr += 2)
+                            if (first_row + rr < p.m) __stcs(to + (uint64_t)rr * p.out_stride, turn[rr * 33 + (lane & 15)]);
+                    }
+                    __syncwarp();
+                    continue;
+                }
 #pragma unroll
                 for (uint32_t i = 0; i < 32; ++i)
                     turn[lane * 33 + i] = (row < p.m && n0 + c0 + i < p.n) ? chained(p.chain, row, n0 + c0 + i, __uint_as_float(r[i])) : 0.0f;

@@ -1118,7 +1118,7 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     // different CTAs, which leave their sums in scratch for gemm_finish_kernel to add in order
     const uint32_t tiles = ((n_all + kGemmBN - 1) / kGemmBN) * ((rows + kGemmBM - 1) / kGemmBM);
     const uint32_t splits = tiles * 2 <= (uint32_t)ctx->sms ? std::min({8u, (uint32_t)ctx->sms / tiles, w->k / kSuperBlock}) : 1u;
-    const bool scratch = pair || splits > 1;
+    const bool scratch = splits > 1;   // (an unsplit pair is joined in the product's own epilogue)
     if (scratch && (rc = ensure(ctx, ctx->pair_out, (uint64_t)splits * rows * n_all * sizeof(float), false))) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
     const uint64_t total = (uint64_t)rows * w->k;
@@ -1150,6 +1150,10 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     steps.n = n_steps;
     for (uint32_t s = 0; s < n_steps; ++s) steps.step[s] = chain[s];
     if (!scratch) p.chain = steps;
+    if (pair && !scratch) {
+        p.pair = 1;
+        p.n_out = w->n;
+    }
     NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((n_all + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM, splits),
                              dim3(kGemmThreads), kGemmSmem, stream, p));
     ctx->launches++;

@@ -72,9 +72,12 @@ def test_prefill_product_at_the_benchmark_rows_on_a_slice_of_its_width(runtime, 
     check(runtime, oracle, 2048, 256, 3584)
 
 
-@pytest.mark.parametrize("m,n,k,residual", [(96, 320, 512, False), (300, 300, 768, True), (1, 16, 256, False)])
+@pytest.mark.parametrize("m,n,k,residual", [(96, 320, 512, False), (300, 300, 768, True), (1, 16, 256, False),
+                                            (300, 4872, 256, True), (520, 4864, 512, False)])
 def test_prefill_product_of_a_sealed_gate_up_pair(runtime, oracle, m, n, k, residual):
-    # the pair's tiles hold 16 gate rows and the 16 up rows of the same columns: out = chain(silu(gate . x) * (up . x))
+    # the pair's tiles hold 16 gate rows and the 16 up rows of the same columns: out = chain(silu(gate . x) * (up . x)).
+    # Few tiles: runs of K in scratch, joined by the finishing kernel; many tiles (the last two cases, 78 and 114 tiles,
+    # a ragged last unit in the first): joined in the product's own epilogue
     gate = oracle.Stream(71).normal(n * k, 0.0, 0.02).reshape(n, k)
     up = oracle.Stream(73).normal(n * k, 0.0, 0.02).reshape(n, k)
     packed_gate, packed_up = oracle.pack_rows(nb.Q4K, gate), oracle.pack_rows(nb.Q4K, up)
