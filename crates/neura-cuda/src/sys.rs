@@ -128,6 +128,7 @@ extern "C" {
     pub fn neura_cuda_set_wait_limit(ctx: *mut NcContext, nanoseconds: u64) -> i32;
     pub fn neura_cuda_reserve(ctx: *mut NcContext, rows: u32, n: u32, k: u32) -> i32;
     pub fn neura_cuda_reserve_decoder(ctx: *mut NcContext, rows: u32, heads: u32, key_heads: u32, width: u32, capacity: u32) -> i32;
+    pub fn neura_cuda_reserve_bf16(ctx: *mut NcContext, rows: u32, k: u32) -> i32;
     pub fn neura_cuda_weight_seal(ctx: *mut NcContext, stream: *mut c_void, element: u32, n: u32, k: u32, gguf_dev: *const c_void, dst_dev: *mut c_void) -> i32;
     pub fn neura_cuda_sealed_pair_bytes(element: u32, n: u32, k: u32) -> u64;
     pub fn neura_cuda_weight_seal_pair(ctx: *mut NcContext, stream: *mut c_void, element: u32, n: u32, k: u32, gate_gguf_dev: *const c_void, up_gguf_dev: *const c_void, dst_dev: *mut c_void) -> i32;

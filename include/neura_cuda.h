@@ -137,6 +137,10 @@ int32_t neura_cuda_set_wait_limit(nc_context *ctx, uint64_t nanoseconds);
  * `rows` activation rows against matrices of up to [n, k] never allocate. */
 int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t k);
 
+/* The same for neura_cuda_linear_bf16: the bf16 copy of up to `rows` rows of `k` activations and the scratch its
+ * split products share, so that a program recorded around such products never sees them move. */
+int32_t neura_cuda_reserve_bf16(nc_context *ctx, uint32_t rows, uint32_t k);
+
 /* The same for the decoder's other scratch: the partial results of an attention over a cache of
  * `capacity` rows and the candidates of an argmax over `rows` rows, so that a decode step can be
  * recorded without having run eagerly first.  (The reference sizes these at plan time,

@@ -24,7 +24,7 @@ SYMBOLS = [
     "neura_cuda_decoder_compile", "neura_cuda_decoder_step", "neura_cuda_decoder_free", "neura_cuda_decoder_trace", "neura_cuda_rope_attend", "neura_cuda_rope_table", "neura_cuda_allreduce_norm_stage", "neura_cuda_staging_select",
     "neura_cuda_linear_staged_then", "neura_cuda_set_wait_limit", "neura_cuda_memory", "neura_cuda_comm_connect_local",
     "neura_cuda_linear_staged_fused", "neura_cuda_rope_cache_rows", "neura_cuda_attend_rows",
-    "neura_cuda_decoder_compile_rank", "neura_cuda_rms_norm",
+    "neura_cuda_decoder_compile_rank", "neura_cuda_rms_norm", "neura_cuda_reserve_bf16",
 ]
 
 
@@ -106,6 +106,7 @@ def load() -> ctypes.CDLL:
         "neura_cuda_sync": (i32, [p, p]),
         "neura_cuda_reserve": (i32, [p, u32, u32, u32]),
         "neura_cuda_reserve_decoder": (i32, [p, u32, u32, u32, u32, u32]),
+        "neura_cuda_reserve_bf16": (i32, [p, u32, u32]),
         "neura_cuda_decoder_compile": (i32, [p, ctypes.POINTER(NcDecoderDesc), pp]),
         "neura_cuda_decoder_compile_rank": (i32, [p, ctypes.POINTER(NcDecoderDesc), p, u32, u32, pp]),
         "neura_cuda_decoder_step": (i32, [p, p, p]),

@@ -740,6 +740,15 @@ int32_t neura_cuda_reserve(nc_context *ctx, uint32_t rows, uint32_t n, uint32_t 
     return 0;
 }
 
+int32_t neura_cuda_reserve_bf16(nc_context *ctx, uint32_t rows, uint32_t k) {
+    if (!ctx || !rows || !k) return refuse(kBadArgument, "reserve needs a context and a shape");
+    NC_CUDA(cudaSetDevice(ctx->device));
+    int32_t rc;
+    if ((rc = ensure(ctx, ctx->x_bf16, (uint64_t)rows * k * 2, false))) return rc;
+    if ((rc = ensure(ctx, ctx->pair_out, (uint64_t)ctx->sms * kGemmBM * kGemmBN * sizeof(float), false))) return rc;
+    return ensure(ctx, ctx->status, 256, true);
+}
+
 int32_t neura_cuda_reserve_decoder(nc_context *ctx, uint32_t rows, uint32_t heads, uint32_t key_heads, uint32_t width,
                                    uint32_t capacity) {
     if (!ctx || !rows || !heads || !key_heads || !width || !capacity)
@@ -1119,7 +1128,9 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     const uint32_t tiles = ((n_all + kGemmBN - 1) / kGemmBN) * ((rows + kGemmBM - 1) / kGemmBM);
     const uint32_t splits = tiles * 2 <= (uint32_t)ctx->sms ? std::min({8u, (uint32_t)ctx->sms / tiles, w->k / kSuperBlock}) : 1u;
     const bool scratch = splits > 1;   // (an unsplit pair is joined in the product's own epilogue)
-    if (scratch && (rc = ensure(ctx, ctx->pair_out, (uint64_t)splits * rows * n_all * sizeof(float), false))) return rc;
+    // (splits <= SMs / tiles and a tile covers at most 256 x 256 outputs, so the runs of any product fit the bound below:
+    // sized once, the scratch never moves under a recorded program)
+    if (scratch && (rc = ensure(ctx, ctx->pair_out, std::max<uint64_t>((uint64_t)splits * rows * n_all, (uint64_t)ctx->sms * kGemmBM * kGemmBN) * sizeof(float), false))) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
     const uint64_t total = (uint64_t)rows * w->k;
     const uint64_t want = (total + 255) / 256;

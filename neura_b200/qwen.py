@@ -128,6 +128,8 @@ class Decoder:
         self.wide = min(int(wide), capacity) if wide else 0
         rt.reserve(most, max(self.vocab, 2 * self.feed_forward, c.hidden), widest_k)   # 2x: a sealed gate|up pair
         rt.reserve_decoder(max(most, self.wide), self.heads, self.key_heads, c.head_width, capacity)
+        if self.wide:
+            rt.reserve_bf16(self.wide, widest_k)
         self._wide_rows = None   # the activation rows of a wide chunk, made at its first use
         self.program: Optional[int] = None
         self._fill_programs: dict = {}   # (plane, rows of a chunk) -> "seen" once, then the chunk's recorded program
@@ -275,29 +277,7 @@ class Decoder:
         held = self._fill_buffers(rows)
         rt.write(held["tokens"], tokens)
         rt.write(held["position"], np.arange(start, start + rows, dtype=np.uint32))
-        # the launches of a chunk depend on (plane, row count) only: tokens and cursors are read from device buffers.
-        # The first chunk of a kind runs as it is issued (it may still size scratch), the second is recorded into a
-        # program, later ones replay it: 700 launches a chunk cost more on the host than on the device otherwise.
-        key = (sequence, rows)
-        state = self._fill_programs.get(key)
-        if isinstance(state, int):
-            rt.run(state)
-            return
-        if state == "seen":
-            rt.capture_begin()
-            try:
-                self._fill_launches(sequence, rows, held)
-            except Exception:
-                try:
-                    rt.program_free(rt.capture_end())
-                except Exception:
-                    pass
-                raise
-            self._fill_programs[key] = rt.capture_end()
-            rt.run(self._fill_programs[key])
-            return
-        self._fill_programs[key] = "seen"
-        self._fill_launches(sequence, rows, held)
+        self._replayed((sequence, rows), lambda: self._fill_launches(sequence, rows, held))
 
     def _fill_launches(self, sequence: int, rows: int, held: dict) -> None:
         """The launches of one prompt chunk of ``rows`` tokens of plane ``sequence`` (tokens and cursors in ``held``)."""
@@ -365,6 +345,36 @@ class Decoder:
         padded[:rows] = np.arange(start, start + rows, dtype=np.uint32)
         padded[rows:] = 0
         rt.write(held["position"], padded)
+        self._replayed(("wide", sequence, rows), lambda: self._wide_launches(sequence, rows, held))
+
+    def _replayed(self, key, launches) -> None:
+        """Runs ``launches`` (a chunk's kernels: tokens and cursors are read from device buffers, so they depend on the
+        key only) as issued the first time (it may still size scratch), records them into a program the second time and
+        replays that from then on: several hundred launches a chunk cost more on the host than on the device."""
+        rt = self.rt
+        state = self._fill_programs.get(key)
+        if isinstance(state, int):
+            rt.run(state)
+            return
+        if state == "seen":
+            rt.capture_begin()
+            try:
+                launches()
+            except Exception:
+                try:   # leave no capture open behind a refused launch
+                    rt.program_free(rt.capture_end())
+                except Exception:
+                    pass
+                raise
+            self._fill_programs[key] = rt.capture_end()
+            rt.run(self._fill_programs[key])
+            return
+        self._fill_programs[key] = "seen"
+        launches()
+
+    def _wide_launches(self, sequence: int, rows: int, held: dict) -> None:
+        """The launches of one wide prompt chunk of ``rows`` tokens of plane ``sequence``."""
+        rt, c, w, n = self.rt, self.config, self.weights, self.norms
         hidden, normed, qkv, attended, mlp = held["hidden"], held["normed"], held["qkv"], held["attended"], held["held"]
         per_plane = self.key_heads * self.capacity * c.head_width * 4
         rt.embed(w["token_embd.weight"], held["tokens"], hidden, rows=rows)

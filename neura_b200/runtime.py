@@ -167,6 +167,10 @@ class Runtime:
     def reserve(self, rows: int, n: int, k: int) -> None:
         _check(self._lib.neura_cuda_reserve(self._ctx, rows, n, k))
 
+    def reserve_bf16(self, rows: int, k: int) -> None:
+        """Sizes what ``linear_bf16`` keeps between its kernels for up to ``rows`` rows of ``k`` activations."""
+        _check(self._lib.neura_cuda_reserve_bf16(self._ctx, rows, k))
+
     def reserve_decoder(self, rows: int, heads: int, key_heads: int, width: int, capacity: int) -> None:
         _check(self._lib.neura_cuda_reserve_decoder(self._ctx, rows, heads, key_heads, width, capacity))
 
