@@ -102,3 +102,23 @@ def test_two_gloo_ranks_reproduce_the_single_device_products(tmp_path):
         row_ok, col_ok = open(tmp_path / f"rank{rank}.txt").read().split()
         assert row_ok == "1", "the all-reduced K shares leave the single-device product"
         assert col_ok == "1", "the gathered row shares are not the single-device product bit for bit"
+
+
+def test_the_decoder_and_the_oracle_stepper_agree_on_what_goes_through_the_wide_path():
+    # the head of a prompt that goes through the tensor-core chunks: all but the last token, in chunks of `wide`, unless
+    # fewer than WIDE_FROM tokens would be left for the last wide chunk (those take the ordinary chunks)
+    import types
+
+    from neura_b200.qwen import Decoder
+    from oracle.decoder import OracleDecoder
+
+    for wide, start in ((0, 64), (512, 64), (128, 64), (8, 5), (100, 64)):
+        one = types.SimpleNamespace(wide=wide, WIDE_FROM=start)
+        for length in (1, 2, 5, 13, 64, 65, 66, 129, 150, 200, 330, 512, 513, 700):
+            got = Decoder.wide_tokens(one, length)
+            assert got == OracleDecoder.wide_tokens(one, length)
+            fed = length - 1
+            if not wide or fed < start:
+                assert got == 0
+            else:
+                assert got in (fed, fed - fed % wide) and (fed - got == 0 or fed - got < start)
