@@ -222,6 +222,12 @@ impl CudaRuntime {
         check(unsafe { sys::neura_cuda_reserve(self.ctx, rows, n, k) });
     }
 
+    /// What `linear_bf16` keeps between its kernels for up to `rows` rows of `k` activations, sized before a program
+    /// is recorded around such products.
+    pub fn reserve_bf16(&self, rows: u32, k: u32) {
+        check(unsafe { sys::neura_cuda_reserve_bf16(self.ctx, rows, k) });
+    }
+
     pub fn reserve_decoder(&self, rows: u32, heads: u32, key_heads: u32, width: u32, capacity: u32) {
         check(unsafe { sys::neura_cuda_reserve_decoder(self.ctx, rows, heads, key_heads, width, capacity) });
     }
