@@ -50,6 +50,10 @@ struct GemmParams {
     // pair = 1: the weight is a sealed gate|up pair (every 32-row unit holds 16 gate rows, then the 16 up rows of the
     // same columns) and the epilogue writes out[r][16 u + i] = chain(silu(gate) * up) for unit u: n_out columns in all
     uint32_t pair, n_out;
+    // tma_out = 1: `out_map` describes the output ([m][n] f32, boxes of 32 x 32, 128-byte swizzled) and the epilogue
+    // hands each 32 x 32 block to a bulk tensor store instead of storing it row by row
+    uint32_t tma_out;
+    CUtensorMap out_map;
 };
 
 // f32 -> bf16 with round-to-nearest-even (crates/neura-precision/src/lib.rs:325-329).
@@ -204,6 +208,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t src_smem) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src_smem)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t gemm_raw[];
     const uint32_t base = (smem_addr(gemm_raw) + 1023u) & ~1023u;   // swizzle atoms want 1024-byte alignment
@@ -285,9 +295,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
             const uint32_t which = (warp >> 2) & 1, lanes = (warp & 3) * 32, columns = (warp >> 3) * (kGemmBN / 2);
             const uint32_t row = m0 + which * 128 + lanes + lane;
             float *turn = reinterpret_cast<float *>(gemm_raw + (base - smem_addr(gemm_raw))) + warp * 32 * 33;
+            const uint32_t stage = base + warp * 8192;   // (the bulk stores' form of `turn`: two blocks of 32 rows x 128 bytes a warp)
+            uint32_t handed = 0;
             for (uint32_t c0 = columns; c0 < columns + kGemmBN / 2; c0 += 32) {
                 uint32_t r[32];
                 tmem_load_32(tmem + (lanes << 16) + which * kGemmBN + c0, r);
+                if (p.tma_out) {
+                    // The block goes to shared memory as the tensor map expects it (row = lane, 16-byte chunk c of row r at
+                    // chunk c ^ (r & 7) of its 128 bytes) and one bulk store writes what of it lies inside the output;
+                    // the warp fills its other buffer meanwhile.
+                    const uint32_t first_row = m0 + which * 128 + lanes;
+                    if (first_row >= p.m || n0 + c0 >= p.n) continue;   // (the same for the whole warp)
+                    if (handed >= 2) {
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        __syncwarp();
+                    }
+                    const uint32_t at = stage + (handed & 1u) * 4096 + lane * 128;
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        float v[4];
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i)
+                            v[i] = (row < p.m && n0 + c0 + 4 * j + i < p.n) ? chained(p.chain, row, n0 + c0 + 4 * j + i, __uint_as_float(r[4 * j + i])) : 0.0f;
+                        sts16(at + ((j ^ (lane & 7)) << 4), __float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) tma_store_2d(&p.out_map, n0 + c0, first_row, stage + (handed & 1u) * 4096);
+                    ++handed;
+                    continue;
+                }
                 // A lane holds 32 consecutive outputs of ONE row; stored as they are, one instruction touches 32
                 // rows (32 sectors), and those stores held the whole kernel back (without them it runs twice as
                 // fast).  So the warp turns its 32 x 32 block through shared memory (the ring is idle by now) and
@@ -326,6 +363,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
                 }
                 __syncwarp();
             }
+            if (p.tma_out && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the shared memory outlives its readers
         } else {
             failed = 1;
         }

@@ -436,6 +436,20 @@ int32_t tensor_map_16bit(CUtensorMap *map, CUtensorMapDataType type, void *base,
     return 0;
 }
 
+// An f32 [rows][cols] output written in boxes of 32 x 32, 128-byte swizzled in shared memory (rows `stride` numbers apart).
+int32_t tensor_map_f32_out(CUtensorMap *map, void *base, uint64_t cols, uint64_t rows, uint64_t stride) {
+    tensor_map_encode_fn encode;
+    int32_t rc;
+    if ((rc = tensor_map_encoder(&encode))) return rc;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride * 4};
+    const cuuint32_t box[2] = {32, 32}, steps[2] = {1, 1};
+    const CUresult made = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (made != CUDA_SUCCESS) return refuse(kBadState, "cuTensorMapEncodeTiled refused the output (%d)", (int)made);
+    return 0;
+}
+
 // ---- the skinny product (skinny_tcgen05.cuh) ---------------------------------------------------------------
 // How many rows one pass of a product carries: up to 16 as digit planes (8 a launch), or, for a Q4_K weight from
 // kSkinnyFrom rows on, up to kSkMaxRows through the skinny kernel, the rows dealt evenly over the passes.
@@ -1164,6 +1178,12 @@ int32_t neura_cuda_linear_bf16(nc_context *ctx, void *stream_, const nc_weight *
     if (pair && !scratch) {
         p.pair = 1;
         p.n_out = w->n;
+    }
+    // a plain product straight into the caller's rows: blocks of the output leave by bulk tensor stores where the
+    // rows allow a tensor map (16-byte aligned, a multiple of 16 bytes apart)
+    if (!pair && !scratch && (uintptr_t)out_dev % 16 == 0 && out_stride % 4 == 0) {
+        if ((rc = tensor_map_f32_out(&p.out_map, out_dev, w->n, rows, out_stride))) return rc;
+        p.tma_out = 1;
     }
     NC_CUDA(launch_dependent(gemm_q4k_tcgen05_kernel, dim3((n_all + kGemmBN - 1) / kGemmBN, (rows + kGemmBM - 1) / kGemmBM, splits),
                              dim3(kGemmThreads), kGemmSmem, stream, p));

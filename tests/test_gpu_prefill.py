@@ -54,6 +54,15 @@ def test_prefill_product_over_several_row_tiles(runtime, oracle, m, n, k):
     check(runtime, oracle, m, n, k)
 
 
+@pytest.mark.parametrize("m,n,k,chain", [(600, 6500, 256, False), (600, 6500, 256, True), (300, 9604, 512, True),
+                                         (600, 6501, 256, True)])
+def test_prefill_product_with_more_tiles_than_half_the_sms(runtime, oracle, m, n, k, chain):
+    # 78 tiles and more: K is not split, the product writes the caller's rows itself, by bulk tensor stores of 32 x 32
+    # blocks where the rows allow a tensor map (ragged last blocks in both directions), row by row where they do not
+    # (rows of 6501 numbers are not a multiple of 16 bytes apart)
+    check(runtime, oracle, m, n, k, chain=chain, residual=chain)
+
+
 def test_prefill_product_applies_the_fused_chain(runtime, oracle):
     check(runtime, oracle, 96, 320, 512, chain=True)
 
