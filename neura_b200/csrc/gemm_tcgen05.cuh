@@ -363,7 +363,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_tcgen05_kernel(const
                 }
                 __syncwarp();
             }
-            if (p.tma_out && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the shared memory outlives its readers
+            if (p.tma_out && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the shared memory outlives its readers
         } else {
             failed = 1;
         }
